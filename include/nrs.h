@@ -1,0 +1,223 @@
+/*
+ * nrs.h — C ABI of libnrs_b200.so, a Blackwell (sm_100a) backend for the
+ * resident-GPU training path of NeuralRs (JackpotMachine777/neuralrs v0.3.0).
+ *
+ * The reference drives its GPU path from Rust through the cudarc crate: one
+ * NVRTC-compiled CUDA-C kernel string per operator, launched by name
+ * (src/cuda/backend.rs:39-42, src/cuda/runtime.rs:24-34).  This header is the
+ * set of entry points a Rust `extern "C"` block would bind instead.  Each
+ * declaration names the reference interface it stands in for.
+ *
+ * Conventions
+ *  - Every pointer named x, w, y, dy, ... is a DEVICE pointer to f32 unless the
+ *    comment says "host".  Tensors are dense, row-major, in the reference's own
+ *    layouts (images NCHW, conv weights [c_out,c_in,kh,kw], Linear weights
+ *    [in,out]).
+ *  - Every call returns an int status (NRS_OK == 0).  The reference panics via
+ *    `.expect(...)` (e.g. src/cuda/runtime.rs:43-45); a binding turns a non-zero
+ *    status into the same panic, with the text from nrs_last_error().
+ *  - All work is enqueued on the context's stream; calls return without
+ *    waiting unless they say otherwise.  A context is bound to one device and is
+ *    not thread-safe, like the reference's single global backend
+ *    (src/cuda/backend.rs:17).
+ *  - There is no CPU fallback: every entry point fails with NRS_ERR_CUDA when no
+ *    usable device is present.
+ *  - Backward entry points take `accumulate`: 0 overwrites the destination
+ *    gradient, non-zero adds to it.  The reference always adds into the parent's
+ *    gradient (src/cuda/runtime.rs:14-18, 67-83); overwrite mode lets the first
+ *    writer skip the zero-fill plus the extra read-modify-write pass.
+ */
+#ifndef NRS_H
+#define NRS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct nrs_ctx nrs_ctx;
+
+enum nrs_status {
+  NRS_OK = 0,
+  NRS_ERR_ARG = 1,         /* null pointer, negative size, bad enum          */
+  NRS_ERR_SHAPE = 2,       /* dimensions inconsistent with each other        */
+  NRS_ERR_ALLOC = 3,       /* device or host allocation failed               */
+  NRS_ERR_CUDA = 4,        /* a CUDA runtime/driver call failed              */
+  NRS_ERR_NCCL = 5,        /* an NCCL call failed or NCCL cannot be loaded   */
+  NRS_ERR_TIMEOUT = 6,     /* a bounded wait ran out                         */
+  NRS_ERR_UNSUPPORTED = 7  /* valid request this build has no kernel for     */
+};
+
+/* Contraction precision.  3xTF32 (default): each f32 operand is split into a
+ * TF32 high part and a TF32 residual and three tensor-core products are summed
+ * in f32 (error ~1e-6 relative).  TF32: one product (error ~1e-3).  FP32: the
+ * CUDA-core FFMA kernels only. */
+enum nrs_math_mode { NRS_MATH_3XTF32 = 0, NRS_MATH_TF32 = 1, NRS_MATH_FP32 = 2 };
+
+/* Activation fused into a contraction's epilogue. */
+enum nrs_act { NRS_ACT_NONE = 0, NRS_ACT_RELU = 1, NRS_ACT_GELU = 2 };
+
+/* ------------------------------------------------------------- lifecycle -- */
+
+/* Create a context on `device` with its own non-blocking stream.
+ * Stands in for the lazily initialised global backend: CudaContext::new(0) +
+ * default_stream (src/cuda/backend.rs:19-32). */
+int nrs_init(int device, nrs_ctx** out);
+int nrs_destroy(nrs_ctx* ctx);
+/* Text of the last failure on this context (never NULL).  With ctx == NULL:
+ * the last failure of a call that had no context (e.g. nrs_init). */
+const char* nrs_last_error(const nrs_ctx* ctx);
+/* Run this context's work on a caller-owned cudaStream_t (e.g. the stream a
+ * host framework is using).  NULL restores the context's own stream. */
+int nrs_set_stream(nrs_ctx* ctx, void* cuda_stream);
+void* nrs_get_stream(nrs_ctx* ctx);
+int nrs_set_math_mode(nrs_ctx* ctx, int mode);
+int nrs_get_math_mode(const nrs_ctx* ctx);
+/* Number of kernels this library has launched on this context so far. */
+uint64_t nrs_launch_count(const nrs_ctx* ctx);
+/* 1 if the tensor-core (tcgen05) kernels were compiled into this build. */
+int nrs_has_tensor_core_path(void);
+
+/* ---------------------------------------------------------------- memory -- */
+/* stream.alloc_zeros / clone_htod / clone_dtoh / memset_zeros / synchronize
+ * (src/cuda/runtime.rs:39-51, 55-62, 108-124).  nrs_alloc draws from a
+ * size-bucketed pool owned by the context, so steady-state training steps call
+ * no cudaMalloc; memory is zero-filled like alloc_zeros only when `zero`. */
+int nrs_alloc(nrs_ctx* ctx, size_t bytes, int zero, void** dptr);
+int nrs_free(nrs_ctx* ctx, void* dptr);
+int nrs_memset_zero(nrs_ctx* ctx, void* dptr, size_t bytes);
+int nrs_h2d(nrs_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+int nrs_d2h(nrs_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes); /* waits */
+int nrs_d2d(nrs_ctx* ctx, void* dst_dev, const void* src_dev, size_t bytes);
+int nrs_sync(nrs_ctx* ctx);
+
+/* ---------------------------------------------------------- contractions -- */
+
+/* C[m,n] = act(op(A).op(B) + bias[n]) + beta*C, all row-major.
+ * trans_a == 0: A is [m,k]; else A is stored [k,m].
+ * trans_b == 0: B is [k,n]; else B is stored [n,k].
+ * bias may be NULL.  beta is 0 or 1.
+ * Replaces mm("matmul_nn"|"matmul_nt"|"matmul_tn") and the bias_add pass
+ * (src/cuda/graph/matmul.rs:269-293, 343-348; src/cuda/graph/add.rs:26-30). */
+int nrs_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int m, int n, int k,
+             const float* a, const float* b, float* c, const float* bias, int act, float beta);
+
+/* Batched C[b] = op(A[b]).op(B[b]) + beta*C[b]; operands densely stacked.
+ * Replaces bmm_forward / bmm_grad_a / bmm_grad_b (src/cuda/graph/bmm.rs:12-56). */
+int nrs_bmm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n, int k,
+            const float* a, const float* b, float* c, float beta);
+
+/* y[N,Co,oh,ow] = act(conv(x[N,Ci,H,W], w[Co,Ci,kh,kw]) + b[Co]); zero padding,
+ * cross-correlation, oh=(H+2p-kh)/s+1.  Replaces conv2d_im2col + matmul_nn +
+ * conv2d_col2out (src/cuda/nn/conv.rs:244-279). */
+int nrs_conv2d_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y,
+                   int n, int ci, int h, int wd, int co, int kh, int kw, int stride, int pad,
+                   int act);
+/* Gradients of nrs_conv2d_fwd (act == NONE) given dy[N,Co,oh,ow]:
+ *   dx[N,Ci,H,W] (skipped when NULL, as for requires_grad == false,
+ *   src/cuda/nn/conv.rs:304), dw[Co,Ci,kh,kw], db[Co]; any may be NULL.
+ * The weight gradient is a split-K contraction reduced in a fixed order, so it
+ * is run-to-run deterministic (the reference's atomicAdd split-K is not,
+ * src/cuda/graph/matmul.rs:207-261).
+ * Replaces out2mm + matmul_tn + col2im + im2col + matmul_nt_splitk + bias_grad
+ * + 3x accumulate (src/cuda/nn/conv.rs:298-324). */
+int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy,
+                   float* dx, float* dw, float* db,
+                   int n, int ci, int h, int wd, int co, int kh, int kw, int stride, int pad,
+                   int accumulate);
+
+/* ------------------------------------------------------------ elementwise -- */
+
+/* out = a + b (src/cuda/graph/add.rs:20-24); out[r,c] = a[r,c] + bias[c]
+ * (:26-30); acc += src (src/cuda/runtime.rs:14-18). */
+int nrs_add(nrs_ctx* ctx, const float* a, const float* b, float* out, size_t n);
+int nrs_bias_add(nrs_ctx* ctx, const float* a, const float* bias, float* out, int rows, int cols);
+int nrs_accumulate(nrs_ctx* ctx, float* acc, const float* src, size_t n);
+/* out[c] (+)= sum_r g[r,c]  — sum_axis0 (src/cuda/reduce.rs:13-20). */
+int nrs_sum_axis0(nrs_ctx* ctx, const float* g, float* out, int rows, int cols, int accumulate);
+/* out[c] (+)= sum_{n,p} g[n,c,p] — conv2d_bias_grad (src/cuda/nn/conv.rs:78-90). */
+int nrs_channel_sum(nrs_ctx* ctx, const float* g, float* out, int n, int c, int plane, int accumulate);
+/* vrelu / relu_grad (src/cuda/graph/relu.rs:17-27): y=max(0,x); dx (+)= g*[x>0]. */
+int nrs_relu_fwd(nrs_ctx* ctx, const float* x, float* y, size_t n);
+int nrs_relu_bwd(nrs_ctx* ctx, const float* x, const float* g, float* dx, size_t n, int accumulate);
+/* vgelu / gelu_grad (src/cuda/graph/gelu.rs:12-32), tanh approximation. */
+int nrs_gelu_fwd(nrs_ctx* ctx, const float* x, float* y, size_t n);
+int nrs_gelu_bwd(nrs_ctx* ctx, const float* x, const float* g, float* dx, size_t n, int accumulate);
+/* vscale / scale_grad (src/cuda/graph/scale.rs:11-19): y = x*s ; dx (+)= g*s. */
+int nrs_scale(nrs_ctx* ctx, const float* x, float* y, size_t n, float s, int accumulate);
+/* transpose2d (src/cuda/graph/transpose.rs:12-23): batched swap of the last two dims;
+ * y[b,j,i] (+)= x[b,i,j]. */
+int nrs_transpose(nrs_ctx* ctx, const float* x, float* y, int batch, int rows, int cols, int accumulate);
+/* slice_fwd / slice_bwd (src/cuda/graph/slice_cols.rs:12-29):
+ * fwd: y[r,c] = x[r,c0+c] for c in [0,c1-c0); bwd: dx[r,c0+c] (+)= g[r,c]. */
+int nrs_slice_cols_fwd(nrs_ctx* ctx, const float* x, float* y, int rows, int total, int c0, int c1);
+int nrs_slice_cols_bwd(nrs_ctx* ctx, const float* g, float* dx, int rows, int total, int c0, int c1, int accumulate);
+/* concat_write / concat_read (src/cuda/graph/concat_cols.rs:12-29). */
+int nrs_concat_write(nrs_ctx* ctx, const float* part, float* out, int rows, int total, int off, int pw);
+int nrs_concat_read(nrs_ctx* ctx, const float* g, float* dpart, int rows, int total, int off, int pw, int accumulate);
+
+/* ---------------------------------------------------------------- pooling -- */
+
+/* maxpool_forward / maxpool_backward (src/cuda/nn/maxpool.rs:19-55): k x k
+ * windows, stride s, no padding, first maximum wins; argmax[N,C,oh,ow] holds
+ * the flat input index (int32) and may be NULL in the forward call.
+ * Backward: dx (+)= scatter of g through argmax.  With accumulate == 0 dx is
+ * fully overwritten (non-winners get 0).  For k == s the backward is a
+ * gather (no atomics, deterministic); otherwise dx is zeroed/kept and an
+ * atomicAdd scatter runs, as in the reference. */
+int nrs_maxpool_fwd(nrs_ctx* ctx, const float* x, float* y, int32_t* argmax,
+                    int n, int c, int h, int w, int k, int stride);
+int nrs_maxpool_bwd(nrs_ctx* ctx, const float* g, const int32_t* argmax, float* dx,
+                    int n, int c, int h, int w, int k, int stride, int accumulate);
+
+/* --------------------------------------------------- layernorm / softmax -- */
+
+/* ln_forward (src/cuda/nn/normalization.rs:14-41): per row of `f` features,
+ * biased variance, eps inside the sqrt; saves xhat[rows,f] and istd[rows]. */
+int nrs_layernorm_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const float* beta,
+                      float* y, float* xhat, float* istd, int rows, int f, float eps);
+/* ln_dx + ln_reduce (src/cuda/nn/normalization.rs:43-78): dx (+)=, dgamma (+)=,
+ * dbeta (+)=; dx may be NULL. */
+int nrs_layernorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd,
+                      const float* gamma, float* dx, float* dgamma, float* dbeta,
+                      int rows, int f, int accumulate_dx, int accumulate_params);
+/* softmax_forward / softmax_backward (src/cuda/graph/softmax.rs:12-35).  The
+ * backward takes the forward OUTPUT y: dx (+)= y*(g - sum(y*g)). */
+int nrs_softmax_fwd(nrs_ctx* ctx, const float* x, float* y, int rows, int width);
+int nrs_softmax_bwd(nrs_ctx* ctx, const float* y, const float* g, float* dx, int rows, int width, int accumulate);
+
+/* ------------------------------------------------------------------- loss -- */
+
+/* ce_forward (src/cuda/loss/cross_entropy.rs:18-36, 74-98): writes
+ * loss_dev[0] = sum_b(-sum_c t*log_softmax(x)) / divisor on the device (no
+ * host round trip).  row_loss[batch] is optional scratch-free output of the
+ * per-row terms.  The reference divides by the row count; data-parallel shards
+ * pass the global batch. */
+int nrs_ce_fwd(nrs_ctx* ctx, const float* logits, const float* target, float* loss_dev,
+               float* row_loss, int batch, int classes, int divisor);
+/* ce_backward (src/cuda/loss/cross_entropy.rs:38-57, 107-128): overwrites
+ * grad = (softmax(x) - t) / divisor. */
+int nrs_ce_bwd(nrs_ctx* ctx, const float* logits, const float* target, float* grad,
+               int batch, int classes, int divisor);
+/* Both in one pass over the logits. */
+int nrs_ce_fwd_bwd(nrs_ctx* ctx, const float* logits, const float* target, float* loss_dev,
+                   float* grad, int batch, int classes, int divisor);
+
+/* -------------------------------------------------------------- optimizer -- */
+
+/* One AdamW update over flat vectors of n elements, as the `adamw` kernel
+ * (src/cuda/optim/adamw.rs:19-35) but one launch for the whole model:
+ *   m = b1*m + (1-b1)*g ; v = b2*v + (1-b2)*g*g ;
+ *   p = p - lr*(m/bc1)/(sqrt(v/bc2)+eps) - lr*wd*p        (pre-update p)
+ * with g = grad_scale*grad.  bc1 = 1-b1^(t+1), bc2 = 1-b2^(t+1) are computed by
+ * the caller exactly as the reference does on the host (:77-78). */
+int nrs_adamw_step(nrs_ctx* ctx, float* p, const float* grad, float* m, float* v, size_t n,
+                   float lr, float beta1, float beta2, float eps, float wd,
+                   float bc1, float bc2, float grad_scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NRS_H */

@@ -1,0 +1,100 @@
+/*
+ * nrs_graph.h — node-level C ABI of libnrs_b200.so.
+ *
+ * The reference's GPU path is used through Rust functions over graph nodes
+ * (`Rc<RefCell<Node>>`): cuda::runtime, cuda::graph, cuda::nn, cuda::loss,
+ * cuda::optim.  This header exports the same operations over opaque node
+ * handles so a caller without a C++ compiler (a Rust shim, a ctypes test) can
+ * run a reference-style program: build nodes, move them to the GPU, call
+ * operators that return new nodes, seed a gradient, run backward_graph, step an
+ * optimizer.  Each entry names the reference function it mirrors.
+ *
+ * Status codes, error text and stream semantics are those of nrs.h.  Handles
+ * are reference counted: every `*_out` handle must be passed to
+ * nrs_node_release once (releasing a node does not free tensors that other
+ * live nodes still use as parents).
+ */
+#ifndef NRS_GRAPH_H
+#define NRS_GRAPH_H
+
+#include "nrs.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct nrs_node nrs_node;
+typedef struct nrs_adamw nrs_adamw;
+typedef struct nrs_trainer nrs_trainer;
+
+/* Node::new(data, shape) — src/autograd/node.rs:60-74.  host_data: host f32,
+ * may be NULL for a node that only receives device data later. */
+int nrs_node_new(nrs_ctx* ctx, const float* host_data, const int64_t* shape, int ndim, nrs_node** out);
+int nrs_node_release(nrs_node* n);
+int nrs_node_ndim(const nrs_node* n);
+int nrs_node_shape(const nrs_node* n, int64_t* shape_out, int capacity);
+int64_t nrs_node_len(const nrs_node* n);
+/* Node.requires_grad — src/autograd/node.rs:33-36,45. */
+int nrs_node_set_requires_grad(nrs_node* n, int flag);
+/* Device pointers of a resident node (NULL when absent). */
+float* nrs_node_data_ptr(nrs_node* n);
+float* nrs_node_grad_ptr(nrs_node* n);
+
+/* cuda::runtime — src/cuda/runtime.rs:39-124. */
+int nrs_to_cuda(nrs_node* n);
+int nrs_to_host(nrs_node* n, float* host_out);
+int nrs_set_grad(nrs_node* n, const float* host_grad);
+int nrs_read_grad(nrs_node* n, float* host_out);
+int nrs_zero_grad(nrs_node* const* params, int count);
+/* Moves resident parameters into one contiguous block (values kept) so the
+ * optimizer runs as one launch.  No reference counterpart. */
+int nrs_flatten_params(nrs_node* const* params, int count);
+
+/* cuda::graph — src/cuda/graph/{matmul,add,relu,gelu,reshape,softmax,bmm,
+ * transpose,scale,slice_cols,concat_cols}.rs */
+int nrs_op_matmul(nrs_node* a, nrs_node* b, nrs_node** out);
+int nrs_op_add(nrs_node* a, nrs_node* b, nrs_node** out);
+int nrs_op_relu(nrs_node* x, nrs_node** out);
+int nrs_op_gelu(nrs_node* x, nrs_node** out);
+int nrs_op_reshape(nrs_node* x, const int64_t* shape, int ndim, nrs_node** out);
+int nrs_op_softmax(nrs_node* x, nrs_node** out);
+int nrs_op_bmm(nrs_node* a, nrs_node* b, nrs_node** out);
+int nrs_op_transpose(nrs_node* x, nrs_node** out);
+int nrs_op_scale(nrs_node* x, float s, nrs_node** out);
+int nrs_op_slice_cols(nrs_node* x, int64_t col_start, int64_t col_end, nrs_node** out);
+int nrs_op_concat_cols(nrs_node* const* parts, int count, nrs_node** out);
+
+/* cuda::nn — src/cuda/nn/{conv,maxpool,flatten,normalization,linear}.rs */
+int nrs_op_conv2d(nrs_node* input, nrs_node* weight, nrs_node* bias, int64_t stride, int64_t pad, nrs_node** out);
+int nrs_op_maxpool2d(nrs_node* input, int64_t kernel, int64_t stride, nrs_node** out);
+int nrs_op_flatten(nrs_node* x, nrs_node** out);
+int nrs_op_layernorm(nrs_node* x, nrs_node* gamma, nrs_node* beta, float eps, nrs_node** out);
+/* Fused x@W+b -> activation and conv+bias -> activation (enum nrs_act). */
+int nrs_op_linear_act(nrs_node* x, nrs_node* w, nrs_node* b, int act, nrs_node** out);
+int nrs_op_conv2d_act(nrs_node* input, nrs_node* weight, nrs_node* bias, int64_t stride, int64_t pad, int act,
+                      nrs_node** out);
+
+/* cuda::loss — src/cuda/loss/cross_entropy.rs:74-128. */
+int nrs_cross_entropy(nrs_node* pred, nrs_node* target, float* loss_out);
+int nrs_cross_entropy_backward(nrs_node* pred, nrs_node* target);
+
+/* autograd::node::backward_graph — src/autograd/node.rs:113-126. */
+int nrs_backward_graph(nrs_node* root);
+
+/* cuda::optim::AdamW — src/cuda/optim/adamw.rs:54-143. */
+int nrs_adamw_new(nrs_ctx* ctx, float lr, float beta1, float beta2, float eps, float weight_decay, nrs_adamw** out);
+int nrs_adamw_free(nrs_adamw* opt);
+int nrs_adamw_step_nodes(nrs_adamw* opt, nrs_node* const* params, int count);
+int64_t nrs_adamw_t(const nrs_adamw* opt);
+/* export_state: number of moment tensors (2 x parameters, 0 before the first
+ * step), the length of tensor i, and a copy of tensor i to the host. */
+int nrs_adamw_state_count(const nrs_adamw* opt);
+int64_t nrs_adamw_state_len(const nrs_adamw* opt, int i);
+int nrs_adamw_state_get(const nrs_adamw* opt, int i, float* host_out);
+/* import_state(t, moments): `lens[i]` floats at `moments[i]`, all m's then all v's. */
+int nrs_adamw_import_state(nrs_adamw* opt, int64_t t, const float* const* moments, const int64_t* lens, int count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NRS_GRAPH_H */

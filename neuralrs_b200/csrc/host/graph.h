@@ -1,0 +1,145 @@
+// Host-side mirror of the reference's resident-GPU operator API.
+//
+// The reference is a Rust crate whose GPU path is a set of free functions over
+// `Rc<RefCell<Node>>` (src/cuda/{runtime,graph,nn,loss,optim}); the graph engine
+// is shared with the CPU path (src/autograd/node.rs:38-151).  No Rust toolchain
+// exists in the build image, so this C++ layer plays the role the Rust side
+// would: the same Node (data/grad buffers, parents, backward closure,
+// requires_grad), the same function names and argument meaning, the same
+// backward_graph ordering and += gradient semantics — all on top of the C ABI
+// in nrs.h, and itself exported through the node-level C ABI in nrs_graph.h so
+// tests can drive it without a compiler.
+#pragma once
+
+#include <functional>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "nrs.h"
+
+namespace nrs {
+
+struct Error : std::runtime_error {
+  int code;
+  Error(int c, const std::string& m) : std::runtime_error(m), code(c) {}
+};
+
+// Throws nrs::Error carrying nrs_last_error() when a C-ABI call fails.
+void check(nrs_ctx* ctx, int status);
+
+struct FlatStore;
+
+// Node of the define-by-run graph (src/autograd/node.rs:38-53).
+struct Node {
+  nrs_ctx* ctx = nullptr;
+  std::vector<size_t> shape;
+  std::vector<float> host;          // `data` before to_cuda()
+  float* data = nullptr;            // GpuBuffers.data
+  float* grad = nullptr;            // GpuBuffers.grad, allocated on first use
+  // false: the gradient is logically all-zero and the first writer overwrites
+  // the buffer instead of adding to it (the reference zero-fills at creation
+  // and always adds; both give the same values).
+  bool grad_valid = false;
+  bool requires_grad = true;
+  bool owns_data = true, owns_grad = true;
+  std::shared_ptr<Node> view_of;     // reshape/flatten alias their parent
+  std::shared_ptr<FlatStore> flat;   // keeps a flat parameter block alive
+  std::vector<std::shared_ptr<Node>> parents;
+  std::function<void()> backward_fn;
+  std::vector<void*> saved;          // argmax, xhat, ... freed with the node
+
+  size_t len() const;
+  bool on_gpu() const { return data != nullptr; }
+  ~Node();
+};
+using NodeP = std::shared_ptr<Node>;
+
+// Contiguous home for a model's parameters: one block each for values and
+// gradients, so the optimizer is one launch and a gradient all-reduce is one
+// call per bucket.  Tensors are padded to 4 floats (16-byte alignment).
+struct FlatStore {
+  nrs_ctx* ctx = nullptr;
+  float* data = nullptr;
+  float* grad = nullptr;
+  size_t total = 0;                  // floats, padding included
+  std::vector<size_t> offset, length;
+  ~FlatStore();
+};
+
+NodeP node_new(nrs_ctx* ctx, const float* host, const std::vector<size_t>& shape);
+
+namespace cuda {
+
+// ---- runtime (src/cuda/runtime.rs:39-124)
+void to_cuda(const NodeP& n);
+std::vector<float> to_host(const NodeP& n);
+void set_grad(const NodeP& n, const float* host);
+std::vector<float> read_grad(const NodeP& n);
+void zero_grad(const std::vector<NodeP>& params);
+void synchronize(nrs_ctx* ctx);
+// Re-homes resident parameters into one FlatStore (values are preserved).
+std::shared_ptr<FlatStore> flatten_params(const std::vector<NodeP>& params);
+
+// ---- graph ops (src/cuda/graph/*.rs)
+NodeP matmul(const NodeP& a, const NodeP& b);
+NodeP add(const NodeP& a, const NodeP& b);   // same shape, or [r,c] + [c]
+NodeP relu(const NodeP& x);
+NodeP gelu(const NodeP& x);
+NodeP reshape(const NodeP& x, const std::vector<size_t>& shape);
+NodeP softmax(const NodeP& x);
+NodeP bmm(const NodeP& a, const NodeP& b);
+NodeP transpose(const NodeP& x);
+NodeP scale(const NodeP& x, float s);
+NodeP slice_cols(const NodeP& x, size_t c0, size_t c1);
+NodeP concat_cols(const std::vector<NodeP>& parts);
+
+// ---- nn (src/cuda/nn/*.rs)
+NodeP conv2d(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size_t pad);
+NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride);
+NodeP flatten(const NodeP& x);
+NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps);
+// Fused variants with no counterpart op in the reference: one kernel for
+// x@W + b followed by an activation, and conv + bias + activation.  Backward is
+// the composition of the unfused backward passes.
+NodeP linear_act(const NodeP& x, const NodeP& w, const NodeP& b, int act);
+NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size_t pad, int act);
+
+// ---- loss (src/cuda/loss/cross_entropy.rs:74-128)
+float cross_entropy(const NodeP& pred, const NodeP& target);
+void cross_entropy_backward(const NodeP& pred, const NodeP& target);
+// Both at once; the loss stays on the device (read it later with d2h) and the
+// mean is taken over `divisor` rows (the global batch under data parallelism).
+void cross_entropy_fused(const NodeP& pred, const NodeP& target, float* loss_dev, int divisor);
+
+// ---- optim (src/cuda/optim/adamw.rs:43-144)
+struct AdamW {
+  float lr, beta1, beta2, epsilon, weight_decay;
+  size_t t = 0;
+  float grad_scale = 1.0f;           // 1/world for averaged all-reduced gradients
+  AdamW(nrs_ctx* ctx, float lr, float b1, float b2, float eps, float wd);
+  ~AdamW();
+  void step(const std::vector<NodeP>& params);
+  // (t, all first moments in parameter order, then all second moments).
+  std::vector<std::vector<float>> export_state(size_t* t_out) const;
+  void import_state(size_t t, const std::vector<std::vector<float>>& moments);
+
+ private:
+  nrs_ctx* ctx_;
+  std::vector<float*> m_, v_;        // per-parameter views
+  std::vector<size_t> len_;
+  float* flat_m_ = nullptr;          // set when the parameters share a FlatStore
+  float* flat_v_ = nullptr;
+  size_t flat_total_ = 0;
+  bool owns_each_ = false;
+  void ensure_state(const std::vector<NodeP>& params);
+  void release();
+};
+
+}  // namespace cuda
+
+// Topological backward pass (src/autograd/node.rs:113-151).
+void backward_graph(const NodeP& root);
+
+}  // namespace nrs

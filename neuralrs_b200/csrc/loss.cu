@@ -1,0 +1,122 @@
+// Cross-entropy on raw logits with dense one-hot (f32) targets.
+// Reference: ce_forward / ce_backward (src/cuda/loss/cross_entropy.rs:18-57),
+// host side :74-128; CPU semantics src/nn/loss.rs:50-107.  The reference runs
+// one thread per row and sums the per-row losses on the host after a blocking
+// device-to-host copy; here a warp owns a row (shuffle reductions, the row is
+// re-read from L1), forward and backward share one pass, and the batch mean is
+// reduced on the device in a fixed order.
+#include "nrs_internal.h"
+
+namespace {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One warp per row.  row_loss (optional) gets -sum_c t*(x - lse); grad (optional)
+// gets (softmax - t) * inv_div.
+__global__ void __launch_bounds__(256)
+ce_rows_kernel(const float* __restrict__ logits, const float* __restrict__ target,
+               float* __restrict__ row_loss, float* __restrict__ grad, int batch, int classes, float inv_div) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5); b < batch; b += gridDim.x * warps_per_block) {
+    const float* row = logits + (size_t)b * classes;
+    const float* trow = target + (size_t)b * classes;
+    float mx = -INFINITY;
+    for (int c = lane; c < classes; c += 32) mx = fmaxf(mx, row[c]);
+    mx = warp_max(mx);
+    float se = 0.0f;
+    for (int c = lane; c < classes; c += 32) se += expf(row[c] - mx);
+    se = warp_sum(se);
+    const float lse = logf(se) + mx;
+    float loss = 0.0f;
+    for (int c = lane; c < classes; c += 32) {
+      const float xv = row[c], tv = trow[c];
+      loss += -tv * (xv - lse);
+      if (grad) grad[(size_t)b * classes + c] = (expf(xv - mx) / se - tv) * inv_div;
+    }
+    if (row_loss) {
+      loss = warp_sum(loss);
+      if (lane == 0) row_loss[b] = loss;
+    }
+  }
+}
+
+// loss_dev[0] = (sum_b row_loss[b]) * inv_div, one block, fixed summation tree.
+__global__ void __launch_bounds__(1024)
+ce_mean_kernel(const float* __restrict__ row_loss, float* __restrict__ loss_dev, int batch, float inv_div) {
+  __shared__ float sm[32];
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < batch; i += blockDim.x) s += row_loss[i];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? sm[threadIdx.x] : 0.0f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) loss_dev[0] = t * inv_div;
+  }
+}
+
+int run_ce(nrs_ctx* ctx, const char* who, const float* logits, const float* target, float* loss_dev,
+           float* row_loss, float* grad, int batch, int classes, int divisor) {
+  NRS_REQUIRE(ctx, batch >= 0 && classes > 0, NRS_ERR_SHAPE, "%s: bad shape [%d,%d]", who, batch, classes);
+  NRS_REQUIRE(ctx, divisor > 0, NRS_ERR_ARG, "%s: divisor must be positive", who);
+  if (batch == 0) {
+    if (loss_dev) NRS_CUDA(ctx, cudaMemsetAsync(loss_dev, 0, sizeof(float), ctx->stream));
+    return NRS_OK;
+  }
+  NRS_REQUIRE(ctx, logits && target, NRS_ERR_ARG, "%s: null tensor", who);
+  float* rl = row_loss;
+  if (loss_dev && !rl) {
+    void* ws = nullptr;
+    const int st = nrs_workspace(ctx, (size_t)batch * sizeof(float), &ws);
+    if (st != NRS_OK) return st;
+    rl = (float*)ws;
+  }
+  const float inv_div = 1.0f / (float)divisor;
+  int blocks = (batch + 7) / 8;
+  if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+  ce_rows_kernel<<<blocks, 256, 0, ctx->stream>>>(logits, target, rl, grad, batch, classes, inv_div);
+  NRS_LAUNCHED(ctx);
+  if (loss_dev) {
+    ce_mean_kernel<<<1, 1024, 0, ctx->stream>>>(rl, loss_dev, batch, inv_div);
+    NRS_LAUNCHED(ctx);
+  }
+  return NRS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nrs_ce_fwd(nrs_ctx* ctx, const float* logits, const float* target, float* loss_dev, float* row_loss,
+               int batch, int classes, int divisor) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, loss_dev || row_loss, NRS_ERR_ARG, "nrs_ce_fwd: no output requested");
+  return run_ce(ctx, "nrs_ce_fwd", logits, target, loss_dev, row_loss, nullptr, batch, classes, divisor);
+}
+
+int nrs_ce_bwd(nrs_ctx* ctx, const float* logits, const float* target, float* grad, int batch, int classes,
+               int divisor) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, grad || batch == 0, NRS_ERR_ARG, "nrs_ce_bwd: null grad");
+  return run_ce(ctx, "nrs_ce_bwd", logits, target, nullptr, nullptr, grad, batch, classes, divisor);
+}
+
+int nrs_ce_fwd_bwd(nrs_ctx* ctx, const float* logits, const float* target, float* loss_dev, float* grad,
+                   int batch, int classes, int divisor) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, loss_dev && (grad || batch == 0), NRS_ERR_ARG, "nrs_ce_fwd_bwd: null output");
+  return run_ce(ctx, "nrs_ce_fwd_bwd", logits, target, loss_dev, nullptr, grad, batch, classes, divisor);
+}
+
+}  // extern "C"

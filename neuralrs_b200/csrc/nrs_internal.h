@@ -1,0 +1,75 @@
+// Internal declarations shared by the translation units of libnrs_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "nrs.h"
+
+// Size-bucketed device memory pool.  Blocks are handed back to a free list
+// keyed by their rounded size instead of being cudaFree'd, so a training loop
+// whose shapes repeat stops calling cudaMalloc after its first step.  All work
+// runs on one stream, so reuse right after release is ordered correctly.
+struct NrsPool {
+  std::multimap<size_t, void*> free_blocks;   // rounded size -> block
+  std::map<void*, size_t> live;               // block -> rounded size
+  size_t bytes_reserved = 0;
+  static size_t round_up(size_t bytes) {
+    const size_t g = bytes <= (1u << 20) ? 512 : (size_t)1 << 16;
+    return (bytes + g - 1) / g * g;
+  }
+};
+
+struct nrs_ctx {
+  int device = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  int math_mode = NRS_MATH_3XTF32;
+  int sm_count = 148;
+  uint64_t launches = 0;
+  std::string err;
+  NrsPool pool;
+  // Grow-only scratch for split-K partial sums and operand staging.
+  void* workspace = nullptr;
+  size_t workspace_bytes = 0;
+};
+
+int nrs_fail(nrs_ctx* ctx, int code, const char* fmt, ...);
+int nrs_workspace(nrs_ctx* ctx, size_t bytes, void** out);
+
+#define NRS_REQUIRE_CTX(ctx) \
+  do { if (!(ctx)) return nrs_fail(nullptr, NRS_ERR_ARG, "%s: null context", __func__); } while (0)
+#define NRS_REQUIRE(ctx, cond, code, ...) \
+  do { if (!(cond)) return nrs_fail((ctx), (code), __VA_ARGS__); } while (0)
+#define NRS_CUDA(ctx, call)                                                              \
+  do {                                                                                   \
+    cudaError_t e__ = (call);                                                            \
+    if (e__ != cudaSuccess)                                                              \
+      return nrs_fail((ctx), NRS_ERR_CUDA, "%s: %s failed: %s", __func__, #call,         \
+                      cudaGetErrorString(e__));                                          \
+  } while (0)
+// After a kernel launch: count it and surface launch-configuration errors.
+#define NRS_LAUNCHED(ctx)                                                                \
+  do {                                                                                   \
+    (ctx)->launches++;                                                                   \
+    cudaError_t e__ = cudaGetLastError();                                                \
+    if (e__ != cudaSuccess)                                                              \
+      return nrs_fail((ctx), NRS_ERR_CUDA, "%s: kernel launch failed: %s", __func__,     \
+                      cudaGetErrorString(e__));                                          \
+  } while (0)
+
+static inline unsigned nrs_blocks(size_t work, unsigned per_block) {
+  return (unsigned)((work + per_block - 1) / per_block);
+}
+
+// Tensor-core contraction entry points (tc_gemm.cu / tc_conv.cu).  Each returns
+// NRS_ERR_UNSUPPORTED (without setting an error text) when the shape is outside
+// what the tcgen05 kernels cover, and the caller then runs the FFMA kernels.
+int nrs_tc_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n, int k,
+                const float* a, const float* b, float* c, const float* bias, int act, float beta);

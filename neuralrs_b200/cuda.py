@@ -1,0 +1,325 @@
+"""ctypes mirror of the reference's ``neuralrs::cuda`` API over the node-level C ABI.
+
+Names and argument order follow the Rust functions so a test can be read next to
+the reference's own (``tests/cuda_*.rs``):
+
+    gi = Node.new(input, [n, c_in, h, w]); runtime.to_cuda(gi)
+    gout = nn.conv2d(gi, gw, gb, stride, pad)
+    runtime.set_grad(gout, seed); backward_graph(gout)
+    g = runtime.read_grad(gi)
+
+All arithmetic happens in libnrs_b200.so on the GPU; this file only marshals
+numpy arrays and handles.  Reference: src/cuda/{runtime,graph,nn,loss,optim}.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import VP, check
+
+_default_ctx = None
+
+
+class Context:
+    """One device context + stream (the reference's global backend, src/cuda/backend.rs:17-32)."""
+
+    def __init__(self, device: int = 0):
+        self._l = _lib.lib()
+        h = VP()
+        st = self._l.nrs_init(device, C.byref(h))
+        if st != 0:
+            raise _lib.NrsError(st, (self._l.nrs_last_error(None) or b"").decode())
+        self.h = h
+        self.device = device
+
+    def set_math_mode(self, mode: int):
+        check(self.h, self._l.nrs_set_math_mode(self.h, mode))
+
+    def set_stream(self, stream_ptr: int | None):
+        check(self.h, self._l.nrs_set_stream(self.h, VP(stream_ptr or 0)))
+
+    def sync(self):
+        check(self.h, self._l.nrs_sync(self.h))
+
+    def launch_count(self) -> int:
+        return int(self._l.nrs_launch_count(self.h))
+
+    def close(self):
+        if self.h:
+            self._l.nrs_destroy(self.h)
+            self.h = None
+
+
+def default_context() -> Context:
+    global _default_ctx
+    if _default_ctx is None:
+        _default_ctx = Context(0)
+    return _default_ctx
+
+
+def set_default_context(ctx: Context | None):
+    global _default_ctx
+    _default_ctx = ctx
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+
+
+def _ptr(a: np.ndarray) -> VP:
+    return VP(a.ctypes.data)
+
+
+class Node:
+    """Handle to a graph node (src/autograd/node.rs:38-53)."""
+
+    def __init__(self, handle: VP, ctx: Context):
+        self.h = handle
+        self.ctx = ctx
+
+    @staticmethod
+    def new(data, shape, ctx: Context | None = None) -> "Node":
+        ctx = ctx or default_context()
+        shape = [int(s) for s in shape]
+        arr = _f32(data).reshape(-1)
+        if arr.size != int(np.prod(shape, dtype=np.int64)) and arr.size != 0:
+            raise ValueError("data does not match shape")
+        sh = (C.c_int64 * len(shape))(*shape)
+        h = VP()
+        check(ctx.h, ctx._l.nrs_node_new(ctx.h, _ptr(arr) if arr.size else None, sh, len(shape), C.byref(h)))
+        return Node(h, ctx)
+
+    @property
+    def shape(self) -> list[int]:
+        l = self.ctx._l
+        nd = l.nrs_node_ndim(self.h)
+        buf = (C.c_int64 * max(nd, 1))()
+        check(self.ctx.h, l.nrs_node_shape(self.h, buf, nd))
+        return [int(buf[i]) for i in range(nd)]
+
+    def __len__(self) -> int:
+        return int(self.ctx._l.nrs_node_len(self.h))
+
+    @property
+    def requires_grad(self):
+        raise AttributeError("write-only")
+
+    @requires_grad.setter
+    def requires_grad(self, flag: bool):
+        check(self.ctx.h, self.ctx._l.nrs_node_set_requires_grad(self.h, int(bool(flag))))
+
+    def data_ptr(self) -> int:
+        return int(self.ctx._l.nrs_node_data_ptr(self.h) or 0)
+
+    def grad_ptr(self) -> int:
+        return int(self.ctx._l.nrs_node_grad_ptr(self.h) or 0)
+
+    def __del__(self):
+        try:
+            if self.h and self.ctx.h:
+                self.ctx._l.nrs_node_release(self.h)
+        except Exception:
+            pass
+        self.h = None
+
+
+def _out(ctx: Context, st: int, h: VP) -> Node:
+    check(ctx.h, st)
+    return Node(h, ctx)
+
+
+def _handles(nodes):
+    arr = (VP * len(nodes))(*[n.h for n in nodes])
+    return arr
+
+
+class runtime:
+    """src/cuda/runtime.rs:39-124."""
+
+    @staticmethod
+    def to_cuda(n: Node):
+        check(n.ctx.h, n.ctx._l.nrs_to_cuda(n.h))
+
+    @staticmethod
+    def to_host(n: Node) -> np.ndarray:
+        out = np.empty(len(n), dtype=np.float32)
+        check(n.ctx.h, n.ctx._l.nrs_to_host(n.h, _ptr(out)))
+        return out
+
+    @staticmethod
+    def set_grad(n: Node, grad):
+        g = _f32(grad).reshape(-1)
+        if g.size != len(n):
+            raise ValueError("gradient size mismatch")
+        check(n.ctx.h, n.ctx._l.nrs_set_grad(n.h, _ptr(g)))
+
+    @staticmethod
+    def read_grad(n: Node) -> np.ndarray:
+        out = np.empty(len(n), dtype=np.float32)
+        check(n.ctx.h, n.ctx._l.nrs_read_grad(n.h, _ptr(out)))
+        return out
+
+    @staticmethod
+    def zero_grad(params):
+        if params:
+            check(params[0].ctx.h, params[0].ctx._l.nrs_zero_grad(_handles(params), len(params)))
+
+    @staticmethod
+    def flatten_params(params):
+        check(params[0].ctx.h, params[0].ctx._l.nrs_flatten_params(_handles(params), len(params)))
+
+    @staticmethod
+    def synchronize(ctx: Context | None = None):
+        (ctx or default_context()).sync()
+
+
+def _unary(name):
+    def f(x: Node) -> Node:
+        h = VP()
+        return _out(x.ctx, getattr(x.ctx._l, name)(x.h, C.byref(h)), h)
+    return staticmethod(f)
+
+
+def _binary(name):
+    def f(a: Node, b: Node) -> Node:
+        h = VP()
+        return _out(a.ctx, getattr(a.ctx._l, name)(a.h, b.h, C.byref(h)), h)
+    return staticmethod(f)
+
+
+class graph:
+    """src/cuda/graph/*.rs."""
+    matmul = _binary("nrs_op_matmul")
+    add = _binary("nrs_op_add")
+    bmm = _binary("nrs_op_bmm")
+    relu = _unary("nrs_op_relu")
+    gelu = _unary("nrs_op_gelu")
+    softmax = _unary("nrs_op_softmax")
+    transpose = _unary("nrs_op_transpose")
+
+    @staticmethod
+    def reshape(x: Node, shape) -> Node:
+        sh = (C.c_int64 * len(shape))(*[int(s) for s in shape])
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_reshape(x.h, sh, len(shape), C.byref(h)), h)
+
+    @staticmethod
+    def scale(x: Node, s: float) -> Node:
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_scale(x.h, C.c_float(s), C.byref(h)), h)
+
+    @staticmethod
+    def slice_cols(x: Node, c0: int, c1: int) -> Node:
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_slice_cols(x.h, int(c0), int(c1), C.byref(h)), h)
+
+    @staticmethod
+    def concat_cols(parts) -> Node:
+        h = VP()
+        return _out(parts[0].ctx, parts[0].ctx._l.nrs_op_concat_cols(_handles(parts), len(parts), C.byref(h)), h)
+
+
+class nn:
+    """src/cuda/nn/{conv,maxpool,flatten,normalization,linear}.rs."""
+    flatten = _unary("nrs_op_flatten")
+
+    @staticmethod
+    def conv2d(x: Node, w: Node, b: Node, stride: int, pad: int) -> Node:
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_conv2d(x.h, w.h, b.h, int(stride), int(pad), C.byref(h)), h)
+
+    @staticmethod
+    def conv2d_act(x: Node, w: Node, b: Node, stride: int, pad: int, act: int) -> Node:
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_conv2d_act(x.h, w.h, b.h, int(stride), int(pad), int(act), C.byref(h)), h)
+
+    @staticmethod
+    def maxpool2d(x: Node, kernel: int, stride: int) -> Node:
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_maxpool2d(x.h, int(kernel), int(stride), C.byref(h)), h)
+
+    @staticmethod
+    def layernorm(x: Node, gamma: Node, beta: Node, eps: float) -> Node:
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_layernorm(x.h, gamma.h, beta.h, C.c_float(eps), C.byref(h)), h)
+
+    @staticmethod
+    def linear_act(x: Node, w: Node, b: Node, act: int) -> Node:
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_linear_act(x.h, w.h, b.h, int(act), C.byref(h)), h)
+
+    class Linear:
+        """weights [in, out], bias [out]; forward = add(matmul(x, W), b) (src/cuda/nn/linear.rs:11-26)."""
+
+        def __init__(self, weights: Node, bias: Node):
+            self.weights, self.bias = weights, bias
+
+        def forward(self, x: Node) -> Node:
+            return graph.add(graph.matmul(x, self.weights), self.bias)
+
+
+class loss:
+    """src/cuda/loss/cross_entropy.rs:74-128."""
+
+    @staticmethod
+    def cross_entropy(pred: Node, target: Node) -> float:
+        out = C.c_float()
+        check(pred.ctx.h, pred.ctx._l.nrs_cross_entropy(pred.h, target.h, C.byref(out)))
+        return float(out.value)
+
+    @staticmethod
+    def cross_entropy_backward(pred: Node, target: Node):
+        check(pred.ctx.h, pred.ctx._l.nrs_cross_entropy_backward(pred.h, target.h))
+
+
+def backward_graph(root: Node):
+    """src/autograd/node.rs:113-126."""
+    check(root.ctx.h, root.ctx._l.nrs_backward_graph(root.h))
+
+
+class optim:
+    class AdamW:
+        """src/cuda/optim/adamw.rs:43-144."""
+
+        def __init__(self, lr, beta1, beta2, epsilon, weight_decay, ctx: Context | None = None):
+            self.ctx = ctx or default_context()
+            h = VP()
+            check(self.ctx.h, self.ctx._l.nrs_adamw_new(self.ctx.h, C.c_float(lr), C.c_float(beta1), C.c_float(beta2),
+                                                         C.c_float(epsilon), C.c_float(weight_decay), C.byref(h)))
+            self.h = h
+
+        @property
+        def t(self) -> int:
+            return int(self.ctx._l.nrs_adamw_t(self.h))
+
+        def step(self, params):
+            check(self.ctx.h, self.ctx._l.nrs_adamw_step_nodes(self.h, _handles(params), len(params)))
+
+        def export_state(self):
+            l = self.ctx._l
+            n = l.nrs_adamw_state_count(self.h)
+            if n < 0:
+                check(self.ctx.h, 4)
+            out = []
+            for i in range(n):
+                a = np.empty(int(l.nrs_adamw_state_len(self.h, i)), dtype=np.float32)
+                check(self.ctx.h, l.nrs_adamw_state_get(self.h, i, _ptr(a)))
+                out.append(a)
+            return self.t, out
+
+        def import_state(self, t: int, moments):
+            arrs = [_f32(m).reshape(-1) for m in moments]
+            ptrs = (VP * len(arrs))(*[a.ctypes.data for a in arrs])
+            lens = (C.c_int64 * len(arrs))(*[a.size for a in arrs])
+            check(self.ctx.h, self.ctx._l.nrs_adamw_import_state(self.h, int(t), ptrs, lens, len(arrs)))
+
+        def __del__(self):
+            try:
+                if self.h and self.ctx.h:
+                    self.ctx._l.nrs_adamw_free(self.h)
+            except Exception:
+                pass
+            self.h = None

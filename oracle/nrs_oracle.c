@@ -1,0 +1,489 @@
+/*
+ * CPU oracle for the NeuralRs resident-GPU training path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file restates, in plain C, the CPU
+ * algorithms of the reference crate (JackpotMachine777/neuralrs v0.3.0) for the
+ * operators on the training hot path.  It is the checker the CUDA library is
+ * compared against; nothing in the shipped library links, loads or calls it.
+ *
+ * Every function names the reference file:line it follows.  The reference is a
+ * Rust crate and no Rust toolchain exists in the build image, so the reference
+ * itself cannot be compiled; parity is pinned instead on the known-answer
+ * vectors of the reference's own tests (tests/nn_conv_test.rs,
+ * tests/nn_conv_padding_test.rs, tests/nn_maxpool_test.rs, ...), which
+ * tests/test_oracle_golden.py replays against this file.
+ *
+ * The file is compiled twice into one shared object:
+ *   -DNRS_ACC=float   -> symbols ending in _f32: accumulates in f32 in the
+ *                        reference's own loop order (bit-faithful where the
+ *                        reference is serial; the reference's Rayon folds are
+ *                        themselves order-nondeterministic).
+ *   -DNRS_ACC=double  -> symbols ending in _f64: same loops, sums carried in
+ *                        f64.  This is the "true value" used to judge the
+ *                        <=1e-4 relative-error bar.
+ * Build with -ffp-contract=off (Rust never contracts a*b+c into an FMA).
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifndef NRS_ACC
+#define NRS_ACC float
+#endif
+#ifndef NRS_SUFFIX
+#define NRS_SUFFIX _f32
+#endif
+#define NRS_CAT2(a, b) a##b
+#define NRS_CAT(a, b) NRS_CAT2(a, b)
+#define FN(name) NRS_CAT(name, NRS_SUFFIX)
+
+typedef NRS_ACC acc_t;
+
+/* ------------------------------------------------------------------ conv2d */
+
+/* Conv2d forward.  src/nn/conv.rs:33-97: zero-pad copy, then a direct
+ * cross-correlation; loop order (ic, i, j); the bias is added after the sum
+ * (:87-92).  Parallel over (sample, out-channel) maps as the Rayon
+ * par_chunks_mut(out_h*out_w) does (:72-75).  out_h=(H+2p-kh)/s+1 (:64-65). */
+void FN(nrs_oracle_conv2d_fwd)(const float* x, const float* w, const float* b, float* y,
+                               int n, int ci, int h, int wd, int co, int kh, int kw,
+                               int stride, int pad) {
+  const int ph = h + 2 * pad, pw = wd + 2 * pad;
+  const int oh = (ph - kh) / stride + 1, ow = (pw - kw) / stride + 1;
+  float* data = (float*)calloc((size_t)n * ci * ph * pw, sizeof(float));
+  for (int ni = 0; ni < n; ++ni)
+    for (int ic = 0; ic < ci; ++ic)
+      for (int yy = 0; yy < h; ++yy)
+        memcpy(&data[(((size_t)ni * ci + ic) * ph + (yy + pad)) * pw + pad],
+               &x[(((size_t)ni * ci + ic) * h + yy) * wd], sizeof(float) * wd);
+#pragma omp parallel for schedule(static)
+  for (int map = 0; map < n * co; ++map) {
+    const int ni = map / co, oc = map % co;
+    float* out_map = y + (size_t)map * oh * ow;
+    for (int oy = 0; oy < oh; ++oy)
+      for (int ox = 0; ox < ow; ++ox) {
+        acc_t sum = 0;
+        for (int ic = 0; ic < ci; ++ic)
+          for (int i = 0; i < kh; ++i)
+            for (int j = 0; j < kw; ++j) {
+              const int iy = oy * stride + i, ix = ox * stride + j;
+              const size_t in_idx = (((size_t)ni * ci + ic) * ph + iy) * pw + ix;
+              const size_t w_idx = (((size_t)oc * ci + ic) * kh + i) * kw + j;
+              sum += (acc_t)(data[in_idx] * w[w_idx]);
+            }
+        sum += (acc_t)b[oc];
+        out_map[oy * ow + ox] = (float)sum;
+      }
+  }
+  free(data);
+}
+
+/* Conv2d backward.  src/nn/conv.rs:110-200.  Weight/bias gradients: a fold
+ * over (sample, out-channel) units (:114-150), serial order inside a unit; the
+ * reference's Rayon reduce order across units is unspecified, here units are
+ * summed in index order.  Input gradient: scatter into a padded buffer per
+ * sample (:152-179), then the un-pad copy accumulates (+=) into the input
+ * grad (:181-193).  dw/db/dx all ACCUMULATE into what the caller passes
+ * (:195-198); dx may be NULL (the GPU twin skips it when requires_grad is
+ * false, src/cuda/nn/conv.rs:304). */
+void FN(nrs_oracle_conv2d_bwd)(const float* x, const float* w, const float* dy,
+                               float* dx, float* dw, float* db,
+                               int n, int ci, int h, int wd, int co, int kh, int kw,
+                               int stride, int pad) {
+  const int ph = h + 2 * pad, pw = wd + 2 * pad;
+  const int oh = (ph - kh) / stride + 1, ow = (pw - kw) / stride + 1;
+  const size_t w_len = (size_t)co * ci * kh * kw;
+  float* data = (float*)calloc((size_t)n * ci * ph * pw, sizeof(float));
+  for (int ni = 0; ni < n; ++ni)
+    for (int ic = 0; ic < ci; ++ic)
+      for (int yy = 0; yy < h; ++yy)
+        memcpy(&data[(((size_t)ni * ci + ic) * ph + (yy + pad)) * pw + pad],
+               &x[(((size_t)ni * ci + ic) * h + yy) * wd], sizeof(float) * wd);
+
+  /* weight + bias gradient: each out-channel's slice of dw depends only on
+   * units (ni, oc) with that oc, so parallelise over oc and walk ni in order. */
+  acc_t* wg = (acc_t*)calloc(w_len, sizeof(acc_t));
+  acc_t* bg = (acc_t*)calloc((size_t)co, sizeof(acc_t));
+#pragma omp parallel for schedule(static)
+  for (int oc = 0; oc < co; ++oc)
+    for (int ni = 0; ni < n; ++ni)
+      for (int oy = 0; oy < oh; ++oy)
+        for (int ox = 0; ox < ow; ++ox) {
+          const float g = dy[(((size_t)ni * co + oc) * oh + oy) * ow + ox];
+          bg[oc] += (acc_t)g;
+          for (int ic = 0; ic < ci; ++ic)
+            for (int i = 0; i < kh; ++i)
+              for (int j = 0; j < kw; ++j) {
+                const int iy = oy * stride + i, ix = ox * stride + j;
+                const size_t in_idx = (((size_t)ni * ci + ic) * ph + iy) * pw + ix;
+                const size_t w_idx = (((size_t)oc * ci + ic) * kh + i) * kw + j;
+                wg[w_idx] += (acc_t)(g * data[in_idx]);
+              }
+        }
+  for (size_t k = 0; k < w_len; ++k) dw[k] += (float)wg[k];
+  for (int k = 0; k < co; ++k) db[k] += (float)bg[k];
+  free(wg);
+  free(bg);
+
+  if (dx) {
+    const size_t in_block = (size_t)ci * ph * pw;
+#pragma omp parallel for schedule(static)
+    for (int ni = 0; ni < n; ++ni) {
+      acc_t* chunk = (acc_t*)calloc(in_block, sizeof(acc_t));
+      for (int oc = 0; oc < co; ++oc)
+        for (int oy = 0; oy < oh; ++oy)
+          for (int ox = 0; ox < ow; ++ox) {
+            const float g = dy[(((size_t)ni * co + oc) * oh + oy) * ow + ox];
+            for (int ic = 0; ic < ci; ++ic)
+              for (int i = 0; i < kh; ++i)
+                for (int j = 0; j < kw; ++j) {
+                  const int iy = oy * stride + i, ix = ox * stride + j;
+                  const size_t in_local = ((size_t)ic * ph + iy) * pw + ix;
+                  const size_t w_idx = (((size_t)oc * ci + ic) * kh + i) * kw + j;
+                  chunk[in_local] += (acc_t)(g * w[w_idx]);
+                }
+          }
+      for (int ic = 0; ic < ci; ++ic)
+        for (int yy = 0; yy < h; ++yy)
+          for (int xx = 0; xx < wd; ++xx)
+            dx[(((size_t)ni * ci + ic) * h + yy) * wd + xx] +=
+                (float)chunk[((size_t)ic * ph + (yy + pad)) * pw + (xx + pad)];
+      free(chunk);
+    }
+  }
+  free(data);
+}
+
+/* ------------------------------------------------------------------ matmul */
+
+/* [m,k] x [k,n] -> [m,n].  src/autograd/graph/matmul.rs:17-24 (i, j, t loop,
+ * data[i*n+j] accumulated in place, i.e. in f32 in the reference). */
+void FN(nrs_oracle_matmul_fwd)(const float* a, const float* b, float* c, int m, int k, int n) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < m; ++i)
+    for (int j = 0; j < n; ++j) {
+      acc_t s = 0;
+      for (int t = 0; t < k; ++t) s += (acc_t)(a[(size_t)i * k + t] * b[(size_t)t * n + j]);
+      c[(size_t)i * n + j] = (float)s;
+    }
+}
+
+/* dA += dC.B^T ; dB += A^T.dC.  src/autograd/graph/matmul.rs:42-62. */
+void FN(nrs_oracle_matmul_bwd)(const float* a, const float* b, const float* dc,
+                               float* da, float* db, int m, int k, int n) {
+  if (da) {
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < m; ++i)
+      for (int t = 0; t < k; ++t) {
+        acc_t g = 0;
+        for (int j = 0; j < n; ++j) g += (acc_t)(dc[(size_t)i * n + j] * b[(size_t)t * n + j]);
+        da[(size_t)i * k + t] += (float)g;
+      }
+  }
+  if (db) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < k; ++t)
+      for (int j = 0; j < n; ++j) {
+        acc_t g = 0;
+        for (int i = 0; i < m; ++i) g += (acc_t)(a[(size_t)i * k + t] * dc[(size_t)i * n + j]);
+        db[(size_t)t * n + j] += (float)g;
+      }
+  }
+}
+
+/* Batched matmul [b,m,k]x[b,k,n].  src/autograd/graph/bmm.rs:13-96. */
+void FN(nrs_oracle_bmm_fwd)(const float* a, const float* b, float* c, int batch, int m, int k, int n) {
+  for (int bi = 0; bi < batch; ++bi)
+    FN(nrs_oracle_matmul_fwd)(a + (size_t)bi * m * k, b + (size_t)bi * k * n,
+                              c + (size_t)bi * m * n, m, k, n);
+}
+void FN(nrs_oracle_bmm_bwd)(const float* a, const float* b, const float* dc, float* da, float* db,
+                            int batch, int m, int k, int n) {
+  for (int bi = 0; bi < batch; ++bi)
+    FN(nrs_oracle_matmul_bwd)(a + (size_t)bi * m * k, b + (size_t)bi * k * n,
+                              dc + (size_t)bi * m * n, da ? da + (size_t)bi * m * k : NULL,
+                              db ? db + (size_t)bi * k * n : NULL, m, k, n);
+}
+
+/* -------------------------------------------------------------- add / bias */
+
+/* Same-shape add and [rows,cols]+[cols] broadcast.  src/autograd/graph/add.rs:
+ * 21-36 (forward), :52-70 (backward: passthrough; bias gets the column sum,
+ * rows walked in order). */
+void FN(nrs_oracle_add_fwd)(const float* a, const float* b, float* out, size_t n) {
+  for (size_t i = 0; i < n; ++i) out[i] = a[i] + b[i];
+}
+void FN(nrs_oracle_bias_add_fwd)(const float* a, const float* bias, float* out, int rows, int cols) {
+  for (int r = 0; r < rows; ++r)
+    for (int c = 0; c < cols; ++c) out[(size_t)r * cols + c] = a[(size_t)r * cols + c] + bias[c];
+}
+void FN(nrs_oracle_bias_add_bwd)(const float* g, float* da, float* dbias, int rows, int cols) {
+  if (da)
+    for (size_t i = 0; i < (size_t)rows * cols; ++i) da[i] += g[i];
+  for (int c = 0; c < cols; ++c) {
+    acc_t s = 0;
+    for (int r = 0; r < rows; ++r) s += (acc_t)g[(size_t)r * cols + c];
+    dbias[c] += (float)s;
+  }
+}
+
+/* ------------------------------------------------------------- activations */
+
+/* ReLU: x>0 ? x : 0, derivative 0 at x<=0.  src/autograd/graph/relu.rs:15-19,
+ * :33-41; the gradient accumulates into the parent (:43-45). */
+void FN(nrs_oracle_relu_fwd)(const float* x, float* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = x[i] > 0.0f ? x[i] : 0.0f;
+}
+void FN(nrs_oracle_relu_bwd)(const float* x, const float* g, float* dx, size_t n) {
+  for (size_t i = 0; i < n; ++i) dx[i] += x[i] > 0.0f ? g[i] : 0.0f;
+}
+
+/* GELU, tanh approximation, constants 0.7978845608 and 0.044715, all in f32.
+ * src/autograd/graph/gelu.rs:10-23 (forward), :36-56 (derivative). */
+void FN(nrs_oracle_gelu_fwd)(const float* x, float* y, size_t n) {
+  const float c = 0.7978845608f;
+  for (size_t i = 0; i < n; ++i) {
+    const float xi = x[i];
+    const float inner = c * (xi + 0.044715f * xi * xi * xi);
+    y[i] = 0.5f * xi * (1.0f + tanhf(inner));
+  }
+}
+void FN(nrs_oracle_gelu_bwd)(const float* x, const float* g, float* dx, size_t n) {
+  const float c = 0.7978845608f;
+  for (size_t i = 0; i < n; ++i) {
+    const float xi = x[i];
+    const float inner = c * (xi + 0.044715f * xi * xi * xi);
+    const float t = tanhf(inner);
+    const float dinner = c * (1.0f + 3.0f * 0.044715f * xi * xi);
+    const float dgelu = 0.5f * (1.0f + t) + 0.5f * xi * (1.0f - t * t) * dinner;
+    dx[i] += dgelu * g[i];
+  }
+}
+
+/* ----------------------------------------------------------------- maxpool */
+
+/* k x k window, stride s, no padding; strict '>' so the first maximum in
+ * row-major window order wins; argmax is the flat input index.
+ * src/nn/maxpool.rs:32-62 (forward), :74-79 (backward scatter-add). */
+void FN(nrs_oracle_maxpool_fwd)(const float* x, float* y, int32_t* argmax,
+                                int n, int c, int h, int w, int k, int stride) {
+  const int oh = (h - k) / stride + 1, ow = (w - k) / stride + 1;
+  for (int ni = 0; ni < n; ++ni)
+    for (int ch = 0; ch < c; ++ch)
+      for (int oy = 0; oy < oh; ++oy)
+        for (int ox = 0; ox < ow; ++ox) {
+          float best = -INFINITY;
+          size_t best_idx = 0;
+          for (int i = 0; i < k; ++i)
+            for (int j = 0; j < k; ++j) {
+              const int iy = oy * stride + i, ix = ox * stride + j;
+              const size_t in_idx = (((size_t)ni * c + ch) * h + iy) * w + ix;
+              if (x[in_idx] > best) { best = x[in_idx]; best_idx = in_idx; }
+            }
+          const size_t out_idx = (((size_t)ni * c + ch) * oh + oy) * ow + ox;
+          y[out_idx] = best;
+          if (argmax) argmax[out_idx] = (int32_t)best_idx;
+        }
+}
+void FN(nrs_oracle_maxpool_bwd)(const float* g, const int32_t* argmax, float* dx, size_t out_len) {
+  for (size_t o = 0; o < out_len; ++o) dx[argmax[o]] += g[o];
+}
+
+/* ----------------------------------------------------------- cross-entropy */
+
+/* Mean over the batch of -sum_c t*log_softmax(x), max-subtracted.
+ * src/nn/loss.rs:50-76.  `divisor` is the batch the mean is taken over: the
+ * reference always uses the row count (:75); data-parallel shards pass the
+ * global batch so that summed shard losses equal the full-batch loss. */
+float FN(nrs_oracle_ce_fwd)(const float* logits, const float* target, int batch, int classes, int divisor) {
+  acc_t total = 0;
+  for (int b = 0; b < batch; ++b) {
+    const float* row = logits + (size_t)b * classes;
+    float mx = -INFINITY;
+    for (int c = 0; c < classes; ++c) mx = fmaxf(mx, row[c]);
+    acc_t sum_exp = 0;
+    for (int c = 0; c < classes; ++c) sum_exp += (acc_t)expf(row[c] - mx);
+    const float lse = logf((float)sum_exp) + mx;
+    for (int c = 0; c < classes; ++c) {
+      const float ls = row[c] - lse;
+      total += (acc_t)(-target[(size_t)b * classes + c] * ls);
+    }
+  }
+  return (float)(total / (acc_t)divisor);
+}
+/* grad = (softmax - t)/batch, OVERWRITING the logits' grad.  src/nn/loss.rs:
+ * 78-104 (pred.grad = grad, :105). */
+void FN(nrs_oracle_ce_bwd)(const float* logits, const float* target, float* grad,
+                           int batch, int classes, int divisor) {
+  for (int b = 0; b < batch; ++b) {
+    const float* row = logits + (size_t)b * classes;
+    float mx = -INFINITY;
+    for (int c = 0; c < classes; ++c) mx = fmaxf(mx, row[c]);
+    acc_t sum = 0;
+    for (int c = 0; c < classes; ++c) sum += (acc_t)expf(row[c] - mx);
+    for (int c = 0; c < classes; ++c) {
+      const float sm = (float)((acc_t)expf(row[c] - mx) / sum);
+      grad[(size_t)b * classes + c] = (sm - target[(size_t)b * classes + c]) / (float)divisor;
+    }
+  }
+}
+
+/* ------------------------------------------------------------------- AdamW */
+
+/* f32 integer power by repeated squaring, as Rust's f32::powi lowers to
+ * (llvm.powi / compiler-rt __powisf2). */
+static float nrs_powi_f32(float a, int b) {
+  const int recip = b < 0;
+  float r = 1.0f;
+  while (1) {
+    if (b & 1) r *= a;
+    b /= 2;
+    if (b == 0) break;
+    a *= a;
+  }
+  return recip ? 1.0f / r : r;
+}
+
+/* One AdamW step over one flat parameter vector; `t` is the 0-based step
+ * counter BEFORE the step (bias correction uses t+1).  Decoupled decay uses the
+ * pre-update parameter.  src/optim/adamw.rs:23-46.  All arithmetic in f32 in
+ * both builds (there is no long sum to carry in f64). */
+void FN(nrs_oracle_adamw_step)(float* p, const float* g, float* m, float* v, size_t n,
+                               float lr, float beta1, float beta2, float eps, float wd, int t) {
+  const float bc1 = 1.0f - nrs_powi_f32(beta1, t + 1);
+  const float bc2 = 1.0f - nrs_powi_f32(beta2, t + 1);
+  for (size_t i = 0; i < n; ++i) {
+    m[i] = beta1 * m[i] + (1.0f - beta1) * g[i];
+    v[i] = beta2 * v[i] + (1.0f - beta2) * g[i] * g[i];
+    const float m_hat = m[i] / bc1;
+    const float v_hat = v[i] / bc2;
+    p[i] = p[i] - lr * m_hat / (sqrtf(v_hat) + eps) - lr * wd * p[i];
+  }
+}
+
+/* --------------------------------------------------------------- LayerNorm */
+
+/* Per row over the last dim: mean, biased variance, istd=1/sqrt(var+eps),
+ * xhat=(x-mean)*istd, y=gamma*xhat+beta.  src/nn/normalization.rs:38-52.
+ * Saves xhat and istd for backward like the reference does. */
+void FN(nrs_oracle_layernorm_fwd)(const float* x, const float* gamma, const float* beta, float* y,
+                                  float* xhat, float* istd_out, int rows, int f, float eps) {
+  for (int r = 0; r < rows; ++r) {
+    const float* row = x + (size_t)r * f;
+    acc_t s = 0;
+    for (int i = 0; i < f; ++i) s += (acc_t)row[i];
+    const float mean = (float)(s / (acc_t)f);
+    acc_t vs = 0;
+    for (int i = 0; i < f; ++i) { const float d = row[i] - mean; vs += (acc_t)(d * d); }
+    const float var = (float)(vs / (acc_t)f);
+    const float istd = 1.0f / sqrtf(var + eps);
+    if (istd_out) istd_out[r] = istd;
+    for (int i = 0; i < f; ++i) {
+      const float xn = (row[i] - mean) * istd;
+      if (xhat) xhat[(size_t)r * f + i] = xn;
+      y[(size_t)r * f + i] = gamma[i] * xn + beta[i];
+    }
+  }
+}
+/* dx += istd*(dxhat - sum1/F - xhat*sum2/F), dgamma += sum_r g*xhat,
+ * dbeta += sum_r g.  src/nn/normalization.rs:66-103. */
+void FN(nrs_oracle_layernorm_bwd)(const float* g, const float* xhat, const float* istd,
+                                  const float* gamma, float* dx, float* dgamma, float* dbeta,
+                                  int rows, int f) {
+  acc_t* dg = (acc_t*)calloc((size_t)f, sizeof(acc_t));
+  acc_t* dbt = (acc_t*)calloc((size_t)f, sizeof(acc_t));
+  const float nf = (float)f;
+  for (int r = 0; r < rows; ++r) {
+    const size_t st = (size_t)r * f;
+    acc_t sum1 = 0, sum2 = 0;
+    for (int i = 0; i < f; ++i) {
+      const float dxhat = g[st + i] * gamma[i];
+      sum1 += (acc_t)dxhat;
+      sum2 += (acc_t)(dxhat * xhat[st + i]);
+    }
+    const float s1 = (float)sum1, s2 = (float)sum2;
+    for (int i = 0; i < f; ++i) {
+      const float dxhat = g[st + i] * gamma[i];
+      if (dx) dx[st + i] += istd[r] * (dxhat - s1 / nf - xhat[st + i] * s2 / nf);
+      dg[i] += (acc_t)(g[st + i] * xhat[st + i]);
+      dbt[i] += (acc_t)g[st + i];
+    }
+  }
+  for (int i = 0; i < f; ++i) { dgamma[i] += (float)dg[i]; dbeta[i] += (float)dbt[i]; }
+  free(dg);
+  free(dbt);
+}
+
+/* ----------------------------------------------------------------- softmax */
+
+/* Row softmax over the last dim with max subtraction; backward
+ * dx += s*(g - sum(s*g)).  src/autograd/graph/softmax.rs:23-35, :49-60. */
+void FN(nrs_oracle_softmax_fwd)(const float* x, float* y, int rows, int width) {
+  for (int r = 0; r < rows; ++r) {
+    const float* row = x + (size_t)r * width;
+    float mx = -INFINITY;
+    for (int i = 0; i < width; ++i) mx = fmaxf(mx, row[i]);
+    acc_t sum = 0;
+    for (int i = 0; i < width; ++i) sum += (acc_t)expf(row[i] - mx);
+    for (int i = 0; i < width; ++i) y[(size_t)r * width + i] = (float)((acc_t)expf(row[i] - mx) / sum);
+  }
+}
+void FN(nrs_oracle_softmax_bwd)(const float* y, const float* g, float* dx, int rows, int width) {
+  for (int r = 0; r < rows; ++r) {
+    const size_t st = (size_t)r * width;
+    acc_t dot = 0;
+    for (int i = 0; i < width; ++i) dot += (acc_t)(y[st + i] * g[st + i]);
+    const float d = (float)dot;
+    for (int i = 0; i < width; ++i) dx[st + i] += y[st + i] * (g[st + i] - d);
+  }
+}
+
+/* ------------------------------------------------------------ manipulation */
+
+/* Batched transpose of the last two dims.  src/autograd/graph/transpose.rs:
+ * 21-28; backward is the transpose of the gradient, accumulated (:45-52). */
+void FN(nrs_oracle_transpose_fwd)(const float* x, float* y, int batch, int rows, int cols) {
+  for (int b = 0; b < batch; ++b) {
+    const size_t off = (size_t)b * rows * cols;
+    for (int i = 0; i < rows; ++i)
+      for (int j = 0; j < cols; ++j) y[off + (size_t)j * rows + i] = x[off + (size_t)i * cols + j];
+  }
+}
+void FN(nrs_oracle_transpose_bwd)(const float* g, float* dx, int batch, int rows, int cols) {
+  for (int b = 0; b < batch; ++b) {
+    const size_t off = (size_t)b * rows * cols;
+    for (int i = 0; i < rows; ++i)
+      for (int j = 0; j < cols; ++j) dx[off + (size_t)i * cols + j] += g[off + (size_t)j * rows + i];
+  }
+}
+/* x*s ; dx += g*s.  src/autograd/graph/scale.rs:11-16, :29-35. */
+void FN(nrs_oracle_scale_fwd)(const float* x, float* y, size_t n, float s) {
+  for (size_t i = 0; i < n; ++i) y[i] = x[i] * s;
+}
+void FN(nrs_oracle_scale_bwd)(const float* g, float* dx, size_t n, float s) {
+  for (size_t i = 0; i < n; ++i) dx[i] += g[i] * s;
+}
+/* Column slice [c0,c1) of a [rows,total] matrix.  src/autograd/graph/
+ * slice_cols.rs:20-25, :39-45. */
+void FN(nrs_oracle_slice_cols_fwd)(const float* x, float* y, int rows, int total, int c0, int c1) {
+  const int sw = c1 - c0;
+  for (int r = 0; r < rows; ++r)
+    for (int c = 0; c < sw; ++c) y[(size_t)r * sw + c] = x[(size_t)r * total + c0 + c];
+}
+void FN(nrs_oracle_slice_cols_bwd)(const float* g, float* dx, int rows, int total, int c0, int c1) {
+  const int sw = c1 - c0;
+  for (int r = 0; r < rows; ++r)
+    for (int c = 0; c < sw; ++c) dx[(size_t)r * total + c0 + c] += g[(size_t)r * sw + c];
+}
+/* Write one part into / read one part out of a column concatenation.
+ * src/autograd/graph/concat_cols.rs:22-33, :47-57. */
+void FN(nrs_oracle_concat_write)(const float* part, float* out, int rows, int total, int off, int pw) {
+  for (int r = 0; r < rows; ++r)
+    for (int c = 0; c < pw; ++c) out[(size_t)r * total + off + c] = part[(size_t)r * pw + c];
+}
+void FN(nrs_oracle_concat_read)(const float* g, float* dpart, int rows, int total, int off, int pw) {
+  for (int r = 0; r < rows; ++r)
+    for (int c = 0; c < pw; ++c) dpart[(size_t)r * pw + c] += g[(size_t)r * total + off + c];
+}
