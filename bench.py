@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""Headline benchmark: training samples/s (forward + backward + AdamW) of the
+CIFAR-shaped VGG-style CNN, global batch 1024 sharded over N GPUs, f32 with
+3xTF32 contractions, synthetic data, He-initialised weights.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload vgg_cifar|small_cnn|wide_mlp] [--math 3xtf32|tf32|fp32]
+
+For N > 1 launch under torchrun (one rank per GPU); run without torchrun the
+script re-launches itself through `python -m torch.distributed.run`.
+Rank 0 prints ONE JSON line.
+
+* value        whole-job samples/s with the step's inputs already resident in HBM
+* e2e          the same through the host-buffer entry point (nrs_trainer_step): pinned
+               host inputs copied in, loss copied out, every step
+* roofline     the dominant contraction family, timed with CUDA events bracketed around
+               its launches inside the timed region (nrs_profile_*)
+* cpu_baseline the CPU restatement of the reference's training loop (oracle/), timed on
+               this host on a bounded batch
+* --impl reference  times that CPU restatement alone (the reference is a Rust crate and
+               no Rust toolchain exists in the image, so its own binary cannot be built)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "train samples/s (fwd+bwd+AdamW)"
+WORKLOADS = {"vgg_cifar": ("VGG_CIFAR", 1024, 3), "small_cnn": ("SMALL_CNN", 64, 1), "wide_mlp": ("WIDE_MLP", 16384, 5)}
+CPU_SAMPLE_BATCH = {"vgg_cifar": 16, "small_cnn": 64, "wide_mlp": 32}
+MATH = {"3xtf32": 0, "tf32": 1, "fp32": 2}
+PROF_NAMES = ["conv_fwd", "conv_dgrad", "conv_wgrad", "gemm", "adamw"]
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="vgg_cifar", choices=list(WORKLOADS))
+    ap.add_argument("--math", default="3xtf32", choices=list(MATH))
+    ap.add_argument("--global-batch", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fuse", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_burst=float(d["bf16_tflops"]),
+                    bf16_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def model_flops_per_sample(layers, in_shape):
+    """Algorithmic FLOP of one forward pass per sample, and of forward+backward (the first
+    layer's data gradient is not computed: its input does not require a gradient)."""
+    shp = list(in_shape)
+    fwd = 0.0
+    total = 0.0
+    first = True
+    for l in layers:
+        if l[0] == "conv":
+            _, ci, co, k, s, p = l
+            oh, ow = (shp[1] + 2 * p - k) // s + 1, (shp[2] + 2 * p - k) // s + 1
+            f = 2.0 * co * oh * ow * ci * k * k
+            fwd += f
+            total += f * (2 if first else 3)
+            shp = [co, oh, ow]
+            first = False
+        elif l[0] == "linear":
+            f = 2.0 * l[1] * l[2]
+            fwd += f
+            total += f * (2 if first else 3)
+            shp = [l[2]]
+            first = False
+        elif l[0] == "maxpool":
+            shp = [shp[0], (shp[1] - l[1]) // l[2] + 1, (shp[2] - l[1]) // l[2] + 1]
+        elif l[0] == "flatten":
+            n = 1
+            for d in shp:
+                n *= d
+            shp = [n]
+    return fwd, total
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 7:
+                    self.rows.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def cpu_reference_run(workload: str, steps: int, warmup: int, min_seconds: float = 0.0):
+    """Times the CPU restatement of the reference's training loop on a bounded batch."""
+    from oracle import models
+    from oracle.nrs_oracle import Oracle
+    cfg = getattr(models, WORKLOADS[workload][0])
+    seed = 1234 + WORKLOADS[workload][2]
+    batch = CPU_SAMPLE_BATCH[workload]
+    o = Oracle("f32")
+    params = models.he_init(cfg["layers"], seed)
+    hp = models.ADAMW_HP
+    opt = models.OracleAdamW(o, hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], hp["wd"])
+    x, t = models.synthetic_batch(cfg, batch, seed + 1, uniform01=(workload == "small_cnn"))
+    for _ in range(max(0, warmup)):
+        models.train_step(o, cfg["layers"], params, opt, x, t)
+    done = 0
+    t0 = time.perf_counter()
+    while done < steps or (time.perf_counter() - t0) < min_seconds:
+        models.train_step(o, cfg["layers"], params, opt, x, t)
+        done += 1
+        if done >= steps and min_seconds <= 0:
+            break
+        if time.perf_counter() - t0 > 120:
+            break
+    dt = time.perf_counter() - t0
+    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    return dict(value=batch * done / dt, ms_per_step=1e3 * dt / done, steps=done, batch=batch, cores=cores,
+                sample=f"{done} training steps of {cfg['name']} at batch {batch} "
+                       f"(conv/matmul loops OpenMP-parallel as the reference's Rayon loops are)")
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    global_batch = args.global_batch or WORKLOADS[args.workload][1]
+    r = cpu_reference_run(args.workload, args.steps, min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "samples/s", "n_gpus": args.gpus,
+        "steps": r["steps"], "warmup": min(args.warmup, 1), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "global_batch": global_batch, "cpu_sample_batch": r["batch"],
+                   "note": "CPU restatement of the reference's own training loop (oracle/); the Rust crate cannot "
+                           "be built here (no cargo/rustc in the image)"},
+        "cpu_baseline": {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "port",
+                         "sample": r["sample"]},
+        "e2e": {"value": r["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from neuralrs_b200 import _lib, cuda
+    from oracle import models   # model tables + synthetic data only; never on the timed path
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = getattr(models, WORKLOADS[args.workload][0])
+    seed = 1234 + WORKLOADS[args.workload][2]
+    global_batch = args.global_batch or WORKLOADS[args.workload][1]
+    b0, b1 = cuda.dp_shard_range(global_batch, rank, world)
+    batch = b1 - b0
+
+    ctx = cuda.Context(local_rank)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx.set_stream(stream.cuda_stream)
+    ctx.set_math_mode(MATH[args.math])
+    hp = models.ADAMW_HP
+    tr = cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
+                      hp["wd"], fuse=not args.no_fuse, ctx=ctx)
+    tr.set_params(models.he_init(cfg["layers"], seed))       # identical bytes on every rank
+    if world > 1:
+        box = [cuda.dp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        tr.enable_dp(rank, world, box[0], global_batch)
+
+    # Synthetic batches: a few distinct ones, rotated, pinned on the host and resident on the device.
+    n_sets = 4
+    xs_pin, ts_pin, xs_dev, ts_dev = [], [], [], []
+    for i in range(n_sets):
+        x, t = models.synthetic_batch(cfg, global_batch, seed + 10 + i, uniform01=(args.workload == "small_cnn"))
+        xp = torch.from_numpy(np.ascontiguousarray(x[b0:b1])).pin_memory()
+        tp = torch.from_numpy(np.ascontiguousarray(t[b0:b1])).pin_memory()
+        xs_pin.append(xp); ts_pin.append(tp)
+        xs_dev.append(xp.cuda(non_blocking=True)); ts_dev.append(tp.cuda(non_blocking=True))
+    torch.cuda.synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            fn(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        barrier()
+        if world > 1:
+            tms = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            ms = float(tms.item())
+        return ms
+
+    dev_step = lambda i: tr.step_device(xs_dev[i % n_sets].data_ptr(), ts_dev[i % n_sets].data_ptr(), batch, False)
+    host_step = lambda i: tr.step_ptr(xs_pin[i % n_sets].data_ptr(), ts_pin[i % n_sets].data_ptr(), batch, True)
+
+    for i in range(max(3, args.warmup)):
+        dev_step(i)
+    l = _lib.lib()
+    _lib.check(ctx.h, l.nrs_profile_reset(ctx.h))
+    _lib.check(ctx.h, l.nrs_profile_enable(ctx.h, 1))
+    launches0 = ctx.launch_count()
+    with ClockSampler(local_rank) as clk:
+        ms = timed(dev_step, args.steps)
+    launches = ctx.launch_count() - launches0
+    import ctypes as C
+    prof = {}
+    for kind, name in enumerate(PROF_NAMES):
+        pms, work, calls = C.c_double(), C.c_double(), C.c_uint64()
+        _lib.check(ctx.h, l.nrs_profile_get(ctx.h, kind, C.byref(pms), C.byref(work), C.byref(calls)))
+        prof[name] = dict(ms=pms.value, work=work.value, calls=int(calls.value))
+    _lib.check(ctx.h, l.nrs_profile_enable(ctx.h, 0))
+    _lib.check(ctx.h, l.nrs_profile_reset(ctx.h))
+    loss = tr.last_loss()
+
+    for i in range(2):
+        host_step(i)
+    ms_e2e = timed(host_step, args.steps)
+
+    if rank == 0:
+        peaks = measured_peaks()
+        value = global_batch * args.steps / (ms / 1e3)
+        e2e_value = global_batch * args.steps / (ms_e2e / 1e3)
+        fwd_flop, step_flop = model_flops_per_sample(cfg["layers"], cfg["in_shape"])
+        # dominant contraction family by device time
+        fam = max(("conv_fwd", "conv_dgrad", "conv_wgrad", "gemm"), key=lambda k: prof[k]["ms"])
+        f = prof[fam]
+        achieved = (f["work"] / (f["ms"] / 1e3) / 1e12) if f["ms"] > 0 else 0.0
+        tf32_peak = peaks["bf16_sustained"] / 2.0
+        contraction_ms = sum(prof[k]["ms"] for k in ("conv_fwd", "conv_dgrad", "conv_wgrad", "gemm"))
+        contraction_work = sum(prof[k]["work"] for k in ("conv_fwd", "conv_dgrad", "conv_wgrad", "gemm"))
+        adam = prof["adamw"]
+        x_bytes = sum(int(np.prod((global_batch,) + tuple(cfg["in_shape"]))) * 4 for _ in range(1))
+        t_bytes = global_batch * cfg["classes"] * 4
+        line = {
+            "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "global_batch": global_batch, "per_gpu_batch": batch,
+                       "parallelism": f"dp{world}", "math": args.math, "fused_epilogues": not args.no_fuse,
+                       "init": "He N(0,sqrt(2/fan_in)), seed %d" % seed,
+                       "l2": "per-step working set (activations + gradients) is several times the 126 MB L2; "
+                             "4 input batches rotated",
+                       "algorithmic_gflop_per_step": step_flop * global_batch / 1e9,
+                       "tensor_core_path": bool(l.nrs_has_tensor_core_path())},
+            "loss": loss,
+            "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": x_bytes + t_bytes, "d2h_bytes_per_step": 4 * world},
+            "gpu_launches": launches * world,
+            "clocks": clk.summary(),
+            "roofline": {"bound": "tensor", "kernel": fam, "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
+                         "frac": achieved / tf32_peak if tf32_peak else None, "traffic": None,
+                         "peak_source": f"{peaks['source']}: sustained bf16 cuBLAS / 2 (dense TF32 runs at half the bf16 "
+                                        f"rate); 3xTF32 issues 3x the algorithmic FLOP counted in `achieved`",
+                         "launch_ms_avg": f["ms"] / f["calls"] if f["calls"] else None, "calls": f["calls"],
+                         "all_contractions_tflops": (contraction_work / (contraction_ms / 1e3) / 1e12) if contraction_ms else None,
+                         "families_ms_per_step": {k: prof[k]["ms"] / args.steps for k in prof},
+                         "adamw_gbs": (adam["work"] / (adam["ms"] / 1e3) / 1e9) if adam["ms"] > 0 else None,
+                         "hbm_peak_gbs": peaks["hbm_gbs"]},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            r = cpu_reference_run(args.workload, 1, 1, min_seconds=10.0)
+            line["cpu_baseline"] = {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "port",
+                                    "sample": r["sample"]}
+        print(json.dumps(line), flush=True)
+    tr.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 500), __file__] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -80,6 +80,21 @@ uint64_t nrs_launch_count(const nrs_ctx* ctx);
 /* 1 if the tensor-core (tcgen05) kernels were compiled into this build. */
 int nrs_has_tensor_core_path(void);
 
+/* Device timing per kernel family, off by default.  While enabled, the library
+ * brackets every launch of the listed families with CUDA events on the
+ * context's stream; nrs_profile_get waits for the stream and returns the
+ * summed device time, the summed algorithmic work (FLOP for contractions,
+ * bytes for AdamW) and the number of bracketed calls since the last reset.
+ * The reference has no profiling hooks (it prints wall-clock times,
+ * examples/cifar_cuda.rs:265,284). */
+enum nrs_prof_kind {
+  NRS_PROF_CONV_FWD = 0, NRS_PROF_CONV_DGRAD = 1, NRS_PROF_CONV_WGRAD = 2,
+  NRS_PROF_GEMM = 3, NRS_PROF_ADAMW = 4, NRS_PROF_KINDS = 5
+};
+int nrs_profile_enable(nrs_ctx* ctx, int on);
+int nrs_profile_reset(nrs_ctx* ctx);
+int nrs_profile_get(nrs_ctx* ctx, int kind, double* ms_out, double* work_out, uint64_t* calls_out);
+
 /* ---------------------------------------------------------------- memory -- */
 /* stream.alloc_zeros / clone_htod / clone_dtoh / memset_zeros / synchronize
  * (src/cuda/runtime.rs:39-51, 55-62, 108-124).  nrs_alloc draws from a

@@ -94,6 +94,69 @@ int nrs_adamw_state_get(const nrs_adamw* opt, int i, float* host_out);
 /* import_state(t, moments): `lens[i]` floats at `moments[i]`, all m's then all v's. */
 int nrs_adamw_import_state(nrs_adamw* opt, int64_t t, const float* const* moments, const int64_t* lens, int count);
 
+/* ------------------------------------------------------------- trainer -- */
+/* The reference leaves the training loop to user code: to_cuda(batch),
+ * zero_grad, forward, cross_entropy(+_backward), backward_graph, optimizer.step
+ * (examples/cifar_cuda.rs:267-286, examples/mnist_cuda_cnn.rs:254-275).  The
+ * trainer runs that same loop natively for a sequential model, so a whole step
+ * is one call (no per-operator crossing of the language boundary), and adds
+ * what the reference does not have: data-parallel gradient all-reduce. */
+enum nrs_layer_kind {
+  NRS_LAYER_CONV = 0,     /* a=c_in b=c_out c=kernel d=stride e=pad              */
+  NRS_LAYER_RELU = 1,
+  NRS_LAYER_MAXPOOL = 2,  /* a=kernel b=stride                                   */
+  NRS_LAYER_FLATTEN = 3,
+  NRS_LAYER_LINEAR = 4,   /* a=in b=out                                          */
+  NRS_LAYER_GELU = 5
+};
+typedef struct nrs_layer_spec { int kind, a, b, c, d, e; } nrs_layer_spec;
+
+/* in_shape: per-sample input shape (e.g. {3,32,32}).  fuse != 0 folds a ReLU
+ * that follows a conv/linear layer into that layer's kernel.  Parameters are
+ * created zero-filled in layer order [w0,b0,w1,b1,...] inside one flat block;
+ * fill them with nrs_trainer_set_param. */
+int nrs_trainer_create(nrs_ctx* ctx, const nrs_layer_spec* layers, int n_layers, const int64_t* in_shape,
+                       int in_ndim, int classes, float lr, float beta1, float beta2, float eps,
+                       float weight_decay, int fuse, nrs_trainer** out);
+int nrs_trainer_free(nrs_trainer* t);
+int nrs_trainer_param_count(const nrs_trainer* t);
+int64_t nrs_trainer_param_len(const nrs_trainer* t, int i);
+int nrs_trainer_set_param(nrs_trainer* t, int i, const float* host);
+int nrs_trainer_get_param(nrs_trainer* t, int i, float* host_out);
+int nrs_trainer_get_grad(nrs_trainer* t, int i, float* host_out);
+/* zero_grad + forward + cross-entropy + backward (no optimizer step).
+ * x_host [batch, in_shape...] and target_host [batch, classes] (one-hot f32) are
+ * HOST buffers copied to the device inside the call; loss_out (host) may be
+ * NULL, otherwise the call waits for the loss. */
+int nrs_trainer_forward_backward(nrs_trainer* t, const float* x_host, const float* target_host, int batch,
+                                 float* loss_out);
+/* A full training step: the above plus the gradient all-reduce (when data
+ * parallel) and one fused AdamW update. */
+int nrs_trainer_step(nrs_trainer* t, const float* x_host, const float* target_host, int batch, float* loss_out);
+/* Same step on inputs already resident on the device. */
+int nrs_trainer_step_device(nrs_trainer* t, const float* x_dev, const float* target_dev, int batch,
+                            float* loss_out);
+/* Loss of the most recent step (waits for it). */
+int nrs_trainer_last_loss(nrs_trainer* t, float* loss_out);
+
+/* Data parallelism (no reference counterpart: the reference is single-GPU).
+ * Rank 0 makes an id with nrs_dp_unique_id (128 bytes, host) and the launcher
+ * broadcasts it; every rank then calls nrs_trainer_enable_dp.  Each rank feeds
+ * its shard of `global_batch`; the loss/gradient are divided by global_batch so
+ * the all-reduced SUM equals the single-GPU full-batch gradient.  Gradients
+ * are reduced in flat buckets of about bucket_bytes on a second stream as soon
+ * as backward has produced them. */
+int nrs_dp_unique_id(void* id_out_128_bytes);
+int nrs_trainer_enable_dp(nrs_trainer* t, int rank, int world, const void* unique_id_128_bytes,
+                          int global_batch, size_t bucket_bytes);
+/* Host-only helpers (usable without a GPU): sample range of a rank, and the
+ * bucket boundaries (in floats, from the END of the flat gradient, the order
+ * backward produces them) for given parameter lengths.  Returns the bucket
+ * count; starts_out/ends_out may be NULL to only count. */
+int nrs_dp_shard_range(int global_batch, int rank, int world, int* begin_out, int* end_out);
+int nrs_dp_plan_buckets(const int64_t* param_lens, int n_params, size_t bucket_bytes,
+                        int64_t* starts_out, int64_t* ends_out, int capacity);
+
 #ifdef __cplusplus
 }
 #endif

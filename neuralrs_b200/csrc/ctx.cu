@@ -38,7 +38,70 @@ int nrs_workspace(nrs_ctx* ctx, size_t bytes, void** out) {
   return NRS_OK;
 }
 
+static cudaEvent_t prof_event(nrs_ctx* ctx) {
+  if (!ctx->prof_free_events.empty()) {
+    cudaEvent_t e = ctx->prof_free_events.back();
+    ctx->prof_free_events.pop_back();
+    return e;
+  }
+  cudaEvent_t e = nullptr;
+  if (cudaEventCreate(&e) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+  return e;
+}
+
+NrsProfScope::NrsProfScope(nrs_ctx* c, int kind, double work) : ctx(c) {
+  if (!c || !c->profiling) return;
+  rec.kind = kind;
+  rec.work = work;
+  rec.start = prof_event(c);
+  rec.stop = prof_event(c);
+  if (!rec.start || !rec.stop) return;
+  active = cudaEventRecord(rec.start, c->stream) == cudaSuccess;
+}
+
+NrsProfScope::~NrsProfScope() {
+  if (!active) return;
+  if (cudaEventRecord(rec.stop, ctx->stream) == cudaSuccess) ctx->prof_records.push_back(rec);
+}
+
 extern "C" {
+
+int nrs_profile_enable(nrs_ctx* ctx, int on) {
+  NRS_REQUIRE_CTX(ctx);
+  ctx->profiling = on != 0;
+  return NRS_OK;
+}
+
+int nrs_profile_reset(nrs_ctx* ctx) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (auto& r : ctx->prof_records) {
+    ctx->prof_free_events.push_back(r.start);
+    ctx->prof_free_events.push_back(r.stop);
+  }
+  ctx->prof_records.clear();
+  return NRS_OK;
+}
+
+int nrs_profile_get(nrs_ctx* ctx, int kind, double* ms_out, double* work_out, uint64_t* calls_out) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, kind >= 0 && kind < NRS_PROF_KINDS, NRS_ERR_ARG, "nrs_profile_get: unknown kind %d", kind);
+  NRS_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  double ms = 0.0, work = 0.0;
+  uint64_t calls = 0;
+  for (auto& r : ctx->prof_records) {
+    if (r.kind != kind) continue;
+    float t = 0.0f;
+    NRS_CUDA(ctx, cudaEventElapsedTime(&t, r.start, r.stop));
+    ms += t;
+    work += r.work;
+    ++calls;
+  }
+  if (ms_out) *ms_out = ms;
+  if (work_out) *work_out = work;
+  if (calls_out) *calls_out = calls;
+  return NRS_OK;
+}
 
 int nrs_init(int device, nrs_ctx** out) {
   if (!out) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_init: null out pointer");
@@ -84,6 +147,8 @@ int nrs_destroy(nrs_ctx* ctx) {
   for (auto& kv : ctx->pool.free_blocks) cudaFree(kv.second);
   for (auto& kv : ctx->pool.live) cudaFree(kv.first);
   if (ctx->workspace) cudaFree(ctx->workspace);
+  for (auto& r : ctx->prof_records) { cudaEventDestroy(r.start); cudaEventDestroy(r.stop); }
+  for (auto& e : ctx->prof_free_events) cudaEventDestroy(e);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
   return NRS_OK;

@@ -1,0 +1,496 @@
+// Native training loop for sequential models + data-parallel gradient exchange.
+//
+// One nrs_trainer_step is the reference's user loop (examples/cifar_cuda.rs:
+// 267-286): to_cuda(batch) -> zero_grad -> forward -> cross-entropy ->
+// backward_graph -> optimizer.step, built from the same graph operators as
+// graph.cu.  Parameters, gradients and AdamW moments live in flat blocks, so
+// the optimizer is one launch and the data-parallel exchange is one
+// ncclAllReduce per bucket, issued on a second stream as soon as backward has
+// produced the bucket, overlapping the rest of backward.
+//
+// NCCL is loaded with dlopen on first use: single-GPU users need no NCCL.
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cstring>
+#include <unordered_set>
+
+#include "host/graph.h"
+#include "nrs_graph.h"
+#include "nrs_internal.h"
+
+namespace {
+
+using nrs::NodeP;
+
+// ------------------------------------------------------------------- NCCL
+struct NcclId { char internal[128]; };
+typedef void* ncclComm_p;
+struct NcclApi {
+  void* handle = nullptr;
+  int (*GetUniqueId)(NcclId*) = nullptr;
+  int (*CommInitRank)(ncclComm_p*, int, NcclId, int) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_p, cudaStream_t) = nullptr;
+  int (*CommDestroy)(ncclComm_p) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  std::string error;
+};
+constexpr int kNcclFloat32 = 7, kNcclSum = 0;
+
+NcclApi* nccl_api() {
+  static NcclApi api;
+  static bool tried = false;
+  if (tried) return api.handle ? &api : nullptr;
+  tried = true;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  for (const char* n : names) {
+    api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (api.handle) break;
+  }
+  if (!api.handle) {
+    api.error = std::string("cannot load libnccl.so.2: ") + (dlerror() ? dlerror() : "unknown");
+    return nullptr;
+  }
+  auto sym = [&](const char* s) { return dlsym(api.handle, s); };
+  api.GetUniqueId = (int (*)(NcclId*))sym("ncclGetUniqueId");
+  api.CommInitRank = (int (*)(ncclComm_p*, int, NcclId, int))sym("ncclCommInitRank");
+  api.AllReduce = (int (*)(const void*, void*, size_t, int, int, ncclComm_p, cudaStream_t))sym("ncclAllReduce");
+  api.CommDestroy = (int (*)(ncclComm_p))sym("ncclCommDestroy");
+  api.GetErrorString = (const char* (*)(int))sym("ncclGetErrorString");
+  if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy || !api.GetErrorString) {
+    api.error = "libnccl.so.2 lacks a required symbol";
+    dlclose(api.handle);
+    api.handle = nullptr;
+    return nullptr;
+  }
+  return &api;
+}
+
+// Buckets over the flat gradient, walking parameters from the LAST to the first
+// (the order backward finishes them); a bucket closes once it holds at least
+// bucket_bytes.  `offsets` are the parameters' (padded) starts, `total` the end.
+struct Bucket { size_t begin, end; int first_param, last_param; };
+std::vector<Bucket> plan_buckets(const std::vector<size_t>& offsets, size_t total, size_t bucket_bytes) {
+  std::vector<Bucket> out;
+  const int n = (int)offsets.size();
+  if (n == 0) return out;
+  const size_t want = std::max<size_t>(1, bucket_bytes / sizeof(float));
+  size_t end = total;
+  int last = n - 1;
+  for (int i = n - 1; i >= 0; --i) {
+    if (end - offsets[i] >= want || i == 0) {
+      out.push_back({offsets[i], end, i, last});
+      end = offsets[i];
+      last = i - 1;
+    }
+  }
+  return out;
+}
+
+}  // namespace
+
+struct nrs_trainer {
+  nrs_ctx* ctx = nullptr;
+  std::vector<nrs_layer_spec> layers;
+  std::vector<size_t> in_shape;
+  int classes = 0;
+  bool fuse = false;
+  std::vector<NodeP> params;            // [w0,b0,w1,b1,...]
+  std::shared_ptr<nrs::FlatStore> flat;
+  std::unique_ptr<nrs::cuda::AdamW> opt;
+  float* loss_dev = nullptr;
+  // staging for host inputs (grow-only device buffers)
+  float* x_dev = nullptr; size_t x_cap = 0;
+  float* t_dev = nullptr; size_t t_cap = 0;
+  // data parallel
+  int rank = 0, world = 1, global_batch = 0;
+  ncclComm_p comm = nullptr;
+  cudaStream_t comm_stream = nullptr;
+  cudaEvent_t ready_ev = nullptr, done_ev = nullptr;
+  std::vector<Bucket> buckets;
+  ~nrs_trainer() {
+    if (comm) { if (NcclApi* a = nccl_api()) a->CommDestroy(comm); }
+    if (comm_stream) cudaStreamDestroy(comm_stream);
+    if (ready_ev) cudaEventDestroy(ready_ev);
+    if (done_ev) cudaEventDestroy(done_ev);
+    opt.reset();
+    params.clear();
+    flat.reset();
+    if (ctx) {
+      if (loss_dev) nrs_free(ctx, loss_dev);
+      if (x_dev) nrs_free(ctx, x_dev);
+      if (t_dev) nrs_free(ctx, t_dev);
+    }
+  }
+};
+
+namespace {
+
+void fail(int code, const std::string& m) { throw nrs::Error(code, m); }
+
+void validate_and_build_params(nrs_trainer* t) {
+  // Walk the shapes once to validate the spec and create the parameters.
+  std::vector<size_t> shp = t->in_shape;  // per-sample
+  for (size_t li = 0; li < t->layers.size(); ++li) {
+    const nrs_layer_spec& l = t->layers[li];
+    switch (l.kind) {
+      case NRS_LAYER_CONV: {
+        if (shp.size() != 3) fail(NRS_ERR_SHAPE, "trainer: conv layer needs a [C,H,W] input");
+        if (l.a != (int)shp[0]) fail(NRS_ERR_SHAPE, "trainer: conv c_in does not match the incoming channels");
+        if (l.b <= 0 || l.c <= 0 || l.d <= 0 || l.e < 0) fail(NRS_ERR_SHAPE, "trainer: bad conv hyper-parameters");
+        if ((int)shp[1] + 2 * l.e < l.c || (int)shp[2] + 2 * l.e < l.c) fail(NRS_ERR_SHAPE, "trainer: conv kernel too large");
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.b, (size_t)l.a, (size_t)l.c, (size_t)l.c}));
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.b}));
+        shp = {(size_t)l.b, (shp[1] + 2 * l.e - l.c) / l.d + 1, (shp[2] + 2 * l.e - l.c) / l.d + 1};
+        break;
+      }
+      case NRS_LAYER_MAXPOOL:
+        if (shp.size() != 3) fail(NRS_ERR_SHAPE, "trainer: maxpool needs a [C,H,W] input");
+        if (l.a <= 0 || l.b <= 0 || l.a > (int)shp[1] || l.a > (int)shp[2]) fail(NRS_ERR_SHAPE, "trainer: bad maxpool window");
+        shp = {shp[0], (shp[1] - l.a) / l.b + 1, (shp[2] - l.a) / l.b + 1};
+        break;
+      case NRS_LAYER_FLATTEN: {
+        size_t n = 1;
+        for (size_t d : shp) n *= d;
+        shp = {n};
+        break;
+      }
+      case NRS_LAYER_LINEAR:
+        if (shp.size() != 1 || (int)shp[0] != l.a || l.b <= 0) fail(NRS_ERR_SHAPE, "trainer: linear layer input size mismatch");
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.a, (size_t)l.b}));
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.b}));
+        shp = {(size_t)l.b};
+        break;
+      case NRS_LAYER_RELU:
+      case NRS_LAYER_GELU:
+        break;
+      default:
+        fail(NRS_ERR_ARG, "trainer: unknown layer kind");
+    }
+  }
+  if (shp.size() != 1 || (int)shp[0] != t->classes) fail(NRS_ERR_SHAPE, "trainer: model output does not match `classes`");
+  if (t->params.empty()) fail(NRS_ERR_ARG, "trainer: model has no parameters");
+  for (auto& p : t->params) {
+    p->host.assign(p->len(), 0.0f);
+    nrs::cuda::to_cuda(p);
+    p->host.clear();
+    p->host.shrink_to_fit();
+  }
+  t->flat = nrs::cuda::flatten_params(t->params);
+}
+
+NodeP forward(nrs_trainer* t, const NodeP& x) {
+  NodeP h = x;
+  size_t pi = 0;
+  for (size_t li = 0; li < t->layers.size(); ++li) {
+    const nrs_layer_spec& l = t->layers[li];
+    const bool relu_next = t->fuse && li + 1 < t->layers.size() && t->layers[li + 1].kind == NRS_LAYER_RELU;
+    switch (l.kind) {
+      case NRS_LAYER_CONV:
+        h = nrs::cuda::conv2d_act(h, t->params[pi], t->params[pi + 1], (size_t)l.d, (size_t)l.e,
+                                  relu_next ? NRS_ACT_RELU : NRS_ACT_NONE);
+        pi += 2;
+        if (relu_next) ++li;
+        break;
+      case NRS_LAYER_LINEAR:
+        if (t->fuse) {
+          const bool gelu_next = li + 1 < t->layers.size() && t->layers[li + 1].kind == NRS_LAYER_GELU;
+          h = nrs::cuda::linear_act(h, t->params[pi], t->params[pi + 1],
+                                    relu_next ? NRS_ACT_RELU : gelu_next ? NRS_ACT_GELU : NRS_ACT_NONE);
+          if (relu_next || gelu_next) ++li;
+        } else {
+          h = nrs::cuda::add(nrs::cuda::matmul(h, t->params[pi]), t->params[pi + 1]);
+        }
+        pi += 2;
+        break;
+      case NRS_LAYER_RELU: h = nrs::cuda::relu(h); break;
+      case NRS_LAYER_GELU: h = nrs::cuda::gelu(h); break;
+      case NRS_LAYER_MAXPOOL: h = nrs::cuda::maxpool2d(h, (size_t)l.a, (size_t)l.b); break;
+      case NRS_LAYER_FLATTEN: h = nrs::cuda::flatten(h); break;
+    }
+  }
+  return h;
+}
+
+void topo_order(const NodeP& root, std::vector<NodeP>& topo) {
+  std::unordered_set<const nrs::Node*> seen;
+  struct Frame { NodeP node; size_t next; };
+  std::vector<Frame> stack;
+  seen.insert(root.get());
+  stack.push_back({root, 0});
+  while (!stack.empty()) {
+    Frame& f = stack.back();
+    if (f.next < f.node->parents.size()) {
+      NodeP p = f.node->parents[f.next++];
+      if (seen.insert(p.get()).second) stack.push_back({p, 0});
+    } else {
+      topo.push_back(f.node);
+      stack.pop_back();
+    }
+  }
+}
+
+// Enqueue the all-reduce of one bucket on the comm stream, after everything the
+// compute stream has enqueued so far.
+void launch_bucket(nrs_trainer* t, const Bucket& b) {
+  NcclApi* api = nccl_api();
+  nrs_ctx* ctx = t->ctx;
+  if (cudaEventRecord(t->ready_ev, ctx->stream) != cudaSuccess ||
+      cudaStreamWaitEvent(t->comm_stream, t->ready_ev, 0) != cudaSuccess)
+    fail(NRS_ERR_CUDA, "trainer: event hand-off to the comm stream failed");
+  float* g = t->flat->grad + b.begin;
+  const int rc = api->AllReduce(g, g, b.end - b.begin, kNcclFloat32, kNcclSum, t->comm, t->comm_stream);
+  if (rc != 0) fail(NRS_ERR_NCCL, std::string("ncclAllReduce: ") + api->GetErrorString(rc));
+}
+
+void run_step(nrs_trainer* t, const float* x_dev, const float* t_dev, int batch, bool optimize) {
+  nrs_ctx* ctx = t->ctx;
+  if (batch <= 0) fail(NRS_ERR_SHAPE, "trainer: batch must be positive");
+  // Input nodes wrap the caller's device buffers (not owned).
+  auto wrap = [&](const float* dev, std::vector<size_t> shape) {
+    auto n = std::make_shared<nrs::Node>();
+    n->ctx = ctx;
+    n->shape = std::move(shape);
+    n->data = const_cast<float*>(dev);
+    n->owns_data = false;
+    n->requires_grad = false;  // examples/cifar_cuda.rs:270: skips the first conv's data gradient
+    return n;
+  };
+  std::vector<size_t> xs{(size_t)batch};
+  xs.insert(xs.end(), t->in_shape.begin(), t->in_shape.end());
+  NodeP x = wrap(x_dev, xs);
+  NodeP target = wrap(t_dev, {(size_t)batch, (size_t)t->classes});
+
+  nrs::cuda::zero_grad(t->params);
+  NodeP logits = forward(t, x);
+  const int divisor = t->world > 1 ? t->global_batch : batch;
+  nrs::cuda::cross_entropy_fused(logits, target, t->loss_dev, divisor);
+
+  std::vector<NodeP> topo;
+  topo_order(logits, topo);
+  const bool dp = t->world > 1 && optimize;
+  size_t next_bucket = 0;
+  for (auto it = topo.rbegin(); it != topo.rend(); ++it) {
+    if ((*it)->backward_fn) (*it)->backward_fn();
+    if (dp) {
+      // A bucket is ready once every parameter in it has received its gradient
+      // (each parameter has exactly one producer in a sequential model).
+      while (next_bucket < t->buckets.size()) {
+        const Bucket& b = t->buckets[next_bucket];
+        bool ready = true;
+        for (int p = b.first_param; p <= b.last_param; ++p) ready = ready && t->params[p]->grad_valid;
+        if (!ready) break;
+        launch_bucket(t, b);
+        ++next_bucket;
+      }
+    }
+  }
+  if (dp) {
+    // Parameters that received no gradient still have to be exchanged as zeros.
+    for (auto& p : t->params)
+      if (!p->grad_valid) {
+        nrs::check(ctx, nrs_memset_zero(ctx, p->grad, p->len() * sizeof(float)));
+        p->grad_valid = true;
+      }
+    for (; next_bucket < t->buckets.size(); ++next_bucket) launch_bucket(t, t->buckets[next_bucket]);
+    if (cudaEventRecord(t->done_ev, t->comm_stream) != cudaSuccess ||
+        cudaStreamWaitEvent(ctx->stream, t->done_ev, 0) != cudaSuccess)
+      fail(NRS_ERR_CUDA, "trainer: event hand-off from the comm stream failed");
+  }
+  if (optimize) t->opt->step(t->params);
+}
+
+void stage(nrs_trainer* t, float** buf, size_t* cap, const float* host, size_t floats) {
+  if (floats > *cap) {
+    if (*buf) nrs_free(t->ctx, *buf);
+    void* p = nullptr;
+    nrs::check(t->ctx, nrs_alloc(t->ctx, floats * sizeof(float), 0, &p));
+    *buf = (float*)p;
+    *cap = floats;
+  }
+  nrs::check(t->ctx, nrs_h2d(t->ctx, *buf, host, floats * sizeof(float)));
+}
+
+template <class F>
+int guarded(nrs_ctx* ctx, F&& f) {
+  try {
+    f();
+    return NRS_OK;
+  } catch (const nrs::Error& e) {
+    return nrs_fail(ctx, e.code, "%s", e.what());
+  } catch (const std::exception& e) {
+    return nrs_fail(ctx, NRS_ERR_ARG, "%s", e.what());
+  }
+}
+
+int host_step(nrs_trainer* t, const float* x_host, const float* target_host, int batch, float* loss_out, bool optimize) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "trainer: null handle");
+  if (!x_host || !target_host) return nrs_fail(t->ctx, NRS_ERR_ARG, "trainer: null input");
+  return guarded(t->ctx, [&] {
+    if (batch <= 0) fail(NRS_ERR_SHAPE, "trainer: batch must be positive");
+    size_t per = 1;
+    for (size_t d : t->in_shape) per *= d;
+    stage(t, &t->x_dev, &t->x_cap, x_host, per * batch);
+    stage(t, &t->t_dev, &t->t_cap, target_host, (size_t)t->classes * batch);
+    run_step(t, t->x_dev, t->t_dev, batch, optimize);
+    if (loss_out) nrs::check(t->ctx, nrs_d2h(t->ctx, loss_out, t->loss_dev, sizeof(float)));
+  });
+}
+
+}  // namespace
+
+extern "C" {
+
+int nrs_trainer_create(nrs_ctx* ctx, const nrs_layer_spec* layers, int n_layers, const int64_t* in_shape,
+                       int in_ndim, int classes, float lr, float beta1, float beta2, float eps,
+                       float weight_decay, int fuse, nrs_trainer** out) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, out != nullptr, NRS_ERR_ARG, "nrs_trainer_create: null out handle");
+  *out = nullptr;
+  NRS_REQUIRE(ctx, layers && n_layers > 0 && in_shape && in_ndim > 0 && classes > 0, NRS_ERR_ARG,
+              "nrs_trainer_create: bad arguments");
+  nrs_trainer* t = new nrs_trainer();
+  const int st = guarded(ctx, [&] {
+    t->ctx = ctx;
+    t->layers.assign(layers, layers + n_layers);
+    for (int i = 0; i < in_ndim; ++i) {
+      if (in_shape[i] <= 0) fail(NRS_ERR_SHAPE, "nrs_trainer_create: non-positive input extent");
+      t->in_shape.push_back((size_t)in_shape[i]);
+    }
+    t->classes = classes;
+    t->fuse = fuse != 0;
+    validate_and_build_params(t);
+    t->opt.reset(new nrs::cuda::AdamW(ctx, lr, beta1, beta2, eps, weight_decay));
+    void* p = nullptr;
+    nrs::check(ctx, nrs_alloc(ctx, sizeof(float), 1, &p));
+    t->loss_dev = (float*)p;
+  });
+  if (st != NRS_OK) { delete t; return st; }
+  *out = t;
+  return NRS_OK;
+}
+
+int nrs_trainer_free(nrs_trainer* t) {
+  if (t && t->ctx) cudaStreamSynchronize(t->ctx->stream);
+  delete t;
+  return NRS_OK;
+}
+
+int nrs_trainer_param_count(const nrs_trainer* t) { return t ? (int)t->params.size() : -1; }
+
+int64_t nrs_trainer_param_len(const nrs_trainer* t, int i) {
+  return (t && i >= 0 && i < (int)t->params.size()) ? (int64_t)t->params[i]->len() : -1;
+}
+
+int nrs_trainer_set_param(nrs_trainer* t, int i, const float* host) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_set_param: null handle");
+  NRS_REQUIRE(t->ctx, host && i >= 0 && i < (int)t->params.size(), NRS_ERR_ARG, "nrs_trainer_set_param: bad index or null data");
+  int st = nrs_h2d(t->ctx, t->params[i]->data, host, t->params[i]->len() * sizeof(float));
+  if (st == NRS_OK) st = nrs_sync(t->ctx);
+  return st;
+}
+
+int nrs_trainer_get_param(nrs_trainer* t, int i, float* host_out) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_get_param: null handle");
+  NRS_REQUIRE(t->ctx, host_out && i >= 0 && i < (int)t->params.size(), NRS_ERR_ARG, "nrs_trainer_get_param: bad index or null output");
+  return nrs_d2h(t->ctx, host_out, t->params[i]->data, t->params[i]->len() * sizeof(float));
+}
+
+int nrs_trainer_get_grad(nrs_trainer* t, int i, float* host_out) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_get_grad: null handle");
+  NRS_REQUIRE(t->ctx, host_out && i >= 0 && i < (int)t->params.size(), NRS_ERR_ARG, "nrs_trainer_get_grad: bad index or null output");
+  return guarded(t->ctx, [&] {
+    auto v = nrs::cuda::read_grad(t->params[i]);
+    std::memcpy(host_out, v.data(), v.size() * sizeof(float));
+  });
+}
+
+int nrs_trainer_forward_backward(nrs_trainer* t, const float* x_host, const float* target_host, int batch, float* loss_out) {
+  return host_step(t, x_host, target_host, batch, loss_out, false);
+}
+
+int nrs_trainer_step(nrs_trainer* t, const float* x_host, const float* target_host, int batch, float* loss_out) {
+  return host_step(t, x_host, target_host, batch, loss_out, true);
+}
+
+int nrs_trainer_step_device(nrs_trainer* t, const float* x_dev, const float* target_dev, int batch, float* loss_out) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_step_device: null handle");
+  if (!x_dev || !target_dev) return nrs_fail(t->ctx, NRS_ERR_ARG, "nrs_trainer_step_device: null input");
+  return guarded(t->ctx, [&] {
+    run_step(t, x_dev, target_dev, batch, true);
+    if (loss_out) nrs::check(t->ctx, nrs_d2h(t->ctx, loss_out, t->loss_dev, sizeof(float)));
+  });
+}
+
+int nrs_trainer_last_loss(nrs_trainer* t, float* loss_out) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_last_loss: null handle");
+  NRS_REQUIRE(t->ctx, loss_out != nullptr, NRS_ERR_ARG, "nrs_trainer_last_loss: null output");
+  return nrs_d2h(t->ctx, loss_out, t->loss_dev, sizeof(float));
+}
+
+int nrs_dp_unique_id(void* id_out) {
+  if (!id_out) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_dp_unique_id: null output");
+  NcclApi* api = nccl_api();
+  if (!api) return nrs_fail(nullptr, NRS_ERR_NCCL, "nrs_dp_unique_id: NCCL is not available");
+  NcclId id;
+  const int rc = api->GetUniqueId(&id);
+  if (rc != 0) return nrs_fail(nullptr, NRS_ERR_NCCL, "ncclGetUniqueId: %s", api->GetErrorString(rc));
+  std::memcpy(id_out, &id, sizeof(id));
+  return NRS_OK;
+}
+
+int nrs_trainer_enable_dp(nrs_trainer* t, int rank, int world, const void* unique_id, int global_batch,
+                          size_t bucket_bytes) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_enable_dp: null handle");
+  nrs_ctx* ctx = t->ctx;
+  NRS_REQUIRE(ctx, world >= 1 && rank >= 0 && rank < world, NRS_ERR_ARG, "nrs_trainer_enable_dp: rank %d / world %d", rank, world);
+  NRS_REQUIRE(ctx, global_batch > 0, NRS_ERR_ARG, "nrs_trainer_enable_dp: global batch must be positive");
+  NRS_REQUIRE(ctx, t->comm == nullptr, NRS_ERR_ARG, "nrs_trainer_enable_dp: already enabled");
+  t->rank = rank;
+  t->world = world;
+  t->global_batch = global_batch;
+  if (world == 1) return NRS_OK;
+  NRS_REQUIRE(ctx, unique_id != nullptr, NRS_ERR_ARG, "nrs_trainer_enable_dp: null unique id");
+  NcclApi* api = nccl_api();
+  if (!api) { t->world = 1; return nrs_fail(ctx, NRS_ERR_NCCL, "nrs_trainer_enable_dp: NCCL is not available"); }
+  NcclId id;
+  std::memcpy(&id, unique_id, sizeof(id));
+  const int rc = api->CommInitRank(&t->comm, world, id, rank);
+  if (rc != 0) { t->world = 1; t->comm = nullptr; return nrs_fail(ctx, NRS_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString(rc)); }
+  NRS_CUDA(ctx, cudaStreamCreateWithFlags(&t->comm_stream, cudaStreamNonBlocking));
+  NRS_CUDA(ctx, cudaEventCreateWithFlags(&t->ready_ev, cudaEventDisableTiming));
+  NRS_CUDA(ctx, cudaEventCreateWithFlags(&t->done_ev, cudaEventDisableTiming));
+  t->buckets = plan_buckets(t->flat->offset, t->flat->total, bucket_bytes ? bucket_bytes : ((size_t)32 << 20));
+  return NRS_OK;
+}
+
+int nrs_dp_shard_range(int global_batch, int rank, int world, int* begin_out, int* end_out) {
+  if (world < 1 || rank < 0 || rank >= world || global_batch < 0 || !begin_out || !end_out)
+    return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_dp_shard_range: bad arguments");
+  // Contiguous shards; the first (global_batch % world) ranks take one extra sample.
+  const int base = global_batch / world, extra = global_batch % world;
+  *begin_out = rank * base + std::min(rank, extra);
+  *end_out = *begin_out + base + (rank < extra ? 1 : 0);
+  return NRS_OK;
+}
+
+int nrs_dp_plan_buckets(const int64_t* param_lens, int n_params, size_t bucket_bytes, int64_t* starts_out,
+                        int64_t* ends_out, int capacity) {
+  if (n_params < 0 || (n_params > 0 && !param_lens)) return -1;
+  std::vector<size_t> offsets;
+  size_t total = 0;
+  for (int i = 0; i < n_params; ++i) {
+    if (param_lens[i] < 0) return -1;
+    offsets.push_back(total);
+    total += ((size_t)param_lens[i] + 3) / 4 * 4;
+  }
+  auto b = plan_buckets(offsets, total, bucket_bytes ? bucket_bytes : ((size_t)32 << 20));
+  if (starts_out && ends_out)
+    for (int i = 0; i < (int)b.size() && i < capacity; ++i) {
+      starts_out[i] = (int64_t)b[i].begin;
+      ends_out[i] = (int64_t)b[i].end;
+    }
+  return (int)b.size();
+}
+
+}  // extern "C"

@@ -10,8 +10,8 @@
 // and says along which index each operand is contiguous in memory so the tile
 // loader can keep global loads coalesced.
 //
-// The functions are __host__ __device__ so the index arithmetic can be checked
-// on a CPU against the oracle without a GPU.
+// The functions are __host__ __device__ so the index arithmetic can be unit
+// tested on a CPU, without a GPU.
 #pragma once
 
 #include <cstddef>

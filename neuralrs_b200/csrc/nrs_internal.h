@@ -26,6 +26,12 @@ struct NrsPool {
   }
 };
 
+struct NrsProfRecord {
+  int kind;
+  double work;
+  cudaEvent_t start, stop;
+};
+
 struct nrs_ctx {
   int device = 0;
   cudaStream_t own_stream = nullptr;
@@ -38,6 +44,20 @@ struct nrs_ctx {
   // Grow-only scratch for split-K partial sums and operand staging.
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
+  // Optional per-family device timing (nrs_profile_*).
+  bool profiling = false;
+  std::vector<NrsProfRecord> prof_records;
+  std::vector<cudaEvent_t> prof_free_events;
+};
+
+// Brackets the launches issued during its lifetime with two events when
+// profiling is on; free otherwise.
+struct NrsProfScope {
+  nrs_ctx* ctx;
+  bool active = false;
+  NrsProfRecord rec{};
+  NrsProfScope(nrs_ctx* c, int kind, double work);
+  ~NrsProfScope();
 };
 
 int nrs_fail(nrs_ctx* ctx, int code, const char* fmt, ...);

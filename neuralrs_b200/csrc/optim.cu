@@ -57,6 +57,7 @@ extern "C" int nrs_adamw_step(nrs_ctx* ctx, float* p, const float* grad, float* 
   size_t blocks = (n / 4 + 255) / 256 + 1;
   const size_t cap = (size_t)ctx->sm_count * 16;
   if (blocks > cap) blocks = cap;
+  NrsProfScope prof(ctx, NRS_PROF_ADAMW, 28.0 * (double)n);
   const AdamWArgs a{lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale};
   adamw_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p, grad, m, v, n, a);
   NRS_LAUNCHED(ctx);

@@ -235,6 +235,7 @@ int nrs_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int m, int n, int k, const 
   NRS_REQUIRE(ctx, beta == 0.0f || beta == 1.0f, NRS_ERR_ARG, "nrs_gemm: beta must be 0 or 1");
   if (m == 0 || n == 0) return NRS_OK;
   NRS_REQUIRE(ctx, c && (k == 0 || (a && b)), NRS_ERR_ARG, "nrs_gemm: null operand");
+  NrsProfScope prof(ctx, NRS_PROF_GEMM, 2.0 * m * n * k);
   if (ctx->math_mode != NRS_MATH_FP32 && k > 0) {
     const int st = nrs_tc_gemm(ctx, trans_a, trans_b, 1, m, n, k, a, b, c, bias, act, beta);
     if (st != NRS_ERR_UNSUPPORTED) return st;
@@ -249,6 +250,7 @@ int nrs_bmm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n, int
   NRS_REQUIRE(ctx, beta == 0.0f || beta == 1.0f, NRS_ERR_ARG, "nrs_bmm: beta must be 0 or 1");
   if (batch == 0 || m == 0 || n == 0) return NRS_OK;
   NRS_REQUIRE(ctx, c && (k == 0 || (a && b)), NRS_ERR_ARG, "nrs_bmm: null operand");
+  NrsProfScope prof(ctx, NRS_PROF_GEMM, 2.0 * batch * m * n * k);
   if (ctx->math_mode != NRS_MATH_FP32 && k > 0) {
     const int st = nrs_tc_gemm(ctx, trans_a, trans_b, batch, m, n, k, a, b, c, nullptr, NRS_ACT_NONE, beta);
     if (st != NRS_ERR_UNSUPPORTED) return st;
@@ -264,6 +266,8 @@ int nrs_conv2d_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b,
   NRS_REQUIRE(ctx, act >= NRS_ACT_NONE && act <= NRS_ACT_GELU, NRS_ERR_ARG, "nrs_conv2d_fwd: unknown activation %d", act);
   if (n == 0) return NRS_OK;
   NRS_REQUIRE(ctx, x && w && y, NRS_ERR_ARG, "nrs_conv2d_fwd: null tensor");
+  NrsProfScope prof(ctx, NRS_PROF_CONV_FWD,
+                    2.0 * n * co * ((h + 2 * pad - kh) / stride + 1) * ((wd + 2 * pad - kw) / stride + 1) * ci * kh * kw);
   NrsConvFpropProb p;
   p.g = NrsConvGeom(n, ci, h, wd, co, kh, kw, stride, pad);
   p.M = n * p.g.oh * p.g.ow; p.N = co; p.K = ci * kh * kw; p.batches = 1;
@@ -288,7 +292,9 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
     }
     return NRS_OK;
   }
+  const double conv_flop = 2.0 * n * co * g.oh * g.ow * ci * kh * kw;
   if (dx) {
+    NrsProfScope prof(ctx, NRS_PROF_CONV_DGRAD, conv_flop);
     NrsConvDgradProb p;
     p.g = g; p.M = n * h * wd; p.N = ci; p.K = co * kh * kw; p.batches = 1;
     p.dy = dy; p.wgt = w; p.dx = dx; p.accumulate = accumulate;
@@ -296,6 +302,7 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
     if (st != NRS_OK) return st;
   }
   if (dw) {
+    NrsProfScope prof(ctx, NRS_PROF_CONV_WGRAD, conv_flop);
     NrsConvWgradProb p;
     p.g = g; p.M = co; p.N = ci * kh * kw; p.K = n * g.oh * g.ow; p.batches = 1;
     p.dy = dy; p.x = x; p.dw = dw; p.accumulate = accumulate;

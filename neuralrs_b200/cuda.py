@@ -323,3 +323,134 @@ class optim:
             except Exception:
                 pass
             self.h = None
+
+
+LAYER_KINDS = {"conv": 0, "relu": 1, "maxpool": 2, "flatten": 3, "linear": 4, "gelu": 5}
+
+
+class _LayerSpec(C.Structure):
+    _fields_ = [("kind", C.c_int), ("a", C.c_int), ("b", C.c_int), ("c", C.c_int), ("d", C.c_int), ("e", C.c_int)]
+
+
+class Trainer:
+    """Native training loop for a sequential model (include/nrs_graph.h, nrs_trainer_*).
+
+    `layers` uses the tuples ("conv", c_in, c_out, k, stride, pad), ("relu",), ("gelu",),
+    ("maxpool", k, stride), ("flatten",), ("linear", n_in, n_out).
+    """
+
+    def __init__(self, layers, in_shape, classes, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=1e-4,
+                 fuse=True, ctx: Context | None = None):
+        self.ctx = ctx or default_context()
+        l = self.ctx._l
+        specs = (_LayerSpec * len(layers))()
+        for i, ly in enumerate(layers):
+            vals = [LAYER_KINDS[ly[0]]] + [int(v) for v in ly[1:]]
+            vals += [0] * (6 - len(vals))
+            specs[i] = _LayerSpec(*vals)
+        shp = (C.c_int64 * len(in_shape))(*[int(s) for s in in_shape])
+        h = VP()
+        check(self.ctx.h, l.nrs_trainer_create(self.ctx.h, specs, len(layers), shp, len(in_shape), int(classes),
+                                               C.c_float(lr), C.c_float(beta1), C.c_float(beta2), C.c_float(eps),
+                                               C.c_float(wd), int(bool(fuse)), C.byref(h)))
+        self.h = h
+        self.in_shape = tuple(int(s) for s in in_shape)
+        self.classes = int(classes)
+
+    @property
+    def n_params(self) -> int:
+        return int(self.ctx._l.nrs_trainer_param_count(self.h))
+
+    def param_len(self, i: int) -> int:
+        return int(self.ctx._l.nrs_trainer_param_len(self.h, i))
+
+    def set_params(self, params):
+        assert len(params) == self.n_params
+        for i, p in enumerate(params):
+            a = _f32(p).reshape(-1)
+            assert a.size == self.param_len(i)
+            check(self.ctx.h, self.ctx._l.nrs_trainer_set_param(self.h, i, _ptr(a)))
+
+    def get_param(self, i: int) -> np.ndarray:
+        out = np.empty(self.param_len(i), np.float32)
+        check(self.ctx.h, self.ctx._l.nrs_trainer_get_param(self.h, i, _ptr(out)))
+        return out
+
+    def get_grad(self, i: int) -> np.ndarray:
+        out = np.empty(self.param_len(i), np.float32)
+        check(self.ctx.h, self.ctx._l.nrs_trainer_get_grad(self.h, i, _ptr(out)))
+        return out
+
+    def _host_call(self, fn, x, target, want_loss):
+        x, target = _f32(x), _f32(target)
+        batch = x.shape[0]
+        loss = C.c_float()
+        check(self.ctx.h, fn(self.h, _ptr(x), _ptr(target), batch, C.byref(loss) if want_loss else None))
+        return float(loss.value) if want_loss else None
+
+    def forward_backward(self, x, target, want_loss=True):
+        return self._host_call(self.ctx._l.nrs_trainer_forward_backward, x, target, want_loss)
+
+    def step(self, x, target, want_loss=True):
+        return self._host_call(self.ctx._l.nrs_trainer_step, x, target, want_loss)
+
+    def step_ptr(self, x_host_ptr: int, target_host_ptr: int, batch: int, want_loss=True):
+        """Step from raw HOST pointers (e.g. pinned torch tensors)."""
+        loss = C.c_float()
+        check(self.ctx.h, self.ctx._l.nrs_trainer_step(self.h, VP(x_host_ptr), VP(target_host_ptr), int(batch),
+                                                       C.byref(loss) if want_loss else None))
+        return float(loss.value) if want_loss else None
+
+    def step_device(self, x_dev_ptr: int, target_dev_ptr: int, batch: int, want_loss=False):
+        loss = C.c_float()
+        check(self.ctx.h, self.ctx._l.nrs_trainer_step_device(self.h, VP(x_dev_ptr), VP(target_dev_ptr), int(batch),
+                                                              C.byref(loss) if want_loss else None))
+        return float(loss.value) if want_loss else None
+
+    def last_loss(self) -> float:
+        loss = C.c_float()
+        check(self.ctx.h, self.ctx._l.nrs_trainer_last_loss(self.h, C.byref(loss)))
+        return float(loss.value)
+
+    def enable_dp(self, rank: int, world: int, unique_id: bytes | None, global_batch: int, bucket_bytes: int = 0):
+        buf = C.create_string_buffer(unique_id, 128) if unique_id is not None else None
+        check(self.ctx.h, self.ctx._l.nrs_trainer_enable_dp(self.h, rank, world, buf, int(global_batch),
+                                                            C.c_size_t(bucket_bytes)))
+
+    def close(self):
+        if self.h and self.ctx.h:
+            self.ctx._l.nrs_trainer_free(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def dp_unique_id() -> bytes:
+    buf = C.create_string_buffer(128)
+    st = _lib.lib().nrs_dp_unique_id(buf)
+    if st != 0:
+        raise _lib.NrsError(st, (_lib.lib().nrs_last_error(None) or b"").decode())
+    return buf.raw
+
+
+def dp_shard_range(global_batch: int, rank: int, world: int) -> tuple[int, int]:
+    b, e = C.c_int(), C.c_int()
+    st = _lib.lib().nrs_dp_shard_range(global_batch, rank, world, C.byref(b), C.byref(e))
+    if st != 0:
+        raise _lib.NrsError(st, (_lib.lib().nrs_last_error(None) or b"").decode())
+    return b.value, e.value
+
+
+def dp_plan_buckets(param_lens, bucket_bytes: int) -> list[tuple[int, int]]:
+    l = _lib.lib()
+    lens = (C.c_int64 * len(param_lens))(*[int(v) for v in param_lens])
+    n = l.nrs_dp_plan_buckets(lens, len(param_lens), C.c_size_t(bucket_bytes), None, None, 0)
+    if n < 0:
+        raise ValueError("bad parameter lengths")
+    s, e = (C.c_int64 * max(n, 1))(), (C.c_int64 * max(n, 1))()
+    l.nrs_dp_plan_buckets(lens, len(param_lens), C.c_size_t(bucket_bytes), s, e, n)
+    return [(int(s[i]), int(e[i])) for i in range(n)]

@@ -1,0 +1,269 @@
+"""GPU-vs-CPU twin tests in the shape of the reference's own tests/cuda_*.rs: same
+input formulas, same call sequence through the mirrored API, same (absolute)
+tolerances; the CPU twin is the oracle."""
+import numpy as np
+import pytest
+
+from neuralrs_b200 import cuda
+from neuralrs_b200.cuda import Node, backward_graph, graph, loss, nn, optim
+from neuralrs_b200.cuda import runtime as gpu
+
+pytestmark = pytest.mark.gpu
+
+
+def seq(n, mod, mul, add):
+    return (np.arange(n) % mod * mul + add).astype(np.float32)
+
+
+def on_gpu(data, shape):
+    n = Node.new(data, shape)
+    gpu.to_cuda(n)
+    return n
+
+
+def test_cuda_conv2d_forward(gpu_ctx, oracle32):
+    # tests/cuda_conv2d_test.rs:15-44
+    n, c_in, in_h, in_w, c_out, kh, kw, stride, pad = 2, 3, 8, 8, 4, 3, 3, 1, 1
+    x = seq(n * c_in * in_h * in_w, 23, 0.05, -0.5)
+    w = seq(c_out * c_in * kh * kw, 13, 0.07, -0.4)
+    b = seq(c_out, 5, 0.1, -0.2)
+    cpu_out = oracle32.conv2d_fwd(x.reshape(n, c_in, in_h, in_w), w.reshape(c_out, c_in, kh, kw), b, stride, pad)
+    gout = nn.conv2d(on_gpu(x, [n, c_in, in_h, in_w]), on_gpu(w, [c_out, c_in, kh, kw]), on_gpu(b, [c_out]), stride, pad)
+    assert gout.shape == list(cpu_out.shape)
+    assert np.abs(gpu.to_host(gout) - cpu_out.ravel()).max() < 1e-4
+
+
+def test_cuda_conv2d_backward(gpu_ctx, oracle32):
+    # tests/cuda_conv2d_test.rs:46-97
+    n, c_in, in_h, in_w, c_out, kh, kw, stride, pad = 2, 3, 7, 7, 5, 3, 3, 1, 1
+    x = seq(n * c_in * in_h * in_w, 23, 0.05, -0.5)
+    w = seq(c_out * c_in * kh * kw, 13, 0.07, -0.4)
+    b = seq(c_out, 5, 0.1, -0.2)
+    x4, w4 = x.reshape(n, c_in, in_h, in_w), w.reshape(c_out, c_in, kh, kw)
+    out_len = oracle32.conv2d_fwd(x4, w4, b, stride, pad).size
+    seed = seq(out_len, 7, 0.2, 0.1)
+    c_igrad, c_wgrad, c_bgrad = oracle32.conv2d_bwd(x4, w4, seed.reshape(n, c_out, in_h, in_w), stride, pad)
+    gi, gw, gb = on_gpu(x, [n, c_in, in_h, in_w]), on_gpu(w, [c_out, c_in, kh, kw]), on_gpu(b, [c_out])
+    gout = nn.conv2d(gi, gw, gb, stride, pad)
+    gpu.set_grad(gout, seed)
+    backward_graph(gout)
+    assert np.abs(gpu.read_grad(gi) - c_igrad.ravel()).max() < 1e-3
+    assert np.abs(gpu.read_grad(gw) - c_wgrad.ravel()).max() < 1e-3
+    assert np.abs(gpu.read_grad(gb) - c_bgrad.ravel()).max() < 1e-3
+    # requires_grad = false skips the input gradient (src/cuda/nn/conv.rs:304)
+    gi2 = on_gpu(x, [n, c_in, in_h, in_w])
+    gi2.requires_grad = False
+    gout2 = nn.conv2d(gi2, gw, gb, stride, pad)
+    gpu.set_grad(gout2, seed)
+    backward_graph(gout2)
+    assert np.all(gpu.read_grad(gi2) == 0)
+    assert np.abs(gpu.read_grad(gw) - 2 * c_wgrad.ravel()).max() < 2e-3     # gradients accumulate (+=)
+
+
+def test_cuda_resident_matmul_backward(gpu_ctx, oracle32):
+    # tests/cuda_matmul_resident_test.rs:8-45
+    m, k, n = 40, 56, 32
+    a, b, seed = seq(m * k, 13, 0.1, -0.6), seq(k * n, 7, 0.2, -0.6), seq(m * n, 5, 0.2, 0.1)
+    cc = oracle32.matmul_fwd(a.reshape(m, k), b.reshape(k, n))
+    cga, cgb = oracle32.matmul_bwd(a.reshape(m, k), b.reshape(k, n), seed.reshape(m, n))
+    ga, gb = on_gpu(a, [m, k]), on_gpu(b, [k, n])
+    gc = graph.matmul(ga, gb)
+    assert np.abs(gpu.to_host(gc) - cc.ravel()).max() < 1e-3
+    gpu.set_grad(gc, seed)
+    backward_graph(gc)
+    assert np.abs(gpu.read_grad(ga) - cga.ravel()).max() < 1e-3
+    assert np.abs(gpu.read_grad(gb) - cgb.ravel()).max() < 1e-3
+
+
+def _linear_inputs():
+    batch, in_f, out_f = 16, 24, 10
+    return (batch, in_f, out_f, seq(batch * in_f, 17, 0.1, -0.8), seq(in_f * out_f, 13, 0.05, -0.3),
+            seq(out_f, 5, 0.2, -0.4))
+
+
+def test_cuda_resident_linear_chain(gpu_ctx, oracle32):
+    # tests/cuda_linear_test.rs:8-58
+    batch, in_f, out_f, x, w, bias = _linear_inputs()
+    seed = seq(batch * out_f, 7, 0.2, 0.1)
+    z = oracle32.matmul_fwd(x.reshape(batch, in_f), w.reshape(in_f, out_f))
+    cy = oracle32.bias_add_fwd(z, bias)
+    _, cgb = oracle32.bias_add_bwd(seed.reshape(batch, out_f))
+    cgx, cgw = oracle32.matmul_bwd(x.reshape(batch, in_f), w.reshape(in_f, out_f), seed.reshape(batch, out_f))
+    gx, gw, gb = on_gpu(x, [batch, in_f]), on_gpu(w, [in_f, out_f]), on_gpu(bias, [out_f])
+    gy = graph.add(graph.matmul(gx, gw), gb)
+    assert np.abs(gpu.to_host(gy) - cy.ravel()).max() < 1e-3
+    gpu.set_grad(gy, seed)
+    backward_graph(gy)
+    assert np.abs(gpu.read_grad(gx) - cgx.ravel()).max() < 1e-3
+    assert np.abs(gpu.read_grad(gw) - cgw.ravel()).max() < 1e-3
+    assert np.abs(gpu.read_grad(gb) - cgb.ravel()).max() < 1e-3
+    # the struct form and the fused form agree with the chain
+    gy2 = nn.Linear(gw, gb).forward(gx)
+    assert np.abs(gpu.to_host(gy2) - cy.ravel()).max() < 1e-3
+    gy3 = nn.linear_act(gx, gw, gb, 0)
+    assert np.abs(gpu.to_host(gy3) - cy.ravel()).max() < 1e-3
+
+
+def test_cuda_cross_entropy_through_linear(gpu_ctx, oracle32):
+    # tests/cuda_ce_test.rs:10-59
+    batch, in_f, classes, x, w, bias = _linear_inputs()
+    target = np.zeros((batch, classes), np.float32)
+    target[np.arange(batch), np.arange(batch) % classes] = 1.0
+    logits = oracle32.bias_add_fwd(oracle32.matmul_fwd(x.reshape(batch, in_f), w.reshape(in_f, classes)), bias)
+    cpu_loss = oracle32.ce_fwd(logits, target)
+    g = oracle32.ce_bwd(logits, target)
+    _, cgb = oracle32.bias_add_bwd(g)
+    cgx, cgw = oracle32.matmul_bwd(x.reshape(batch, in_f), w.reshape(in_f, classes), g)
+    gx, gw, gb, gt = on_gpu(x, [batch, in_f]), on_gpu(w, [in_f, classes]), on_gpu(bias, [classes]), on_gpu(target, [batch, classes])
+    glogits = graph.add(graph.matmul(gx, gw), gb)
+    gpu_loss = loss.cross_entropy(glogits, gt)
+    loss.cross_entropy_backward(glogits, gt)
+    backward_graph(glogits)
+    assert abs(gpu_loss - cpu_loss) < 1e-3
+    assert np.abs(gpu.read_grad(gx) - cgx.ravel()).max() < 1e-3
+    assert np.abs(gpu.read_grad(gw) - cgw.ravel()).max() < 1e-3
+    assert np.abs(gpu.read_grad(gb) - cgb.ravel()).max() < 1e-3
+
+
+def test_cuda_adamw_matches_cpu(gpu_ctx, oracle32):
+    # tests/cuda_adamw_test.rs:9-39
+    n = 256
+    init, grad = seq(n, 17, 0.1, -0.8), seq(n, 11, 0.05, -0.25)
+    lr, b1, b2, eps, wd, steps = 0.001, 0.9, 0.999, 1e-8, 0.01, 10
+    p, m, v = init.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    for t in range(steps):
+        oracle32.adamw_step(p, grad, m, v, lr, b1, b2, eps, wd, t)
+    gp = on_gpu(init, [n])
+    gopt = optim.AdamW(lr, b1, b2, eps, wd)
+    for _ in range(steps):
+        gpu.set_grad(gp, grad)
+        gopt.step([gp])
+    assert np.abs(gpu.to_host(gp) - p).max() < 1e-4
+
+
+def test_cuda_adamw_state_roundtrip(gpu_ctx):
+    # tests/cuda_adamw_test.rs:41-83
+    n = 64
+    init = seq(n, 11, 0.1, -0.5)
+    g1, g2, g3 = seq(n, 7, 0.05, 0.01), seq(n, 5, 0.04, -0.08), seq(n, 9, 0.03, 0.02)
+    a, b = on_gpu(init, [n]), on_gpu(init, [n])
+    oa, ob = optim.AdamW(0.01, 0.9, 0.999, 1e-8, 0.01), optim.AdamW(0.01, 0.9, 0.999, 1e-8, 0.01)
+    for g in (g1, g2):
+        gpu.set_grad(a, g); oa.step([a])
+        gpu.set_grad(b, g); ob.step([b])
+    t, moments = ob.export_state()
+    assert t == 2 and len(moments) == 2
+    ob2 = optim.AdamW(0.01, 0.9, 0.999, 1e-8, 0.01)
+    ob2.import_state(t, moments)
+    gpu.set_grad(a, g3); oa.step([a])
+    gpu.set_grad(b, g3); ob2.step([b])
+    assert np.abs(gpu.to_host(a) - gpu.to_host(b)).max() < 1e-6
+
+
+def test_adamw_flat_and_per_tensor_agree(gpu_ctx):
+    rng = np.random.default_rng(0)
+    shapes = [(5, 7), (7,), (3, 3, 3, 3), (3,)]
+    vals = [rng.normal(size=s).astype(np.float32) for s in shapes]
+    grads = [rng.normal(size=s).astype(np.float32) for s in shapes]
+    pa = [on_gpu(v, list(v.shape)) for v in vals]
+    pb = [on_gpu(v, list(v.shape)) for v in vals]
+    gpu.flatten_params(pb)
+    oa, ob = optim.AdamW(0.01, 0.9, 0.999, 1e-8, 0.01), optim.AdamW(0.01, 0.9, 0.999, 1e-8, 0.01)
+    for _ in range(3):
+        for p, g in zip(pa, grads): gpu.set_grad(p, g)
+        for p, g in zip(pb, grads): gpu.set_grad(p, g)
+        oa.step(pa); ob.step(pb)
+    for p, q in zip(pa, pb):
+        assert np.array_equal(gpu.to_host(p), gpu.to_host(q))
+    ta, ma = oa.export_state()
+    tb, mb = ob.export_state()
+    assert ta == tb == 3 and len(ma) == len(mb) == 8
+    for x, y in zip(ma, mb):
+        assert np.array_equal(x, y)
+
+
+@pytest.mark.parametrize("cfg", [(2, 3, 8, 8, 2, 2), (2, 3, 7, 7, 3, 1)])
+def test_cuda_maxpool(gpu_ctx, oracle32, cfg):
+    # tests/cuda_maxpool_test.rs:8-58
+    n, c, in_h, in_w, k, stride = cfg
+    in_len = n * c * in_h * in_w
+    x = ((np.arange(in_len) * 31 + 7) % 97 * 0.05 - 2.0).astype(np.float32)
+    cout, am = oracle32.maxpool_fwd(x.reshape(n, c, in_h, in_w), k, stride)
+    seed = seq(cout.size, 7, 0.2, 0.1)
+    c_igrad = oracle32.maxpool_bwd(seed, am, (n, c, in_h, in_w))
+    gi = on_gpu(x, [n, c, in_h, in_w])
+    gout = nn.maxpool2d(gi, k, stride)
+    assert gout.shape == list(cout.shape)
+    assert np.abs(gpu.to_host(gout) - cout.ravel()).max() < 1e-5
+    gpu.set_grad(gout, seed)
+    backward_graph(gout)
+    assert np.abs(gpu.read_grad(gi) - c_igrad.ravel()).max() < 1e-4
+
+
+def test_cuda_resident_relu_gelu_backward(gpu_ctx, oracle32):
+    # tests/cuda_relu_test.rs:8-39 (+ the gelu twin, tests/cuda_activations_test.rs)
+    n = 4096
+    a, seed = seq(n, 21, 0.1, -1.0), seq(n, 7, 0.3, 0.1)
+    for op, fwd, bwd, tol in ((graph.relu, oracle32.relu_fwd, oracle32.relu_bwd, 1e-4),
+                              (graph.gelu, oracle32.gelu_fwd, oracle32.gelu_bwd, 1e-4)):
+        ga = on_gpu(a, [n])
+        gout = op(ga)
+        assert np.abs(gpu.to_host(gout) - fwd(a)).max() < tol
+        gpu.set_grad(gout, seed)
+        backward_graph(gout)
+        assert np.abs(gpu.read_grad(ga) - bwd(a, seed)).max() < tol
+
+
+def test_branching_graph_accumulates(gpu_ctx, oracle32):
+    # residual: y = relu(x) + x ; both paths add into x.grad (src/autograd/node.rs:113-126)
+    n = 1000
+    a, seed = seq(n, 21, 0.1, -1.0), seq(n, 7, 0.3, 0.1)
+    ga = on_gpu(a, [n])
+    y = graph.add(graph.relu(ga), ga)
+    gpu.set_grad(y, seed)
+    backward_graph(y)
+    assert np.abs(gpu.read_grad(ga) - (oracle32.relu_bwd(a, seed) + seed)).max() < 1e-6
+
+
+def test_layernorm_softmax_manip_graph(gpu_ctx, oracle64):
+    rng = np.random.default_rng(5)
+    rows, f = 12, 16
+    x, g = rng.normal(size=(rows, f)).astype(np.float32), rng.normal(size=(rows, f)).astype(np.float32)
+    gamma, beta = rng.normal(size=f).astype(np.float32), rng.normal(size=f).astype(np.float32)
+    yr, xh, ist = oracle64.layernorm_fwd(x, gamma, beta, 1e-5)
+    dxr, dgr, dbr = oracle64.layernorm_bwd(g, xh, ist, gamma)
+    gx, gg, gb = on_gpu(x, [rows, f]), on_gpu(gamma, [f]), on_gpu(beta, [f])
+    y = nn.layernorm(gx, gg, gb, 1e-5)
+    assert np.abs(gpu.to_host(y) - yr.ravel()).max() < 1e-4
+    gpu.set_grad(y, g)
+    backward_graph(y)
+    assert np.abs(gpu.read_grad(gx) - dxr.ravel()).max() < 1e-4
+    assert np.abs(gpu.read_grad(gg) - dgr).max() < 1e-4
+    assert np.abs(gpu.read_grad(gb) - dbr).max() < 1e-4
+    # softmax -> slice -> concat -> transpose -> scale, gradients through the chain
+    gx2 = on_gpu(x, [rows, f])
+    s = graph.softmax(gx2)
+    parts = [graph.slice_cols(s, 0, 8), graph.slice_cols(s, 8, 16)]
+    cat = graph.concat_cols(parts[::-1])
+    out = graph.scale(graph.transpose(graph.reshape(cat, [1, rows, f])), 0.5)
+    assert out.shape == [1, f, rows]
+    sr = oracle64.softmax_fwd(x)
+    ref = 0.5 * np.concatenate([sr[:, 8:], sr[:, :8]], 1).T
+    assert np.abs(gpu.to_host(out) - ref.ravel()).max() < 1e-6
+    gt = rng.normal(size=(f, rows)).astype(np.float32)
+    gpu.set_grad(out, gt)
+    backward_graph(out)
+    gcat = 0.5 * gt.T
+    gs = np.concatenate([gcat[:, 8:], gcat[:, :8]], 1)
+    assert np.abs(gpu.read_grad(gx2) - oracle64.softmax_bwd(sr, gs).ravel()).max() < 1e-5
+
+
+def test_errors_are_reported_not_fatal(gpu_ctx):
+    a, b = on_gpu(np.zeros(6), [2, 3]), on_gpu(np.zeros(8), [4, 2])
+    with pytest.raises(cuda._lib.NrsError, match="inner dims"):
+        graph.matmul(a, b)
+    host_only = Node.new(np.zeros(6), [2, 3])
+    with pytest.raises(cuda._lib.NrsError, match="not on GPU"):
+        graph.relu(host_only)
+    # the context is still usable afterwards
+    assert np.all(gpu.to_host(graph.relu(a)) == 0)

@@ -1,0 +1,79 @@
+"""Whole-step parity: the native trainer against the reference's CPU training loop
+(oracle/models.py) on the benchmark model families, on identical seeded inputs
+and He-initialised weights.  Bars: loss and every parameter gradient within
+1e-4 relative of the f64-accumulated oracle in 3xTF32/FP32 mode, 1e-2 in TF32."""
+import numpy as np
+import pytest
+
+from neuralrs_b200 import _lib, cuda
+from oracle import models
+from .conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+MODES = [(_lib.MATH_FP32, 1e-4), (_lib.MATH_3XTF32, 1e-4), (_lib.MATH_TF32, 1e-2)]
+
+
+def run_parity(gpu_ctx, oracle64, cfg, batch, seed, fuse, mode, tol, uniform01=False, steps=1):
+    gpu_ctx.set_math_mode(mode)
+    try:
+        params = models.he_init(cfg["layers"], seed)
+        # non-zero biases so their path is exercised
+        rng = np.random.default_rng(seed + 1)
+        for i in range(1, len(params), 2):
+            params[i] = (rng.standard_normal(params[i].shape) * 0.05).astype(np.float32)
+        x, t = models.synthetic_batch(cfg, batch, seed + 2, uniform01)
+        hp = models.ADAMW_HP
+        tr = cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"],
+                          hp["eps"], hp["wd"], fuse=fuse, ctx=gpu_ctx)
+        tr.set_params(params)
+        ref_params = [p.copy() for p in params]
+        loss_ref, grads_ref, _ = models.forward_backward(oracle64, cfg["layers"], ref_params, x, t)
+        loss = tr.forward_backward(x, t)
+        assert abs(loss - loss_ref) <= tol * max(1.0, abs(loss_ref)), (loss, loss_ref)
+        for i, g in enumerate(grads_ref):
+            assert rel_l2(tr.get_grad(i), g) <= tol, f"param {i}"
+        # full steps: parameters after AdamW follow the oracle's trajectory
+        opt = models.OracleAdamW(oracle64, hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], hp["wd"])
+        for s in range(steps):
+            lref = models.train_step(oracle64, cfg["layers"], ref_params, opt, x, t)
+            l = tr.step(x, t)
+            assert abs(l - lref) <= 10 * tol * max(1.0, abs(lref))
+        for i, p in enumerate(ref_params):
+            # one AdamW step moves a weight by ~lr regardless of the gradient's size, so a
+            # sign flip of a near-zero gradient shows up as 2*lr: bound the distance by that.
+            assert np.abs(tr.get_param(i) - p.ravel()).max() <= 2.5 * hp["lr"] * steps
+            assert rel_l2(tr.get_param(i), p) <= 5e-3
+        tr.close()
+    finally:
+        gpu_ctx.set_math_mode(_lib.MATH_3XTF32)
+
+
+@pytest.mark.parametrize("mode,tol", MODES, ids=["fp32", "3xtf32", "tf32"])
+@pytest.mark.parametrize("fuse", [False, True], ids=["unfused", "fused"])
+def test_small_cnn_step(gpu_ctx, oracle64, mode, tol, fuse):
+    run_parity(gpu_ctx, oracle64, models.SMALL_CNN, batch=64, seed=1235, fuse=fuse, mode=mode, tol=tol,
+               uniform01=True, steps=2)
+
+
+@pytest.mark.parametrize("mode,tol", MODES, ids=["fp32", "3xtf32", "tf32"])
+def test_vgg_cifar_step_reduced_batch(gpu_ctx, oracle64, mode, tol):
+    run_parity(gpu_ctx, oracle64, models.VGG_CIFAR, batch=8, seed=1237, fuse=True, mode=mode, tol=tol, steps=1)
+
+
+@pytest.mark.parametrize("mode,tol", MODES, ids=["fp32", "3xtf32", "tf32"])
+def test_mlp_step_reduced_width(gpu_ctx, oracle64, mode, tol):
+    cfg = dict(name="mlp_small", in_shape=(256,), classes=100,
+               layers=[("linear", 256, 512), ("gelu",), ("linear", 512, 512), ("gelu",), ("linear", 512, 100)])
+    run_parity(gpu_ctx, oracle64, cfg, batch=128, seed=1239, fuse=True, mode=mode, tol=tol, steps=2)
+
+
+def test_loss_decreases_over_steps(gpu_ctx):
+    # convergence smoke, as tests/cnn_integration_test.rs does on the CPU path
+    cfg = models.SMALL_CNN
+    tr = cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], lr=1e-3, ctx=gpu_ctx)
+    tr.set_params(models.he_init(cfg["layers"], 7))
+    x, t = models.synthetic_batch(cfg, 64, 8, uniform01=True)
+    losses = [tr.step(x, t) for _ in range(30)]
+    assert losses[-1] < 0.5 * losses[0]
+    tr.close()
