@@ -38,6 +38,50 @@ int nrs_workspace(nrs_ctx* ctx, size_t bytes, void** out) {
   return NRS_OK;
 }
 
+int nrs_ws_slot(nrs_ctx* ctx, int slot, size_t bytes, void** out) {
+  if (slot < 0 || slot >= NRS_WS_COUNT) return nrs_fail(ctx, NRS_ERR_ARG, "workspace: bad slot %d", slot);
+  if (bytes > ctx->ws_slot_bytes[slot]) {
+    if (ctx->ws_slot[slot]) {
+      NRS_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // kernels in flight may still read the old block
+      NRS_CUDA(ctx, cudaFree(ctx->ws_slot[slot]));
+      ctx->ws_slot[slot] = nullptr;
+      ctx->ws_slot_bytes[slot] = 0;
+    }
+    const size_t want = (bytes + ((size_t)1 << 20) - 1) >> 20 << 20;
+    cudaError_t e = cudaMalloc(&ctx->ws_slot[slot], want);
+    if (e != cudaSuccess) {
+      ctx->ws_slot[slot] = nullptr;
+      (void)cudaGetLastError();
+      return nrs_fail(ctx, NRS_ERR_ALLOC, "workspace slot %d: cudaMalloc(%zu) failed: %s", slot, want, cudaGetErrorString(e));
+    }
+    ctx->ws_slot_bytes[slot] = want;
+  }
+  *out = ctx->ws_slot[slot];
+  return NRS_OK;
+}
+
+int nrs_err_flag(nrs_ctx* ctx, int** out) {
+  if (!ctx->err_flag) {
+    NRS_CUDA(ctx, cudaMalloc(&ctx->err_flag, sizeof(int)));
+    NRS_CUDA(ctx, cudaMemsetAsync(ctx->err_flag, 0, sizeof(int), ctx->stream));
+  }
+  *out = ctx->err_flag;
+  return NRS_OK;
+}
+
+int nrs_check_device_error(nrs_ctx* ctx) {
+  if (!ctx->err_flag) return NRS_OK;
+  int code = 0;
+  NRS_CUDA(ctx, cudaMemcpyAsync(&code, ctx->err_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  NRS_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (code == 0) return NRS_OK;
+  NRS_CUDA(ctx, cudaMemsetAsync(ctx->err_flag, 0, sizeof(int), ctx->stream));
+  static const char* what[] = {"", "TMA producer waiting for a free ring slot", "UMMA issuer waiting for a filled ring slot",
+                               "epilogue waiting for the accumulator", "draining outstanding TMA loads"};
+  return nrs_fail(ctx, NRS_ERR_TIMEOUT, "a tensor-core kernel gave up a bounded wait (%s); its output is invalid",
+                  code >= 1 && code <= 4 ? what[code] : "unknown stage");
+}
+
 static cudaEvent_t prof_event(nrs_ctx* ctx) {
   if (!ctx->prof_free_events.empty()) {
     cudaEvent_t e = ctx->prof_free_events.back();
@@ -147,6 +191,8 @@ int nrs_destroy(nrs_ctx* ctx) {
   for (auto& kv : ctx->pool.free_blocks) cudaFree(kv.second);
   for (auto& kv : ctx->pool.live) cudaFree(kv.first);
   if (ctx->workspace) cudaFree(ctx->workspace);
+  for (int i = 0; i < NRS_WS_COUNT; ++i) if (ctx->ws_slot[i]) cudaFree(ctx->ws_slot[i]);
+  if (ctx->err_flag) cudaFree(ctx->err_flag);
   for (auto& r : ctx->prof_records) { cudaEventDestroy(r.start); cudaEventDestroy(r.stop); }
   for (auto& e : ctx->prof_free_events) cudaEventDestroy(e);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
@@ -239,7 +285,7 @@ int nrs_d2h(nrs_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes) {
   NRS_REQUIRE(ctx, (dst_host && src_dev) || bytes == 0, NRS_ERR_ARG, "nrs_d2h: null pointer");
   if (bytes) NRS_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
   NRS_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  return NRS_OK;
+  return nrs_check_device_error(ctx);
 }
 
 int nrs_d2d(nrs_ctx* ctx, void* dst_dev, const void* src_dev, size_t bytes) {
@@ -252,7 +298,7 @@ int nrs_d2d(nrs_ctx* ctx, void* dst_dev, const void* src_dev, size_t bytes) {
 int nrs_sync(nrs_ctx* ctx) {
   NRS_REQUIRE_CTX(ctx);
   NRS_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  return NRS_OK;
+  return nrs_check_device_error(ctx);
 }
 
 }  // extern "C"

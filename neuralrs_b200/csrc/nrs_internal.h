@@ -44,6 +44,11 @@ struct nrs_ctx {
   // Grow-only scratch for split-K partial sums and operand staging.
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
+  // Named grow-only scratch blocks (operand staging for the tensor-core kernels).
+  void* ws_slot[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t ws_slot_bytes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  // Device word the tensor-core kernels set when a bounded wait runs out; read at sync points.
+  int* err_flag = nullptr;
   // Optional per-family device timing (nrs_profile_*).
   bool profiling = false;
   std::vector<NrsProfRecord> prof_records;
@@ -62,6 +67,11 @@ struct NrsProfScope {
 
 int nrs_fail(nrs_ctx* ctx, int code, const char* fmt, ...);
 int nrs_workspace(nrs_ctx* ctx, size_t bytes, void** out);
+enum { NRS_WS_A_HI = 0, NRS_WS_A_LO = 1, NRS_WS_B_HI = 2, NRS_WS_B_LO = 3, NRS_WS_PARTIAL = 4, NRS_WS_COUNT = 8 };
+int nrs_ws_slot(nrs_ctx* ctx, int slot, size_t bytes, void** out);
+int nrs_err_flag(nrs_ctx* ctx, int** out);
+// Reads and clears the device error word (the stream must be idle); NRS_ERR_TIMEOUT if a kernel gave up a wait.
+int nrs_check_device_error(nrs_ctx* ctx);
 
 #define NRS_REQUIRE_CTX(ctx) \
   do { if (!(ctx)) return nrs_fail(nullptr, NRS_ERR_ARG, "%s: null context", __func__); } while (0)

@@ -281,17 +281,17 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
   NRS_REQUIRE_CTX(ctx);
   int st = check_conv_dims(ctx, "nrs_conv2d_bwd", n, ci, h, wd, co, kh, kw, stride, pad);
   if (st != NRS_OK) return st;
-  NRS_REQUIRE(ctx, dy || n == 0, NRS_ERR_ARG, "nrs_conv2d_bwd: null dy");
-  NRS_REQUIRE(ctx, !dx || w, NRS_ERR_ARG, "nrs_conv2d_bwd: dx requested without w");
-  NRS_REQUIRE(ctx, !dw || x, NRS_ERR_ARG, "nrs_conv2d_bwd: dw requested without x");
   const NrsConvGeom g(n, ci, h, wd, co, kh, kw, stride, pad);
-  if (n == 0) {
+  if (n == 0) {  // an empty batch contributes zero gradients
     if (!accumulate) {
       if (dw) NRS_CUDA(ctx, cudaMemsetAsync(dw, 0, sizeof(float) * co * ci * kh * kw, ctx->stream));
       if (db) NRS_CUDA(ctx, cudaMemsetAsync(db, 0, sizeof(float) * co, ctx->stream));
     }
     return NRS_OK;
   }
+  NRS_REQUIRE(ctx, dy != nullptr, NRS_ERR_ARG, "nrs_conv2d_bwd: null dy");
+  NRS_REQUIRE(ctx, !dx || w, NRS_ERR_ARG, "nrs_conv2d_bwd: dx requested without w");
+  NRS_REQUIRE(ctx, !dw || x, NRS_ERR_ARG, "nrs_conv2d_bwd: dw requested without x");
   const double conv_flop = 2.0 * n * co * g.oh * g.ow * ci * kh * kw;
   if (dx) {
     NrsProfScope prof(ctx, NRS_PROF_CONV_DGRAD, conv_flop);

@@ -173,13 +173,15 @@ def test_adamw_flat_and_per_tensor_agree(gpu_ctx):
         for p, g in zip(pa, grads): gpu.set_grad(p, g)
         for p, g in zip(pb, grads): gpu.set_grad(p, g)
         oa.step(pa); ob.step(pb)
+    # the flat launch takes the 128-bit path, single tensors may take the scalar tail:
+    # same formula, fused-multiply-add contraction may differ by an ulp
     for p, q in zip(pa, pb):
-        assert np.array_equal(gpu.to_host(p), gpu.to_host(q))
+        assert np.abs(gpu.to_host(p) - gpu.to_host(q)).max() <= 1e-6
     ta, ma = oa.export_state()
     tb, mb = ob.export_state()
     assert ta == tb == 3 and len(ma) == len(mb) == 8
     for x, y in zip(ma, mb):
-        assert np.array_equal(x, y)
+        assert np.abs(x - y).max() <= 1e-6
 
 
 @pytest.mark.parametrize("cfg", [(2, 3, 8, 8, 2, 2), (2, 3, 7, 7, 3, 1)])
