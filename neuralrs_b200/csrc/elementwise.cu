@@ -132,33 +132,47 @@ __global__ void colsum_fold_kernel(const float* __restrict__ partial, float* __r
 }
 
 // out[c] (+)= sum over n and the `plane` contiguous elements of channel c.
-// One block per (channel, sample-split); float4 reads along the plane.
+// One block per (channel, sample-split).  Each warp walks its own images (8 in
+// flight per block, 128-bit loads along the plane); warp sums are folded in a
+// fixed order, so the result is run-to-run deterministic.
 __global__ void __launch_bounds__(256)
 chansum_kernel(const float* __restrict__ g, float* __restrict__ out, int n, int c, int plane, int splits,
                int accumulate, float* __restrict__ partial) {
   __shared__ float sm[8];
   const int ch = blockIdx.x, split = blockIdx.y;
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
   const int n_per = (n + splits - 1) / splits;
   const int n0 = split * n_per, n1 = min(n, n0 + n_per);
   float s = 0.0f;
-  for (int img = n0; img < n1; ++img) {
+  const bool vec = (plane & 3) == 0 && aligned16(g);
+  for (int img = n0 + wrp; img < n1; img += 8) {
     const float* base = g + ((size_t)img * c + ch) * plane;
-    if ((plane & 3) == 0 && aligned16(base)) {
-      for (int i = threadIdx.x; i < plane / 4; i += blockDim.x) {
-        const float4 v = reinterpret_cast<const float4*>(base)[i];
-        s += (v.x + v.y) + (v.z + v.w);
+    if (vec) {
+      float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+      int i = lane;
+      for (; i + 32 < plane / 4; i += 64) {
+        const float4 v0 = reinterpret_cast<const float4*>(base)[i];
+        const float4 v1 = reinterpret_cast<const float4*>(base)[i + 32];
+        a0.x += v0.x; a0.y += v0.y; a0.z += v0.z; a0.w += v0.w;
+        a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
       }
+      for (; i < plane / 4; i += 32) {
+        const float4 v0 = reinterpret_cast<const float4*>(base)[i];
+        a0.x += v0.x; a0.y += v0.y; a0.z += v0.z; a0.w += v0.w;
+      }
+      s += ((a0.x + a0.y) + (a0.z + a0.w)) + ((a1.x + a1.y) + (a1.z + a1.w));
     } else {
-      for (int i = threadIdx.x; i < plane; i += blockDim.x) s += base[i];
+      for (int i = lane; i < plane; i += 32) s += base[i];
     }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = s;
+  if (lane == 0) sm[wrp] = s;
   __syncthreads();
   if (threadIdx.x == 0) {
     float t = 0.0f;
-    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += sm[i];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += sm[i];
     if (splits > 1) partial[(size_t)split * c + ch] = t;
     else out[ch] = accumulate ? out[ch] + t : t;
   }
@@ -279,9 +293,9 @@ int nrs_channel_sum(nrs_ctx* ctx, const float* g, float* out, int n, int c, int 
   if (c == 0) return NRS_OK;
   NRS_REQUIRE(ctx, out && (n == 0 || plane == 0 || g), NRS_ERR_ARG, "nrs_channel_sum: null tensor");
   int splits = 1;
-  if (c < 2 * ctx->sm_count && n >= 8) {
-    splits = (2 * ctx->sm_count + c - 1) / c;
-    if (splits > n / 4) splits = n / 4;
+  if (c < 16 * ctx->sm_count && n >= 16) {
+    splits = (16 * ctx->sm_count + c - 1) / c;
+    if (splits > n / 8) splits = n / 8;
     if (splits < 1) splits = 1;
     if (splits > 65535) splits = 65535;
   }

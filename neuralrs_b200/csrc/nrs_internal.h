@@ -103,3 +103,9 @@ static inline unsigned nrs_blocks(size_t work, unsigned per_block) {
 // what the tcgen05 kernels cover, and the caller then runs the FFMA kernels.
 int nrs_tc_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n, int k,
                 const float* a, const float* b, float* c, const float* bias, int act, float beta);
+int nrs_tc_conv_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y, int n, int ci, int h,
+                    int wd, int co, int kh, int kw, int stride, int pad, int act);
+int nrs_tc_conv_dgrad(nrs_ctx* ctx, const float* w, const float* dy, float* dx, int n, int ci, int h, int wd, int co,
+                      int kh, int kw, int stride, int pad, int accumulate);
+int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
+                      int kh, int kw, int stride, int pad, int accumulate);

@@ -268,6 +268,10 @@ int nrs_conv2d_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b,
   NRS_REQUIRE(ctx, x && w && y, NRS_ERR_ARG, "nrs_conv2d_fwd: null tensor");
   NrsProfScope prof(ctx, NRS_PROF_CONV_FWD,
                     2.0 * n * co * ((h + 2 * pad - kh) / stride + 1) * ((wd + 2 * pad - kw) / stride + 1) * ci * kh * kw);
+  if (ctx->math_mode != NRS_MATH_FP32) {
+    st = nrs_tc_conv_fwd(ctx, x, w, b, y, n, ci, h, wd, co, kh, kw, stride, pad, act);
+    if (st != NRS_ERR_UNSUPPORTED) return st;
+  }
   NrsConvFpropProb p;
   p.g = NrsConvGeom(n, ci, h, wd, co, kh, kw, stride, pad);
   p.M = n * p.g.oh * p.g.ow; p.N = co; p.K = ci * kh * kw; p.batches = 1;
@@ -295,19 +299,31 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
   const double conv_flop = 2.0 * n * co * g.oh * g.ow * ci * kh * kw;
   if (dx) {
     NrsProfScope prof(ctx, NRS_PROF_CONV_DGRAD, conv_flop);
+    st = ctx->math_mode != NRS_MATH_FP32
+             ? nrs_tc_conv_dgrad(ctx, w, dy, dx, n, ci, h, wd, co, kh, kw, stride, pad, accumulate)
+             : NRS_ERR_UNSUPPORTED;
+    if (st != NRS_OK && st != NRS_ERR_UNSUPPORTED) return st;
+    if (st == NRS_ERR_UNSUPPORTED) {
     NrsConvDgradProb p;
     p.g = g; p.M = n * h * wd; p.N = ci; p.K = co * kh * kw; p.batches = 1;
     p.dy = dy; p.wgt = w; p.dx = dx; p.accumulate = accumulate;
     st = run_igemm(ctx, p, "nrs_conv2d_bwd(dx)");
     if (st != NRS_OK) return st;
+    }
   }
   if (dw) {
     NrsProfScope prof(ctx, NRS_PROF_CONV_WGRAD, conv_flop);
+    st = ctx->math_mode != NRS_MATH_FP32
+             ? nrs_tc_conv_wgrad(ctx, x, dy, dw, n, ci, h, wd, co, kh, kw, stride, pad, accumulate)
+             : NRS_ERR_UNSUPPORTED;
+    if (st != NRS_OK && st != NRS_ERR_UNSUPPORTED) return st;
+    if (st == NRS_ERR_UNSUPPORTED) {
     NrsConvWgradProb p;
     p.g = g; p.M = co; p.N = ci * kh * kw; p.K = n * g.oh * g.ow; p.batches = 1;
     p.dy = dy; p.x = x; p.dw = dw; p.accumulate = accumulate;
     st = run_igemm(ctx, p, "nrs_conv2d_bwd(dw)");
     if (st != NRS_OK) return st;
+    }
   }
   if (db) {
     st = nrs_channel_sum(ctx, dy, db, n, co, g.oh * g.ow, accumulate);

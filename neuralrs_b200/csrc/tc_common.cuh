@@ -146,6 +146,17 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
          ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// The same descriptor for MN-major 32-bit operands.  kind::tf32 accepts an MN-major
+// operand only in the "128-byte swizzle, 32-byte atom" layout (layout type 1): the 16-byte
+// chunk index bits [5,7) are XORed with the row bits [7,9), so the pattern repeats every
+// 4 K-rows (512 B).  One UMMA K-step (8 elements of K) spans two such groups, SBO apart;
+// 32-element blocks along MN sit LBO apart.  TMA writes this layout with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+__device__ __forceinline__ uint64_t make_smem_desc_sw128_32b(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (1ull << 61);
+}
+
 // Round-to-nearest TF32 of an f32 (low 13 mantissa bits cleared in the result).
 __device__ __forceinline__ float tf32_rn(float x) {
   uint32_t u;
@@ -179,7 +190,7 @@ inline PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
 // f32 tensor of `rank` dims (dim[0] innermost, contiguous), strides in BYTES for dims 1..rank-1
 // (multiples of 16), box extents per dim (box[0]*4 must be 128 for the 128-byte swizzle).
 inline bool encode_tmap_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dim, const uint64_t* stride_bytes,
-                            const uint32_t* box) {
+                            const uint32_t* box, bool atom32 = false) {
   auto enc = tensor_map_encoder();
   if (!enc) return false;
   cuuint64_t gdim[5];
@@ -188,7 +199,8 @@ inline bool encode_tmap_f32(CUtensorMap* out, const void* base, int rank, const 
   for (int i = 0; i < rank; ++i) { gdim[i] = dim[i]; bx[i] = box[i]; es[i] = 1; }
   for (int i = 0; i + 1 < rank; ++i) gstr[i] = stride_bytes[i];
   const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }

@@ -1,0 +1,196 @@
+// Convolution forward and data gradient as implicit GEMM on tcgen05 (TF32 / 3xTF32).
+//
+// No im2col matrix exists anywhere.  The activation is staged once as NHWC
+// (channels innermost) planes; output pixels are GEMM rows (a tile is Wt x Ht x Nt
+// = up to 128 pixels of Nt images), output channels are GEMM columns, and the
+// reduction runs over (tap, 32-channel block).  For every tap the A slice is ONE
+// 4-D TMA box {32 channels, Wt, Ht, Nt} whose spatial origin is shifted by the
+// tap offset; rows or columns that fall outside the image are zero-filled by TMA,
+// which is exactly the zero padding.  (The shift lands on the W/H coordinates;
+// the innermost, 16-byte-aligned coordinate is the channel block.)  The B slice
+// is a plain 2-D box of the re-laid-out weights [out_ch][(tap, in_ch)].
+//
+//   forward        y[n,co,oy,ox]  = act(b[co] + sum x[n,ci,oy+i-p,ox+j-p] w[co,ci,i,j])
+//   data gradient  dx[n,ci,y,x] (+)= sum dy[n,co,y-i+p,x-j+p] w[co,ci,i,j]
+// are the same kernel with the tap sign flipped and the roles of the channel
+// counts exchanged.  The epilogue writes NCHW directly: for a fixed channel the 32
+// lanes of a warp hold 32 consecutive pixels, so every store is a full 128-byte line.
+//
+// Stride-1 convolutions with channel counts that are multiples of 32 run here;
+// everything else (first layers with 1 or 3 channels, strides) runs on the FFMA
+// implicit-GEMM kernel.
+//
+// Reference counterparts: conv2d_im2col + matmul_nn + conv2d_col2out (forward),
+// conv2d_out2mm + matmul_tn + conv2d_col2im (data gradient) — src/cuda/nn/conv.rs:27-149,
+// 244-312.
+#include "tc_mainloop.cuh"
+
+namespace {
+
+struct ConvPolicy {
+  int Wt, Ht, Nt, tiles_y;
+  int out_h, out_w, n_img, n_ch_out;
+  int cblocks, kw_taps;
+  int sgn, base_y, base_x;
+  float* out;
+  const float* bias;
+  int act, accumulate;
+  uint32_t slice_bytes;
+
+  __device__ __forceinline__ uint32_t a_slice_bytes() const { return slice_bytes; }
+  __device__ __forceinline__ void load_a(void* dst, const CUtensorMap* tm, uint64_t* bar, int kb, int tile_m, int) const {
+    const int tap = kb / cblocks, cb = kb - tap * cblocks;
+    const int i = tap / kw_taps, j = tap - i * kw_taps;
+    const int n0 = (tile_m / tiles_y) * Nt, y0 = (tile_m % tiles_y) * Ht;
+    tc::tma_load_4d(dst, tm, bar, cb * 32, sgn * j + base_x, y0 + sgn * i + base_y, n0);
+  }
+  __device__ __forceinline__ bool locate(int tile_m, int row, size_t* pix_off) const {
+    if (row >= Wt * Ht * Nt) return false;
+    const int xt = row % Wt, t = row / Wt;
+    const int yt = t % Ht, nt = t / Ht;
+    const int n = (tile_m / tiles_y) * Nt + nt, y = (tile_m % tiles_y) * Ht + yt;
+    if (n >= n_img || y >= out_h) return false;
+    *pix_off = (size_t)n * n_ch_out * out_h * out_w + (size_t)y * out_w + xt;
+    return true;
+  }
+  __device__ __forceinline__ void store(int tile_m, int, int row, int ch, float v) const {
+    size_t off;
+    if (ch >= n_ch_out || !locate(tile_m, row, &off)) return;
+    float* dst = out + off + (size_t)ch * out_h * out_w;
+    if (bias) v += bias[ch];
+    v = nrs_apply_act(v, act);
+    *dst = accumulate ? *dst + v : v;
+  }
+  __device__ __forceinline__ void epilogue(int tile_m, int, int row, int nb, int ncols, const uint32_t (&r)[32]) const {
+    size_t off;
+    if (!locate(tile_m, row, &off)) return;
+    const size_t plane = (size_t)out_h * out_w;
+    float* dst = out + off + (size_t)nb * plane;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < ncols && nb + j < n_ch_out) {
+        float v = __uint_as_float(r[j]);
+        if (bias) v += bias[nb + j];
+        v = nrs_apply_act(v, act);
+        if (accumulate) v += dst[(size_t)j * plane];
+        dst[(size_t)j * plane] = v;
+      }
+    }
+  }
+};
+
+struct ConvPlan {
+  // activation read by the A operand: [n_img][a_h][a_w][a_ch] NHWC planes, staged from NCHW `act_src`
+  const float* act_src;
+  int n_img, a_ch, a_h, a_w;
+  // weights and which re-layout
+  const float* w;
+  int co, ci, kh, kw, for_dgrad;
+  // output NCHW [n_img][n_ch_out][out_h][out_w]
+  float* out;
+  int n_ch_out, out_h, out_w;
+  int sgn, base;
+  const float* bias;
+  int act, accumulate;
+};
+
+template <int BN, int NPLANES>
+int run_conv(nrs_ctx* ctx, const ConvPlan& p, const float* a_hi, const float* a_lo, const float* w_hi, const float* w_lo,
+             const ConvPolicy& pol, int tiles_m) {
+  const int taps = p.kh * p.kw;
+  const int kdim = taps * p.a_ch;
+  CUtensorMap ta_hi, ta_lo, tb_hi, tb_lo;
+  const uint64_t adim[4] = {(uint64_t)p.a_ch, (uint64_t)p.a_w, (uint64_t)p.a_h, (uint64_t)p.n_img};
+  const uint64_t astr[3] = {(uint64_t)p.a_ch * 4, (uint64_t)p.a_w * p.a_ch * 4, (uint64_t)p.a_h * p.a_w * p.a_ch * 4};
+  const uint32_t abox[4] = {32, (uint32_t)pol.Wt, (uint32_t)pol.Ht, (uint32_t)pol.Nt};
+  const uint64_t bdim[3] = {(uint64_t)kdim, (uint64_t)p.n_ch_out, 1};
+  const uint64_t bstr[2] = {(uint64_t)kdim * 4, (uint64_t)kdim * p.n_ch_out * 4};
+  const uint32_t bbox[3] = {32, (uint32_t)BN, 1};
+  bool ok = tc::encode_tmap_f32(&ta_hi, a_hi, 4, adim, astr, abox) && tc::encode_tmap_f32(&tb_hi, w_hi, 3, bdim, bstr, bbox);
+  if (NPLANES == 2) ok = ok && tc::encode_tmap_f32(&ta_lo, a_lo, 4, adim, astr, abox) && tc::encode_tmap_f32(&tb_lo, w_lo, 3, bdim, bstr, bbox);
+  else { ta_lo = ta_hi; tb_lo = tb_hi; }
+  NRS_REQUIRE(ctx, ok, NRS_ERR_CUDA, "tc_conv: cuTensorMapEncodeTiled failed");
+  return tc::launch<BN, NPLANES, ConvPolicy>(ctx, ta_hi, ta_lo, tb_hi, tb_lo, pol, tiles_m, p.n_ch_out, 1, taps * (p.a_ch / 32),
+                                             "tc_conv");
+}
+
+int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
+  if (!tc::tensor_map_encoder() || getenv("NRS_DISABLE_TC")) return NRS_ERR_UNSUPPORTED;
+  if (p.a_ch % 32 != 0 || p.n_ch_out % 32 != 0 || p.out_w > 128 || p.out_w < 1) return NRS_ERR_UNSUPPORTED;
+  if (p.a_w > 256 * 1024 || p.n_img < 1) return NRS_ERR_UNSUPPORTED;
+  const bool split = ctx->math_mode == NRS_MATH_3XTF32;
+
+  // tile geometry in output space
+  ConvPolicy pol{};
+  pol.Wt = p.out_w;
+  pol.Ht = 128 / pol.Wt;
+  if (pol.Ht > p.out_h) pol.Ht = p.out_h;
+  pol.Nt = 1;
+  if (pol.Ht == p.out_h) {
+    pol.Nt = 128 / (pol.Wt * pol.Ht);
+    if (pol.Nt > p.n_img) pol.Nt = p.n_img;
+    if (pol.Nt < 1) pol.Nt = 1;
+  }
+  // keep every TMA box inside the tensor's extents (only the origin may leave it)
+  if (pol.Wt > p.a_w || pol.Ht > p.a_h || pol.Nt > p.n_img) return NRS_ERR_UNSUPPORTED;
+  pol.tiles_y = (p.out_h + pol.Ht - 1) / pol.Ht;
+  const long tiles_m = (long)((p.n_img + pol.Nt - 1) / pol.Nt) * pol.tiles_y;
+  if (tiles_m > 2147483647L) return NRS_ERR_UNSUPPORTED;
+  pol.out_h = p.out_h; pol.out_w = p.out_w; pol.n_img = p.n_img; pol.n_ch_out = p.n_ch_out;
+  pol.cblocks = p.a_ch / 32; pol.kw_taps = p.kw;
+  pol.sgn = p.sgn; pol.base_y = p.base; pol.base_x = p.base;
+  pol.out = p.out; pol.bias = p.bias; pol.act = p.act; pol.accumulate = p.accumulate;
+  pol.slice_bytes = (uint32_t)(pol.Wt * pol.Ht * pol.Nt) * 128u;
+
+  // stage the activation: per image [C][H*W] -> [H*W][C] planes
+  const size_t a_plane = (size_t)p.n_img * p.a_h * p.a_w * p.a_ch;
+  const size_t w_plane = (size_t)p.co * p.ci * p.kh * p.kw;
+  void *a_hi = nullptr, *a_lo = nullptr, *w_hi = nullptr, *w_lo = nullptr;
+  int st = nrs_ws_slot(ctx, NRS_WS_A_HI, a_plane * sizeof(float), &a_hi);
+  if (st == NRS_OK && split) st = nrs_ws_slot(ctx, NRS_WS_A_LO, a_plane * sizeof(float), &a_lo);
+  if (st == NRS_OK) st = nrs_ws_slot(ctx, NRS_WS_B_HI, w_plane * sizeof(float), &w_hi);
+  if (st == NRS_OK && split) st = nrs_ws_slot(ctx, NRS_WS_B_LO, w_plane * sizeof(float), &w_lo);
+  if (st != NRS_OK) return st;
+  const size_t img = (size_t)p.a_h * p.a_w * p.a_ch;
+  st = nrs_tc_stage(ctx, p.act_src, (float*)a_hi, (float*)a_lo, p.a_h * p.a_w, p.a_ch, p.a_ch, p.n_img, img, img, true);
+  if (st != NRS_OK) return st;
+  st = nrs_tc_stage_conv_weight(ctx, p.w, (float*)w_hi, (float*)w_lo, p.co, p.ci, p.kh, p.kw, p.for_dgrad);
+  if (st != NRS_OK) return st;
+
+  const int bn = p.n_ch_out % 128 == 0 ? 128 : (p.n_ch_out % 64 == 0 ? 64 : 32);
+#define NRS_RUN(BN_)                                                                                                     \
+  return split ? run_conv<BN_, 2>(ctx, p, (const float*)a_hi, (const float*)a_lo, (const float*)w_hi, (const float*)w_lo, pol, (int)tiles_m) \
+               : run_conv<BN_, 1>(ctx, p, (const float*)a_hi, nullptr, (const float*)w_hi, nullptr, pol, (int)tiles_m)
+  if (bn == 128) { NRS_RUN(128); }
+  if (bn == 64) { NRS_RUN(64); }
+  NRS_RUN(32);
+#undef NRS_RUN
+}
+
+}  // namespace
+
+// y = act(conv(x, w) + b); NRS_ERR_UNSUPPORTED when the shape is outside this kernel's range.
+int nrs_tc_conv_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y, int n, int ci, int h,
+                    int wd, int co, int kh, int kw, int stride, int pad, int act) {
+  if (stride != 1) return NRS_ERR_UNSUPPORTED;
+  ConvPlan p{};
+  p.act_src = x; p.n_img = n; p.a_ch = ci; p.a_h = h; p.a_w = wd;
+  p.w = w; p.co = co; p.ci = ci; p.kh = kh; p.kw = kw; p.for_dgrad = 0;
+  p.out = y; p.n_ch_out = co; p.out_h = h + 2 * pad - kh + 1; p.out_w = wd + 2 * pad - kw + 1;
+  p.sgn = 1; p.base = -pad;
+  p.bias = b; p.act = act; p.accumulate = 0;
+  return conv_common(ctx, p);
+}
+
+// dx (+)= conv_transpose(dy, w)
+int nrs_tc_conv_dgrad(nrs_ctx* ctx, const float* w, const float* dy, float* dx, int n, int ci, int h, int wd, int co,
+                      int kh, int kw, int stride, int pad, int accumulate) {
+  if (stride != 1) return NRS_ERR_UNSUPPORTED;
+  ConvPlan p{};
+  p.act_src = dy; p.n_img = n; p.a_ch = co; p.a_h = h + 2 * pad - kh + 1; p.a_w = wd + 2 * pad - kw + 1;
+  p.w = w; p.co = co; p.ci = ci; p.kh = kh; p.kw = kw; p.for_dgrad = 1;
+  p.out = dx; p.n_ch_out = ci; p.out_h = h; p.out_w = wd;
+  p.sgn = -1; p.base = pad;
+  p.bias = nullptr; p.act = NRS_ACT_NONE; p.accumulate = accumulate;
+  return conv_common(ctx, p);
+}

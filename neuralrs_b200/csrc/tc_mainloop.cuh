@@ -1,0 +1,276 @@
+// Shared tcgen05 main loop: D[128 x BN] (TMEM, f32) = sum over K-slices of
+// A[128 x 32] . B[BN x 32]^T, both operands K-major in 128-byte-swizzled shared
+// memory, fed by TMA, consumed by tcgen05.mma kind::tf32.
+//
+// One CTA per (row tile, column tile, batch x K-split).  Six warps, fixed roles:
+//   warp 0     TMA producer (one thread): per K-slice, one mbarrier-tracked ring
+//              slot holding the A and B slices (and their residual planes for 3xTF32)
+//   warp 1     TMEM allocation; one thread issues the UMMAs (M=128, N=BN, K=8) and
+//              commits ring slots back to the producer, then the accumulator to the
+//              epilogue
+//   warps 2-5  epilogue: tcgen05.ld (thread = accumulator row), policy-defined store
+// A Policy supplies how an A slice is fetched (dense rows for GEMM, a shifted
+// NHWC window for convolution) and what the epilogue does with a row of results.
+//
+// 3xTF32 (NPLANES == 2): per K-slice three UMMAs lo*hi + hi*lo + hi*hi accumulate
+// into the same TMEM tile.  The tensor core's f32 accumulation is not
+// round-to-nearest; its error grows linearly with the length of one
+// accumulation chain (about 7e-9 relative per K element), so callers keep a
+// chain at or below kMaxChainK by splitting K across CTAs, whose partial tiles
+// are summed in f32 by tc_splitk_reduce_kernel in a fixed order.
+//
+// Every mbarrier wait is bounded: on expiry the kernel records an error code,
+// waits (bounded) for TMA loads it already issued, frees its TMEM and returns.
+#pragma once
+
+#include "igemm_problems.cuh"
+#include "nrs_internal.h"
+#include "tc_common.cuh"
+
+namespace tc {
+
+constexpr int BM = 128, BK = 32;   // BK f32 = 128 bytes = one swizzle row
+constexpr int kThreads = 192;
+constexpr int kMaxChainK = 4096;   // longest single accumulation chain in 3xTF32 mode
+
+template <int BN, int NPLANES>
+struct SmemLayout {
+  static constexpr int kATile = BM * BK * 4;   // 16 KB
+  static constexpr int kBTile = BN * BK * 4;
+  static constexpr int kStage = NPLANES * (kATile + kBTile);
+  static constexpr int kStages = (200 * 1024) / kStage >= 8 ? 8 : (200 * 1024) / kStage;
+  static constexpr int kBytes = kStages * kStage + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+};
+
+struct SplitInfo {
+  int splits;          // K-splits per (tile, batch)
+  int kb_per_split;    // K-slices per split
+  int kb_total;        // K-slices in all
+  int batches;
+  float* partial;      // [split][batch][tiles_m*128][n_total] when splits > 1
+  int n_total;
+  int rows_total;      // tiles_m * 128
+};
+
+template <int BN, int NPLANES, class Policy>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
+          const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
+          const Policy pol, const SplitInfo sp, int* __restrict__ err_flag) {
+  using L = SmemLayout<BN, NPLANES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStage);
+  uint64_t* empty_bar = full_bar + L::kStages;
+  uint64_t* accum_bar = empty_bar + L::kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_m = blockIdx.x, n0 = blockIdx.y * BN;
+  const int batch = blockIdx.z / sp.splits, split = blockIdx.z - batch * sp.splits;
+  const int kb_begin = split * sp.kb_per_split;
+  const int kb_end = min(sp.kb_total, kb_begin + sp.kb_per_split);
+  const int nkb = kb_end - kb_begin;   // >= 1 by construction
+
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tm_a_hi);
+    prefetch_tmap(&tm_b_hi);
+    if (NPLANES == 2) { prefetch_tmap(&tm_a_lo); prefetch_tmap(&tm_b_lo); }
+    for (int s = 0; s < L::kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(accum_bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, L::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer
+      const uint32_t stage_bytes = (uint32_t)NPLANES * (pol.a_slice_bytes() + (uint32_t)L::kBTile);
+      int issued = 0;
+      bool ok = true;
+      for (int it = 0; it < nkb; ++it, ++issued) {
+        const int s = it % L::kStages;
+        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(err_flag, kErrProducerWait); ok = false; break; }
+        uint8_t* st = smem + s * L::kStage;
+        const int kb = kb_begin + it;
+        mbar_expect_tx(&full_bar[s], stage_bytes);
+        pol.load_a(st, &tm_a_hi, &full_bar[s], kb, tile_m, batch);
+        tma_load_3d(st + L::kATile, &tm_b_hi, &full_bar[s], kb * BK, n0, batch);
+        if (NPLANES == 2) {
+          pol.load_a(st + L::kATile + L::kBTile, &tm_a_lo, &full_bar[s], kb, tile_m, batch);
+          tma_load_3d(st + 2 * L::kATile + L::kBTile, &tm_b_lo, &full_bar[s], kb * BK, n0, batch);
+        }
+      }
+      if (!ok) {
+        // Loads already issued still land in this CTA's shared memory: wait for them
+        // (bounded) before the CTA may retire.
+        for (int it = (issued > L::kStages ? issued - L::kStages : 0); it < issued; ++it) {
+          const int s = it % L::kStages;
+          if (!mbar_wait(&full_bar[s], (uint32_t)(it / L::kStages) & 1u)) { atomicExch(err_flag, kErrDrainWait); break; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- UMMA issuer
+      constexpr uint32_t idesc = make_idesc_tf32(BM, BN, false, false);
+      bool ok = true;
+      for (int it = 0; it < nkb; ++it) {
+        const int s = it % L::kStages;
+        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
+        if (!mbar_wait(&full_bar[s], ph)) { atomicExch(err_flag, kErrMmaWait); ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t a_hi = smem_u32(smem + s * L::kStage);
+        const uint32_t b_hi = a_hi + L::kATile;
+        const uint32_t a_lo = b_hi + L::kBTile;
+        const uint32_t b_lo = a_lo + L::kATile;
+#pragma unroll
+        for (int k = 0; k < BK / 8; ++k) {
+          const uint32_t koff = k * 32;  // 8 f32 along K inside the 128-byte swizzle row
+          const uint64_t da_hi = make_smem_desc_sw128(a_hi + koff, 16, 1024);
+          const uint64_t db_hi = make_smem_desc_sw128(b_hi + koff, 16, 1024);
+          if (NPLANES == 2) {
+            const uint64_t da_lo = make_smem_desc_sw128(a_lo + koff, 16, 1024);
+            const uint64_t db_lo = make_smem_desc_sw128(b_lo + koff, 16, 1024);
+            umma_tf32(tmem_base, da_lo, db_hi, idesc, (it | k) != 0);
+            umma_tf32(tmem_base, da_hi, db_lo, idesc, 1);
+            umma_tf32(tmem_base, da_hi, db_hi, idesc, 1);
+          } else {
+            umma_tf32(tmem_base, da_hi, db_hi, idesc, (it | k) != 0);
+          }
+        }
+        umma_commit(&empty_bar[s]);  // slot reusable once these UMMAs have read it
+      }
+      if (ok) umma_commit(accum_bar);
+    }
+  } else {
+    // ---------------- epilogue: warp w owns TMEM lanes [32*(w%4), +32)
+    const int q = warp & 3;
+    const bool ok = mbar_wait(accum_bar, 0);
+    if (!ok && lane == 0) atomicExch(err_flag, kErrEpilogueWait);
+    if (ok) {
+      tc_fence_after_sync();
+      const int row = q * 32 + lane;   // row inside the tile
+#pragma unroll 1
+      for (int c = 0; c < (BN + 31) / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        if (sp.splits > 1) {
+          float* dst = sp.partial + (((size_t)split * sp.batches + batch) * sp.rows_total + (size_t)tile_m * BM + row) * sp.n_total;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = n0 + c * 32 + j;
+            if (c * 32 + j < BN && n < sp.n_total) dst[n] = __uint_as_float(r[j]);
+          }
+        } else {
+          pol.epilogue(tile_m, batch, row, n0 + c * 32, (BN - c * 32) < 32 ? (BN - c * 32) : 32, r);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, L::kTmemCols);
+  }
+}
+
+// out(row, n) = policy.store(sum over splits of partial), fixed summation order.
+template <class Policy>
+__global__ void __launch_bounds__(256)
+tc_splitk_reduce_kernel(const Policy pol, const SplitInfo sp) {
+  const size_t per = (size_t)sp.batches * sp.rows_total * sp.n_total;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= per) return;
+  float s = 0.0f;
+  for (int z = 0; z < sp.splits; ++z) s += sp.partial[(size_t)z * per + idx];
+  const int n = (int)(idx % sp.n_total);
+  const size_t t = idx / sp.n_total;
+  const int row_lin = (int)(t % sp.rows_total);
+  const int b = (int)(t / sp.rows_total);
+  pol.store(row_lin / BM, b, row_lin % BM, n, s);
+}
+
+// Chooses the K-split: enough CTAs to fill the GPU, and no accumulation chain longer
+// than kMaxChainK elements when `limit_chain`.
+inline void plan_split(const nrs_ctx* ctx, long tiles, int kb_total, bool limit_chain, int* splits, int* kb_per_split) {
+  int s = 1;
+  if (tiles < ctx->sm_count && kb_total >= 16) {
+    s = (int)((ctx->sm_count + tiles - 1) / tiles);
+    if (s > kb_total / 8) s = kb_total / 8;
+  }
+  if (limit_chain) {
+    const int need = (kb_total * BK + kMaxChainK - 1) / kMaxChainK;
+    if (s < need) s = need;
+  }
+  if (s < 1) s = 1;
+  int per = (kb_total + s - 1) / s;
+  if (per < 1) per = 1;
+  *kb_per_split = per;
+  *splits = (kb_total + per - 1) / per;
+}
+
+template <int BN, int NPLANES, class Policy>
+int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, const CUtensorMap& tb_hi,
+           const CUtensorMap& tb_lo, const Policy& pol, int tiles_m, int n_total, int batches, int kb_total,
+           const char* who) {
+  using L = SmemLayout<BN, NPLANES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    NRS_CUDA(ctx, cudaFuncSetAttribute(tc_kernel<BN, NPLANES, Policy>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    attr_set = true;
+  }
+  const int tiles_n = (n_total + BN - 1) / BN;
+  SplitInfo sp{};
+  plan_split(ctx, (long)tiles_m * tiles_n * batches, kb_total, NPLANES == 2, &sp.splits, &sp.kb_per_split);
+  if ((long)batches * sp.splits > 65535) return NRS_ERR_UNSUPPORTED;
+  sp.kb_total = kb_total;
+  sp.batches = batches;
+  sp.n_total = n_total;
+  sp.rows_total = tiles_m * BM;
+  sp.partial = nullptr;
+  if (sp.splits > 1) {
+    void* ws = nullptr;
+    const int st = nrs_ws_slot(ctx, NRS_WS_PARTIAL, (size_t)sp.splits * batches * sp.rows_total * n_total * sizeof(float), &ws);
+    if (st != NRS_OK) return st;
+    sp.partial = (float*)ws;
+  }
+  int* err = nullptr;
+  int st = nrs_err_flag(ctx, &err);
+  if (st != NRS_OK) return st;
+  dim3 grid((unsigned)tiles_m, (unsigned)tiles_n, (unsigned)(batches * sp.splits));
+  tc_kernel<BN, NPLANES, Policy><<<grid, kThreads, L::kBytes, ctx->stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, pol, sp, err);
+  NRS_LAUNCHED(ctx);
+  if (sp.splits > 1) {
+    const size_t per = (size_t)batches * sp.rows_total * n_total;
+    tc_splitk_reduce_kernel<Policy><<<nrs_blocks(per, 256), 256, 0, ctx->stream>>>(pol, sp);
+    NRS_LAUNCHED(ctx);
+  }
+  (void)who;
+  return NRS_OK;
+}
+
+}  // namespace tc
+
+// Operand staging (tc_stage.cu).  Planes are [batch][rows][ldk] f32 with ldk a multiple of
+// 32 and zeros beyond K; `lo == nullptr` means no split (hi = the values themselves).
+// src_k_by_rows: the source is stored [K][rows] (transposed) instead of [rows][K].
+int nrs_tc_stage(nrs_ctx* ctx, const float* src, float* hi, float* lo, int rows, int K, int ldk, int batch,
+                 size_t src_bstride, size_t dst_bstride, bool src_k_by_rows);
+// Conv weights w[co][ci][kh][kw] -> K-major planes.
+//  for_dgrad == 0: out[co][(i*kw + j)*ci_n + ci]   (forward B operand)
+//  for_dgrad == 1: out[ci][(i*kw + j)*co_n + co]   (data-gradient B operand)
+int nrs_tc_stage_conv_weight(nrs_ctx* ctx, const float* w, float* hi, float* lo, int co, int ci, int kh, int kw,
+                             int for_dgrad);

@@ -1,0 +1,138 @@
+// Operand staging for the tensor-core kernels: one memory-bound pass that brings an
+// operand into the K-major, 32-float-aligned form TMA wants and, for 3xTF32,
+// splits it into a TF32 high plane (round-to-nearest) and an f32 residual plane
+// (x - hi, exact).  Without the split the single plane is still rounded to nearest
+// TF32: the tensor core truncates its inputs, and truncation's systematic bias
+// compounds through a deep network where rounding's does not.  Transposed sources ([K][rows], e.g. NCHW images seen as
+// [C][H*W]) go through 32x32 shared-memory tiles so both sides stay coalesced.
+#include "tc_mainloop.cuh"
+
+namespace {
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(256)
+stage_rows_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, int rows, int K,
+                  int ldk, size_t src_bstride, size_t dst_bstride) {
+  const int b = blockIdx.y;
+  src += b * src_bstride;
+  hi += b * dst_bstride;
+  if (SPLIT) lo += b * dst_bstride;
+  const int q = ldk / 4;
+  const size_t total4 = (size_t)rows * q;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const bool vec = (K & 3) == 0 && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += stride) {
+    const size_t r = i / q;
+    const int k = (int)(i - r * q) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (vec) {
+      if (k < K) v = *reinterpret_cast<const float4*>(src + r * K + k);
+    } else {
+      if (k + 0 < K) v.x = src[r * K + k + 0];
+      if (k + 1 < K) v.y = src[r * K + k + 1];
+      if (k + 2 < K) v.z = src[r * K + k + 2];
+      if (k + 3 < K) v.w = src[r * K + k + 3];
+    }
+    if (SPLIT) {
+      const float4 h = make_float4(tc::tf32_rn(v.x), tc::tf32_rn(v.y), tc::tf32_rn(v.z), tc::tf32_rn(v.w));
+      *reinterpret_cast<float4*>(lo + r * ldk + k) = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+      *reinterpret_cast<float4*>(hi + r * ldk + k) = h;
+    } else {
+      *reinterpret_cast<float4*>(hi + r * ldk + k) =
+          make_float4(tc::tf32_rn(v.x), tc::tf32_rn(v.y), tc::tf32_rn(v.z), tc::tf32_rn(v.w));
+    }
+  }
+}
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(256)
+stage_transpose_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, int rows, int K,
+                       int ldk, size_t src_bstride, size_t dst_bstride) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z;
+  src += b * src_bstride;
+  hi += b * dst_bstride;
+  if (SPLIT) lo += b * dst_bstride;
+  const int r0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int i = ty; i < 32; i += 8) {
+    const int k = k0 + i, r = r0 + tx;
+    tile[i][tx] = (k < K && r < rows) ? src[(size_t)k * rows + r] : 0.0f;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int r = r0 + i, k = k0 + tx;  // k < ldk always: ldk is a multiple of 32
+    if (r < rows) {
+      const float v = tile[tx][i];
+      if (SPLIT) {
+        const float h = tc::tf32_rn(v);
+        hi[(size_t)r * ldk + k] = h;
+        lo[(size_t)r * ldk + k] = v - h;
+      } else {
+        hi[(size_t)r * ldk + k] = tc::tf32_rn(v);
+      }
+    }
+  }
+}
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(256)
+stage_conv_weight_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int co_n, int ci_n,
+                         int kh, int kw, int for_dgrad) {
+  const size_t total = (size_t)co_n * ci_n * kh * kw;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  // idx enumerates the OUTPUT so writes are coalesced.
+  const int taps = kh * kw;
+  int co, ci, t;
+  if (!for_dgrad) {            // out[co][t*ci_n + ci]
+    ci = (int)(idx % ci_n);
+    t = (int)((idx / ci_n) % taps);
+    co = (int)(idx / ((size_t)ci_n * taps));
+  } else {                     // out[ci][t*co_n + co]
+    co = (int)(idx % co_n);
+    t = (int)((idx / co_n) % taps);
+    ci = (int)(idx / ((size_t)co_n * taps));
+  }
+  const float v = w[((size_t)co * ci_n + ci) * taps + t];
+  if (SPLIT) {
+    const float h = tc::tf32_rn(v);
+    hi[idx] = h;
+    lo[idx] = v - h;
+  } else {
+    hi[idx] = tc::tf32_rn(v);
+  }
+}
+
+}  // namespace
+
+int nrs_tc_stage(nrs_ctx* ctx, const float* src, float* hi, float* lo, int rows, int K, int ldk, int batch,
+                 size_t src_bstride, size_t dst_bstride, bool src_k_by_rows) {
+  if (rows <= 0 || K <= 0 || batch <= 0) return NRS_OK;
+  if (!src_k_by_rows) {
+    size_t blocks = ((size_t)rows * (ldk / 4) + 255) / 256;
+    const size_t cap = (size_t)ctx->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    if (batch > 65535) return NRS_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)blocks, (unsigned)batch);
+    if (lo) stage_rows_kernel<true><<<grid, 256, 0, ctx->stream>>>(src, hi, lo, rows, K, ldk, src_bstride, dst_bstride);
+    else stage_rows_kernel<false><<<grid, 256, 0, ctx->stream>>>(src, hi, nullptr, rows, K, ldk, src_bstride, dst_bstride);
+  } else {
+    dim3 grid((unsigned)((rows + 31) / 32), (unsigned)(ldk / 32), (unsigned)batch);
+    if (grid.y > 65535 || grid.z > 65535) return NRS_ERR_UNSUPPORTED;
+    if (lo) stage_transpose_kernel<true><<<grid, 256, 0, ctx->stream>>>(src, hi, lo, rows, K, ldk, src_bstride, dst_bstride);
+    else stage_transpose_kernel<false><<<grid, 256, 0, ctx->stream>>>(src, hi, nullptr, rows, K, ldk, src_bstride, dst_bstride);
+  }
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
+int nrs_tc_stage_conv_weight(nrs_ctx* ctx, const float* w, float* hi, float* lo, int co, int ci, int kh, int kw,
+                             int for_dgrad) {
+  const size_t total = (size_t)co * ci * kh * kw;
+  if (total == 0) return NRS_OK;
+  if (lo) stage_conv_weight_kernel<true><<<nrs_blocks(total, 256), 256, 0, ctx->stream>>>(w, hi, lo, co, ci, kh, kw, for_dgrad);
+  else stage_conv_weight_kernel<false><<<nrs_blocks(total, 256), 256, 0, ctx->stream>>>(w, hi, nullptr, co, ci, kh, kw, for_dgrad);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}

@@ -1,0 +1,335 @@
+// Convolution weight gradient as implicit GEMM on tcgen05 (TF32 / 3xTF32).
+//
+//   dw[co,ci,i,j] (+)= sum over (n,oy,ox) of dy[n,co,oy,ox] * x[n,ci,oy+i-p,ox+j-p]
+//
+// GEMM view: rows = 128 output channels, columns = (tap, ci) for a group of taps
+// (up to 256 columns), reduction over output pixels.  Both operands come from
+// the NHWC planes the forward / data-gradient kernels also use, so along the
+// reduction (pixels) they are MN-major: a TMA box {32 channels, Wt, Ht, Nt}
+// lands in shared memory as [pixel][32 channels = 128 B].  For 32-bit operands
+// kind::tf32 takes MN-major data only in the 128-byte swizzle with 32-byte atoms
+// (4 pixels x 128 B per swizzle group), which TMA produces with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.  A K-step of 8 pixels is two groups (SBO =
+// 512 B apart); 32-channel blocks sit LBO bytes apart.  The x operand of
+// tap (i,j) is the same box shifted by (i-p, j-p) with TMA zero fill as padding.
+//
+// The reduction is long (batch x H x W pixels) and the output tiny, so pixels
+// are split across CTAs; each CTA writes its partial tile and a second kernel
+// sums the partials in a fixed order (deterministic, unlike the reference's
+// atomicAdd split-K, src/cuda/graph/matmul.rs:207-261) and scatters into the
+// [co][ci][kh][kw] layout.  In 3xTF32 mode no CTA accumulates more than
+// tc::kMaxChainK pixels (the tensor core's f32 accumulation error grows with the
+// chain length).
+//
+// Replaces conv2d_im2col + conv2d_out2mm + matmul_nt_splitk (src/cuda/nn/conv.rs:
+// 298-320).
+#include "tc_mainloop.cuh"
+
+namespace {
+
+constexpr int kWgThreads = 192;
+constexpr int kMaxN = 256;        // widest UMMA
+constexpr int kABlocks = 4;       // 4 x 32 output channels = 128 rows
+
+struct WgradParams {
+  int Wt, Ht, Nt, tiles_y;        // pixel tile (box) geometry in dy space
+  int kp;                         // pixels per tile = Wt*Ht*Nt (multiple of 8)
+  int n_tiles;                    // pixel tiles in all
+  int tiles_per_split;
+  int co, ci, kh, kw, pad;
+  int taps_per_group, n_groups;   // taps handled by one CTA
+  int cblocks;                    // ci / 32
+  int m_blocks;                   // ceil(co / 128)
+  float* partial;                 // [split][m_block][group][128][group_cols]
+  int group_cols;                 // taps_per_group * ci
+};
+
+template <int NPLANES, int STAGES>
+__global__ void __launch_bounds__(kWgThreads, 1)
+tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_constant__ CUtensorMap tm_dy_lo,
+                const __grid_constant__ CUtensorMap tm_x_hi, const __grid_constant__ CUtensorMap tm_x_lo,
+                const WgradParams p, const int n_cols /*UMMA N, multiple of 16*/, int* __restrict__ err_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t blk_bytes = (uint32_t)p.kp * 128u;               // one 32-channel block of one plane
+  const uint32_t a_bytes = kABlocks * blk_bytes;                   // per plane
+  const uint32_t b_bytes = (uint32_t)(p.group_cols / 32) * blk_bytes;
+  const uint32_t stage_bytes = NPLANES * (a_bytes + b_bytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * stage_bytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* accum_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mb = blockIdx.x / p.n_groups, grp = blockIdx.x - mb * p.n_groups;
+  const int split = blockIdx.y;
+  const int t_begin = split * p.tiles_per_split;
+  const int t_end = min(p.n_tiles, t_begin + p.tiles_per_split);
+  const int ntiles = t_end - t_begin;
+  const int tap0 = grp * p.taps_per_group;
+  const int ntaps = min(p.taps_per_group, p.kh * p.kw - tap0);
+  const int a_blocks_live = min(kABlocks, (p.co - mb * 128 + 31) / 32);
+
+  if (warp == 0 && lane == 0) {
+    tc::prefetch_tmap(&tm_dy_hi);
+    tc::prefetch_tmap(&tm_x_hi);
+    if (NPLANES == 2) { tc::prefetch_tmap(&tm_dy_lo); tc::prefetch_tmap(&tm_x_lo); }
+    for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full_bar[s], 1); tc::mbar_init(&empty_bar[s], 1); }
+    tc::mbar_init(accum_bar, 1);
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, kMaxN);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer: one pixel tile per ring slot
+      const uint32_t tx = NPLANES * (uint32_t)(a_blocks_live + ntaps * p.cblocks) * blk_bytes;
+      int issued = 0;
+      bool ok = true;
+      for (int it = 0; it < ntiles; ++it, ++issued) {
+        const int s = it % STAGES;
+        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+        if (!tc::mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(err_flag, tc::kErrProducerWait); ok = false; break; }
+        const int pt = t_begin + it;
+        const int n0 = (pt / p.tiles_y) * p.Nt, y0 = (pt % p.tiles_y) * p.Ht;
+        uint8_t* st = smem + (size_t)s * stage_bytes;
+        tc::mbar_expect_tx(&full_bar[s], tx);
+#pragma unroll 1
+        for (int pl = 0; pl < NPLANES; ++pl) {
+          const CUtensorMap* tdy = pl == 0 ? &tm_dy_hi : &tm_dy_lo;
+          const CUtensorMap* txm = pl == 0 ? &tm_x_hi : &tm_x_lo;
+          uint8_t* a_dst = st + pl * (a_bytes + b_bytes);
+          uint8_t* b_dst = a_dst + a_bytes;
+          for (int blk = 0; blk < a_blocks_live; ++blk)
+            tc::tma_load_4d(a_dst + blk * blk_bytes, tdy, &full_bar[s], mb * 128 + blk * 32, 0, y0, n0);
+          for (int t = 0; t < ntaps; ++t) {
+            const int tap = tap0 + t, i = tap / p.kw, j = tap - i * p.kw;
+            for (int cb = 0; cb < p.cblocks; ++cb)
+              tc::tma_load_4d(b_dst + (t * p.cblocks + cb) * blk_bytes, txm, &full_bar[s], cb * 32, j - p.pad,
+                              y0 + i - p.pad, n0);
+          }
+        }
+      }
+      if (!ok) {
+        for (int it = (issued > STAGES ? issued - STAGES : 0); it < issued; ++it) {
+          const int s = it % STAGES;
+          if (!tc::mbar_wait(&full_bar[s], (uint32_t)(it / STAGES) & 1u)) { atomicExch(err_flag, tc::kErrDrainWait); break; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- UMMA issuer: both operands MN-major, K-step = 8 pixels = one 1024 B atom
+      const uint32_t idesc = tc::make_idesc_tf32(128, n_cols, true, true);
+      bool ok = true;
+      const int ksteps = p.kp / 8;
+      for (int it = 0; it < ntiles; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+        if (!tc::mbar_wait(&full_bar[s], ph)) { atomicExch(err_flag, tc::kErrMmaWait); ok = false; break; }
+        tc::tc_fence_after_sync();
+        const uint32_t a_hi = tc::smem_u32(smem + (size_t)s * stage_bytes);
+        const uint32_t b_hi = a_hi + a_bytes;
+        const uint32_t a_lo = b_hi + b_bytes;
+        const uint32_t b_lo = a_lo + a_bytes;
+#pragma unroll 1
+        for (int k = 0; k < ksteps; ++k) {
+          const uint32_t koff = (uint32_t)k * 1024u;
+          const uint64_t da_hi = tc::make_smem_desc_sw128_32b(a_hi + koff, blk_bytes, 512);
+          const uint64_t db_hi = tc::make_smem_desc_sw128_32b(b_hi + koff, blk_bytes, 512);
+          if (NPLANES == 2) {
+            const uint64_t da_lo = tc::make_smem_desc_sw128_32b(a_lo + koff, blk_bytes, 512);
+            const uint64_t db_lo = tc::make_smem_desc_sw128_32b(b_lo + koff, blk_bytes, 512);
+            tc::umma_tf32(tmem_base, da_lo, db_hi, idesc, (it | k) != 0);
+            tc::umma_tf32(tmem_base, da_hi, db_lo, idesc, 1);
+            tc::umma_tf32(tmem_base, da_hi, db_hi, idesc, 1);
+          } else {
+            tc::umma_tf32(tmem_base, da_hi, db_hi, idesc, (it | k) != 0);
+          }
+        }
+        tc::umma_commit(&empty_bar[s]);
+      }
+      if (ok) tc::umma_commit(accum_bar);
+    }
+  } else {
+    // ---------------- epilogue: raw partial tile to the workspace
+    const int q = warp & 3;
+    const bool ok = tc::mbar_wait(accum_bar, 0);
+    if (!ok && lane == 0) atomicExch(err_flag, tc::kErrEpilogueWait);
+    if (ok) {
+      tc::tc_fence_after_sync();
+      const int row = q * 32 + lane;
+      const int live_cols = ntaps * p.ci;
+      float* dst = p.partial + ((((size_t)split * p.m_blocks + mb) * p.n_groups + grp) * 128 + row) * p.group_cols;
+      const bool row_live = mb * 128 + row < p.co;
+#pragma unroll 1
+      for (int c = 0; c < (live_cols + 31) / 32; ++c) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        tc::tmem_ld_wait();
+        if (row_live) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            if (c * 32 + j < live_cols)
+              *reinterpret_cast<float4*>(dst + c * 32 + j) =
+                  make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        }
+      }
+    }
+  }
+
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after_sync();
+    tc::tmem_dealloc(tmem_base, kMaxN);
+  }
+}
+
+// dw[co][ci][tap] (+)= sum over splits of partial[split][mb][grp][row][t*ci + c], fixed order.
+__global__ void __launch_bounds__(256)
+tc_wgrad_reduce_kernel(const WgradParams p, int splits, float* __restrict__ dw, int accumulate) {
+  const int taps = p.kh * p.kw;
+  const size_t total = (size_t)p.co * p.ci * taps;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  // idx enumerates (co, tap, ci) so that reads of the partials are coalesced along ci
+  const int c = (int)(idx % p.ci);
+  const int tap = (int)((idx / p.ci) % taps);
+  const int co = (int)(idx / ((size_t)p.ci * taps));
+  const int mb = co / 128, row = co - mb * 128;
+  const int grp = tap / p.taps_per_group, t = tap - grp * p.taps_per_group;
+  const size_t tile = (size_t)128 * p.group_cols;
+  const size_t off = (((size_t)mb * p.n_groups + grp) * 128 + row) * p.group_cols + (size_t)t * p.ci + c;
+  const size_t split_stride = (size_t)p.m_blocks * p.n_groups * tile;
+  float s = 0.0f;
+  for (int z = 0; z < splits; ++z) s += p.partial[(size_t)z * split_stride + off];
+  float* dst = dw + ((size_t)co * p.ci + c) * taps + tap;
+  *dst = accumulate ? *dst + s : s;
+}
+
+}  // namespace
+
+namespace {
+
+template <int NPLANES, int STAGES>
+int launch_wgrad(nrs_ctx* ctx, const CUtensorMap* maps, const WgradParams& p, int splits, size_t smem_bytes) {
+  static size_t attr_bytes = 0;
+  if (smem_bytes > attr_bytes) {
+    NRS_CUDA(ctx, cudaFuncSetAttribute(tc_wgrad_kernel<NPLANES, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem_bytes));
+    attr_bytes = smem_bytes;
+  }
+  int* err = nullptr;
+  const int st = nrs_err_flag(ctx, &err);
+  if (st != NRS_OK) return st;
+  dim3 grid((unsigned)(p.m_blocks * p.n_groups), (unsigned)splits);
+  tc_wgrad_kernel<NPLANES, STAGES><<<grid, kWgThreads, smem_bytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p,
+                                                                                  p.group_cols, err);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
+}  // namespace
+
+int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
+                      int kh, int kw, int stride, int pad, int accumulate) {
+  if (!tc::tensor_map_encoder() || getenv("NRS_DISABLE_TC") || getenv("NRS_DISABLE_TC_WGRAD")) return NRS_ERR_UNSUPPORTED;
+  if (stride != 1 || ci % 32 != 0 || co % 32 != 0 || ci > kMaxN || n < 1) return NRS_ERR_UNSUPPORTED;
+  const int oh = h + 2 * pad - kh + 1, ow = wd + 2 * pad - kw + 1;
+  if (ow > wd || oh > h || ow < 1 || oh < 1 || ow > 64) return NRS_ERR_UNSUPPORTED;
+  const bool split3 = ctx->math_mode == NRS_MATH_3XTF32;
+  const int planes = split3 ? 2 : 1;
+
+  WgradParams p{};
+  p.Wt = ow;
+  p.Ht = 32 / ow > 1 ? 32 / ow : 1;
+  if (p.Ht > oh) p.Ht = oh;
+  while ((p.Wt * p.Ht) % 8 != 0 && p.Ht < oh) ++p.Ht;
+  p.Nt = 1;
+  if (p.Ht == oh && p.Wt * p.Ht < 32) {
+    p.Nt = 32 / (p.Wt * p.Ht);
+    if (p.Nt > n) p.Nt = n;
+  }
+  p.kp = p.Wt * p.Ht * p.Nt;
+  if (p.kp % 8 != 0 || p.kp > 64) return NRS_ERR_UNSUPPORTED;
+  p.tiles_y = (oh + p.Ht - 1) / p.Ht;
+  p.n_tiles = ((n + p.Nt - 1) / p.Nt) * p.tiles_y;
+  p.co = co; p.ci = ci; p.kh = kh; p.kw = kw; p.pad = pad;
+  p.cblocks = ci / 32;
+  p.m_blocks = (co + 127) / 128;
+  const int taps = kh * kw;
+  int tpg = kMaxN / ci;
+  if (tpg > taps) tpg = taps;
+  p.n_groups = (taps + tpg - 1) / tpg;
+  p.taps_per_group = (taps + p.n_groups - 1) / p.n_groups;
+  p.group_cols = p.taps_per_group * ci;
+
+  // ring depth from the shared-memory budget
+  const size_t stage_bytes = (size_t)planes * (kABlocks + p.group_cols / 32) * p.kp * 128;
+  int stages = (int)((200 * 1024) / stage_bytes);
+  if (stages < 2) return NRS_ERR_UNSUPPORTED;
+  if (stages > 4) stages = 4;
+  const size_t smem_bytes = stages * stage_bytes + 1024 + 256;
+
+  // pixel split: fill the GPU, and bound the accumulation chain in 3xTF32 mode
+  const int ctas_per_split = p.m_blocks * p.n_groups;
+  int splits = (2 * ctx->sm_count + ctas_per_split - 1) / ctas_per_split;
+  int tps = (p.n_tiles + splits - 1) / splits;
+  if (tps < 8) tps = 8;
+  if (split3 && tps * p.kp > tc::kMaxChainK) tps = tc::kMaxChainK / p.kp;
+  if (tps > p.n_tiles) tps = p.n_tiles;
+  if (tps < 1) tps = 1;
+  p.tiles_per_split = tps;
+  splits = (p.n_tiles + tps - 1) / tps;
+  if (splits > 65535) return NRS_ERR_UNSUPPORTED;
+
+  // workspaces: NHWC planes of dy and x, and the partial tiles
+  const size_t dy_plane = (size_t)n * oh * ow * co, x_plane = (size_t)n * h * wd * ci;
+  const size_t partial_floats = (size_t)splits * p.m_blocks * p.n_groups * 128 * p.group_cols;
+  void *dy_hi = nullptr, *dy_lo = nullptr, *x_hi = nullptr, *x_lo = nullptr, *part = nullptr;
+  int st = nrs_ws_slot(ctx, NRS_WS_A_HI, dy_plane * sizeof(float), &dy_hi);
+  if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_A_LO, dy_plane * sizeof(float), &dy_lo);
+  if (st == NRS_OK) st = nrs_ws_slot(ctx, NRS_WS_B_HI, x_plane * sizeof(float), &x_hi);
+  if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_B_LO, x_plane * sizeof(float), &x_lo);
+  if (st == NRS_OK) st = nrs_ws_slot(ctx, NRS_WS_PARTIAL, partial_floats * sizeof(float), &part);
+  if (st != NRS_OK) return st;
+  p.partial = (float*)part;
+  const size_t dy_img = (size_t)oh * ow * co, x_img = (size_t)h * wd * ci;
+  st = nrs_tc_stage(ctx, dy, (float*)dy_hi, (float*)dy_lo, oh * ow, co, co, n, dy_img, dy_img, true);
+  if (st == NRS_OK) st = nrs_tc_stage(ctx, x, (float*)x_hi, (float*)x_lo, h * wd, ci, ci, n, x_img, x_img, true);
+  if (st != NRS_OK) return st;
+
+  CUtensorMap maps[4];
+  const uint64_t ddim[4] = {(uint64_t)co, (uint64_t)ow, (uint64_t)oh, (uint64_t)n};
+  const uint64_t dstr[3] = {(uint64_t)co * 4, (uint64_t)ow * co * 4, (uint64_t)oh * ow * co * 4};
+  const uint64_t xdim[4] = {(uint64_t)ci, (uint64_t)wd, (uint64_t)h, (uint64_t)n};
+  const uint64_t xstr[3] = {(uint64_t)ci * 4, (uint64_t)wd * ci * 4, (uint64_t)h * wd * ci * 4};
+  const uint32_t box[4] = {32, (uint32_t)p.Wt, (uint32_t)p.Ht, (uint32_t)p.Nt};
+  bool ok = tc::encode_tmap_f32(&maps[0], dy_hi, 4, ddim, dstr, box, true) && tc::encode_tmap_f32(&maps[2], x_hi, 4, xdim, xstr, box, true);
+  if (split3) ok = ok && tc::encode_tmap_f32(&maps[1], dy_lo, 4, ddim, dstr, box, true) && tc::encode_tmap_f32(&maps[3], x_lo, 4, xdim, xstr, box, true);
+  else { maps[1] = maps[0]; maps[3] = maps[2]; }
+  NRS_REQUIRE(ctx, ok, NRS_ERR_CUDA, "tc_wgrad: cuTensorMapEncodeTiled failed");
+
+  if (split3) {
+    if (stages >= 4) st = launch_wgrad<2, 4>(ctx, maps, p, splits, smem_bytes);
+    else if (stages == 3) st = launch_wgrad<2, 3>(ctx, maps, p, splits, smem_bytes);
+    else st = launch_wgrad<2, 2>(ctx, maps, p, splits, smem_bytes);
+  } else {
+    if (stages >= 4) st = launch_wgrad<1, 4>(ctx, maps, p, splits, smem_bytes);
+    else if (stages == 3) st = launch_wgrad<1, 3>(ctx, maps, p, splits, smem_bytes);
+    else st = launch_wgrad<1, 2>(ctx, maps, p, splits, smem_bytes);
+  }
+  if (st != NRS_OK) return st;
+  const size_t total = (size_t)co * ci * taps;
+  tc_wgrad_reduce_kernel<<<nrs_blocks(total, 256), 256, 0, ctx->stream>>>(p, splits, dw, accumulate);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
