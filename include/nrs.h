@@ -152,6 +152,17 @@ int nrs_bias_add(nrs_ctx* ctx, const float* a, const float* bias, float* out, in
 int nrs_accumulate(nrs_ctx* ctx, float* acc, const float* src, size_t n);
 /* out[c] (+)= sum_r g[r,c]  — sum_axis0 (src/cuda/reduce.rs:13-20). */
 int nrs_sum_axis0(nrs_ctx* ctx, const float* g, float* out, int rows, int cols, int accumulate);
+/* Same result as nrs_sum_axis0, for callers that must not allocate device memory
+ * (inside a stream capture, in a real-time loop, or under a host framework that
+ * owns all device memory).  It has no counterpart in the reference.  The split
+ * partial sums go to a fixed 1 MiB array built into the library instead of the
+ * context's cudaMalloc'ed workspace, so the call never reaches cudaMalloc/cudaFree.
+ * Limits and caveats: cols <= 8192 (larger is refused with NRS_ERR_UNSUPPORTED);
+ * the first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress) — make that first call before any stream capture; all
+ * calls on a device share the one array, so two calls that overlap on the GPU
+ * (different streams) race — serialise them. */
+int nrs_sum_axis0_static(nrs_ctx* ctx, const float* g, float* out, int rows, int cols, int accumulate);
 /* out[c] (+)= sum_{n,p} g[n,c,p] — conv2d_bias_grad (src/cuda/nn/conv.rs:78-90). */
 int nrs_channel_sum(nrs_ctx* ctx, const float* g, float* out, int n, int c, int plane, int accumulate);
 /* vrelu / relu_grad (src/cuda/graph/relu.rs:17-27): y=max(0,x); dx (+)= g*[x>0]. */

@@ -393,3 +393,68 @@ int nrs_concat_read(nrs_ctx* ctx, const float* g, float* dpart, int rows, int to
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Column sum that allocates nothing.
+//
+// nrs_sum_axis0 keeps its split partial sums in a workspace the context grows with
+// cudaMalloc on demand.  Some callers cannot tolerate that: code running while a
+// CUDA graph is being captured, a real-time loop that must not hit the driver's
+// allocator, or a host framework that owns all device memory and forbids foreign
+// allocations.  For them the same two kernels run against a fixed scratch array
+// that lives in the library image itself.  Every GPU that loads the library holds
+// these kStaticSplits x kStaticMaxCols floats (1 MiB) until the process exits.
+namespace {
+constexpr int kStaticMaxCols = 8192;
+constexpr int kStaticSplits = 32;
+constexpr int kStaticMaxDevices = 64;
+static __device__ __align__(256) float g_colsum_static_scratch[kStaticSplits * kStaticMaxCols];
+// Device address of the array above, per device ordinal.  The symbol's name is only a
+// host-side handle; kernels must be given the address cudaGetSymbolAddress reports.
+static float* g_colsum_static_addr[kStaticMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int nrs_sum_axis0_static(nrs_ctx* ctx, const float* g, float* out, int rows, int cols, int accumulate) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, rows >= 0 && cols >= 0, NRS_ERR_SHAPE, "nrs_sum_axis0_static: negative dimension");
+  NRS_REQUIRE(ctx, cols <= kStaticMaxCols, NRS_ERR_UNSUPPORTED,
+              "nrs_sum_axis0_static: %d columns exceed the built-in scratch (max %d); use nrs_sum_axis0", cols,
+              kStaticMaxCols);
+  if (cols == 0) return NRS_OK;
+  NRS_REQUIRE(ctx, out && (rows == 0 || g), NRS_ERR_ARG, "nrs_sum_axis0_static: null tensor");
+  NRS_REQUIRE(ctx, ctx->device >= 0 && ctx->device < kStaticMaxDevices, NRS_ERR_UNSUPPORTED,
+              "nrs_sum_axis0_static: device ordinal %d not supported", ctx->device);
+  float* scratch = g_colsum_static_addr[ctx->device];
+  if (!scratch) {
+    // One-time set-up for this device, with that device current.
+    int current = -1;
+    NRS_CUDA(ctx, cudaGetDevice(&current));
+    if (current != ctx->device) NRS_CUDA(ctx, cudaSetDevice(ctx->device));
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_colsum_static_scratch);
+    if (current != ctx->device) (void)cudaSetDevice(current);
+    if (e != cudaSuccess || !p) {
+      (void)cudaGetLastError();
+      return nrs_fail(ctx, NRS_ERR_CUDA, "nrs_sum_axis0_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    }
+    scratch = static_cast<float*>(p);
+    g_colsum_static_addr[ctx->device] = scratch;
+  }
+  const int col_blocks = (cols + 31) / 32;
+  int splits = 1;
+  if (col_blocks < 2 * ctx->sm_count && rows >= 256) {
+    splits = (2 * ctx->sm_count + col_blocks - 1) / col_blocks;
+    if (splits > rows / 64) splits = rows / 64;
+    if (splits > kStaticSplits) splits = kStaticSplits;
+    if (splits < 1) splits = 1;
+  }
+  // Every partial the fold reads is written by the first kernel, so stale contents of the
+  // shared scratch never need clearing.
+  colsum_kernel<<<dim3(col_blocks, splits), 256, 0, ctx->stream>>>(g, out, rows, cols, splits, accumulate, scratch);
+  NRS_LAUNCHED(ctx);
+  if (splits > 1) {
+    colsum_fold_kernel<<<nrs_blocks(cols, 256), 256, 0, ctx->stream>>>(scratch, out, cols, splits, accumulate);
+    NRS_LAUNCHED(ctx);
+  }
+  return NRS_OK;
+}
