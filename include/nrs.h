@@ -214,6 +214,22 @@ int nrs_layernorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const flo
 int nrs_softmax_fwd(nrs_ctx* ctx, const float* x, float* y, int rows, int width);
 int nrs_softmax_bwd(nrs_ctx* ctx, const float* y, const float* g, float* dx, int rows, int width, int accumulate);
 
+/* ------------------------------------------------------------ transformer -- */
+
+/* embed_forward / embed_backward (src/cuda/nn/embedding.rs:13-30): row gather
+ * out[t,:] = weight[idx[t],:] for `tokens` int32 device indices, and the
+ * scatter-add of the gradient back into dweight[vocab,dim] (+)=.  The backward
+ * walks tokens in order per vocabulary row: deterministic, unlike the
+ * reference's atomicAdd.  Indices must lie in [0, vocab) (the caller checks, as
+ * the reference asserts on the host, embedding.rs:55-57). */
+int nrs_embedding_fwd(nrs_ctx* ctx, const float* weight, const int32_t* idx, float* out, int tokens, int dim);
+int nrs_embedding_bwd(nrs_ctx* ctx, const float* g, const int32_t* idx, float* dweight, int tokens, int dim,
+                      int vocab, int accumulate);
+/* Causal mask over [batch, s, s] attention scores.  No reference counterpart (the
+ * reference has no mask).  backward == 0: y = (j > i) ? -1e30 : x;
+ * backward != 0: y (+)= (j > i) ? 0 : x. */
+int nrs_causal_mask(nrs_ctx* ctx, const float* x, float* y, int batch, int s, int backward, int accumulate);
+
 /* ------------------------------------------------------------------- loss -- */
 
 /* ce_forward (src/cuda/loss/cross_entropy.rs:18-36, 74-98): writes

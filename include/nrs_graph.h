@@ -74,6 +74,32 @@ int nrs_op_linear_act(nrs_node* x, nrs_node* w, nrs_node* b, int act, nrs_node**
 int nrs_op_conv2d_act(nrs_node* input, nrs_node* weight, nrs_node* bias, int64_t stride, int64_t pad, int act,
                       nrs_node** out);
 
+/* Transformer pieces — src/cuda/nn/{embedding,positional,attention,multihead,
+ * transformer_block}.rs.
+ * Embedding::forward(indices) -> [count, dim]; the batched form -> [batch, seq, dim]
+ * (the reference has it on the CPU only, src/nn/embedding.rs:60-113).  `indices`
+ * is a HOST array of token ids, checked against the weight's row count. */
+int nrs_op_embedding(nrs_node* weight, const int32_t* indices_host, int64_t count, nrs_node** out);
+int nrs_op_embedding_batch(nrs_node* weight, const int32_t* indices_host, int64_t batch, int64_t seq, nrs_node** out);
+/* PositionalEncoding::new(d_model, max_len): the resident sinusoidal table, and
+ * forward(x) = x + table[:seq] for x [seq, d] or [batch, seq, d]. */
+int nrs_positional_new(nrs_ctx* ctx, int64_t d_model, int64_t max_len, nrs_node** table_out);
+int nrs_op_positional(nrs_node* x, nrs_node* table, nrs_node** out);
+/* attention_batch(q, k, v) on [batch, seq, d_head]; causal != 0 masks j > i
+ * (an extension: the reference has no mask). */
+int nrs_op_causal_mask(nrs_node* scores, nrs_node** out);
+int nrs_op_attention_batch(nrs_node* q, nrs_node* k, nrs_node* v, int causal, nrs_node** out);
+/* MultiHeadAttention::forward_batch(x) with weights [d,d] and no biases. */
+int nrs_op_mha(nrs_node* x, nrs_node* w_q, nrs_node* w_k, nrs_node* w_v, nrs_node* w_o, int64_t num_heads,
+               int causal, nrs_node** out);
+/* TransformerBlock::forward / forward_no_final_norm.  params: 12 nodes in the
+ * order w_q, w_k, w_v, w_o, norm1.gamma, norm1.beta, norm2.gamma, norm2.beta,
+ * ff1.weights, ff1.bias, ff2.weights, ff2.bias (the reference's parameters()
+ * order, src/nn/transformer_block.rs:58-66).  act: NRS_ACT_RELU as the reference,
+ * or NRS_ACT_GELU. */
+int nrs_op_transformer_block(nrs_node* x, nrs_node* const* params, int64_t num_heads, float eps, int act,
+                             int causal, int final_norm, nrs_node** out);
+
 /* cuda::loss — src/cuda/loss/cross_entropy.rs:74-128. */
 int nrs_cross_entropy(nrs_node* pred, nrs_node* target, float* loss_out);
 int nrs_cross_entropy_backward(nrs_node* pred, nrs_node* target);

@@ -91,6 +91,16 @@ static NodeP make_out(nrs_ctx* ctx, const std::vector<size_t>& shape, std::vecto
   return out;
 }
 
+// Public faces of the helpers above, for operator files outside this one.
+GradSlot grad_slot(const NodeP& n) {
+  GradTarget t = grad_target(n);
+  return GradSlot{t.ptr, t.accumulate};
+}
+const float* grad_view(Node* n) { return grad_in(n); }
+NodeP make_result(nrs_ctx* ctx, const std::vector<size_t>& shape, std::vector<NodeP> parents) {
+  return make_out(ctx, shape, std::move(parents));
+}
+
 namespace cuda {
 
 // ------------------------------------------------------------------ runtime

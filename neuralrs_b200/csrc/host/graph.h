@@ -70,6 +70,15 @@ struct FlatStore {
 
 NodeP node_new(nrs_ctx* ctx, const float* host, const std::vector<size_t>& shape);
 
+// Building blocks for operators defined outside graph.cu.
+struct GradSlot {
+  float* ptr;      // where to write the gradient of a parent
+  int accumulate;  // 0: overwrite (first writer), 1: add
+};
+GradSlot grad_slot(const NodeP& n);   // marks the gradient as written
+const float* grad_view(Node* n);      // a node's own incoming gradient (zeros if nothing wrote it)
+NodeP make_result(nrs_ctx* ctx, const std::vector<size_t>& shape, std::vector<NodeP> parents);
+
 namespace cuda {
 
 // ---- runtime (src/cuda/runtime.rs:39-124)
@@ -105,6 +114,53 @@ NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps
 // the composition of the unfused backward passes.
 NodeP linear_act(const NodeP& x, const NodeP& w, const NodeP& b, int act);
 NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size_t pad, int act);
+
+// ---- transformer pieces (src/cuda/nn/{embedding,positional,attention,multihead,
+//      normalization,linear,transformer_block}.rs), defined in transformer_graph.cu
+// scores[..., i, j > i] = -1e30; no reference counterpart (the reference has no mask).
+NodeP causal_mask(const NodeP& scores);
+// softmax(Q K^T / sqrt(d_head)) V on [batch, seq, d_head]  (attention.rs:23-32).
+NodeP attention_batch(const NodeP& q, const NodeP& k, const NodeP& v, bool causal = false);
+
+struct Linear {                       // linear.rs:11-26
+  NodeP weights, bias;
+  NodeP forward(const NodeP& x) const;
+};
+struct LayerNorm {                    // normalization.rs (struct form of layernorm())
+  NodeP gamma, beta;
+  float eps = 1e-5f;
+  NodeP forward(const NodeP& x) const;
+};
+struct Embedding {                    // embedding.rs:41-100
+  NodeP weight;
+  size_t vocab_size = 0, embedding_dim = 0;
+  // indices: `count` token ids; result is [count, dim] (forward) or [batch, seq, dim] (forward_batch,
+  // which the reference has on the CPU only: src/nn/embedding.rs:60-113).
+  NodeP forward(const int32_t* indices, size_t count) const;
+  NodeP forward_batch(const int32_t* indices, size_t batch, size_t seq) const;
+};
+struct PositionalEncoding {           // positional.rs:18-44; the table is computed once and kept resident
+  size_t d_model = 0, max_len = 0;
+  NodeP table;                        // [max_len, d_model], no gradient
+  static PositionalEncoding make(nrs_ctx* ctx, size_t d_model, size_t max_len);
+  // x: [seq, d] as in the reference, or [batch, seq, d] (table broadcast over the batch).
+  NodeP forward(const NodeP& x) const;
+};
+struct MultiHeadAttention {           // multihead.rs:57-85; no biases
+  NodeP w_q, w_k, w_v, w_o;
+  size_t d_model = 0, num_heads = 1;
+  bool causal = false;                // extension
+  NodeP forward_batch(const NodeP& x) const;
+};
+struct TransformerBlock {             // transformer_block.rs:28-60: post-LN, ReLU feed-forward
+  MultiHeadAttention mha;
+  LayerNorm norm1, norm2;
+  Linear ff1, ff2;
+  size_t d_model = 0, d_ff = 0;
+  int act = NRS_ACT_RELU;             // NRS_ACT_GELU is an extension for the LM benchmark configuration
+  NodeP forward(const NodeP& x) const;
+  NodeP forward_no_final_norm(const NodeP& x) const;
+};
 
 // ---- loss (src/cuda/loss/cross_entropy.rs:74-128)
 float cross_entropy(const NodeP& pred, const NodeP& target);

@@ -226,6 +226,86 @@ int nrs_op_linear_act(nrs_node* x, nrs_node* w, nrs_node* b, int act, nrs_node**
   return wrap(ctx_of(x), out, [&] { return nrs::cuda::linear_act(x->p, w->p, b->p, act); });
 }
 
+int nrs_op_embedding(nrs_node* weight, const int32_t* indices_host, int64_t count, nrs_node** out) {
+  NODE_OK(weight);
+  if (count < 0 || weight->p->shape.size() != 2) return nrs_fail(ctx_of(weight), NRS_ERR_SHAPE, "embedding: weight must be [vocab, dim]");
+  return wrap(ctx_of(weight), out, [&] {
+    nrs::cuda::Embedding e{weight->p, weight->p->shape[0], weight->p->shape[1]};
+    return e.forward(indices_host, (size_t)count);
+  });
+}
+
+int nrs_op_embedding_batch(nrs_node* weight, const int32_t* indices_host, int64_t batch, int64_t seq, nrs_node** out) {
+  NODE_OK(weight);
+  if (batch < 0 || seq < 0 || weight->p->shape.size() != 2) return nrs_fail(ctx_of(weight), NRS_ERR_SHAPE, "embedding: bad shape");
+  return wrap(ctx_of(weight), out, [&] {
+    nrs::cuda::Embedding e{weight->p, weight->p->shape[0], weight->p->shape[1]};
+    return e.forward_batch(indices_host, (size_t)batch, (size_t)seq);
+  });
+}
+
+int nrs_positional_new(nrs_ctx* ctx, int64_t d_model, int64_t max_len, nrs_node** table_out) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, d_model > 0 && max_len > 0, NRS_ERR_SHAPE, "nrs_positional_new: non-positive size");
+  return wrap(ctx, table_out, [&] { return nrs::cuda::PositionalEncoding::make(ctx, (size_t)d_model, (size_t)max_len).table; });
+}
+
+int nrs_op_positional(nrs_node* x, nrs_node* table, nrs_node** out) {
+  NODE_OK(x);
+  NODE_OK(table);
+  if (table->p->shape.size() != 2) return nrs_fail(ctx_of(x), NRS_ERR_SHAPE, "positional: table must be [max_len, d_model]");
+  return wrap(ctx_of(x), out, [&] {
+    nrs::cuda::PositionalEncoding pe;
+    pe.max_len = table->p->shape[0];
+    pe.d_model = table->p->shape[1];
+    pe.table = table->p;
+    return pe.forward(x->p);
+  });
+}
+
+UNARY(nrs_op_causal_mask, nrs::cuda::causal_mask(x->p))
+
+int nrs_op_attention_batch(nrs_node* q, nrs_node* k, nrs_node* v, int causal, nrs_node** out) {
+  NODE_OK(q);
+  NODE_OK(k);
+  NODE_OK(v);
+  return wrap(ctx_of(q), out, [&] { return nrs::cuda::attention_batch(q->p, k->p, v->p, causal != 0); });
+}
+
+int nrs_op_mha(nrs_node* x, nrs_node* w_q, nrs_node* w_k, nrs_node* w_v, nrs_node* w_o, int64_t num_heads,
+               int causal, nrs_node** out) {
+  NODE_OK(x);
+  NODE_OK(w_q);
+  NODE_OK(w_k);
+  NODE_OK(w_v);
+  NODE_OK(w_o);
+  if (num_heads < 1 || x->p->shape.size() != 3) return nrs_fail(ctx_of(x), NRS_ERR_SHAPE, "mha: bad heads or input rank");
+  return wrap(ctx_of(x), out, [&] {
+    nrs::cuda::MultiHeadAttention m{w_q->p, w_k->p, w_v->p, w_o->p, x->p->shape[2], (size_t)num_heads, causal != 0};
+    return m.forward_batch(x->p);
+  });
+}
+
+int nrs_op_transformer_block(nrs_node* x, nrs_node* const* params, int64_t num_heads, float eps, int act,
+                             int causal, int final_norm, nrs_node** out) {
+  NODE_OK(x);
+  if (num_heads < 1 || x->p->shape.size() != 3) return nrs_fail(ctx_of(x), NRS_ERR_SHAPE, "transformer block: bad heads or input rank");
+  if (act != NRS_ACT_RELU && act != NRS_ACT_GELU) return nrs_fail(ctx_of(x), NRS_ERR_ARG, "transformer block: act must be ReLU or GELU");
+  return wrap(ctx_of(x), out, [&] {
+    auto p = gather(params, 12);
+    nrs::cuda::TransformerBlock b;
+    b.mha = nrs::cuda::MultiHeadAttention{p[0], p[1], p[2], p[3], x->p->shape[2], (size_t)num_heads, causal != 0};
+    b.norm1 = nrs::cuda::LayerNorm{p[4], p[5], eps};
+    b.norm2 = nrs::cuda::LayerNorm{p[6], p[7], eps};
+    b.ff1 = nrs::cuda::Linear{p[8], p[9]};
+    b.ff2 = nrs::cuda::Linear{p[10], p[11]};
+    b.d_model = x->p->shape[2];
+    b.d_ff = p[8]->shape.size() == 2 ? p[8]->shape[1] : 0;
+    b.act = act;
+    return final_norm ? b.forward(x->p) : b.forward_no_final_norm(x->p);
+  });
+}
+
 int nrs_cross_entropy(nrs_node* pred, nrs_node* target, float* loss_out) {
   NODE_OK(pred);
   NODE_OK(target);

@@ -1,0 +1,160 @@
+// Transformer-side operators of the graph layer: embedding, positional encoding,
+// batched attention, multi-head attention, the post-LN transformer block.
+// They are written the way the reference writes them — compositions of the
+// resident graph ops (src/cuda/nn/attention.rs:23-32, multihead.rs:57-85,
+// transformer_block.rs:28-60) — plus the embedding gather/scatter kernels and
+// the causal mask, which need their own backward closures.
+#include <cmath>
+#include <cstring>
+
+#include "host/graph.h"
+
+namespace nrs {
+namespace cuda {
+
+static void fail(int code, const std::string& m) { throw Error(code, m); }
+
+NodeP causal_mask(const NodeP& scores) {
+  if (!scores || !scores->on_gpu()) fail(NRS_ERR_ARG, "cuda causal_mask: input not on GPU");
+  const size_t nd = scores->shape.size();
+  if (nd < 2 || scores->shape[nd - 1] != scores->shape[nd - 2]) fail(NRS_ERR_SHAPE, "cuda causal_mask: last two dims must be equal");
+  nrs_ctx* ctx = scores->ctx;
+  const int s = (int)scores->shape[nd - 1];
+  const int batch = (int)(scores->len() / ((size_t)s * s));
+  NodeP out = make_result(ctx, scores->shape, {scores});
+  check(ctx, nrs_causal_mask(ctx, scores->data, out->data, batch, s, 0, 0));
+  Node* self = out.get();
+  out->backward_fn = [self, scores, batch, s]() {
+    if (!scores->requires_grad) return;
+    const float* g = grad_view(self);
+    GradSlot t = grad_slot(scores);
+    check(self->ctx, nrs_causal_mask(self->ctx, g, t.ptr, batch, s, 1, t.accumulate));
+  };
+  return out;
+}
+
+NodeP attention_batch(const NodeP& q, const NodeP& k, const NodeP& v, bool causal) {
+  if (!q || q->shape.size() != 3) fail(NRS_ERR_SHAPE, "cuda attention_batch: q must be [batch, seq, d_head]");
+  const float scale_factor = 1.0f / std::sqrt((float)q->shape[2]);
+  NodeP scores = scale(bmm(q, transpose(k)), scale_factor);
+  if (causal) scores = causal_mask(scores);
+  return bmm(softmax(scores), v);
+}
+
+NodeP Linear::forward(const NodeP& x) const { return add(matmul(x, weights), bias); }
+
+NodeP LayerNorm::forward(const NodeP& x) const { return layernorm(x, gamma, beta, eps); }
+
+static NodeP embed(const Embedding& e, const int32_t* indices, size_t count, const std::vector<size_t>& out_shape) {
+  if (!e.weight || !e.weight->on_gpu()) fail(NRS_ERR_ARG, "cuda embedding: weight not on GPU");
+  if (!indices && count) fail(NRS_ERR_ARG, "cuda embedding: null indices");
+  for (size_t i = 0; i < count; ++i)
+    if (indices[i] < 0 || (size_t)indices[i] >= e.vocab_size) fail(NRS_ERR_ARG, "embedding: token index out of vocab range");
+  nrs_ctx* ctx = e.weight->ctx;
+  const int dim = (int)e.embedding_dim;
+  NodeP out = make_result(ctx, out_shape, {e.weight});
+  void* idx_dev = nullptr;
+  check(ctx, nrs_alloc(ctx, (count ? count : 1) * sizeof(int32_t), 0, &idx_dev));
+  out->saved.push_back(idx_dev);
+  check(ctx, nrs_h2d(ctx, idx_dev, indices, count * sizeof(int32_t)));
+  check(ctx, nrs_sync(ctx));  // the caller's index buffer may go away
+  check(ctx, nrs_embedding_fwd(ctx, e.weight->data, (const int32_t*)idx_dev, out->data, (int)count, dim));
+  Node* self = out.get();
+  const NodeP w = e.weight;
+  const int vocab = (int)e.vocab_size;
+  out->backward_fn = [self, w, idx_dev, count, dim, vocab]() {
+    if (!w->requires_grad) return;
+    const float* g = grad_view(self);
+    GradSlot t = grad_slot(w);
+    check(self->ctx, nrs_embedding_bwd(self->ctx, g, (const int32_t*)idx_dev, t.ptr, (int)count, dim, vocab, t.accumulate));
+  };
+  return out;
+}
+
+NodeP Embedding::forward(const int32_t* indices, size_t count) const {
+  return embed(*this, indices, count, {count, embedding_dim});
+}
+
+NodeP Embedding::forward_batch(const int32_t* indices, size_t batch, size_t seq) const {
+  return embed(*this, indices, batch * seq, {batch, seq, embedding_dim});
+}
+
+PositionalEncoding PositionalEncoding::make(nrs_ctx* ctx, size_t d_model, size_t max_len) {
+  // The table is computed on the host in f32 exactly as the reference does
+  // (src/cuda/nn/positional.rs:24-33), once, and stays resident.
+  std::vector<float> pe(max_len * d_model);
+  for (size_t pos = 0; pos < max_len; ++pos)
+    for (size_t i = 0; i < d_model; ++i) {
+      const float exponent = (float)(2 * (i / 2)) / (float)d_model;
+      const float freq = 1.0f / std::pow(10000.0f, exponent);
+      const float angle = (float)pos * freq;
+      pe[pos * d_model + i] = (i % 2 == 0) ? std::sin(angle) : std::cos(angle);
+    }
+  PositionalEncoding p;
+  p.d_model = d_model;
+  p.max_len = max_len;
+  p.table = node_new(ctx, pe.data(), {max_len, d_model});
+  p.table->requires_grad = false;
+  to_cuda(p.table);
+  synchronize(ctx);
+  return p;
+}
+
+NodeP PositionalEncoding::forward(const NodeP& x) const {
+  if (!x || !x->on_gpu()) fail(NRS_ERR_ARG, "cuda positional: input not on GPU");
+  const size_t nd = x->shape.size();
+  if (nd != 2 && nd != 3) fail(NRS_ERR_SHAPE, "cuda positional: input must be [seq, d] or [batch, seq, d]");
+  const size_t seq = x->shape[nd - 2], d = x->shape[nd - 1];
+  if (d != d_model) fail(NRS_ERR_SHAPE, "cuda positional: feature size differs from d_model");
+  if (seq > max_len) fail(NRS_ERR_SHAPE, "sequence longer than max_len");
+  nrs_ctx* ctx = x->ctx;
+  const size_t batch = nd == 3 ? x->shape[0] : 1;
+  // out[b, i] = x[b, i] + pe[i] over the first seq*d entries of the table: a row-broadcast add.
+  NodeP out = make_result(ctx, x->shape, {x});
+  check(ctx, nrs_bias_add(ctx, x->data, table->data, out->data, (int)batch, (int)(seq * d)));
+  Node* self = out.get();
+  const size_t len = x->len();
+  out->backward_fn = [self, x, len]() {
+    if (!x->requires_grad) return;
+    const float* g = grad_view(self);
+    GradSlot t = grad_slot(x);
+    if (t.accumulate) check(self->ctx, nrs_accumulate(self->ctx, t.ptr, g, len));
+    else check(self->ctx, nrs_d2d(self->ctx, t.ptr, g, len * sizeof(float)));
+  };
+  return out;
+}
+
+NodeP MultiHeadAttention::forward_batch(const NodeP& x) const {
+  if (!x || x->shape.size() != 3) fail(NRS_ERR_SHAPE, "cuda mha: input must be [batch, seq, d_model]");
+  const size_t batch = x->shape[0], seq = x->shape[1], d = x->shape[2];
+  if (d != d_model || num_heads == 0 || d_model % num_heads != 0) fail(NRS_ERR_SHAPE, "cuda mha: d_model / num_heads mismatch");
+  auto proj = [&](const NodeP& w) { return reshape(matmul(reshape(x, {batch * seq, d}), w), {batch, seq, d}); };
+  NodeP q = proj(w_q), k = proj(w_k), v = proj(w_v);
+  const size_t d_head = d_model / num_heads;
+  std::vector<NodeP> heads;
+  for (size_t h = 0; h < num_heads; ++h) {
+    const size_t c0 = h * d_head, c1 = c0 + d_head;
+    heads.push_back(attention_batch(slice_cols(q, c0, c1), slice_cols(k, c0, c1), slice_cols(v, c0, c1), causal));
+  }
+  NodeP concat = concat_cols(heads);
+  return reshape(matmul(reshape(concat, {batch * seq, d}), w_o), {batch, seq, d});
+}
+
+static NodeP block_body(const TransformerBlock& b, const NodeP& x, bool final_norm) {
+  if (!x || x->shape.size() != 3) fail(NRS_ERR_SHAPE, "cuda transformer block: input must be [batch, seq, d_model]");
+  const size_t batch = x->shape[0], seq = x->shape[1], d = x->shape[2];
+  NodeP attn_out = b.mha.forward_batch(x);
+  NodeP x1 = b.norm1.forward(add(x, attn_out));
+  NodeP flat = reshape(x1, {batch * seq, d});
+  NodeP h = b.ff1.forward(flat);
+  h = b.act == NRS_ACT_GELU ? gelu(h) : relu(h);
+  NodeP ff_out = reshape(b.ff2.forward(h), {batch, seq, d});
+  NodeP x2 = add(x1, ff_out);
+  return final_norm ? b.norm2.forward(x2) : x2;
+}
+
+NodeP TransformerBlock::forward(const NodeP& x) const { return block_body(*this, x, true); }
+NodeP TransformerBlock::forward_no_final_norm(const NodeP& x) const { return block_body(*this, x, false); }
+
+}  // namespace cuda
+}  // namespace nrs

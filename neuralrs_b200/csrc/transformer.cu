@@ -1,0 +1,113 @@
+// Embedding gather / scatter-add and the causal score mask.
+// Reference: embed_forward / embed_backward (src/cuda/nn/embedding.rs:13-30; CPU
+// semantics src/nn/embedding.rs:19-113).  The reference's backward is a per-element
+// atomicAdd scatter (sum order varies run to run); here every vocabulary row is
+// owned by one block that walks the tokens in order, so the weight gradient is
+// deterministic and needs no atomics.  The causal mask has no reference
+// counterpart (the reference has no mask): scores[i, j > i] are set to -1e30
+// before the softmax, and their gradient is dropped.
+#include "nrs_internal.h"
+
+namespace {
+
+__global__ void __launch_bounds__(256)
+embed_fwd_kernel(const float* __restrict__ w, const int32_t* __restrict__ idx, float* __restrict__ out, int tokens,
+                 int dim) {
+  const size_t total = (size_t)tokens * dim;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if ((dim & 3) == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    const int d4 = dim >> 2;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total / 4; i += stride) {
+      const size_t t = i / d4;
+      const int c = (int)(i - t * d4);
+      reinterpret_cast<float4*>(out)[i] = reinterpret_cast<const float4*>(w + (size_t)idx[t] * dim)[c];
+    }
+  } else {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const size_t t = i / dim;
+      out[i] = w[(size_t)idx[t] * dim + (i - t * dim)];
+    }
+  }
+}
+
+// One block per vocabulary row; thread d owns feature d (strided when dim > blockDim).
+// Token indices are staged through shared memory in chunks.
+__global__ void __launch_bounds__(256)
+embed_bwd_kernel(const float* __restrict__ g, const int32_t* __restrict__ idx, float* dw, int tokens, int dim,
+                 int accumulate) {
+  __shared__ int32_t s_idx[1024];
+  const int row = blockIdx.x;
+  for (int d0 = 0; d0 < dim; d0 += blockDim.x) {
+    const int d = d0 + threadIdx.x;
+    float acc = 0.0f;
+    for (int t0 = 0; t0 < tokens; t0 += 1024) {
+      const int nt = min(1024, tokens - t0);
+      __syncthreads();
+      for (int i = threadIdx.x; i < nt; i += blockDim.x) s_idx[i] = idx[t0 + i];
+      __syncthreads();
+      if (d < dim)
+        for (int i = 0; i < nt; ++i)
+          if (s_idx[i] == row) acc += g[(size_t)(t0 + i) * dim + d];
+    }
+    if (d < dim) {
+      float* dst = dw + (size_t)row * dim + d;
+      *dst = accumulate ? *dst + acc : acc;
+    }
+  }
+}
+
+// x, y: [batch, s, s].  forward: y = (j > i) ? -1e30 : x.  backward: y (+)= (j > i) ? 0 : x.
+__global__ void __launch_bounds__(256)
+causal_mask_kernel(const float* __restrict__ x, float* y, size_t total, int s, int backward, int accumulate) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const int j = (int)(idx % s);
+    const int i = (int)((idx / s) % s);
+    float v = x[idx];
+    if (j > i) v = backward ? 0.0f : -1e30f;
+    y[idx] = accumulate ? y[idx] + v : v;
+  }
+}
+
+unsigned grid_for(const nrs_ctx* ctx, size_t work) {
+  size_t blocks = (work + 255) / 256;
+  const size_t cap = (size_t)ctx->sm_count * 16;
+  return (unsigned)(blocks > cap ? cap : (blocks ? blocks : 1));
+}
+
+}  // namespace
+
+extern "C" {
+
+int nrs_embedding_fwd(nrs_ctx* ctx, const float* weight, const int32_t* idx, float* out, int tokens, int dim) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, tokens >= 0 && dim > 0, NRS_ERR_SHAPE, "nrs_embedding_fwd: bad shape [%d,%d]", tokens, dim);
+  if (tokens == 0) return NRS_OK;
+  NRS_REQUIRE(ctx, weight && idx && out, NRS_ERR_ARG, "nrs_embedding_fwd: null tensor");
+  embed_fwd_kernel<<<grid_for(ctx, (size_t)tokens * dim / 4 + 1), 256, 0, ctx->stream>>>(weight, idx, out, tokens, dim);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
+int nrs_embedding_bwd(nrs_ctx* ctx, const float* g, const int32_t* idx, float* dweight, int tokens, int dim,
+                      int vocab, int accumulate) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, tokens >= 0 && dim > 0 && vocab > 0, NRS_ERR_SHAPE, "nrs_embedding_bwd: bad shape");
+  NRS_REQUIRE(ctx, dweight && (tokens == 0 || (g && idx)), NRS_ERR_ARG, "nrs_embedding_bwd: null tensor");
+  embed_bwd_kernel<<<vocab, 256, 0, ctx->stream>>>(g, idx, dweight, tokens, dim, accumulate);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
+int nrs_causal_mask(nrs_ctx* ctx, const float* x, float* y, int batch, int s, int backward, int accumulate) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, batch >= 0 && s >= 0, NRS_ERR_SHAPE, "nrs_causal_mask: negative dimension");
+  const size_t total = (size_t)batch * s * s;
+  if (total == 0) return NRS_OK;
+  NRS_REQUIRE(ctx, x && y, NRS_ERR_ARG, "nrs_causal_mask: null tensor");
+  causal_mask_kernel<<<grid_for(ctx, total), 256, 0, ctx->stream>>>(x, y, total, s, backward, accumulate);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
+}  // extern "C"

@@ -199,6 +199,7 @@ class graph:
     gelu = _unary("nrs_op_gelu")
     softmax = _unary("nrs_op_softmax")
     transpose = _unary("nrs_op_transpose")
+    causal_mask = _unary("nrs_op_causal_mask")   # extension: the reference has no mask
 
     @staticmethod
     def reshape(x: Node, shape) -> Node:
@@ -250,6 +251,92 @@ class nn:
     def linear_act(x: Node, w: Node, b: Node, act: int) -> Node:
         h = VP()
         return _out(x.ctx, x.ctx._l.nrs_op_linear_act(x.h, w.h, b.h, int(act), C.byref(h)), h)
+
+    @staticmethod
+    def attention_batch(q: Node, k: Node, v: Node, causal: bool = False) -> Node:
+        """src/cuda/nn/attention.rs:23-32 (causal is an extension)."""
+        h = VP()
+        return _out(q.ctx, q.ctx._l.nrs_op_attention_batch(q.h, k.h, v.h, int(causal), C.byref(h)), h)
+
+    class LayerNorm:
+        """src/cuda/nn/normalization.rs (struct form)."""
+
+        def __init__(self, gamma: Node, beta: Node, eps: float = 1e-5):
+            self.gamma, self.beta, self.eps = gamma, beta, eps
+
+        def forward(self, x: Node) -> Node:
+            return nn.layernorm(x, self.gamma, self.beta, self.eps)
+
+    class Embedding:
+        """src/cuda/nn/embedding.rs:41-100; forward_batch mirrors src/nn/embedding.rs:60-113."""
+
+        def __init__(self, weight: Node, vocab_size: int, embedding_dim: int):
+            self.weight, self.vocab_size, self.embedding_dim = weight, vocab_size, embedding_dim
+
+        def forward(self, indices) -> Node:
+            idx = np.ascontiguousarray(indices, dtype=np.int32).reshape(-1)
+            h = VP()
+            l = self.weight.ctx._l
+            return _out(self.weight.ctx, l.nrs_op_embedding(self.weight.h, _ptr(idx), idx.size, C.byref(h)), h)
+
+        def forward_batch(self, batch_indices) -> Node:
+            idx = np.ascontiguousarray(batch_indices, dtype=np.int32)
+            b, s = idx.shape
+            h = VP()
+            l = self.weight.ctx._l
+            return _out(self.weight.ctx, l.nrs_op_embedding_batch(self.weight.h, _ptr(idx), b, s, C.byref(h)), h)
+
+    class PositionalEncoding:
+        """src/cuda/nn/positional.rs:18-44; the table is built once and stays on the device."""
+
+        def __init__(self, d_model: int, max_len: int, ctx: Context | None = None):
+            ctx = ctx or default_context()
+            h = VP()
+            check(ctx.h, ctx._l.nrs_positional_new(ctx.h, int(d_model), int(max_len), C.byref(h)))
+            self.table = Node(h, ctx)
+            self.d_model, self.max_len = d_model, max_len
+
+        def forward(self, x: Node) -> Node:
+            h = VP()
+            return _out(x.ctx, x.ctx._l.nrs_op_positional(x.h, self.table.h, C.byref(h)), h)
+
+    class MultiHeadAttention:
+        """src/cuda/nn/multihead.rs:20-85 (weights [d,d], no biases)."""
+
+        def __init__(self, w_q, w_k, w_v, w_o, d_model: int, num_heads: int, causal: bool = False):
+            self.w_q, self.w_k, self.w_v, self.w_o = w_q, w_k, w_v, w_o
+            self.d_model, self.num_heads, self.causal = d_model, num_heads, causal
+
+        def parameters(self):
+            return [self.w_q, self.w_k, self.w_v, self.w_o]
+
+        def forward_batch(self, x: Node) -> Node:
+            h = VP()
+            return _out(x.ctx, x.ctx._l.nrs_op_mha(x.h, self.w_q.h, self.w_k.h, self.w_v.h, self.w_o.h,
+                                                  int(self.num_heads), int(self.causal), C.byref(h)), h)
+
+    class TransformerBlock:
+        """src/cuda/nn/transformer_block.rs:14-60."""
+
+        def __init__(self, mha, norm1, norm2, ff1, ff2, d_model: int, d_ff: int, act: int = 1):
+            self.mha, self.norm1, self.norm2, self.ff1, self.ff2 = mha, norm1, norm2, ff1, ff2
+            self.d_model, self.d_ff, self.act = d_model, d_ff, act
+
+        def parameters(self):
+            return self.mha.parameters() + [self.norm1.gamma, self.norm1.beta, self.norm2.gamma, self.norm2.beta,
+                                            self.ff1.weights, self.ff1.bias, self.ff2.weights, self.ff2.bias]
+
+        def _run(self, x: Node, final_norm: bool) -> Node:
+            h = VP()
+            return _out(x.ctx, x.ctx._l.nrs_op_transformer_block(
+                x.h, _handles(self.parameters()), int(self.mha.num_heads), C.c_float(self.norm1.eps), int(self.act),
+                int(self.mha.causal), int(final_norm), C.byref(h)), h)
+
+        def forward(self, x: Node) -> Node:
+            return self._run(x, True)
+
+        def forward_no_final_norm(self, x: Node) -> Node:
+            return self._run(x, False)
 
     class Linear:
         """weights [in, out], bias [out]; forward = add(matmul(x, W), b) (src/cuda/nn/linear.rs:11-26)."""

@@ -487,3 +487,33 @@ void FN(nrs_oracle_concat_read)(const float* g, float* dpart, int rows, int tota
   for (int r = 0; r < rows; ++r)
     for (int c = 0; c < pw; ++c) dpart[(size_t)r * pw + c] += g[(size_t)r * total + off + c];
 }
+
+/* --------------------------------------------------------------- embedding */
+
+/* Row gather out[t,:] = weight[idx[t],:]; backward scatter-add in token order.
+ * src/nn/embedding.rs:19-30 (forward), :47-55 (backward); the batched form
+ * (:60-113) is the same over batch*seq tokens. */
+void FN(nrs_oracle_embedding_fwd)(const float* weight, const int32_t* idx, float* out, int tokens, int dim) {
+  for (int t = 0; t < tokens; ++t)
+    memcpy(out + (size_t)t * dim, weight + (size_t)idx[t] * dim, sizeof(float) * dim);
+}
+void FN(nrs_oracle_embedding_bwd)(const float* g, const int32_t* idx, float* dweight, int tokens, int dim, int vocab) {
+  acc_t* acc = (acc_t*)calloc((size_t)vocab * dim, sizeof(acc_t));
+  for (int t = 0; t < tokens; ++t)
+    for (int d = 0; d < dim; ++d) acc[(size_t)idx[t] * dim + d] += (acc_t)g[(size_t)t * dim + d];
+  for (size_t i = 0; i < (size_t)vocab * dim; ++i) dweight[i] += (float)acc[i];
+  free(acc);
+}
+
+/* Sinusoidal table pe[pos,i]: exponent = 2*(i/2)/d, freq = 1/10000^exponent,
+ * angle = pos*freq, even i -> sin, odd i -> cos, all in f32.
+ * src/nn/positional.rs:20-33. */
+void FN(nrs_oracle_positional_table)(float* pe, int max_len, int d_model) {
+  for (int pos = 0; pos < max_len; ++pos)
+    for (int i = 0; i < d_model; ++i) {
+      const float exponent = (float)(2 * (i / 2)) / (float)d_model;
+      const float freq = 1.0f / powf(10000.0f, exponent);
+      const float angle = (float)pos * freq;
+      pe[(size_t)pos * d_model + i] = (i % 2 == 0) ? sinf(angle) : cosf(angle);
+    }
+}

@@ -247,3 +247,31 @@ class Oracle:
         dx = np.zeros(in_shape, np.float32)
         self._fn("nrs_oracle_slice_cols_bwd")(_p(g), _p(dx), dx.size // total, total, c0, c1)
         return dx
+
+    # ---- embedding / positional encoding (src/nn/embedding.rs, src/nn/positional.rs)
+    def embedding_fwd(self, weight, idx):
+        weight = _f(weight)
+        idx = np.ascontiguousarray(idx, dtype=np.int32).reshape(-1)
+        out = np.empty((idx.size, weight.shape[1]), np.float32)
+        self._fn("nrs_oracle_embedding_fwd")(_p(weight), _p(idx), _p(out), idx.size, weight.shape[1])
+        return out
+
+    def embedding_bwd(self, g, idx, vocab):
+        g = _f(g)
+        idx = np.ascontiguousarray(idx, dtype=np.int32).reshape(-1)
+        dim = g.size // idx.size
+        dw = np.zeros((vocab, dim), np.float32)
+        self._fn("nrs_oracle_embedding_bwd")(_p(g), _p(idx), _p(dw), idx.size, dim, vocab)
+        return dw
+
+    def positional_table(self, max_len, d_model):
+        pe = np.empty((max_len, d_model), np.float32)
+        self._fn("nrs_oracle_positional_table")(_p(pe), max_len, d_model)
+        return pe
+
+    def transpose_bwd(self, g):
+        # the gradient of a transpose is the transpose of the gradient (transpose.rs:45-52)
+        return self.transpose_fwd(g)
+
+    def scale_fwd(self, x, s):
+        return (_f(x) * np.float32(s)).astype(np.float32)
