@@ -1,6 +1,8 @@
 // Define-by-run graph over the C ABI: Node, the resident operators with their
 // backward closures, backward_graph and AdamW.  See graph.h for what it mirrors.
 #include "host/graph.h"
+#include "nrs_internal.h"
+#include "tc_mainloop.cuh"
 
 #include <cmath>
 #include <cstring>
@@ -28,6 +30,11 @@ size_t Node::len() const {
 
 Node::~Node() {
   if (!ctx) return;
+  if (planes_hi) {
+    ctx->plane_hints.erase(data);
+    nrs_free(ctx, planes_hi);
+    if (planes_lo) nrs_free(ctx, planes_lo);
+  }
   if (data && owns_data) nrs_free(ctx, data);
   if (grad && owns_grad) nrs_free(ctx, grad);
   for (void* p : saved) nrs_free(ctx, p);
@@ -99,6 +106,23 @@ GradSlot grad_slot(const NodeP& n) {
 const float* grad_view(Node* n) { return grad_in(n); }
 NodeP make_result(nrs_ctx* ctx, const std::vector<size_t>& shape, std::vector<NodeP> parents) {
   return make_out(ctx, shape, std::move(parents));
+}
+
+// Stages NHWC planes of an NCHW tensor [n,c,h,w] at `src` into fresh pool blocks and registers
+// them with the context under `src`.  Returns false (nothing allocated) when the tensor-core
+// convolutions would not take this tensor (FP32 mode, channel count not a multiple of 32).
+static bool stage_planes(nrs_ctx* ctx, const float* src, const std::vector<size_t>& shape, float** hi, float** lo) {
+  *hi = *lo = nullptr;
+  if (ctx->math_mode == NRS_MATH_FP32 || shape.size() != 4 || shape[1] % 32 != 0 || shape[0] == 0) return false;
+  if (!tc::tensor_map_encoder() || getenv("NRS_DISABLE_TC") || getenv("NRS_NO_PLANE_CACHE")) return false;
+  if (ctx->plane_hints.count(src)) return false;   // already there (the tensor feeds two convolutions)
+  const bool split = ctx->math_mode == NRS_MATH_3XTF32;
+  const size_t n = shape[0], c = shape[1], hw = shape[2] * shape[3];
+  *hi = dalloc(ctx, n * c * hw);
+  if (split) *lo = dalloc(ctx, n * c * hw);
+  check(ctx, nrs_tc_stage(ctx, src, *hi, *lo, (int)hw, (int)c, (int)c, (int)n, c * hw, c * hw, true));
+  ctx->plane_hints[src] = NrsPlanes{*hi, *lo, split ? 1 : 0};
+  return true;
 }
 
 namespace cuda {
@@ -473,6 +497,11 @@ NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, 
   if (h + 2 * (int)pad < kh || wd + 2 * (int)pad < kw) fail(NRS_ERR_SHAPE, "cuda conv2d: kernel larger than padded input");
   const int oh = (h + 2 * (int)pad - kh) / (int)stride + 1, ow = (wd + 2 * (int)pad - kw) / (int)stride + 1;
   NodeP out = make_out(ctx, {(size_t)n, (size_t)co, (size_t)oh, (size_t)ow}, {x, w, b});
+  // The input's NHWC planes serve this forward pass and, later, the weight gradient.
+  if (stride == 1 && !x->planes_hi && co % 32 == 0 && w->requires_grad) {
+    float *phi = nullptr, *plo = nullptr;
+    if (stage_planes(ctx, x->data, x->shape, &phi, &plo)) { x->planes_hi = phi; x->planes_lo = plo; }
+  }
   check(ctx, nrs_conv2d_fwd(ctx, x->data, w->data, b->data, out->data, n, ci, h, wd, co, kh, kw, (int)stride,
                             (int)pad, act));
   Node* self = out.get();
@@ -486,7 +515,15 @@ NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, 
       check(ctx, nrs_relu_bwd(ctx, self->data, dy, masked, self->len(), 0));
       dy = masked;
     }
+    // dy feeds both the data and the weight gradient: stage its planes once.
+    float *dhi = nullptr, *dlo = nullptr;
+    const bool staged = s == 1 && ci % 32 == 0 && stage_planes(ctx, dy, self->shape, &dhi, &dlo);
     conv_backward(self, x, w, b, dy, n, ci, h, wd, co, kh, kw, s, p);
+    if (staged) {
+      ctx->plane_hints.erase(dy);
+      nrs_free(ctx, dhi);
+      if (dlo) nrs_free(ctx, dlo);
+    }
     if (masked) nrs_free(ctx, masked);
   };
   return out;

@@ -49,6 +49,10 @@ struct Node {
   std::vector<std::shared_ptr<Node>> parents;
   std::function<void()> backward_fn;
   std::vector<void*> saved;          // argmax, xhat, ... freed with the node
+  // NHWC operand planes of `data` for the tensor-core convolutions, staged once and shared
+  // by the forward pass and the weight gradient (registered with the context while alive).
+  float* planes_hi = nullptr;
+  float* planes_lo = nullptr;
 
   size_t len() const;
   bool on_gpu() const { return data != nullptr; }

@@ -32,6 +32,15 @@ struct NrsProfRecord {
   cudaEvent_t start, stop;
 };
 
+// NHWC planes of an NCHW activation, staged ahead of time by a caller that knows
+// the tensor will feed several tensor-core convolutions (forward and weight gradient,
+// or data and weight gradient).  lo is null unless `split` (3xTF32).
+struct NrsPlanes {
+  float* hi;
+  float* lo;
+  int split;
+};
+
 struct nrs_ctx {
   int device = 0;
   cudaStream_t own_stream = nullptr;
@@ -49,6 +58,9 @@ struct nrs_ctx {
   size_t ws_slot_bytes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   // Device word the tensor-core kernels set when a bounded wait runs out; read at sync points.
   int* err_flag = nullptr;
+  // Planes registered for a source tensor (keyed by its device pointer); the conv kernels
+  // use them instead of staging again.  Whoever registers keeps both alive and unregisters.
+  std::map<const void*, NrsPlanes> plane_hints;
   // Optional per-family device timing (nrs_profile_*).
   bool profiling = false;
   std::vector<NrsProfRecord> prof_records;
@@ -70,6 +82,11 @@ int nrs_workspace(nrs_ctx* ctx, size_t bytes, void** out);
 enum { NRS_WS_A_HI = 0, NRS_WS_A_LO = 1, NRS_WS_B_HI = 2, NRS_WS_B_LO = 3, NRS_WS_PARTIAL = 4, NRS_WS_COUNT = 8 };
 int nrs_ws_slot(nrs_ctx* ctx, int slot, size_t bytes, void** out);
 int nrs_err_flag(nrs_ctx* ctx, int** out);
+inline const NrsPlanes* nrs_planes_find(nrs_ctx* ctx, const void* src, bool split) {
+  auto it = ctx->plane_hints.find(src);
+  if (it == ctx->plane_hints.end() || (it->second.split != 0) != split) return nullptr;
+  return &it->second;
+}
 // Reads and clears the device error word (the stream must be idle); NRS_ERR_TIMEOUT if a kernel gave up a wait.
 int nrs_check_device_error(nrs_ctx* ctx);
 

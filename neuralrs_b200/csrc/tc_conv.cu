@@ -146,13 +146,21 @@ int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
   const size_t a_plane = (size_t)p.n_img * p.a_h * p.a_w * p.a_ch;
   const size_t w_plane = (size_t)p.co * p.ci * p.kh * p.kw;
   void *a_hi = nullptr, *a_lo = nullptr, *w_hi = nullptr, *w_lo = nullptr;
-  int st = nrs_ws_slot(ctx, NRS_WS_A_HI, a_plane * sizeof(float), &a_hi);
-  if (st == NRS_OK && split) st = nrs_ws_slot(ctx, NRS_WS_A_LO, a_plane * sizeof(float), &a_lo);
-  if (st == NRS_OK) st = nrs_ws_slot(ctx, NRS_WS_B_HI, w_plane * sizeof(float), &w_hi);
+  int st = NRS_OK;
+  const NrsPlanes* ready = nrs_planes_find(ctx, p.act_src, split);
+  if (ready) {
+    a_hi = ready->hi;
+    a_lo = ready->lo;
+  } else {
+    st = nrs_ws_slot(ctx, NRS_WS_A_HI, a_plane * sizeof(float), &a_hi);
+    if (st == NRS_OK && split) st = nrs_ws_slot(ctx, NRS_WS_A_LO, a_plane * sizeof(float), &a_lo);
+    if (st != NRS_OK) return st;
+    const size_t img = (size_t)p.a_h * p.a_w * p.a_ch;
+    st = nrs_tc_stage(ctx, p.act_src, (float*)a_hi, (float*)a_lo, p.a_h * p.a_w, p.a_ch, p.a_ch, p.n_img, img, img, true);
+    if (st != NRS_OK) return st;
+  }
+  st = nrs_ws_slot(ctx, NRS_WS_B_HI, w_plane * sizeof(float), &w_hi);
   if (st == NRS_OK && split) st = nrs_ws_slot(ctx, NRS_WS_B_LO, w_plane * sizeof(float), &w_lo);
-  if (st != NRS_OK) return st;
-  const size_t img = (size_t)p.a_h * p.a_w * p.a_ch;
-  st = nrs_tc_stage(ctx, p.act_src, (float*)a_hi, (float*)a_lo, p.a_h * p.a_w, p.a_ch, p.a_ch, p.n_img, img, img, true);
   if (st != NRS_OK) return st;
   st = nrs_tc_stage_conv_weight(ctx, p.w, (float*)w_hi, (float*)w_lo, p.co, p.ci, p.kh, p.kw, p.for_dgrad);
   if (st != NRS_OK) return st;

@@ -295,17 +295,28 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   const size_t dy_plane = (size_t)n * oh * ow * co, x_plane = (size_t)n * h * wd * ci;
   const size_t partial_floats = (size_t)splits * p.m_blocks * p.n_groups * 128 * p.group_cols;
   void *dy_hi = nullptr, *dy_lo = nullptr, *x_hi = nullptr, *x_lo = nullptr, *part = nullptr;
-  int st = nrs_ws_slot(ctx, NRS_WS_A_HI, dy_plane * sizeof(float), &dy_hi);
-  if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_A_LO, dy_plane * sizeof(float), &dy_lo);
-  if (st == NRS_OK) st = nrs_ws_slot(ctx, NRS_WS_B_HI, x_plane * sizeof(float), &x_hi);
-  if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_B_LO, x_plane * sizeof(float), &x_lo);
-  if (st == NRS_OK) st = nrs_ws_slot(ctx, NRS_WS_PARTIAL, partial_floats * sizeof(float), &part);
+  int st = nrs_ws_slot(ctx, NRS_WS_PARTIAL, partial_floats * sizeof(float), &part);
   if (st != NRS_OK) return st;
   p.partial = (float*)part;
   const size_t dy_img = (size_t)oh * ow * co, x_img = (size_t)h * wd * ci;
-  st = nrs_tc_stage(ctx, dy, (float*)dy_hi, (float*)dy_lo, oh * ow, co, co, n, dy_img, dy_img, true);
-  if (st == NRS_OK) st = nrs_tc_stage(ctx, x, (float*)x_hi, (float*)x_lo, h * wd, ci, ci, n, x_img, x_img, true);
-  if (st != NRS_OK) return st;
+  if (const NrsPlanes* ready = nrs_planes_find(ctx, dy, split3)) {
+    dy_hi = ready->hi;
+    dy_lo = ready->lo;
+  } else {
+    st = nrs_ws_slot(ctx, NRS_WS_A_HI, dy_plane * sizeof(float), &dy_hi);
+    if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_A_LO, dy_plane * sizeof(float), &dy_lo);
+    if (st == NRS_OK) st = nrs_tc_stage(ctx, dy, (float*)dy_hi, (float*)dy_lo, oh * ow, co, co, n, dy_img, dy_img, true);
+    if (st != NRS_OK) return st;
+  }
+  if (const NrsPlanes* ready = nrs_planes_find(ctx, x, split3)) {
+    x_hi = ready->hi;
+    x_lo = ready->lo;
+  } else {
+    st = nrs_ws_slot(ctx, NRS_WS_B_HI, x_plane * sizeof(float), &x_hi);
+    if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_B_LO, x_plane * sizeof(float), &x_lo);
+    if (st == NRS_OK) st = nrs_tc_stage(ctx, x, (float*)x_hi, (float*)x_lo, h * wd, ci, ci, n, x_img, x_img, true);
+    if (st != NRS_OK) return st;
+  }
 
   CUtensorMap maps[4];
   const uint64_t ddim[4] = {(uint64_t)co, (uint64_t)ow, (uint64_t)oh, (uint64_t)n};
