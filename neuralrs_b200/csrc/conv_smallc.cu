@@ -1,0 +1,216 @@
+// Direct convolution kernels for layers with very few input channels (the image
+// layer of a CNN: c_in = 1 or 3, 3x3, stride 1).  With K = c_in*kh*kw = 9 or 27 the
+// contraction is too short for a tensor-core K-block and a 128x128 implicit-GEMM
+// tile is mostly padding, so these layers get their own FFMA kernels:
+//   forward        one thread per output pixel holds the K-element input patch in
+//                  registers and sweeps the output channels against weights kept
+//                  in shared memory (128-bit broadcast loads); stores are full
+//                  128-byte lines per channel
+//   weight grad    dW[co][k] = sum_p dy[p][co] * patch[p][k]: blocks stream pixel
+//                  tiles through shared memory, each thread accumulates a 3 x 8
+//                  (k x co) register tile; per-block partials are summed in a
+//                  fixed order by a second kernel (deterministic)
+// Exact f32.  Reference counterparts: conv2d_im2col + matmul_nn + col2out and
+// im2col + matmul_nt_splitk (src/cuda/nn/conv.rs:244-320).
+#include "igemm_problems.cuh"
+#include "nrs_internal.h"
+
+namespace {
+
+template <int CI, int KS>
+__global__ void __launch_bounds__(256)
+smallc_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                  float* __restrict__ y, int n, int h, int wd, int co, int pad, int oh, int ow, int act) {
+  constexpr int K = CI * KS * KS;
+  constexpr int K4 = (K + 3) / 4 * 4;
+  extern __shared__ __align__(16) float smem_f[];
+  float* w_s = smem_f;               // [co][K4]
+  float* b_s = smem_f + (size_t)co * K4;
+  for (int i = threadIdx.x; i < co * K4; i += blockDim.x) {
+    const int c = i / K4, k = i - c * K4;
+    w_s[i] = k < K ? w[(size_t)c * K + k] : 0.0f;
+  }
+  for (int i = threadIdx.x; i < co; i += blockDim.x) b_s[i] = b ? b[i] : 0.0f;
+  __syncthreads();
+  const size_t plane = (size_t)oh * ow;
+  const size_t total = (size_t)n * plane;
+  for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < total; p += (size_t)gridDim.x * blockDim.x) {
+    const size_t img = p / plane;
+    const int pix = (int)(p - img * plane);
+    const int oy = pix / ow, ox = pix - oy * ow;
+    float patch[K4];
+#pragma unroll
+    for (int k = 0; k < K4; ++k) {
+      float v = 0.0f;
+      if (k < K) {
+        const int c = k / (KS * KS), t = k - c * KS * KS, i = t / KS, j = t - i * KS;
+        const int iy = oy + i - pad, ix = ox + j - pad;
+        if ((unsigned)iy < (unsigned)h && (unsigned)ix < (unsigned)wd)
+          v = x[((img * CI + c) * h + iy) * wd + ix];
+      }
+      patch[k] = v;
+    }
+    float* dst = y + img * co * plane + pix;
+    for (int c = 0; c < co; ++c) {
+      float acc = b_s[c];
+      const float4* wr = reinterpret_cast<const float4*>(w_s + (size_t)c * K4);
+#pragma unroll
+      for (int k4 = 0; k4 < K4 / 4; ++k4) {
+        const float4 wv = wr[k4];
+        acc = fmaf(patch[4 * k4 + 0], wv.x, acc);
+        acc = fmaf(patch[4 * k4 + 1], wv.y, acc);
+        acc = fmaf(patch[4 * k4 + 2], wv.z, acc);
+        acc = fmaf(patch[4 * k4 + 3], wv.w, acc);
+      }
+      dst[(size_t)c * plane] = nrs_apply_act(acc, act);
+    }
+  }
+}
+
+constexpr int TP = 128;   // pixels per shared-memory tile (weight gradient)
+
+template <int CI, int KS>
+__global__ void __launch_bounds__(256)
+smallc_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ partial, int n, int h,
+                    int wd, int co, int pad, int oh, int ow, int tiles_per_img, int total_tiles, int ns) {
+  constexpr int K = CI * KS * KS;
+  constexpr int KG = K / 3;            // thread owns 3 consecutive k
+  extern __shared__ __align__(16) float smem_f[];
+  float* dy_s = smem_f;                               // [co][TP+1]
+  float* pa_s = smem_f + (size_t)co * (TP + 1);       // [K][TP+1]
+  const int cob = co / 8;
+  const int t = threadIdx.x;
+  const bool active = t < ns * KG * cob;
+  const int kg = t % KG, cb = (t / KG) % cob, s = t / (KG * cob);
+  float acc[3][8];
+#pragma unroll
+  for (int a = 0; a < 3; ++a)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[a][c] = 0.0f;
+  const int plane = oh * ow;
+  for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    const int img = tile / tiles_per_img, p0 = (tile - img * tiles_per_img) * TP;
+    const int tp = min(TP, plane - p0);
+    __syncthreads();   // previous tile fully consumed
+    for (int i = t; i < co * TP; i += blockDim.x) {
+      const int c = i / TP, p = i - c * TP;
+      dy_s[c * (TP + 1) + p] = p < tp ? dy[((size_t)img * co + c) * plane + p0 + p] : 0.0f;
+    }
+    for (int i = t; i < K * TP; i += blockDim.x) {
+      const int k = i / TP, p = i - k * TP;
+      float v = 0.0f;
+      if (p < tp) {
+        const int pix = p0 + p, oy = pix / ow, ox = pix - oy * ow;
+        const int c = k / (KS * KS), tt = k - c * KS * KS, ii = tt / KS, jj = tt - ii * KS;
+        const int iy = oy + ii - pad, ix = ox + jj - pad;
+        if ((unsigned)iy < (unsigned)h && (unsigned)ix < (unsigned)wd)
+          v = x[(((size_t)img * CI + c) * h + iy) * wd + ix];
+      }
+      pa_s[k * (TP + 1) + p] = v;
+    }
+    __syncthreads();
+    if (active) {
+      for (int p = s; p < tp; p += ns) {
+        float a[3], d[8];
+#pragma unroll
+        for (int q = 0; q < 3; ++q) a[q] = pa_s[(3 * kg + q) * (TP + 1) + p];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) d[c] = dy_s[(8 * cb + c) * (TP + 1) + p];
+#pragma unroll
+        for (int q = 0; q < 3; ++q)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[q][c] = fmaf(a[q], d[c], acc[q][c]);
+      }
+    }
+  }
+  if (active) {
+    float* dst = partial + ((size_t)blockIdx.x * ns + s) * co * K;
+#pragma unroll
+    for (int q = 0; q < 3; ++q)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) dst[(size_t)(8 * cb + c) * K + 3 * kg + q] = acc[q][c];
+  }
+}
+
+__global__ void smallc_wgrad_reduce_kernel(const float* __restrict__ partial, float* dw, int parts, int len, int accumulate) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= len) return;
+  float s = 0.0f;
+  for (int z = 0; z < parts; ++z) s += partial[(size_t)z * len + i];
+  dw[i] = accumulate ? dw[i] + s : s;
+}
+
+template <int CI, int KS>
+int run_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y, int n, int h, int wd, int co,
+            int pad, int oh, int ow, int act) {
+  constexpr int K4 = (CI * KS * KS + 3) / 4 * 4;
+  const size_t smem = ((size_t)co * K4 + co) * sizeof(float);
+  static size_t attr = 0;
+  if (smem > 48 * 1024 && smem > attr) {
+    NRS_CUDA(ctx, cudaFuncSetAttribute(smallc_fwd_kernel<CI, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = smem;
+  }
+  const size_t total = (size_t)n * oh * ow;
+  size_t blocks = (total + 255) / 256;
+  const size_t cap = (size_t)ctx->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  smallc_fwd_kernel<CI, KS><<<(unsigned)blocks, 256, smem, ctx->stream>>>(x, w, b, y, n, h, wd, co, pad, oh, ow, act);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
+template <int CI, int KS>
+int run_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int h, int wd, int co, int pad, int oh,
+              int ow, int accumulate) {
+  constexpr int K = CI * KS * KS, KG = K / 3;
+  const int cob = co / 8;
+  int ns = 256 / (KG * cob);
+  if (ns < 1) return NRS_ERR_UNSUPPORTED;
+  if (ns > 8) ns = 8;
+  const size_t smem = ((size_t)co + K) * (TP + 1) * sizeof(float);
+  if (smem > 200 * 1024) return NRS_ERR_UNSUPPORTED;
+  static size_t attr = 0;
+  if (smem > 48 * 1024 && smem > attr) {
+    NRS_CUDA(ctx, cudaFuncSetAttribute(smallc_wgrad_kernel<CI, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = smem;
+  }
+  const int plane = oh * ow;
+  const int tiles_per_img = (plane + TP - 1) / TP;
+  const long total_tiles = (long)tiles_per_img * n;
+  if (total_tiles > 2147483647L) return NRS_ERR_UNSUPPORTED;
+  int blocks = ctx->sm_count * 4;
+  if (blocks > total_tiles) blocks = (int)total_tiles;
+  void* ws = nullptr;
+  const int st = nrs_workspace(ctx, (size_t)blocks * ns * co * K * sizeof(float), &ws);
+  if (st != NRS_OK) return st;
+  smallc_wgrad_kernel<CI, KS><<<blocks, 256, smem, ctx->stream>>>(x, dy, (float*)ws, n, h, wd, co, pad, oh, ow,
+                                                                  tiles_per_img, (int)total_tiles, ns);
+  NRS_LAUNCHED(ctx);
+  smallc_wgrad_reduce_kernel<<<nrs_blocks((size_t)co * K, 256), 256, 0, ctx->stream>>>((const float*)ws, dw, blocks * ns,
+                                                                                      co * K, accumulate);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
+bool eligible(int ci, int kh, int kw, int stride, int co) {
+  return stride == 1 && kh == 3 && kw == 3 && (ci == 1 || ci == 3) && co >= 8 && co % 8 == 0 && co <= 256;
+}
+
+}  // namespace
+
+// NRS_ERR_UNSUPPORTED when the layer is not a 3x3 stride-1 convolution over 1 or 3 channels.
+int nrs_smallc_conv_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y, int n, int ci, int h,
+                        int wd, int co, int kh, int kw, int stride, int pad, int act) {
+  if (!eligible(ci, kh, kw, stride, co) || getenv("NRS_DISABLE_SMALLC")) return NRS_ERR_UNSUPPORTED;
+  const int oh = h + 2 * pad - 2, ow = wd + 2 * pad - 2;
+  if (ci == 1) return run_fwd<1, 3>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act);
+  return run_fwd<3, 3>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act);
+}
+
+int nrs_smallc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
+                          int kh, int kw, int stride, int pad, int accumulate) {
+  if (!eligible(ci, kh, kw, stride, co) || co > 128 || getenv("NRS_DISABLE_SMALLC")) return NRS_ERR_UNSUPPORTED;
+  const int oh = h + 2 * pad - 2, ow = wd + 2 * pad - 2;
+  if (ci == 1) return run_wgrad<1, 3>(ctx, x, dy, dw, n, h, wd, co, pad, oh, ow, accumulate);
+  return run_wgrad<3, 3>(ctx, x, dy, dw, n, h, wd, co, pad, oh, ow, accumulate);
+}

@@ -268,6 +268,8 @@ int nrs_conv2d_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b,
   NRS_REQUIRE(ctx, x && w && y, NRS_ERR_ARG, "nrs_conv2d_fwd: null tensor");
   NrsProfScope prof(ctx, NRS_PROF_CONV_FWD,
                     2.0 * n * co * ((h + 2 * pad - kh) / stride + 1) * ((wd + 2 * pad - kw) / stride + 1) * ci * kh * kw);
+  st = nrs_smallc_conv_fwd(ctx, x, w, b, y, n, ci, h, wd, co, kh, kw, stride, pad, act);
+  if (st != NRS_ERR_UNSUPPORTED) return st;
   if (ctx->math_mode != NRS_MATH_FP32) {
     st = nrs_tc_conv_fwd(ctx, x, w, b, y, n, ci, h, wd, co, kh, kw, stride, pad, act);
     if (st != NRS_ERR_UNSUPPORTED) return st;
@@ -313,9 +315,9 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
   }
   if (dw) {
     NrsProfScope prof(ctx, NRS_PROF_CONV_WGRAD, conv_flop);
-    st = ctx->math_mode != NRS_MATH_FP32
-             ? nrs_tc_conv_wgrad(ctx, x, dy, dw, n, ci, h, wd, co, kh, kw, stride, pad, accumulate)
-             : NRS_ERR_UNSUPPORTED;
+    st = nrs_smallc_conv_wgrad(ctx, x, dy, dw, n, ci, h, wd, co, kh, kw, stride, pad, accumulate);
+    if (st == NRS_ERR_UNSUPPORTED && ctx->math_mode != NRS_MATH_FP32)
+      st = nrs_tc_conv_wgrad(ctx, x, dy, dw, n, ci, h, wd, co, kh, kw, stride, pad, accumulate);
     if (st != NRS_OK && st != NRS_ERR_UNSUPPORTED) return st;
     if (st == NRS_ERR_UNSUPPORTED) {
     NrsConvWgradProb p;
