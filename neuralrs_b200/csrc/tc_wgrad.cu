@@ -32,13 +32,14 @@ constexpr int kMaxN = 256;        // widest UMMA
 constexpr int kABlocks = 4;       // 4 x 32 output channels = 128 rows
 
 struct WgradParams {
-  int Wt, Ht, Nt, tiles_y;        // pixel tile (box) geometry in dy space
+  int Wt, Ht, Nt, tiles_y, tiles_x;  // pixel tile (box) geometry in dy space
   int kp;                         // pixels per tile = Wt*Ht*Nt (multiple of 8)
   int n_tiles;                    // pixel tiles in all
   int tiles_per_split;
   int co, ci, kh, kw, pad;
   int taps_per_group, n_groups;   // taps handled by one CTA
   int cblocks;                    // ci / 32
+  int a_box_blocks;               // 32-channel blocks of dy one box brings (min(4, co/32))
   int m_blocks;                   // ceil(co / 128)
   float* partial;                 // [split][m_block][group][128][group_cols]
   int group_cols;                 // taps_per_group * ci
@@ -68,7 +69,6 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
   const int ntiles = t_end - t_begin;
   const int tap0 = grp * p.taps_per_group;
   const int ntaps = min(p.taps_per_group, p.kh * p.kw - tap0);
-  const int a_blocks_live = min(kABlocks, (p.co - mb * 128 + 31) / 32);
 
   if (warp == 0 && lane == 0) {
     tc::prefetch_tmap(&tm_dy_hi);
@@ -90,7 +90,12 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer: one pixel tile per ring slot
-      const uint32_t tx = NPLANES * (uint32_t)(a_blocks_live + ntaps * p.cblocks) * blk_bytes;
+      // One 5-D box per operand plane brings all 32-channel blocks of a pixel tile at once
+      // (the channel-block index is the outermost box dimension), so a tile costs
+      // planes x (1 + taps) TMA instructions instead of one per block.
+      const uint32_t tx = NPLANES * (uint32_t)(p.a_box_blocks + ntaps * p.cblocks) * blk_bytes;
+      int tap_i[9], tap_j[9];
+      for (int t = 0; t < ntaps && t < 9; ++t) { tap_i[t] = (tap0 + t) / p.kw; tap_j[t] = (tap0 + t) - tap_i[t] * p.kw; }
       int issued = 0;
       bool ok = true;
       for (int it = 0; it < ntiles; ++it, ++issued) {
@@ -98,7 +103,8 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
         const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
         if (!tc::mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(err_flag, tc::kErrProducerWait); ok = false; break; }
         const int pt = t_begin + it;
-        const int n0 = (pt / p.tiles_y) * p.Nt, y0 = (pt % p.tiles_y) * p.Ht;
+        const int xt = pt % p.tiles_x, rest = pt / p.tiles_x;
+        const int n0 = (rest / p.tiles_y) * p.Nt, y0 = (rest % p.tiles_y) * p.Ht, x0 = xt * p.Wt;
         uint8_t* st = smem + (size_t)s * stage_bytes;
         tc::mbar_expect_tx(&full_bar[s], tx);
 #pragma unroll 1
@@ -107,14 +113,10 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
           const CUtensorMap* txm = pl == 0 ? &tm_x_hi : &tm_x_lo;
           uint8_t* a_dst = st + pl * (a_bytes + b_bytes);
           uint8_t* b_dst = a_dst + a_bytes;
-          for (int blk = 0; blk < a_blocks_live; ++blk)
-            tc::tma_load_4d(a_dst + blk * blk_bytes, tdy, &full_bar[s], mb * 128 + blk * 32, 0, y0, n0);
-          for (int t = 0; t < ntaps; ++t) {
-            const int tap = tap0 + t, i = tap / p.kw, j = tap - i * p.kw;
-            for (int cb = 0; cb < p.cblocks; ++cb)
-              tc::tma_load_4d(b_dst + (t * p.cblocks + cb) * blk_bytes, txm, &full_bar[s], cb * 32, j - p.pad,
-                              y0 + i - p.pad, n0);
-          }
+          tc::tma_load_5d(a_dst, tdy, &full_bar[s], 0, x0, y0, n0, mb * kABlocks);
+          for (int t = 0; t < ntaps; ++t)
+            tc::tma_load_5d(b_dst + (size_t)t * p.cblocks * blk_bytes, txm, &full_bar[s], 0, x0 + tap_j[t] - p.pad,
+                            y0 + tap_i[t] - p.pad, n0, 0);
         }
       }
       if (!ok) {
@@ -248,20 +250,25 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   const bool split3 = ctx->math_mode == NRS_MATH_3XTF32;
   const int planes = split3 ? 2 : 1;
 
+  // Pixel tile = one TMA box {32 channels, Wt, Ht, Nt}.  Small tiles keep the ring deep (the
+  // two-plane 3xTF32 stage is 2.5 KB per pixel): 16 pixels per tile with planes, 32 without.
+  const int target = getenv("NRS_WGRAD_KP") ? atoi(getenv("NRS_WGRAD_KP")) : 32;
   WgradParams p{};
   p.Wt = ow;
-  p.Ht = 32 / ow > 1 ? 32 / ow : 1;
+  if (ow > target && ow % target == 0) p.Wt = target;
+  p.tiles_x = ow / p.Wt;
+  p.Ht = target / p.Wt > 1 ? target / p.Wt : 1;
   if (p.Ht > oh) p.Ht = oh;
   while ((p.Wt * p.Ht) % 8 != 0 && p.Ht < oh) ++p.Ht;
   p.Nt = 1;
-  if (p.Ht == oh && p.Wt * p.Ht < 32) {
-    p.Nt = 32 / (p.Wt * p.Ht);
+  if (p.Ht == oh && p.Wt * p.Ht < target) {
+    p.Nt = target / (p.Wt * p.Ht);
     if (p.Nt > n) p.Nt = n;
   }
   p.kp = p.Wt * p.Ht * p.Nt;
   if (p.kp % 8 != 0 || p.kp > 64) return NRS_ERR_UNSUPPORTED;
   p.tiles_y = (oh + p.Ht - 1) / p.Ht;
-  p.n_tiles = ((n + p.Nt - 1) / p.Nt) * p.tiles_y;
+  p.n_tiles = ((n + p.Nt - 1) / p.Nt) * p.tiles_y * p.tiles_x;
   p.co = co; p.ci = ci; p.kh = kh; p.kw = kw; p.pad = pad;
   p.cblocks = ci / 32;
   p.m_blocks = (co + 127) / 128;
@@ -276,14 +283,14 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   const size_t stage_bytes = (size_t)planes * (kABlocks + p.group_cols / 32) * p.kp * 128;
   int stages = (int)((200 * 1024) / stage_bytes);
   if (stages < 2) return NRS_ERR_UNSUPPORTED;
-  if (stages > 4) stages = 4;
+  if (stages > 6) stages = 6;
   const size_t smem_bytes = stages * stage_bytes + 1024 + 256;
 
   // pixel split: fill the GPU, and bound the accumulation chain in 3xTF32 mode
   const int ctas_per_split = p.m_blocks * p.n_groups;
   int splits = (2 * ctx->sm_count + ctas_per_split - 1) / ctas_per_split;
   int tps = (p.n_tiles + splits - 1) / splits;
-  if (tps < 8) tps = 8;
+  if (tps * p.kp < 512) tps = 512 / p.kp;   // amortise the prologue and the partial-tile store
   if (split3 && tps * p.kp > tc::kMaxChainK) tps = tc::kMaxChainK / p.kp;
   if (tps > p.n_tiles) tps = p.n_tiles;
   if (tps < 1) tps = 1;
@@ -319,25 +326,29 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   }
 
   CUtensorMap maps[4];
-  const uint64_t ddim[4] = {(uint64_t)co, (uint64_t)ow, (uint64_t)oh, (uint64_t)n};
-  const uint64_t dstr[3] = {(uint64_t)co * 4, (uint64_t)ow * co * 4, (uint64_t)oh * ow * co * 4};
-  const uint64_t xdim[4] = {(uint64_t)ci, (uint64_t)wd, (uint64_t)h, (uint64_t)n};
-  const uint64_t xstr[3] = {(uint64_t)ci * 4, (uint64_t)wd * ci * 4, (uint64_t)h * wd * ci * 4};
-  const uint32_t box[4] = {32, (uint32_t)p.Wt, (uint32_t)p.Ht, (uint32_t)p.Nt};
-  bool ok = tc::encode_tmap_f32(&maps[0], dy_hi, 4, ddim, dstr, box, true) && tc::encode_tmap_f32(&maps[2], x_hi, 4, xdim, xstr, box, true);
-  if (split3) ok = ok && tc::encode_tmap_f32(&maps[1], dy_lo, 4, ddim, dstr, box, true) && tc::encode_tmap_f32(&maps[3], x_lo, 4, xdim, xstr, box, true);
+  p.a_box_blocks = co / 32 < kABlocks ? co / 32 : kABlocks;
+  // planes viewed as [channel block][n][h][w][32 channels]: the block index is the outermost dimension
+  const uint64_t ddim[5] = {32, (uint64_t)ow, (uint64_t)oh, (uint64_t)n, (uint64_t)(co / 32)};
+  const uint64_t dstr[4] = {(uint64_t)co * 4, (uint64_t)ow * co * 4, (uint64_t)oh * ow * co * 4, 128};
+  const uint64_t xdim[5] = {32, (uint64_t)wd, (uint64_t)h, (uint64_t)n, (uint64_t)(ci / 32)};
+  const uint64_t xstr[4] = {(uint64_t)ci * 4, (uint64_t)wd * ci * 4, (uint64_t)h * wd * ci * 4, 128};
+  const uint32_t dbox[5] = {32, (uint32_t)p.Wt, (uint32_t)p.Ht, (uint32_t)p.Nt, (uint32_t)p.a_box_blocks};
+  const uint32_t xbox[5] = {32, (uint32_t)p.Wt, (uint32_t)p.Ht, (uint32_t)p.Nt, (uint32_t)p.cblocks};
+  bool ok = tc::encode_tmap_f32(&maps[0], dy_hi, 5, ddim, dstr, dbox, true) && tc::encode_tmap_f32(&maps[2], x_hi, 5, xdim, xstr, xbox, true);
+  if (split3) ok = ok && tc::encode_tmap_f32(&maps[1], dy_lo, 5, ddim, dstr, dbox, true) && tc::encode_tmap_f32(&maps[3], x_lo, 5, xdim, xstr, xbox, true);
   else { maps[1] = maps[0]; maps[3] = maps[2]; }
   NRS_REQUIRE(ctx, ok, NRS_ERR_CUDA, "tc_wgrad: cuTensorMapEncodeTiled failed");
 
-  if (split3) {
-    if (stages >= 4) st = launch_wgrad<2, 4>(ctx, maps, p, splits, smem_bytes);
-    else if (stages == 3) st = launch_wgrad<2, 3>(ctx, maps, p, splits, smem_bytes);
-    else st = launch_wgrad<2, 2>(ctx, maps, p, splits, smem_bytes);
-  } else {
-    if (stages >= 4) st = launch_wgrad<1, 4>(ctx, maps, p, splits, smem_bytes);
-    else if (stages == 3) st = launch_wgrad<1, 3>(ctx, maps, p, splits, smem_bytes);
-    else st = launch_wgrad<1, 2>(ctx, maps, p, splits, smem_bytes);
+#define NRS_WG(PL)                                                                     \
+  switch (stages) {                                                                    \
+    case 2: st = launch_wgrad<PL, 2>(ctx, maps, p, splits, smem_bytes); break;         \
+    case 3: st = launch_wgrad<PL, 3>(ctx, maps, p, splits, smem_bytes); break;         \
+    case 4: st = launch_wgrad<PL, 4>(ctx, maps, p, splits, smem_bytes); break;         \
+    case 5: st = launch_wgrad<PL, 5>(ctx, maps, p, splits, smem_bytes); break;         \
+    default: st = launch_wgrad<PL, 6>(ctx, maps, p, splits, smem_bytes); break;        \
   }
+  if (split3) { NRS_WG(2) } else { NRS_WG(1) }
+#undef NRS_WG
   if (st != NRS_OK) return st;
   const size_t total = (size_t)co * ci * taps;
   tc_wgrad_reduce_kernel<<<nrs_blocks(total, 256), 256, 0, ctx->stream>>>(p, splits, dw, accumulate);
