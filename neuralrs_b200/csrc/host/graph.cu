@@ -35,6 +35,11 @@ Node::~Node() {
     nrs_free(ctx, planes_hi);
     if (planes_lo) nrs_free(ctx, planes_lo);
   }
+  if (gplanes_hi) {
+    ctx->plane_hints.erase(grad);
+    nrs_free(ctx, gplanes_hi);
+    if (gplanes_lo) nrs_free(ctx, gplanes_lo);
+  }
   if (data && owns_data) nrs_free(ctx, data);
   if (grad && owns_grad) nrs_free(ctx, grad);
   for (void* p : saved) nrs_free(ctx, p);
@@ -69,6 +74,13 @@ struct GradTarget {
 static GradTarget grad_target(const NodeP& n) {
   Node* r = grad_root(n.get());
   if (!r->grad) r->grad = dalloc(r->ctx, r->len());
+  if (r->grad_premasked) {
+    // A second consumer adds an unmasked share: drop the claim (and the now stale planes); the
+    // ReLU mask is a 0/1 factor, so masking the sum later leaves the first share unchanged.
+    r->grad_premasked = false;
+    if (r->gplanes_hi) { nrs_free(r->ctx, r->gplanes_hi); r->gplanes_hi = nullptr; }
+    if (r->gplanes_lo) { nrs_free(r->ctx, r->gplanes_lo); r->gplanes_lo = nullptr; }
+  }
   GradTarget t{r->grad, r->grad_valid ? 1 : 0};
   r->grad_valid = true;
   return t;
@@ -123,6 +135,11 @@ static bool stage_planes(nrs_ctx* ctx, const float* src, const std::vector<size_
   check(ctx, nrs_tc_stage(ctx, src, *hi, *lo, (int)hw, (int)c, (int)c, (int)n, c * hw, c * hw, true));
   ctx->plane_hints[src] = NrsPlanes{*hi, *lo, split ? 1 : 0};
   return true;
+}
+
+static bool planes_possible(nrs_ctx* ctx) {
+  return ctx->math_mode != NRS_MATH_FP32 && tc::tensor_map_encoder() && !getenv("NRS_DISABLE_TC") &&
+         !getenv("NRS_NO_PLANE_CACHE");
 }
 
 namespace cuda {
@@ -506,24 +523,44 @@ NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, 
                             (int)pad, act));
   Node* self = out.get();
   const int s = (int)stride, p = (int)pad;
+  out->relu_folded = act == NRS_ACT_RELU;
+  out->wants_grad_planes = act == NRS_ACT_RELU && s == 1 && ci % 32 == 0 && co % 32 == 0;
   out->backward_fn = [self, x, w, b, n, ci, h, wd, co, kh, kw, s, p, act]() {
     nrs_ctx* ctx = self->ctx;
     const float* dy = grad_in(self);
     float* masked = nullptr;
-    if (act == NRS_ACT_RELU) {  // y > 0 exactly where the pre-activation was > 0
-      masked = dalloc(ctx, self->len());
-      check(ctx, nrs_relu_bwd(ctx, self->data, dy, masked, self->len(), 0));
-      dy = masked;
-    }
-    // dy feeds both the data and the weight gradient: stage its planes once.
     float *dhi = nullptr, *dlo = nullptr;
-    const bool staged = s == 1 && ci % 32 == 0 && stage_planes(ctx, dy, self->shape, &dhi, &dlo);
-    conv_backward(self, x, w, b, dy, n, ci, h, wd, co, kh, kw, s, p);
-    if (staged) {
-      ctx->plane_hints.erase(dy);
-      nrs_free(ctx, dhi);
-      if (dlo) nrs_free(ctx, dlo);
+    bool staged = false;
+    // Do the tensor-core data / weight gradients want NHWC planes of dy?
+    const bool want_planes = s == 1 && ci % 32 == 0 && co % 32 == 0 && planes_possible(ctx);
+    if (self->grad_premasked) {
+      // A max-pool above already folded the ReLU mask into this gradient (and may have left planes).
+      if (self->gplanes_hi && want_planes && !ctx->plane_hints.count(dy)) {
+        ctx->plane_hints[dy] = NrsPlanes{self->gplanes_hi, self->gplanes_lo, self->gplanes_lo ? 1 : 0};
+        staged = true;   // owned by the node, only unregistered below
+      }
+    } else if (act == NRS_ACT_RELU) {  // y > 0 exactly where the pre-activation was > 0
+      masked = dalloc(ctx, self->len());
+      if (want_planes) {   // mask and stage in one pass
+        const bool split = ctx->math_mode == NRS_MATH_3XTF32;
+        dhi = dalloc(ctx, self->len());
+        if (split) dlo = dalloc(ctx, self->len());
+        check(ctx, nrs_tc_stage_masked(ctx, 0, dy, self->data, nullptr, n, co, (int)self->shape[2], (int)self->shape[3], 1,
+                                       masked, dhi, dlo));
+        ctx->plane_hints[masked] = NrsPlanes{dhi, dlo, split ? 1 : 0};
+        staged = true;
+      } else {
+        check(ctx, nrs_relu_bwd(ctx, self->data, dy, masked, self->len(), 0));
+      }
+      dy = masked;
+    } else if (want_planes) {
+      // dy feeds both the data and the weight gradient: stage its planes once.
+      staged = stage_planes(ctx, dy, self->shape, &dhi, &dlo);
     }
+    conv_backward(self, x, w, b, dy, n, ci, h, wd, co, kh, kw, s, p);
+    if (staged) ctx->plane_hints.erase(dy);
+    if (dhi) nrs_free(ctx, dhi);
+    if (dlo) nrs_free(ctx, dlo);
     if (masked) nrs_free(ctx, masked);
   };
   return out;
@@ -549,9 +586,27 @@ NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride) {
   Node* self = out.get();
   out->backward_fn = [self, x, am, n, c, h, w, k, s]() {
     if (!x->requires_grad) return;
+    nrs_ctx* ctx = self->ctx;
     const float* g = grad_in(self);
+    // Pool over the output of a convolution with a folded ReLU: one pass computes that
+    // convolution's masked gradient (and its NHWC planes when its tensor-core backward wants
+    // them) instead of pool-backward, ReLU-backward and staging as three passes.
+    Node* xr = x.get();
+    if (k == s && xr->relu_folded && !xr->view_of && !xr->grad_valid && !xr->grad_premasked) {
+      GradTarget t = grad_target(x);   // overwrite mode by construction
+      float *phi = nullptr, *plo = nullptr;
+      if (xr->wants_grad_planes && planes_possible(ctx) && !xr->gplanes_hi) {
+        phi = dalloc(ctx, xr->len());
+        if (ctx->math_mode == NRS_MATH_3XTF32) plo = dalloc(ctx, xr->len());
+      }
+      check(ctx, nrs_tc_stage_masked(ctx, 1, g, xr->data, (const int32_t*)am, n, c, h, w, k, t.ptr, phi, plo));
+      xr->gplanes_hi = phi;
+      xr->gplanes_lo = plo;
+      xr->grad_premasked = true;
+      return;
+    }
     GradTarget t = grad_target(x);
-    check(self->ctx, nrs_maxpool_bwd(self->ctx, g, (const int32_t*)am, t.ptr, n, c, h, w, k, s, t.accumulate));
+    check(ctx, nrs_maxpool_bwd(ctx, g, (const int32_t*)am, t.ptr, n, c, h, w, k, s, t.accumulate));
   };
   return out;
 }

@@ -53,6 +53,12 @@ struct Node {
   // by the forward pass and the weight gradient (registered with the context while alive).
   float* planes_hi = nullptr;
   float* planes_lo = nullptr;
+  // Set on the output of a convolution that folded a ReLU into its epilogue.  A max-pool
+  // directly above may then hand back a gradient that already carries the ReLU mask
+  // (grad_premasked), together with its NHWC planes (gplanes_*, freed with the node).
+  bool relu_folded = false, wants_grad_planes = false, grad_premasked = false;
+  float* gplanes_hi = nullptr;
+  float* gplanes_lo = nullptr;
 
   size_t len() const;
   bool on_gpu() const { return data != nullptr; }

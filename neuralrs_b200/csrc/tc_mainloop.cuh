@@ -269,6 +269,11 @@ int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, con
 // src_k_by_rows: the source is stored [K][rows] (transposed) instead of [rows][K].
 int nrs_tc_stage(nrs_ctx* ctx, const float* src, float* hi, float* lo, int rows, int K, int ldk, int batch,
                  size_t src_bstride, size_t dst_bstride, bool src_k_by_rows);
+// Masked gradient staging (see stage_masked_kernel): mode 0 = ReLU mask of dy[n,c,h,w] by y;
+// mode 1 = gradient of a k x k / stride-k max-pool (g[n,c,h/k,w/k], argmax) followed by the ReLU
+// mask by y[n,c,h,w].  nchw_out and the planes are each optional (lo only with hi).
+int nrs_tc_stage_masked(nrs_ctx* ctx, int mode, const float* g, const float* y, const int32_t* argmax, int n, int c,
+                        int h, int w, int k, float* nchw_out, float* hi, float* lo);
 // Conv weights w[co][ci][kh][kw] -> K-major planes.
 //  for_dgrad == 0: out[co][(i*kw + j)*ci_n + ci]   (forward B operand)
 //  for_dgrad == 1: out[ci][(i*kw + j)*co_n + co]   (data-gradient B operand)

@@ -104,7 +104,72 @@ stage_conv_weight_kernel(const float* __restrict__ w, float* __restrict__ hi, fl
   }
 }
 
+// Gradient staging fused with the masks that precede a convolution's backward pass.
+//   MODE 0  v = (y > 0) ? dy : 0                          (ReLU folded into the conv: y is its output)
+//   MODE 1  v = (argmax[o] == idx && y > 0) ? g[o] : 0     (k x k / stride k max-pool on top of that)
+// One pass reads the NCHW sources through 32 channel x 32 pixel tiles and writes the
+// masked gradient in NCHW (optional) and as NHWC TF32 planes (optional).
+template <bool SPLIT, int MODE>
+__global__ void __launch_bounds__(256)
+stage_masked_kernel(const float* __restrict__ g, const float* __restrict__ y, const int32_t* __restrict__ argmax,
+                    float* __restrict__ nchw_out, float* __restrict__ hi, float* __restrict__ lo, int c_n, int h,
+                    int w, int k, int oh, int ow) {
+  __shared__ float tile[32][33];
+  const int img = blockIdx.z, hw = h * w;
+  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int i = ty; i < 32; i += 8) {
+    const int c = c0 + i, px = p0 + tx;
+    float v = 0.0f;
+    if (c < c_n && px < hw) {
+      const size_t idx = ((size_t)img * c_n + c) * hw + px;
+      if (MODE == 0) {
+        v = y[idx] > 0.0f ? g[idx] : 0.0f;
+      } else {
+        const int yy = px / w, xx = px - yy * w;
+        const int oy = yy / k, ox = xx / k;
+        if (oy < oh && ox < ow) {
+          const size_t o = (((size_t)img * c_n + c) * oh + oy) * ow + ox;
+          if ((size_t)argmax[o] == idx && y[idx] > 0.0f) v = g[o];
+        }
+      }
+      if (nchw_out) nchw_out[idx] = v;
+    }
+    tile[i][tx] = v;
+  }
+  if (!hi) return;
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int px = p0 + i, c = c0 + tx;
+    if (px < hw && c < c_n) {
+      const float v = tile[tx][i];
+      const size_t o = ((size_t)img * hw + px) * c_n + c;
+      const float hv = tc::tf32_rn(v);
+      hi[o] = hv;
+      if (SPLIT) lo[o] = v - hv;
+    }
+  }
+}
+
 }  // namespace
+
+int nrs_tc_stage_masked(nrs_ctx* ctx, int mode, const float* g, const float* y, const int32_t* argmax, int n, int c,
+                        int h, int w, int k, float* nchw_out, float* hi, float* lo) {
+  if (n <= 0 || c <= 0) return NRS_OK;
+  const int oh = mode == 1 ? h / k : h, ow = mode == 1 ? w / k : w;
+  dim3 grid((unsigned)((h * w + 31) / 32), (unsigned)((c + 31) / 32), (unsigned)n);
+  if (grid.y > 65535 || grid.z > 65535) return NRS_ERR_UNSUPPORTED;
+  const bool split = lo != nullptr;
+  if (mode == 0) {
+    if (split) stage_masked_kernel<true, 0><<<grid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
+    else stage_masked_kernel<false, 0><<<grid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
+  } else {
+    if (split) stage_masked_kernel<true, 1><<<grid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
+    else stage_masked_kernel<false, 1><<<grid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
+  }
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
 
 int nrs_tc_stage(nrs_ctx* ctx, const float* src, float* hi, float* lo, int rows, int K, int ldk, int batch,
                  size_t src_bstride, size_t dst_bstride, bool src_k_by_rows) {

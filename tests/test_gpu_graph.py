@@ -269,3 +269,36 @@ def test_errors_are_reported_not_fatal(gpu_ctx):
         graph.relu(host_only)
     # the context is still usable afterwards
     assert np.all(gpu.to_host(graph.relu(a)) == 0)
+
+
+def test_pool_over_fused_relu_conv_with_second_consumer(gpu_ctx, oracle64):
+    """conv+ReLU (folded) feeds a max-pool AND a second consumer.  The pool's backward hands the
+    convolution a gradient that already carries the ReLU mask; the other consumer adds an
+    unmasked share.  Whatever the visiting order, the sum must end up masked exactly once."""
+    rng = np.random.default_rng(12)
+    n, ci, h, w, co = 2, 32, 8, 8, 32
+    x = rng.normal(size=(n, ci, h, w)).astype(np.float32)
+    wt = (rng.normal(size=(co, ci, 3, 3)) * 0.1).astype(np.float32)
+    b = (rng.normal(size=co) * 0.1).astype(np.float32)
+    gx, gw, gb = on_gpu(x, x.shape), on_gpu(wt, wt.shape), on_gpu(b, b.shape)
+    z = oracle64.conv2d_fwd(x, wt, b, 1, 1)
+    yr = oracle64.relu_fwd(z)
+    _, am = oracle64.maxpool_fwd(yr, 2, 2)
+    for pool_first in (True, False):
+        y = nn.conv2d_act(gx, gw, gb, 1, 1, 1)
+        pooled = nn.maxpool2d(y, 2, 2)
+        scaled = graph.scale(y, 0.5)
+        parts = [graph.reshape(pooled, [1, len(pooled)]), graph.reshape(scaled, [1, len(scaled)])]
+        sp = rng.normal(size=len(pooled)).astype(np.float32)
+        ss = rng.normal(size=len(scaled)).astype(np.float32)
+        # the branch listed LAST is visited first by the reverse topological walk
+        both = graph.concat_cols(parts[::-1] if pool_first else parts)
+        seed = np.concatenate([ss, sp] if pool_first else [sp, ss])
+        gpu.zero_grad([gx, gw, gb])
+        gpu.set_grad(both, seed)
+        backward_graph(both)
+        dy = oracle64.maxpool_bwd(sp.reshape(n, co, h // 2, w // 2), am, yr.shape) + 0.5 * ss.reshape(yr.shape)
+        dxr, dwr, dbr = oracle64.conv2d_bwd(x, wt, oracle64.relu_bwd(z, dy), 1, 1)
+        assert np.linalg.norm(gpu.read_grad(gw) - dwr.ravel()) <= 1e-4 * np.linalg.norm(dwr)
+        assert np.linalg.norm(gpu.read_grad(gx) - dxr.ravel()) <= 1e-4 * np.linalg.norm(dxr)
+        assert np.linalg.norm(gpu.read_grad(gb) - dbr.ravel()) <= 1e-4 * np.linalg.norm(dbr)
