@@ -168,6 +168,44 @@ def cpu_reference_run(workload: str, steps: int, warmup: int, min_seconds: float
                        f"(conv/matmul loops OpenMP-parallel as the reference's Rayon loops are)")
 
 
+def conv_microbench(ctx, stream, iters=10):
+    """BASELINE config C2: Conv2d [256,64,32,32] -> 128, 3x3 s1 p1; forward, data gradient and weight
+    gradient timed separately through the raw C ABI (staging included), algorithmic TFLOP/s each."""
+    import ctypes as C
+    import torch
+    from neuralrs_b200 import _lib
+    l = _lib.lib()
+    n, ci, h, w, co = 256, 64, 32, 32, 128
+    g = torch.Generator(device="cuda").manual_seed(1236)
+    x = torch.randn(n, ci, h, w, device="cuda", generator=g)
+    wt = torch.randn(co, ci, 3, 3, device="cuda", generator=g) * (2.0 / (ci * 9)) ** 0.5
+    b = torch.zeros(co, device="cuda")
+    dy = torch.randn(n, co, h, w, device="cuda", generator=g)
+    y, dx, dw = torch.empty_like(dy), torch.empty_like(x), torch.empty_like(wt)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    dims = (n, ci, h, w, co, 3, 3, 1, 1)
+    calls = {
+        "fwd": lambda: l.nrs_conv2d_fwd(ctx.h, P(x), P(wt), P(b), P(y), *dims, 0),
+        "dgrad": lambda: l.nrs_conv2d_bwd(ctx.h, P(x), P(wt), P(dy), P(dx), None, None, *dims, 0),
+        "wgrad": lambda: l.nrs_conv2d_bwd(ctx.h, P(x), P(wt), P(dy), None, P(dw), None, *dims, 0),
+    }
+    flop = 2.0 * n * co * h * w * ci * 9
+    out = {"shape": "x[256,64,32,32] w[128,64,3,3] s1 p1", "gflop_per_pass": flop / 1e9}
+    for name, fn in calls.items():
+        for _ in range(3):
+            _lib.check(ctx.h, fn())
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            _lib.check(ctx.h, fn())
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        out[name] = {"ms": ms, "tflops": flop / (ms / 1e3) / 1e12}
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -325,6 +363,8 @@ def run_ours(args):
                          "adamw_gbs": (adam["work"] / (adam["ms"] / 1e3) / 1e9) if adam["ms"] > 0 else None,
                          "hbm_peak_gbs": peaks["hbm_gbs"]},
         }
+        if world == 1 and args.workload == "vgg_cifar":
+            line["conv_microbench"] = conv_microbench(ctx, stream)
         if world == 1 and not args.no_cpu_baseline:
             r = cpu_reference_run(args.workload, 1, 1, min_seconds=10.0)
             line["cpu_baseline"] = {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "port",

@@ -250,9 +250,9 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   const bool split3 = ctx->math_mode == NRS_MATH_3XTF32;
   const int planes = split3 ? 2 : 1;
 
-  // Pixel tile = one TMA box {32 channels, Wt, Ht, Nt}.  Small tiles keep the ring deep (the
-  // two-plane 3xTF32 stage is 2.5 KB per pixel): 16 pixels per tile with planes, 32 without.
-  const int target = getenv("NRS_WGRAD_KP") ? atoi(getenv("NRS_WGRAD_KP")) : 32;
+  // Pixel tile = one TMA box {32 channels, Wt, Ht, Nt} of about 32 pixels.  (Measured: 16-pixel
+  // tiles with a deeper ring are slower — the single producer thread becomes TMA-issue bound.)
+  const int target = 32;
   WgradParams p{};
   p.Wt = ow;
   if (ow > target && ow % target == 0) p.Wt = target;
