@@ -2,22 +2,29 @@
 // A[128 x 32] . B[BN x 32]^T, both operands K-major in 128-byte-swizzled shared
 // memory, fed by TMA, consumed by tcgen05.mma kind::tf32.
 //
-// One CTA per (row tile, column tile, batch x K-split).  Six warps, fixed roles:
+// Persistent CTAs (one per SM) walk a list of output tiles (row tile, column tile,
+// batch x K-split).  Six warps, fixed roles:
 //   warp 0     TMA producer (one thread): per K-slice, one mbarrier-tracked ring
-//              slot holding the A and B slices (and their residual planes for 3xTF32)
-//   warp 1     TMEM allocation; one thread issues the UMMAs (M=128, N=BN, K=8) and
-//              commits ring slots back to the producer, then the accumulator to the
-//              epilogue
+//              slot holding the A and B slices (and their residual planes for 3xTF32);
+//              the ring runs ahead across tile boundaries
+//   warp 1     TMEM allocation; one thread issues the UMMAs (M=128, K=8) and commits
+//              ring slots back to the producer, then the accumulator to the epilogue
 //   warps 2-5  epilogue: tcgen05.ld (thread = accumulator row), policy-defined store
+// TMEM holds two accumulators, so the epilogue of tile i runs under the main loop of
+// tile i+1.
 // A Policy supplies how an A slice is fetched (dense rows for GEMM, a shifted
 // NHWC window for convolution) and what the epilogue does with a row of results.
 //
-// 3xTF32 (NPLANES == 2): per K-slice three UMMAs lo*hi + hi*lo + hi*hi accumulate
-// into the same TMEM tile.  The tensor core's f32 accumulation is not
-// round-to-nearest; its error grows linearly with the length of one
-// accumulation chain (about 7e-9 relative per K element), so callers keep a
-// chain at or below kMaxChainK by splitting K across CTAs, whose partial tiles
-// are summed in f32 by tc_splitk_reduce_kernel in a fixed order.
+// 3xTF32 (NPLANES == 2): the residual plane of B sits directly behind its high plane in
+// the ring slot, so one UMMA of width 2*BN computes A_hi.[B_hi ; B_lo] (hi*hi in columns
+// [0,BN), hi*lo in [BN,2BN)) and a second of width BN adds A_lo.B_hi onto the first half;
+// the epilogue sums the halves.  Against three UMMAs of width BN this reads a quarter
+// less shared memory per K-step, which is what bounds the narrow (BN = 64) tiles.
+// The tensor core's f32 accumulation is not round-to-nearest; its error grows
+// linearly with the length of one accumulation chain (about 7e-9 relative per K
+// element), so callers keep a chain at or below kMaxChainK by splitting K across
+// tiles, whose partial results are summed in f32 by tc_splitk_reduce_kernel in a
+// fixed order.
 //
 // Every mbarrier wait is bounded: on expiry the kernel records an error code,
 // waits (bounded) for TMA loads it already issued, frees its TMEM and returns.
@@ -32,15 +39,18 @@ namespace tc {
 constexpr int BM = 128, BK = 32;   // BK f32 = 128 bytes = one swizzle row
 constexpr int kThreads = 192;
 constexpr int kMaxChainK = 4096;   // longest single accumulation chain in 3xTF32 mode
+constexpr int kGroupM = 16;        // row tiles per raster group (see TileMap)
 
 template <int BN, int NPLANES>
 struct SmemLayout {
   static constexpr int kATile = BM * BK * 4;   // 16 KB
   static constexpr int kBTile = BN * BK * 4;
-  static constexpr int kStage = NPLANES * (kATile + kBTile);
+  static constexpr int kStage = NPLANES * (kATile + kBTile);   // [A_hi][B_hi][B_lo][A_lo]
   static constexpr int kStages = (200 * 1024) / kStage >= 8 ? 8 : (200 * 1024) / kStage;
   static constexpr int kBytes = kStages * kStage + 1024 /*align*/ + 256 /*barriers*/;
-  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr int kAccCols = NPLANES * BN;                 // one accumulator
+  static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;   // two of them
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM allocation must be a power of two <= 512");
 };
 
 struct SplitInfo {
@@ -53,32 +63,47 @@ struct SplitInfo {
   int rows_total;      // tiles_m * 128
 };
 
+// Tile list of one launch.  Within a (batch, split) plane tiles are visited in groups of
+// kGroupM row tiles x all column tiles, row tile fastest, so the tiles in flight at any
+// moment cover a compact block of the output and share operand slices through L2.
+struct TileMap {
+  int tiles_m, tiles_n;
+  long total;          // tiles_m * tiles_n * batches * splits
+  __device__ __forceinline__ void decode(long t, int* tile_m, int* tile_n, int* z) const {
+    const int per_z = tiles_m * tiles_n;
+    *z = (int)(t / per_z);
+    const int r = (int)(t - (long)*z * per_z);
+    const int group = r / (kGroupM * tiles_n);
+    const int first = group * kGroupM;
+    const int gm = min(kGroupM, tiles_m - first);
+    const int rr = r - group * kGroupM * tiles_n;
+    *tile_n = rr / gm;
+    *tile_m = first + (rr - *tile_n * gm);
+  }
+};
+
 template <int BN, int NPLANES, class Policy>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
           const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
-          const Policy pol, const SplitInfo sp, int* __restrict__ err_flag) {
+          const Policy pol, const SplitInfo sp, const TileMap tmap, int* __restrict__ err_flag) {
   using L = SmemLayout<BN, NPLANES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStage);
   uint64_t* empty_bar = full_bar + L::kStages;
-  uint64_t* accum_bar = empty_bar + L::kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint64_t* acc_full = empty_bar + L::kStages;   // [2] accumulator ready for the epilogue
+  uint64_t* acc_empty = acc_full + 2;            // [2] accumulator drained by the epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_m = blockIdx.x, n0 = blockIdx.y * BN;
-  const int batch = blockIdx.z / sp.splits, split = blockIdx.z - batch * sp.splits;
-  const int kb_begin = split * sp.kb_per_split;
-  const int kb_end = min(sp.kb_total, kb_begin + sp.kb_per_split);
-  const int nkb = kb_end - kb_begin;   // >= 1 by construction
 
   if (warp == 0 && lane == 0) {
     prefetch_tmap(&tm_a_hi);
     prefetch_tmap(&tm_b_hi);
     if (NPLANES == 2) { prefetch_tmap(&tm_a_lo); prefetch_tmap(&tm_b_lo); }
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -94,77 +119,115 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
     if (lane == 0) {
       // ---------------- TMA producer
       const uint32_t stage_bytes = (uint32_t)NPLANES * (pol.a_slice_bytes() + (uint32_t)L::kBTile);
-      int issued = 0;
+      uint32_t it = 0;   // ring position, runs on across tiles
       bool ok = true;
-      for (int it = 0; it < nkb; ++it, ++issued) {
-        const int s = it % L::kStages;
-        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(err_flag, kErrProducerWait); ok = false; break; }
-        uint8_t* st = smem + s * L::kStage;
-        const int kb = kb_begin + it;
-        mbar_expect_tx(&full_bar[s], stage_bytes);
-        pol.load_a(st, &tm_a_hi, &full_bar[s], kb, tile_m, batch);
-        tma_load_3d(st + L::kATile, &tm_b_hi, &full_bar[s], kb * BK, n0, batch);
-        if (NPLANES == 2) {
-          pol.load_a(st + L::kATile + L::kBTile, &tm_a_lo, &full_bar[s], kb, tile_m, batch);
-          tma_load_3d(st + 2 * L::kATile + L::kBTile, &tm_b_lo, &full_bar[s], kb * BK, n0, batch);
+      for (long t = blockIdx.x; t < tmap.total && ok; t += gridDim.x) {
+        int tile_m, tile_n, z;
+        tmap.decode(t, &tile_m, &tile_n, &z);
+        const int batch = z / sp.splits, split = z - batch * sp.splits;
+        const int kb_begin = split * sp.kb_per_split;
+        const int kb_end = min(sp.kb_total, kb_begin + sp.kb_per_split);
+        const int n0 = tile_n * BN;
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const int s = it % L::kStages;
+          const uint32_t ph = (it / L::kStages) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(err_flag, kErrProducerWait); ok = false; break; }
+          uint8_t* st = smem + s * L::kStage;
+          mbar_expect_tx(&full_bar[s], stage_bytes);
+          pol.load_a(st, &tm_a_hi, &full_bar[s], kb, tile_m, batch);
+          tma_load_3d(st + L::kATile, &tm_b_hi, &full_bar[s], kb * BK, n0, batch);
+          if (NPLANES == 2) {
+            tma_load_3d(st + L::kATile + L::kBTile, &tm_b_lo, &full_bar[s], kb * BK, n0, batch);
+            pol.load_a(st + L::kATile + 2 * L::kBTile, &tm_a_lo, &full_bar[s], kb, tile_m, batch);
+          }
         }
       }
       if (!ok) {
         // Loads already issued still land in this CTA's shared memory: wait for them
         // (bounded) before the CTA may retire.
-        for (int it = (issued > L::kStages ? issued - L::kStages : 0); it < issued; ++it) {
-          const int s = it % L::kStages;
-          if (!mbar_wait(&full_bar[s], (uint32_t)(it / L::kStages) & 1u)) { atomicExch(err_flag, kErrDrainWait); break; }
+        for (uint32_t j = (it > (uint32_t)L::kStages ? it - L::kStages : 0); j < it; ++j) {
+          const int s = j % L::kStages;
+          if (!mbar_wait(&full_bar[s], (j / L::kStages) & 1u)) { atomicExch(err_flag, kErrDrainWait); break; }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- UMMA issuer
-      constexpr uint32_t idesc = make_idesc_tf32(BM, BN, false, false);
+      constexpr uint32_t idesc_wide = make_idesc_tf32(BM, NPLANES * BN, false, false);
+      constexpr uint32_t idesc_half = make_idesc_tf32(BM, BN, false, false);
+      uint32_t it = 0, local = 0;
       bool ok = true;
-      for (int it = 0; it < nkb; ++it) {
-        const int s = it % L::kStages;
-        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
-        if (!mbar_wait(&full_bar[s], ph)) { atomicExch(err_flag, kErrMmaWait); ok = false; break; }
+      for (long t = blockIdx.x; t < tmap.total && ok; t += gridDim.x, ++local) {
+        int tile_m, tile_n, z;
+        tmap.decode(t, &tile_m, &tile_n, &z);
+        const int split = z % sp.splits;
+        const int kb_begin = split * sp.kb_per_split;
+        const int nkb = min(sp.kb_total, kb_begin + sp.kb_per_split) - kb_begin;   // >= 1 by construction
+        const uint32_t buf = local & 1u, use = local >> 1;
+        if (!mbar_wait(&acc_empty[buf], (use & 1u) ^ 1u)) { atomicExch(err_flag, kErrMmaWait); break; }
         tc_fence_after_sync();
-        const uint32_t a_hi = smem_u32(smem + s * L::kStage);
-        const uint32_t b_hi = a_hi + L::kATile;
-        const uint32_t a_lo = b_hi + L::kBTile;
-        const uint32_t b_lo = a_lo + L::kATile;
+        const uint32_t d = tmem_base + buf * (uint32_t)L::kAccCols;
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % L::kStages;
+          const uint32_t ph = (it / L::kStages) & 1u;
+          if (!mbar_wait(&full_bar[s], ph)) { atomicExch(err_flag, kErrMmaWait); ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_hi = smem_u32(smem + s * L::kStage);
+          const uint32_t b_hi = a_hi + L::kATile;                 // B_lo follows B_hi directly
+          const uint32_t a_lo = b_hi + 2 * L::kBTile;
 #pragma unroll
-        for (int k = 0; k < BK / 8; ++k) {
-          const uint32_t koff = k * 32;  // 8 f32 along K inside the 128-byte swizzle row
-          const uint64_t da_hi = make_smem_desc_sw128(a_hi + koff, 16, 1024);
-          const uint64_t db_hi = make_smem_desc_sw128(b_hi + koff, 16, 1024);
-          if (NPLANES == 2) {
-            const uint64_t da_lo = make_smem_desc_sw128(a_lo + koff, 16, 1024);
-            const uint64_t db_lo = make_smem_desc_sw128(b_lo + koff, 16, 1024);
-            umma_tf32(tmem_base, da_lo, db_hi, idesc, (it | k) != 0);
-            umma_tf32(tmem_base, da_hi, db_lo, idesc, 1);
-            umma_tf32(tmem_base, da_hi, db_hi, idesc, 1);
-          } else {
-            umma_tf32(tmem_base, da_hi, db_hi, idesc, (it | k) != 0);
+          for (int k = 0; k < BK / 8; ++k) {
+            const uint32_t koff = k * 32;  // 8 f32 along K inside the 128-byte swizzle row
+            const uint64_t da_hi = make_smem_desc_sw128(a_hi + koff, 16, 1024);
+            const uint64_t db_hi = make_smem_desc_sw128(b_hi + koff, 16, 1024);
+            umma_tf32(d, da_hi, db_hi, idesc_wide, (i | k) != 0);   // hi*hi | hi*lo
+            if (NPLANES == 2) {
+              const uint64_t da_lo = make_smem_desc_sw128(a_lo + koff, 16, 1024);
+              umma_tf32(d, da_lo, db_hi, idesc_half, 1);             // + lo*hi
+            }
           }
+          umma_commit(&empty_bar[s]);  // slot reusable once these UMMAs have read it
         }
-        umma_commit(&empty_bar[s]);  // slot reusable once these UMMAs have read it
+        if (ok) umma_commit(&acc_full[buf]);
       }
-      if (ok) umma_commit(accum_bar);
     }
   } else {
     // ---------------- epilogue: warp w owns TMEM lanes [32*(w%4), +32)
     const int q = warp & 3;
-    const bool ok = mbar_wait(accum_bar, 0);
-    if (!ok && lane == 0) atomicExch(err_flag, kErrEpilogueWait);
-    if (ok) {
+    const int row = q * 32 + lane;   // row inside the tile
+    uint32_t local = 0;
+    for (long t = blockIdx.x; t < tmap.total; t += gridDim.x, ++local) {
+      int tile_m, tile_n, z;
+      tmap.decode(t, &tile_m, &tile_n, &z);
+      const int batch = z / sp.splits, split = z - batch * sp.splits;
+      const int n0 = tile_n * BN;
+      const uint32_t buf = local & 1u, use = local >> 1;
+      if (!mbar_wait(&acc_full[buf], use & 1u)) {
+        if (lane == 0) atomicExch(err_flag, kErrEpilogueWait);
+        break;
+      }
       tc_fence_after_sync();
-      const int row = q * 32 + lane;   // row inside the tile
+      const uint32_t acc = tmem_base + buf * (uint32_t)L::kAccCols + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < (BN + 31) / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
+        tmem_ld_32x32(acc + (uint32_t)(c * 32), r);
+        if (NPLANES == 2) {
+          uint32_t r2[32];
+          tmem_ld_32x32(acc + (uint32_t)(BN + c * 32), r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+        } else {
+          tmem_ld_wait();
+        }
+        if (c == (BN + 31) / 32 - 1) {
+          // Everything this warp needs is in registers: hand the accumulator back.
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
         if (sp.splits > 1) {
           float* dst = sp.partial + (((size_t)split * sp.batches + batch) * sp.rows_total + (size_t)tile_m * BM + row) * sp.n_total;
 #pragma unroll
@@ -235,7 +298,6 @@ int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, con
   const int tiles_n = (n_total + BN - 1) / BN;
   SplitInfo sp{};
   plan_split(ctx, (long)tiles_m * tiles_n * batches, kb_total, NPLANES == 2, &sp.splits, &sp.kb_per_split);
-  if ((long)batches * sp.splits > 65535) return NRS_ERR_UNSUPPORTED;
   sp.kb_total = kb_total;
   sp.batches = batches;
   sp.n_total = n_total;
@@ -250,8 +312,9 @@ int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, con
   int* err = nullptr;
   int st = nrs_err_flag(ctx, &err);
   if (st != NRS_OK) return st;
-  dim3 grid((unsigned)tiles_m, (unsigned)tiles_n, (unsigned)(batches * sp.splits));
-  tc_kernel<BN, NPLANES, Policy><<<grid, kThreads, L::kBytes, ctx->stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, pol, sp, err);
+  TileMap tmap{tiles_m, tiles_n, (long)tiles_m * tiles_n * batches * sp.splits};
+  const unsigned grid = (unsigned)(tmap.total < ctx->sm_count ? tmap.total : ctx->sm_count);
+  tc_kernel<BN, NPLANES, Policy><<<grid, kThreads, L::kBytes, ctx->stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, pol, sp, tmap, err);
   NRS_LAUNCHED(ctx);
   if (sp.splits > 1) {
     const size_t per = (size_t)batches * sp.rows_total * n_total;
