@@ -5,7 +5,8 @@
 //   forward        one thread per output pixel holds the K-element input patch in
 //                  registers and sweeps the output channels against weights kept
 //                  in shared memory (128-bit broadcast loads); stores are full
-//                  128-byte lines per channel
+//                  128-byte lines per channel; on request the result is also
+//                  written as NHWC TF32 planes for the tensor-core layer behind it
 //   weight grad    dW[co][k] = sum_p dy[p][co] * patch[p][k]: blocks stream pixel
 //                  tiles through shared memory, each thread accumulates a 3 x 8
 //                  (k x co) register tile; per-block partials are summed in a
@@ -14,35 +15,48 @@
 // im2col + matmul_nt_splitk (src/cuda/nn/conv.rs:244-320).
 #include "igemm_problems.cuh"
 #include "nrs_internal.h"
+#include "tc_common.cuh"
 
 namespace {
 
-template <int CI, int KS>
+constexpr int kTileLd = 36;   // floats per pixel row of the plane-emission tile (16-byte aligned, spreads banks)
+
+// EMIT: also write the result as NHWC TF32 planes (hi, and lo when non-null) for a tensor-core
+// convolution that reads it next.  Each warp (32 consecutive pixels) passes 32 channels at a
+// time through a shared-memory tile so that every plane store covers four full 128-byte lines.
+template <int CI, int KS, bool EMIT>
 __global__ void __launch_bounds__(256)
 smallc_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
-                  float* __restrict__ y, int n, int h, int wd, int co, int pad, int oh, int ow, int act) {
+                  float* __restrict__ y, int n, int h, int wd, int co, int pad, int oh, int ow, int act,
+                  float* __restrict__ hi, float* __restrict__ lo) {
   constexpr int K = CI * KS * KS;
   constexpr int K4 = (K + 3) / 4 * 4;
   extern __shared__ __align__(16) float smem_f[];
   float* w_s = smem_f;               // [co][K4]
   float* b_s = smem_f + (size_t)co * K4;
+  // [warp][32 pixels][kTileLd], 16-byte aligned behind the bias
+  float* tile = smem_f + (((size_t)co * K4 + co + 3) / 4 * 4) + (size_t)(threadIdx.x >> 5) * 32 * kTileLd;
   for (int i = threadIdx.x; i < co * K4; i += blockDim.x) {
     const int c = i / K4, k = i - c * K4;
     w_s[i] = k < K ? w[(size_t)c * K + k] : 0.0f;
   }
   for (int i = threadIdx.x; i < co; i += blockDim.x) b_s[i] = b ? b[i] : 0.0f;
   __syncthreads();
+  const int lane = threadIdx.x & 31;
   const size_t plane = (size_t)oh * ow;
   const size_t total = (size_t)n * plane;
-  for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < total; p += (size_t)gridDim.x * blockDim.x) {
-    const size_t img = p / plane;
-    const int pix = (int)(p - img * plane);
+  // warp-uniform trip count: `base` is the warp's first pixel
+  for (size_t base = (size_t)blockIdx.x * blockDim.x + (threadIdx.x - lane); base < total; base += (size_t)gridDim.x * blockDim.x) {
+    const size_t p = base + lane;
+    const bool live = p < total;
+    const size_t img = live ? p / plane : 0;
+    const int pix = live ? (int)(p - img * plane) : 0;
     const int oy = pix / ow, ox = pix - oy * ow;
     float patch[K4];
 #pragma unroll
     for (int k = 0; k < K4; ++k) {
       float v = 0.0f;
-      if (k < K) {
+      if (k < K && live) {
         const int c = k / (KS * KS), t = k - c * KS * KS, i = t / KS, j = t - i * KS;
         const int iy = oy + i - pad, ix = ox + j - pad;
         if ((unsigned)iy < (unsigned)h && (unsigned)ix < (unsigned)wd)
@@ -51,18 +65,39 @@ smallc_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, cons
       patch[k] = v;
     }
     float* dst = y + img * co * plane + pix;
-    for (int c = 0; c < co; ++c) {
-      float acc = b_s[c];
-      const float4* wr = reinterpret_cast<const float4*>(w_s + (size_t)c * K4);
+    for (int c0 = 0; c0 < co; c0 += 32) {
+      const int cn = min(32, co - c0);
+      for (int cc = 0; cc < cn; ++cc) {
+        const int c = c0 + cc;
+        float acc = b_s[c];
+        const float4* wr = reinterpret_cast<const float4*>(w_s + (size_t)c * K4);
 #pragma unroll
-      for (int k4 = 0; k4 < K4 / 4; ++k4) {
-        const float4 wv = wr[k4];
-        acc = fmaf(patch[4 * k4 + 0], wv.x, acc);
-        acc = fmaf(patch[4 * k4 + 1], wv.y, acc);
-        acc = fmaf(patch[4 * k4 + 2], wv.z, acc);
-        acc = fmaf(patch[4 * k4 + 3], wv.w, acc);
+        for (int k4 = 0; k4 < K4 / 4; ++k4) {
+          const float4 wv = wr[k4];
+          acc = fmaf(patch[4 * k4 + 0], wv.x, acc);
+          acc = fmaf(patch[4 * k4 + 1], wv.y, acc);
+          acc = fmaf(patch[4 * k4 + 2], wv.z, acc);
+          acc = fmaf(patch[4 * k4 + 3], wv.w, acc);
+        }
+        acc = nrs_apply_act(acc, act);
+        if (live) dst[(size_t)c * plane] = acc;
+        if (EMIT) tile[lane * kTileLd + cc] = acc;
       }
-      dst[(size_t)c * plane] = nrs_apply_act(acc, act);
+      if (EMIT) {   // co is a multiple of 32 on this path
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int pr = i * 4 + (lane >> 3), chunk = (lane & 7) * 4;
+          const float4 v = *reinterpret_cast<const float4*>(tile + pr * kTileLd + chunk);
+          if (base + pr < total) {
+            const size_t o = (base + pr) * co + c0 + chunk;
+            const float4 hv = make_float4(tc::tf32_rn(v.x), tc::tf32_rn(v.y), tc::tf32_rn(v.z), tc::tf32_rn(v.w));
+            *reinterpret_cast<float4*>(hi + o) = hv;
+            if (lo) *reinterpret_cast<float4*>(lo + o) = make_float4(v.x - hv.x, v.y - hv.y, v.z - hv.z, v.w - hv.w);
+          }
+        }
+        __syncwarp();
+      }
     }
   }
 }
@@ -140,21 +175,22 @@ __global__ void smallc_wgrad_reduce_kernel(const float* __restrict__ partial, fl
   dw[i] = accumulate ? dw[i] + s : s;
 }
 
-template <int CI, int KS>
+template <int CI, int KS, bool EMIT>
 int run_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y, int n, int h, int wd, int co,
-            int pad, int oh, int ow, int act) {
+            int pad, int oh, int ow, int act, float* hi, float* lo) {
   constexpr int K4 = (CI * KS * KS + 3) / 4 * 4;
-  const size_t smem = ((size_t)co * K4 + co) * sizeof(float);
+  size_t smem = (((size_t)co * K4 + co + 3) / 4 * 4) * sizeof(float);
+  if (EMIT) smem += (size_t)8 * 32 * kTileLd * sizeof(float);
   static size_t attr = 0;
   if (smem > 48 * 1024 && smem > attr) {
-    NRS_CUDA(ctx, cudaFuncSetAttribute(smallc_fwd_kernel<CI, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    NRS_CUDA(ctx, cudaFuncSetAttribute(smallc_fwd_kernel<CI, KS, EMIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = smem;
   }
   const size_t total = (size_t)n * oh * ow;
   size_t blocks = (total + 255) / 256;
   const size_t cap = (size_t)ctx->sm_count * 8;
   if (blocks > cap) blocks = cap;
-  smallc_fwd_kernel<CI, KS><<<(unsigned)blocks, 256, smem, ctx->stream>>>(x, w, b, y, n, h, wd, co, pad, oh, ow, act);
+  smallc_fwd_kernel<CI, KS, EMIT><<<(unsigned)blocks, 256, smem, ctx->stream>>>(x, w, b, y, n, h, wd, co, pad, oh, ow, act, hi, lo);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -203,8 +239,20 @@ int nrs_smallc_conv_fwd(nrs_ctx* ctx, const float* x, const float* w, const floa
                         int wd, int co, int kh, int kw, int stride, int pad, int act) {
   if (!eligible(ci, kh, kw, stride, co) || getenv("NRS_DISABLE_SMALLC")) return NRS_ERR_UNSUPPORTED;
   const int oh = h + 2 * pad - 2, ow = wd + 2 * pad - 2;
-  if (ci == 1) return run_fwd<1, 3>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act);
-  return run_fwd<3, 3>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act);
+  // Planes of the result requested by the caller (a tensor-core convolution reads it next)?
+  float *hi = nullptr, *lo = nullptr;
+  auto extras = ctx->out_extras.find(y);
+  if (extras != ctx->out_extras.end() && !extras->second.relu_mask_src && extras->second.hi && co % 32 == 0) {
+    hi = extras->second.hi;
+    lo = extras->second.lo;
+    ctx->out_extras.erase(extras);   // honoured
+  }
+  if (hi) {
+    if (ci == 1) return run_fwd<1, 3, true>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act, hi, lo);
+    return run_fwd<3, 3, true>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act, hi, lo);
+  }
+  if (ci == 1) return run_fwd<1, 3, false>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act, nullptr, nullptr);
+  return run_fwd<3, 3, false>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act, nullptr, nullptr);
 }
 
 int nrs_smallc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,

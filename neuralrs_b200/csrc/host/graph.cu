@@ -483,9 +483,33 @@ static void conv_backward(Node* self, const NodeP& x, const NodeP& w, const Node
   nrs_ctx* ctx = self->ctx;
   // Each output may be in a different accumulate state, so issue them separately.
   if (x->requires_grad) {
+    // x is the output of a convolution with a folded ReLU and this is the first share of its
+    // gradient: the data-gradient kernel can apply that ReLU's mask and emit the NHWC planes the
+    // producer's own backward pass wants, instead of a separate mask-and-stage pass later.
+    Node* xr = x.get();
+    const bool fold = xr->relu_folded && !xr->view_of && !xr->grad_valid && !xr->grad_premasked && !xr->gplanes_hi &&
+                      planes_possible(ctx);
     GradTarget t = grad_target(x);
+    float *ghi = nullptr, *glo = nullptr;
+    if (fold) {
+      if (xr->wants_grad_planes) {
+        ghi = dalloc(ctx, xr->len());
+        if (ctx->math_mode == NRS_MATH_3XTF32) glo = dalloc(ctx, xr->len());
+      }
+      ctx->out_extras[t.ptr] = NrsOutExtras{xr->data, ghi, glo};
+    }
     check(ctx, nrs_conv2d_bwd(ctx, x->data, w->data, dy, t.ptr, nullptr, nullptr, n, ci, h, wd, co, kh, kw, stride,
                               pad, t.accumulate));
+    if (fold) {
+      if (ctx->out_extras.erase(t.ptr)) {   // not honoured (the kernel that ran does not fold)
+        if (ghi) nrs_free(ctx, ghi);
+        if (glo) nrs_free(ctx, glo);
+      } else {
+        xr->gplanes_hi = ghi;
+        xr->gplanes_lo = glo;
+        xr->grad_premasked = true;
+      }
+    }
   }
   if (w->requires_grad) {
     GradTarget t = grad_target(w);
@@ -499,7 +523,7 @@ static void conv_backward(Node* self, const NodeP& x, const NodeP& w, const Node
   }
 }
 
-NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size_t pad, int act) {
+NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size_t pad, int act, bool emit_planes) {
   require_gpu(x, "cuda conv2d: input");
   require_gpu(w, "cuda conv2d: weight");
   require_gpu(b, "cuda conv2d: bias");
@@ -519,8 +543,26 @@ NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, 
     float *phi = nullptr, *plo = nullptr;
     if (stage_planes(ctx, x->data, x->shape, &phi, &plo)) { x->planes_hi = phi; x->planes_lo = plo; }
   }
+  // The caller knows a tensor-core convolution consumes this output: let the kernel write the
+  // output's NHWC planes itself (otherwise the consumer stages them in a pass of its own).
+  float *ohi = nullptr, *olo = nullptr;
+  if (emit_planes && co % 32 == 0 && planes_possible(ctx)) {
+    ohi = dalloc(ctx, out->len());
+    if (ctx->math_mode == NRS_MATH_3XTF32) olo = dalloc(ctx, out->len());
+    ctx->out_extras[out->data] = NrsOutExtras{nullptr, ohi, olo};
+  }
   check(ctx, nrs_conv2d_fwd(ctx, x->data, w->data, b->data, out->data, n, ci, h, wd, co, kh, kw, (int)stride,
                             (int)pad, act));
+  if (ohi) {
+    if (ctx->out_extras.erase(out->data)) {   // not honoured
+      nrs_free(ctx, ohi);
+      if (olo) nrs_free(ctx, olo);
+    } else {
+      out->planes_hi = ohi;
+      out->planes_lo = olo;
+      ctx->plane_hints[out->data] = NrsPlanes{ohi, olo, olo ? 1 : 0};
+    }
+  }
   Node* self = out.get();
   const int s = (int)stride, p = (int)pad;
   out->relu_folded = act == NRS_ACT_RELU;
@@ -534,7 +576,8 @@ NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, 
     // Do the tensor-core data / weight gradients want NHWC planes of dy?
     const bool want_planes = s == 1 && ci % 32 == 0 && co % 32 == 0 && planes_possible(ctx);
     if (self->grad_premasked) {
-      // A max-pool above already folded the ReLU mask into this gradient (and may have left planes).
+      // The consumer (a max-pool's backward pass or a convolution's data-gradient epilogue) already
+      // folded the ReLU mask into this gradient, and may have left its planes.
       if (self->gplanes_hi && want_planes && !ctx->plane_hints.count(dy)) {
         ctx->plane_hints[dy] = NrsPlanes{self->gplanes_hi, self->gplanes_lo, self->gplanes_lo ? 1 : 0};
         staged = true;   // owned by the node, only unregistered below
@@ -567,7 +610,7 @@ NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, 
 }
 
 NodeP conv2d(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size_t pad) {
-  return conv2d_act(x, w, b, stride, pad, NRS_ACT_NONE);
+  return conv2d_act(x, w, b, stride, pad, NRS_ACT_NONE, false);
 }
 
 NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride) {
@@ -599,7 +642,8 @@ NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride) {
         phi = dalloc(ctx, xr->len());
         if (ctx->math_mode == NRS_MATH_3XTF32) plo = dalloc(ctx, xr->len());
       }
-      check(ctx, nrs_tc_stage_masked(ctx, 1, g, xr->data, (const int32_t*)am, n, c, h, w, k, t.ptr, phi, plo));
+      // self->data (the pooled maximum) is > 0 exactly where the ReLU let the winner through.
+      check(ctx, nrs_tc_stage_masked(ctx, 1, g, self->data, (const int32_t*)am, n, c, h, w, k, t.ptr, phi, plo));
       xr->gplanes_hi = phi;
       xr->gplanes_lo = plo;
       xr->grad_premasked = true;

@@ -123,7 +123,10 @@ NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps
 // x@W + b followed by an activation, and conv + bias + activation.  Backward is
 // the composition of the unfused backward passes.
 NodeP linear_act(const NodeP& x, const NodeP& w, const NodeP& b, int act);
-NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size_t pad, int act);
+// emit_planes: the caller knows a tensor-core convolution reads the result next, so the kernel
+// also writes the result's NHWC operand planes (a hint; ignored where it does not apply).
+NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size_t pad, int act,
+                 bool emit_planes = false);
 
 // ---- transformer pieces (src/cuda/nn/{embedding,positional,attention,multihead,
 //      normalization,linear,transformer_block}.rs), defined in transformer_graph.cu

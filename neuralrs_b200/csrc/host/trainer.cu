@@ -186,12 +186,17 @@ NodeP forward(nrs_trainer* t, const NodeP& x) {
     const nrs_layer_spec& l = t->layers[li];
     const bool relu_next = t->fuse && li + 1 < t->layers.size() && t->layers[li + 1].kind == NRS_LAYER_RELU;
     switch (l.kind) {
-      case NRS_LAYER_CONV:
+      case NRS_LAYER_CONV: {
+        // The layer list shows what reads this output: if it is a stride-1 convolution, its
+        // NHWC operand planes are written by this layer's kernel.
+        const size_t nx = li + (relu_next ? 2 : 1);
+        const bool conv_reads = nx < t->layers.size() && t->layers[nx].kind == NRS_LAYER_CONV && t->layers[nx].d == 1;
         h = nrs::cuda::conv2d_act(h, t->params[pi], t->params[pi + 1], (size_t)l.d, (size_t)l.e,
-                                  relu_next ? NRS_ACT_RELU : NRS_ACT_NONE);
+                                  relu_next ? NRS_ACT_RELU : NRS_ACT_NONE, conv_reads);
         pi += 2;
         if (relu_next) ++li;
         break;
+      }
       case NRS_LAYER_LINEAR:
         if (t->fuse) {
           const bool gelu_next = li + 1 < t->layers.size() && t->layers[li + 1].kind == NRS_LAYER_GELU;

@@ -41,6 +41,15 @@ struct NrsPlanes {
   int split;
 };
 
+// Extra work a convolution kernel can fold into the epilogue that writes `out` (keyed by the
+// output pointer in nrs_ctx::out_extras).  A kernel that honours the request erases the entry;
+// an entry still present after the call means the caller has to do the work itself.
+struct NrsOutExtras {
+  const float* relu_mask_src;   // NCHW tensor of out's shape: out = relu_mask_src > 0 ? out : 0 (or null)
+  float* hi;                    // NHWC TF32 planes of the (masked) result, or null
+  float* lo;                    // residual plane (3xTF32), or null
+};
+
 struct nrs_ctx {
   int device = 0;
   cudaStream_t own_stream = nullptr;
@@ -61,6 +70,7 @@ struct nrs_ctx {
   // Planes registered for a source tensor (keyed by its device pointer); the conv kernels
   // use them instead of staging again.  Whoever registers keeps both alive and unregisters.
   std::map<const void*, NrsPlanes> plane_hints;
+  std::map<const void*, NrsOutExtras> out_extras;
   // Optional per-family device timing (nrs_profile_*).
   bool profiling = false;
   std::vector<NrsProfRecord> prof_records;

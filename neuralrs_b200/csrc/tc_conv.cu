@@ -36,6 +36,11 @@ struct ConvPolicy {
   const float* bias;
   int act, accumulate;
   uint32_t slice_bytes;
+  // optional: ReLU mask taken from an NCHW tensor of the output's shape, and NHWC TF32 planes of
+  // the result for the next tensor-core kernel
+  const float* mask_src;
+  float* out_hi;
+  float* out_lo;
 
   __device__ __forceinline__ uint32_t a_slice_bytes() const { return slice_bytes; }
   __device__ __forceinline__ void load_a(void* dst, const CUtensorMap* tm, uint64_t* bar, int kb, int tile_m, int) const {
@@ -44,38 +49,79 @@ struct ConvPolicy {
     const int n0 = (tile_m / tiles_y) * Nt, y0 = (tile_m % tiles_y) * Ht;
     tc::tma_load_4d(dst, tm, bar, cb * 32, sgn * j + base_x, y0 + sgn * i + base_y, n0);
   }
-  __device__ __forceinline__ bool locate(int tile_m, int row, size_t* pix_off) const {
+  // NCHW offset of channel 0 of the pixel behind accumulator row `row`, and the pixel's linear index.
+  __device__ __forceinline__ bool locate(int tile_m, int row, size_t* nchw_off, size_t* pixel) const {
     if (row >= Wt * Ht * Nt) return false;
     const int xt = row % Wt, t = row / Wt;
     const int yt = t % Ht, nt = t / Ht;
     const int n = (tile_m / tiles_y) * Nt + nt, y = (tile_m % tiles_y) * Ht + yt;
     if (n >= n_img || y >= out_h) return false;
-    *pix_off = (size_t)n * n_ch_out * out_h * out_w + (size_t)y * out_w + xt;
+    *nchw_off = (size_t)n * n_ch_out * out_h * out_w + (size_t)y * out_w + xt;
+    *pixel = ((size_t)n * out_h + y) * out_w + xt;
     return true;
   }
   __device__ __forceinline__ void store(int tile_m, int, int row, int ch, float v) const {
-    size_t off;
-    if (ch >= n_ch_out || !locate(tile_m, row, &off)) return;
-    float* dst = out + off + (size_t)ch * out_h * out_w;
+    size_t off, pixel;
+    if (ch >= n_ch_out || !locate(tile_m, row, &off, &pixel)) return;
+    off += (size_t)ch * out_h * out_w;
     if (bias) v += bias[ch];
     v = nrs_apply_act(v, act);
-    *dst = accumulate ? *dst + v : v;
+    if (accumulate) v += out[off];
+    if (mask_src && !(mask_src[off] > 0.0f)) v = 0.0f;
+    out[off] = v;
+    if (out_hi) {
+      const float hv = tc::tf32_rn(v);
+      out_hi[pixel * n_ch_out + ch] = hv;
+      if (out_lo) out_lo[pixel * n_ch_out + ch] = v - hv;
+    }
   }
-  __device__ __forceinline__ void epilogue(int tile_m, int, int row, int nb, int ncols, const uint32_t (&r)[32]) const {
-    size_t off;
-    if (!locate(tile_m, row, &off)) return;
+  static constexpr bool kCanEmit = true;
+  // TMA-store origin (x, y, image) of tile_m's pixel box in the NHWC planes.
+  __device__ __forceinline__ void out_origin(int tile_m, int* x0, int* y0, int* n0) const {
+    *x0 = 0;
+    *y0 = (tile_m % tiles_y) * Ht;
+    *n0 = (tile_m / tiles_y) * Nt;
+  }
+  // One accumulator row, 32 consecutive channels [nb, nb+32): bias, activation, accumulate, mask,
+  // NCHW store; the finished values come back in v (zeros for rows outside the tensor) so the
+  // caller can emit them as planes.  Loads are issued in batches ahead of the stores.
+  __device__ __forceinline__ void epilogue(int tile_m, int, int row, int nb, int, const uint32_t (&r)[32], float (&v)[32]) const {
+    size_t off, pixel;
+    const bool live = nb < n_ch_out && locate(tile_m, row, &off, &pixel);   // channel counts are multiples of 32
+    if (!live) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+      return;
+    }
     const size_t plane = (size_t)out_h * out_w;
     float* dst = out + off + (size_t)nb * plane;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (j < ncols && nb + j < n_ch_out) {
-        float v = __uint_as_float(r[j]);
-        if (bias) v += bias[nb + j];
-        v = nrs_apply_act(v, act);
-        if (accumulate) v += dst[(size_t)j * plane];
-        dst[(size_t)j * plane] = v;
-      }
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (bias) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += __ldg(bias + nb + j);
     }
+    if (act != NRS_ACT_NONE) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = nrs_apply_act(v[j], act);
+    }
+    if (accumulate) {
+      float o[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o[j] = dst[(size_t)j * plane];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += o[j];
+    }
+    if (mask_src) {
+      const float* m = mask_src + off + (size_t)nb * plane;
+      float mv[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) mv[j] = __ldg(m + (size_t)j * plane);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = mv[j] > 0.0f ? v[j] : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dst[(size_t)j * plane] = v[j];
   }
 };
 
@@ -109,9 +155,17 @@ int run_conv(nrs_ctx* ctx, const ConvPlan& p, const float* a_hi, const float* a_
   bool ok = tc::encode_tmap_f32(&ta_hi, a_hi, 4, adim, astr, abox) && tc::encode_tmap_f32(&tb_hi, w_hi, 3, bdim, bstr, bbox);
   if (NPLANES == 2) ok = ok && tc::encode_tmap_f32(&ta_lo, a_lo, 4, adim, astr, abox) && tc::encode_tmap_f32(&tb_lo, w_lo, 3, bdim, bstr, bbox);
   else { ta_lo = ta_hi; tb_lo = tb_hi; }
+  // Output planes (optional): the same box geometry as an activation load, in output space.
+  CUtensorMap to_hi, to_lo;
+  if (pol.out_hi) {
+    const uint64_t odim[4] = {(uint64_t)p.n_ch_out, (uint64_t)p.out_w, (uint64_t)p.out_h, (uint64_t)p.n_img};
+    const uint64_t ostr[3] = {(uint64_t)p.n_ch_out * 4, (uint64_t)p.out_w * p.n_ch_out * 4, (uint64_t)p.out_h * p.out_w * p.n_ch_out * 4};
+    ok = ok && tc::encode_tmap_f32(&to_hi, pol.out_hi, 4, odim, ostr, abox);
+    if (pol.out_lo) ok = ok && tc::encode_tmap_f32(&to_lo, pol.out_lo, 4, odim, ostr, abox);
+  }
   NRS_REQUIRE(ctx, ok, NRS_ERR_CUDA, "tc_conv: cuTensorMapEncodeTiled failed");
   return tc::launch<BN, NPLANES, ConvPolicy>(ctx, ta_hi, ta_lo, tb_hi, tb_lo, pol, tiles_m, p.n_ch_out, 1, taps * (p.a_ch / 32),
-                                             "tc_conv");
+                                             pol.out_hi ? &to_hi : nullptr, pol.out_lo ? &to_lo : nullptr);
 }
 
 int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
@@ -141,6 +195,13 @@ int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
   pol.sgn = p.sgn; pol.base_y = p.base; pol.base_x = p.base;
   pol.out = p.out; pol.bias = p.bias; pol.act = p.act; pol.accumulate = p.accumulate;
   pol.slice_bytes = (uint32_t)(pol.Wt * pol.Ht * pol.Nt) * 128u;
+  auto extras = ctx->out_extras.find(p.out);
+  if (extras != ctx->out_extras.end()) {
+    const NrsOutExtras& e = extras->second;
+    if (e.relu_mask_src && p.accumulate) return NRS_ERR_UNSUPPORTED;   // the mask would hit the old content too
+    if (e.lo && !split) return NRS_ERR_UNSUPPORTED;
+    pol.mask_src = e.relu_mask_src; pol.out_hi = e.hi; pol.out_lo = e.lo;
+  }
 
   // stage the activation: per image [C][H*W] -> [H*W][C] planes
   const size_t a_plane = (size_t)p.n_img * p.a_h * p.a_w * p.a_ch;
@@ -166,6 +227,7 @@ int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
   if (st != NRS_OK) return st;
 
   const int bn = p.n_ch_out % 128 == 0 ? 128 : (p.n_ch_out % 64 == 0 ? 64 : 32);
+  if (extras != ctx->out_extras.end()) ctx->out_extras.erase(extras);   // honoured from here on
 #define NRS_RUN(BN_)                                                                                                     \
   return split ? run_conv<BN_, 2>(ctx, p, (const float*)a_hi, (const float*)a_lo, (const float*)w_hi, (const float*)w_lo, pol, (int)tiles_m) \
                : run_conv<BN_, 1>(ctx, p, (const float*)a_hi, nullptr, (const float*)w_hi, nullptr, pol, (int)tiles_m)

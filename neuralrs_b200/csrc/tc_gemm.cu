@@ -23,6 +23,7 @@ struct GemmPolicy {
   int M, N;
   size_t batch_stride;
   bool vec_ok;
+  static constexpr bool kCanEmit = false;
 
   __device__ __forceinline__ uint32_t a_slice_bytes() const { return tc::BM * tc::BK * 4; }
   __device__ __forceinline__ void load_a(void* dst, const CUtensorMap* tm, uint64_t* bar, int kb, int tile_m, int batch) const {
@@ -122,7 +123,7 @@ int run(nrs_ctx* ctx, const Operand& A, const Operand& B, int batch, int m, int 
   else { ta_lo = ta_hi; tb_lo = tb_hi; }
   NRS_REQUIRE(ctx, ok, NRS_ERR_CUDA, "tc_gemm: cuTensorMapEncodeTiled failed (m=%d n=%d k=%d)", m, n, k);
   return tc::launch<BN, NPLANES, GemmPolicy>(ctx, ta_hi, ta_lo, tb_hi, tb_lo, pol, (m + tc::BM - 1) / tc::BM, n, batch,
-                                             (k + tc::BK - 1) / tc::BK, "tc_gemm");
+                                             (k + tc::BK - 1) / tc::BK);
 }
 
 }  // namespace

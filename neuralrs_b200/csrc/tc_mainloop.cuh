@@ -14,6 +14,11 @@
 // tile i+1.
 // A Policy supplies how an A slice is fetched (dense rows for GEMM, a shifted
 // NHWC window for convolution) and what the epilogue does with a row of results.
+// A policy with kCanEmit may also hand the finished values back: the epilogue warps then
+// write them as TF32 high / residual planes ([row][32 columns], 128-byte swizzle) into a
+// staging tile and one thread sends each tile to global memory with a TMA store — the
+// operand planes of the next tensor-core kernel, written in full lines without a pass of
+// their own.
 //
 // 3xTF32 (NPLANES == 2): the residual plane of B sits directly behind its high plane in
 // the ring slot, so one UMMA of width 2*BN computes A_hi.[B_hi ; B_lo] (hi*hi in columns
@@ -41,13 +46,15 @@ constexpr int kThreads = 192;
 constexpr int kMaxChainK = 4096;   // longest single accumulation chain in 3xTF32 mode
 constexpr int kGroupM = 16;        // row tiles per raster group (see TileMap)
 
-template <int BN, int NPLANES>
+template <int BN, int NPLANES, int EMIT_BYTES = 0>
 struct SmemLayout {
   static constexpr int kATile = BM * BK * 4;   // 16 KB
   static constexpr int kBTile = BN * BK * 4;
   static constexpr int kStage = NPLANES * (kATile + kBTile);   // [A_hi][B_hi][B_lo][A_lo]
-  static constexpr int kStages = (200 * 1024) / kStage >= 8 ? 8 : (200 * 1024) / kStage;
-  static constexpr int kBytes = kStages * kStage + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kExtra = EMIT_BYTES /*plane staging tile*/ + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kRing = 227 * 1024 - kExtra;
+  static constexpr int kStages = kRing / kStage >= 8 ? 8 : kRing / kStage;
+  static constexpr int kBytes = kStages * kStage + kExtra;
   static constexpr int kAccCols = NPLANES * BN;                 // one accumulator
   static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;   // two of them
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM allocation must be a power of two <= 512");
@@ -82,19 +89,28 @@ struct TileMap {
   }
 };
 
+// Shared memory of the plane-emission staging tile: one [128 rows][128 B] tile per plane.
+template <int NPLANES, class Policy>
+__host__ __device__ constexpr int emit_bytes() { return Policy::kCanEmit ? NPLANES * BM * 128 : 0; }
+
 template <int BN, int NPLANES, class Policy>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
           const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
-          const Policy pol, const SplitInfo sp, const TileMap tmap, int* __restrict__ err_flag) {
-  using L = SmemLayout<BN, NPLANES>;
+          const __grid_constant__ CUtensorMap tm_out_hi, const __grid_constant__ CUtensorMap tm_out_lo,
+          const Policy pol, const SplitInfo sp, const TileMap tmap, const int emit /*planes to emit: 0, 1 or 2*/,
+          int* __restrict__ err_flag) {
+  constexpr int kEmitBytes = emit_bytes<NPLANES, Policy>();
+  using L = SmemLayout<BN, NPLANES, kEmitBytes>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStage);
+  uint8_t* emit_tile = smem + L::kStages * L::kStage;   // [planes][128 rows][128 B], 1024-byte aligned
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(emit_tile + kEmitBytes);
   uint64_t* empty_bar = full_bar + L::kStages;
   uint64_t* acc_full = empty_bar + L::kStages;   // [2] accumulator ready for the epilogue
   uint64_t* acc_empty = acc_full + 2;            // [2] accumulator drained by the epilogue
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* emit_bar = acc_empty + 2;            // [2] staging tile free / staging tile written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(emit_bar + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -102,8 +118,10 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
     prefetch_tmap(&tm_a_hi);
     prefetch_tmap(&tm_b_hi);
     if (NPLANES == 2) { prefetch_tmap(&tm_a_lo); prefetch_tmap(&tm_b_lo); }
+    if (emit >= 1) prefetch_tmap(&tm_out_hi);
+    if (emit == 2) prefetch_tmap(&tm_out_lo);
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); mbar_init(&emit_bar[b], 128); }
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -196,8 +214,10 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
     // ---------------- epilogue: warp w owns TMEM lanes [32*(w%4), +32)
     const int q = warp & 3;
     const int row = q * 32 + lane;   // row inside the tile
-    uint32_t local = 0;
-    for (long t = blockIdx.x; t < tmap.total; t += gridDim.x, ++local) {
+    const bool emit_issuer = warp == 2 && lane == 0;
+    uint32_t local = 0, emitted = 0;
+    bool ok = true;
+    for (long t = blockIdx.x; t < tmap.total && ok; t += gridDim.x, ++local) {
       int tile_m, tile_n, z;
       tmap.decode(t, &tile_m, &tile_n, &z);
       const int batch = z / sp.splits, split = z - batch * sp.splits;
@@ -228,6 +248,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
+        const int ncols = (BN - c * 32) < 32 ? (BN - c * 32) : 32;
         if (sp.splits > 1) {
           float* dst = sp.partial + (((size_t)split * sp.batches + batch) * sp.rows_total + (size_t)tile_m * BM + row) * sp.n_total;
 #pragma unroll
@@ -235,11 +256,44 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
             const int n = n0 + c * 32 + j;
             if (c * 32 + j < BN && n < sp.n_total) dst[n] = __uint_as_float(r[j]);
           }
+        } else if constexpr (Policy::kCanEmit) {
+          float v[32];
+          pol.epilogue(tile_m, batch, row, n0 + c * 32, ncols, r, v);
+          if (emit) {
+            // The staging tile is free once the previous TMA store has read it; the issuer
+            // arrives on emit_bar[0] only after that.
+            const uint32_t ph = emitted & 1u;
+            ++emitted;
+            if (emit_issuer) bulk_wait_read();
+            mbar_arrive(&emit_bar[0]);
+            if (!mbar_wait(&emit_bar[0], ph)) { atomicExch(err_flag, kErrEpilogueWait); ok = false; break; }
+            uint8_t* row_hi = emit_tile + row * 128;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const int chunk = (g ^ (row & 7)) * 16;   // 128-byte swizzle: 16-byte chunk index XOR row % 8
+              const float4 h = make_float4(tf32_rn(v[4 * g]), tf32_rn(v[4 * g + 1]), tf32_rn(v[4 * g + 2]), tf32_rn(v[4 * g + 3]));
+              *reinterpret_cast<float4*>(row_hi + chunk) = h;
+              if (NPLANES == 2 && emit == 2)
+                *reinterpret_cast<float4*>(row_hi + BM * 128 + chunk) =
+                    make_float4(v[4 * g] - h.x, v[4 * g + 1] - h.y, v[4 * g + 2] - h.z, v[4 * g + 3] - h.w);
+            }
+            fence_proxy_async();   // generic-proxy writes -> visible to the TMA engine
+            mbar_arrive(&emit_bar[1]);
+            if (emit_issuer) {
+              if (!mbar_wait(&emit_bar[1], ph)) { atomicExch(err_flag, kErrEpilogueWait); ok = false; break; }
+              int c1, c2, c3;
+              pol.out_origin(tile_m, &c1, &c2, &c3);
+              tma_store_4d(&tm_out_hi, emit_tile, n0 + c * 32, c1, c2, c3);
+              if (NPLANES == 2 && emit == 2) tma_store_4d(&tm_out_lo, emit_tile + BM * 128, n0 + c * 32, c1, c2, c3);
+              bulk_commit();
+            }
+          }
         } else {
-          pol.epilogue(tile_m, batch, row, n0 + c * 32, (BN - c * 32) < 32 ? (BN - c * 32) : 32, r);
+          pol.epilogue(tile_m, batch, row, n0 + c * 32, ncols, r);
         }
       }
     }
+    if (emit_issuer) bulk_wait_all();   // shared memory must outlive the stores that read it
   }
 
   tc_fence_before_sync();
@@ -288,11 +342,13 @@ inline void plan_split(const nrs_ctx* ctx, long tiles, int kb_total, bool limit_
 template <int BN, int NPLANES, class Policy>
 int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, const CUtensorMap& tb_hi,
            const CUtensorMap& tb_lo, const Policy& pol, int tiles_m, int n_total, int batches, int kb_total,
-           const char* who) {
-  using L = SmemLayout<BN, NPLANES>;
+           const CUtensorMap* out_hi = nullptr, const CUtensorMap* out_lo = nullptr) {
+  using L = SmemLayout<BN, NPLANES, emit_bytes<NPLANES, Policy>()>;
+  constexpr int kSmem = L::kBytes;
+  static_assert(kSmem <= 227 * 1024 && L::kStages >= 2, "shared memory budget");
   static bool attr_set = false;
   if (!attr_set) {
-    NRS_CUDA(ctx, cudaFuncSetAttribute(tc_kernel<BN, NPLANES, Policy>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    NRS_CUDA(ctx, cudaFuncSetAttribute(tc_kernel<BN, NPLANES, Policy>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
     attr_set = true;
   }
   const int tiles_n = (n_total + BN - 1) / BN;
@@ -314,14 +370,16 @@ int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, con
   if (st != NRS_OK) return st;
   TileMap tmap{tiles_m, tiles_n, (long)tiles_m * tiles_n * batches * sp.splits};
   const unsigned grid = (unsigned)(tmap.total < ctx->sm_count ? tmap.total : ctx->sm_count);
-  tc_kernel<BN, NPLANES, Policy><<<grid, kThreads, L::kBytes, ctx->stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, pol, sp, tmap, err);
+  // Planes can only be emitted by the direct epilogue; with a K-split the policy's store() writes them.
+  const int emit = (Policy::kCanEmit && out_hi && sp.splits == 1) ? (out_lo && NPLANES == 2 ? 2 : 1) : 0;
+  tc_kernel<BN, NPLANES, Policy><<<grid, kThreads, kSmem, ctx->stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, out_hi ? *out_hi : ta_hi,
+                                                                         out_lo ? *out_lo : ta_hi, pol, sp, tmap, emit, err);
   NRS_LAUNCHED(ctx);
   if (sp.splits > 1) {
     const size_t per = (size_t)batches * sp.rows_total * n_total;
     tc_splitk_reduce_kernel<Policy><<<nrs_blocks(per, 256), 256, 0, ctx->stream>>>(pol, sp);
     NRS_LAUNCHED(ctx);
   }
-  (void)who;
   return NRS_OK;
 }
 
@@ -334,7 +392,8 @@ int nrs_tc_stage(nrs_ctx* ctx, const float* src, float* hi, float* lo, int rows,
                  size_t src_bstride, size_t dst_bstride, bool src_k_by_rows);
 // Masked gradient staging (see stage_masked_kernel): mode 0 = ReLU mask of dy[n,c,h,w] by y;
 // mode 1 = gradient of a k x k / stride-k max-pool (g[n,c,h/k,w/k], argmax) followed by the ReLU
-// mask by y[n,c,h,w].  nchw_out and the planes are each optional (lo only with hi).
+// mask, taken from the pooled output y[n,c,h/k,w/k].  nchw_out and the planes are each optional
+// (lo only with hi).
 int nrs_tc_stage_masked(nrs_ctx* ctx, int mode, const float* g, const float* y, const int32_t* argmax, int n, int c,
                         int h, int w, int k, float* nchw_out, float* hi, float* lo);
 // Conv weights w[co][ci][kh][kw] -> K-major planes.

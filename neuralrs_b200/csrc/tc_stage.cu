@@ -106,7 +106,9 @@ stage_conv_weight_kernel(const float* __restrict__ w, float* __restrict__ hi, fl
 
 // Gradient staging fused with the masks that precede a convolution's backward pass.
 //   MODE 0  v = (y > 0) ? dy : 0                          (ReLU folded into the conv: y is its output)
-//   MODE 1  v = (argmax[o] == idx && y > 0) ? g[o] : 0     (k x k / stride k max-pool on top of that)
+//   MODE 1  v = (argmax[o] == idx && y[o] > 0) ? g[o] : 0  (k x k / stride k max-pool on top of that;
+//           y is the POOLED output here: the window's maximum is > 0 exactly where the winner
+//           passed the ReLU, so the full-resolution activation is not read at all)
 // One pass reads the NCHW sources through 32 channel x 32 pixel tiles and writes the
 // masked gradient in NCHW (optional) and as NHWC TF32 planes (optional).
 template <bool SPLIT, int MODE>
@@ -130,7 +132,7 @@ stage_masked_kernel(const float* __restrict__ g, const float* __restrict__ y, co
         const int oy = yy / k, ox = xx / k;
         if (oy < oh && ox < ow) {
           const size_t o = (((size_t)img * c_n + c) * oh + oy) * ow + ox;
-          if ((size_t)argmax[o] == idx && y[idx] > 0.0f) v = g[o];
+          if ((size_t)argmax[o] == idx && y[o] > 0.0f) v = g[o];
         }
       }
       if (nchw_out) nchw_out[idx] = v;

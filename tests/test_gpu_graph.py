@@ -302,3 +302,91 @@ def test_pool_over_fused_relu_conv_with_second_consumer(gpu_ctx, oracle64):
         assert np.linalg.norm(gpu.read_grad(gw) - dwr.ravel()) <= 1e-4 * np.linalg.norm(dwr)
         assert np.linalg.norm(gpu.read_grad(gx) - dxr.ravel()) <= 1e-4 * np.linalg.norm(dxr)
         assert np.linalg.norm(gpu.read_grad(gb) - dbr.ravel()) <= 1e-4 * np.linalg.norm(dbr)
+
+
+def test_conv_over_fused_relu_conv_with_second_consumer(gpu_ctx, oracle64):
+    """conv+ReLU (folded) feeds a second convolution AND another consumer.  The second
+    convolution's data-gradient kernel applies the first one's ReLU mask in its epilogue and
+    leaves the gradient's operand planes; the other consumer adds an unmasked share.  Whatever
+    the visiting order, the first convolution must see the masked sum."""
+    rng = np.random.default_rng(13)
+    n, ci, h, w, c1, c2 = 2, 32, 8, 8, 64, 32
+    x = rng.normal(size=(n, ci, h, w)).astype(np.float32)
+    w1 = (rng.normal(size=(c1, ci, 3, 3)) * 0.1).astype(np.float32)
+    b1 = (rng.normal(size=c1) * 0.1).astype(np.float32)
+    w2 = (rng.normal(size=(c2, c1, 3, 3)) * 0.1).astype(np.float32)
+    b2 = (rng.normal(size=c2) * 0.1).astype(np.float32)
+    gx, gw1, gb1 = on_gpu(x, x.shape), on_gpu(w1, w1.shape), on_gpu(b1, b1.shape)
+    gw2, gb2 = on_gpu(w2, w2.shape), on_gpu(b2, b2.shape)
+    z1 = oracle64.conv2d_fwd(x, w1, b1, 1, 1)
+    y1 = oracle64.relu_fwd(z1)
+    for conv_first in (True, False):
+        y = nn.conv2d_act(gx, gw1, gb1, 1, 1, 1)
+        y2 = nn.conv2d(y, gw2, gb2, 1, 1)
+        scaled = graph.scale(y, 0.5)
+        parts = [graph.reshape(y2, [1, len(y2)]), graph.reshape(scaled, [1, len(scaled)])]
+        s2 = rng.normal(size=len(y2)).astype(np.float32)
+        ss = rng.normal(size=len(scaled)).astype(np.float32)
+        # the branch listed LAST is visited first by the reverse topological walk
+        both = graph.concat_cols(parts[::-1] if conv_first else parts)
+        seed = np.concatenate([ss, s2] if conv_first else [s2, ss])
+        params = [gx, gw1, gb1, gw2, gb2]
+        gpu.zero_grad(params)
+        gpu.set_grad(both, seed)
+        backward_graph(both)
+        dy2 = s2.reshape(n, c2, h, w)
+        dy1_from_conv, dw2r, db2r = oracle64.conv2d_bwd(y1, w2, dy2, 1, 1)
+        dy1 = dy1_from_conv + 0.5 * ss.reshape(y1.shape)
+        dxr, dw1r, db1r = oracle64.conv2d_bwd(x, w1, oracle64.relu_bwd(z1, dy1), 1, 1)
+        for got, want in ((gw2, dw2r), (gb2, db2r), (gw1, dw1r), (gb1, db1r), (gx, dxr)):
+            assert np.linalg.norm(gpu.read_grad(got) - want.ravel()) <= 1e-4 * np.linalg.norm(want)
+
+
+@pytest.mark.parametrize("chans", [[32, 64, 64, 32], [3, 32, 64, 32]])   # second: image layer on the FFMA kernels
+@pytest.mark.parametrize("n,h,w", [(3, 16, 16), (20, 32, 32)])   # split-K reduce store / direct epilogue
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32", "fp32"])
+def test_conv_relu_conv_chain_all_modes(gpu_ctx, oracle64, mode, n, h, w, chans):
+    """Three stacked conv+ReLU layers (no pooling): every inner gradient reaches its producer
+    through the data-gradient epilogue (mask folded, planes emitted) in the tensor-core modes
+    and through the separate passes in FP32 mode."""
+    from neuralrs_b200 import cuda as api
+    modes = {"3xtf32": 0, "tf32": 1, "fp32": 2}
+    tol = {"3xtf32": 1e-4, "tf32": 1e-2, "fp32": 1e-4}[mode]
+    rng = np.random.default_rng(14)
+    x = rng.normal(size=(n, chans[0], h, w)).astype(np.float32)
+    ws = [(rng.normal(size=(chans[i + 1], chans[i], 3, 3)) * np.sqrt(2.0 / (9 * chans[i]))).astype(np.float32) for i in range(3)]
+    bs = [(rng.normal(size=chans[i + 1]) * 0.1).astype(np.float32) for i in range(3)]
+    gpu_ctx.set_math_mode(modes[mode])
+    try:
+        gx = on_gpu(x, x.shape)
+        gws = [on_gpu(a, a.shape) for a in ws]
+        gbs = [on_gpu(a, a.shape) for a in bs]
+        hcur = gx
+        outs = []
+        for i in range(3):
+            hcur = nn.conv2d_act(hcur, gws[i], gbs[i], 1, 1, 1)
+            outs.append(hcur)
+        seed = rng.normal(size=len(hcur)).astype(np.float32)
+        gpu.zero_grad([gx] + gws + gbs)
+        gpu.set_grad(hcur, seed)
+        backward_graph(hcur)
+        # oracle
+        acts, zs = [x], []
+        for i in range(3):
+            z = oracle64.conv2d_fwd(acts[-1], ws[i], bs[i], 1, 1)
+            zs.append(z)
+            acts.append(oracle64.relu_fwd(z))
+        assert np.linalg.norm(gpu.to_host(hcur) - acts[-1].ravel()) <= tol * np.linalg.norm(acts[-1])
+        # A pre-activation within rounding error of zero may fall on the other side of the ReLU on
+        # the device; one flipped element moves a gradient by far more than the tolerance.  The
+        # backward pass is therefore checked with the ReLU masks the device actually used.
+        g = seed.reshape(acts[-1].shape)
+        for i in (2, 1, 0):
+            mask_src = gpu.to_host(outs[i]).reshape(zs[i].shape)
+            assert np.mean((mask_src > 0) != (zs[i] > 0)) < 1e-3
+            g, dw, db = oracle64.conv2d_bwd(acts[i], ws[i], oracle64.relu_bwd(mask_src, g), 1, 1)
+            assert np.linalg.norm(gpu.read_grad(gws[i]) - dw.ravel()) <= tol * np.linalg.norm(dw), (mode, i)
+            assert np.linalg.norm(gpu.read_grad(gbs[i]) - db.ravel()) <= tol * np.linalg.norm(db), (mode, i)
+        assert np.linalg.norm(gpu.read_grad(gx) - g.ravel()) <= tol * np.linalg.norm(g)
+    finally:
+        gpu_ctx.set_math_mode(0)
