@@ -7,7 +7,10 @@
 //                  in shared memory (128-bit broadcast loads); stores are full
 //                  128-byte lines per channel; on request the result is also
 //                  written as NHWC TF32 planes for the tensor-core layer behind it
-//   weight grad    dW[co][k] = sum_p dy[p][co] * patch[p][k]: blocks stream pixel
+//   weight grad    TF32 modes: the patches are written out as [pixels][32] operand planes
+//                  and the tensor-core weight-gradient kernel treats them as a 32-channel
+//                  1x1 layer.  FP32 mode, FFMA:
+//                  dW[co][k] = sum_p dy[p][co] * patch[p][k]: blocks stream pixel
 //                  tiles through shared memory, each thread accumulates a 3 x 8
 //                  (k x co) register tile; per-block partials are summed in a
 //                  fixed order by a second kernel (deterministic)
@@ -100,6 +103,64 @@ smallc_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, cons
       }
     }
   }
+}
+
+// Patch planes for the tensor-core weight gradient of an image layer: row p of the
+// [pixels][32] matrix holds the K = CI*KS*KS input values under output pixel p (zeros
+// beyond K and outside the image), as a TF32 high plane and, when lo != null, a residual
+// plane.  Seen as an NHWC tensor with 32 channels, the layer's weight gradient is then a
+// 1x1 convolution's: dW[co][k] = sum_p dy[p][co] * patch[p][k].
+template <int CI, int KS>
+__global__ void __launch_bounds__(256)
+smallc_patch_planes_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo, int n, int h,
+                           int wd, int pad, int oh, int ow) {
+  constexpr int K = CI * KS * KS;
+  static_assert(K <= 32, "patch must fit one 32-channel block");
+  __shared__ __align__(16) float tiles[8][32 * kTileLd];
+  float* tile = tiles[threadIdx.x >> 5];
+  const int lane = threadIdx.x & 31;
+  const size_t plane = (size_t)oh * ow;
+  const size_t total = (size_t)n * plane;
+  for (size_t base = (size_t)blockIdx.x * blockDim.x + (threadIdx.x - lane); base < total; base += (size_t)gridDim.x * blockDim.x) {
+    const size_t p = base + lane;
+    const bool live = p < total;
+    const size_t img = live ? p / plane : 0;
+    const int pix = live ? (int)(p - img * plane) : 0;
+    const int oy = pix / ow, ox = pix - oy * ow;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      float v = 0.0f;
+      if (k < K && live) {
+        const int c = k / (KS * KS), t = k - c * KS * KS, i = t / KS, j = t - i * KS;
+        const int iy = oy + i - pad, ix = ox + j - pad;
+        if ((unsigned)iy < (unsigned)h && (unsigned)ix < (unsigned)wd) v = x[((img * CI + c) * h + iy) * wd + ix];
+      }
+      tile[lane * kTileLd + k] = v;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int pr = i * 4 + (lane >> 3), chunk = (lane & 7) * 4;
+      const float4 v = *reinterpret_cast<const float4*>(tile + pr * kTileLd + chunk);
+      if (base + pr < total) {
+        const size_t o = (base + pr) * 32 + chunk;
+        const float4 hv = make_float4(tc::tf32_rn(v.x), tc::tf32_rn(v.y), tc::tf32_rn(v.z), tc::tf32_rn(v.w));
+        *reinterpret_cast<float4*>(hi + o) = hv;
+        if (lo) *reinterpret_cast<float4*>(lo + o) = make_float4(v.x - hv.x, v.y - hv.y, v.z - hv.z, v.w - hv.w);
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// dw[co][k] (+)= wide[co][k] for k < K (wide rows are 32 long).
+__global__ void __launch_bounds__(256)
+smallc_narrow_kernel(const float* __restrict__ wide, float* __restrict__ dw, int co, int K, int accumulate) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= co * K) return;
+  const int c = idx / K, k = idx - c * K;
+  const float v = wide[c * 32 + k];
+  dw[idx] = accumulate ? dw[idx] + v : v;
 }
 
 constexpr int TP = 128;   // pixels per shared-memory tile (weight gradient)
@@ -228,6 +289,42 @@ int run_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, i
   return NRS_OK;
 }
 
+// Tensor-core route (TF32 modes): patch planes, then the general weight-gradient kernel on them
+// as a 1x1 convolution over 32 "channels".
+template <int CI, int KS>
+int run_wgrad_tc(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int h, int wd, int co, int pad, int oh,
+                 int ow, int accumulate) {
+  constexpr int K = CI * KS * KS;
+  const bool split = ctx->math_mode == NRS_MATH_3XTF32;
+  const size_t pixels = (size_t)n * oh * ow;
+  void *phi = nullptr, *plo = nullptr, *wide = nullptr;
+  int st = nrs_alloc(ctx, pixels * 32 * sizeof(float), 0, &phi);
+  if (st == NRS_OK && split) st = nrs_alloc(ctx, pixels * 32 * sizeof(float), 0, &plo);
+  if (st == NRS_OK) st = nrs_alloc(ctx, (size_t)co * 32 * sizeof(float), 0, &wide);
+  if (st == NRS_OK) {
+    size_t blocks = (pixels + 255) / 256;
+    const size_t cap = (size_t)ctx->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    smallc_patch_planes_kernel<CI, KS><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (float*)phi, (float*)plo, n, h, wd, pad, oh, ow);
+    ctx->launches++;
+    if (cudaGetLastError() != cudaSuccess) st = NRS_ERR_CUDA;
+  }
+  if (st == NRS_OK) {
+    ctx->plane_hints[phi] = NrsPlanes{(float*)phi, (float*)plo, split ? 1 : 0};
+    st = nrs_tc_conv_wgrad(ctx, (const float*)phi, dy, (float*)wide, n, 32, oh, ow, co, 1, 1, 1, 0, 0);
+    ctx->plane_hints.erase(phi);
+  }
+  if (st == NRS_OK) {
+    smallc_narrow_kernel<<<nrs_blocks((size_t)co * K, 256), 256, 0, ctx->stream>>>((const float*)wide, dw, co, K, accumulate);
+    ctx->launches++;
+    if (cudaGetLastError() != cudaSuccess) st = NRS_ERR_CUDA;
+  }
+  if (phi) nrs_free(ctx, phi);
+  if (plo) nrs_free(ctx, plo);
+  if (wide) nrs_free(ctx, wide);
+  return st;
+}
+
 bool eligible(int ci, int kh, int kw, int stride, int co) {
   return stride == 1 && kh == 3 && kw == 3 && (ci == 1 || ci == 3) && co >= 8 && co % 8 == 0 && co <= 256;
 }
@@ -259,6 +356,11 @@ int nrs_smallc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* 
                           int kh, int kw, int stride, int pad, int accumulate) {
   if (!eligible(ci, kh, kw, stride, co) || co > 128 || getenv("NRS_DISABLE_SMALLC")) return NRS_ERR_UNSUPPORTED;
   const int oh = h + 2 * pad - 2, ow = wd + 2 * pad - 2;
+  if (ctx->math_mode != NRS_MATH_FP32 && co % 32 == 0 && (long)n * oh * ow >= 4096 && !getenv("NRS_DISABLE_TC")) {
+    const int st = ci == 1 ? run_wgrad_tc<1, 3>(ctx, x, dy, dw, n, h, wd, co, pad, oh, ow, accumulate)
+                           : run_wgrad_tc<3, 3>(ctx, x, dy, dw, n, h, wd, co, pad, oh, ow, accumulate);
+    if (st != NRS_ERR_UNSUPPORTED) return st;
+  }
   if (ci == 1) return run_wgrad<1, 3>(ctx, x, dy, dw, n, h, wd, co, pad, oh, ow, accumulate);
   return run_wgrad<3, 3>(ctx, x, dy, dw, n, h, wd, co, pad, oh, ow, accumulate);
 }

@@ -566,15 +566,18 @@ NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, 
   Node* self = out.get();
   const int s = (int)stride, p = (int)pad;
   out->relu_folded = act == NRS_ACT_RELU;
-  out->wants_grad_planes = act == NRS_ACT_RELU && s == 1 && ci % 32 == 0 && co % 32 == 0;
-  out->backward_fn = [self, x, w, b, n, ci, h, wd, co, kh, kw, s, p, act]() {
+  // (an image layer with 1 or 3 input channels takes dy planes too: its weight gradient runs on the
+  // tensor cores over patch planes)
+  const bool image_layer = (ci == 1 || ci == 3) && kh == 3 && kw == 3;
+  out->wants_grad_planes = act == NRS_ACT_RELU && s == 1 && (ci % 32 == 0 || image_layer) && co % 32 == 0;
+  out->backward_fn = [self, x, w, b, n, ci, h, wd, co, kh, kw, s, p, act, image_layer]() {
     nrs_ctx* ctx = self->ctx;
     const float* dy = grad_in(self);
     float* masked = nullptr;
     float *dhi = nullptr, *dlo = nullptr;
     bool staged = false;
     // Do the tensor-core data / weight gradients want NHWC planes of dy?
-    const bool want_planes = s == 1 && ci % 32 == 0 && co % 32 == 0 && planes_possible(ctx);
+    const bool want_planes = s == 1 && (ci % 32 == 0 || image_layer) && co % 32 == 0 && planes_possible(ctx);
     if (self->grad_premasked) {
       // The consumer (a max-pool's backward pass or a convolution's data-gradient epilogue) already
       // folded the ReLU mask into this gradient, and may have left its planes.

@@ -136,6 +136,9 @@ int nrs_tc_conv_dgrad(nrs_ctx* ctx, const float* w, const float* dy, float* dx, 
                       int kh, int kw, int stride, int pad, int accumulate);
 int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
                       int kh, int kw, int stride, int pad, int accumulate);
+// Row-streaming variant for 3x3 / stride 1 / pad 1 (tc_wgrad_rows.cu); tried first.
+int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
+                           int kh, int kw, int stride, int pad, int accumulate);
 // Direct FFMA kernels for 3x3 stride-1 layers over 1 or 3 input channels (conv_smallc.cu).
 int nrs_smallc_conv_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y, int n, int ci, int h,
                         int wd, int co, int kh, int kw, int stride, int pad, int act);

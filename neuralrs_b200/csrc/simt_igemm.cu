@@ -317,6 +317,8 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
     NrsProfScope prof(ctx, NRS_PROF_CONV_WGRAD, conv_flop);
     st = nrs_smallc_conv_wgrad(ctx, x, dy, dw, n, ci, h, wd, co, kh, kw, stride, pad, accumulate);
     if (st == NRS_ERR_UNSUPPORTED && ctx->math_mode != NRS_MATH_FP32)
+      st = nrs_tc_conv_wgrad_rows(ctx, x, dy, dw, n, ci, h, wd, co, kh, kw, stride, pad, accumulate);
+    if (st == NRS_ERR_UNSUPPORTED && ctx->math_mode != NRS_MATH_FP32)
       st = nrs_tc_conv_wgrad(ctx, x, dy, dw, n, ci, h, wd, co, kh, kw, stride, pad, accumulate);
     if (st != NRS_OK && st != NRS_ERR_UNSUPPORTED) return st;
     if (st == NRS_ERR_UNSUPPORTED) {

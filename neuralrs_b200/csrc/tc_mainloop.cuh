@@ -189,8 +189,9 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
         for (int i = 0; i < nkb; ++i, ++it) {
           const int s = it % L::kStages;
           const uint32_t ph = (it / L::kStages) & 1u;
+          // (No tcgen05 fence here: the mbarrier's complete_tx orders the TMA writes before the
+          // UMMAs, and a fence would make the issuing thread wait out the UMMAs in flight.)
           if (!mbar_wait(&full_bar[s], ph)) { atomicExch(err_flag, kErrMmaWait); ok = false; break; }
-          tc_fence_after_sync();
           const uint32_t a_hi = smem_u32(smem + s * L::kStage);
           const uint32_t b_hi = a_hi + L::kATile;                 // B_lo follows B_hi directly
           const uint32_t a_lo = b_hi + 2 * L::kBTile;

@@ -136,7 +136,6 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
         const int s = it % STAGES;
         const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
         if (!tc::mbar_wait(&full_bar[s], ph)) { atomicExch(err_flag, tc::kErrMmaWait); ok = false; break; }
-        tc::tc_fence_after_sync();
         const uint32_t a_hi = tc::smem_u32(smem + (size_t)s * stage_bytes);
         const uint32_t b_hi = a_hi + a_bytes;
         const uint32_t a_lo = b_hi + b_bytes;

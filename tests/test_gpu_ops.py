@@ -88,6 +88,14 @@ CONV_CASES = [
     (4, 128, 8, 8, 256, 3, 3, 1, 1),
     (2, 32, 12, 20, 48, 1, 1, 1, 0),    # 1x1
     (1, 3, 32, 32, 64, 3, 3, 1, 1),     # VGG first layer
+    # row-streaming weight gradient: two channel chunks, a ragged last m-block, one-row images,
+    # a 96-channel chunk, enough rows for several splits, and a shape it must leave to the general kernel
+    (5, 256, 8, 8, 256, 3, 3, 1, 1),
+    (3, 96, 8, 16, 160, 3, 3, 1, 1),
+    (7, 32, 1, 8, 32, 3, 3, 1, 1),
+    (40, 64, 16, 16, 64, 3, 3, 1, 1),
+    (2, 32, 6, 12, 32, 3, 3, 1, 1),
+    (2, 64, 10, 10, 64, 5, 5, 1, 2),
 ]
 
 
