@@ -206,6 +206,26 @@ def conv_microbench(ctx, stream, iters=10):
     return out
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel of a family from
+# the `ncu --set full` captures summarised under profiles/: (bytes, per-GPU batch of the capture,
+# kernel).  Traffic of these kernels is proportional to the pixel count, so it is scaled to the
+# per-GPU batch of this run.
+NCU_TRAFFIC = {
+    ("vgg_cifar", "3xtf32", "conv_wgrad"): (275.33e6 + 11.02e6, 256, "tc_wgrad_rows_kernel<2,4> (64->64 ch, 32x32)"),
+    ("vgg_cifar", "3xtf32", "conv_fwd"): (38.33e6 + 0.36e6, 256, "tc_kernel<128,2,ConvPolicy> (128->128 ch, 16x16)"),
+    ("vgg_cifar", "3xtf32", "conv_dgrad"): (38.33e6 + 0.36e6, 256, "tc_kernel<128,2,ConvPolicy> (128->128 ch, 16x16)"),
+}
+
+
+def ncu_traffic(workload, math, family, per_gpu_batch):
+    hit = NCU_TRAFFIC.get((workload, math, family))
+    if not hit:
+        return {"traffic": None}
+    nbytes, cap_batch, kernel = hit
+    return {"traffic": nbytes * per_gpu_batch / cap_batch, "traffic_unit": "bytes per launch", "traffic_kernel": kernel,
+            "traffic_source": f"ncu --set full capture at per-GPU batch {cap_batch} (profiles/), scaled by the pixel count"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -354,7 +374,8 @@ def run_ours(args):
             "gpu_launches": launches * world,
             "clocks": clk.summary(),
             "roofline": {"bound": "tensor", "kernel": fam, "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
-                         "frac": achieved / tf32_peak if tf32_peak else None, "traffic": None,
+                         "frac": achieved / tf32_peak if tf32_peak else None,
+                         **ncu_traffic(args.workload, args.math, fam, batch),
                          "peak_source": f"{peaks['source']}: sustained bf16 cuBLAS / 2 (dense TF32 runs at half the bf16 "
                                         f"rate); 3xTF32 issues 3x the algorithmic FLOP counted in `achieved`",
                          "launch_ms_avg": f["ms"] / f["calls"] if f["calls"] else None, "calls": f["calls"],
