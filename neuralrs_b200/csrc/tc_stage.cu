@@ -153,6 +153,70 @@ stage_masked_kernel(const float* __restrict__ g, const float* __restrict__ y, co
   }
 }
 
+
+// MODE 1 for 2x2 / stride-2 pooling over even-sized images, organised around the POOLED
+// elements (a quarter of the output): a block takes 32 channels x 32 consecutive pooled
+// positions (counted across images), reads g, the pooled output and argmax once, coalesced,
+// and produces the 2x2 windows: NCHW as float2 row segments, NHWC planes one full 128-byte
+// line (32 channels of a pixel) per warp store, through a shared-memory tile.
+template <bool SPLIT>
+__global__ void __launch_bounds__(256)
+pool2_bwd_planes_kernel(const float* __restrict__ g, const float* __restrict__ pooled, const int32_t* __restrict__ argmax,
+                        float* __restrict__ nchw_out, float* __restrict__ hi, float* __restrict__ lo, int n_img, int c_n,
+                        int h, int w) {
+  __shared__ float tile[32][129];   // [channel][q*32 + position], q = 2*dy + dx inside the window
+  __shared__ long long pix_base[32]; // linear index of each position's top-left pixel, -1 beyond the end
+  const int oh = h >> 1, ow = w >> 1, ohw = oh * ow, hw = h * w;
+  const long total_pos = (long)n_img * ohw;
+  const long gp0 = (long)blockIdx.x * 32;
+  const int c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  {
+    const long gp = gp0 + tx;
+    const bool live = gp < total_pos;
+    const int img = live ? (int)(gp / ohw) : 0;
+    const int po = live ? (int)(gp - (long)img * ohw) : 0;
+    const int oy = po / ow, ox = po - oy * ow;
+    if (ty == 0) pix_base[tx] = live ? (long long)img * hw + (long long)(2 * oy) * w + 2 * ox : -1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int cl = ty + 8 * i, c = c0 + cl;
+      float v0 = 0.0f, v1 = 0.0f, v2 = 0.0f, v3 = 0.0f;
+      if (live && c < c_n) {
+        const size_t chan = (size_t)img * c_n + c;
+        const size_t o = chan * ohw + po;
+        const float gv = pooled[o] > 0.0f ? g[o] : 0.0f;
+        const int local = (int)((size_t)argmax[o] - chan * hw);   // winner inside the channel plane
+        const int wy = local / w, wx = local - wy * w;
+        const int q = ((wy - 2 * oy) << 1) | (wx - 2 * ox);
+        v0 = q == 0 ? gv : 0.0f; v1 = q == 1 ? gv : 0.0f; v2 = q == 2 ? gv : 0.0f; v3 = q == 3 ? gv : 0.0f;
+        if (nchw_out) {
+          float* dst = nchw_out + chan * hw + (size_t)(2 * oy) * w + 2 * ox;
+          *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
+          *reinterpret_cast<float2*>(dst + w) = make_float2(v2, v3);
+        }
+      }
+      tile[cl][tx] = v0; tile[cl][32 + tx] = v1; tile[cl][64 + tx] = v2; tile[cl][96 + tx] = v3;
+    }
+  }
+  if (!hi) return;
+  __syncthreads();
+  // warp ty writes pixels k = ty, ty+8, ...: lane = channel
+  const int c = c0 + tx;
+  if (c >= c_n) return;
+#pragma unroll 4
+  for (int k = ty; k < 128; k += 8) {
+    const int q = k >> 5, pl = k & 31;
+    const long long base = pix_base[pl];
+    if (base < 0) continue;
+    const size_t pixel = (size_t)base + (size_t)(q >> 1) * w + (q & 1);
+    const float v = tile[tx][k];
+    const float hv = tc::tf32_rn(v);
+    hi[pixel * c_n + c] = hv;
+    if (SPLIT) lo[pixel * c_n + c] = v - hv;
+  }
+}
+
 }  // namespace
 
 int nrs_tc_stage_masked(nrs_ctx* ctx, int mode, const float* g, const float* y, const int32_t* argmax, int n, int c,
@@ -162,6 +226,13 @@ int nrs_tc_stage_masked(nrs_ctx* ctx, int mode, const float* g, const float* y, 
   dim3 grid((unsigned)((h * w + 31) / 32), (unsigned)((c + 31) / 32), (unsigned)n);
   if (grid.y > 65535 || grid.z > 65535) return NRS_ERR_UNSUPPORTED;
   const bool split = lo != nullptr;
+  if (mode == 1 && k == 2 && h % 2 == 0 && w % 2 == 0 && (long)n * (h / 2) * (w / 2) / 32 < 2147483647L) {
+    dim3 pgrid((unsigned)(((long)n * (h / 2) * (w / 2) + 31) / 32), (unsigned)((c + 31) / 32));
+    if (split) pool2_bwd_planes_kernel<true><<<pgrid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, n, c, h, w);
+    else pool2_bwd_planes_kernel<false><<<pgrid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, n, c, h, w);
+    NRS_LAUNCHED(ctx);
+    return NRS_OK;
+  }
   if (mode == 0) {
     if (split) stage_masked_kernel<true, 0><<<grid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
     else stage_masked_kernel<false, 0><<<grid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);

@@ -13,7 +13,11 @@
 // three vertical taps are separate column ranges of the TMEM accumulator
 // (128 x 3*chunk f32).  Per pixel the CTA loads 128 + chunk values instead of
 // 128 + 3*chunk, and vertical taps that fall off the image are skipped instead
-// of multiplied by zeros.
+// of multiplied by zeros.  With 64 output channels or fewer the 128 accumulator
+// rows would be half empty, so a CTA takes TWO horizontal taps: the upper rows get a
+// second copy of the dy row fetched one pixel to the right, which turns the same x
+// operand into the neighbouring tap (sum_p dy[p+1] x[p] = sum_p dy[p] x[p-1]); two
+// kinds of CTA then cover the three taps instead of three.
 //
 // Shared memory: a ring of dy rows and rings of x rows (one per plane), each with its
 // own full/empty mbarriers.  The dy row of step t is consumed at step t and goes back
@@ -42,6 +46,9 @@ struct RowParams {
   int co, ci;
   int chunk, n_chunks;            // input channels per CTA (multiple of 32, <= 128) and how many chunks
   int a_blocks;                   // 32-channel blocks of dy one box brings (min(4, co/32))
+  int pack;                       // co <= 64: accumulator rows [0,h) and [h,2h), h = 32*a_blocks, hold two
+                                  // horizontal taps (the second from a copy of the dy row shifted one pixel)
+  int jtypes;                     // CTA kinds along the horizontal taps: 3, or 2 when packed
   int m_blocks;                   // ceil(co / 128)
   int rows_total;                 // n_img * H
   int rows_per_split;
@@ -88,7 +95,8 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr uint32_t blk = (uint32_t)KS * 8u * 128u;         // one 32-channel block of one row (W = 8*KS pixels)
-  const uint32_t a_plane = (uint32_t)p.a_blocks * blk;       // dy row, one plane
+  const uint32_t a_box = (uint32_t)p.a_blocks * blk;         // one TMA box of dy
+  const uint32_t a_plane = (p.pack ? 2u : 1u) * a_box;       // dy row, one plane (packed: plain + shifted copy)
   const uint32_t a_slot = NPLANES * a_plane;
   const uint32_t x_slot = (uint32_t)(p.chunk / 32) * blk;    // x row, one plane
   const uint32_t x_ring = (uint32_t)p.SX * x_slot;
@@ -103,10 +111,14 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // blockIdx.x = (m block, horizontal tap j, channel chunk)
+  // blockIdx.x = (m block, horizontal tap kind, channel chunk).  Unpacked: kind = tap j, x shifted by
+  // j - 1.  Packed: kind 0 shifts x by 0 and holds taps j = 1 (plain dy rows) and j = 0 (dy shifted one
+  // pixel: sum_p dy[p+1] x[p] = sum_p dy[p] x[p-1]); kind 1 shifts x by +1 and holds j = 2 alone.
   const int cc = blockIdx.x % p.n_chunks;
-  const int j = (blockIdx.x / p.n_chunks) % 3;
-  const int mb = blockIdx.x / (p.n_chunks * 3);
+  const int jk = (blockIdx.x / p.n_chunks) % p.jtypes;
+  const int mb = blockIdx.x / (p.n_chunks * p.jtypes);
+  const int x_shift = p.pack ? jk : jk - 1;
+  const bool two_taps = p.pack && jk == 0;
   const int split = blockIdx.y;
   const int r0 = split * p.rows_per_split;
   const int r1 = min(p.rows_total, r0 + p.rows_per_split);
@@ -146,18 +158,22 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
         const bool has_x = xr >= 0 && xr < p.rows_total;
         if (has_x) {
           tc::mbar_expect_tx(&full_x[sx], NPLANES * x_slot);
-          tc::tma_load_5d(x_base + (size_t)sx * x_slot, &tm_x_hi, &full_x[sx], 0, j - 1, xy, xn, cc * (p.chunk / 32));
+          tc::tma_load_5d(x_base + (size_t)sx * x_slot, &tm_x_hi, &full_x[sx], 0, x_shift, xy, xn, cc * (p.chunk / 32));
           if (NPLANES == 2)
-            tc::tma_load_5d(x_base + x_ring + (size_t)sx * x_slot, &tm_x_lo, &full_x[sx], 0, j - 1, xy, xn, cc * (p.chunk / 32));
+            tc::tma_load_5d(x_base + x_ring + (size_t)sx * x_slot, &tm_x_lo, &full_x[sx], 0, x_shift, xy, xn, cc * (p.chunk / 32));
         } else {
           tc::mbar_arrive(&full_x[sx]);
         }
         if (t >= 2) {
           if (!tc::mbar_wait(&empty_a[sa], pha ^ 1u)) { atomicExch(err_flag, tc::kErrProducerWait); ok = false; ++t; break; }
-          tc::mbar_expect_tx(&full_a[sa], NPLANES * a_plane);
-          tc::tma_load_5d(a_base + (size_t)sa * a_slot, &tm_dy_hi, &full_a[sa], 0, 0, dyy, dn, mb * 4);
-          if (NPLANES == 2)
-            tc::tma_load_5d(a_base + (size_t)sa * a_slot + a_plane, &tm_dy_lo, &full_a[sa], 0, 0, dyy, dn, mb * 4);
+          tc::mbar_expect_tx(&full_a[sa], NPLANES * (two_taps ? 2u : 1u) * a_box);
+          uint8_t* a_dst = a_base + (size_t)sa * a_slot;
+          tc::tma_load_5d(a_dst, &tm_dy_hi, &full_a[sa], 0, 0, dyy, dn, mb * 4);
+          if (two_taps) tc::tma_load_5d(a_dst + a_box, &tm_dy_hi, &full_a[sa], 0, 1, dyy, dn, mb * 4);
+          if (NPLANES == 2) {
+            tc::tma_load_5d(a_dst + a_plane, &tm_dy_lo, &full_a[sa], 0, 0, dyy, dn, mb * 4);
+            if (two_taps) tc::tma_load_5d(a_dst + a_plane + a_box, &tm_dy_lo, &full_a[sa], 0, 1, dyy, dn, mb * 4);
+          }
           if (++sa == p.SA) { sa = 0; pha ^= 1u; }
           if (++dyy == p.H) { dyy = 0; ++dn; }
         }
@@ -231,7 +247,9 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
       const int row = q * 32 + lane;
       const int cols = kTaps * p.chunk;
       float* dst = p.partial + (((size_t)split * gridDim.x + blockIdx.x) * 128 + row) * cols;
-      const bool row_live = mb * 128 + row < p.co;
+      // packed: rows [0,h) are tap j = 1 or 2, rows [h,2h) tap j = 0 (kind 0 only)
+      const int half = 32 * p.a_blocks;
+      const bool row_live = p.pack ? (row < half || (two_taps && row < 2 * half)) : (mb * 128 + row < p.co);
       uint32_t valid = 0;
       for (int i = 0; i < kTaps; ++i) valid |= tap_ever_valid(i, r0, r1, p.H) ? (1u << i) : 0u;
 #pragma unroll 1
@@ -270,9 +288,14 @@ tc_wgrad_rows_reduce_kernel(const RowParams p, int splits, int ctas, float* __re
   const int i = (int)((idx / p.ci) % 3);
   const int j = (int)((idx / ((size_t)p.ci * 3)) % 3);
   const int co = (int)(idx / ((size_t)p.ci * 9));
-  const int mb = co / 128, row = co - mb * 128;
+  int mb = co / 128, row = co - mb * 128, jk = j;
+  if (p.pack) {   // tap 1 -> kind 0 rows [0,h); tap 0 -> kind 0 rows [h,2h); tap 2 -> kind 1 rows [0,h)
+    mb = 0;
+    jk = j == 2 ? 1 : 0;
+    row = co + (j == 0 ? 32 * p.a_blocks : 0);
+  }
   const int cc = ci / p.chunk, c = ci - cc * p.chunk;
-  const int cta = (mb * 3 + j) * p.n_chunks + cc;
+  const int cta = (mb * p.jtypes + jk) * p.n_chunks + cc;
   const size_t cols = (size_t)kTaps * p.chunk;
   const size_t off = ((size_t)cta * 128 + row) * cols + (size_t)i * p.chunk + c;
   const size_t split_stride = (size_t)ctas * 128 * cols;
@@ -318,13 +341,15 @@ int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float*
   p.chunk = ci % 128 == 0 ? 128 : (ci <= 128 ? ci : (ci % 96 == 0 ? 96 : (ci % 64 == 0 ? 64 : 32)));
   p.n_chunks = ci / p.chunk;
   p.a_blocks = co / 32 < 4 ? co / 32 : 4;
+  p.pack = co <= 64 ? 1 : 0;
+  p.jtypes = p.pack ? 2 : 3;
   p.m_blocks = (co + 127) / 128;
   p.rows_total = n * h;
   p.max_run = 256 / p.chunk < kTaps ? 256 / p.chunk : kTaps;
 
   // ring depths: a dy row lives one step, an x row three; d rows of prefetch on top of that
   const size_t blk = (size_t)wd * 128;
-  const size_t a_slot = (size_t)planes * p.a_blocks * blk, x_slot = (size_t)planes * (p.chunk / 32) * blk;
+  const size_t a_slot = (size_t)planes * (p.pack ? 2 : 1) * p.a_blocks * blk, x_slot = (size_t)planes * (p.chunk / 32) * blk;
   const long budget = 200 * 1024;
   long d = (budget - 3 * (long)x_slot - (long)a_slot) / (long)(x_slot + a_slot);
   if (d > 8) d = 8;
@@ -335,7 +360,7 @@ int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float*
   if (smem_bytes > 227 * 1024) return NRS_ERR_UNSUPPORTED;
 
   // row split: fill the GPU, bound the accumulation chain in 3xTF32 mode, amortise the partial tile
-  const int ctas = p.m_blocks * 3 * p.n_chunks;
+  const int ctas = p.m_blocks * p.jtypes * p.n_chunks;
   int splits = (2 * ctx->sm_count + ctas - 1) / ctas;
   int rps = (p.rows_total + splits - 1) / splits;
   const int min_rows = (512 + wd - 1) / wd;

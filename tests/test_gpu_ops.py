@@ -96,6 +96,9 @@ CONV_CASES = [
     (40, 64, 16, 16, 64, 3, 3, 1, 1),
     (2, 32, 6, 12, 32, 3, 3, 1, 1),
     (2, 64, 10, 10, 64, 5, 5, 1, 2),
+    (3, 32, 16, 16, 32, 3, 3, 1, 1),    # 32 / 64 output channels: two horizontal taps share the accumulator rows
+    (2, 64, 8, 32, 64, 3, 3, 1, 1),
+    (2, 128, 5, 64, 96, 3, 3, 1, 1),    # 64-pixel rows
 ]
 
 
