@@ -340,6 +340,30 @@ inline void plan_split(const nrs_ctx* ctx, long tiles, int kb_total, bool limit_
   *splits = (kb_total + per - 1) / per;
 }
 
+// Work units (pixel tiles, image rows) per CTA for a reduction that is split across CTAs, `ctas`
+// CTAs per split and one CTA per SM at a time.  Candidates put the CTA count just under a whole
+// number of waves (a count just over one costs a whole extra round); a CTA's fixed cost
+// (prologue, partial-tile store) is weighed in as `overhead_units`; more than max_units per CTA
+// (the accumulation-chain limit) is not allowed, fewer than min_units not worthwhile.
+inline int plan_units_per_cta(int sm_count, int ctas, long units, int min_units, int max_units, int overhead_units) {
+  if (units < 1) return 1;
+  long best_u = -1, best_cost = 0;
+  for (int w = 1; w <= 64; ++w) {
+    const long splits = (long)w * sm_count / ctas;
+    if (splits < 1) continue;
+    long u = (units + splits - 1) / splits;
+    if (u < min_units) u = min_units;
+    if (u > units) u = units;
+    if (u > max_units) continue;
+    const long actual = (units + u - 1) / u;
+    const long rounds = (actual * ctas + sm_count - 1) / sm_count;
+    const long cost = rounds * (u + overhead_units);
+    if (best_u < 0 || cost < best_cost) { best_u = u; best_cost = cost; }
+  }
+  if (best_u < 0) best_u = max_units < units ? max_units : units;
+  return (int)(best_u < 1 ? 1 : best_u);
+}
+
 template <int BN, int NPLANES, class Policy>
 int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, const CUtensorMap& tb_hi,
            const CUtensorMap& tb_lo, const Policy& pol, int tiles_m, int n_total, int batches, int kb_total,

@@ -287,14 +287,12 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
 
   // pixel split: fill the GPU, and bound the accumulation chain in 3xTF32 mode
   const int ctas_per_split = p.m_blocks * p.n_groups;
-  int splits = (2 * ctx->sm_count + ctas_per_split - 1) / ctas_per_split;
-  int tps = (p.n_tiles + splits - 1) / splits;
-  if (tps * p.kp < 512) tps = 512 / p.kp;   // amortise the prologue and the partial-tile store
-  if (split3 && tps * p.kp > tc::kMaxChainK) tps = tc::kMaxChainK / p.kp;
-  if (tps > p.n_tiles) tps = p.n_tiles;
-  if (tps < 1) tps = 1;
+  const int max_tiles = split3 ? tc::kMaxChainK / p.kp : 1 << 30;
+  int min_tiles = 512 / p.kp;   // amortise the prologue and the partial-tile store
+  if (min_tiles > max_tiles) min_tiles = max_tiles;
+  const int tps = tc::plan_units_per_cta(ctx->sm_count, ctas_per_split, p.n_tiles, min_tiles, max_tiles, 8);
   p.tiles_per_split = tps;
-  splits = (p.n_tiles + tps - 1) / tps;
+  const int splits = (p.n_tiles + tps - 1) / tps;
   if (splits > 65535) return NRS_ERR_UNSUPPORTED;
 
   // workspaces: NHWC planes of dy and x, and the partial tiles

@@ -361,15 +361,12 @@ int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float*
 
   // row split: fill the GPU, bound the accumulation chain in 3xTF32 mode, amortise the partial tile
   const int ctas = p.m_blocks * p.jtypes * p.n_chunks;
-  int splits = (2 * ctx->sm_count + ctas - 1) / ctas;
-  int rps = (p.rows_total + splits - 1) / splits;
-  const int min_rows = (512 + wd - 1) / wd;
-  if (rps < min_rows) rps = min_rows;
-  if (split3 && rps * wd > tc::kMaxChainK) rps = tc::kMaxChainK / wd;
-  if (rps > p.rows_total) rps = p.rows_total;
-  if (rps < 1) rps = 1;
+  const int max_rows = split3 ? tc::kMaxChainK / wd : 1 << 30;
+  int min_rows = (512 + wd - 1) / wd;
+  if (min_rows > max_rows) min_rows = max_rows;
+  const int rps = tc::plan_units_per_cta(ctx->sm_count, ctas, p.rows_total, min_rows, max_rows, 2 + 256 / wd);
   p.rows_per_split = rps;
-  splits = (p.rows_total + rps - 1) / rps;
+  const int splits = (p.rows_total + rps - 1) / rps;
   if (splits > 65535) return NRS_ERR_UNSUPPORTED;
 
   // workspaces: NHWC planes of dy and x (or the caller's registered planes), and the partial tiles
