@@ -40,6 +40,7 @@ Node::~Node() {
     nrs_free(ctx, gplanes_hi);
     if (gplanes_lo) nrs_free(ctx, gplanes_lo);
   }
+  if (gchan_partial) nrs_free(ctx, gchan_partial);
   if (data && owns_data) nrs_free(ctx, data);
   if (grad && owns_grad) nrs_free(ctx, grad);
   for (void* p : saved) nrs_free(ctx, p);
@@ -80,6 +81,7 @@ static GradTarget grad_target(const NodeP& n) {
     r->grad_premasked = false;
     if (r->gplanes_hi) { nrs_free(r->ctx, r->gplanes_hi); r->gplanes_hi = nullptr; }
     if (r->gplanes_lo) { nrs_free(r->ctx, r->gplanes_lo); r->gplanes_lo = nullptr; }
+    if (r->gchan_partial) { nrs_free(r->ctx, r->gchan_partial); r->gchan_partial = nullptr; r->gchan_rows = 0; }
   }
   GradTarget t{r->grad, r->grad_valid ? 1 : 0};
   r->grad_valid = true;
@@ -497,17 +499,30 @@ static void conv_backward(Node* self, const NodeP& x, const NodeP& w, const Node
         if (ctx->math_mode == NRS_MATH_3XTF32) glo = dalloc(ctx, xr->len());
       }
       ctx->out_extras[t.ptr] = NrsOutExtras{xr->data, ghi, glo};
+      // ... and per-tile channel sums of the masked gradient, for the producer's bias gradient.
+      const size_t pixels = (size_t)n * h * wd;
+      const int cap = (int)(4 * (pixels / 64 + 2));
+      ctx->colsum_requests[t.ptr] = NrsColsumRequest{dalloc(ctx, (size_t)cap * ci), cap, 0};
     }
     check(ctx, nrs_conv2d_bwd(ctx, x->data, w->data, dy, t.ptr, nullptr, nullptr, n, ci, h, wd, co, kh, kw, stride,
                               pad, t.accumulate));
     if (fold) {
+      NrsColsumRequest sums = ctx->colsum_requests[t.ptr];
+      ctx->colsum_requests.erase(t.ptr);
       if (ctx->out_extras.erase(t.ptr)) {   // not honoured (the kernel that ran does not fold)
         if (ghi) nrs_free(ctx, ghi);
         if (glo) nrs_free(ctx, glo);
+        sums.rows = 0;
       } else {
         xr->gplanes_hi = ghi;
         xr->gplanes_lo = glo;
         xr->grad_premasked = true;
+      }
+      if (sums.rows > 0) {
+        xr->gchan_partial = sums.partial;
+        xr->gchan_rows = sums.rows;
+      } else {
+        nrs_free(ctx, sums.partial);
       }
     }
   }
@@ -518,8 +533,11 @@ static void conv_backward(Node* self, const NodeP& x, const NodeP& w, const Node
   }
   if (b->requires_grad) {
     GradTarget t = grad_target(b);
-    check(ctx, nrs_conv2d_bwd(ctx, x->data, w->data, dy, nullptr, nullptr, t.ptr, n, ci, h, wd, co, kh, kw, stride,
-                              pad, t.accumulate));
+    if (self->grad_premasked && self->gchan_partial && self->gchan_rows > 0)   // the producer of dy left channel sums
+      check(ctx, nrs_sum_axis0(ctx, self->gchan_partial, t.ptr, self->gchan_rows, co, t.accumulate));
+    else
+      check(ctx, nrs_conv2d_bwd(ctx, x->data, w->data, dy, nullptr, nullptr, t.ptr, n, ci, h, wd, co, kh, kw, stride,
+                                pad, t.accumulate));
   }
 }
 
@@ -616,7 +634,7 @@ NodeP conv2d(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size
   return conv2d_act(x, w, b, stride, pad, NRS_ACT_NONE, false);
 }
 
-NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride) {
+NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride, bool emit_planes) {
   require_gpu(x, "cuda maxpool: input");
   if (x->shape.size() != 4) fail(NRS_ERR_SHAPE, "cuda maxpool: input must be 4-D");
   nrs_ctx* ctx = x->ctx;
@@ -628,7 +646,24 @@ NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride) {
   void* am = nullptr;
   check(ctx, nrs_alloc(ctx, out->len() * sizeof(int32_t), 0, &am));
   out->saved.push_back(am);
-  check(ctx, nrs_maxpool_fwd(ctx, x->data, out->data, (int32_t*)am, n, c, h, w, k, s));
+  bool done = false;
+  if (emit_planes && k == 2 && s == 2 && c % 32 == 0 && planes_possible(ctx)) {
+    // a tensor-core convolution reads the result next: write its operand planes in the same pass
+    float* phi = dalloc(ctx, out->len());
+    float* plo = ctx->math_mode == NRS_MATH_3XTF32 ? dalloc(ctx, out->len()) : nullptr;
+    const int st = nrs_tc_pool2_fwd_planes(ctx, x->data, out->data, (int32_t*)am, phi, plo, n, c, h, w);
+    if (st == NRS_OK) {
+      out->planes_hi = phi;
+      out->planes_lo = plo;
+      ctx->plane_hints[out->data] = NrsPlanes{phi, plo, plo ? 1 : 0};
+      done = true;
+    } else {
+      nrs_free(ctx, phi);
+      if (plo) nrs_free(ctx, plo);
+      if (st != NRS_ERR_UNSUPPORTED) check(ctx, st);
+    }
+  }
+  if (!done) check(ctx, nrs_maxpool_fwd(ctx, x->data, out->data, (int32_t*)am, n, c, h, w, k, s));
   Node* self = out.get();
   out->backward_fn = [self, x, am, n, c, h, w, k, s]() {
     if (!x->requires_grad) return;
@@ -646,9 +681,15 @@ NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride) {
         if (ctx->math_mode == NRS_MATH_3XTF32) plo = dalloc(ctx, xr->len());
       }
       // self->data (the pooled maximum) is > 0 exactly where the ReLU let the winner through.
-      check(ctx, nrs_tc_stage_masked(ctx, 1, g, self->data, (const int32_t*)am, n, c, h, w, k, t.ptr, phi, plo));
+      float* partial = k == 2 ? dalloc(ctx, nrs_stage_masked_partial_rows(n, h, w) * (size_t)c) : nullptr;
+      int partial_rows = 0;
+      check(ctx, nrs_tc_stage_masked(ctx, 1, g, self->data, (const int32_t*)am, n, c, h, w, k, t.ptr, phi, plo, partial,
+                                     &partial_rows));
+      if (partial && partial_rows == 0) { nrs_free(ctx, partial); partial = nullptr; }
       xr->gplanes_hi = phi;
       xr->gplanes_lo = plo;
+      xr->gchan_partial = partial;
+      xr->gchan_rows = partial_rows;
       xr->grad_premasked = true;
       return;
     }

@@ -59,6 +59,10 @@ struct Node {
   bool relu_folded = false, wants_grad_planes = false, grad_premasked = false;
   float* gplanes_hi = nullptr;
   float* gplanes_lo = nullptr;
+  // With a premasked gradient: per-block channel sums of it ([rows][channels]), which the
+  // convolution's bias gradient folds instead of summing the whole NCHW gradient again.
+  float* gchan_partial = nullptr;
+  int gchan_rows = 0;
 
   size_t len() const;
   bool on_gpu() const { return data != nullptr; }
@@ -116,7 +120,7 @@ NodeP concat_cols(const std::vector<NodeP>& parts);
 
 // ---- nn (src/cuda/nn/*.rs)
 NodeP conv2d(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size_t pad);
-NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride);
+NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride, bool emit_planes = false);   // hint as in conv2d_act
 NodeP flatten(const NodeP& x);
 NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps);
 // Fused variants with no counterpart op in the reference: one kernel for

@@ -210,7 +210,11 @@ NodeP forward(nrs_trainer* t, const NodeP& x) {
         break;
       case NRS_LAYER_RELU: h = nrs::cuda::relu(h); break;
       case NRS_LAYER_GELU: h = nrs::cuda::gelu(h); break;
-      case NRS_LAYER_MAXPOOL: h = nrs::cuda::maxpool2d(h, (size_t)l.a, (size_t)l.b); break;
+      case NRS_LAYER_MAXPOOL: {
+        const bool conv_reads = li + 1 < t->layers.size() && t->layers[li + 1].kind == NRS_LAYER_CONV && t->layers[li + 1].d == 1;
+        h = nrs::cuda::maxpool2d(h, (size_t)l.a, (size_t)l.b, conv_reads);
+        break;
+      }
       case NRS_LAYER_FLATTEN: h = nrs::cuda::flatten(h); break;
     }
   }

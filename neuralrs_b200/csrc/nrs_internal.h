@@ -50,6 +50,16 @@ struct NrsOutExtras {
   float* lo;                    // residual plane (3xTF32), or null
 };
 
+// Request for per-tile channel sums of a convolution kernel's (masked) output, keyed by the output
+// pointer in nrs_ctx::colsum_requests: the bias gradient of the layer below is then a fold of
+// [rows][channels] partial sums instead of a pass over the whole gradient.  A kernel that honours
+// it sets `rows` (> 0); the caller removes the entry either way.
+struct NrsColsumRequest {
+  float* partial;   // [cap_rows][channels]
+  int cap_rows;
+  int rows;         // out: rows written, 0 = not honoured
+};
+
 struct nrs_ctx {
   int device = 0;
   cudaStream_t own_stream = nullptr;
@@ -71,6 +81,7 @@ struct nrs_ctx {
   // use them instead of staging again.  Whoever registers keeps both alive and unregisters.
   std::map<const void*, NrsPlanes> plane_hints;
   std::map<const void*, NrsOutExtras> out_extras;
+  std::map<const void*, NrsColsumRequest> colsum_requests;
   // Optional per-family device timing (nrs_profile_*).
   bool profiling = false;
   std::vector<NrsProfRecord> prof_records;

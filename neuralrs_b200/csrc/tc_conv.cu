@@ -41,6 +41,8 @@ struct ConvPolicy {
   const float* mask_src;
   float* out_hi;
   float* out_lo;
+  // optional: [tiles_m * 4][n_ch_out] sums of the finished values over each epilogue warp's 32 rows
+  float* colsum_partial;
 
   __device__ __forceinline__ uint32_t a_slice_bytes() const { return slice_bytes; }
   __device__ __forceinline__ void load_a(void* dst, const CUtensorMap* tm, uint64_t* bar, int kb, int tile_m, int) const {
@@ -76,6 +78,9 @@ struct ConvPolicy {
     }
   }
   static constexpr bool kCanEmit = true;
+  __device__ __forceinline__ float* colsum_row(int tile_m, int q) const {
+    return colsum_partial ? colsum_partial + ((size_t)tile_m * 4 + q) * n_ch_out : nullptr;
+  }
   // TMA-store origin (x, y, image) of tile_m's pixel box in the NHWC planes.
   __device__ __forceinline__ void out_origin(int tile_m, int* x0, int* y0, int* n0) const {
     *x0 = 0;
@@ -142,7 +147,7 @@ struct ConvPlan {
 
 template <int BN, int NPLANES>
 int run_conv(nrs_ctx* ctx, const ConvPlan& p, const float* a_hi, const float* a_lo, const float* w_hi, const float* w_lo,
-             const ConvPolicy& pol, int tiles_m) {
+             const ConvPolicy& pol, int tiles_m, int* splits_out) {
   const int taps = p.kh * p.kw;
   const int kdim = taps * p.a_ch;
   CUtensorMap ta_hi, ta_lo, tb_hi, tb_lo;
@@ -165,7 +170,7 @@ int run_conv(nrs_ctx* ctx, const ConvPlan& p, const float* a_hi, const float* a_
   }
   NRS_REQUIRE(ctx, ok, NRS_ERR_CUDA, "tc_conv: cuTensorMapEncodeTiled failed");
   return tc::launch<BN, NPLANES, ConvPolicy>(ctx, ta_hi, ta_lo, tb_hi, tb_lo, pol, tiles_m, p.n_ch_out, 1, taps * (p.a_ch / 32),
-                                             pol.out_hi ? &to_hi : nullptr, pol.out_lo ? &to_lo : nullptr);
+                                             pol.out_hi ? &to_hi : nullptr, pol.out_lo ? &to_lo : nullptr, splits_out);
 }
 
 int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
@@ -202,6 +207,9 @@ int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
     if (e.lo && !split) return NRS_ERR_UNSUPPORTED;
     pol.mask_src = e.relu_mask_src; pol.out_hi = e.hi; pol.out_lo = e.lo;
   }
+  auto colsum = ctx->colsum_requests.find(p.out);
+  if (colsum != ctx->colsum_requests.end() && !p.accumulate && tiles_m * 4 <= colsum->second.cap_rows)
+    pol.colsum_partial = colsum->second.partial;
 
   // stage the activation: per image [C][H*W] -> [H*W][C] planes
   const size_t a_plane = (size_t)p.n_img * p.a_h * p.a_w * p.a_ch;
@@ -228,13 +236,17 @@ int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
 
   const int bn = p.n_ch_out % 128 == 0 ? 128 : (p.n_ch_out % 64 == 0 ? 64 : 32);
   if (extras != ctx->out_extras.end()) ctx->out_extras.erase(extras);   // honoured from here on
+  int splits = 0;
 #define NRS_RUN(BN_)                                                                                                     \
-  return split ? run_conv<BN_, 2>(ctx, p, (const float*)a_hi, (const float*)a_lo, (const float*)w_hi, (const float*)w_lo, pol, (int)tiles_m) \
-               : run_conv<BN_, 1>(ctx, p, (const float*)a_hi, nullptr, (const float*)w_hi, nullptr, pol, (int)tiles_m)
+  st = split ? run_conv<BN_, 2>(ctx, p, (const float*)a_hi, (const float*)a_lo, (const float*)w_hi, (const float*)w_lo, pol, (int)tiles_m, &splits) \
+             : run_conv<BN_, 1>(ctx, p, (const float*)a_hi, nullptr, (const float*)w_hi, nullptr, pol, (int)tiles_m, &splits)
   if (bn == 128) { NRS_RUN(128); }
-  if (bn == 64) { NRS_RUN(64); }
-  NRS_RUN(32);
+  else if (bn == 64) { NRS_RUN(64); }
+  else { NRS_RUN(32); }
 #undef NRS_RUN
+  // channel sums come from the direct epilogue only (a K-split stores through the reduce kernel)
+  if (st == NRS_OK && pol.colsum_partial && splits == 1) colsum->second.rows = (int)tiles_m * 4;
+  return st;
 }
 
 }  // namespace

@@ -260,6 +260,24 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
         } else if constexpr (Policy::kCanEmit) {
           float v[32];
           pol.epilogue(tile_m, batch, row, n0 + c * 32, ncols, r, v);
+          if (float* cs = pol.colsum_row(tile_m, q)) {
+            // Sum over this warp's 32 rows, one channel per lane: a 32 x 32 transpose-reduce in 31
+            // shuffles (each stage halves the values a lane holds; fixed order, deterministic).
+            float s[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) s[j] = v[j];
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) {
+              const bool up = (lane & d) != 0;
+#pragma unroll
+              for (int i = 0; i < d; ++i) {
+                const float keep = up ? s[i + d] : s[i];
+                const float send = up ? s[i] : s[i + d];
+                s[i] = keep + __shfl_xor_sync(0xffffffffu, send, d);
+              }
+            }
+            cs[n0 + c * 32 + lane] = s[0];
+          }
           if (emit) {
             // The staging tile is free once the previous TMA store has read it; the issuer
             // arrives on emit_bar[0] only after that.
@@ -367,7 +385,7 @@ inline int plan_units_per_cta(int sm_count, int ctas, long units, int min_units,
 template <int BN, int NPLANES, class Policy>
 int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, const CUtensorMap& tb_hi,
            const CUtensorMap& tb_lo, const Policy& pol, int tiles_m, int n_total, int batches, int kb_total,
-           const CUtensorMap* out_hi = nullptr, const CUtensorMap* out_lo = nullptr) {
+           const CUtensorMap* out_hi = nullptr, const CUtensorMap* out_lo = nullptr, int* splits_out = nullptr) {
   using L = SmemLayout<BN, NPLANES, emit_bytes<NPLANES, Policy>()>;
   constexpr int kSmem = L::kBytes;
   static_assert(kSmem <= 227 * 1024 && L::kStages >= 2, "shared memory budget");
@@ -384,6 +402,7 @@ int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, con
   sp.n_total = n_total;
   sp.rows_total = tiles_m * BM;
   sp.partial = nullptr;
+  if (splits_out) *splits_out = sp.splits;
   if (sp.splits > 1) {
     void* ws = nullptr;
     const int st = nrs_ws_slot(ctx, NRS_WS_PARTIAL, (size_t)sp.splits * batches * sp.rows_total * n_total * sizeof(float), &ws);
@@ -418,9 +437,17 @@ int nrs_tc_stage(nrs_ctx* ctx, const float* src, float* hi, float* lo, int rows,
 // Masked gradient staging (see stage_masked_kernel): mode 0 = ReLU mask of dy[n,c,h,w] by y;
 // mode 1 = gradient of a k x k / stride-k max-pool (g[n,c,h/k,w/k], argmax) followed by the ReLU
 // mask, taken from the pooled output y[n,c,h/k,w/k].  nchw_out and the planes are each optional
-// (lo only with hi).
+// (lo only with hi).  chan_partial (optional, nrs_stage_masked_partial_rows(...) x c floats): per-block
+// channel sums of the result, for the bias gradient; *chan_partial_rows receives how many rows
+// were written (0: this path does not produce them and the caller sums the NCHW gradient).
 int nrs_tc_stage_masked(nrs_ctx* ctx, int mode, const float* g, const float* y, const int32_t* argmax, int n, int c,
-                        int h, int w, int k, float* nchw_out, float* hi, float* lo);
+                        int h, int w, int k, float* nchw_out, float* hi, float* lo, float* chan_partial = nullptr,
+                        int* chan_partial_rows = nullptr);
+// 2x2 / stride-2 max-pool forward that also writes the NHWC planes of the pooled output
+// (NRS_ERR_UNSUPPORTED for odd image sizes).
+int nrs_tc_pool2_fwd_planes(nrs_ctx* ctx, const float* x, float* y, int32_t* argmax, float* hi, float* lo, int n, int c,
+                            int h, int w);
+inline size_t nrs_stage_masked_partial_rows(int n, int h, int w) { return ((size_t)n * (h / 2) * (w / 2) + 31) / 32; }
 // Conv weights w[co][ci][kh][kw] -> K-major planes.
 //  for_dgrad == 0: out[co][(i*kw + j)*ci_n + ci]   (forward B operand)
 //  for_dgrad == 1: out[ci][(i*kw + j)*co_n + co]   (data-gradient B operand)

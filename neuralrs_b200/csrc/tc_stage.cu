@@ -162,8 +162,9 @@ stage_masked_kernel(const float* __restrict__ g, const float* __restrict__ y, co
 template <bool SPLIT>
 __global__ void __launch_bounds__(256)
 pool2_bwd_planes_kernel(const float* __restrict__ g, const float* __restrict__ pooled, const int32_t* __restrict__ argmax,
-                        float* __restrict__ nchw_out, float* __restrict__ hi, float* __restrict__ lo, int n_img, int c_n,
-                        int h, int w) {
+                        float* __restrict__ nchw_out, float* __restrict__ hi, float* __restrict__ lo,
+                        float* __restrict__ chan_partial /*[gridDim.x][c_n] per-block channel sums, or null*/, int n_img,
+                        int c_n, int h, int w) {
   __shared__ float tile[32][129];   // [channel][q*32 + position], q = 2*dy + dx inside the window
   __shared__ long long pix_base[32]; // linear index of each position's top-left pixel, -1 beyond the end
   const int oh = h >> 1, ow = w >> 1, ohw = oh * ow, hw = h * w;
@@ -181,11 +182,11 @@ pool2_bwd_planes_kernel(const float* __restrict__ g, const float* __restrict__ p
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int cl = ty + 8 * i, c = c0 + cl;
-      float v0 = 0.0f, v1 = 0.0f, v2 = 0.0f, v3 = 0.0f;
+      float v0 = 0.0f, v1 = 0.0f, v2 = 0.0f, v3 = 0.0f, gv = 0.0f;
       if (live && c < c_n) {
         const size_t chan = (size_t)img * c_n + c;
         const size_t o = chan * ohw + po;
-        const float gv = pooled[o] > 0.0f ? g[o] : 0.0f;
+        gv = pooled[o] > 0.0f ? g[o] : 0.0f;
         const int local = (int)((size_t)argmax[o] - chan * hw);   // winner inside the channel plane
         const int wy = local / w, wx = local - wy * w;
         const int q = ((wy - 2 * oy) << 1) | (wx - 2 * ox);
@@ -197,6 +198,12 @@ pool2_bwd_planes_kernel(const float* __restrict__ g, const float* __restrict__ p
         }
       }
       tile[cl][tx] = v0; tile[cl][32 + tx] = v1; tile[cl][64 + tx] = v2; tile[cl][96 + tx] = v3;
+      if (chan_partial) {   // the window's four outputs sum to gv: fixed-order butterfly over the 32 positions
+        float sum = gv;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+        if (tx == 0 && c < c_n) chan_partial[(size_t)blockIdx.x * c_n + c] = sum;
+      }
     }
   }
   if (!hi) return;
@@ -217,10 +224,80 @@ pool2_bwd_planes_kernel(const float* __restrict__ g, const float* __restrict__ p
   }
 }
 
+
+// 2x2 / stride-2 max-pool forward over even-sized images that also writes the pooled output's
+// NHWC planes (the next convolution's operand).  Same tiling as pool2_bwd_planes_kernel: 32
+// channels x 32 consecutive pooled positions per block; the first maximum in row-major window
+// order wins and argmax is the flat input index, as in maxpool2x2_fwd_kernel.
+template <bool SPLIT>
+__global__ void __launch_bounds__(256)
+pool2_fwd_planes_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ argmax,
+                        float* __restrict__ hi, float* __restrict__ lo, int n_img, int c_n, int h, int w) {
+  __shared__ float tile[32][33];
+  const int oh = h >> 1, ow = w >> 1, ohw = oh * ow, hw = h * w;
+  const long total_pos = (long)n_img * ohw;
+  const long gp0 = (long)blockIdx.x * 32;
+  const int c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  {
+    const long gp = gp0 + tx;
+    const bool live = gp < total_pos;
+    const int img = live ? (int)(gp / ohw) : 0;
+    const int po = live ? (int)(gp - (long)img * ohw) : 0;
+    const int oy = po / ow, ox = po - oy * ow;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int cl = ty + 8 * i, c = c0 + cl;
+      float best = 0.0f;
+      if (live && c < c_n) {
+        const size_t chan = (size_t)img * c_n + c;
+        const size_t first = chan * hw + (size_t)(2 * oy) * w + 2 * ox;
+        const float2 r0 = *reinterpret_cast<const float2*>(x + first);
+        const float2 r1 = *reinterpret_cast<const float2*>(x + first + w);
+        best = r0.x;
+        size_t bi = first;
+        if (r0.y > best) { best = r0.y; bi = first + 1; }
+        if (r1.x > best) { best = r1.x; bi = first + w; }
+        if (r1.y > best) { best = r1.y; bi = first + w + 1; }
+        y[chan * ohw + po] = best;
+        if (argmax) argmax[chan * ohw + po] = (int32_t)bi;
+      }
+      tile[cl][tx] = best;
+    }
+  }
+  __syncthreads();
+  const int c = c0 + tx;   // lane = channel: one full 128-byte line per warp store
+  if (c >= c_n) return;
+#pragma unroll
+  for (int k = ty; k < 32; k += 8) {
+    const long gp = gp0 + k;
+    if (gp >= total_pos) continue;
+    const float v = tile[tx][k];
+    const float hv = tc::tf32_rn(v);
+    hi[(size_t)gp * c_n + c] = hv;
+    if (SPLIT) lo[(size_t)gp * c_n + c] = v - hv;
+  }
+}
+
 }  // namespace
 
+int nrs_tc_pool2_fwd_planes(nrs_ctx* ctx, const float* x, float* y, int32_t* argmax, float* hi, float* lo, int n, int c,
+                            int h, int w) {
+  if (n <= 0 || c <= 0) return NRS_OK;
+  if (h % 2 != 0 || w % 2 != 0 || !hi || (reinterpret_cast<uintptr_t>(x) & 7) != 0) return NRS_ERR_UNSUPPORTED;
+  const long blocks = ((long)n * (h / 2) * (w / 2) + 31) / 32;
+  if (blocks > 2147483647L || (c + 31) / 32 > 65535) return NRS_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)blocks, (unsigned)((c + 31) / 32));
+  if (lo) pool2_fwd_planes_kernel<true><<<grid, 256, 0, ctx->stream>>>(x, y, argmax, hi, lo, n, c, h, w);
+  else pool2_fwd_planes_kernel<false><<<grid, 256, 0, ctx->stream>>>(x, y, argmax, hi, nullptr, n, c, h, w);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
 int nrs_tc_stage_masked(nrs_ctx* ctx, int mode, const float* g, const float* y, const int32_t* argmax, int n, int c,
-                        int h, int w, int k, float* nchw_out, float* hi, float* lo) {
+                        int h, int w, int k, float* nchw_out, float* hi, float* lo, float* chan_partial,
+                        int* chan_partial_rows) {
+  if (chan_partial_rows) *chan_partial_rows = 0;
   if (n <= 0 || c <= 0) return NRS_OK;
   const int oh = mode == 1 ? h / k : h, ow = mode == 1 ? w / k : w;
   dim3 grid((unsigned)((h * w + 31) / 32), (unsigned)((c + 31) / 32), (unsigned)n);
@@ -228,9 +305,10 @@ int nrs_tc_stage_masked(nrs_ctx* ctx, int mode, const float* g, const float* y, 
   const bool split = lo != nullptr;
   if (mode == 1 && k == 2 && h % 2 == 0 && w % 2 == 0 && (long)n * (h / 2) * (w / 2) / 32 < 2147483647L) {
     dim3 pgrid((unsigned)(((long)n * (h / 2) * (w / 2) + 31) / 32), (unsigned)((c + 31) / 32));
-    if (split) pool2_bwd_planes_kernel<true><<<pgrid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, n, c, h, w);
-    else pool2_bwd_planes_kernel<false><<<pgrid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, n, c, h, w);
+    if (split) pool2_bwd_planes_kernel<true><<<pgrid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, chan_partial, n, c, h, w);
+    else pool2_bwd_planes_kernel<false><<<pgrid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, chan_partial, n, c, h, w);
     NRS_LAUNCHED(ctx);
+    if (chan_partial && chan_partial_rows) *chan_partial_rows = (int)pgrid.x;
     return NRS_OK;
   }
   if (mode == 0) {
