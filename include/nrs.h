@@ -229,6 +229,12 @@ int nrs_embedding_bwd(nrs_ctx* ctx, const float* g, const int32_t* idx, float* d
  * reference has no mask).  backward == 0: y = (j > i) ? -1e30 : x;
  * backward != 0: y (+)= (j > i) ? 0 : x. */
 int nrs_causal_mask(nrs_ctx* ctx, const float* x, float* y, int batch, int s, int backward, int accumulate);
+/* Head split / merge for multi-head attention: to_heads != 0 maps x[batch, s, heads*d_head] to
+ * y[batch*heads, s, d_head] (head h = column slice [h*d_head, (h+1)*d_head), exactly the slices
+ * src/nn/multihead.rs:94-107 takes one by one); to_heads == 0 is the inverse, i.e. the
+ * reference's concat_cols of the per-head results.  y (+)= when accumulate. */
+int nrs_permute_heads(nrs_ctx* ctx, const float* x, float* y, int batch, int s, int heads, int d_head, int to_heads,
+                      int accumulate);
 
 /* ------------------------------------------------------------------- loss -- */
 

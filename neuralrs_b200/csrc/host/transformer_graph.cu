@@ -124,19 +124,36 @@ NodeP PositionalEncoding::forward(const NodeP& x) const {
   return out;
 }
 
+// [batch, seq, heads*d_head] <-> [batch*heads, seq, d_head]; the backward pass is the opposite permutation.
+static NodeP permute_heads(const NodeP& x, size_t batch, size_t seq, size_t heads, size_t d_head, bool to_heads) {
+  nrs_ctx* ctx = x->ctx;
+  NodeP out = make_result(ctx, to_heads ? std::vector<size_t>{batch * heads, seq, d_head}
+                                        : std::vector<size_t>{batch, seq, heads * d_head}, {x});
+  check(ctx, nrs_permute_heads(ctx, x->data, out->data, (int)batch, (int)seq, (int)heads, (int)d_head, to_heads ? 1 : 0, 0));
+  Node* self = out.get();
+  out->backward_fn = [self, x, batch, seq, heads, d_head, to_heads]() {
+    if (!x->requires_grad) return;
+    const float* g = grad_view(self);
+    GradSlot t = grad_slot(x);
+    check(self->ctx, nrs_permute_heads(self->ctx, g, t.ptr, (int)batch, (int)seq, (int)heads, (int)d_head, to_heads ? 0 : 1,
+                                       t.accumulate));
+  };
+  return out;
+}
+
 NodeP MultiHeadAttention::forward_batch(const NodeP& x) const {
   if (!x || x->shape.size() != 3) fail(NRS_ERR_SHAPE, "cuda mha: input must be [batch, seq, d_model]");
   const size_t batch = x->shape[0], seq = x->shape[1], d = x->shape[2];
   if (d != d_model || num_heads == 0 || d_model % num_heads != 0) fail(NRS_ERR_SHAPE, "cuda mha: d_model / num_heads mismatch");
   auto proj = [&](const NodeP& w) { return reshape(matmul(reshape(x, {batch * seq, d}), w), {batch, seq, d}); };
   NodeP q = proj(w_q), k = proj(w_k), v = proj(w_v);
+  // The reference slices the heads out column by column, runs attention_batch per head and
+  // concatenates (multihead.rs:94-107).  The same arithmetic in one pass: heads become extra
+  // batch entries, attention_batch runs once over [batch*heads, seq, d_head].
   const size_t d_head = d_model / num_heads;
-  std::vector<NodeP> heads;
-  for (size_t h = 0; h < num_heads; ++h) {
-    const size_t c0 = h * d_head, c1 = c0 + d_head;
-    heads.push_back(attention_batch(slice_cols(q, c0, c1), slice_cols(k, c0, c1), slice_cols(v, c0, c1), causal));
-  }
-  NodeP concat = concat_cols(heads);
+  auto split = [&](const NodeP& t) { return permute_heads(t, batch, seq, num_heads, d_head, true); };
+  NodeP attended = attention_batch(split(q), split(k), split(v), causal);
+  NodeP concat = permute_heads(attended, batch, seq, num_heads, d_head, false);
   return reshape(matmul(reshape(concat, {batch * seq, d}), w_o), {batch, seq, d});
 }
 

@@ -343,8 +343,10 @@ tc_splitk_reduce_kernel(const Policy pol, const SplitInfo sp) {
 // than kMaxChainK elements when `limit_chain`.
 inline void plan_split(const nrs_ctx* ctx, long tiles, int kb_total, bool limit_chain, int* splits, int* kb_per_split) {
   int s = 1;
-  if (tiles < ctx->sm_count && kb_total >= 16) {
-    s = (int)((ctx->sm_count + tiles - 1) / tiles);
+  // (More than half a wave of tiles runs unsplit: the second pass over the partial tiles costs more
+  // than the idle SMs.)
+  if (2 * tiles <= ctx->sm_count && kb_total >= 16) {
+    s = (int)(ctx->sm_count / tiles);
     if (s > kb_total / 8) s = kb_total / 8;
   }
   if (limit_chain) {

@@ -75,6 +75,26 @@ unsigned grid_for(const nrs_ctx* ctx, size_t work) {
   return (unsigned)(blocks > cap ? cap : (blocks ? blocks : 1));
 }
 
+// to_heads: y[((b*H + h)*S + s)*dh + e] = x[((b*S + s)*H + h)*dh + e]; otherwise the inverse.
+__global__ void __launch_bounds__(256)
+permute_heads_kernel(const float* __restrict__ x, float* y, size_t total, int S, int H, int dh, int to_heads,
+                     int accumulate) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    // idx walks the [b][s][h][e] order
+    const int e = (int)(idx % dh);
+    size_t t = idx / dh;
+    const int h = (int)(t % H);
+    t /= H;
+    const int s = (int)(t % S);
+    const size_t b = t / S;
+    const size_t head_major = ((b * H + h) * S + s) * dh + e;
+    const size_t src = to_heads ? idx : head_major, dst = to_heads ? head_major : idx;
+    const float v = x[src];
+    y[dst] = accumulate ? y[dst] + v : v;
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -106,6 +126,18 @@ int nrs_causal_mask(nrs_ctx* ctx, const float* x, float* y, int batch, int s, in
   if (total == 0) return NRS_OK;
   NRS_REQUIRE(ctx, x && y, NRS_ERR_ARG, "nrs_causal_mask: null tensor");
   causal_mask_kernel<<<grid_for(ctx, total), 256, 0, ctx->stream>>>(x, y, total, s, backward, accumulate);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
+int nrs_permute_heads(nrs_ctx* ctx, const float* x, float* y, int batch, int s, int heads, int d_head, int to_heads,
+                      int accumulate) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, batch >= 0 && s >= 0 && heads > 0 && d_head > 0, NRS_ERR_SHAPE, "nrs_permute_heads: bad shape");
+  const size_t total = (size_t)batch * s * heads * d_head;
+  if (total == 0) return NRS_OK;
+  NRS_REQUIRE(ctx, x && y, NRS_ERR_ARG, "nrs_permute_heads: null tensor");
+  permute_heads_kernel<<<grid_for(ctx, total), 256, 0, ctx->stream>>>(x, y, total, s, heads, d_head, to_heads, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }

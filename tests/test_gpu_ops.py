@@ -302,3 +302,21 @@ def test_manipulation(gpu_ctx, oracle32):
     part = Dev(gpu_ctx, shape=(3 * 37, 20))
     call(gpu_ctx, "nrs_concat_read", out, part, 3 * 37, 70, 50, 20, 0)
     assert np.array_equal(part.get(), s.get())
+
+
+def test_permute_heads(gpu_ctx, oracle32):
+    """Head split = the reference's per-head column slices stacked along the batch
+    (src/nn/multihead.rs:94-107); merge = its concat_cols; both bit-exact, merge(split(x)) == x."""
+    rng = np.random.default_rng(12)
+    b, s, h, dh = 3, 7, 4, 5
+    x = rng.normal(size=(b, s, h * dh)).astype(np.float32)
+    heads = Dev(gpu_ctx, shape=(b * h, s, dh))
+    call(gpu_ctx, "nrs_permute_heads", Dev(gpu_ctx, x), heads, b, s, h, dh, 1, 0)
+    want = np.stack([oracle32.slice_cols_fwd(x.reshape(-1, h * dh), k * dh, (k + 1) * dh).reshape(b, s, dh)
+                     for k in range(h)], axis=1).reshape(b * h, s, dh)
+    assert np.array_equal(heads.get(), want)
+    back = Dev(gpu_ctx, shape=x.shape)
+    call(gpu_ctx, "nrs_permute_heads", heads, back, b, s, h, dh, 0, 0)
+    assert np.array_equal(back.get(), x)
+    call(gpu_ctx, "nrs_permute_heads", heads, back, b, s, h, dh, 0, 1)   # accumulate
+    assert np.array_equal(back.get(), 2 * x)
