@@ -2,7 +2,10 @@
 // layer of a CNN: c_in = 1 or 3, 3x3, stride 1).  With K = c_in*kh*kw = 9 or 27 the
 // contraction is too short for a tensor-core K-block and a 128x128 implicit-GEMM
 // tile is mostly padding, so these layers get their own FFMA kernels:
-//   forward        one thread per output pixel holds the K-element input patch in
+//   forward        TF32 modes: the same patch planes as the weight gradient, run through the
+//                  tensor-core convolution kernel as a 1x1 layer (its epilogue adds the bias,
+//                  the ReLU and the output's planes).  FP32 mode, FFMA:
+//                  one thread per output pixel holds the K-element input patch in
 //                  registers and sweeps the output channels against weights kept
 //                  in shared memory (128-bit broadcast loads); stores are full
 //                  128-byte lines per channel; on request the result is also
@@ -289,29 +292,70 @@ int run_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, i
   return NRS_OK;
 }
 
-// Tensor-core route (TF32 modes): patch planes, then the general weight-gradient kernel on them
-// as a 1x1 convolution over 32 "channels".
+// wide[co][32] = w[co][K] padded with zeros (the 32-"channel" 1x1 weights of the patch formulation).
+__global__ void __launch_bounds__(256)
+smallc_widen_kernel(const float* __restrict__ w, float* __restrict__ wide, int co, int K) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= co * 32) return;
+  const int c = idx >> 5, k = idx & 31;
+  wide[idx] = k < K ? w[c * K + k] : 0.0f;
+}
+
+template <int CI, int KS>
+int launch_patches(nrs_ctx* ctx, const float* x, float* hi, float* lo, int n, int h, int wd, int pad, int oh, int ow) {
+  const size_t pixels = (size_t)n * oh * ow;
+  size_t blocks = (pixels + 255) / 256;
+  const size_t cap = (size_t)ctx->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  smallc_patch_planes_kernel<CI, KS><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, hi, lo, n, h, wd, pad, oh, ow);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
+// The patch planes of x: the caller's registered ones, or fresh ones in pool blocks (*owned).
+template <int CI, int KS>
+int get_patches(nrs_ctx* ctx, const float* x, int n, int h, int wd, int pad, int oh, int ow, float** hi, float** lo, bool* owned) {
+  const bool split = ctx->math_mode == NRS_MATH_3XTF32;
+  *owned = false;
+  auto it = ctx->patch_hints.find(x);
+  // (`split` of a patch hint: bit 0 = residual plane present, bits 8.. = the padding it was made for)
+  if (it != ctx->patch_hints.end() && ((it->second.split & 1) != 0) == split && (it->second.split >> 8) == pad) {
+    *hi = it->second.hi;
+    *lo = it->second.lo;
+    return NRS_OK;
+  }
+  const size_t pixels = (size_t)n * oh * ow;
+  void *phi = nullptr, *plo = nullptr;
+  int st = nrs_alloc(ctx, pixels * 32 * sizeof(float), 0, &phi);
+  if (st == NRS_OK && split) st = nrs_alloc(ctx, pixels * 32 * sizeof(float), 0, &plo);
+  if (st == NRS_OK) st = launch_patches<CI, KS>(ctx, x, (float*)phi, (float*)plo, n, h, wd, pad, oh, ow);
+  if (st != NRS_OK) {
+    if (phi) nrs_free(ctx, phi);
+    if (plo) nrs_free(ctx, plo);
+    return st;
+  }
+  *hi = (float*)phi;
+  *lo = (float*)plo;
+  *owned = true;
+  return NRS_OK;
+}
+
+// Tensor-core route (TF32 modes): with the input written out as patch planes the layer is a 1x1
+// convolution over 32 "channels", and the general tensor-core kernels run it.
 template <int CI, int KS>
 int run_wgrad_tc(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int h, int wd, int co, int pad, int oh,
                  int ow, int accumulate) {
   constexpr int K = CI * KS * KS;
   const bool split = ctx->math_mode == NRS_MATH_3XTF32;
-  const size_t pixels = (size_t)n * oh * ow;
-  void *phi = nullptr, *plo = nullptr, *wide = nullptr;
-  int st = nrs_alloc(ctx, pixels * 32 * sizeof(float), 0, &phi);
-  if (st == NRS_OK && split) st = nrs_alloc(ctx, pixels * 32 * sizeof(float), 0, &plo);
-  if (st == NRS_OK) st = nrs_alloc(ctx, (size_t)co * 32 * sizeof(float), 0, &wide);
+  float *phi = nullptr, *plo = nullptr;
+  bool owned = false;
+  int st = get_patches<CI, KS>(ctx, x, n, h, wd, pad, oh, ow, &phi, &plo, &owned);
+  if (st != NRS_OK) return st;
+  void* wide = nullptr;
+  st = nrs_alloc(ctx, (size_t)co * 32 * sizeof(float), 0, &wide);
   if (st == NRS_OK) {
-    size_t blocks = (pixels + 255) / 256;
-    const size_t cap = (size_t)ctx->sm_count * 16;
-    if (blocks > cap) blocks = cap;
-    smallc_patch_planes_kernel<CI, KS><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (float*)phi, (float*)plo, n, h, wd, pad, oh, ow);
-    ctx->launches++;
-    if (cudaGetLastError() != cudaSuccess) st = NRS_ERR_CUDA;
-  }
-  if (st == NRS_OK) {
-    ctx->plane_hints[phi] = NrsPlanes{(float*)phi, (float*)plo, split ? 1 : 0};
-    st = nrs_tc_conv_wgrad(ctx, (const float*)phi, dy, (float*)wide, n, 32, oh, ow, co, 1, 1, 1, 0, 0);
+    ctx->plane_hints[phi] = NrsPlanes{phi, plo, split ? 1 : 0};
+    st = nrs_tc_conv_wgrad(ctx, phi, dy, (float*)wide, n, 32, oh, ow, co, 1, 1, 1, 0, 0);
     ctx->plane_hints.erase(phi);
   }
   if (st == NRS_OK) {
@@ -319,8 +363,39 @@ int run_wgrad_tc(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n
     ctx->launches++;
     if (cudaGetLastError() != cudaSuccess) st = NRS_ERR_CUDA;
   }
-  if (phi) nrs_free(ctx, phi);
-  if (plo) nrs_free(ctx, plo);
+  if (owned) {
+    nrs_free(ctx, phi);
+    if (plo) nrs_free(ctx, plo);
+  }
+  if (wide) nrs_free(ctx, wide);
+  return st;
+}
+
+template <int CI, int KS>
+int run_fwd_tc(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y, int n, int h, int wd, int co, int pad,
+               int oh, int ow, int act) {
+  constexpr int K = CI * KS * KS;
+  const bool split = ctx->math_mode == NRS_MATH_3XTF32;
+  float *phi = nullptr, *plo = nullptr;
+  bool owned = false;
+  int st = get_patches<CI, KS>(ctx, x, n, h, wd, pad, oh, ow, &phi, &plo, &owned);
+  if (st != NRS_OK) return st;
+  void* wide = nullptr;
+  st = nrs_alloc(ctx, (size_t)co * 32 * sizeof(float), 0, &wide);
+  if (st == NRS_OK) {
+    smallc_widen_kernel<<<nrs_blocks((size_t)co * 32, 256), 256, 0, ctx->stream>>>(w, (float*)wide, co, K);
+    ctx->launches++;
+    if (cudaGetLastError() != cudaSuccess) st = NRS_ERR_CUDA;
+  }
+  if (st == NRS_OK) {
+    ctx->plane_hints[phi] = NrsPlanes{phi, plo, split ? 1 : 0};
+    st = nrs_tc_conv_fwd(ctx, phi, (const float*)wide, b, y, n, 32, oh, ow, co, 1, 1, 1, 0, act);
+    ctx->plane_hints.erase(phi);
+  }
+  if (owned) {
+    nrs_free(ctx, phi);
+    if (plo) nrs_free(ctx, plo);
+  }
   if (wide) nrs_free(ctx, wide);
   return st;
 }
@@ -336,6 +411,12 @@ int nrs_smallc_conv_fwd(nrs_ctx* ctx, const float* x, const float* w, const floa
                         int wd, int co, int kh, int kw, int stride, int pad, int act) {
   if (!eligible(ci, kh, kw, stride, co) || getenv("NRS_DISABLE_SMALLC")) return NRS_ERR_UNSUPPORTED;
   const int oh = h + 2 * pad - 2, ow = wd + 2 * pad - 2;
+  if (ctx->math_mode != NRS_MATH_FP32 && co % 32 == 0 && (long)n * oh * ow >= 4096 && !getenv("NRS_DISABLE_TC") &&
+      !getenv("NRS_SMALLC_FFMA_FWD")) {
+    const int st = ci == 1 ? run_fwd_tc<1, 3>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act)
+                           : run_fwd_tc<3, 3>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act);
+    if (st != NRS_ERR_UNSUPPORTED) return st;
+  }
   // Planes of the result requested by the caller (a tensor-core convolution reads it next)?
   float *hi = nullptr, *lo = nullptr;
   auto extras = ctx->out_extras.find(y);
@@ -350,6 +431,12 @@ int nrs_smallc_conv_fwd(nrs_ctx* ctx, const float* x, const float* w, const floa
   }
   if (ci == 1) return run_fwd<1, 3, false>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act, nullptr, nullptr);
   return run_fwd<3, 3, false>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act, nullptr, nullptr);
+}
+
+int nrs_smallc_patch_planes(nrs_ctx* ctx, const float* x, float* hi, float* lo, int n, int ci, int h, int wd, int pad) {
+  const int oh = h + 2 * pad - 2, ow = wd + 2 * pad - 2;
+  if ((ci != 1 && ci != 3) || oh < 1 || ow < 1 || n < 1) return NRS_ERR_UNSUPPORTED;
+  return ci == 1 ? launch_patches<1, 3>(ctx, x, hi, lo, n, h, wd, pad, oh, ow) : launch_patches<3, 3>(ctx, x, hi, lo, n, h, wd, pad, oh, ow);
 }
 
 int nrs_smallc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,

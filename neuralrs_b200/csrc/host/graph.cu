@@ -35,6 +35,11 @@ Node::~Node() {
     nrs_free(ctx, planes_hi);
     if (planes_lo) nrs_free(ctx, planes_lo);
   }
+  if (patches_hi) {
+    ctx->patch_hints.erase(data);
+    nrs_free(ctx, patches_hi);
+    if (patches_lo) nrs_free(ctx, patches_lo);
+  }
   if (gplanes_hi) {
     ctx->plane_hints.erase(grad);
     nrs_free(ctx, gplanes_hi);
@@ -560,6 +565,24 @@ NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, 
   if (stride == 1 && !x->planes_hi && co % 32 == 0 && w->requires_grad) {
     float *phi = nullptr, *plo = nullptr;
     if (stage_planes(ctx, x->data, x->shape, &phi, &plo)) { x->planes_hi = phi; x->planes_lo = plo; }
+  }
+  // Image layer in a TF32 mode: forward and weight gradient both run on the tensor cores over the
+  // input's patch planes; make them once.
+  if ((ci == 1 || ci == 3) && kh == 3 && kw == 3 && stride == 1 && co % 32 == 0 && !x->patches_hi && planes_possible(ctx) &&
+      (size_t)n * oh * ow >= 4096 && !ctx->patch_hints.count(x->data)) {
+    const size_t floats = (size_t)n * oh * ow * 32;
+    float* phi = dalloc(ctx, floats);
+    float* plo = ctx->math_mode == NRS_MATH_3XTF32 ? dalloc(ctx, floats) : nullptr;
+    const int st = nrs_smallc_patch_planes(ctx, x->data, phi, plo, n, ci, h, wd, (int)pad);
+    if (st == NRS_OK) {
+      x->patches_hi = phi;
+      x->patches_lo = plo;
+      ctx->patch_hints[x->data] = NrsPlanes{phi, plo, (plo ? 1 : 0) | ((int)pad << 8)};
+    } else {
+      nrs_free(ctx, phi);
+      if (plo) nrs_free(ctx, plo);
+      if (st != NRS_ERR_UNSUPPORTED) check(ctx, st);
+    }
   }
   // The caller knows a tensor-core convolution consumes this output: let the kernel write the
   // output's NHWC planes itself (otherwise the consumer stages them in a pass of its own).

@@ -53,6 +53,10 @@ struct Node {
   // by the forward pass and the weight gradient (registered with the context while alive).
   float* planes_hi = nullptr;
   float* planes_lo = nullptr;
+  // For an image tensor (1 or 3 channels) read by a 3x3 layer: its patch planes, shared by that
+  // layer's forward pass and weight gradient (registered with the context while alive).
+  float* patches_hi = nullptr;
+  float* patches_lo = nullptr;
   // Set on the output of a convolution that folded a ReLU into its epilogue.  A max-pool
   // directly above may then hand back a gradient that already carries the ReLU mask
   // (grad_premasked), together with its NHWC planes (gplanes_*, freed with the node).

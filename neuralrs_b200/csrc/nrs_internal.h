@@ -82,6 +82,10 @@ struct nrs_ctx {
   std::map<const void*, NrsPlanes> plane_hints;
   std::map<const void*, NrsOutExtras> out_extras;
   std::map<const void*, NrsColsumRequest> colsum_requests;
+  // Patch planes ([pixels][32], see conv_smallc.cu) of an image tensor, keyed by its device pointer:
+  // the host graph makes them once per step for the image layer's forward pass and weight gradient
+  // (`split`: bit 0 = residual plane present, bits 8.. = the padding they were made for).
+  std::map<const void*, NrsPlanes> patch_hints;
   // Optional per-family device timing (nrs_profile_*).
   bool profiling = false;
   std::vector<NrsProfRecord> prof_records;
@@ -150,6 +154,8 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
 // Row-streaming variant for 3x3 / stride 1 / pad 1 (tc_wgrad_rows.cu); tried first.
 int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
                            int kh, int kw, int stride, int pad, int accumulate);
+// Patch planes of x[n,ci,h,w] for a 3x3 / pad `pad` image layer (ci = 1 or 3): hi/lo [n*oh*ow][32].
+int nrs_smallc_patch_planes(nrs_ctx* ctx, const float* x, float* hi, float* lo, int n, int ci, int h, int wd, int pad);
 // Direct FFMA kernels for 3x3 stride-1 layers over 1 or 3 input channels (conv_smallc.cu).
 int nrs_smallc_conv_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y, int n, int ci, int h,
                         int wd, int co, int kh, int kw, int stride, int pad, int act);
