@@ -208,6 +208,46 @@ int simt_gemm(nrs_ctx* ctx, int ta, int tb, int batch, int m, int n, int k, cons
   return run_gemm_t<true, true>(ctx, batch, m, n, k, a, b, c, bias, act, beta, who);
 }
 
+// Thin products (a classifier head: n or k of a dozen): one thread per output element walks K.
+// A 128 x 128 tile would be nine tenths padding, and the whole product is a few MFLOP, so
+// the only thing that matters is not paying for a tile pipeline.  Exact f32 (serial FMA chain
+// in k order, like the reference's CPU loops).
+template <bool TA, bool TB>
+__global__ void __launch_bounds__(256)
+thin_gemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c, const float* __restrict__ bias, int m,
+                 int n, int k, int act, float beta) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)m * n) return;
+  const int col = (int)(idx % n);
+  const int row = (int)(idx / n);
+  // A is [m][k] (or [k][m] when TA), B is [k][n] (or [n][k] when TB)
+  const float* ap = TA ? a + row : a + (size_t)row * k;
+  const float* bp = TB ? b + (size_t)col * k : b + col;
+  const size_t as = TA ? (size_t)m : 1, bs = TB ? 1 : (size_t)n;
+  float acc = 0.0f;
+#pragma unroll 4
+  for (int kk = 0; kk < k; ++kk) acc = fmaf(ap[kk * as], bp[kk * bs], acc);
+  if (bias) acc += bias[col];
+  acc = nrs_apply_act(acc, act);
+  if (beta != 0.0f) acc += beta * c[idx];
+  c[idx] = acc;
+}
+
+bool thin_gemm_applies(int m, int n, int k) {
+  return (n <= 16 || k <= 16) && (double)m * n * k <= 6.4e7 && (long)m * n >= 1024;
+}
+
+int thin_gemm(nrs_ctx* ctx, int ta, int tb, int m, int n, int k, const float* a, const float* b, float* c,
+              const float* bias, int act, float beta) {
+  const unsigned blocks = nrs_blocks((size_t)m * n, 256);
+  if (!ta && !tb) thin_gemm_kernel<false, false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+  else if (!ta && tb) thin_gemm_kernel<false, true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+  else if (ta && !tb) thin_gemm_kernel<true, false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+  else thin_gemm_kernel<true, true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
 int check_conv_dims(nrs_ctx* ctx, const char* who, int n, int ci, int h, int wd, int co, int kh, int kw,
                     int stride, int pad) {
   NRS_REQUIRE(ctx, n >= 0 && ci > 0 && h > 0 && wd > 0 && co > 0 && kh > 0 && kw > 0, NRS_ERR_SHAPE,
@@ -236,6 +276,7 @@ int nrs_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int m, int n, int k, const 
   if (m == 0 || n == 0) return NRS_OK;
   NRS_REQUIRE(ctx, c && (k == 0 || (a && b)), NRS_ERR_ARG, "nrs_gemm: null operand");
   NrsProfScope prof(ctx, NRS_PROF_GEMM, 2.0 * m * n * k);
+  if (k > 0 && thin_gemm_applies(m, n, k)) return thin_gemm(ctx, trans_a, trans_b, m, n, k, a, b, c, bias, act, beta);
   if (ctx->math_mode != NRS_MATH_FP32 && k > 0) {
     const int st = nrs_tc_gemm(ctx, trans_a, trans_b, 1, m, n, k, a, b, c, bias, act, beta);
     if (st != NRS_ERR_UNSUPPORTED) return st;

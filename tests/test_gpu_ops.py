@@ -24,7 +24,8 @@ def math_mode(request, gpu_ctx):
 
 
 GEMM_SHAPES = [(40, 32, 56), (16, 10, 24), (1, 1, 1), (129, 257, 65), (64, 128, 3136), (256, 512, 1024),
-               (300, 1000, 256), (128, 128, 128), (512, 256, 8)]
+               (300, 1000, 256), (128, 128, 128), (512, 256, 8),
+               (1024, 10, 512), (1024, 512, 10), (512, 10, 1024)]   # classifier head: the thin-product kernel
 
 
 @pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
