@@ -211,9 +211,9 @@ def conv_microbench(ctx, stream, iters=10):
 # kernel).  Traffic of these kernels is proportional to the pixel count, so it is scaled to the
 # per-GPU batch of this run.
 NCU_TRAFFIC = {
-    ("vgg_cifar", "3xtf32", "conv_wgrad"): (275.33e6 + 11.02e6, 256, "tc_wgrad_rows_kernel<2,4> (64->64 ch, 32x32)"),
-    ("vgg_cifar", "3xtf32", "conv_fwd"): (38.33e6 + 0.36e6, 256, "tc_kernel<128,2,ConvPolicy> (128->128 ch, 16x16)"),
-    ("vgg_cifar", "3xtf32", "conv_dgrad"): (38.33e6 + 0.36e6, 256, "tc_kernel<128,2,ConvPolicy> (128->128 ch, 16x16)"),
+    ("vgg_cifar", "3xtf32", "conv_wgrad"): (270.87e6 + 3.69e6, 256, "tc_wgrad_rows_kernel<2,4> (64->64 ch, 32x32)"),
+    ("vgg_cifar", "3xtf32", "conv_fwd"): (68.37e6 + 5.44e6, 256, "tc_kernel<128,2,ConvPolicy> (128->128 ch, 16x16)"),
+    ("vgg_cifar", "3xtf32", "conv_dgrad"): (68.37e6 + 5.44e6, 256, "tc_kernel<128,2,ConvPolicy> (128->128 ch, 16x16)"),
 }
 
 

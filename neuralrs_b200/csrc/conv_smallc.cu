@@ -409,10 +409,9 @@ bool eligible(int ci, int kh, int kw, int stride, int co) {
 // NRS_ERR_UNSUPPORTED when the layer is not a 3x3 stride-1 convolution over 1 or 3 channels.
 int nrs_smallc_conv_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y, int n, int ci, int h,
                         int wd, int co, int kh, int kw, int stride, int pad, int act) {
-  if (!eligible(ci, kh, kw, stride, co) || getenv("NRS_DISABLE_SMALLC")) return NRS_ERR_UNSUPPORTED;
+  if (!eligible(ci, kh, kw, stride, co)) return NRS_ERR_UNSUPPORTED;
   const int oh = h + 2 * pad - 2, ow = wd + 2 * pad - 2;
-  if (ctx->math_mode != NRS_MATH_FP32 && co % 32 == 0 && (long)n * oh * ow >= 4096 && !getenv("NRS_DISABLE_TC") &&
-      !getenv("NRS_SMALLC_FFMA_FWD")) {
+  if (ctx->math_mode != NRS_MATH_FP32 && co % 32 == 0 && (long)n * oh * ow >= 4096) {
     const int st = ci == 1 ? run_fwd_tc<1, 3>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act)
                            : run_fwd_tc<3, 3>(ctx, x, w, b, y, n, h, wd, co, pad, oh, ow, act);
     if (st != NRS_ERR_UNSUPPORTED) return st;
@@ -441,9 +440,9 @@ int nrs_smallc_patch_planes(nrs_ctx* ctx, const float* x, float* hi, float* lo, 
 
 int nrs_smallc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
                           int kh, int kw, int stride, int pad, int accumulate) {
-  if (!eligible(ci, kh, kw, stride, co) || co > 128 || getenv("NRS_DISABLE_SMALLC")) return NRS_ERR_UNSUPPORTED;
+  if (!eligible(ci, kh, kw, stride, co) || co > 128) return NRS_ERR_UNSUPPORTED;
   const int oh = h + 2 * pad - 2, ow = wd + 2 * pad - 2;
-  if (ctx->math_mode != NRS_MATH_FP32 && co % 32 == 0 && (long)n * oh * ow >= 4096 && !getenv("NRS_DISABLE_TC")) {
+  if (ctx->math_mode != NRS_MATH_FP32 && co % 32 == 0 && (long)n * oh * ow >= 4096) {
     const int st = ci == 1 ? run_wgrad_tc<1, 3>(ctx, x, dy, dw, n, h, wd, co, pad, oh, ow, accumulate)
                            : run_wgrad_tc<3, 3>(ctx, x, dy, dw, n, h, wd, co, pad, oh, ow, accumulate);
     if (st != NRS_ERR_UNSUPPORTED) return st;

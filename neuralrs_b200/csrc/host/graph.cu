@@ -133,7 +133,7 @@ NodeP make_result(nrs_ctx* ctx, const std::vector<size_t>& shape, std::vector<No
 static bool stage_planes(nrs_ctx* ctx, const float* src, const std::vector<size_t>& shape, float** hi, float** lo) {
   *hi = *lo = nullptr;
   if (ctx->math_mode == NRS_MATH_FP32 || shape.size() != 4 || shape[1] % 32 != 0 || shape[0] == 0) return false;
-  if (!tc::tensor_map_encoder() || getenv("NRS_DISABLE_TC") || getenv("NRS_NO_PLANE_CACHE")) return false;
+  if (!tc::tensor_map_encoder()) return false;
   if (ctx->plane_hints.count(src)) return false;   // already there (the tensor feeds two convolutions)
   const bool split = ctx->math_mode == NRS_MATH_3XTF32;
   const size_t n = shape[0], c = shape[1], hw = shape[2] * shape[3];
@@ -145,8 +145,7 @@ static bool stage_planes(nrs_ctx* ctx, const float* src, const std::vector<size_
 }
 
 static bool planes_possible(nrs_ctx* ctx) {
-  return ctx->math_mode != NRS_MATH_FP32 && tc::tensor_map_encoder() && !getenv("NRS_DISABLE_TC") &&
-         !getenv("NRS_NO_PLANE_CACHE");
+  return ctx->math_mode != NRS_MATH_FP32 && tc::tensor_map_encoder();
 }
 
 namespace cuda {

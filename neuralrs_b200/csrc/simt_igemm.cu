@@ -208,24 +208,24 @@ int simt_gemm(nrs_ctx* ctx, int ta, int tb, int batch, int m, int n, int k, cons
   return run_gemm_t<true, true>(ctx, batch, m, n, k, a, b, c, bias, act, beta, who);
 }
 
-// Thin products (a classifier head: n or k of a dozen): one thread per output element walks K.
-// A 128 x 128 tile would be nine tenths padding, and the whole product is a few MFLOP, so
-// the only thing that matters is not paying for a tile pipeline.  Exact f32 (serial FMA chain
-// in k order, like the reference's CPU loops).
+// Thin products (a classifier head: n or k of a dozen).  A 128 x 128 tile would be nine tenths
+// padding and the whole product is a few MFLOP, so what matters is not paying for a tile
+// pipeline.  Exact f32; every sum has a fixed order (deterministic).
+constexpr int kThinN = 16;
+
+// k <= 16: one thread per output element.
 template <bool TA, bool TB>
 __global__ void __launch_bounds__(256)
-thin_gemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c, const float* __restrict__ bias, int m,
-                 int n, int k, int act, float beta) {
+thin_k_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c, const float* __restrict__ bias, int m,
+              int n, int k, int act, float beta) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)m * n) return;
   const int col = (int)(idx % n);
   const int row = (int)(idx / n);
-  // A is [m][k] (or [k][m] when TA), B is [k][n] (or [n][k] when TB)
   const float* ap = TA ? a + row : a + (size_t)row * k;
   const float* bp = TB ? b + (size_t)col * k : b + col;
   const size_t as = TA ? (size_t)m : 1, bs = TB ? 1 : (size_t)n;
   float acc = 0.0f;
-#pragma unroll 4
   for (int kk = 0; kk < k; ++kk) acc = fmaf(ap[kk * as], bp[kk * bs], acc);
   if (bias) acc += bias[col];
   acc = nrs_apply_act(acc, act);
@@ -233,17 +233,102 @@ thin_gemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float
   c[idx] = acc;
 }
 
+// n <= 16, A row-major [m][k]: one warp per output row, lanes stride over k (coalesced reads of
+// the A row), each lane keeps n partial sums, butterfly reduction at the end.
+template <bool TB>
+__global__ void __launch_bounds__(256)
+thin_n_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c, const float* __restrict__ bias, int m,
+                   int n, int k, int act, float beta) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= m) return;
+  float acc[kThinN];
+#pragma unroll
+  for (int j = 0; j < kThinN; ++j) acc[j] = 0.0f;
+  const float* ar = a + (size_t)row * k;
+  for (int kk = lane; kk < k; kk += 32) {
+    const float av = ar[kk];
+#pragma unroll
+    for (int j = 0; j < kThinN; ++j)
+      if (j < n) acc[j] = fmaf(av, TB ? b[(size_t)j * k + kk] : b[(size_t)kk * n + j], acc[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < kThinN; ++j)
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], d);
+  if (lane < n) {
+    float v = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kThinN; ++j)
+      if (j == lane) v = acc[j];
+    if (bias) v += bias[lane];
+    v = nrs_apply_act(v, act);
+    float* dst = c + (size_t)row * n + lane;
+    if (beta != 0.0f) v += beta * *dst;
+    *dst = v;
+  }
+}
+
+// n <= 16, A stored [k][m] (a weight gradient X^T . dY): a block owns 32 output rows, lanes are
+// rows (coalesced reads of A[kk][row0..row0+31]), the 8 warps split k and their partial sums are
+// added in warp order through shared memory.
+template <bool TB>
+__global__ void __launch_bounds__(256)
+thin_n_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c, const float* __restrict__ bias, int m,
+                   int n, int k, int act, float beta) {
+  __shared__ float part[8][kThinN][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * 32 + lane;
+  float acc[kThinN];
+#pragma unroll
+  for (int j = 0; j < kThinN; ++j) acc[j] = 0.0f;
+  const int per = (k + 7) / 8, k0 = warp * per, k1 = min(k, k0 + per);
+  if (row < m)
+    for (int kk = k0; kk < k1; ++kk) {
+      const float av = a[(size_t)kk * m + row];
+#pragma unroll
+      for (int j = 0; j < kThinN; ++j)
+        if (j < n) acc[j] = fmaf(av, TB ? b[(size_t)j * k + kk] : b[(size_t)kk * n + j], acc[j]);
+    }
+#pragma unroll
+  for (int j = 0; j < kThinN; ++j) part[warp][j][lane] = acc[j];
+  __syncthreads();
+  // thread -> (row r, column j) of the block's 32 x n outputs
+  for (int o = threadIdx.x; o < 32 * n; o += blockDim.x) {
+    const int r = o / n, j = o - r * n;
+    if (blockIdx.x * 32 + r >= m) continue;
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) v += part[w][j][r];
+    if (bias) v += bias[j];
+    v = nrs_apply_act(v, act);
+    float* dst = c + (size_t)(blockIdx.x * 32 + r) * n + j;
+    if (beta != 0.0f) v += beta * *dst;
+    *dst = v;
+  }
+}
+
 bool thin_gemm_applies(int m, int n, int k) {
-  return (n <= 16 || k <= 16) && (double)m * n * k <= 6.4e7 && (long)m * n >= 1024;
+  return (n <= kThinN || k <= 16) && (double)m * n * k <= 6.4e7 && (long)m * n >= 1024;
 }
 
 int thin_gemm(nrs_ctx* ctx, int ta, int tb, int m, int n, int k, const float* a, const float* b, float* c,
               const float* bias, int act, float beta) {
-  const unsigned blocks = nrs_blocks((size_t)m * n, 256);
-  if (!ta && !tb) thin_gemm_kernel<false, false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
-  else if (!ta && tb) thin_gemm_kernel<false, true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
-  else if (ta && !tb) thin_gemm_kernel<true, false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
-  else thin_gemm_kernel<true, true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+  if (k <= 16) {
+    const unsigned blocks = nrs_blocks((size_t)m * n, 256);
+    if (!ta && !tb) thin_k_kernel<false, false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+    else if (!ta && tb) thin_k_kernel<false, true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+    else if (ta && !tb) thin_k_kernel<true, false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+    else thin_k_kernel<true, true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+  } else if (!ta) {
+    const unsigned blocks = nrs_blocks((size_t)m, 8);
+    if (tb) thin_n_rows_kernel<true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+    else thin_n_rows_kernel<false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+  } else {
+    const unsigned blocks = nrs_blocks((size_t)m, 32);
+    if (tb) thin_n_cols_kernel<true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+    else thin_n_cols_kernel<false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+  }
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }

@@ -174,7 +174,7 @@ int run_conv(nrs_ctx* ctx, const ConvPlan& p, const float* a_hi, const float* a_
 }
 
 int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
-  if (!tc::tensor_map_encoder() || getenv("NRS_DISABLE_TC")) return NRS_ERR_UNSUPPORTED;
+  if (!tc::tensor_map_encoder()) return NRS_ERR_UNSUPPORTED;
   if (p.a_ch % 32 != 0 || p.n_ch_out % 32 != 0 || p.out_w > 128 || p.out_w < 1) return NRS_ERR_UNSUPPORTED;
   if (p.a_w > 256 * 1024 || p.n_img < 1) return NRS_ERR_UNSUPPORTED;
   const bool split = ctx->math_mode == NRS_MATH_3XTF32;

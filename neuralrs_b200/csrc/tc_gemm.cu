@@ -131,7 +131,6 @@ int run(nrs_ctx* ctx, const Operand& A, const Operand& B, int batch, int m, int 
 int nrs_tc_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n, int k, const float* a, const float* b,
                 float* c, const float* bias, int act, float beta) {
   if (!tc::tensor_map_encoder()) return NRS_ERR_UNSUPPORTED;
-  if (getenv("NRS_DISABLE_TC")) return NRS_ERR_UNSUPPORTED;
   // Small or skinny problems stay on the FFMA kernel: a 128-row tile would be mostly padding.
   if (m < 64 || n < 32 || k < 32) return NRS_ERR_UNSUPPORTED;
   if (batch > 65535) return NRS_ERR_UNSUPPORTED;

@@ -242,7 +242,7 @@ int launch_wgrad(nrs_ctx* ctx, const CUtensorMap* maps, const WgradParams& p, in
 
 int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
                       int kh, int kw, int stride, int pad, int accumulate) {
-  if (!tc::tensor_map_encoder() || getenv("NRS_DISABLE_TC") || getenv("NRS_DISABLE_TC_WGRAD")) return NRS_ERR_UNSUPPORTED;
+  if (!tc::tensor_map_encoder()) return NRS_ERR_UNSUPPORTED;
   if (stride != 1 || ci % 32 != 0 || co % 32 != 0 || ci > kMaxN || n < 1) return NRS_ERR_UNSUPPORTED;
   const int oh = h + 2 * pad - kh + 1, ow = wd + 2 * pad - kw + 1;
   if (ow > wd || oh > h || ow < 1 || oh < 1 || ow > 64) return NRS_ERR_UNSUPPORTED;

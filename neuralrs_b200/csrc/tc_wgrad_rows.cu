@@ -327,8 +327,7 @@ int launch_rows(nrs_ctx* ctx, const CUtensorMap* maps, const RowParams& p, int c
 // that are multiples of 32 and image rows of 16, 32 or 64 pixels.
 int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
                            int kh, int kw, int stride, int pad, int accumulate) {
-  if (!tc::tensor_map_encoder() || getenv("NRS_DISABLE_TC") || getenv("NRS_DISABLE_TC_WGRAD") || getenv("NRS_WGRAD_GENERAL"))
-    return NRS_ERR_UNSUPPORTED;
+  if (!tc::tensor_map_encoder()) return NRS_ERR_UNSUPPORTED;
   if (kh != 3 || kw != 3 || stride != 1 || pad != 1 || ci % 32 != 0 || co % 32 != 0 || n < 1) return NRS_ERR_UNSUPPORTED;
   // Rows of 16, 32 or 64 pixels; narrower images amortise the per-row bookkeeping of the single
   // issuing thread poorly and do better on the general kernel's multi-row pixel tiles.
