@@ -91,6 +91,13 @@ enum nrs_prof_kind {
   NRS_PROF_CONV_FWD = 0, NRS_PROF_CONV_DGRAD = 1, NRS_PROF_CONV_WGRAD = 2,
   NRS_PROF_GEMM = 3, NRS_PROF_ADAMW = 4, NRS_PROF_KINDS = 5
 };
+/* Self-test of the time-out path (no reference counterpart).  Every device-side wait of the
+ * tensor-core kernels is bounded: on expiry the kernel records a code, and the next nrs_sync /
+ * nrs_d2h returns NRS_ERR_TIMEOUT while the context stays usable.  This entry point launches a
+ * one-thread kernel that waits `limit_clocks` SM clocks on a barrier nobody completes, so that path
+ * can be exercised without a fault or a hang. */
+int nrs_selftest_bounded_wait(nrs_ctx* ctx, int64_t limit_clocks);
+
 int nrs_profile_enable(nrs_ctx* ctx, int on);
 int nrs_profile_reset(nrs_ctx* ctx);
 int nrs_profile_get(nrs_ctx* ctx, int kind, double* ms_out, double* work_out, uint64_t* calls_out);

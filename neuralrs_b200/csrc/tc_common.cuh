@@ -42,15 +42,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the barrier did not flip within kWaitClocks.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait: false when the barrier did not flip within `limit` SM clocks.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kWaitClocks) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_limit(bar, parity, kWaitClocks); }
 
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -128,6 +128,31 @@ int run(nrs_ctx* ctx, const Operand& A, const Operand& B, int batch, int m, int 
 
 }  // namespace
 
+namespace {
+// Waits on an mbarrier nobody ever arrives on, with the kernels' own bounded-wait primitive and a
+// short limit, and reports the expiry the way they do.
+__global__ void bounded_wait_probe_kernel(long long limit_clocks, int* __restrict__ err_flag) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&bar, 1);
+    tc::fence_barrier_init();
+    if (!tc::mbar_wait_limit(&bar, 0, limit_clocks)) atomicExch(err_flag, tc::kErrMmaWait);
+  }
+}
+}  // namespace
+
+extern "C" int nrs_selftest_bounded_wait(nrs_ctx* ctx, int64_t limit_clocks) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, limit_clocks > 0 && limit_clocks <= 100000000, NRS_ERR_ARG,
+              "nrs_selftest_bounded_wait: limit must be in (0, 1e8] clocks");
+  int* err = nullptr;
+  const int st = nrs_err_flag(ctx, &err);
+  if (st != NRS_OK) return st;
+  bounded_wait_probe_kernel<<<1, 32, 0, ctx->stream>>>((long long)limit_clocks, err);
+  NRS_LAUNCHED(ctx);
+  return NRS_OK;
+}
+
 int nrs_tc_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n, int k, const float* a, const float* b,
                 float* c, const float* bias, int act, float beta) {
   if (!tc::tensor_map_encoder()) return NRS_ERR_UNSUPPORTED;

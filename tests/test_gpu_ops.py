@@ -321,3 +321,17 @@ def test_permute_heads(gpu_ctx, oracle32):
     assert np.array_equal(back.get(), x)
     call(gpu_ctx, "nrs_permute_heads", heads, back, b, s, h, dh, 0, 1)   # accumulate
     assert np.array_equal(back.get(), 2 * x)
+
+
+def test_bounded_wait_times_out_and_context_survives(gpu_ctx):
+    """A device wait that runs out is reported as NRS_ERR_TIMEOUT at the next sync; nothing faults,
+    and the context keeps working afterwards."""
+    l = _lib.lib()
+    assert l.nrs_selftest_bounded_wait(gpu_ctx.h, 200000) == 0           # ~0.1 ms on a barrier nobody completes
+    assert l.nrs_sync(gpu_ctx.h) == 6                                     # NRS_ERR_TIMEOUT
+    assert b"bounded wait" in l.nrs_last_error(gpu_ctx.h)
+    assert l.nrs_sync(gpu_ctx.h) == 0                                     # the error word was consumed
+    a = np.arange(12, dtype=np.float32).reshape(3, 4)
+    out = Dev(gpu_ctx, shape=(3, 3))
+    call(gpu_ctx, "nrs_gemm", 0, 1, 3, 3, 4, Dev(gpu_ctx, a), Dev(gpu_ctx, a), out, None, 0, 0.0)
+    assert np.allclose(out.get(), a @ a.T)
