@@ -246,6 +246,7 @@ thin_n_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
 #pragma unroll
   for (int j = 0; j < kThinN; ++j) acc[j] = 0.0f;
   const float* ar = a + (size_t)row * k;
+#pragma unroll 4
   for (int kk = lane; kk < k; kk += 32) {
     const float av = ar[kk];
 #pragma unroll
@@ -284,7 +285,8 @@ thin_n_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
   for (int j = 0; j < kThinN; ++j) acc[j] = 0.0f;
   const int per = (k + 7) / 8, k0 = warp * per, k1 = min(k, k0 + per);
   if (row < m)
-    for (int kk = k0; kk < k1; ++kk) {
+#pragma unroll 8
+    for (int kk = k0; kk < k1; ++kk) {   // unrolled so that several rows of A and B are in flight
       const float av = a[(size_t)kk * m + row];
 #pragma unroll
       for (int j = 0; j < kThinN; ++j)
