@@ -236,6 +236,19 @@ int nrs_embedding_bwd(nrs_ctx* ctx, const float* g, const int32_t* idx, float* d
  * reference has no mask).  backward == 0: y = (j > i) ? -1e30 : x;
  * backward != 0: y (+)= (j > i) ? 0 : x. */
 int nrs_causal_mask(nrs_ctx* ctx, const float* x, float* y, int batch, int s, int backward, int accumulate);
+/* Fused attention core for short sequences (nrs_attention_supported: seq <= 128, d_head <= 32).
+ * q, k, v, out, dout, dq, dk, dv: [batch, seq, heads*d_head] (head h = columns [h*d_head, (h+1)*d_head));
+ * probs: [batch*heads, seq, seq], written by the forward pass and read by the backward pass.
+ *   out = softmax(q k^T / sqrt(d_head), masked above the diagonal when causal) v     per (batch, head)
+ * i.e. src/cuda/nn/attention.rs:23-32 applied to every head of src/cuda/nn/multihead.rs:57-85 at once,
+ * without the slice / transpose / scale / concat passes.  The backward pass writes (acc_* == 0) or
+ * adds to (acc_* != 0) dq, dk, dv.  Deterministic. */
+int nrs_attention_supported(int seq, int d_head);
+int nrs_attention_fwd(nrs_ctx* ctx, const float* q, const float* k, const float* v, float* out, float* probs, int batch,
+                      int seq, int heads, int d_head, int causal);
+int nrs_attention_bwd(nrs_ctx* ctx, const float* q, const float* k, const float* v, const float* probs, const float* dout,
+                      float* dq, float* dk, float* dv, int batch, int seq, int heads, int d_head, int acc_q, int acc_k,
+                      int acc_v);
 /* Head split / merge for multi-head attention: to_heads != 0 maps x[batch, s, heads*d_head] to
  * y[batch*heads, s, d_head] (head h = column slice [h*d_head, (h+1)*d_head), exactly the slices
  * src/nn/multihead.rs:94-107 takes one by one); to_heads == 0 is the inverse, i.e. the

@@ -33,8 +33,45 @@ NodeP causal_mask(const NodeP& scores) {
   return out;
 }
 
+// softmax(q k^T / sqrt(d_head)) v for every head of [batch, seq, heads*d_head] tensors in one kernel
+// (shapes inside nrs_attention_supported only).
+static NodeP fused_attention(const NodeP& q, const NodeP& k, const NodeP& v, size_t heads, bool causal) {
+  nrs_ctx* ctx = q->ctx;
+  const size_t batch = q->shape[0], seq = q->shape[1], d = q->shape[2], d_head = d / heads;
+  if (k->shape != q->shape || v->shape != q->shape) fail(NRS_ERR_SHAPE, "cuda attention: q, k, v shapes differ");
+  NodeP out = make_result(ctx, q->shape, {q, k, v});
+  void* probs = nullptr;
+  check(ctx, nrs_alloc(ctx, std::max<size_t>(1, batch * heads * seq * seq) * sizeof(float), 0, &probs));
+  out->saved.push_back(probs);
+  check(ctx, nrs_attention_fwd(ctx, q->data, k->data, v->data, out->data, (float*)probs, (int)batch, (int)seq, (int)heads,
+                               (int)d_head, causal ? 1 : 0));
+  Node* self = out.get();
+  out->backward_fn = [self, q, k, v, probs, batch, seq, heads, d_head]() {
+    nrs_ctx* ctx = self->ctx;
+    const float* g = grad_view(self);
+    // a tensor that needs no gradient still gets a scratch target: the kernel computes all three
+    const size_t len = self->len();
+    auto target = [&](const NodeP& n, float** scratch) {
+      if (n->requires_grad) return grad_slot(n);
+      void* p = nullptr;
+      check(ctx, nrs_alloc(ctx, std::max<size_t>(1, len) * sizeof(float), 0, &p));
+      *scratch = (float*)p;
+      return GradSlot{(float*)p, 0};
+    };
+    float *sq = nullptr, *sk = nullptr, *sv = nullptr;
+    GradSlot tq = target(q, &sq), tk = target(k, &sk), tv = target(v, &sv);
+    check(ctx, nrs_attention_bwd(ctx, q->data, k->data, v->data, (const float*)probs, g, tq.ptr, tk.ptr, tv.ptr, (int)batch,
+                                 (int)seq, (int)heads, (int)d_head, tq.accumulate, tk.accumulate, tv.accumulate));
+    for (float* s : {sq, sk, sv})
+      if (s) nrs_free(ctx, s);
+  };
+  return out;
+}
+
 NodeP attention_batch(const NodeP& q, const NodeP& k, const NodeP& v, bool causal) {
   if (!q || q->shape.size() != 3) fail(NRS_ERR_SHAPE, "cuda attention_batch: q must be [batch, seq, d_head]");
+  if (k && v && k->on_gpu() && v->on_gpu() && q->on_gpu() && nrs_attention_supported((int)q->shape[1], (int)q->shape[2]))
+    return fused_attention(q, k, v, 1, causal);
   const float scale_factor = 1.0f / std::sqrt((float)q->shape[2]);
   NodeP scores = scale(bmm(q, transpose(k)), scale_factor);
   if (causal) scores = causal_mask(scores);
@@ -151,6 +188,8 @@ NodeP MultiHeadAttention::forward_batch(const NodeP& x) const {
   // concatenates (multihead.rs:94-107).  The same arithmetic in one pass: heads become extra
   // batch entries, attention_batch runs once over [batch*heads, seq, d_head].
   const size_t d_head = d_model / num_heads;
+  if (nrs_attention_supported((int)seq, (int)d_head))   // short sequences: the whole core in one kernel, heads in place
+    return reshape(matmul(reshape(fused_attention(q, k, v, num_heads, causal), {batch * seq, d}), w_o), {batch, seq, d});
   auto split = [&](const NodeP& t) { return permute_heads(t, batch, seq, num_heads, d_head, true); };
   NodeP attended = attention_batch(split(q), split(k), split(v), causal);
   NodeP concat = permute_heads(attended, batch, seq, num_heads, d_head, false);

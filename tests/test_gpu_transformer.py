@@ -77,7 +77,7 @@ def test_attention_batch(gpu_ctx, oracle64, causal):
     # tests/attention_batch_test.rs shapes, plus the LM config's head shape [b*?, 128, 32]
     g = og.Graph(oracle64)
     rng = np.random.default_rng(1)
-    for b, s, d in [(2, 4, 8), (3, 128, 32)]:
+    for b, s, d in [(2, 4, 8), (3, 128, 32), (2, 20, 48), (2, 160, 16)]:   # the last two: outside the fused kernel's range
         q, k, v = (rng.standard_normal((b, s, d)).astype(np.float32) for _ in range(3))
         cq, ck, cv = og.Node(q), og.Node(k), og.Node(v)
         cout = g.attention_batch(cq, ck, cv, causal)
@@ -94,7 +94,7 @@ def test_attention_batch(gpu_ctx, oracle64, causal):
 
 
 @pytest.mark.parametrize("act,causal", [("relu", False), ("gelu", True)])
-@pytest.mark.parametrize("shape", [(2, 4, 8, 2, 16), (4, 32, 64, 8, 256)])
+@pytest.mark.parametrize("shape", [(2, 4, 8, 2, 16), (4, 32, 64, 8, 256), (2, 8, 128, 2, 64), (2, 130, 32, 4, 32)])  # last two: batched-head path
 def test_transformer_block(gpu_ctx, oracle64, act, causal, shape):
     # tests/cuda_transformer_test.rs:19-27 (batch 2, seq 4, d 8, 2 heads, ff 16), bar 3e-3 absolute there
     B, S, D, H, FF = shape
