@@ -42,6 +42,7 @@ __device__ __forceinline__ void axpy32(float (&a)[kMaxDh], float s_, const float
 __global__ void __launch_bounds__(256)
 attn_fwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                 float* __restrict__ out, float* __restrict__ probs, int S, int H, int dh, int causal, float scale) {
+  NRS_PDL_PROLOGUE();
   __shared__ __align__(16) float Ks[kMaxSeq * kLd];
   __shared__ __align__(16) float Vs[kMaxSeq * kLd];
   const int tid = threadIdx.x;
@@ -108,6 +109,7 @@ __global__ void __launch_bounds__(256)
 attn_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                 const float* __restrict__ probs, const float* __restrict__ dout, float* dq, float* dk, float* dv, int S,
                 int H, int dh, float scale, int acc_q, int acc_k, int acc_v) {
+  NRS_PDL_PROLOGUE();
   extern __shared__ __align__(16) float sm[];
   float* Qs = sm;                       // [S][kLd]
   float* Ks = Qs + kMaxSeq * kLd;
@@ -230,7 +232,7 @@ int nrs_attention_fwd(nrs_ctx* ctx, const float* q, const float* k, const float*
   if (batch == 0) return NRS_OK;
   NRS_REQUIRE(ctx, q && k && v && out && probs, NRS_ERR_ARG, "nrs_attention_fwd: null tensor");
   NRS_REQUIRE(ctx, (long)batch * heads <= 2147483647L, NRS_ERR_UNSUPPORTED, "nrs_attention_fwd: too many (batch, head) pairs");
-  attn_fwd_kernel<<<(unsigned)(batch * heads), 256, 0, ctx->stream>>>(q, k, v, out, probs, seq, heads, d_head, causal,
+  NRS_PDL_LAUNCH(attn_fwd_kernel, (unsigned)(batch * heads), 256, 0, ctx->stream, q, k, v, out, probs, seq, heads, d_head, causal,
                                                                       1.0f / sqrtf((float)d_head));
   NRS_LAUNCHED(ctx);
   return NRS_OK;
@@ -250,7 +252,7 @@ int nrs_attention_bwd(nrs_ctx* ctx, const float* q, const float* k, const float*
     NRS_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwdSmem));
     attr_set = true;
   }
-  attn_bwd_kernel<<<(unsigned)(batch * heads), 256, kBwdSmem, ctx->stream>>>(q, k, v, probs, dout, dq, dk, dv, seq, heads, d_head,
+  NRS_PDL_LAUNCH(attn_bwd_kernel, (unsigned)(batch * heads), 256, kBwdSmem, ctx->stream, q, k, v, probs, dout, dq, dk, dv, seq, heads, d_head,
                                                                                1.0f / sqrtf((float)d_head), acc_q, acc_k, acc_v);
   NRS_LAUNCHED(ctx);
   return NRS_OK;

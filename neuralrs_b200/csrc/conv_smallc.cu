@@ -117,6 +117,7 @@ template <int CI, int KS>
 __global__ void __launch_bounds__(256)
 smallc_patch_planes_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo, int n, int h,
                            int wd, int pad, int oh, int ow) {
+  NRS_PDL_PROLOGUE();
   constexpr int K = CI * KS * KS;
   static_assert(K <= 32, "patch must fit one 32-channel block");
   __shared__ __align__(16) float tiles[8][32 * kTileLd];
@@ -159,6 +160,7 @@ smallc_patch_planes_kernel(const float* __restrict__ x, float* __restrict__ hi, 
 // dw[co][k] (+)= wide[co][k] for k < K (wide rows are 32 long).
 __global__ void __launch_bounds__(256)
 smallc_narrow_kernel(const float* __restrict__ wide, float* __restrict__ dw, int co, int K, int accumulate) {
+  NRS_PDL_PROLOGUE();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= co * K) return;
   const int c = idx / K, k = idx - c * K;
@@ -295,6 +297,7 @@ int run_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, i
 // wide[co][32] = w[co][K] padded with zeros (the 32-"channel" 1x1 weights of the patch formulation).
 __global__ void __launch_bounds__(256)
 smallc_widen_kernel(const float* __restrict__ w, float* __restrict__ wide, int co, int K) {
+  NRS_PDL_PROLOGUE();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= co * 32) return;
   const int c = idx >> 5, k = idx & 31;
@@ -307,7 +310,7 @@ int launch_patches(nrs_ctx* ctx, const float* x, float* hi, float* lo, int n, in
   size_t blocks = (pixels + 255) / 256;
   const size_t cap = (size_t)ctx->sm_count * 16;
   if (blocks > cap) blocks = cap;
-  smallc_patch_planes_kernel<CI, KS><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, hi, lo, n, h, wd, pad, oh, ow);
+  NRS_PDL_LAUNCH((smallc_patch_planes_kernel<CI, KS>), (unsigned)blocks, 256, 0, ctx->stream, x, hi, lo, n, h, wd, pad, oh, ow);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -359,7 +362,7 @@ int run_wgrad_tc(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n
     ctx->plane_hints.erase(phi);
   }
   if (st == NRS_OK) {
-    smallc_narrow_kernel<<<nrs_blocks((size_t)co * K, 256), 256, 0, ctx->stream>>>((const float*)wide, dw, co, K, accumulate);
+    NRS_PDL_LAUNCH(smallc_narrow_kernel, nrs_blocks((size_t)co * K, 256), 256, 0, ctx->stream, (const float*)wide, dw, co, K, accumulate);
     ctx->launches++;
     if (cudaGetLastError() != cudaSuccess) st = NRS_ERR_CUDA;
   }
@@ -383,7 +386,7 @@ int run_fwd_tc(nrs_ctx* ctx, const float* x, const float* w, const float* b, flo
   void* wide = nullptr;
   st = nrs_alloc(ctx, (size_t)co * 32 * sizeof(float), 0, &wide);
   if (st == NRS_OK) {
-    smallc_widen_kernel<<<nrs_blocks((size_t)co * 32, 256), 256, 0, ctx->stream>>>(w, (float*)wide, co, K);
+    NRS_PDL_LAUNCH(smallc_widen_kernel, nrs_blocks((size_t)co * 32, 256), 256, 0, ctx->stream, w, (float*)wide, co, K);
     ctx->launches++;
     if (cudaGetLastError() != cudaSuccess) st = NRS_ERR_CUDA;
   }

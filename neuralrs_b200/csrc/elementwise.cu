@@ -24,6 +24,7 @@ __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_c
 template <class F, bool HasB, bool ReadOut>
 __global__ void __launch_bounds__(EW_THREADS)
 ew_kernel(const float* a, const float* b, float* out, size_t n, F f) {
+  NRS_PDL_PROLOGUE();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const bool vec = aligned16(a) && aligned16(out) && (!HasB || aligned16(b));
@@ -48,7 +49,7 @@ int launch_ew(nrs_ctx* ctx, const float* a, const float* b, float* out, size_t n
   size_t blocks = (n / 4 + EW_THREADS - 1) / EW_THREADS + 1;
   const size_t cap = (size_t)ctx->sm_count * 16;
   if (blocks > cap) blocks = cap;
-  ew_kernel<F, HasB, ReadOut><<<(unsigned)blocks, EW_THREADS, 0, ctx->stream>>>(a, b, out, n, f);
+  NRS_PDL_LAUNCH((ew_kernel<F, HasB, ReadOut>), (unsigned)blocks, EW_THREADS, 0, ctx->stream, a, b, out, n, f);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -81,6 +82,7 @@ struct FScale {
 __global__ void __launch_bounds__(EW_THREADS)
 bias_add_kernel(const float* __restrict__ a, const float* __restrict__ bias, float* __restrict__ out,
                 int rows, int cols) {
+  NRS_PDL_PROLOGUE();
   const size_t n = (size_t)rows * cols;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -103,6 +105,7 @@ bias_add_kernel(const float* __restrict__ a, const float* __restrict__ bias, flo
 __global__ void __launch_bounds__(256)
 colsum_kernel(const float* __restrict__ g, float* __restrict__ out, int rows, int cols, int row_splits,
               int accumulate, float* __restrict__ partial) {
+  NRS_PDL_PROLOGUE();
   __shared__ float sm[8][33];
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + lane;
@@ -124,6 +127,7 @@ colsum_kernel(const float* __restrict__ g, float* __restrict__ out, int rows, in
 }
 __global__ void colsum_fold_kernel(const float* __restrict__ partial, float* __restrict__ out, int cols,
                                    int row_splits, int accumulate) {
+  NRS_PDL_PROLOGUE();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
   float t = 0.0f;
@@ -138,6 +142,7 @@ __global__ void colsum_fold_kernel(const float* __restrict__ partial, float* __r
 __global__ void __launch_bounds__(256)
 chansum_kernel(const float* __restrict__ g, float* __restrict__ out, int n, int c, int plane, int splits,
                int accumulate, float* __restrict__ partial) {
+  NRS_PDL_PROLOGUE();
   __shared__ float sm[8];
   const int ch = blockIdx.x, split = blockIdx.y;
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
@@ -181,6 +186,7 @@ chansum_kernel(const float* __restrict__ g, float* __restrict__ out, int n, int 
 // Batched transpose through a padded 32x32 shared tile: coalesced both ways.
 __global__ void __launch_bounds__(256)
 transpose_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int cols, int accumulate) {
+  NRS_PDL_PROLOGUE();
   __shared__ float tile[32][33];
   const size_t off = (size_t)blockIdx.z * rows * cols;
   const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
@@ -204,6 +210,7 @@ transpose_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, i
 __global__ void __launch_bounds__(EW_THREADS)
 block_copy_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int width, int src_ld,
                   int sc0, int dst_ld, int dc0, int accumulate) {
+  NRS_PDL_PROLOGUE();
   const size_t n = (size_t)rows * width;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -222,7 +229,7 @@ int launch_block_copy(nrs_ctx* ctx, const float* src, float* dst, int rows, int 
   size_t blocks = (n + EW_THREADS - 1) / EW_THREADS;
   const size_t cap = (size_t)ctx->sm_count * 16;
   if (blocks > cap) blocks = cap;
-  block_copy_kernel<<<(unsigned)blocks, EW_THREADS, 0, ctx->stream>>>(src, dst, rows, width, src_ld, sc0,
+  NRS_PDL_LAUNCH(block_copy_kernel, (unsigned)blocks, EW_THREADS, 0, ctx->stream, src, dst, rows, width, src_ld, sc0,
                                                                       dst_ld, dc0, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
@@ -247,7 +254,7 @@ int nrs_bias_add(nrs_ctx* ctx, const float* a, const float* bias, float* out, in
   size_t blocks = (n / 4 + EW_THREADS - 1) / EW_THREADS + 1;
   const size_t cap = (size_t)ctx->sm_count * 16;
   if (blocks > cap) blocks = cap;
-  bias_add_kernel<<<(unsigned)blocks, EW_THREADS, 0, ctx->stream>>>(a, bias, out, rows, cols);
+  NRS_PDL_LAUNCH(bias_add_kernel, (unsigned)blocks, EW_THREADS, 0, ctx->stream, a, bias, out, rows, cols);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -278,10 +285,10 @@ int nrs_sum_axis0(nrs_ctx* ctx, const float* g, float* out, int rows, int cols, 
     if (st != NRS_OK) return st;
     partial = (float*)ws;
   }
-  colsum_kernel<<<dim3(col_blocks, splits), 256, 0, ctx->stream>>>(g, out, rows, cols, splits, accumulate, partial);
+  NRS_PDL_LAUNCH(colsum_kernel, dim3(col_blocks, splits), 256, 0, ctx->stream, g, out, rows, cols, splits, accumulate, partial);
   NRS_LAUNCHED(ctx);
   if (splits > 1) {
-    colsum_fold_kernel<<<nrs_blocks(cols, 256), 256, 0, ctx->stream>>>(partial, out, cols, splits, accumulate);
+    NRS_PDL_LAUNCH(colsum_fold_kernel, nrs_blocks(cols, 256), 256, 0, ctx->stream, partial, out, cols, splits, accumulate);
     NRS_LAUNCHED(ctx);
   }
   return NRS_OK;
@@ -306,10 +313,10 @@ int nrs_channel_sum(nrs_ctx* ctx, const float* g, float* out, int n, int c, int 
     if (st != NRS_OK) return st;
     partial = (float*)ws;
   }
-  chansum_kernel<<<dim3(c, splits), 256, 0, ctx->stream>>>(g, out, n, c, plane, splits, accumulate, partial);
+  NRS_PDL_LAUNCH(chansum_kernel, dim3(c, splits), 256, 0, ctx->stream, g, out, n, c, plane, splits, accumulate, partial);
   NRS_LAUNCHED(ctx);
   if (splits > 1) {
-    colsum_fold_kernel<<<nrs_blocks(c, 256), 256, 0, ctx->stream>>>(partial, out, c, splits, accumulate);
+    NRS_PDL_LAUNCH(colsum_fold_kernel, nrs_blocks(c, 256), 256, 0, ctx->stream, partial, out, c, splits, accumulate);
     NRS_LAUNCHED(ctx);
   }
   return NRS_OK;
@@ -355,7 +362,7 @@ int nrs_transpose(nrs_ctx* ctx, const float* x, float* y, int batch, int rows, i
   NRS_REQUIRE(ctx, x && y, NRS_ERR_ARG, "nrs_transpose: null tensor");
   NRS_REQUIRE(ctx, batch <= 65535 && (rows + 31) / 32 <= 65535, NRS_ERR_UNSUPPORTED, "nrs_transpose: grid too large");
   dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch);
-  transpose_kernel<<<grid, 256, 0, ctx->stream>>>(x, y, rows, cols, accumulate);
+  NRS_PDL_LAUNCH(transpose_kernel, grid, 256, 0, ctx->stream, x, y, rows, cols, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -450,10 +457,10 @@ extern "C" int nrs_sum_axis0_static(nrs_ctx* ctx, const float* g, float* out, in
   }
   // Every partial the fold reads is written by the first kernel, so stale contents of the
   // shared scratch never need clearing.
-  colsum_kernel<<<dim3(col_blocks, splits), 256, 0, ctx->stream>>>(g, out, rows, cols, splits, accumulate, scratch);
+  NRS_PDL_LAUNCH(colsum_kernel, dim3(col_blocks, splits), 256, 0, ctx->stream, g, out, rows, cols, splits, accumulate, scratch);
   NRS_LAUNCHED(ctx);
   if (splits > 1) {
-    colsum_fold_kernel<<<nrs_blocks(cols, 256), 256, 0, ctx->stream>>>(scratch, out, cols, splits, accumulate);
+    NRS_PDL_LAUNCH(colsum_fold_kernel, nrs_blocks(cols, 256), 256, 0, ctx->stream, scratch, out, cols, splits, accumulate);
     NRS_LAUNCHED(ctx);
   }
   return NRS_OK;

@@ -25,6 +25,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 __global__ void __launch_bounds__(256)
 ce_rows_kernel(const float* __restrict__ logits, const float* __restrict__ target,
                float* __restrict__ row_loss, float* __restrict__ grad, int batch, int classes, float inv_div) {
+  NRS_PDL_PROLOGUE();
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   for (int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5); b < batch; b += gridDim.x * warps_per_block) {
@@ -53,6 +54,7 @@ ce_rows_kernel(const float* __restrict__ logits, const float* __restrict__ targe
 // loss_dev[0] = (sum_b row_loss[b]) * inv_div, one block, fixed summation tree.
 __global__ void __launch_bounds__(1024)
 ce_mean_kernel(const float* __restrict__ row_loss, float* __restrict__ loss_dev, int batch, float inv_div) {
+  NRS_PDL_PROLOGUE();
   __shared__ float sm[32];
   float s = 0.0f;
   for (int i = threadIdx.x; i < batch; i += blockDim.x) s += row_loss[i];
@@ -85,10 +87,10 @@ int run_ce(nrs_ctx* ctx, const char* who, const float* logits, const float* targ
   const float inv_div = 1.0f / (float)divisor;
   int blocks = (batch + 7) / 8;
   if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
-  ce_rows_kernel<<<blocks, 256, 0, ctx->stream>>>(logits, target, rl, grad, batch, classes, inv_div);
+  NRS_PDL_LAUNCH(ce_rows_kernel, blocks, 256, 0, ctx->stream, logits, target, rl, grad, batch, classes, inv_div);
   NRS_LAUNCHED(ctx);
   if (loss_dev) {
-    ce_mean_kernel<<<1, 1024, 0, ctx->stream>>>(rl, loss_dev, batch, inv_div);
+    NRS_PDL_LAUNCH(ce_mean_kernel, 1, 1024, 0, ctx->stream, rl, loss_dev, batch, inv_div);
     NRS_LAUNCHED(ctx);
   }
   return NRS_OK;

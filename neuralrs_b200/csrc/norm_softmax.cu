@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(256)
 ln_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
               float* __restrict__ y, float* __restrict__ xhat, float* __restrict__ istd_out, int rows, int f,
               float eps) {
+  NRS_PDL_PROLOGUE();
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
     const float* row = x + (size_t)r * f;
@@ -45,6 +46,7 @@ ln_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma, cons
 __global__ void __launch_bounds__(256)
 ln_dx_kernel(const float* __restrict__ g, const float* __restrict__ xhat, const float* __restrict__ istd,
              const float* __restrict__ gamma, float* dx, int rows, int f, int accumulate) {
+  NRS_PDL_PROLOGUE();
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   const float nf = (float)f;
   for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
@@ -70,6 +72,7 @@ ln_dx_kernel(const float* __restrict__ g, const float* __restrict__ xhat, const 
 __global__ void __launch_bounds__(256)
 ln_param_kernel(const float* __restrict__ g, const float* __restrict__ xhat, float* __restrict__ partial,
                 int rows, int f, int splits) {
+  NRS_PDL_PROLOGUE();
   __shared__ float sg[8][33], sb[8][33];
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + lane, split = blockIdx.y;
@@ -95,6 +98,7 @@ ln_param_kernel(const float* __restrict__ g, const float* __restrict__ xhat, flo
 }
 __global__ void ln_param_fold_kernel(const float* __restrict__ partial, float* dgamma, float* dbeta, int f,
                                      int splits, int accumulate) {
+  NRS_PDL_PROLOGUE();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= f) return;
   float tg = 0.0f, tb = 0.0f;
@@ -108,6 +112,7 @@ __global__ void ln_param_fold_kernel(const float* __restrict__ partial, float* d
 
 __global__ void __launch_bounds__(256)
 softmax_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int width) {
+  NRS_PDL_PROLOGUE();
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
     const float* row = x + (size_t)r * width;
@@ -124,6 +129,7 @@ softmax_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int rows,
 __global__ void __launch_bounds__(256)
 softmax_bwd_kernel(const float* __restrict__ y, const float* __restrict__ g, float* dx, int rows, int width,
                    int accumulate) {
+  NRS_PDL_PROLOGUE();
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
     const size_t st = (size_t)r * width;
@@ -153,7 +159,7 @@ int nrs_layernorm_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const fl
   NRS_REQUIRE(ctx, rows >= 0 && f > 0, NRS_ERR_SHAPE, "nrs_layernorm_fwd: bad shape [%d,%d]", rows, f);
   if (rows == 0) return NRS_OK;
   NRS_REQUIRE(ctx, x && gamma && beta && y, NRS_ERR_ARG, "nrs_layernorm_fwd: null tensor");
-  ln_fwd_kernel<<<row_grid(ctx, rows), 256, 0, ctx->stream>>>(x, gamma, beta, y, xhat, istd, rows, f, eps);
+  NRS_PDL_LAUNCH(ln_fwd_kernel, row_grid(ctx, rows), 256, 0, ctx->stream, x, gamma, beta, y, xhat, istd, rows, f, eps);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -174,7 +180,7 @@ int nrs_layernorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const flo
   }
   NRS_REQUIRE(ctx, g && xhat && istd && gamma, NRS_ERR_ARG, "nrs_layernorm_bwd: null tensor");
   if (dx) {
-    ln_dx_kernel<<<row_grid(ctx, rows), 256, 0, ctx->stream>>>(g, xhat, istd, gamma, dx, rows, f, accumulate_dx);
+    NRS_PDL_LAUNCH(ln_dx_kernel, row_grid(ctx, rows), 256, 0, ctx->stream, g, xhat, istd, gamma, dx, rows, f, accumulate_dx);
     NRS_LAUNCHED(ctx);
   }
   if (dgamma) {
@@ -186,9 +192,9 @@ int nrs_layernorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const flo
     void* ws = nullptr;
     const int st = nrs_workspace(ctx, (size_t)splits * 2 * f * sizeof(float), &ws);
     if (st != NRS_OK) return st;
-    ln_param_kernel<<<dim3(col_blocks, splits), 256, 0, ctx->stream>>>(g, xhat, (float*)ws, rows, f, splits);
+    NRS_PDL_LAUNCH(ln_param_kernel, dim3(col_blocks, splits), 256, 0, ctx->stream, g, xhat, (float*)ws, rows, f, splits);
     NRS_LAUNCHED(ctx);
-    ln_param_fold_kernel<<<nrs_blocks(f, 256), 256, 0, ctx->stream>>>((const float*)ws, dgamma, dbeta, f, splits,
+    NRS_PDL_LAUNCH(ln_param_fold_kernel, nrs_blocks(f, 256), 256, 0, ctx->stream, (const float*)ws, dgamma, dbeta, f, splits,
                                                                       accumulate_params);
     NRS_LAUNCHED(ctx);
   }
@@ -200,7 +206,7 @@ int nrs_softmax_fwd(nrs_ctx* ctx, const float* x, float* y, int rows, int width)
   NRS_REQUIRE(ctx, rows >= 0 && width > 0, NRS_ERR_SHAPE, "nrs_softmax_fwd: bad shape [%d,%d]", rows, width);
   if (rows == 0) return NRS_OK;
   NRS_REQUIRE(ctx, x && y, NRS_ERR_ARG, "nrs_softmax_fwd: null tensor");
-  softmax_fwd_kernel<<<row_grid(ctx, rows), 256, 0, ctx->stream>>>(x, y, rows, width);
+  NRS_PDL_LAUNCH(softmax_fwd_kernel, row_grid(ctx, rows), 256, 0, ctx->stream, x, y, rows, width);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -210,7 +216,7 @@ int nrs_softmax_bwd(nrs_ctx* ctx, const float* y, const float* g, float* dx, int
   NRS_REQUIRE(ctx, rows >= 0 && width > 0, NRS_ERR_SHAPE, "nrs_softmax_bwd: bad shape [%d,%d]", rows, width);
   if (rows == 0) return NRS_OK;
   NRS_REQUIRE(ctx, y && g && dx, NRS_ERR_ARG, "nrs_softmax_bwd: null tensor");
-  softmax_bwd_kernel<<<row_grid(ctx, rows), 256, 0, ctx->stream>>>(y, g, dx, rows, width, accumulate);
+  NRS_PDL_LAUNCH(softmax_bwd_kernel, row_grid(ctx, rows), 256, 0, ctx->stream, y, g, dx, rows, width, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }

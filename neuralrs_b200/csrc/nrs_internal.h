@@ -136,6 +136,36 @@ int nrs_check_device_error(nrs_ctx* ctx);
                       cudaGetErrorString(e__));                                          \
   } while (0)
 
+// Programmatic dependent launch.  A kernel launched through nrs_pdl_launch may be scheduled while
+// the kernel before it in the stream is still running (as SMs free up in its last wave), so that its
+// launch latency and prologue overlap with that kernel's tail; it must execute NRS_PDL_WAIT() before
+// its first global-memory access — the wait returns once the preceding kernel has completed and its
+// writes are visible.  NRS_PDL_TRIGGER() lets the NEXT kernel start the same way; every CTA of a grid
+// has to issue it (or exit) before that happens, so only a grid's last wave is ever shared.
+#define NRS_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
+#define NRS_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+#define NRS_PDL_PROLOGUE() \
+  do { NRS_PDL_TRIGGER(); NRS_PDL_WAIT(); } while (0)
+
+template <class... P, class... A>
+inline cudaError_t nrs_pdl_launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+// kernel<<<grid, block, smem, stream>>>(args...) as a programmatic dependent launch.  The kernel
+// expression goes in parentheses when its template arguments contain commas.
+#define NRS_PDL_LAUNCH(kernel, grid, block, smem, stream, ...) \
+  (void)nrs_pdl_launch(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
+
 static inline unsigned nrs_blocks(size_t work, unsigned per_block) {
   return (unsigned)((work + per_block - 1) / per_block);
 }

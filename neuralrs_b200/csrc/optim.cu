@@ -24,6 +24,7 @@ __device__ __forceinline__ void adamw_one(float& p, float g, float& m, float& v,
 __global__ void __launch_bounds__(256)
 adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
              size_t n, AdamWArgs a) {
+  NRS_PDL_PROLOGUE();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
@@ -59,7 +60,7 @@ extern "C" int nrs_adamw_step(nrs_ctx* ctx, float* p, const float* grad, float* 
   if (blocks > cap) blocks = cap;
   NrsProfScope prof(ctx, NRS_PROF_ADAMW, 28.0 * (double)n);
   const AdamWArgs a{lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale};
-  adamw_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p, grad, m, v, n, a);
+  NRS_PDL_LAUNCH(adamw_kernel, (unsigned)blocks, 256, 0, ctx->stream, p, grad, m, v, n, a);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }

@@ -10,6 +10,7 @@ namespace {
 __global__ void __launch_bounds__(256)
 maxpool2x2_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ argmax,
                       size_t planes, int h, int w, int oh, int ow) {
+  NRS_PDL_PROLOGUE();
   const size_t total = planes * oh * ow;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const bool vec = (w & 1) == 0 && ((reinterpret_cast<uintptr_t>(x) & 7) == 0);
@@ -39,6 +40,7 @@ maxpool2x2_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_
 __global__ void __launch_bounds__(256)
 maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ argmax,
                    size_t planes, int h, int w, int k, int s, int oh, int ow) {
+  NRS_PDL_PROLOGUE();
   const size_t total = planes * oh * ow;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
@@ -65,6 +67,7 @@ maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* 
 __global__ void __launch_bounds__(256)
 maxpool_bwd_gather_kernel(const float* __restrict__ g, const int32_t* __restrict__ argmax, float* dx,
                           size_t planes, int h, int w, int k, int oh, int ow, int accumulate) {
+  NRS_PDL_PROLOGUE();
   const size_t total = planes * h * w;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
@@ -84,6 +87,7 @@ maxpool_bwd_gather_kernel(const float* __restrict__ g, const int32_t* __restrict
 
 __global__ void __launch_bounds__(256)
 maxpool_bwd_scatter_kernel(const float* __restrict__ g, const int32_t* __restrict__ argmax, float* dx, size_t total) {
+  NRS_PDL_PROLOGUE();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride)
     atomicAdd(&dx[argmax[idx]], g[idx]);
@@ -118,9 +122,9 @@ int nrs_maxpool_fwd(nrs_ctx* ctx, const float* x, float* y, int32_t* argmax, int
   if (total == 0) return NRS_OK;
   NRS_REQUIRE(ctx, x && y, NRS_ERR_ARG, "nrs_maxpool_fwd: null tensor");
   if (k == 2 && stride == 2)
-    maxpool2x2_fwd_kernel<<<grid_for(ctx, total), 256, 0, ctx->stream>>>(x, y, argmax, planes, h, w, oh, ow);
+    NRS_PDL_LAUNCH(maxpool2x2_fwd_kernel, grid_for(ctx, total), 256, 0, ctx->stream, x, y, argmax, planes, h, w, oh, ow);
   else
-    maxpool_fwd_kernel<<<grid_for(ctx, total), 256, 0, ctx->stream>>>(x, y, argmax, planes, h, w, k, stride, oh, ow);
+    NRS_PDL_LAUNCH(maxpool_fwd_kernel, grid_for(ctx, total), 256, 0, ctx->stream, x, y, argmax, planes, h, w, k, stride, oh, ow);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -135,12 +139,12 @@ int nrs_maxpool_bwd(nrs_ctx* ctx, const float* g, const int32_t* argmax, float* 
   if (in_total == 0) return NRS_OK;
   NRS_REQUIRE(ctx, g && argmax && dx, NRS_ERR_ARG, "nrs_maxpool_bwd: null tensor");
   if (k == stride) {
-    maxpool_bwd_gather_kernel<<<grid_for(ctx, in_total), 256, 0, ctx->stream>>>(g, argmax, dx, planes, h, w, k,
+    NRS_PDL_LAUNCH(maxpool_bwd_gather_kernel, grid_for(ctx, in_total), 256, 0, ctx->stream, g, argmax, dx, planes, h, w, k,
                                                                                 oh, ow, accumulate);
     NRS_LAUNCHED(ctx);
   } else {
     if (!accumulate) NRS_CUDA(ctx, cudaMemsetAsync(dx, 0, in_total * sizeof(float), ctx->stream));
-    maxpool_bwd_scatter_kernel<<<grid_for(ctx, out_total), 256, 0, ctx->stream>>>(g, argmax, dx, out_total);
+    NRS_PDL_LAUNCH(maxpool_bwd_scatter_kernel, grid_for(ctx, out_total), 256, 0, ctx->stream, g, argmax, dx, out_total);
     NRS_LAUNCHED(ctx);
   }
   return NRS_OK;

@@ -36,6 +36,7 @@ struct LoadMap {
 template <class P>
 __global__ void __launch_bounds__(NTHREADS)
 igemm_kernel(const P p, const int splits, const int k_per_split, float* __restrict__ partial) {
+  NRS_PDL_PROLOGUE();
   __shared__ __align__(16) float As[2][BK][BM + PADM];
   __shared__ __align__(16) float Bs[2][BK][BN + PADM];
   using LA = LoadMap<P::kAContigM>;
@@ -141,6 +142,7 @@ igemm_kernel(const P p, const int splits, const int k_per_split, float* __restri
 template <class P>
 __global__ void __launch_bounds__(256)
 igemm_splitk_reduce(const P p, const int splits, const float* __restrict__ partial) {
+  NRS_PDL_PROLOGUE();
   const size_t per = (size_t)p.batches * p.M * p.N;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= per) return;
@@ -180,11 +182,11 @@ int run_igemm(nrs_ctx* ctx, const P& p, const char* who) {
     partial = (float*)ws;
   }
   dim3 grid((unsigned)tiles_m, (unsigned)tiles_n, (unsigned)(p.batches * splits));
-  igemm_kernel<P><<<grid, NTHREADS, 0, ctx->stream>>>(p, splits, k_per_split, partial);
+  NRS_PDL_LAUNCH((igemm_kernel<P>), grid, NTHREADS, 0, ctx->stream, p, splits, k_per_split, partial);
   NRS_LAUNCHED(ctx);
   if (splits > 1) {
     const size_t per = (size_t)p.batches * p.M * p.N;
-    igemm_splitk_reduce<P><<<nrs_blocks(per, 256), 256, 0, ctx->stream>>>(p, splits, partial);
+    NRS_PDL_LAUNCH((igemm_splitk_reduce<P>), nrs_blocks(per, 256), 256, 0, ctx->stream, p, splits, partial);
     NRS_LAUNCHED(ctx);
   }
   return NRS_OK;
@@ -218,6 +220,7 @@ template <bool TA, bool TB>
 __global__ void __launch_bounds__(256)
 thin_k_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c, const float* __restrict__ bias, int m,
               int n, int k, int act, float beta) {
+  NRS_PDL_PROLOGUE();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)m * n) return;
   const int col = (int)(idx % n);
@@ -239,6 +242,7 @@ template <bool TB>
 __global__ void __launch_bounds__(256)
 thin_n_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c, const float* __restrict__ bias, int m,
                    int n, int k, int act, float beta) {
+  NRS_PDL_PROLOGUE();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= m) return;
@@ -277,6 +281,7 @@ template <bool TB>
 __global__ void __launch_bounds__(256)
 thin_n_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c, const float* __restrict__ bias, int m,
                    int n, int k, int act, float beta) {
+  NRS_PDL_PROLOGUE();
   __shared__ float part[8][kThinN][33];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = blockIdx.x * 32 + lane;
@@ -318,18 +323,18 @@ int thin_gemm(nrs_ctx* ctx, int ta, int tb, int m, int n, int k, const float* a,
               const float* bias, int act, float beta) {
   if (k <= 16) {
     const unsigned blocks = nrs_blocks((size_t)m * n, 256);
-    if (!ta && !tb) thin_k_kernel<false, false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
-    else if (!ta && tb) thin_k_kernel<false, true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
-    else if (ta && !tb) thin_k_kernel<true, false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
-    else thin_k_kernel<true, true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+    if (!ta && !tb) NRS_PDL_LAUNCH((thin_k_kernel<false, false>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
+    else if (!ta && tb) NRS_PDL_LAUNCH((thin_k_kernel<false, true>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
+    else if (ta && !tb) NRS_PDL_LAUNCH((thin_k_kernel<true, false>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
+    else NRS_PDL_LAUNCH((thin_k_kernel<true, true>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
   } else if (!ta) {
     const unsigned blocks = nrs_blocks((size_t)m, 8);
-    if (tb) thin_n_rows_kernel<true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
-    else thin_n_rows_kernel<false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+    if (tb) NRS_PDL_LAUNCH((thin_n_rows_kernel<true>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
+    else NRS_PDL_LAUNCH((thin_n_rows_kernel<false>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
   } else {
     const unsigned blocks = nrs_blocks((size_t)m, 32);
-    if (tb) thin_n_cols_kernel<true><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
-    else thin_n_cols_kernel<false><<<blocks, 256, 0, ctx->stream>>>(a, b, c, bias, m, n, k, act, beta);
+    if (tb) NRS_PDL_LAUNCH((thin_n_cols_kernel<true>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
+    else NRS_PDL_LAUNCH((thin_n_cols_kernel<false>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
   }
   NRS_LAUNCHED(ctx);
   return NRS_OK;

@@ -113,6 +113,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(emit_bar + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  NRS_PDL_TRIGGER();   // the next kernel may be scheduled as this grid's SMs free up
 
   if (warp == 0 && lane == 0) {
     prefetch_tmap(&tm_a_hi);
@@ -132,6 +133,9 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above (barriers, tensor memory, descriptor prefetch) may overlap the tail of the kernel
+  // before this one in the stream; from here on its results are needed.
+  NRS_PDL_WAIT();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -327,6 +331,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
 template <class Policy>
 __global__ void __launch_bounds__(256)
 tc_splitk_reduce_kernel(const Policy pol, const SplitInfo sp) {
+  NRS_PDL_PROLOGUE();
   const size_t per = (size_t)sp.batches * sp.rows_total * sp.n_total;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= per) return;
@@ -418,12 +423,12 @@ int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, con
   const unsigned grid = (unsigned)(tmap.total < ctx->sm_count ? tmap.total : ctx->sm_count);
   // Planes can only be emitted by the direct epilogue; with a K-split the policy's store() writes them.
   const int emit = (Policy::kCanEmit && out_hi && sp.splits == 1) ? (out_lo && NPLANES == 2 ? 2 : 1) : 0;
-  tc_kernel<BN, NPLANES, Policy><<<grid, kThreads, kSmem, ctx->stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, out_hi ? *out_hi : ta_hi,
-                                                                         out_lo ? *out_lo : ta_hi, pol, sp, tmap, emit, err);
+  NRS_PDL_LAUNCH((tc_kernel<BN, NPLANES, Policy>), grid, kThreads, kSmem, ctx->stream, ta_hi, ta_lo, tb_hi, tb_lo,
+                 out_hi ? *out_hi : ta_hi, out_lo ? *out_lo : ta_hi, pol, sp, tmap, emit, err);
   NRS_LAUNCHED(ctx);
   if (sp.splits > 1) {
     const size_t per = (size_t)batches * sp.rows_total * n_total;
-    tc_splitk_reduce_kernel<Policy><<<nrs_blocks(per, 256), 256, 0, ctx->stream>>>(pol, sp);
+    NRS_PDL_LAUNCH((tc_splitk_reduce_kernel<Policy>), nrs_blocks(per, 256), 256, 0, ctx->stream, pol, sp);
     NRS_LAUNCHED(ctx);
   }
   return NRS_OK;

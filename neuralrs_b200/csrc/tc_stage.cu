@@ -13,6 +13,7 @@ template <bool SPLIT>
 __global__ void __launch_bounds__(256)
 stage_rows_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, int rows, int K,
                   int ldk, size_t src_bstride, size_t dst_bstride) {
+  NRS_PDL_PROLOGUE();
   const int b = blockIdx.y;
   src += b * src_bstride;
   hi += b * dst_bstride;
@@ -48,6 +49,7 @@ template <bool SPLIT>
 __global__ void __launch_bounds__(256)
 stage_transpose_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, int rows, int K,
                        int ldk, size_t src_bstride, size_t dst_bstride) {
+  NRS_PDL_PROLOGUE();
   __shared__ float tile[32][33];
   const int b = blockIdx.z;
   src += b * src_bstride;
@@ -79,6 +81,7 @@ template <bool SPLIT>
 __global__ void __launch_bounds__(256)
 stage_conv_weight_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int co_n, int ci_n,
                          int kh, int kw, int for_dgrad) {
+  NRS_PDL_PROLOGUE();
   const size_t total = (size_t)co_n * ci_n * kh * kw;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -116,6 +119,7 @@ __global__ void __launch_bounds__(256)
 stage_masked_kernel(const float* __restrict__ g, const float* __restrict__ y, const int32_t* __restrict__ argmax,
                     float* __restrict__ nchw_out, float* __restrict__ hi, float* __restrict__ lo, int c_n, int h,
                     int w, int k, int oh, int ow) {
+  NRS_PDL_PROLOGUE();
   __shared__ float tile[32][33];
   const int img = blockIdx.z, hw = h * w;
   const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
@@ -165,6 +169,7 @@ pool2_bwd_planes_kernel(const float* __restrict__ g, const float* __restrict__ p
                         float* __restrict__ nchw_out, float* __restrict__ hi, float* __restrict__ lo,
                         float* __restrict__ chan_partial /*[gridDim.x][c_n] per-block channel sums, or null*/, int n_img,
                         int c_n, int h, int w) {
+  NRS_PDL_PROLOGUE();
   __shared__ float tile[32][129];   // [channel][q*32 + position], q = 2*dy + dx inside the window
   __shared__ long long pix_base[32]; // linear index of each position's top-left pixel, -1 beyond the end
   const int oh = h >> 1, ow = w >> 1, ohw = oh * ow, hw = h * w;
@@ -233,6 +238,7 @@ template <bool SPLIT>
 __global__ void __launch_bounds__(256)
 pool2_fwd_planes_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ argmax,
                         float* __restrict__ hi, float* __restrict__ lo, int n_img, int c_n, int h, int w) {
+  NRS_PDL_PROLOGUE();
   __shared__ float tile[32][33];
   const int oh = h >> 1, ow = w >> 1, ohw = oh * ow, hw = h * w;
   const long total_pos = (long)n_img * ohw;
@@ -288,8 +294,8 @@ int nrs_tc_pool2_fwd_planes(nrs_ctx* ctx, const float* x, float* y, int32_t* arg
   const long blocks = ((long)n * (h / 2) * (w / 2) + 31) / 32;
   if (blocks > 2147483647L || (c + 31) / 32 > 65535) return NRS_ERR_UNSUPPORTED;
   dim3 grid((unsigned)blocks, (unsigned)((c + 31) / 32));
-  if (lo) pool2_fwd_planes_kernel<true><<<grid, 256, 0, ctx->stream>>>(x, y, argmax, hi, lo, n, c, h, w);
-  else pool2_fwd_planes_kernel<false><<<grid, 256, 0, ctx->stream>>>(x, y, argmax, hi, nullptr, n, c, h, w);
+  if (lo) NRS_PDL_LAUNCH((pool2_fwd_planes_kernel<true>), grid, 256, 0, ctx->stream, x, y, argmax, hi, lo, n, c, h, w);
+  else NRS_PDL_LAUNCH((pool2_fwd_planes_kernel<false>), grid, 256, 0, ctx->stream, x, y, argmax, hi, nullptr, n, c, h, w);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -305,18 +311,18 @@ int nrs_tc_stage_masked(nrs_ctx* ctx, int mode, const float* g, const float* y, 
   const bool split = lo != nullptr;
   if (mode == 1 && k == 2 && h % 2 == 0 && w % 2 == 0 && (long)n * (h / 2) * (w / 2) / 32 < 2147483647L) {
     dim3 pgrid((unsigned)(((long)n * (h / 2) * (w / 2) + 31) / 32), (unsigned)((c + 31) / 32));
-    if (split) pool2_bwd_planes_kernel<true><<<pgrid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, chan_partial, n, c, h, w);
-    else pool2_bwd_planes_kernel<false><<<pgrid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, chan_partial, n, c, h, w);
+    if (split) NRS_PDL_LAUNCH((pool2_bwd_planes_kernel<true>), pgrid, 256, 0, ctx->stream, g, y, argmax, nchw_out, hi, lo, chan_partial, n, c, h, w);
+    else NRS_PDL_LAUNCH((pool2_bwd_planes_kernel<false>), pgrid, 256, 0, ctx->stream, g, y, argmax, nchw_out, hi, lo, chan_partial, n, c, h, w);
     NRS_LAUNCHED(ctx);
     if (chan_partial && chan_partial_rows) *chan_partial_rows = (int)pgrid.x;
     return NRS_OK;
   }
   if (mode == 0) {
-    if (split) stage_masked_kernel<true, 0><<<grid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
-    else stage_masked_kernel<false, 0><<<grid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
+    if (split) NRS_PDL_LAUNCH((stage_masked_kernel<true, 0>), grid, 256, 0, ctx->stream, g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
+    else NRS_PDL_LAUNCH((stage_masked_kernel<false, 0>), grid, 256, 0, ctx->stream, g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
   } else {
-    if (split) stage_masked_kernel<true, 1><<<grid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
-    else stage_masked_kernel<false, 1><<<grid, 256, 0, ctx->stream>>>(g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
+    if (split) NRS_PDL_LAUNCH((stage_masked_kernel<true, 1>), grid, 256, 0, ctx->stream, g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
+    else NRS_PDL_LAUNCH((stage_masked_kernel<false, 1>), grid, 256, 0, ctx->stream, g, y, argmax, nchw_out, hi, lo, c, h, w, k, oh, ow);
   }
   NRS_LAUNCHED(ctx);
   return NRS_OK;
@@ -331,13 +337,13 @@ int nrs_tc_stage(nrs_ctx* ctx, const float* src, float* hi, float* lo, int rows,
     if (blocks > cap) blocks = cap;
     if (batch > 65535) return NRS_ERR_UNSUPPORTED;
     dim3 grid((unsigned)blocks, (unsigned)batch);
-    if (lo) stage_rows_kernel<true><<<grid, 256, 0, ctx->stream>>>(src, hi, lo, rows, K, ldk, src_bstride, dst_bstride);
-    else stage_rows_kernel<false><<<grid, 256, 0, ctx->stream>>>(src, hi, nullptr, rows, K, ldk, src_bstride, dst_bstride);
+    if (lo) NRS_PDL_LAUNCH((stage_rows_kernel<true>), grid, 256, 0, ctx->stream, src, hi, lo, rows, K, ldk, src_bstride, dst_bstride);
+    else NRS_PDL_LAUNCH((stage_rows_kernel<false>), grid, 256, 0, ctx->stream, src, hi, nullptr, rows, K, ldk, src_bstride, dst_bstride);
   } else {
     dim3 grid((unsigned)((rows + 31) / 32), (unsigned)(ldk / 32), (unsigned)batch);
     if (grid.y > 65535 || grid.z > 65535) return NRS_ERR_UNSUPPORTED;
-    if (lo) stage_transpose_kernel<true><<<grid, 256, 0, ctx->stream>>>(src, hi, lo, rows, K, ldk, src_bstride, dst_bstride);
-    else stage_transpose_kernel<false><<<grid, 256, 0, ctx->stream>>>(src, hi, nullptr, rows, K, ldk, src_bstride, dst_bstride);
+    if (lo) NRS_PDL_LAUNCH((stage_transpose_kernel<true>), grid, 256, 0, ctx->stream, src, hi, lo, rows, K, ldk, src_bstride, dst_bstride);
+    else NRS_PDL_LAUNCH((stage_transpose_kernel<false>), grid, 256, 0, ctx->stream, src, hi, nullptr, rows, K, ldk, src_bstride, dst_bstride);
   }
   NRS_LAUNCHED(ctx);
   return NRS_OK;
@@ -347,8 +353,8 @@ int nrs_tc_stage_conv_weight(nrs_ctx* ctx, const float* w, float* hi, float* lo,
                              int for_dgrad) {
   const size_t total = (size_t)co * ci * kh * kw;
   if (total == 0) return NRS_OK;
-  if (lo) stage_conv_weight_kernel<true><<<nrs_blocks(total, 256), 256, 0, ctx->stream>>>(w, hi, lo, co, ci, kh, kw, for_dgrad);
-  else stage_conv_weight_kernel<false><<<nrs_blocks(total, 256), 256, 0, ctx->stream>>>(w, hi, nullptr, co, ci, kh, kw, for_dgrad);
+  if (lo) NRS_PDL_LAUNCH((stage_conv_weight_kernel<true>), nrs_blocks(total, 256), 256, 0, ctx->stream, w, hi, lo, co, ci, kh, kw, for_dgrad);
+  else NRS_PDL_LAUNCH((stage_conv_weight_kernel<false>), nrs_blocks(total, 256), 256, 0, ctx->stream, w, hi, nullptr, co, ci, kh, kw, for_dgrad);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }

@@ -62,6 +62,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  NRS_PDL_TRIGGER();
   const int mb = blockIdx.x / p.n_groups, grp = blockIdx.x - mb * p.n_groups;
   const int split = blockIdx.y;
   const int t_begin = split * p.tiles_per_split;
@@ -86,6 +87,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  NRS_PDL_WAIT();   // set-up above may overlap the previous kernel's tail; its results are needed from here
 
   if (warp == 0) {
     if (lane == 0) {
@@ -197,6 +199,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
 // dw[co][ci][tap] (+)= sum over splits of partial[split][mb][grp][row][t*ci + c], fixed order.
 __global__ void __launch_bounds__(256)
 tc_wgrad_reduce_kernel(const WgradParams p, int splits, float* __restrict__ dw, int accumulate) {
+  NRS_PDL_PROLOGUE();
   const int taps = p.kh * p.kw;
   const size_t total = (size_t)p.co * p.ci * taps;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -232,8 +235,8 @@ int launch_wgrad(nrs_ctx* ctx, const CUtensorMap* maps, const WgradParams& p, in
   const int st = nrs_err_flag(ctx, &err);
   if (st != NRS_OK) return st;
   dim3 grid((unsigned)(p.m_blocks * p.n_groups), (unsigned)splits);
-  tc_wgrad_kernel<NPLANES, STAGES><<<grid, kWgThreads, smem_bytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p,
-                                                                                  p.group_cols, err);
+  NRS_PDL_LAUNCH((tc_wgrad_kernel<NPLANES, STAGES>), grid, kWgThreads, smem_bytes, ctx->stream, maps[0], maps[1], maps[2],
+                 maps[3], p, p.group_cols, err);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -348,7 +351,7 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
 #undef NRS_WG
   if (st != NRS_OK) return st;
   const size_t total = (size_t)co * ci * taps;
-  tc_wgrad_reduce_kernel<<<nrs_blocks(total, 256), 256, 0, ctx->stream>>>(p, splits, dw, accumulate);
+  NRS_PDL_LAUNCH(tc_wgrad_reduce_kernel, nrs_blocks(total, 256), 256, 0, ctx->stream, p, splits, dw, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }

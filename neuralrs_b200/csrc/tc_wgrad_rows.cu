@@ -111,6 +111,7 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  NRS_PDL_TRIGGER();
   // blockIdx.x = (m block, horizontal tap kind, channel chunk).  Unpacked: kind = tap j, x shifted by
   // j - 1.  Packed: kind 0 shifts x by 0 and holds taps j = 1 (plain dy rows) and j = 0 (dy shifted one
   // pixel: sum_p dy[p+1] x[p] = sum_p dy[p] x[p-1]); kind 1 shifts x by +1 and holds j = 2 alone.
@@ -142,6 +143,7 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  NRS_PDL_WAIT();   // set-up above may overlap the previous kernel's tail; its results are needed from here
 
   if (warp == 0) {
     if (lane == 0) {
@@ -280,6 +282,7 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
 // dw[co][ci][i][j] (+)= sum over splits of partial[split][(mb, j, chunk)][row][i*chunk + c], fixed order.
 __global__ void __launch_bounds__(256)
 tc_wgrad_rows_reduce_kernel(const RowParams p, int splits, int ctas, float* __restrict__ dw, int accumulate) {
+  NRS_PDL_PROLOGUE();
   const size_t total = (size_t)p.co * 9 * p.ci;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -316,7 +319,8 @@ int launch_rows(nrs_ctx* ctx, const CUtensorMap* maps, const RowParams& p, int c
   const int st = nrs_err_flag(ctx, &err);
   if (st != NRS_OK) return st;
   dim3 grid((unsigned)ctas, (unsigned)splits);
-  tc_wgrad_rows_kernel<NPLANES, KS><<<grid, kRowThreads, smem_bytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p, err);
+  NRS_PDL_LAUNCH((tc_wgrad_rows_kernel<NPLANES, KS>), grid, kRowThreads, smem_bytes, ctx->stream, maps[0], maps[1], maps[2],
+                 maps[3], p, err);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -415,7 +419,7 @@ int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float*
   }
   if (st != NRS_OK) return st;
   const size_t total = (size_t)co * ci * 9;
-  tc_wgrad_rows_reduce_kernel<<<nrs_blocks(total, 256), 256, 0, ctx->stream>>>(p, splits, ctas, dw, accumulate);
+  NRS_PDL_LAUNCH(tc_wgrad_rows_reduce_kernel, nrs_blocks(total, 256), 256, 0, ctx->stream, p, splits, ctas, dw, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }

@@ -13,6 +13,7 @@ namespace {
 __global__ void __launch_bounds__(256)
 embed_fwd_kernel(const float* __restrict__ w, const int32_t* __restrict__ idx, float* __restrict__ out, int tokens,
                  int dim) {
+  NRS_PDL_PROLOGUE();
   const size_t total = (size_t)tokens * dim;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   if ((dim & 3) == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
@@ -35,6 +36,7 @@ embed_fwd_kernel(const float* __restrict__ w, const int32_t* __restrict__ idx, f
 __global__ void __launch_bounds__(256)
 embed_bwd_kernel(const float* __restrict__ g, const int32_t* __restrict__ idx, float* dw, int tokens, int dim,
                  int accumulate) {
+  NRS_PDL_PROLOGUE();
   __shared__ int32_t s_idx[1024];
   const int row = blockIdx.x;
   for (int d0 = 0; d0 < dim; d0 += blockDim.x) {
@@ -59,6 +61,7 @@ embed_bwd_kernel(const float* __restrict__ g, const int32_t* __restrict__ idx, f
 // x, y: [batch, s, s].  forward: y = (j > i) ? -1e30 : x.  backward: y (+)= (j > i) ? 0 : x.
 __global__ void __launch_bounds__(256)
 causal_mask_kernel(const float* __restrict__ x, float* y, size_t total, int s, int backward, int accumulate) {
+  NRS_PDL_PROLOGUE();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
     const int j = (int)(idx % s);
@@ -79,6 +82,7 @@ unsigned grid_for(const nrs_ctx* ctx, size_t work) {
 __global__ void __launch_bounds__(256)
 permute_heads_kernel(const float* __restrict__ x, float* y, size_t total, int S, int H, int dh, int to_heads,
                      int accumulate) {
+  NRS_PDL_PROLOGUE();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
     // idx walks the [b][s][h][e] order
@@ -104,7 +108,7 @@ int nrs_embedding_fwd(nrs_ctx* ctx, const float* weight, const int32_t* idx, flo
   NRS_REQUIRE(ctx, tokens >= 0 && dim > 0, NRS_ERR_SHAPE, "nrs_embedding_fwd: bad shape [%d,%d]", tokens, dim);
   if (tokens == 0) return NRS_OK;
   NRS_REQUIRE(ctx, weight && idx && out, NRS_ERR_ARG, "nrs_embedding_fwd: null tensor");
-  embed_fwd_kernel<<<grid_for(ctx, (size_t)tokens * dim / 4 + 1), 256, 0, ctx->stream>>>(weight, idx, out, tokens, dim);
+  NRS_PDL_LAUNCH(embed_fwd_kernel, grid_for(ctx, (size_t)tokens * dim / 4 + 1), 256, 0, ctx->stream, weight, idx, out, tokens, dim);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -114,7 +118,7 @@ int nrs_embedding_bwd(nrs_ctx* ctx, const float* g, const int32_t* idx, float* d
   NRS_REQUIRE_CTX(ctx);
   NRS_REQUIRE(ctx, tokens >= 0 && dim > 0 && vocab > 0, NRS_ERR_SHAPE, "nrs_embedding_bwd: bad shape");
   NRS_REQUIRE(ctx, dweight && (tokens == 0 || (g && idx)), NRS_ERR_ARG, "nrs_embedding_bwd: null tensor");
-  embed_bwd_kernel<<<vocab, 256, 0, ctx->stream>>>(g, idx, dweight, tokens, dim, accumulate);
+  NRS_PDL_LAUNCH(embed_bwd_kernel, vocab, 256, 0, ctx->stream, g, idx, dweight, tokens, dim, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -125,7 +129,7 @@ int nrs_causal_mask(nrs_ctx* ctx, const float* x, float* y, int batch, int s, in
   const size_t total = (size_t)batch * s * s;
   if (total == 0) return NRS_OK;
   NRS_REQUIRE(ctx, x && y, NRS_ERR_ARG, "nrs_causal_mask: null tensor");
-  causal_mask_kernel<<<grid_for(ctx, total), 256, 0, ctx->stream>>>(x, y, total, s, backward, accumulate);
+  NRS_PDL_LAUNCH(causal_mask_kernel, grid_for(ctx, total), 256, 0, ctx->stream, x, y, total, s, backward, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
@@ -137,7 +141,7 @@ int nrs_permute_heads(nrs_ctx* ctx, const float* x, float* y, int batch, int s, 
   const size_t total = (size_t)batch * s * heads * d_head;
   if (total == 0) return NRS_OK;
   NRS_REQUIRE(ctx, x && y, NRS_ERR_ARG, "nrs_permute_heads: null tensor");
-  permute_heads_kernel<<<grid_for(ctx, total), 256, 0, ctx->stream>>>(x, y, total, s, heads, d_head, to_heads, accumulate);
+  NRS_PDL_LAUNCH(permute_heads_kernel, grid_for(ctx, total), 256, 0, ctx->stream, x, y, total, s, heads, d_head, to_heads, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
