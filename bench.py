@@ -169,7 +169,7 @@ def cpu_reference_run(workload: str, steps: int, warmup: int, min_seconds: float
 
 
 def conv_microbench(ctx, stream, iters=10):
-    """BASELINE config C2: Conv2d [256,64,32,32] -> 128, 3x3 s1 p1; forward, data gradient and weight
+    """The conv microbenchmark configuration: Conv2d [256,64,32,32] -> 128, 3x3 s1 p1; forward, data gradient and weight
     gradient timed separately through the raw C ABI (staging included), algorithmic TFLOP/s each."""
     import ctypes as C
     import torch
@@ -398,7 +398,7 @@ def run_ours(args):
 
 
 def run_transformer_lm(args):
-    """BASELINE config C4 (a parity configuration, not the headline): token embedding + positional
+    """The transformer language-model configuration (a parity configuration, not the headline): token embedding + positional
     encoding + 2 post-LN transformer blocks (GELU feed-forward, causal attention) + vocabulary head +
     cross-entropy + AdamW at batch 32, sequence 128, vocabulary 1000, d_model 256, 8 heads, d_ff 1024,
     driven op by op through the node-level C ABI the way the reference's examples drive its API."""

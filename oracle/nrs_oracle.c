@@ -19,7 +19,7 @@
  *                        reference is serial; the reference's Rayon folds are
  *                        themselves order-nondeterministic).
  *   -DNRS_ACC=double  -> symbols ending in _f64: same loops, sums carried in
- *                        f64.  This is the "true value" used to judge the
+ *                        f64.  This is the "true value" used to check the
  *                        <=1e-4 relative-error bar.
  * Build with -ffp-contract=off (Rust never contracts a*b+c into an FMA).
  */

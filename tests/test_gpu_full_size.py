@@ -26,7 +26,7 @@ def dot(a, b):
 
 
 def test_conv_microbench_full_size_properties(gpu_ctx, oracle64):
-    """BASELINE conv microbenchmark: x[256,64,32,32], w[128,64,3,3], stride 1, pad 1."""
+    """The conv microbenchmark configuration: x[256,64,32,32], w[128,64,3,3], stride 1, pad 1."""
     n, ci, h, w, co = 256, 64, 32, 32, 128
     rng = np.random.default_rng(1236)
     x = rng.standard_normal((n, ci, h, w), dtype=np.float32)
@@ -70,7 +70,7 @@ def test_conv_microbench_full_size_properties(gpu_ctx, oracle64):
 
 
 def test_vgg_full_batch_step_properties(gpu_ctx):
-    """BASELINE C3: the VGG-style CNN at batch 1024.  The whole-batch loss and gradients are the
+    """The headline configuration: the VGG-style CNN at batch 1024.  The whole-batch loss and gradients are the
     means of the two half-batch ones (cross-entropy averages over the batch), and two runs from the
     same state agree bit for bit."""
     cfg = models.VGG_CIFAR
@@ -99,7 +99,7 @@ def test_vgg_full_batch_step_properties(gpu_ctx):
 
 
 def test_wide_mlp_layer_full_size_properties(gpu_ctx, oracle64):
-    """BASELINE C5's hidden layer at full size: [16384, 4096] x [4096, 4096] with bias and GELU."""
+    """The wide-MLP configuration's hidden layer at full size: [16384, 4096] x [4096, 4096] with bias and GELU."""
     m, k, n = 16384, 4096, 4096
     rng = np.random.default_rng(1239)
     a = rng.standard_normal((m, k), dtype=np.float32)
