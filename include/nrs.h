@@ -221,6 +221,38 @@ int nrs_layernorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const flo
 int nrs_softmax_fwd(nrs_ctx* ctx, const float* x, float* y, int rows, int width);
 int nrs_softmax_bwd(nrs_ctx* ctx, const float* y, const float* g, float* dx, int rows, int width, int accumulate);
 
+/* ------------------------------------------------ batchnorm / dropout -- */
+
+/* bn2d_stats + bn2d_normalize (src/cuda/nn/batchnorm2d.rs:22-75) and, with hw == 1,
+ * bn_stats + bn_normalize (src/cuda/nn/batchnorm.rs:20-63): x is [n, c, hw],
+ * statistics pool over n and hw per channel.  training != 0: batch mean and biased
+ * variance; running = momentum*running + (1-momentum)*batch (updated in place).
+ * training == 0: the running statistics normalise.  Saves xhat[n,c,hw] (may be
+ * NULL when no backward follows) and istd[c] = 1/sqrt(var + eps). */
+int nrs_batchnorm_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const float* beta,
+                      float* running_mean, float* running_var, float* y, float* xhat, float* istd,
+                      int n, int c, int hw, float eps, float momentum, int training);
+/* bn2d_reduce + bn2d_dx (src/cuda/nn/batchnorm2d.rs:77-117; batchnorm.rs:65-108):
+ * dgamma (+)= sum g*xhat, dbeta (+)= sum g, dx (+)= istd*(g*gamma - gamma*dbeta/N -
+ * xhat*gamma*dgamma/N) in training, g*gamma*istd in evaluation.  dx may be NULL;
+ * dgamma and dbeta are given together or not at all. */
+int nrs_batchnorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd,
+                      const float* gamma, float* dx, float* dgamma, float* dbeta,
+                      int n, int c, int hw, int training, int accumulate_dx, int accumulate_params);
+/* mask_mul (src/cuda/nn/dropout.rs:17-22) with hw == 1 and mask_mul_channels
+ * (src/cuda/nn/dropout2d.rs:18-27) with hw = h*w: out (+)= a * mask[i / hw].  The
+ * same call routes the gradient in the backward pass. */
+int nrs_mask_mul(nrs_ctx* ctx, const float* a, const float* mask, float* out, size_t total, int hw, int accumulate);
+/* The mask the reference draws on the host (dropout.rs:45-48: 0 with probability
+ * p, else 1/(1-p)), generated on the device instead: Philox-4x32-10 keyed by the
+ * context's seed; element i is word i%4 of counter block (offset + i/4),
+ * u = (word >> 8) * 2^-24, mask = u < p ? 0 : 1/(1-p).  Each call consumes
+ * ceil(count/4) counter blocks.  nrs_rng_seed sets the seed and rewinds the
+ * offset to 0; nrs_rng_offset reads the next unused block. */
+int nrs_dropout_mask(nrs_ctx* ctx, float* mask, size_t count, float p);
+int nrs_rng_seed(nrs_ctx* ctx, uint64_t seed);
+int nrs_rng_offset(nrs_ctx* ctx, uint64_t* offset);
+
 /* ------------------------------------------------------------ transformer -- */
 
 /* embed_forward / embed_backward (src/cuda/nn/embedding.rs:13-30): row gather

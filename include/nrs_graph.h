@@ -69,6 +69,22 @@ int nrs_op_conv2d(nrs_node* input, nrs_node* weight, nrs_node* bias, int64_t str
 int nrs_op_maxpool2d(nrs_node* input, int64_t kernel, int64_t stride, nrs_node** out);
 int nrs_op_flatten(nrs_node* x, nrs_node** out);
 int nrs_op_layernorm(nrs_node* x, nrs_node* gamma, nrs_node* beta, float eps, nrs_node** out);
+/* batchnorm (src/cuda/nn/batchnorm.rs:110-232, x [batch, features]) and batchnorm2d
+ * (src/cuda/nn/batchnorm2d.rs:130-232, x [batch, channels, h, w]).  running_mean and
+ * running_var are resident nodes of length channels; training != 0 updates them in
+ * place (running = momentum*running + (1-momentum)*batch). */
+int nrs_op_batchnorm(nrs_node* x, nrs_node* gamma, nrs_node* beta, nrs_node* running_mean, nrs_node* running_var,
+                     float momentum, float eps, int training, nrs_node** out);
+int nrs_op_batchnorm2d(nrs_node* x, nrs_node* gamma, nrs_node* beta, nrs_node* running_mean, nrs_node* running_var,
+                       float momentum, float eps, int training, nrs_node** out);
+/* dropout (src/cuda/nn/dropout.rs:31-84) and dropout2d (src/cuda/nn/dropout2d.rs:37-).
+ * training == 0 hands back the input node itself (one more reference on it).  `mask`
+ * NULL draws the mask on the device (nrs_dropout_mask: the context's seed and
+ * counter); a resident mask node (one value per element, or per (sample, channel)
+ * plane for dropout2d; values 0 or 1/(1-p)) is used as given, which is how a caller
+ * replays masks drawn elsewhere. */
+int nrs_op_dropout(nrs_node* x, float p, int training, nrs_node* mask, nrs_node** out);
+int nrs_op_dropout2d(nrs_node* x, float p, int training, nrs_node* mask, nrs_node** out);
 /* Fused x@W+b -> activation and conv+bias -> activation (enum nrs_act). */
 int nrs_op_linear_act(nrs_node* x, nrs_node* w, nrs_node* b, int act, nrs_node** out);
 int nrs_op_conv2d_act(nrs_node* input, nrs_node* weight, nrs_node* bias, int64_t stride, int64_t pad, int act,

@@ -765,6 +765,121 @@ NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps
   return out;
 }
 
+// batchnorm (src/cuda/nn/batchnorm.rs:110-232) for [batch, features] and batchnorm2d
+// (src/cuda/nn/batchnorm2d.rs:130-232) for [batch, channels, h, w]: the running statistics are resident
+// nodes owned by the caller and updated in place in training mode.
+NodeP batchnorm_nd(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
+                   const NodeP& running_var, float momentum, float eps, bool training, size_t want_dims,
+                   const char* what) {
+  const std::string w(what);
+  require_gpu(x, (w + ": input").c_str());
+  require_gpu(gamma, (w + ": gamma").c_str());
+  require_gpu(beta, (w + ": beta").c_str());
+  require_gpu(running_mean, (w + ": running_mean").c_str());
+  require_gpu(running_var, (w + ": running_var").c_str());
+  if (x->shape.size() != want_dims) fail(NRS_ERR_SHAPE, (w + ": input has the wrong number of dimensions").c_str());
+  nrs_ctx* ctx = x->ctx;
+  const int n = (int)x->shape[0], c = (int)x->shape[1];
+  if (n < 1 || c < 1 || x->len() == 0) fail(NRS_ERR_SHAPE, (w + ": empty input").c_str());
+  const int hw = (int)(x->len() / ((size_t)n * c));
+  if ((int)gamma->len() != c || (int)beta->len() != c || (int)running_mean->len() != c || (int)running_var->len() != c)
+    fail(NRS_ERR_SHAPE, (w + ": gamma/beta/running statistics length mismatch").c_str());
+  NodeP out = make_out(ctx, x->shape, {x, gamma, beta});
+  float* xhat = dalloc(ctx, x->len());
+  float* istd = dalloc(ctx, (size_t)c);
+  out->saved.push_back(xhat);
+  out->saved.push_back(istd);
+  check(ctx, nrs_batchnorm_fwd(ctx, x->data, gamma->data, beta->data, running_mean->data, running_var->data, out->data,
+                               xhat, istd, n, c, hw, eps, momentum, training ? 1 : 0));
+  Node* self = out.get();
+  out->backward_fn = [self, x, gamma, beta, xhat, istd, n, c, hw, training]() {
+    nrs_ctx* ctx = self->ctx;
+    const float* g = grad_in(self);
+    float *dg = nullptr, *db = nullptr;
+    int acc_p = 0;
+    if (gamma->requires_grad || beta->requires_grad) {
+      GradTarget tg = grad_target(gamma), tb = grad_target(beta);
+      if (tg.accumulate != tb.accumulate) {  // bring both to "accumulate" state
+        if (!tg.accumulate) check(ctx, nrs_memset_zero(ctx, tg.ptr, sizeof(float) * c));
+        if (!tb.accumulate) check(ctx, nrs_memset_zero(ctx, tb.ptr, sizeof(float) * c));
+        tg.accumulate = tb.accumulate = 1;
+      }
+      dg = tg.ptr;
+      db = tb.ptr;
+      acc_p = tg.accumulate;
+    }
+    float* dx = nullptr;
+    int acc_x = 0;
+    if (x->requires_grad) {
+      GradTarget t = grad_target(x);
+      dx = t.ptr;
+      acc_x = t.accumulate;
+    }
+    check(ctx, nrs_batchnorm_bwd(ctx, g, xhat, istd, gamma->data, dx, dg, db, n, c, hw, training ? 1 : 0, acc_x, acc_p));
+  };
+  return out;
+}
+
+NodeP batchnorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
+                const NodeP& running_var, float momentum, float eps, bool training) {
+  return batchnorm_nd(x, gamma, beta, running_mean, running_var, momentum, eps, training, 2, "cuda bn");
+}
+
+NodeP batchnorm2d(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
+                  const NodeP& running_var, float momentum, float eps, bool training) {
+  return batchnorm_nd(x, gamma, beta, running_mean, running_var, momentum, eps, training, 4, "cuda bn2d");
+}
+
+// dropout (src/cuda/nn/dropout.rs:31-84) and dropout2d (src/cuda/nn/dropout2d.rs:37-end): evaluation returns
+// the input node itself; training multiplies by a mask of 0 / 1/(1-p) values (one per element, or one per
+// (sample, channel) plane) that also routes the gradient.  `mask` == nullptr draws the mask on the device
+// from the context's counter-based generator; otherwise the caller's resident mask is used as it is.
+NodeP dropout_nd(const NodeP& x, float p, bool training, const NodeP& mask, bool spatial, const char* what) {
+  if (!training) return x;
+  const std::string w(what);
+  require_gpu(x, (w + ": input").c_str());
+  if (!(p >= 0.0f && p <= 1.0f)) fail(NRS_ERR_ARG, (w + ": probability outside [0,1]").c_str());
+  nrs_ctx* ctx = x->ctx;
+  size_t hw = 1;
+  if (spatial) {
+    if (x->shape.size() != 4) fail(NRS_ERR_SHAPE, (w + ": input must be [batch, channels, h, w]").c_str());
+    hw = x->shape[2] * x->shape[3];
+  }
+  if (x->len() == 0 || hw == 0) fail(NRS_ERR_SHAPE, (w + ": empty input").c_str());
+  const size_t mask_len = x->len() / hw;
+  const float* mask_ptr = nullptr;
+  NodeP out = make_out(ctx, x->shape, {x});
+  if (mask) {
+    require_gpu(mask, (w + ": mask").c_str());
+    if (mask->len() != mask_len) fail(NRS_ERR_SHAPE, (w + ": mask length mismatch").c_str());
+    mask_ptr = mask->data;
+    out->parents.push_back(mask);   // keeps the caller's mask alive until the backward pass has run
+  } else {
+    float* m = dalloc(ctx, mask_len);
+    out->saved.push_back(m);
+    check(ctx, nrs_dropout_mask(ctx, m, mask_len, p));
+    mask_ptr = m;
+  }
+  check(ctx, nrs_mask_mul(ctx, x->data, mask_ptr, out->data, x->len(), (int)hw, 0));
+  Node* self = out.get();
+  const size_t total = x->len();
+  out->backward_fn = [self, x, mask_ptr, total, hw]() {
+    if (!x->requires_grad) return;
+    nrs_ctx* ctx = self->ctx;
+    GradTarget t = grad_target(x);
+    check(ctx, nrs_mask_mul(ctx, grad_in(self), mask_ptr, t.ptr, total, (int)hw, t.accumulate));
+  };
+  return out;
+}
+
+NodeP dropout(const NodeP& x, float p, bool training, const NodeP& mask) {
+  return dropout_nd(x, p, training, mask, false, "cuda dropout");
+}
+
+NodeP dropout2d(const NodeP& x, float p, bool training, const NodeP& mask) {
+  return dropout_nd(x, p, training, mask, true, "cuda dropout2d");
+}
+
 NodeP linear_act(const NodeP& x, const NodeP& w, const NodeP& b, int act) {
   require_gpu(x, "cuda linear: input");
   require_gpu(w, "cuda linear: weights");

@@ -127,6 +127,14 @@ NodeP conv2d(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size
 NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride, bool emit_planes = false);   // hint as in conv2d_act
 NodeP flatten(const NodeP& x);
 NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps);
+// batchnorm.rs / batchnorm2d.rs: running_mean / running_var are resident nodes updated in place when training
+NodeP batchnorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
+                const NodeP& running_var, float momentum, float eps, bool training);
+NodeP batchnorm2d(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
+                  const NodeP& running_var, float momentum, float eps, bool training);
+// dropout.rs / dropout2d.rs: evaluation returns `x` itself; `mask` == nullptr draws the mask on the device
+NodeP dropout(const NodeP& x, float p, bool training, const NodeP& mask = nullptr);
+NodeP dropout2d(const NodeP& x, float p, bool training, const NodeP& mask = nullptr);
 // Fused variants with no counterpart op in the reference: one kernel for
 // x@W + b followed by an activation, and conv + bias + activation.  Backward is
 // the composition of the unfused backward passes.

@@ -219,6 +219,42 @@ int nrs_op_layernorm(nrs_node* x, nrs_node* gamma, nrs_node* beta, float eps, nr
   return wrap(ctx_of(x), out, [&] { return nrs::cuda::layernorm(x->p, gamma->p, beta->p, eps); });
 }
 
+int nrs_op_batchnorm(nrs_node* x, nrs_node* gamma, nrs_node* beta, nrs_node* running_mean, nrs_node* running_var,
+                     float momentum, float eps, int training, nrs_node** out) {
+  NODE_OK(x);
+  NODE_OK(gamma);
+  NODE_OK(beta);
+  NODE_OK(running_mean);
+  NODE_OK(running_var);
+  return wrap(ctx_of(x), out, [&] {
+    return nrs::cuda::batchnorm(x->p, gamma->p, beta->p, running_mean->p, running_var->p, momentum, eps, training != 0);
+  });
+}
+
+int nrs_op_batchnorm2d(nrs_node* x, nrs_node* gamma, nrs_node* beta, nrs_node* running_mean, nrs_node* running_var,
+                       float momentum, float eps, int training, nrs_node** out) {
+  NODE_OK(x);
+  NODE_OK(gamma);
+  NODE_OK(beta);
+  NODE_OK(running_mean);
+  NODE_OK(running_var);
+  return wrap(ctx_of(x), out, [&] {
+    return nrs::cuda::batchnorm2d(x->p, gamma->p, beta->p, running_mean->p, running_var->p, momentum, eps, training != 0);
+  });
+}
+
+int nrs_op_dropout(nrs_node* x, float p, int training, nrs_node* mask, nrs_node** out) {
+  NODE_OK(x);
+  if (mask) NODE_OK(mask);
+  return wrap(ctx_of(x), out, [&] { return nrs::cuda::dropout(x->p, p, training != 0, mask ? mask->p : nullptr); });
+}
+
+int nrs_op_dropout2d(nrs_node* x, float p, int training, nrs_node* mask, nrs_node** out) {
+  NODE_OK(x);
+  if (mask) NODE_OK(mask);
+  return wrap(ctx_of(x), out, [&] { return nrs::cuda::dropout2d(x->p, p, training != 0, mask ? mask->p : nullptr); });
+}
+
 int nrs_op_linear_act(nrs_node* x, nrs_node* w, nrs_node* b, int act, nrs_node** out) {
   NODE_OK(x);
   NODE_OK(w);

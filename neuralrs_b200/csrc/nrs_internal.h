@@ -86,6 +86,8 @@ struct nrs_ctx {
   // the host graph makes them once per step for the image layer's forward pass and weight gradient
   // (`split`: bit 0 = residual plane present, bits 8.. = the padding they were made for).
   std::map<const void*, NrsPlanes> patch_hints;
+  // Counter-based generator state of the dropout masks (dropout.cu): seed, and the next unused counter block.
+  uint64_t rng_seed = 0, rng_offset = 0;
   // Optional per-family device timing (nrs_profile_*).
   bool profiling = false;
   std::vector<NrsProfRecord> prof_records;
@@ -165,6 +167,11 @@ inline cudaError_t nrs_pdl_launch(void (*kernel)(P...), dim3 grid, dim3 block, s
 // expression goes in parentheses when its template arguments contain commas.
 #define NRS_PDL_LAUNCH(kernel, grid, block, smem, stream, ...) \
   (void)nrs_pdl_launch(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
+
+// Split reduces of the weight-gradient kernels: threads per block, and how many of them share one output
+// (each summing every lanes-th split) for a given number of splits.
+constexpr int kReduceThreads = 256;
+static inline int reduce_lanes(int splits) { return splits >= 32 ? 8 : splits >= 16 ? 4 : splits >= 8 ? 2 : 1; }
 
 static inline unsigned nrs_blocks(size_t work, unsigned per_block) {
   return (unsigned)((work + per_block - 1) / per_block);

@@ -196,14 +196,20 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
   }
 }
 
-// dw[co][ci][tap] (+)= sum over splits of partial[split][mb][grp][row][t*ci + c], fixed order.
-__global__ void __launch_bounds__(256)
-tc_wgrad_reduce_kernel(const WgradParams p, int splits, float* __restrict__ dw, int accumulate) {
+// dw[co][ci][tap] (+)= sum over splits of partial[split][mb][grp][row][t*ci + c].  A block is
+// (kReduceThreads / lanes) outputs x `lanes` split lanes: lane y sums splits y, y+lanes, ... and the lanes are
+// combined in lane order through shared memory, so the order of the additions is fixed (bit-reproducible)
+// while the loads of one output are spread over `lanes` threads instead of one serial chain.
+__global__ void __launch_bounds__(kReduceThreads)
+tc_wgrad_reduce_kernel(const WgradParams p, int splits, int lanes, float* __restrict__ dw, int accumulate) {
   NRS_PDL_PROLOGUE();
+  __shared__ float lane_sum[kReduceThreads];
+  const int per_block = kReduceThreads / lanes;   // outputs of this block
+  const int lane = threadIdx.x / per_block, slot = threadIdx.x - lane * per_block;
   const int taps = p.kh * p.kw;
   const size_t total = (size_t)p.co * p.ci * taps;
-  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= total) return;
+  const size_t idx = (size_t)blockIdx.x * per_block + slot;
+  const bool live = idx < total;
   // idx enumerates (co, tap, ci) so that reads of the partials are coalesced along ci
   const int c = (int)(idx % p.ci);
   const int tap = (int)((idx / p.ci) % taps);
@@ -214,7 +220,14 @@ tc_wgrad_reduce_kernel(const WgradParams p, int splits, float* __restrict__ dw, 
   const size_t off = (((size_t)mb * p.n_groups + grp) * 128 + row) * p.group_cols + (size_t)t * p.ci + c;
   const size_t split_stride = (size_t)p.m_blocks * p.n_groups * tile;
   float s = 0.0f;
-  for (int z = 0; z < splits; ++z) s += p.partial[(size_t)z * split_stride + off];
+  if (live) {
+#pragma unroll 4
+    for (int z = lane; z < splits; z += lanes) s += p.partial[(size_t)z * split_stride + off];
+  }
+  lane_sum[threadIdx.x] = s;
+  __syncthreads();
+  if (lane != 0 || !live) return;
+  for (int l = 1; l < lanes; ++l) s += lane_sum[l * per_block + slot];
   float* dst = dw + ((size_t)co * p.ci + c) * taps + tap;
   *dst = accumulate ? *dst + s : s;
 }
@@ -351,7 +364,9 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
 #undef NRS_WG
   if (st != NRS_OK) return st;
   const size_t total = (size_t)co * ci * taps;
-  NRS_PDL_LAUNCH(tc_wgrad_reduce_kernel, nrs_blocks(total, 256), 256, 0, ctx->stream, p, splits, dw, accumulate);
+  const int lanes = reduce_lanes(splits);
+  NRS_PDL_LAUNCH(tc_wgrad_reduce_kernel, nrs_blocks(total, kReduceThreads / lanes), kReduceThreads, 0, ctx->stream, p, splits, lanes, dw,
+                 accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }

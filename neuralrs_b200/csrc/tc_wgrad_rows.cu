@@ -279,13 +279,19 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
   }
 }
 
-// dw[co][ci][i][j] (+)= sum over splits of partial[split][(mb, j, chunk)][row][i*chunk + c], fixed order.
-__global__ void __launch_bounds__(256)
-tc_wgrad_rows_reduce_kernel(const RowParams p, int splits, int ctas, float* __restrict__ dw, int accumulate) {
+// dw[co][ci][i][j] (+)= sum over splits of the partial accumulators.  A block is
+// (kReduceThreads / lanes) outputs x `lanes` split lanes: lane y sums splits y, y+lanes, ... and the lanes are
+// combined in lane order through shared memory: a fixed order of additions (bit-reproducible) without one
+// serial load chain per output.
+__global__ void __launch_bounds__(kReduceThreads)
+tc_wgrad_rows_reduce_kernel(const RowParams p, int splits, int ctas, int lanes, float* __restrict__ dw, int accumulate) {
   NRS_PDL_PROLOGUE();
+  __shared__ float lane_sum[kReduceThreads];
+  const int per_block = kReduceThreads / lanes;   // outputs of this block
+  const int lane = threadIdx.x / per_block, slot = threadIdx.x - lane * per_block;
   const size_t total = (size_t)p.co * 9 * p.ci;
-  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= total) return;
+  const size_t idx = (size_t)blockIdx.x * per_block + slot;
+  const bool live = idx < total;
   // idx enumerates (co, j, i, ci): consecutive threads read consecutive partial columns
   const int ci = (int)(idx % p.ci);
   const int i = (int)((idx / p.ci) % 3);
@@ -303,7 +309,14 @@ tc_wgrad_rows_reduce_kernel(const RowParams p, int splits, int ctas, float* __re
   const size_t off = ((size_t)cta * 128 + row) * cols + (size_t)i * p.chunk + c;
   const size_t split_stride = (size_t)ctas * 128 * cols;
   float s = 0.0f;
-  for (int z = 0; z < splits; ++z) s += p.partial[(size_t)z * split_stride + off];
+  if (live) {
+#pragma unroll 4
+    for (int z = lane; z < splits; z += lanes) s += p.partial[(size_t)z * split_stride + off];
+  }
+  lane_sum[threadIdx.x] = s;
+  __syncthreads();
+  if (lane != 0 || !live) return;
+  for (int l = 1; l < lanes; ++l) s += lane_sum[l * per_block + slot];
   float* dst = dw + (((size_t)co * p.ci + ci) * 3 + i) * 3 + j;
   *dst = accumulate ? *dst + s : s;
 }
@@ -419,7 +432,9 @@ int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float*
   }
   if (st != NRS_OK) return st;
   const size_t total = (size_t)co * ci * 9;
-  NRS_PDL_LAUNCH(tc_wgrad_rows_reduce_kernel, nrs_blocks(total, 256), 256, 0, ctx->stream, p, splits, ctas, dw, accumulate);
+  const int lanes = reduce_lanes(splits);
+  NRS_PDL_LAUNCH(tc_wgrad_rows_reduce_kernel, nrs_blocks(total, kReduceThreads / lanes), kReduceThreads, 0, ctx->stream, p, splits,
+                 ctas, lanes, dw, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }

@@ -248,6 +248,34 @@ class nn:
         return _out(x.ctx, x.ctx._l.nrs_op_layernorm(x.h, gamma.h, beta.h, C.c_float(eps), C.byref(h)), h)
 
     @staticmethod
+    def batchnorm(x: Node, gamma: Node, beta: Node, running_mean: Node, running_var: Node, momentum: float,
+                  eps: float, training: bool) -> Node:
+        """src/cuda/nn/batchnorm.rs:110-232: x [batch, features]; the running statistics are updated in place."""
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_batchnorm(x.h, gamma.h, beta.h, running_mean.h, running_var.h,
+                                                      C.c_float(momentum), C.c_float(eps), int(training), C.byref(h)), h)
+
+    @staticmethod
+    def batchnorm2d(x: Node, gamma: Node, beta: Node, running_mean: Node, running_var: Node, momentum: float,
+                    eps: float, training: bool) -> Node:
+        """src/cuda/nn/batchnorm2d.rs:130-232: x [batch, channels, h, w]."""
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_batchnorm2d(x.h, gamma.h, beta.h, running_mean.h, running_var.h,
+                                                        C.c_float(momentum), C.c_float(eps), int(training), C.byref(h)), h)
+
+    @staticmethod
+    def dropout(x: Node, p: float, training: bool, mask: Node | None = None) -> Node:
+        """src/cuda/nn/dropout.rs:31-84.  mask=None draws the mask on the device (context seed and counter)."""
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_dropout(x.h, C.c_float(p), int(training), mask.h if mask else None, C.byref(h)), h)
+
+    @staticmethod
+    def dropout2d(x: Node, p: float, training: bool, mask: Node | None = None) -> Node:
+        """src/cuda/nn/dropout2d.rs: one mask value per (sample, channel) plane."""
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_dropout2d(x.h, C.c_float(p), int(training), mask.h if mask else None, C.byref(h)), h)
+
+    @staticmethod
     def linear_act(x: Node, w: Node, b: Node, act: int) -> Node:
         h = VP()
         return _out(x.ctx, x.ctx._l.nrs_op_linear_act(x.h, w.h, b.h, int(act), C.byref(h)), h)

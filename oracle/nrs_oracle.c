@@ -517,3 +517,132 @@ void FN(nrs_oracle_positional_table)(float* pe, int max_len, int d_model) {
       pe[(size_t)pos * d_model + i] = (i % 2 == 0) ? sinf(angle) : cosf(angle);
     }
 }
+
+/* --------------------------------------------------------------- BatchNorm */
+
+/* x is [n, c, hw]; hw == 1 is BatchNorm over [batch, features]
+ * (src/nn/batchnorm.rs:28-84), hw = h*w is BatchNorm2d (src/nn/batchnorm2d.rs:28-101).
+ * Training: per channel, mean then the biased variance of (x - mean) in a second
+ * pass (:47-64), running = momentum*running + (1-momentum)*batch value (:66-67),
+ * istd = 1/sqrt(var + eps) (:69).  Evaluation: the running statistics (:83-86).
+ * xhat = (x - mean)*istd, y = gamma*xhat + beta (:72-78). */
+void FN(nrs_oracle_batchnorm_fwd)(const float* x, const float* gamma, const float* beta, float* running_mean,
+                                  float* running_var, float* y, float* xhat, float* istd_out, int n, int c,
+                                  int hw, float eps, float momentum, int training) {
+  const float count = (float)(n * hw);
+  for (int ch = 0; ch < c; ++ch) {
+    float mean, var;
+    if (training) {
+      acc_t s = 0;
+      for (int ni = 0; ni < n; ++ni) {
+        const size_t base = ((size_t)ni * c + ch) * hw;
+        for (int p = 0; p < hw; ++p) s += (acc_t)x[base + p];
+      }
+      mean = (float)(s / (acc_t)count);
+      acc_t vs = 0;
+      for (int ni = 0; ni < n; ++ni) {
+        const size_t base = ((size_t)ni * c + ch) * hw;
+        for (int p = 0; p < hw; ++p) { const float d = x[base + p] - mean; vs += (acc_t)(d * d); }
+      }
+      var = (float)(vs / (acc_t)count);
+      running_mean[ch] = momentum * running_mean[ch] + (1.0f - momentum) * mean;
+      running_var[ch] = momentum * running_var[ch] + (1.0f - momentum) * var;
+    } else {
+      mean = running_mean[ch];
+      var = running_var[ch];
+    }
+    const float istd = 1.0f / sqrtf(var + eps);
+    istd_out[ch] = istd;
+    for (int ni = 0; ni < n; ++ni) {
+      const size_t base = ((size_t)ni * c + ch) * hw;
+      for (int p = 0; p < hw; ++p) {
+        const float xn = (x[base + p] - mean) * istd;
+        if (xhat) xhat[base + p] = xn;
+        y[base + p] = gamma[ch] * xn + beta[ch];
+      }
+    }
+  }
+}
+/* src/nn/batchnorm2d.rs:112-163 (batchnorm.rs:97-139): training
+ * dx += istd*(dxhat - sum1/N - xhat*sum2/N) with dxhat = g*gamma, sum1 = sum dxhat,
+ * sum2 = sum dxhat*xhat; evaluation dx += g*gamma*istd; dgamma += sum g*xhat,
+ * dbeta += sum g in both modes. */
+void FN(nrs_oracle_batchnorm_bwd)(const float* g, const float* xhat, const float* istd, const float* gamma,
+                                  float* dx, float* dgamma, float* dbeta, int n, int c, int hw, int training) {
+  const float cnt = (float)(n * hw);
+  for (int ch = 0; ch < c; ++ch) {
+    acc_t sum1 = 0, sum2 = 0, dg = 0, db = 0;
+    for (int ni = 0; ni < n; ++ni) {
+      const size_t base = ((size_t)ni * c + ch) * hw;
+      for (int p = 0; p < hw; ++p) {
+        const float dxhat = g[base + p] * gamma[ch];
+        sum1 += (acc_t)dxhat;
+        sum2 += (acc_t)(dxhat * xhat[base + p]);
+        dg += (acc_t)(g[base + p] * xhat[base + p]);
+        db += (acc_t)g[base + p];
+      }
+    }
+    const float s1 = (float)sum1, s2 = (float)sum2;
+    if (dx) {
+      for (int ni = 0; ni < n; ++ni) {
+        const size_t base = ((size_t)ni * c + ch) * hw;
+        for (int p = 0; p < hw; ++p) {
+          const float dxhat = g[base + p] * gamma[ch];
+          if (training) dx[base + p] += istd[ch] * (dxhat - s1 / cnt - xhat[base + p] * s2 / cnt);
+          else dx[base + p] += g[base + p] * gamma[ch] * istd[ch];
+        }
+      }
+    }
+    if (dgamma) dgamma[ch] += (float)dg;
+    if (dbeta) dbeta[ch] += (float)db;
+  }
+}
+
+/* ----------------------------------------------------------------- Dropout */
+
+/* out (+)= a * mask[i / hw].  hw == 1: Dropout forward `in*scale or 0` and backward
+ * `grad*mask` (src/nn/dropout.rs:29-50); hw = h*w: Dropout2d, one mask value per
+ * (sample, channel) plane (src/nn/dropout2d.rs, src/cuda/nn/dropout2d.rs:18-27). */
+void FN(nrs_oracle_mask_mul)(const float* a, const float* mask, float* out, size_t total, int hw, int accumulate) {
+  for (size_t i = 0; i < total; ++i) {
+    const float r = a[i] * mask[i / (size_t)hw];
+    out[i] = accumulate ? out[i] + r : r;
+  }
+}
+
+/* Philox-4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as
+ * 1, 2, 3", SC'11): ten rounds of two 32x32->64 multiplies with the key bumped by
+ * the Weyl constants between rounds. */
+void FN(nrs_oracle_philox4x32_10)(const uint32_t ctr_in[4], const uint32_t key[2], uint32_t out[4]) {
+  uint32_t c0 = ctr_in[0], c1 = ctr_in[1], c2 = ctr_in[2], c3 = ctr_in[3], k0 = key[0], k1 = key[1];
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0, n1 = (uint32_t)p1;
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1, n3 = (uint32_t)p0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+/* The mask of Dropout / Dropout2d: 0 with probability p, else 1/(1-p)
+ * (src/nn/dropout.rs:26-37, src/cuda/nn/dropout.rs:38-48).  The reference draws u from
+ * the `rand` crate's thread-local generator, which cannot be reproduced; the
+ * device library specifies its own stream instead and this restates it: element i
+ * is word i%4 of the Philox block at counter (offset + i/4, 0) under the 64-bit
+ * seed, u = (word >> 8) * 2^-24. */
+void FN(nrs_oracle_dropout_mask)(float* mask, size_t count, float p, uint64_t seed, uint64_t offset) {
+  const float scale = 1.0f / (1.0f - p);
+  const uint32_t key[2] = {(uint32_t)seed, (uint32_t)(seed >> 32)};
+  for (size_t b = 0; b * 4 < count; ++b) {
+    const uint64_t at = offset + b;
+    const uint32_t ctr[4] = {(uint32_t)at, (uint32_t)(at >> 32), 0u, 0u};
+    uint32_t w[4];
+    FN(nrs_oracle_philox4x32_10)(ctr, key, w);
+    for (int j = 0; j < 4 && b * 4 + j < count; ++j) {
+      const float u = (float)(w[j] >> 8) * (1.0f / 16777216.0f);
+      mask[b * 4 + j] = u < p ? 0.0f : scale;
+    }
+  }
+}

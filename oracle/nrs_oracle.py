@@ -209,6 +209,52 @@ class Oracle:
                                              rows, f)
         return dx, dgamma, dbeta
 
+    # ---- batchnorm (src/nn/batchnorm.rs:28-150 with hw == 1, src/nn/batchnorm2d.rs:28-164)
+    @staticmethod
+    def _bn_dims(x):
+        n, c = x.shape[0], x.shape[1]
+        return n, c, x.size // (n * c)
+
+    def batchnorm_fwd(self, x, gamma, beta, running_mean, running_var, eps, momentum, training):
+        """Returns y, xhat, istd and the running statistics after the call (the inputs are not modified)."""
+        x, gamma, beta = _f(x), _f(gamma), _f(beta)
+        rm, rv = _f(running_mean).copy(), _f(running_var).copy()
+        n, c, hw = self._bn_dims(x)
+        y, xhat = np.empty_like(x), np.empty_like(x)
+        istd = np.empty(c, np.float32)
+        self._fn("nrs_oracle_batchnorm_fwd")(_p(x), _p(gamma), _p(beta), _p(rm), _p(rv), _p(y), _p(xhat), _p(istd),
+                                             n, c, hw, C.c_float(eps), C.c_float(momentum), int(bool(training)))
+        return y, xhat, istd, rm, rv
+
+    def batchnorm_bwd(self, g, xhat, istd, gamma, training):
+        g, xhat, istd, gamma = _f(g), _f(xhat), _f(istd), _f(gamma)
+        n, c, hw = self._bn_dims(g)
+        dx = np.zeros_like(g)
+        dgamma, dbeta = np.zeros(c, np.float32), np.zeros(c, np.float32)
+        self._fn("nrs_oracle_batchnorm_bwd")(_p(g), _p(xhat), _p(istd), _p(gamma), _p(dx), _p(dgamma), _p(dbeta),
+                                             n, c, hw, int(bool(training)))
+        return dx, dgamma, dbeta
+
+    # ---- dropout (src/nn/dropout.rs:19-56, src/nn/dropout2d.rs; mask stream: the device library's own)
+    def mask_mul(self, a, mask, hw=1):
+        a, mask = _f(a), _f(mask)
+        out = np.empty_like(a)
+        self._fn("nrs_oracle_mask_mul")(_p(a), _p(mask), _p(out), C.c_size_t(a.size), int(hw), 0)
+        return out
+
+    def philox4x32_10(self, ctr, key):
+        ctr = np.ascontiguousarray(ctr, np.uint32)
+        key = np.ascontiguousarray(key, np.uint32)
+        out = np.empty(4, np.uint32)
+        self._fn("nrs_oracle_philox4x32_10")(_p(ctr), _p(key), _p(out))
+        return out
+
+    def dropout_mask(self, count, p, seed, offset=0):
+        mask = np.empty(count, np.float32)
+        self._fn("nrs_oracle_dropout_mask")(_p(mask), C.c_size_t(count), C.c_float(p), C.c_uint64(seed),
+                                            C.c_uint64(offset))
+        return mask
+
     # ---- softmax (src/autograd/graph/softmax.rs:14-64)
     def softmax_fwd(self, x):
         x = _f(x)
