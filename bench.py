@@ -4,15 +4,17 @@ CIFAR-shaped VGG-style CNN, global batch 1024 sharded over N GPUs, f32 with
 3xTF32 contractions, synthetic data, He-initialised weights.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload vgg_cifar|small_cnn|wide_mlp] [--math 3xtf32|tf32|fp32]
+                    [--workload vgg_cifar|vgg_cifar_bn|small_cnn|wide_mlp|transformer_lm] [--math 3xtf32|tf32|fp32]
 
 For N > 1 launch under torchrun (one rank per GPU); run without torchrun the
 script re-launches itself through `python -m torch.distributed.run`.
 Rank 0 prints ONE JSON line.
 
 * value        whole-job samples/s with the step's inputs already resident in HBM
-* e2e          the same through the host-buffer entry point (nrs_trainer_step): pinned
-               host inputs copied in, loss copied out, every step
+* e2e          the same through the host-buffer entry points (nrs_trainer_stage_next +
+               nrs_trainer_step_staged): pinned host inputs copied in (the copy of batch i+1
+               overlapping step i), loss copied out, every step; `unpipelined_value` is the
+               plain nrs_trainer_step (copy, step, read-back in sequence)
 * roofline     the dominant contraction family, timed with CUDA events bracketed around
                its launches inside the timed region (nrs_profile_*; every fourth timed step)
 * cpu_baseline the CPU restatement of the reference's training loop (oracle/), timed on
@@ -36,8 +38,9 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 METRIC = "train samples/s (fwd+bwd+AdamW)"
-WORKLOADS = {"vgg_cifar": ("VGG_CIFAR", 1024, 3), "small_cnn": ("SMALL_CNN", 64, 1), "wide_mlp": ("WIDE_MLP", 16384, 5)}
-CPU_SAMPLE_BATCH = {"vgg_cifar": 16, "small_cnn": 64, "wide_mlp": 32}
+WORKLOADS = {"vgg_cifar": ("VGG_CIFAR", 1024, 3), "small_cnn": ("SMALL_CNN", 64, 1), "wide_mlp": ("WIDE_MLP", 16384, 5),
+             "vgg_cifar_bn": ("VGG_CIFAR_BN", 1024, 7)}
+CPU_SAMPLE_BATCH = {"vgg_cifar": 16, "small_cnn": 64, "wide_mlp": 32, "vgg_cifar_bn": 16}
 MATH = {"3xtf32": 0, "tf32": 1, "fp32": 2}
 PROF_NAMES = ["conv_fwd", "conv_dgrad", "conv_wgrad", "gemm", "adamw"]
 
@@ -150,12 +153,13 @@ def cpu_reference_run(workload: str, steps: int, warmup: int, min_seconds: float
     hp = models.ADAMW_HP
     opt = models.OracleAdamW(o, hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], hp["wd"])
     x, t = models.synthetic_batch(cfg, batch, seed + 1, uniform01=(workload == "small_cnn"))
+    extra = dict(buffers=models.bn_buffers(cfg["layers"]), rng={"seed": seed, "offset": 0})
     for _ in range(max(0, warmup)):
-        models.train_step(o, cfg["layers"], params, opt, x, t)
+        models.train_step(o, cfg["layers"], params, opt, x, t, **extra)
     done = 0
     t0 = time.perf_counter()
     while done < steps or (time.perf_counter() - t0) < min_seconds:
-        models.train_step(o, cfg["layers"], params, opt, x, t)
+        models.train_step(o, cfg["layers"], params, opt, x, t, **extra)
         done += 1
         if done >= steps and min_seconds <= 0:
             break
@@ -203,6 +207,52 @@ def conv_microbench(ctx, stream, iters=10):
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / iters
         out[name] = {"ms": ms, "tflops": flop / (ms / 1e3) / 1e12}
+    return out
+
+
+def batchnorm_microbench(ctx, stream, hbm_peak_gbs, iters=10):
+    """BatchNorm2d (training mode) and Dropout on the conv microbenchmark's activation shape [256,64,32,32]
+    through the raw C ABI.  HBM-bound: the algorithmic bytes are one read of every input tensor and one write
+    of every output tensor (forward x -> y, xhat: 3 tensors; backward g, xhat -> dx: 3 tensors; dropout
+    a, mask -> out: 3 tensors); the kernels read their inputs twice (statistics, then the elementwise pass),
+    which the fraction shows."""
+    import ctypes as C
+    import torch
+    from neuralrs_b200 import _lib
+    l = _lib.lib()
+    n, c, h, w = 256, 64, 32, 32
+    g = torch.Generator(device="cuda").manual_seed(1240)
+    x = torch.randn(n, c, h, w, device="cuda", generator=g) * 2 + 1
+    dy = torch.randn(n, c, h, w, device="cuda", generator=g)
+    gamma, beta = torch.ones(c, device="cuda"), torch.zeros(c, device="cuda")
+    rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    y, xhat, dx, mask = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+    istd, dg, db = torch.empty(c, device="cuda"), torch.empty(c, device="cuda"), torch.empty(c, device="cuda")
+    P = lambda t: C.c_void_p(t.data_ptr())
+    F = C.c_float
+    tensor_bytes = x.numel() * 4
+    calls = {
+        "bn_fwd": (3, lambda: l.nrs_batchnorm_fwd(ctx.h, P(x), P(gamma), P(beta), P(rm), P(rv), P(y), P(xhat), P(istd),
+                                                  n, c, h * w, F(1e-5), F(0.9), 1)),
+        "bn_bwd": (3, lambda: l.nrs_batchnorm_bwd(ctx.h, P(dy), P(xhat), P(istd), P(gamma), P(dx), P(dg), P(db),
+                                                  n, c, h * w, 1, 0, 0)),
+        "dropout_mask": (1, lambda: l.nrs_dropout_mask(ctx.h, P(mask), x.numel(), F(0.3))),
+        "mask_mul": (3, lambda: l.nrs_mask_mul(ctx.h, P(x), P(mask), P(y), x.numel(), 1, 0)),
+    }
+    out = {"shape": "x[256,64,32,32]", "tensor_mb": tensor_bytes / 1e6, "hbm_peak_gbs": hbm_peak_gbs}
+    for name, (tensors, fn) in calls.items():
+        for _ in range(3):
+            _lib.check(ctx.h, fn())
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            _lib.check(ctx.h, fn())
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        gbs = tensors * tensor_bytes / (ms / 1e3) / 1e9
+        out[name] = {"ms": ms, "algorithmic_gbs": gbs, "frac": gbs / hbm_peak_gbs}
     return out
 
 
@@ -319,6 +369,18 @@ def run_ours(args):
     dev_step = lambda i: tr.step_device(xs_dev[i % n_sets].data_ptr(), ts_dev[i % n_sets].data_ptr(), batch, False)
     host_step = lambda i: tr.step_ptr(xs_pin[i % n_sets].data_ptr(), ts_pin[i % n_sets].data_ptr(), batch, True)
 
+    def staged_loop(total):
+        """End-to-end steps with the input copy double-buffered: batch i+1 is staged (asynchronous copy from
+        pinned memory on the copy stream) before step i is issued; every step still reads its loss back."""
+        def fn(i):
+            if i == 0:
+                tr.stage_next_ptr(xs_pin[0].data_ptr(), ts_pin[0].data_ptr(), batch)
+            if i + 1 < total:
+                j = (i + 1) % n_sets
+                tr.stage_next_ptr(xs_pin[j].data_ptr(), ts_pin[j].data_ptr(), batch)
+            tr.step_staged(True)
+        return fn
+
     for i in range(max(3, args.warmup)):
         dev_step(i)
     l = _lib.lib()
@@ -348,7 +410,11 @@ def run_ours(args):
 
     for i in range(2):
         host_step(i)
-    ms_e2e = timed(host_step, args.steps)
+    ms_e2e_plain = timed(host_step, args.steps)
+    warm = staged_loop(2)
+    for i in range(2):
+        warm(i)
+    ms_e2e = timed(staged_loop(args.steps), args.steps)
 
     if rank == 0:
         peaks = measured_peaks()
@@ -378,7 +444,10 @@ def run_ours(args):
                        "tensor_core_path": bool(l.nrs_has_tensor_core_path())},
             "loss": loss,
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": x_bytes + t_bytes, "d2h_bytes_per_step": 4 * world},
+                    "h2d_bytes_per_step": x_bytes + t_bytes, "d2h_bytes_per_step": 4 * world,
+                    "api": "nrs_trainer_stage_next + nrs_trainer_step_staged: the copy of batch i+1 overlaps step i",
+                    "unpipelined_value": global_batch * args.steps / (ms_e2e_plain / 1e3),
+                    "unpipelined_api": "nrs_trainer_step: copy, step and loss read-back in sequence"},
             "gpu_launches": launches * world,
             "clocks": clk.summary(),
             "roofline": {"bound": "tensor", "kernel": fam, "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
@@ -395,6 +464,7 @@ def run_ours(args):
         }
         if world == 1 and args.workload == "vgg_cifar":
             line["conv_microbench"] = conv_microbench(ctx, stream)
+            line["batchnorm_microbench"] = batchnorm_microbench(ctx, stream, peaks["hbm_gbs"])
         if world == 1 and not args.no_cpu_baseline:
             r = cpu_reference_run(args.workload, 1, 1, min_seconds=10.0)
             line["cpu_baseline"] = {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "port",

@@ -149,14 +149,21 @@ enum nrs_layer_kind {
   NRS_LAYER_MAXPOOL = 2,  /* a=kernel b=stride                                   */
   NRS_LAYER_FLATTEN = 3,
   NRS_LAYER_LINEAR = 4,   /* a=in b=out                                          */
-  NRS_LAYER_GELU = 5
+  NRS_LAYER_GELU = 5,
+  NRS_LAYER_BATCHNORM = 6, /* a=channels (features after flatten): BatchNorm2d on [C,H,W], BatchNorm on [F];
+                              momentum 0.9, eps 1e-5 unless nrs_trainer_set_batchnorm says otherwise */
+  NRS_LAYER_DROPOUT = 7,   /* a=drop probability in parts per million (500000 = 0.5) */
+  NRS_LAYER_DROPOUT2D = 8  /* a=as above; whole (sample, channel) planes             */
 };
 typedef struct nrs_layer_spec { int kind, a, b, c, d, e; } nrs_layer_spec;
 
 /* in_shape: per-sample input shape (e.g. {3,32,32}).  fuse != 0 folds a ReLU
  * that follows a conv/linear layer into that layer's kernel.  Parameters are
- * created zero-filled in layer order [w0,b0,w1,b1,...] inside one flat block;
- * fill them with nrs_trainer_set_param. */
+ * created zero-filled in layer order [w0,b0,w1,b1,...] inside one flat block
+ * (a batchnorm layer adds [gamma,beta]); fill them with nrs_trainer_set_param.
+ * The running statistics of batchnorm layers are buffers [mean0,var0,mean1,...],
+ * created at 0 / 1, updated by training-mode steps, never touched by the
+ * optimizer (examples/cifar_cuda.rs:44-66 keeps them out of `trainable`). */
 int nrs_trainer_create(nrs_ctx* ctx, const nrs_layer_spec* layers, int n_layers, const int64_t* in_shape,
                        int in_ndim, int classes, float lr, float beta1, float beta2, float eps,
                        float weight_decay, int fuse, nrs_trainer** out);
@@ -166,6 +173,14 @@ int64_t nrs_trainer_param_len(const nrs_trainer* t, int i);
 int nrs_trainer_set_param(nrs_trainer* t, int i, const float* host);
 int nrs_trainer_get_param(nrs_trainer* t, int i, float* host_out);
 int nrs_trainer_get_grad(nrs_trainer* t, int i, float* host_out);
+int nrs_trainer_buffer_count(const nrs_trainer* t);
+int64_t nrs_trainer_buffer_len(const nrs_trainer* t, int i);
+int nrs_trainer_set_buffer(nrs_trainer* t, int i, const float* host);
+int nrs_trainer_get_buffer(nrs_trainer* t, int i, float* host_out);
+/* Training (default) or evaluation mode of the batchnorm and dropout layers
+ * (`training` of src/cuda/nn/batchnorm2d.rs:139 and dropout.rs:31). */
+int nrs_trainer_set_training(nrs_trainer* t, int training);
+int nrs_trainer_set_batchnorm(nrs_trainer* t, float momentum, float eps);
 /* zero_grad + forward + cross-entropy + backward (no optimizer step).
  * x_host [batch, in_shape...] and target_host [batch, classes] (one-hot f32) are
  * HOST buffers copied to the device inside the call; loss_out (host) may be
@@ -175,6 +190,18 @@ int nrs_trainer_forward_backward(nrs_trainer* t, const float* x_host, const floa
 /* A full training step: the above plus the gradient all-reduce (when data
  * parallel) and one fused AdamW update. */
 int nrs_trainer_step(nrs_trainer* t, const float* x_host, const float* target_host, int batch, float* loss_out);
+/* The same step with its input copy taken off the critical path (the reference
+ * uploads synchronously at the top of every step, src/cuda/runtime.rs:43).
+ * nrs_trainer_stage_next starts an asynchronous copy of a batch from host memory
+ * (pinned, for the copy to overlap) into the idle one of two device slots on a
+ * copy stream and returns at once; nrs_trainer_step_staged runs a full training
+ * step on the oldest staged batch as soon as its copy has landed.  Staging batch
+ * i+1 before stepping batch i overlaps the copy with the step; at most two
+ * batches can be staged and unconsumed (a third is refused with NRS_ERR_ARG).
+ * The host buffers must stay valid and unchanged until the step that consumes
+ * them has been issued and the stream synchronised (loss_out != NULL does that). */
+int nrs_trainer_stage_next(nrs_trainer* t, const float* x_host, const float* target_host, int batch);
+int nrs_trainer_step_staged(nrs_trainer* t, float* loss_out);
 /* Same step on inputs already resident on the device. */
 int nrs_trainer_step_device(nrs_trainer* t, const float* x_dev, const float* target_dev, int batch,
                             float* loss_out);

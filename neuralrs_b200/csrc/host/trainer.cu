@@ -96,12 +96,29 @@ struct nrs_trainer {
   int classes = 0;
   bool fuse = false;
   std::vector<NodeP> params;            // [w0,b0,w1,b1,...]
+  std::vector<NodeP> buffers;           // running statistics of the batchnorm layers [mean0,var0,...]
+  bool training = true;
+  float bn_momentum = 0.9f, bn_eps = 1e-5f;
   std::shared_ptr<nrs::FlatStore> flat;
   std::unique_ptr<nrs::cuda::AdamW> opt;
   float* loss_dev = nullptr;
   // staging for host inputs (grow-only device buffers)
   float* x_dev = nullptr; size_t x_cap = 0;
   float* t_dev = nullptr; size_t t_cap = 0;
+  // Double-buffered input staging (nrs_trainer_stage_next / nrs_trainer_step_staged): while the compute
+  // stream works on one slot, the copy stream fills the other from host memory.  The slots are plain
+  // cudaMalloc blocks, not pool blocks: the pool recycles in compute-stream order, which a second stream
+  // writing into a recycled block would violate.
+  struct Slot {
+    float* x = nullptr; size_t x_cap = 0;
+    float* t = nullptr; size_t t_cap = 0;
+    int batch = 0;
+    bool pending = false, used = false;
+    cudaEvent_t filled = nullptr, consumed = nullptr;
+  };
+  Slot slots[2];
+  int fill_idx = 0, run_idx = 0;
+  cudaStream_t copy_stream = nullptr;
   // data parallel
   int rank = 0, world = 1, global_batch = 0;
   ncclComm_p comm = nullptr;
@@ -113,8 +130,16 @@ struct nrs_trainer {
     if (comm_stream) cudaStreamDestroy(comm_stream);
     if (ready_ev) cudaEventDestroy(ready_ev);
     if (done_ev) cudaEventDestroy(done_ev);
+    if (copy_stream) { cudaStreamSynchronize(copy_stream); cudaStreamDestroy(copy_stream); }
+    for (Slot& sl : slots) {
+      if (sl.filled) cudaEventDestroy(sl.filled);
+      if (sl.consumed) cudaEventDestroy(sl.consumed);
+      if (sl.x) cudaFree(sl.x);
+      if (sl.t) cudaFree(sl.t);
+    }
     opt.reset();
     params.clear();
+    buffers.clear();
     flat.reset();
     if (ctx) {
       if (loss_dev) nrs_free(ctx, loss_dev);
@@ -164,6 +189,25 @@ void validate_and_build_params(nrs_trainer* t) {
       case NRS_LAYER_RELU:
       case NRS_LAYER_GELU:
         break;
+      case NRS_LAYER_BATCHNORM: {
+        if ((shp.size() != 3 && shp.size() != 1) || l.a != (int)shp[0])
+          fail(NRS_ERR_SHAPE, "trainer: batchnorm channels do not match the incoming [C,H,W] or [F]");
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.a}));   // gamma
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.a}));   // beta
+        std::vector<float> zeros((size_t)l.a, 0.0f), ones((size_t)l.a, 1.0f);
+        for (const std::vector<float>* init : {&zeros, &ones}) {
+          NodeP b = nrs::node_new(t->ctx, init->data(), {(size_t)l.a});
+          b->requires_grad = false;
+          nrs::cuda::to_cuda(b);
+          t->buffers.push_back(b);
+        }
+        break;
+      }
+      case NRS_LAYER_DROPOUT:
+      case NRS_LAYER_DROPOUT2D:
+        if (l.a < 0 || l.a > 1000000) fail(NRS_ERR_ARG, "trainer: dropout probability outside [0, 1000000] ppm");
+        if (l.kind == NRS_LAYER_DROPOUT2D && shp.size() != 3) fail(NRS_ERR_SHAPE, "trainer: dropout2d needs a [C,H,W] input");
+        break;
       default:
         fail(NRS_ERR_ARG, "trainer: unknown layer kind");
     }
@@ -181,7 +225,7 @@ void validate_and_build_params(nrs_trainer* t) {
 
 NodeP forward(nrs_trainer* t, const NodeP& x) {
   NodeP h = x;
-  size_t pi = 0;
+  size_t pi = 0, bi = 0;
   for (size_t li = 0; li < t->layers.size(); ++li) {
     const nrs_layer_spec& l = t->layers[li];
     const bool relu_next = t->fuse && li + 1 < t->layers.size() && t->layers[li + 1].kind == NRS_LAYER_RELU;
@@ -216,6 +260,17 @@ NodeP forward(nrs_trainer* t, const NodeP& x) {
         break;
       }
       case NRS_LAYER_FLATTEN: h = nrs::cuda::flatten(h); break;
+      case NRS_LAYER_BATCHNORM:
+        h = h->shape.size() == 4
+                ? nrs::cuda::batchnorm2d(h, t->params[pi], t->params[pi + 1], t->buffers[bi], t->buffers[bi + 1],
+                                         t->bn_momentum, t->bn_eps, t->training)
+                : nrs::cuda::batchnorm(h, t->params[pi], t->params[pi + 1], t->buffers[bi], t->buffers[bi + 1],
+                                       t->bn_momentum, t->bn_eps, t->training);
+        pi += 2;
+        bi += 2;
+        break;
+      case NRS_LAYER_DROPOUT: h = nrs::cuda::dropout(h, (float)l.a * 1e-6f, t->training); break;
+      case NRS_LAYER_DROPOUT2D: h = nrs::cuda::dropout2d(h, (float)l.a * 1e-6f, t->training); break;
     }
   }
   return h;
@@ -320,6 +375,64 @@ void stage(nrs_trainer* t, float** buf, size_t* cap, const float* host, size_t f
   nrs::check(t->ctx, nrs_h2d(t->ctx, *buf, host, floats * sizeof(float)));
 }
 
+void cuda_ok(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) fail(NRS_ERR_CUDA, std::string("trainer: ") + what + " failed: " + cudaGetErrorString(e));
+}
+
+// Grows a staging block.  Growth is rare (the first batch, or a larger one): it waits for everything in
+// flight so that nothing still reads the old block.
+void grow_slot_block(float** buf, size_t* cap, size_t floats) {
+  if (floats <= *cap) return;
+  cuda_ok(cudaDeviceSynchronize(), "synchronize before growing a staging block");
+  if (*buf) cuda_ok(cudaFree(*buf), "cudaFree of a staging block");
+  *buf = nullptr;
+  *cap = 0;
+  void* p = nullptr;
+  if (cudaMalloc(&p, floats * sizeof(float)) != cudaSuccess) {
+    cudaGetLastError();
+    fail(NRS_ERR_ALLOC, "trainer: out of device memory for an input staging block");
+  }
+  *buf = (float*)p;
+  *cap = floats;
+}
+
+void stage_next(nrs_trainer* t, const float* x_host, const float* target_host, int batch) {
+  if (batch <= 0) fail(NRS_ERR_SHAPE, "trainer: batch must be positive");
+  nrs_trainer::Slot& sl = t->slots[t->fill_idx];
+  if (sl.pending) fail(NRS_ERR_ARG, "trainer: both staging slots hold a batch that no step has consumed yet");
+  if (!t->copy_stream) cuda_ok(cudaStreamCreateWithFlags(&t->copy_stream, cudaStreamNonBlocking), "copy stream creation");
+  if (!sl.filled) {
+    cuda_ok(cudaEventCreateWithFlags(&sl.filled, cudaEventDisableTiming), "event creation");
+    cuda_ok(cudaEventCreateWithFlags(&sl.consumed, cudaEventDisableTiming), "event creation");
+  }
+  size_t per = 1;
+  for (size_t d : t->in_shape) per *= d;
+  grow_slot_block(&sl.x, &sl.x_cap, per * batch);
+  grow_slot_block(&sl.t, &sl.t_cap, (size_t)t->classes * batch);
+  // the step that last read this slot must have finished with it
+  if (sl.used) cuda_ok(cudaStreamWaitEvent(t->copy_stream, sl.consumed, 0), "wait for the slot's last consumer");
+  cuda_ok(cudaMemcpyAsync(sl.x, x_host, per * batch * sizeof(float), cudaMemcpyHostToDevice, t->copy_stream), "input copy");
+  cuda_ok(cudaMemcpyAsync(sl.t, target_host, (size_t)t->classes * batch * sizeof(float), cudaMemcpyHostToDevice, t->copy_stream),
+          "target copy");
+  cuda_ok(cudaEventRecord(sl.filled, t->copy_stream), "event record");
+  sl.batch = batch;
+  sl.pending = true;
+  t->fill_idx ^= 1;
+}
+
+
+void step_staged(nrs_trainer* t, float* loss_out) {
+  nrs_trainer::Slot& sl = t->slots[t->run_idx];
+  if (!sl.pending) fail(NRS_ERR_ARG, "trainer: no staged batch (call nrs_trainer_stage_next first)");
+  cuda_ok(cudaStreamWaitEvent(t->ctx->stream, sl.filled, 0), "wait for the staged batch");
+  run_step(t, sl.x, sl.t, sl.batch, true);
+  cuda_ok(cudaEventRecord(sl.consumed, t->ctx->stream), "event record");
+  sl.pending = false;
+  sl.used = true;
+  t->run_idx ^= 1;
+  if (loss_out) nrs::check(t->ctx, nrs_d2h(t->ctx, loss_out, t->loss_dev, sizeof(float)));
+}
+
 template <class F>
 int guarded(nrs_ctx* ctx, F&& f) {
   try {
@@ -387,6 +500,41 @@ int nrs_trainer_free(nrs_trainer* t) {
 
 int nrs_trainer_param_count(const nrs_trainer* t) { return t ? (int)t->params.size() : -1; }
 
+int nrs_trainer_buffer_count(const nrs_trainer* t) { return t ? (int)t->buffers.size() : -1; }
+
+int64_t nrs_trainer_buffer_len(const nrs_trainer* t, int i) {
+  return (t && i >= 0 && i < (int)t->buffers.size()) ? (int64_t)t->buffers[i]->len() : -1;
+}
+
+int nrs_trainer_set_buffer(nrs_trainer* t, int i, const float* host) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_set_buffer: null handle");
+  NRS_REQUIRE(t->ctx, host && i >= 0 && i < (int)t->buffers.size(), NRS_ERR_ARG, "nrs_trainer_set_buffer: bad index or null data");
+  int st = nrs_h2d(t->ctx, t->buffers[i]->data, host, t->buffers[i]->len() * sizeof(float));
+  if (st == NRS_OK) st = nrs_sync(t->ctx);
+  return st;
+}
+
+int nrs_trainer_get_buffer(nrs_trainer* t, int i, float* host_out) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_get_buffer: null handle");
+  NRS_REQUIRE(t->ctx, host_out && i >= 0 && i < (int)t->buffers.size(), NRS_ERR_ARG, "nrs_trainer_get_buffer: bad index or null output");
+  return nrs_d2h(t->ctx, host_out, t->buffers[i]->data, t->buffers[i]->len() * sizeof(float));
+}
+
+int nrs_trainer_set_training(nrs_trainer* t, int training) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_set_training: null handle");
+  t->training = training != 0;
+  return NRS_OK;
+}
+
+int nrs_trainer_set_batchnorm(nrs_trainer* t, float momentum, float eps) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_set_batchnorm: null handle");
+  NRS_REQUIRE(t->ctx, momentum >= 0.0f && momentum <= 1.0f && eps > 0.0f, NRS_ERR_ARG,
+              "nrs_trainer_set_batchnorm: momentum must lie in [0,1] and eps must be positive");
+  t->bn_momentum = momentum;
+  t->bn_eps = eps;
+  return NRS_OK;
+}
+
 int64_t nrs_trainer_param_len(const nrs_trainer* t, int i) {
   return (t && i >= 0 && i < (int)t->params.size()) ? (int64_t)t->params[i]->len() : -1;
 }
@@ -420,6 +568,17 @@ int nrs_trainer_forward_backward(nrs_trainer* t, const float* x_host, const floa
 
 int nrs_trainer_step(nrs_trainer* t, const float* x_host, const float* target_host, int batch, float* loss_out) {
   return host_step(t, x_host, target_host, batch, loss_out, true);
+}
+
+int nrs_trainer_stage_next(nrs_trainer* t, const float* x_host, const float* target_host, int batch) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_stage_next: null handle");
+  if (!x_host || !target_host) return nrs_fail(t->ctx, NRS_ERR_ARG, "nrs_trainer_stage_next: null input");
+  return guarded(t->ctx, [&] { stage_next(t, x_host, target_host, batch); });
+}
+
+int nrs_trainer_step_staged(nrs_trainer* t, float* loss_out) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_step_staged: null handle");
+  return guarded(t->ctx, [&] { step_staged(t, loss_out); });
 }
 
 int nrs_trainer_step_device(nrs_trainer* t, const float* x_dev, const float* target_dev, int batch, float* loss_out) {

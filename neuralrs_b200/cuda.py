@@ -440,7 +440,8 @@ class optim:
             self.h = None
 
 
-LAYER_KINDS = {"conv": 0, "relu": 1, "maxpool": 2, "flatten": 3, "linear": 4, "gelu": 5}
+LAYER_KINDS = {"conv": 0, "relu": 1, "maxpool": 2, "flatten": 3, "linear": 4, "gelu": 5, "batchnorm": 6, "dropout": 7,
+               "dropout2d": 8}
 
 
 class _LayerSpec(C.Structure):
@@ -451,7 +452,8 @@ class Trainer:
     """Native training loop for a sequential model (include/nrs_graph.h, nrs_trainer_*).
 
     `layers` uses the tuples ("conv", c_in, c_out, k, stride, pad), ("relu",), ("gelu",),
-    ("maxpool", k, stride), ("flatten",), ("linear", n_in, n_out).
+    ("maxpool", k, stride), ("flatten",), ("linear", n_in, n_out), ("batchnorm", channels),
+    ("dropout", p), ("dropout2d", p).
     """
 
     def __init__(self, layers, in_shape, classes, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=1e-4,
@@ -460,7 +462,10 @@ class Trainer:
         l = self.ctx._l
         specs = (_LayerSpec * len(layers))()
         for i, ly in enumerate(layers):
-            vals = [LAYER_KINDS[ly[0]]] + [int(v) for v in ly[1:]]
+            if ly[0] in ("dropout", "dropout2d"):      # the probability crosses as parts per million
+                vals = [LAYER_KINDS[ly[0]], int(round(float(ly[1]) * 1e6))]
+            else:
+                vals = [LAYER_KINDS[ly[0]]] + [int(v) for v in ly[1:]]
             vals += [0] * (6 - len(vals))
             specs[i] = _LayerSpec(*vals)
         shp = (C.c_int64 * len(in_shape))(*[int(s) for s in in_shape])
@@ -496,6 +501,24 @@ class Trainer:
         check(self.ctx.h, self.ctx._l.nrs_trainer_get_grad(self.h, i, _ptr(out)))
         return out
 
+    @property
+    def n_buffers(self) -> int:
+        return int(self.ctx._l.nrs_trainer_buffer_count(self.h))
+
+    def get_buffer(self, i: int) -> np.ndarray:
+        """Running statistics of the batchnorm layers: [mean0, var0, mean1, var1, ...]."""
+        out = np.empty(int(self.ctx._l.nrs_trainer_buffer_len(self.h, i)), np.float32)
+        check(self.ctx.h, self.ctx._l.nrs_trainer_get_buffer(self.h, i, _ptr(out)))
+        return out
+
+    def set_buffer(self, i: int, values):
+        a = _f32(values).reshape(-1)
+        assert a.size == int(self.ctx._l.nrs_trainer_buffer_len(self.h, i))
+        check(self.ctx.h, self.ctx._l.nrs_trainer_set_buffer(self.h, i, _ptr(a)))
+
+    def set_training(self, training: bool):
+        check(self.ctx.h, self.ctx._l.nrs_trainer_set_training(self.h, int(bool(training))))
+
     def _host_call(self, fn, x, target, want_loss):
         x, target = _f32(x), _f32(target)
         batch = x.shape[0]
@@ -514,6 +537,24 @@ class Trainer:
         loss = C.c_float()
         check(self.ctx.h, self.ctx._l.nrs_trainer_step(self.h, VP(x_host_ptr), VP(target_host_ptr), int(batch),
                                                        C.byref(loss) if want_loss else None))
+        return float(loss.value) if want_loss else None
+
+    def stage_next_ptr(self, x_host_ptr: int, target_host_ptr: int, batch: int):
+        """Starts the asynchronous copy of a batch from (pinned) HOST pointers into the idle staging slot."""
+        check(self.ctx.h, self.ctx._l.nrs_trainer_stage_next(self.h, VP(x_host_ptr), VP(target_host_ptr), int(batch)))
+
+    def stage_next(self, x, target):
+        """As stage_next_ptr for numpy arrays; the arrays are kept alive until their step has been issued."""
+        x, target = _f32(x), _f32(target)
+        self._staged = getattr(self, "_staged", []) + [(x, target)]
+        self.stage_next_ptr(x.ctypes.data, target.ctypes.data, x.shape[0])
+
+    def step_staged(self, want_loss=True):
+        """A full training step on the oldest staged batch."""
+        loss = C.c_float()
+        check(self.ctx.h, self.ctx._l.nrs_trainer_step_staged(self.h, C.byref(loss) if want_loss else None))
+        if want_loss and getattr(self, "_staged", None):
+            self._staged.pop(0)   # the step has run to completion: its host arrays may go
         return float(loss.value) if want_loss else None
 
     def step_device(self, x_dev_ptr: int, target_dev_ptr: int, batch: int, want_loss=False):

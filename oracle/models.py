@@ -10,9 +10,14 @@ A model is a list of layer tuples, applied in order, exactly as the reference's
     ("maxpool", k, stride)                   MaxPool2d       src/nn/maxpool.rs
     ("flatten",)                             Flatten         src/nn/flatten.rs
     ("linear", n_in, n_out)                  Linear          src/nn/linear.rs (matmul + bias add)
+    ("batchnorm", c)                         BatchNorm / BatchNorm2d  src/nn/batchnorm.rs, batchnorm2d.rs
+                                             (momentum 0.9, eps 1e-5 as in examples/cifar_cuda.rs:44-48)
+    ("dropout", p) / ("dropout2d", p)        Dropout / Dropout2d      src/nn/dropout.rs, dropout2d.rs
 
 Parameters are a flat list [w0, b0, w1, b1, ...] in layer order — the order
-``ADAMW::step`` flattens them in (src/optim/adamw.rs:48-54).
+``ADAMW::step`` flattens them in (src/optim/adamw.rs:48-54); a batchnorm layer adds
+[gamma, beta].  Its running statistics are buffers, not parameters: a separate list
+[mean0, var0, mean1, var1, ...] that training-mode forward passes update in place.
 """
 from __future__ import annotations
 
@@ -31,6 +36,20 @@ VGG_CIFAR = dict(
             ("conv", 64, 128, 3, 1, 1), ("relu",), ("conv", 128, 128, 3, 1, 1), ("relu",), ("maxpool", 2, 2),
             ("conv", 128, 256, 3, 1, 1), ("relu",), ("conv", 256, 256, 3, 1, 1), ("relu",), ("maxpool", 2, 2),
             ("flatten",), ("linear", 4096, 512), ("relu",), ("linear", 512, 10)])
+
+# The model of the reference's examples/cifar_cuda.rs:99-136: conv + BatchNorm2d + ReLU units, and a
+# Linear -> BatchNorm -> ReLU -> Dropout(0.5) -> Linear head.
+def _conv_bn(ci, co):
+    return [("conv", ci, co, 3, 1, 1), ("batchnorm", co), ("relu",)]
+
+
+VGG_CIFAR_BN = dict(
+    name="vgg_cifar_bn", in_shape=(3, 32, 32), classes=10,
+    layers=_conv_bn(3, 64) + _conv_bn(64, 64) + [("maxpool", 2, 2)] + _conv_bn(64, 128) + _conv_bn(128, 128)
+    + [("maxpool", 2, 2)] + _conv_bn(128, 256) + _conv_bn(256, 256) + [("maxpool", 2, 2)]
+    + [("flatten",), ("linear", 4096, 512), ("batchnorm", 512), ("relu",), ("dropout", 0.5), ("linear", 512, 10)])
+
+BN_MOMENTUM, BN_EPS = 0.9, 1e-5
 
 WIDE_MLP = dict(
     name="wide_mlp", in_shape=(4096,), classes=1000,
@@ -54,7 +73,19 @@ def he_init(layers, seed: int):
             _, n_in, n_out = l
             params.append((rng.standard_normal((n_in, n_out)) * np.sqrt(2.0 / n_in)).astype(np.float32))
             params.append(np.zeros(n_out, np.float32))
+        elif l[0] == "batchnorm":   # gamma = 1, beta = 0 (examples/cifar_cuda.rs:42)
+            params.append(np.ones(l[1], np.float32))
+            params.append(np.zeros(l[1], np.float32))
     return params
+
+
+def bn_buffers(layers):
+    """Running statistics of the batchnorm layers, [mean0, var0, ...], at their initial 0 / 1."""
+    out = []
+    for l in layers:
+        if l[0] == "batchnorm":
+            out += [np.zeros(l[1], np.float32), np.ones(l[1], np.float32)]
+    return out
 
 
 def synthetic_batch(cfg, batch: int, seed: int, uniform01: bool = False):
@@ -68,15 +99,20 @@ def synthetic_batch(cfg, batch: int, seed: int, uniform01: bool = False):
     return x, t
 
 
-def forward_backward(o, layers, params, x, target, divisor=None, input_requires_grad=False):
+def forward_backward(o, layers, params, x, target, divisor=None, input_requires_grad=False, buffers=None,
+                     training=True, rng=None):
     """One forward + backward pass; returns (loss, grads in parameter order, logits).
+
+    `buffers` (bn_buffers) are updated in place by training-mode batchnorm layers.  `rng` = {"seed", "offset"}
+    is the dropout mask stream (the device library's definition, nrs_oracle.c); each dropout layer consumes
+    ceil(mask_len / 4) counter blocks and advances the offset.
 
     Backward visits layers in reverse and ACCUMULATES into zeroed gradients, like
     zero_grad + loss_fn.backward + sync_grads (src/nn/sequential.rs:42-58,
     src/nn/loss.rs:78-107)."""
     acts = [np.ascontiguousarray(x, dtype=np.float32)]
     saved = []
-    pi = 0
+    pi = bi = 0
     for l in layers:
         a = acts[-1]
         if l[0] == "conv":
@@ -102,6 +138,25 @@ def forward_backward(o, layers, params, x, target, divisor=None, input_requires_
         elif l[0] == "flatten":
             saved.append(None)
             acts.append(a.reshape(a.shape[0], -1))
+        elif l[0] == "batchnorm":
+            y, xhat, istd, rm, rv = o.batchnorm_fwd(a, params[pi], params[pi + 1], buffers[bi], buffers[bi + 1],
+                                                    BN_EPS, BN_MOMENTUM, training)
+            buffers[bi][...], buffers[bi + 1][...] = rm, rv
+            saved.append((pi, xhat, istd))
+            pi += 2
+            bi += 2
+            acts.append(y)
+        elif l[0] in ("dropout", "dropout2d"):
+            if not training:
+                saved.append(None)
+                acts.append(a)
+                continue
+            hw = a.shape[2] * a.shape[3] if l[0] == "dropout2d" else 1
+            mask_len = a.size // hw
+            mask = o.dropout_mask(mask_len, l[1], rng["seed"], rng["offset"])
+            rng["offset"] += (mask_len + 3) // 4
+            saved.append((mask, hw))
+            acts.append(o.mask_mul(a, mask, hw))
         else:
             raise ValueError(l)
     logits = acts[-1]
@@ -132,6 +187,15 @@ def forward_backward(o, layers, params, x, target, divisor=None, input_requires_
             g = o.maxpool_bwd(g, saved[li], a_in.shape)
         elif l[0] == "flatten":
             g = g.reshape(a_in.shape)
+        elif l[0] == "batchnorm":
+            pidx, xhat, istd = saved[li]
+            dx, dg, db = o.batchnorm_bwd(g, xhat, istd, params[pidx], training)
+            grads[pidx] += dg
+            grads[pidx + 1] += db
+            g = dx
+        elif l[0] in ("dropout", "dropout2d"):
+            if saved[li] is not None:
+                g = o.mask_mul(g, saved[li][0], saved[li][1])
     return loss, grads, logits
 
 
@@ -150,8 +214,8 @@ class OracleAdamW:
         self.t += 1
 
 
-def train_step(o, layers, params, opt, x, target):
+def train_step(o, layers, params, opt, x, target, buffers=None, rng=None):
     """zero_grad -> forward -> loss -> backward -> optimizer.step; returns the loss."""
-    loss, grads, _ = forward_backward(o, layers, params, x, target)
+    loss, grads, _ = forward_backward(o, layers, params, x, target, buffers=buffers, rng=rng)
     opt.step(params, grads)
     return loss

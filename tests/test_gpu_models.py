@@ -85,3 +85,127 @@ def test_loss_decreases_over_steps(gpu_ctx):
     losses = [tr.step(x, t) for _ in range(30)]
     assert losses[-1] < 0.5 * losses[0]
     tr.close()
+
+
+BN_SMALL = dict(
+    name="bn_small", in_shape=(3, 16, 16), classes=10,
+    layers=[("conv", 3, 32, 3, 1, 1), ("batchnorm", 32), ("relu",), ("conv", 32, 32, 3, 1, 1), ("batchnorm", 32), ("relu",),
+            ("dropout2d", 0.25), ("maxpool", 2, 2), ("flatten",), ("linear", 2048, 64), ("batchnorm", 64), ("relu",),
+            ("dropout", 0.5), ("linear", 64, 10)])
+
+
+def _bn_model_parity(gpu_ctx, oracle64, cfg, batch, seed, mode, tol):
+    """Trainer vs oracle on a model with BatchNorm and Dropout layers: loss, gradients, running statistics,
+    two optimizer steps, then an evaluation-mode pass.  The dropout masks come from the same (seed, offset)
+    stream on both sides."""
+    l = _lib.lib()
+    gpu_ctx.set_math_mode(mode)
+    try:
+        layers = cfg["layers"]
+        params = models.he_init(layers, seed)
+        rng = np.random.default_rng(seed + 1)
+        params = [p if p.ndim > 1 else (p + rng.standard_normal(p.shape) * 0.05).astype(np.float32) for p in params]
+        x, t = models.synthetic_batch(cfg, batch, seed + 2)
+        hp = models.ADAMW_HP
+        tr = cuda.Trainer(layers, cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], hp["wd"],
+                          fuse=True, ctx=gpu_ctx)
+        tr.set_params(params)
+        assert tr.n_buffers == 2 * sum(1 for ly in layers if ly[0] == "batchnorm")
+        _lib.check(gpu_ctx.h, l.nrs_rng_seed(gpu_ctx.h, 4242))
+        stream = {"seed": 4242, "offset": 0}
+        ref_params, buffers = [p.copy() for p in params], models.bn_buffers(layers)
+        loss_ref, grads_ref, _ = models.forward_backward(oracle64, layers, ref_params, x, t, buffers=buffers, rng=stream)
+        loss = tr.forward_backward(x, t)
+        assert abs(loss - loss_ref) <= tol * max(1.0, abs(loss_ref)), (loss, loss_ref)
+        # a bias in front of a BatchNorm has a mathematically zero gradient (the layer removes the mean): both
+        # sides hold rounding noise there, compared on the scale of the weight gradient beside it
+        pi, cancelled = 0, set()
+        for li, ly in enumerate(layers):
+            if ly[0] in ("conv", "linear"):
+                if li + 1 < len(layers) and layers[li + 1][0] == "batchnorm":
+                    cancelled.add(pi + 1)
+                pi += 2
+            elif ly[0] == "batchnorm":
+                pi += 2
+        for i, g in enumerate(grads_ref):
+            got = tr.get_grad(i)
+            if i in cancelled:
+                assert np.abs(got - g.ravel()).max() <= tol * np.abs(grads_ref[i - 1]).max(), i
+            else:
+                assert rel_l2(got, g) <= tol, (i, rel_l2(got, g))
+        for i, b in enumerate(buffers):
+            assert np.abs(tr.get_buffer(i) - b).max() <= 1e-5 * max(1.0, np.abs(b).max()), i
+        opt = models.OracleAdamW(oracle64, hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], hp["wd"])
+        for _ in range(2):
+            lref = models.train_step(oracle64, layers, ref_params, opt, x, t, buffers=buffers, rng=stream)
+            lgot = tr.step(x, t)
+            assert abs(lgot - lref) <= 10 * tol * max(1.0, abs(lref))
+        off = __import__("ctypes").c_uint64()
+        _lib.check(gpu_ctx.h, l.nrs_rng_offset(gpu_ctx.h, __import__("ctypes").byref(off)))
+        assert off.value == stream["offset"]                      # three passes consumed the same stream length
+        # (after optimizer steps the parameters themselves agree to ~2.5*lr per step only, see run_parity, and
+        # a running mean is a cancelling sum of pre-activations: bounded absolutely, on the scale of the
+        # unit-variance activations it is the mean of)
+        for i, b in enumerate(buffers):
+            assert np.abs(tr.get_buffer(i) - b).max() <= 1e-3 * max(1.0, np.abs(b).max()), i
+        # evaluation mode: running statistics normalise, dropout passes through, nothing is updated
+        tr.set_training(False)
+        before = [tr.get_buffer(i).copy() for i in range(tr.n_buffers)]
+        eval_params = [tr.get_param(i).reshape(p.shape) for i, p in enumerate(ref_params)]
+        loss_eval_ref, _, _ = models.forward_backward(oracle64, layers, eval_params, x, t, buffers=[b.copy() for b in before],
+                                                      training=False)
+        loss_eval = tr.forward_backward(x, t)
+        assert abs(loss_eval - loss_eval_ref) <= tol * max(1.0, abs(loss_eval_ref))
+        assert all(np.array_equal(tr.get_buffer(i), b) for i, b in enumerate(before))
+        tr.close()
+    finally:
+        gpu_ctx.set_math_mode(_lib.MATH_3XTF32)
+
+
+@pytest.mark.parametrize("mode,tol", MODES[:2], ids=["fp32", "3xtf32"])
+def test_batchnorm_dropout_model(gpu_ctx, oracle64, mode, tol):
+    _bn_model_parity(gpu_ctx, oracle64, BN_SMALL, 16, 400, mode, tol)
+
+
+def test_vgg_batchnorm_model_of_the_reference_example(gpu_ctx, oracle64):
+    """The model of the reference's examples/cifar_cuda.rs (conv+BN+ReLU units, BN + Dropout head) at batch 8."""
+    _bn_model_parity(gpu_ctx, oracle64, models.VGG_CIFAR_BN, 8, 410, _lib.MATH_3XTF32, 1e-4)
+
+
+def test_staged_steps_equal_plain_steps(gpu_ctx):
+    """Double-buffered input staging changes when the copies run, not what is computed: four steps on four
+    different batches through stage_next / step_staged give bit-identical losses and parameters to the same
+    steps through the plain host entry point; a third unconsumed batch is refused."""
+    cfg = models.SMALL_CNN
+    hp = models.ADAMW_HP
+    params = models.he_init(cfg["layers"], 500)
+    batches = [models.synthetic_batch(cfg, 32 if i != 2 else 48, 510 + i, uniform01=True) for i in range(4)]
+
+    def make():
+        tr = cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
+                          hp["wd"], fuse=True, ctx=gpu_ctx)
+        tr.set_params(params)
+        return tr
+
+    plain = make()
+    losses_plain = [plain.step(x, t) for x, t in batches]
+    staged = make()
+    losses_staged = []
+    staged.stage_next(*batches[0])
+    for i in range(len(batches)):
+        if i + 1 < len(batches):
+            staged.stage_next(*batches[i + 1])          # copy of batch i+1 overlaps step i
+        losses_staged.append(staged.step_staged())
+    assert losses_staged == losses_plain
+    for i in range(plain.n_params):
+        assert np.array_equal(staged.get_param(i), plain.get_param(i))
+    # nothing staged: refused; three staged and unconsumed: the third is refused
+    with pytest.raises(_lib.NrsError):
+        staged.step_staged()
+    staged.stage_next(*batches[0])
+    staged.stage_next(*batches[1])
+    with pytest.raises(_lib.NrsError):
+        staged.stage_next(*batches[2])
+    assert staged.step_staged() is not None and staged.step_staged() is not None
+    plain.close()
+    staged.close()
