@@ -253,6 +253,21 @@ int nrs_dropout_mask(nrs_ctx* ctx, float* mask, size_t count, float p);
 int nrs_rng_seed(nrs_ctx* ctx, uint64_t seed);
 int nrs_rng_offset(nrs_ctx* ctx, uint64_t* offset);
 
+/* ------------------------------------------------------- input pipeline -- */
+
+/* `augment` of examples/cifar_cuda.rs:146-169 on a resident batch x[n,c,h,w] -> y:
+ * per image a horizontal flip (probability 1/2, when flip != 0) and a shift by
+ * (dx, dy) in [-max_shift, max_shift] with zero fill: y[ch,yy,xx] = x[ch, yy-dy,
+ * flip ? w-1-(xx-dx) : xx-dx].  Draws: Philox block (offset + image) of the
+ * context's stream (nrs_rng_seed): flip = top bit of word 0, dx = floor(u(word 1)
+ * * (2*max_shift+1)) - max_shift, dy likewise from word 2.  Consumes n blocks.
+ * x and y must not alias. */
+int nrs_augment_flip_shift(nrs_ctx* ctx, const float* x, float* y, int n, int c, int h, int w, int max_shift, int flip);
+/* One-hot f32 target rows from int32 class indices (what the reference's loaders
+ * hand to cross_entropy): out[b, k] = (labels[b] == k).  An index outside
+ * [0, classes) gives an all-zero row. */
+int nrs_onehot(nrs_ctx* ctx, const int32_t* labels, float* out, int batch, int classes);
+
 /* ------------------------------------------------------------ transformer -- */
 
 /* embed_forward / embed_backward (src/cuda/nn/embedding.rs:13-30): row gather

@@ -202,6 +202,15 @@ int nrs_trainer_step(nrs_trainer* t, const float* x_host, const float* target_ho
  * them has been issued and the stream synchronised (loss_out != NULL does that). */
 int nrs_trainer_stage_next(nrs_trainer* t, const float* x_host, const float* target_host, int batch);
 int nrs_trainer_step_staged(nrs_trainer* t, float* loss_out);
+/* As nrs_trainer_stage_next with int32 class indices instead of one-hot rows
+ * (batch * 4 bytes over the bus instead of batch * classes * 4); the step
+ * expands them on the device (nrs_onehot). */
+int nrs_trainer_stage_next_indexed(nrs_trainer* t, const float* x_host, const int32_t* labels_host, int batch);
+/* On-device augmentation of staged [C,H,W] batches in training mode
+ * (nrs_augment_flip_shift: shift by up to max_shift pixels, horizontal flip when
+ * flip != 0; examples/cifar_cuda.rs:146-169 does this on the host before the
+ * upload).  max_shift < 0 switches it off (the default). */
+int nrs_trainer_set_augment(nrs_trainer* t, int max_shift, int flip);
 /* Same step on inputs already resident on the device. */
 int nrs_trainer_step_device(nrs_trainer* t, const float* x_dev, const float* target_dev, int batch,
                             float* loss_out);

@@ -112,13 +112,17 @@ struct nrs_trainer {
   struct Slot {
     float* x = nullptr; size_t x_cap = 0;
     float* t = nullptr; size_t t_cap = 0;
+    float* labels = nullptr; size_t labels_cap = 0;   // int32 class indices (in a float-sized block) when `indexed`
     int batch = 0;
-    bool pending = false, used = false;
+    bool pending = false, used = false, indexed = false;
     cudaEvent_t filled = nullptr, consumed = nullptr;
   };
   Slot slots[2];
   int fill_idx = 0, run_idx = 0;
   cudaStream_t copy_stream = nullptr;
+  // On-device augmentation of staged batches (nrs_trainer_set_augment): off when max_shift < 0.
+  int aug_shift = -1, aug_flip = 0;
+  float* aug_buf = nullptr; size_t aug_cap = 0;
   // data parallel
   int rank = 0, world = 1, global_batch = 0;
   ncclComm_p comm = nullptr;
@@ -136,7 +140,9 @@ struct nrs_trainer {
       if (sl.consumed) cudaEventDestroy(sl.consumed);
       if (sl.x) cudaFree(sl.x);
       if (sl.t) cudaFree(sl.t);
+      if (sl.labels) cudaFree(sl.labels);
     }
+    if (aug_buf) cudaFree(aug_buf);
     opt.reset();
     params.clear();
     buffers.clear();
@@ -396,7 +402,7 @@ void grow_slot_block(float** buf, size_t* cap, size_t floats) {
   *cap = floats;
 }
 
-void stage_next(nrs_trainer* t, const float* x_host, const float* target_host, int batch) {
+void stage_next(nrs_trainer* t, const float* x_host, const float* target_host, const int32_t* labels_host, int batch) {
   if (batch <= 0) fail(NRS_ERR_SHAPE, "trainer: batch must be positive");
   nrs_trainer::Slot& sl = t->slots[t->fill_idx];
   if (sl.pending) fail(NRS_ERR_ARG, "trainer: both staging slots hold a batch that no step has consumed yet");
@@ -409,11 +415,18 @@ void stage_next(nrs_trainer* t, const float* x_host, const float* target_host, i
   for (size_t d : t->in_shape) per *= d;
   grow_slot_block(&sl.x, &sl.x_cap, per * batch);
   grow_slot_block(&sl.t, &sl.t_cap, (size_t)t->classes * batch);
+  if (labels_host) grow_slot_block(&sl.labels, &sl.labels_cap, (size_t)batch);
   // the step that last read this slot must have finished with it
   if (sl.used) cuda_ok(cudaStreamWaitEvent(t->copy_stream, sl.consumed, 0), "wait for the slot's last consumer");
   cuda_ok(cudaMemcpyAsync(sl.x, x_host, per * batch * sizeof(float), cudaMemcpyHostToDevice, t->copy_stream), "input copy");
-  cuda_ok(cudaMemcpyAsync(sl.t, target_host, (size_t)t->classes * batch * sizeof(float), cudaMemcpyHostToDevice, t->copy_stream),
-          "target copy");
+  if (labels_host) {
+    cuda_ok(cudaMemcpyAsync(sl.labels, labels_host, (size_t)batch * sizeof(int32_t), cudaMemcpyHostToDevice, t->copy_stream),
+            "label copy");
+  } else {
+    cuda_ok(cudaMemcpyAsync(sl.t, target_host, (size_t)t->classes * batch * sizeof(float), cudaMemcpyHostToDevice, t->copy_stream),
+            "target copy");
+  }
+  sl.indexed = labels_host != nullptr;
   cuda_ok(cudaEventRecord(sl.filled, t->copy_stream), "event record");
   sl.batch = batch;
   sl.pending = true;
@@ -425,7 +438,18 @@ void step_staged(nrs_trainer* t, float* loss_out) {
   nrs_trainer::Slot& sl = t->slots[t->run_idx];
   if (!sl.pending) fail(NRS_ERR_ARG, "trainer: no staged batch (call nrs_trainer_stage_next first)");
   cuda_ok(cudaStreamWaitEvent(t->ctx->stream, sl.filled, 0), "wait for the staged batch");
-  run_step(t, sl.x, sl.t, sl.batch, true);
+  if (sl.indexed)   // class indices -> one-hot rows, on the compute stream
+    nrs::check(t->ctx, nrs_onehot(t->ctx, reinterpret_cast<const int32_t*>(sl.labels), sl.t, sl.batch, t->classes));
+  const float* x_in = sl.x;
+  if (t->aug_shift >= 0 && t->training && t->in_shape.size() == 3) {
+    size_t per = 1;
+    for (size_t d : t->in_shape) per *= d;
+    grow_slot_block(&t->aug_buf, &t->aug_cap, per * sl.batch);
+    nrs::check(t->ctx, nrs_augment_flip_shift(t->ctx, sl.x, t->aug_buf, sl.batch, (int)t->in_shape[0], (int)t->in_shape[1],
+                                              (int)t->in_shape[2], t->aug_shift, t->aug_flip));
+    x_in = t->aug_buf;
+  }
+  run_step(t, x_in, sl.t, sl.batch, true);
   cuda_ok(cudaEventRecord(sl.consumed, t->ctx->stream), "event record");
   sl.pending = false;
   sl.used = true;
@@ -573,7 +597,23 @@ int nrs_trainer_step(nrs_trainer* t, const float* x_host, const float* target_ho
 int nrs_trainer_stage_next(nrs_trainer* t, const float* x_host, const float* target_host, int batch) {
   if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_stage_next: null handle");
   if (!x_host || !target_host) return nrs_fail(t->ctx, NRS_ERR_ARG, "nrs_trainer_stage_next: null input");
-  return guarded(t->ctx, [&] { stage_next(t, x_host, target_host, batch); });
+  return guarded(t->ctx, [&] { stage_next(t, x_host, target_host, nullptr, batch); });
+}
+
+int nrs_trainer_stage_next_indexed(nrs_trainer* t, const float* x_host, const int32_t* labels_host, int batch) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_stage_next_indexed: null handle");
+  if (!x_host || !labels_host) return nrs_fail(t->ctx, NRS_ERR_ARG, "nrs_trainer_stage_next_indexed: null input");
+  return guarded(t->ctx, [&] { stage_next(t, x_host, nullptr, labels_host, batch); });
+}
+
+int nrs_trainer_set_augment(nrs_trainer* t, int max_shift, int flip) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_set_augment: null handle");
+  NRS_REQUIRE(t->ctx, max_shift < 4096, NRS_ERR_ARG, "nrs_trainer_set_augment: bad shift range %d", max_shift);
+  NRS_REQUIRE(t->ctx, max_shift < 0 || t->in_shape.size() == 3, NRS_ERR_SHAPE,
+              "nrs_trainer_set_augment: augmentation needs [C,H,W] samples");
+  t->aug_shift = max_shift;
+  t->aug_flip = flip != 0;
+  return NRS_OK;
 }
 
 int nrs_trainer_step_staged(nrs_trainer* t, float* loss_out) {

@@ -549,6 +549,18 @@ class Trainer:
         self._staged = getattr(self, "_staged", []) + [(x, target)]
         self.stage_next_ptr(x.ctypes.data, target.ctypes.data, x.shape[0])
 
+    def stage_next_indexed(self, x, labels):
+        """As stage_next with int32 class indices; the step expands them to one-hot rows on the device."""
+        x = _f32(x)
+        labels = np.ascontiguousarray(labels, np.int32)
+        self._staged = getattr(self, "_staged", []) + [(x, labels)]
+        check(self.ctx.h, self.ctx._l.nrs_trainer_stage_next_indexed(self.h, VP(x.ctypes.data), VP(labels.ctypes.data),
+                                                                      int(x.shape[0])))
+
+    def set_augment(self, max_shift: int, flip: bool = True):
+        """On-device flip/shift augmentation of staged batches (max_shift < 0: off)."""
+        check(self.ctx.h, self.ctx._l.nrs_trainer_set_augment(self.h, int(max_shift), int(bool(flip))))
+
     def step_staged(self, want_loss=True):
         """A full training step on the oldest staged batch."""
         loss = C.c_float()

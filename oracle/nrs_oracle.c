@@ -646,3 +646,33 @@ void FN(nrs_oracle_dropout_mask)(float* mask, size_t count, float p, uint64_t se
     }
   }
 }
+
+/* ---------------------------------------------------------- input pipeline */
+
+/* `augment` of examples/cifar_cuda.rs:148-169 for one image [c,h,w] with the draws
+ * given: out[ch,y,x] = img[ch, y-dy, flip ? w-1-(x-dx) : x-dx] inside the image,
+ * zero outside. */
+void FN(nrs_oracle_augment_image)(const float* img, float* out, int c, int h, int w, int flip, int dx, int dy) {
+  for (int ch = 0; ch < c; ++ch)
+    for (int y = 0; y < h; ++y)
+      for (int x = 0; x < w; ++x) {
+        const int sx = x - dx, sy = y - dy;
+        float v = 0.0f;
+        if (sx >= 0 && sx < w && sy >= 0 && sy < h) v = img[((size_t)ch * h + sy) * w + (flip ? w - 1 - sx : sx)];
+        out[((size_t)ch * h + y) * w + x] = v;
+      }
+}
+/* The draws of the device library's augmentation stream for image `index` of a
+ * call that starts at `offset`: flip = top bit of word 0, dx / dy = floor(u * (2s+1)) - s
+ * from words 1 / 2 (the reference draws `(random::<f32>() * 9.0) as i32 - 4`, :151-152). */
+void FN(nrs_oracle_augment_draw)(uint64_t seed, uint64_t offset, uint64_t index, int max_shift, int* flip, int* dx, int* dy) {
+  const uint64_t at = offset + index;
+  const uint32_t ctr[4] = {(uint32_t)at, (uint32_t)(at >> 32), 0u, 0u};
+  const uint32_t key[2] = {(uint32_t)seed, (uint32_t)(seed >> 32)};
+  uint32_t w[4];
+  FN(nrs_oracle_philox4x32_10)(ctr, key, w);
+  *flip = (int)(w[0] >> 31);
+  const float u1 = (float)(w[1] >> 8) * (1.0f / 16777216.0f), u2 = (float)(w[2] >> 8) * (1.0f / 16777216.0f);
+  *dx = (int)(u1 * (float)(2 * max_shift + 1)) - max_shift;
+  *dy = (int)(u2 * (float)(2 * max_shift + 1)) - max_shift;
+}

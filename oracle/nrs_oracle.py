@@ -255,6 +255,28 @@ class Oracle:
                                             C.c_uint64(offset))
         return mask
 
+    # ---- input pipeline (examples/cifar_cuda.rs:148-169; draws: the device library's stream)
+    def augment_image(self, img, flip, dx, dy):
+        img = _f(img)
+        c, h, w = img.shape
+        out = np.empty_like(img)
+        self._fn("nrs_oracle_augment_image")(_p(img), _p(out), c, h, w, int(flip), int(dx), int(dy))
+        return out
+
+    def augment_draw(self, seed, offset, index, max_shift):
+        flip, dx, dy = C.c_int(), C.c_int(), C.c_int()
+        self._fn("nrs_oracle_augment_draw")(C.c_uint64(seed), C.c_uint64(offset), C.c_uint64(index), int(max_shift),
+                                            C.byref(flip), C.byref(dx), C.byref(dy))
+        return flip.value, dx.value, dy.value
+
+    def augment_batch(self, x, seed, offset, max_shift, flip=True):
+        x = _f(x)
+        out = np.empty_like(x)
+        for i in range(x.shape[0]):
+            f, dx, dy = self.augment_draw(seed, offset, i, max_shift)
+            out[i] = self.augment_image(x[i], f and flip, dx, dy)
+        return out
+
     # ---- softmax (src/autograd/graph/softmax.rs:14-64)
     def softmax_fwd(self, x):
         x = _f(x)

@@ -1,7 +1,8 @@
 """Pins the oracle's BatchNorm / Dropout restatement to the reference: the known answers of the
 reference's own tests (tests/nn_batchnorm_test.rs, tests/batchnorm_eval_test.rs,
 tests/gradcheck_batchnorm2d_test.rs, tests/dropout2d_test.rs) and an independent float64 restatement.
-The mask stream (Philox-4x32-10) is pinned to the published known-answer vectors of that generator."""
+The mask stream (Philox-4x32-10) is pinned to the published known-answer vectors of that generator; the
+augmentation restatement (examples/cifar_cuda.rs:146-169) to hand-worked cases and the reference's draw ranges."""
 import numpy as np
 import pytest
 
@@ -111,3 +112,22 @@ def test_dropout_mask_and_routing():
     out2 = o.mask_mul(x2, m2, hw=49)
     assert np.array_equal(out2, x2 * m2.reshape(8, 16, 1, 1))
     assert abs(float((m2 == 0).mean()) - 0.4) < 0.15
+
+
+def test_augment_draws_cover_the_reference_range():
+    """examples/cifar_cuda.rs:150-152: flip with probability 1/2, dx and dy uniform over -4..=4."""
+    draws = np.array([_oracle('f32').augment_draw(11, 0, i, 4) for i in range(4000)])
+    assert abs(draws[:, 0].mean() - 0.5) < 0.05
+    for col in (1, 2):
+        vals, counts = np.unique(draws[:, col], return_counts=True)
+        assert vals.tolist() == list(range(-4, 5))
+        assert np.abs(counts / 4000 - 1 / 9).max() < 0.03
+
+
+def test_augment_image_known_cases():
+    img = np.arange(12, dtype=np.float32).reshape(1, 3, 4)
+    assert np.array_equal(_oracle('f32').augment_image(img, 0, 0, 0), img)
+    assert np.array_equal(_oracle('f32').augment_image(img, 1, 0, 0), img[:, :, ::-1])
+    want = np.zeros_like(img)
+    want[0, 1:, 1:] = img[0, :-1, :-1]                      # dx = dy = 1 moves the content right and down
+    assert np.array_equal(_oracle('f32').augment_image(img, 0, 1, 1), want)
