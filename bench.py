@@ -107,28 +107,41 @@ class ClockSampler:
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
-
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                parts = [p.strip() for p in out.strip().split(",")]
-                if len(parts) >= 7:
-                    self.rows.append(parts)
-            except Exception:
-                pass
-            self._stop.wait(0.2)
+        self.index, self.rows, self._proc, self._t0 = index, [], None, 0.0
 
     def __enter__(self):
-        self._t = threading.Thread(target=self._run, daemon=True)
-        self._t.start()
+        # one long-running sampler (50 ms period): a fresh nvidia-smi per sample takes longer than a short timed region
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu=timestamp,{self.Q}",
+                                           "--format=csv,noheader,nounits", "-lms", "50"],
+                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            time.sleep(0.3)          # let it come up; samples from before this point are dropped
+        except Exception:
+            self._proc = None
+        self._t0 = time.time()
         return self
 
     def __exit__(self, *a):
-        self._stop.set()
-        self._t.join(timeout=6)
+        if not self._proc:
+            return
+        t1 = time.time()
+        self._proc.terminate()
+        try:
+            out, _ = self._proc.communicate(timeout=5)
+        except Exception:
+            self._proc.kill()
+            out = ""
+        import datetime
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+            except ValueError:
+                continue
+            if self._t0 - 0.02 <= ts <= t1 + 0.02:
+                self.rows.append(parts[1:])
 
     def summary(self):
         if not self.rows:

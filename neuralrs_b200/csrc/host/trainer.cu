@@ -16,6 +16,10 @@
 #include <unordered_set>
 
 #include "host/graph.h"
+#include "host/checkpoint.h"
+#include "nrs_checkpoint.h"
+#include <map>
+#include <cstdio>
 #include "nrs_graph.h"
 #include "nrs_internal.h"
 
@@ -542,6 +546,98 @@ int nrs_trainer_get_buffer(nrs_trainer* t, int i, float* host_out) {
   if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_get_buffer: null handle");
   NRS_REQUIRE(t->ctx, host_out && i >= 0 && i < (int)t->buffers.size(), NRS_ERR_ARG, "nrs_trainer_get_buffer: bad index or null output");
   return nrs_d2h(t->ctx, host_out, t->buffers[i]->data, t->buffers[i]->len() * sizeof(float));
+}
+
+namespace {
+
+std::string tensor_name(const char* const* names, size_t i, const char* prefix, size_t k) {
+  if (names) {
+    if (!names[i]) throw nrs::Error(NRS_ERR_ARG, "trainer checkpoint: null name");
+    return names[i];
+  }
+  char buf[32];
+  std::snprintf(buf, sizeof buf, "%s.%02zu", prefix, k);
+  return buf;
+}
+
+std::vector<float> download(nrs_ctx* ctx, const NodeP& n) {
+  std::vector<float> h(n->len());
+  nrs::check(ctx, nrs_d2h(ctx, h.data(), n->data, h.size() * sizeof(float)));
+  return h;
+}
+
+void save_checkpoint(nrs_trainer* t, const char* const* names, const char* path) {
+  std::vector<nrs::checkpoint::Tensor> out;
+  const size_t np = t->params.size();
+  for (size_t i = 0; i < np + t->buffers.size(); ++i) {
+    const NodeP& n = i < np ? t->params[i] : t->buffers[i - np];
+    nrs::checkpoint::Tensor ct;
+    ct.name = i < np ? tensor_name(names, i, "param", i) : tensor_name(names, i, "buffer", i - np);
+    ct.shape.assign(n->shape.begin(), n->shape.end());
+    ct.data = download(t->ctx, n);
+    out.push_back(std::move(ct));
+  }
+  // examples/mnist_cuda_cnn.rs:173-185: optim.t as one f32 (exact below 2^24), then the moments, flat
+  size_t steps = 0;
+  std::vector<std::vector<float>> moments = t->opt->export_state(&steps);
+  out.push_back({"optim.t", {1}, {(float)steps}});
+  const size_t half = moments.size() / 2;
+  for (size_t i = 0; i < moments.size(); ++i) {
+    char buf[32];
+    std::snprintf(buf, sizeof buf, i < half ? "optim.m.%02zu" : "optim.v.%02zu", i < half ? i : i - half);
+    const int64_t len = (int64_t)moments[i].size();
+    out.push_back({buf, {len}, std::move(moments[i])});
+  }
+  nrs::checkpoint::save(out, path);
+}
+
+void load_checkpoint(nrs_trainer* t, const char* const* names, const char* path) {
+  std::vector<nrs::checkpoint::Tensor> file = nrs::checkpoint::load(path);
+  const std::string p(path);
+  const bool named = p.size() >= 12 && p.compare(p.size() - 12, 12, ".safetensors") == 0;
+  std::map<std::string, const nrs::checkpoint::Tensor*> by_name;
+  for (const auto& ct : file) by_name[ct.name] = &ct;
+  const size_t np = t->params.size(), total = np + t->buffers.size();
+  auto lookup = [&](size_t i, const std::string& name) -> const nrs::checkpoint::Tensor* {
+    if (!named) return i < file.size() ? &file[i] : nullptr;   // the text format is positional
+    auto it = by_name.find(name);
+    return it == by_name.end() ? nullptr : it->second;
+  };
+  for (size_t i = 0; i < total; ++i) {
+    const NodeP& n = i < np ? t->params[i] : t->buffers[i - np];
+    const std::string name = i < np ? tensor_name(names, i, "param", i) : tensor_name(names, i, "buffer", i - np);
+    const nrs::checkpoint::Tensor* ct = lookup(i, name);
+    if (!ct) throw nrs::Error(NRS_ERR_ARG, "checkpoint is missing tensor `" + name + "`");
+    if (ct->data.size() != n->len()) throw nrs::Error(NRS_ERR_SHAPE, "checkpoint tensor `" + name + "` has the wrong size");
+    nrs::check(t->ctx, nrs_h2d(t->ctx, n->data, ct->data.data(), ct->data.size() * sizeof(float)));
+  }
+  nrs::check(t->ctx, nrs_sync(t->ctx));
+  // examples/mnist_cuda_cnn.rs:208-218: the optimizer state rides along when "optim.t" is present
+  const nrs::checkpoint::Tensor* tt = lookup(total, "optim.t");
+  if (!tt || tt->data.size() != 1 || (!named && file.size() != total + 1 + 2 * np)) return;
+  std::vector<std::vector<float>> moments;
+  for (int pass = 0; pass < 2; ++pass)
+    for (size_t i = 0; i < np; ++i) {
+      char buf[32];
+      std::snprintf(buf, sizeof buf, pass == 0 ? "optim.m.%02zu" : "optim.v.%02zu", i);
+      const nrs::checkpoint::Tensor* ct = lookup(total + 1 + (size_t)pass * np + i, buf);
+      if (!ct) throw nrs::Error(NRS_ERR_ARG, std::string("checkpoint is missing tensor `") + buf + "`");
+      if (ct->data.size() != t->params[i]->len()) throw nrs::Error(NRS_ERR_SHAPE, std::string("checkpoint tensor `") + buf + "` has the wrong size");
+      moments.push_back(ct->data);
+    }
+  t->opt->import_state((size_t)tt->data[0], moments);
+}
+
+}  // namespace
+
+int nrs_trainer_save_checkpoint(nrs_trainer* t, const char* const* names, const char* path) {
+  if (!t || !path) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_save_checkpoint: null handle or path");
+  return guarded(t->ctx, [&] { save_checkpoint(t, names, path); });
+}
+
+int nrs_trainer_load_checkpoint(nrs_trainer* t, const char* const* names, const char* path) {
+  if (!t || !path) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_load_checkpoint: null handle or path");
+  return guarded(t->ctx, [&] { load_checkpoint(t, names, path); });
 }
 
 int nrs_trainer_set_training(nrs_trainer* t, int training) {

@@ -516,6 +516,15 @@ class Trainer:
         assert a.size == int(self.ctx._l.nrs_trainer_buffer_len(self.h, i))
         check(self.ctx.h, self.ctx._l.nrs_trainer_set_buffer(self.h, i, _ptr(a)))
 
+    def save_checkpoint(self, path: str, names=None):
+        """Parameters, batchnorm running statistics and the AdamW state (optim.t, optim.m.NN, optim.v.NN)."""
+        arr = (C.c_char_p * len(names))(*[n.encode() for n in names]) if names else None
+        check(self.ctx.h, self.ctx._l.nrs_trainer_save_checkpoint(self.h, arr, str(path).encode()))
+
+    def load_checkpoint(self, path: str, names=None):
+        arr = (C.c_char_p * len(names))(*[n.encode() for n in names]) if names else None
+        check(self.ctx.h, self.ctx._l.nrs_trainer_load_checkpoint(self.h, arr, str(path).encode()))
+
     def set_training(self, training: bool):
         check(self.ctx.h, self.ctx._l.nrs_trainer_set_training(self.h, int(bool(training))))
 
@@ -622,3 +631,43 @@ def dp_plan_buckets(param_lens, bucket_bytes: int) -> list[tuple[int, int]]:
     s, e = (C.c_int64 * max(n, 1))(), (C.c_int64 * max(n, 1))()
     l.nrs_dp_plan_buckets(lens, len(param_lens), C.c_size_t(bucket_bytes), s, e, n)
     return [(int(s[i]), int(e[i])) for i in range(n)]
+
+
+class serialize:
+    """src/serialize.rs `save` / `load` through the library's host-side reader / writer (include/nrs_checkpoint.h)."""
+
+    class _Named(C.Structure):
+        _fields_ = [("name", C.c_char_p), ("shape", C.POINTER(C.c_int64)), ("ndim", C.c_int), ("data", C.c_void_p)]
+
+    @staticmethod
+    def save(tensors, path: str):
+        """tensors: [(name, shape, data)]; '.safetensors' writes safetensors, anything else the positional text format."""
+        l = _lib.lib()
+        keep, arr = [], (serialize._Named * len(tensors))()
+        for i, (name, shape, data) in enumerate(tensors):
+            d = _f32(data).reshape(-1)
+            if d.size != int(np.prod([int(s) for s in shape], dtype=np.int64)):
+                # the C struct carries no length: the shape says how many floats are read (serialize.rs:204 panics here)
+                raise ValueError(f"save: tensor shape does not match its data length ({name})")
+            sh = (C.c_int64 * len(shape))(*[int(s) for s in shape])
+            keep += [d, sh]
+            arr[i] = serialize._Named(name.encode(), sh, len(shape), d.ctypes.data)
+        _lib.check(None, l.nrs_save(arr, len(tensors), str(path).encode()))
+
+    @staticmethod
+    def load(path: str):
+        """-> [(name, shape, data)]: sorted by name for safetensors, tensor_{i} / flat length for text."""
+        l = _lib.lib()
+        h = VP()
+        _lib.check(None, l.nrs_load(str(path).encode(), C.byref(h)))
+        try:
+            out = []
+            for i in range(l.nrs_checkpoint_count(h)):
+                name = C.string_at(l.nrs_checkpoint_name(h, i)).decode()
+                shape = [int(l.nrs_checkpoint_dim(h, i, d)) for d in range(l.nrs_checkpoint_ndim(h, i))]
+                n = int(l.nrs_checkpoint_len(h, i))
+                data = np.frombuffer(C.string_at(l.nrs_checkpoint_data(h, i), n * 4), np.float32).copy() if n else np.zeros(0, np.float32)
+                out.append((name, shape, data))
+            return out
+        finally:
+            l.nrs_checkpoint_free(h)

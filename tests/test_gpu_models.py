@@ -209,3 +209,61 @@ def test_staged_steps_equal_plain_steps(gpu_ctx):
     assert staged.step_staged() is not None and staged.step_staged() is not None
     plain.close()
     staged.close()
+
+
+@pytest.mark.parametrize("ext", ["safetensors", "txt"])
+def test_checkpoint_resume_is_exact(gpu_ctx, tmp_path, ext):
+    """save_checkpoint / load_checkpoint of the reference's examples (examples/mnist_cuda_cnn.rs:160-221): after two
+    steps the parameters, BatchNorm running statistics and AdamW state go to a file; a fresh trainer that loads it
+    continues with bit-identical losses and parameters.  Names follow the example (PyTorch style + optim.*)."""
+    from neuralrs_b200.cuda import serialize
+    cfg = dict(in_shape=(3, 8, 8), classes=10,
+               layers=[("conv", 3, 32, 3, 1, 1), ("batchnorm", 32), ("relu",), ("maxpool", 2, 2), ("flatten",),
+                       ("linear", 512, 10)])
+    names = ["c1.weight", "c1.bias", "c1.bn.gamma", "c1.bn.beta", "fc.weight", "fc.bias", "c1.bn.running_mean",
+             "c1.bn.running_var"]
+    hp = models.ADAMW_HP
+    params = models.he_init(cfg["layers"], 700)
+    batches = [models.synthetic_batch(cfg, 16, 710 + i) for i in range(4)]
+
+    def make():
+        return cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
+                            hp["wd"], fuse=True, ctx=gpu_ctx)
+
+    a = make()
+    a.set_params(params)
+    for x, t in batches[:2]:
+        a.step(x, t)
+    path = str(tmp_path / f"ck.{ext}")
+    a.save_checkpoint(path, names)
+    file = serialize.load(path)
+    if ext == "safetensors":
+        got = {n: (s, d) for n, s, d in file}
+        assert set(got) == set(names) | {"optim.t"} | {f"optim.{k}.{i:02d}" for k in "mv" for i in range(6)}
+        assert got["optim.t"][1].tolist() == [2.0]
+        assert got["c1.weight"][0] == [32, 3, 3, 3] and got["optim.m.00"][0] == [864]
+        assert np.array_equal(got["fc.bias"][1], a.get_param(5))
+        assert np.array_equal(got["c1.bn.running_var"][1], a.get_buffer(1))
+    else:
+        assert len(file) == 8 + 1 + 12 and file[0][0] == "tensor_0"
+    b = make()
+    b.load_checkpoint(path, names)
+    for i in range(a.n_params):
+        assert np.array_equal(a.get_param(i), b.get_param(i))
+    for x, t in batches[2:]:
+        assert a.step(x, t) == b.step(x, t)
+    for i in range(a.n_params):
+        assert np.array_equal(a.get_param(i), b.get_param(i))
+    for i in range(a.n_buffers):
+        assert np.array_equal(a.get_buffer(i), b.get_buffer(i))
+    # a checkpoint without one of the model's tensors, or with a tensor of the wrong size, is refused
+    if ext == "safetensors":
+        serialize.save([f for f in file if f[0] != "fc.bias"], str(tmp_path / "missing.safetensors"))
+        with pytest.raises(_lib.NrsError, match="missing tensor `fc.bias`"):
+            make().load_checkpoint(str(tmp_path / "missing.safetensors"), names)
+        serialize.save([(n, [3], np.zeros(3, np.float32)) if n == "fc.bias" else (n, s, d) for n, s, d in file],
+                       str(tmp_path / "size.safetensors"))
+        with pytest.raises(_lib.NrsError, match="wrong size"):
+            make().load_checkpoint(str(tmp_path / "size.safetensors"), names)
+    a.close()
+    b.close()
