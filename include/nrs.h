@@ -239,6 +239,20 @@ int nrs_batchnorm_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const fl
 int nrs_batchnorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd,
                       const float* gamma, float* dx, float* dgamma, float* dbeta,
                       int n, int c, int hw, int training, int accumulate_dx, int accumulate_params);
+/* The same two passes with the ReLU that follows the layer in the reference's
+ * models (examples/cifar_cuda.rs:44-48: conv -> batchnorm2d -> relu) folded in:
+ * act = NRS_ACT_RELU writes y = max(0, gamma*xhat + beta), and the backward pass
+ * masks the incoming gradient where that output was not positive (relu_backward,
+ * src/cuda/graph/relu.rs:28-45: strict >) before the BatchNorm arithmetic.  The
+ * mask is recomputed from xhat, gamma and beta with the forward pass's own
+ * expression, so no activation or mask tensor is stored or read.  act =
+ * NRS_ACT_NONE is nrs_batchnorm_fwd / _bwd. */
+int nrs_batchnorm_act_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const float* beta,
+                          float* running_mean, float* running_var, float* y, float* xhat, float* istd,
+                          int n, int c, int hw, float eps, float momentum, int training, int act);
+int nrs_batchnorm_act_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd,
+                          const float* gamma, const float* beta, float* dx, float* dgamma, float* dbeta,
+                          int n, int c, int hw, int training, int accumulate_dx, int accumulate_params, int act);
 /* mask_mul (src/cuda/nn/dropout.rs:17-22) with hw == 1 and mask_mul_channels
  * (src/cuda/nn/dropout2d.rs:18-27) with hw = h*w: out (+)= a * mask[i / hw].  The
  * same call routes the gradient in the backward pass. */

@@ -77,6 +77,10 @@ int nrs_op_batchnorm(nrs_node* x, nrs_node* gamma, nrs_node* beta, nrs_node* run
                      float momentum, float eps, int training, nrs_node** out);
 int nrs_op_batchnorm2d(nrs_node* x, nrs_node* gamma, nrs_node* beta, nrs_node* running_mean, nrs_node* running_var,
                        float momentum, float eps, int training, nrs_node** out);
+/* Either of the two (chosen by the input's rank, 2 or 4) with the activation that
+ * follows it fused (enum nrs_act: NONE or RELU), like nrs_op_conv2d_act. */
+int nrs_op_batchnorm_act(nrs_node* x, nrs_node* gamma, nrs_node* beta, nrs_node* running_mean, nrs_node* running_var,
+                         float momentum, float eps, int training, int act, nrs_node** out);
 /* dropout (src/cuda/nn/dropout.rs:31-84) and dropout2d (src/cuda/nn/dropout2d.rs:37-).
  * training == 0 hands back the input node itself (one more reference on it).  `mask`
  * NULL draws the mask on the device (nrs_dropout_mask: the context's seed and

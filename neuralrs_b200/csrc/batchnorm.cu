@@ -37,12 +37,15 @@ __device__ __forceinline__ void contribute(float a, float b, float k, float& s, 
   }
 }
 
-// Planes layout (hw >= 2): one block per (channel, sample split); each warp walks its own images, lanes
-// stride the plane (128-bit loads when the plane allows).  partial[split][ch] = (S, Q).
-template <bool FWD>
+// Planes layout (hw >= 2): one block per (channel, sample split), 128-bit loads when the plane allows.
+// partial[split][ch] = (S, Q).
+// RELU (backward only): the layer's output went through a ReLU fused into the normalise pass; the incoming
+// gradient is masked where that output was not positive, the output being recomputed from xhat with the very
+// expression of the forward pass (fmaf(gamma, xhat, beta)), so the mask is the forward one bit for bit.
+template <bool FWD, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_pair_planes_kernel(const float* __restrict__ a, const float* __restrict__ b, float2* __restrict__ partial, int n,
-                      int c, int hw, int splits) {
+                      int c, int hw, int splits, const float* __restrict__ gamma, const float* __restrict__ beta) {
   NRS_PDL_PROLOGUE();
   __shared__ float2 sm[kThreads / 32];
   const int ch = blockIdx.x, split = blockIdx.y;
@@ -50,27 +53,39 @@ bn_pair_planes_kernel(const float* __restrict__ a, const float* __restrict__ b, 
   const int n_per = (n + splits - 1) / splits;
   const int n0 = split * n_per, n1 = min(n, n0 + n_per);
   const float k = FWD ? a[(size_t)ch * hw] : 0.0f;
+  const float ga = RELU ? gamma[ch] : 0.0f, be = RELU ? beta[ch] : 0.0f;
   const bool vec = (hw & 3) == 0 && aligned16(a) && (FWD || aligned16(b));
-  float s = 0.0f, q = 0.0f;
-  for (int img = n0 + wrp; img < n1; img += kThreads / 32) {
-    const size_t base = ((size_t)img * c + ch) * hw;
+  // The block's threads walk the split's (image, element) pairs as one flat index, so that planes shorter
+  // than a warp's reach (8x8, 4x4 feature maps) still keep every lane loading.
+  float s = 0.0f, q = 0.0f, s1 = 0.0f, q1 = 0.0f;
+  const int per = vec ? hw / 4 : hw;                       // items per plane
+  const int items = max(n1 - n0, 0) * per;               // n * hw < 2^31 is checked on the host
+  for (int j = threadIdx.x; j < items; j += kThreads) {
+    const int di = j / per, i = j - di * per;
+    const size_t base = ((size_t)(n0 + di) * c + ch) * hw;
     if (vec) {
-      float s1 = 0.0f, q1 = 0.0f;
-      for (int i = lane; i < hw / 4; i += 32) {
-        const float4 va = reinterpret_cast<const float4*>(a + base)[i];
-        float4 vb = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (!FWD) vb = reinterpret_cast<const float4*>(b + base)[i];
-        contribute<FWD>(va.x, vb.x, k, s, q);
-        contribute<FWD>(va.y, vb.y, k, s1, q1);
-        contribute<FWD>(va.z, vb.z, k, s, q);
-        contribute<FWD>(va.w, vb.w, k, s1, q1);
+      float4 va = reinterpret_cast<const float4*>(a + base)[i];
+      float4 vb = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (!FWD) vb = reinterpret_cast<const float4*>(b + base)[i];
+      if (RELU) {
+        va.x = fmaf(ga, vb.x, be) > 0.0f ? va.x : 0.0f;
+        va.y = fmaf(ga, vb.y, be) > 0.0f ? va.y : 0.0f;
+        va.z = fmaf(ga, vb.z, be) > 0.0f ? va.z : 0.0f;
+        va.w = fmaf(ga, vb.w, be) > 0.0f ? va.w : 0.0f;
       }
-      s += s1;
-      q += q1;
+      contribute<FWD>(va.x, vb.x, k, s, q);
+      contribute<FWD>(va.y, vb.y, k, s1, q1);
+      contribute<FWD>(va.z, vb.z, k, s, q);
+      contribute<FWD>(va.w, vb.w, k, s1, q1);
     } else {
-      for (int i = lane; i < hw; i += 32) contribute<FWD>(a[base + i], FWD ? 0.0f : b[base + i], k, s, q);
+      const float vb = FWD ? 0.0f : b[base + i];
+      float va = a[base + i];
+      if (RELU) va = fmaf(ga, vb, be) > 0.0f ? va : 0.0f;
+      contribute<FWD>(va, vb, k, s, q);
     }
   }
+  s += s1;
+  q += q1;
   s = wsum(s);
   q = wsum(q);
   if (lane == 0) sm[wrp] = make_float2(s, q);
@@ -85,10 +100,10 @@ bn_pair_planes_kernel(const float* __restrict__ a, const float* __restrict__ b, 
 
 // Columns layout (hw == 1): a block owns 32 features and a slice of the rows; its 8 warps stride the rows
 // reading 128-byte row segments.
-template <bool FWD>
+template <bool FWD, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_pair_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, float2* __restrict__ partial, int rows,
-                    int cols, int splits) {
+                    int cols, int splits, const float* __restrict__ gamma, const float* __restrict__ beta) {
   NRS_PDL_PROLOGUE();
   __shared__ float2 sm[kThreads / 32][33];
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
@@ -98,9 +113,13 @@ bn_pair_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, fl
   float s = 0.0f, q = 0.0f;
   if (col < cols) {
     const float k = FWD ? a[col] : 0.0f;
+    const float ga = RELU ? gamma[col] : 0.0f, be = RELU ? beta[col] : 0.0f;
     for (int r = r0 + wrp; r < r1; r += kThreads / 32) {
       const size_t i = (size_t)r * cols + col;
-      contribute<FWD>(a[i], FWD ? 0.0f : b[i], k, s, q);
+      const float vb = FWD ? 0.0f : b[i];
+      float va = a[i];
+      if (RELU) va = fmaf(ga, vb, be) > 0.0f ? va : 0.0f;
+      contribute<FWD>(va, vb, k, s, q);
     }
   }
   sm[wrp][lane] = make_float2(s, q);
@@ -162,7 +181,7 @@ __global__ void bn_grad_finish_kernel(const float2* __restrict__ partial, float2
 }
 
 // y = gamma * xhat + beta, xhat = (x - mean) * istd (bn2d_normalize, batchnorm2d.rs:62-75).
-template <bool VEC>
+template <bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_normalize_kernel(const float* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ istd,
                     const float* __restrict__ gamma, const float* __restrict__ beta, float* __restrict__ y,
@@ -177,25 +196,28 @@ bn_normalize_kernel(const float* __restrict__ x, const float* __restrict__ mean,
       const float4 v = reinterpret_cast<const float4*>(x)[i];
       const float4 h = make_float4((v.x - m) * is, (v.y - m) * is, (v.z - m) * is, (v.w - m) * is);
       if (xhat) reinterpret_cast<float4*>(xhat)[i] = h;
-      reinterpret_cast<float4*>(y)[i] = make_float4(ga * h.x + be, ga * h.y + be, ga * h.z + be, ga * h.w + be);
+      float4 o = make_float4(fmaf(ga, h.x, be), fmaf(ga, h.y, be), fmaf(ga, h.z, be), fmaf(ga, h.w, be));
+      if (RELU) o = make_float4(fmaxf(o.x, 0.0f), fmaxf(o.y, 0.0f), fmaxf(o.z, 0.0f), fmaxf(o.w, 0.0f));
+      reinterpret_cast<float4*>(y)[i] = o;
     }
   } else {
     for (size_t i = tid; i < total; i += stride) {
       const int ch = (int)((i / hw) % c);
       const float h = (x[i] - mean[ch]) * istd[ch];
       if (xhat) xhat[i] = h;
-      y[i] = gamma[ch] * h + beta[ch];
+      const float o = fmaf(gamma[ch], h, beta[ch]);
+      y[i] = RELU ? fmaxf(o, 0.0f) : o;
     }
   }
 }
 
 // bn2d_dx (batchnorm2d.rs:96-117): training dx = istd * (g*gamma - gamma*dbeta/N - xhat*gamma*dgamma/N);
 // evaluation dx = g * gamma * istd.
-template <bool VEC>
+template <bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_dx_kernel(const float* __restrict__ g, const float* __restrict__ xhat, const float* __restrict__ istd,
-             const float* __restrict__ gamma, const float2* __restrict__ sums, float* dx, size_t total, int c, int hw,
-             float count, int training, int accumulate) {
+             const float* __restrict__ gamma, const float* __restrict__ beta, const float2* __restrict__ sums, float* dx,
+             size_t total, int c, int hw, float count, int training, int accumulate) {
   NRS_PDL_PROLOGUE();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -203,12 +225,20 @@ bn_dx_kernel(const float* __restrict__ g, const float* __restrict__ xhat, const 
     for (size_t i = tid; i < total / 4; i += stride) {
       const int ch = (int)((i * 4 / hw) % c);
       const float ga = gamma[ch], is = istd[ch];
-      const float4 vg = reinterpret_cast<const float4*>(g)[i];
+      float4 vg = reinterpret_cast<const float4*>(g)[i];
+      float4 vh = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (training || RELU) vh = reinterpret_cast<const float4*>(xhat)[i];
+      if (RELU) {
+        const float be = beta[ch];
+        vg.x = fmaf(ga, vh.x, be) > 0.0f ? vg.x : 0.0f;
+        vg.y = fmaf(ga, vh.y, be) > 0.0f ? vg.y : 0.0f;
+        vg.z = fmaf(ga, vh.z, be) > 0.0f ? vg.z : 0.0f;
+        vg.w = fmaf(ga, vh.w, be) > 0.0f ? vg.w : 0.0f;
+      }
       float4 r;
       if (training) {
         const float2 sm = sums[ch];
         const float m1 = ga * sm.x / count, m2 = ga * sm.y / count;
-        const float4 vh = reinterpret_cast<const float4*>(xhat)[i];
         r = make_float4(is * (vg.x * ga - m1 - vh.x * m2), is * (vg.y * ga - m1 - vh.y * m2),
                         is * (vg.z * ga - m1 - vh.z * m2), is * (vg.w * ga - m1 - vh.w * m2));
       } else {
@@ -225,12 +255,14 @@ bn_dx_kernel(const float* __restrict__ g, const float* __restrict__ xhat, const 
     for (size_t i = tid; i < total; i += stride) {
       const int ch = (int)((i / hw) % c);
       const float ga = gamma[ch], is = istd[ch];
+      float gi = g[i];
+      if (RELU) gi = fmaf(ga, xhat[i], beta[ch]) > 0.0f ? gi : 0.0f;
       float r;
       if (training) {
         const float2 sm = sums[ch];
-        r = is * (g[i] * ga - ga * sm.x / count - xhat[i] * (ga * sm.y / count));
+        r = is * (gi * ga - ga * sm.x / count - xhat[i] * (ga * sm.y / count));
       } else {
-        r = g[i] * ga * is;
+        r = gi * ga * is;
       }
       dx[i] = accumulate ? dx[i] + r : r;
     }
@@ -249,12 +281,15 @@ int plan_splits(const nrs_ctx* ctx, int n, int c, int hw) {
   return splits;
 }
 
-template <bool FWD>
-int launch_pair(nrs_ctx* ctx, const float* a, const float* b, float2* partial, int n, int c, int hw, int splits) {
+template <bool FWD, bool RELU>
+int launch_pair(nrs_ctx* ctx, const float* a, const float* b, float2* partial, int n, int c, int hw, int splits,
+                const float* gamma, const float* beta) {
   if (hw == 1) {
-    NRS_PDL_LAUNCH(bn_pair_cols_kernel<FWD>, dim3((c + 31) / 32, splits), kThreads, 0, ctx->stream, a, b, partial, n, c, splits);
+    NRS_PDL_LAUNCH((bn_pair_cols_kernel<FWD, RELU>), dim3((c + 31) / 32, splits), kThreads, 0, ctx->stream, a, b, partial, n, c,
+                   splits, gamma, beta);
   } else {
-    NRS_PDL_LAUNCH(bn_pair_planes_kernel<FWD>, dim3(c, splits), kThreads, 0, ctx->stream, a, b, partial, n, c, hw, splits);
+    NRS_PDL_LAUNCH((bn_pair_planes_kernel<FWD, RELU>), dim3(c, splits), kThreads, 0, ctx->stream, a, b, partial, n, c, hw,
+                   splits, gamma, beta);
   }
   NRS_LAUNCHED(ctx);
   return NRS_OK;
@@ -267,18 +302,20 @@ unsigned ew_blocks(const nrs_ctx* ctx, size_t work_items) {
 }
 
 bool check_dims(int n, int c, int hw) {
-  return n >= 1 && c >= 1 && hw >= 1 && (size_t)n * c * hw <= (size_t)1 << 40 && (size_t)c * hw <= 0x7fffffffu;
+  return n >= 1 && c >= 1 && hw >= 1 && (size_t)n * c * hw <= (size_t)1 << 40 && (size_t)c * hw <= 0x7fffffffu &&
+         (size_t)n * hw <= 0x7fffffffu;
 }
 
 }  // namespace
 
-int nrs_batchnorm_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const float* beta, float* running_mean,
-                      float* running_var, float* y, float* xhat, float* istd, int n, int c, int hw, float eps,
-                      float momentum, int training) {
+namespace {
+
+int bn_forward(nrs_ctx* ctx, const char* who, const float* x, const float* gamma, const float* beta, float* running_mean,
+               float* running_var, float* y, float* xhat, float* istd, int n, int c, int hw, float eps, float momentum,
+               int training, bool relu) {
   NRS_REQUIRE_CTX(ctx);
-  NRS_REQUIRE(ctx, check_dims(n, c, hw), NRS_ERR_SHAPE, "nrs_batchnorm_fwd: bad shape [%d,%d,%d]", n, c, hw);
-  NRS_REQUIRE(ctx, x && gamma && beta && running_mean && running_var && y && istd, NRS_ERR_ARG,
-              "nrs_batchnorm_fwd: null tensor");
+  NRS_REQUIRE(ctx, check_dims(n, c, hw), NRS_ERR_SHAPE, "%s: bad shape [%d,%d,%d]", who, n, c, hw);
+  NRS_REQUIRE(ctx, x && gamma && beta && running_mean && running_var && y && istd, NRS_ERR_ARG, "%s: null tensor", who);
   const int splits = training ? plan_splits(ctx, n, c, hw) : 1;
   void* ws = nullptr;
   const int st = nrs_workspace(ctx, ((size_t)splits * c * 2 + c) * sizeof(float), &ws);
@@ -286,7 +323,7 @@ int nrs_batchnorm_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const fl
   float2* partial = (float2*)ws;
   float* mean = (float*)(partial + (size_t)splits * c);
   if (training) {
-    const int sp = launch_pair<true>(ctx, x, nullptr, partial, n, c, hw, splits);
+    const int sp = launch_pair<true, false>(ctx, x, nullptr, partial, n, c, hw, splits, nullptr, nullptr);
     if (sp != NRS_OK) return sp;
   }
   NRS_PDL_LAUNCH(bn_stats_finish_kernel, nrs_blocks(c, 128), 128, 0, ctx->stream, (const float2*)partial, x, mean, istd,
@@ -294,25 +331,24 @@ int nrs_batchnorm_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const fl
   NRS_LAUNCHED(ctx);
   const size_t total = (size_t)n * c * hw;
   const bool vec = (hw & 3) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)xhat & 15) == 0;
-  if (vec) {
-    NRS_PDL_LAUNCH(bn_normalize_kernel<true>, ew_blocks(ctx, total / 4), kThreads, 0, ctx->stream, x, (const float*)mean,
-                   (const float*)istd, gamma, beta, y, xhat, total, c, hw);
-  } else {
-    NRS_PDL_LAUNCH(bn_normalize_kernel<false>, ew_blocks(ctx, total), kThreads, 0, ctx->stream, x, (const float*)mean,
-                   (const float*)istd, gamma, beta, y, xhat, total, c, hw);
-  }
+  const unsigned blocks = ew_blocks(ctx, vec ? total / 4 : total);
+#define NRS_BN_NORM(V, R)                                                                                          \
+  NRS_PDL_LAUNCH((bn_normalize_kernel<V, R>), blocks, kThreads, 0, ctx->stream, x, (const float*)mean, (const float*)istd, \
+                 gamma, beta, y, xhat, total, c, hw)
+  if (vec) { if (relu) NRS_BN_NORM(true, true); else NRS_BN_NORM(true, false); }
+  else { if (relu) NRS_BN_NORM(false, true); else NRS_BN_NORM(false, false); }
+#undef NRS_BN_NORM
   NRS_LAUNCHED(ctx);
   return NRS_OK;
 }
 
-int nrs_batchnorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd, const float* gamma, float* dx,
-                      float* dgamma, float* dbeta, int n, int c, int hw, int training, int accumulate_dx,
-                      int accumulate_params) {
+int bn_backward(nrs_ctx* ctx, const char* who, const float* g, const float* xhat, const float* istd, const float* gamma,
+                const float* beta, float* dx, float* dgamma, float* dbeta, int n, int c, int hw, int training,
+                int accumulate_dx, int accumulate_params, bool relu) {
   NRS_REQUIRE_CTX(ctx);
-  NRS_REQUIRE(ctx, check_dims(n, c, hw), NRS_ERR_SHAPE, "nrs_batchnorm_bwd: bad shape [%d,%d,%d]", n, c, hw);
-  NRS_REQUIRE(ctx, (dgamma == nullptr) == (dbeta == nullptr), NRS_ERR_ARG,
-              "nrs_batchnorm_bwd: dgamma and dbeta must be given together");
-  NRS_REQUIRE(ctx, g && xhat && istd && gamma, NRS_ERR_ARG, "nrs_batchnorm_bwd: null tensor");
+  NRS_REQUIRE(ctx, check_dims(n, c, hw), NRS_ERR_SHAPE, "%s: bad shape [%d,%d,%d]", who, n, c, hw);
+  NRS_REQUIRE(ctx, (dgamma == nullptr) == (dbeta == nullptr), NRS_ERR_ARG, "%s: dgamma and dbeta must be given together", who);
+  NRS_REQUIRE(ctx, g && xhat && istd && gamma && (!relu || beta), NRS_ERR_ARG, "%s: null tensor", who);
   if (!dx && !dgamma) return NRS_OK;
   const bool need_sums = dgamma || training;
   const int splits = need_sums ? plan_splits(ctx, n, c, hw) : 1;
@@ -322,7 +358,8 @@ int nrs_batchnorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const flo
   float2* partial = (float2*)ws;
   float2* sums = partial + (size_t)splits * c;
   if (need_sums) {
-    const int sp = launch_pair<false>(ctx, g, xhat, partial, n, c, hw, splits);
+    const int sp = relu ? launch_pair<false, true>(ctx, g, xhat, partial, n, c, hw, splits, gamma, beta)
+                        : launch_pair<false, false>(ctx, g, xhat, partial, n, c, hw, splits, nullptr, nullptr);
     if (sp != NRS_OK) return sp;
     NRS_PDL_LAUNCH(bn_grad_finish_kernel, nrs_blocks(c, 128), 128, 0, ctx->stream, (const float2*)partial, sums, dgamma, dbeta,
                    c, splits, accumulate_params);
@@ -332,13 +369,50 @@ int nrs_batchnorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const flo
   const size_t total = (size_t)n * c * hw;
   const float count = (float)((double)n * hw);
   const bool vec = (hw & 3) == 0 && ((uintptr_t)g & 15) == 0 && ((uintptr_t)xhat & 15) == 0 && ((uintptr_t)dx & 15) == 0;
-  if (vec) {
-    NRS_PDL_LAUNCH(bn_dx_kernel<true>, ew_blocks(ctx, total / 4), kThreads, 0, ctx->stream, g, xhat, istd, gamma,
-                   (const float2*)sums, dx, total, c, hw, count, training, accumulate_dx);
-  } else {
-    NRS_PDL_LAUNCH(bn_dx_kernel<false>, ew_blocks(ctx, total), kThreads, 0, ctx->stream, g, xhat, istd, gamma,
-                   (const float2*)sums, dx, total, c, hw, count, training, accumulate_dx);
-  }
+  const unsigned blocks = ew_blocks(ctx, vec ? total / 4 : total);
+#define NRS_BN_DX(V, R)                                                                                              \
+  NRS_PDL_LAUNCH((bn_dx_kernel<V, R>), blocks, kThreads, 0, ctx->stream, g, xhat, istd, gamma, beta, (const float2*)sums, dx, \
+                 total, c, hw, count, training, accumulate_dx)
+  if (vec) { if (relu) NRS_BN_DX(true, true); else NRS_BN_DX(true, false); }
+  else { if (relu) NRS_BN_DX(false, true); else NRS_BN_DX(false, false); }
+#undef NRS_BN_DX
   NRS_LAUNCHED(ctx);
   return NRS_OK;
+}
+
+bool act_ok(int act) { return act == NRS_ACT_NONE || act == NRS_ACT_RELU; }
+
+}  // namespace
+
+int nrs_batchnorm_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const float* beta, float* running_mean,
+                      float* running_var, float* y, float* xhat, float* istd, int n, int c, int hw, float eps,
+                      float momentum, int training) {
+  return bn_forward(ctx, "nrs_batchnorm_fwd", x, gamma, beta, running_mean, running_var, y, xhat, istd, n, c, hw, eps,
+                    momentum, training, false);
+}
+
+int nrs_batchnorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd, const float* gamma, float* dx,
+                      float* dgamma, float* dbeta, int n, int c, int hw, int training, int accumulate_dx,
+                      int accumulate_params) {
+  return bn_backward(ctx, "nrs_batchnorm_bwd", g, xhat, istd, gamma, nullptr, dx, dgamma, dbeta, n, c, hw, training,
+                     accumulate_dx, accumulate_params, false);
+}
+
+int nrs_batchnorm_act_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const float* beta, float* running_mean,
+                          float* running_var, float* y, float* xhat, float* istd, int n, int c, int hw, float eps,
+                          float momentum, int training, int act) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, act_ok(act), NRS_ERR_ARG, "nrs_batchnorm_act_fwd: activation %d is not NONE or RELU", act);
+  NRS_REQUIRE(ctx, act == NRS_ACT_NONE || xhat, NRS_ERR_ARG, "nrs_batchnorm_act_fwd: a fused ReLU needs xhat saved");
+  return bn_forward(ctx, "nrs_batchnorm_act_fwd", x, gamma, beta, running_mean, running_var, y, xhat, istd, n, c, hw, eps,
+                    momentum, training, act == NRS_ACT_RELU);
+}
+
+int nrs_batchnorm_act_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd, const float* gamma,
+                          const float* beta, float* dx, float* dgamma, float* dbeta, int n, int c, int hw, int training,
+                          int accumulate_dx, int accumulate_params, int act) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, act_ok(act), NRS_ERR_ARG, "nrs_batchnorm_act_bwd: activation %d is not NONE or RELU", act);
+  return bn_backward(ctx, "nrs_batchnorm_act_bwd", g, xhat, istd, gamma, beta, dx, dgamma, dbeta, n, c, hw, training,
+                     accumulate_dx, accumulate_params, act == NRS_ACT_RELU);
 }

@@ -770,14 +770,16 @@ NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps
 // nodes owned by the caller and updated in place in training mode.
 NodeP batchnorm_nd(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
                    const NodeP& running_var, float momentum, float eps, bool training, size_t want_dims,
-                   const char* what) {
+                   const char* what, int act = NRS_ACT_NONE) {
   const std::string w(what);
   require_gpu(x, (w + ": input").c_str());
   require_gpu(gamma, (w + ": gamma").c_str());
   require_gpu(beta, (w + ": beta").c_str());
   require_gpu(running_mean, (w + ": running_mean").c_str());
   require_gpu(running_var, (w + ": running_var").c_str());
-  if (x->shape.size() != want_dims) fail(NRS_ERR_SHAPE, (w + ": input has the wrong number of dimensions").c_str());
+  if (x->shape.size() != want_dims && !(want_dims == 0 && (x->shape.size() == 2 || x->shape.size() == 4)))
+    fail(NRS_ERR_SHAPE, (w + ": input has the wrong number of dimensions").c_str());
+  if (act != NRS_ACT_NONE && act != NRS_ACT_RELU) fail(NRS_ERR_ARG, (w + ": only a ReLU can be fused").c_str());
   nrs_ctx* ctx = x->ctx;
   const int n = (int)x->shape[0], c = (int)x->shape[1];
   if (n < 1 || c < 1 || x->len() == 0) fail(NRS_ERR_SHAPE, (w + ": empty input").c_str());
@@ -789,10 +791,10 @@ NodeP batchnorm_nd(const NodeP& x, const NodeP& gamma, const NodeP& beta, const 
   float* istd = dalloc(ctx, (size_t)c);
   out->saved.push_back(xhat);
   out->saved.push_back(istd);
-  check(ctx, nrs_batchnorm_fwd(ctx, x->data, gamma->data, beta->data, running_mean->data, running_var->data, out->data,
-                               xhat, istd, n, c, hw, eps, momentum, training ? 1 : 0));
+  check(ctx, nrs_batchnorm_act_fwd(ctx, x->data, gamma->data, beta->data, running_mean->data, running_var->data, out->data,
+                                   xhat, istd, n, c, hw, eps, momentum, training ? 1 : 0, act));
   Node* self = out.get();
-  out->backward_fn = [self, x, gamma, beta, xhat, istd, n, c, hw, training]() {
+  out->backward_fn = [self, x, gamma, beta, xhat, istd, n, c, hw, training, act]() {
     nrs_ctx* ctx = self->ctx;
     const float* g = grad_in(self);
     float *dg = nullptr, *db = nullptr;
@@ -815,7 +817,8 @@ NodeP batchnorm_nd(const NodeP& x, const NodeP& gamma, const NodeP& beta, const 
       dx = t.ptr;
       acc_x = t.accumulate;
     }
-    check(ctx, nrs_batchnorm_bwd(ctx, g, xhat, istd, gamma->data, dx, dg, db, n, c, hw, training ? 1 : 0, acc_x, acc_p));
+    check(ctx, nrs_batchnorm_act_bwd(ctx, g, xhat, istd, gamma->data, beta->data, dx, dg, db, n, c, hw, training ? 1 : 0,
+                                     acc_x, acc_p, act));
   };
   return out;
 }
@@ -828,6 +831,13 @@ NodeP batchnorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, const Nod
 NodeP batchnorm2d(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
                   const NodeP& running_var, float momentum, float eps, bool training) {
   return batchnorm_nd(x, gamma, beta, running_mean, running_var, momentum, eps, training, 4, "cuda bn2d");
+}
+
+// batchnorm / batchnorm2d (by the input's rank) followed by `act` (NRS_ACT_NONE or NRS_ACT_RELU) in the same
+// two passes: the conv -> batchnorm2d -> relu unit of examples/cifar_cuda.rs:44-48 without the ReLU's own passes.
+NodeP batchnorm_act(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
+                    const NodeP& running_var, float momentum, float eps, bool training, int act) {
+  return batchnorm_nd(x, gamma, beta, running_mean, running_var, momentum, eps, training, 0, "cuda bn+act", act);
 }
 
 // dropout (src/cuda/nn/dropout.rs:31-84) and dropout2d (src/cuda/nn/dropout2d.rs:37-end): evaluation returns

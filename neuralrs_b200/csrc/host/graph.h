@@ -132,6 +132,9 @@ NodeP batchnorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, const Nod
                 const NodeP& running_var, float momentum, float eps, bool training);
 NodeP batchnorm2d(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
                   const NodeP& running_var, float momentum, float eps, bool training);
+// either of the two followed by a fused activation (NRS_ACT_NONE / NRS_ACT_RELU); rank 2 or 4 input
+NodeP batchnorm_act(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
+                    const NodeP& running_var, float momentum, float eps, bool training, int act);
 // dropout.rs / dropout2d.rs: evaluation returns `x` itself; `mask` == nullptr draws the mask on the device
 NodeP dropout(const NodeP& x, float p, bool training, const NodeP& mask = nullptr);
 NodeP dropout2d(const NodeP& x, float p, bool training, const NodeP& mask = nullptr);

@@ -243,6 +243,18 @@ int nrs_op_batchnorm2d(nrs_node* x, nrs_node* gamma, nrs_node* beta, nrs_node* r
   });
 }
 
+int nrs_op_batchnorm_act(nrs_node* x, nrs_node* gamma, nrs_node* beta, nrs_node* running_mean, nrs_node* running_var,
+                         float momentum, float eps, int training, int act, nrs_node** out) {
+  NODE_OK(x);
+  NODE_OK(gamma);
+  NODE_OK(beta);
+  NODE_OK(running_mean);
+  NODE_OK(running_var);
+  return wrap(ctx_of(x), out, [&] {
+    return nrs::cuda::batchnorm_act(x->p, gamma->p, beta->p, running_mean->p, running_var->p, momentum, eps, training != 0, act);
+  });
+}
+
 int nrs_op_dropout(nrs_node* x, float p, int training, nrs_node* mask, nrs_node** out) {
   NODE_OK(x);
   if (mask) NODE_OK(mask);

@@ -271,13 +271,12 @@ NodeP forward(nrs_trainer* t, const NodeP& x) {
       }
       case NRS_LAYER_FLATTEN: h = nrs::cuda::flatten(h); break;
       case NRS_LAYER_BATCHNORM:
-        h = h->shape.size() == 4
-                ? nrs::cuda::batchnorm2d(h, t->params[pi], t->params[pi + 1], t->buffers[bi], t->buffers[bi + 1],
-                                         t->bn_momentum, t->bn_eps, t->training)
-                : nrs::cuda::batchnorm(h, t->params[pi], t->params[pi + 1], t->buffers[bi], t->buffers[bi + 1],
-                                       t->bn_momentum, t->bn_eps, t->training);
+        // a ReLU behind the layer rides in its two passes (relu_next is only set when fusing is on)
+        h = nrs::cuda::batchnorm_act(h, t->params[pi], t->params[pi + 1], t->buffers[bi], t->buffers[bi + 1],
+                                     t->bn_momentum, t->bn_eps, t->training, relu_next ? NRS_ACT_RELU : NRS_ACT_NONE);
         pi += 2;
         bi += 2;
+        if (relu_next) ++li;
         break;
       case NRS_LAYER_DROPOUT: h = nrs::cuda::dropout(h, (float)l.a * 1e-6f, t->training); break;
       case NRS_LAYER_DROPOUT2D: h = nrs::cuda::dropout2d(h, (float)l.a * 1e-6f, t->training); break;

@@ -264,6 +264,15 @@ class nn:
                                                         C.c_float(momentum), C.c_float(eps), int(training), C.byref(h)), h)
 
     @staticmethod
+    def batchnorm_act(x: Node, gamma: Node, beta: Node, running_mean: Node, running_var: Node, momentum: float,
+                      eps: float, training: bool, act: int) -> Node:
+        """batchnorm / batchnorm2d (by rank) with the following ReLU fused (act: _lib.ACT_NONE / ACT_RELU)."""
+        h = VP()
+        return _out(x.ctx, x.ctx._l.nrs_op_batchnorm_act(x.h, gamma.h, beta.h, running_mean.h, running_var.h,
+                                                          C.c_float(momentum), C.c_float(eps), int(training), int(act),
+                                                          C.byref(h)), h)
+
+    @staticmethod
     def dropout(x: Node, p: float, training: bool, mask: Node | None = None) -> Node:
         """src/cuda/nn/dropout.rs:31-84.  mask=None draws the mask on the device (context seed and counter)."""
         h = VP()

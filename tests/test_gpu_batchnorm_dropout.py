@@ -266,3 +266,64 @@ def test_cuda_dropout2d_channel_mechanics(gpu_ctx, oracle32):
     assert np.array_equal(gpu.to_host(ev), x)
     with pytest.raises(_lib.NrsError):
         nn.dropout2d(on_gpu(x, [total]), p, True)
+
+
+@pytest.mark.parametrize("n,c,hw", [(16, 8, 1), (4, 3, 25), (64, 32, 64), (32, 64, 256), (128, 256, 16), (300, 70, 1)])
+@pytest.mark.parametrize("training", [True, False], ids=["train", "eval"])
+def test_batchnorm_with_fused_relu(gpu_ctx, oracle64, n, c, hw, training):
+    """nrs_batchnorm_act_* with NRS_ACT_RELU against BatchNorm followed by ReLU in the oracle
+    (src/autograd/graph/relu.rs:12-49: y = max(0, x), gradient passes where x > 0)."""
+    rng = np.random.default_rng(n + c + hw)
+    x = (rng.normal(size=(n, c, hw)) * 1.5 + rng.normal(size=(1, c, 1))).astype(np.float32)
+    gamma, beta = rng.normal(1.0, 0.5, size=c).astype(np.float32), rng.normal(size=c).astype(np.float32)
+    rm0, rv0 = rng.normal(size=c).astype(np.float32), rng.uniform(0.5, 2.0, size=c).astype(np.float32)
+    g = rng.normal(size=(n, c, hw)).astype(np.float32)
+    yr, xhr, isr, _, _ = oracle64.batchnorm_fwd(x, gamma, beta, rm0, rv0, 1e-5, 0.9, training)
+    y, xh, ist = Dev(gpu_ctx, shape=x.shape), Dev(gpu_ctx, shape=x.shape), Dev(gpu_ctx, shape=(c,))
+    dga, dbe = Dev(gpu_ctx, gamma), Dev(gpu_ctx, beta)
+    call(gpu_ctx, "nrs_batchnorm_act_fwd", Dev(gpu_ctx, x), dga, dbe, Dev(gpu_ctx, rm0), Dev(gpu_ctx, rv0), y, xh, ist,
+         n, c, hw, F(1e-5), F(0.9), int(training), _lib.ACT_RELU)
+    got = y.get()
+    assert (got >= 0).all()
+    assert np.abs(got - oracle64.relu_fwd(yr)).max() <= 1e-4 * max(1.0, np.abs(yr).max())
+    # outputs within rounding of zero may fall on either side of the ReLU: bound their share, then compare the
+    # backward arithmetic under the device's own mask
+    mask = got > 0
+    assert ((yr > 0) != mask).mean() <= 1e-3
+    dxr, dgr, dbr = oracle64.batchnorm_bwd(g * mask, xhr, isr, gamma, training)
+    gx, gg, gb = Dev(gpu_ctx, shape=x.shape), Dev(gpu_ctx, shape=(c,)), Dev(gpu_ctx, shape=(c,))
+    call(gpu_ctx, "nrs_batchnorm_act_bwd", Dev(gpu_ctx, g), xh, ist, dga, dbe, gx, gg, gb, n, c, hw, int(training), 0, 0,
+         _lib.ACT_RELU)
+    assert rel_l2(gg.get(), dgr) <= 1e-4 and rel_l2(gb.get(), dbr) <= 1e-4
+    assert rel_l2(gx.get(), dxr) <= 1e-4
+    # act = NONE is the plain pair of entry points, bit for bit
+    y0, xh0, ist0 = Dev(gpu_ctx, shape=x.shape), Dev(gpu_ctx, shape=x.shape), Dev(gpu_ctx, shape=(c,))
+    y1, xh1, ist1 = Dev(gpu_ctx, shape=x.shape), Dev(gpu_ctx, shape=x.shape), Dev(gpu_ctx, shape=(c,))
+    call(gpu_ctx, "nrs_batchnorm_act_fwd", Dev(gpu_ctx, x), dga, dbe, Dev(gpu_ctx, rm0), Dev(gpu_ctx, rv0), y0, xh0, ist0,
+         n, c, hw, F(1e-5), F(0.9), int(training), _lib.ACT_NONE)
+    call(gpu_ctx, "nrs_batchnorm_fwd", Dev(gpu_ctx, x), dga, dbe, Dev(gpu_ctx, rm0), Dev(gpu_ctx, rv0), y1, xh1, ist1,
+         n, c, hw, F(1e-5), F(0.9), int(training))
+    assert np.array_equal(y0.get(), y1.get()) and np.array_equal(xh0.get(), xh1.get())
+
+
+def test_batchnorm_act_graph_matches_separate_relu(gpu_ctx):
+    """The fused node and batchnorm2d followed by a relu node agree bit for bit, forward and backward."""
+    rng = np.random.default_rng(91)
+    shape, c = (8, 16, 12, 12), 16
+    x = rng.normal(size=shape).astype(np.float32)
+    gamma, beta = rng.normal(1.0, 0.3, size=c).astype(np.float32), rng.normal(size=c).astype(np.float32)
+    seed = rng.normal(size=shape).astype(np.float32)
+    res = []
+    for fused in (True, False):
+        gi, gg, gb = on_gpu(x, shape), on_gpu(gamma, [c]), on_gpu(beta, [c])
+        rm, rv = on_gpu(np.zeros(c), [c]), on_gpu(np.ones(c), [c])
+        if fused:
+            out = nn.batchnorm_act(gi, gg, gb, rm, rv, 0.9, 1e-5, True, _lib.ACT_RELU)
+        else:
+            out = graph.relu(nn.batchnorm2d(gi, gg, gb, rm, rv, 0.9, 1e-5, True))
+        y = gpu.to_host(out)
+        gpu.set_grad(out, seed.ravel())
+        backward_graph(out)
+        res.append((y, gpu.read_grad(gi), gpu.read_grad(gg), gpu.read_grad(gb), gpu.to_host(rm), gpu.to_host(rv)))
+    for a, b in zip(*res):
+        assert np.array_equal(a, b)
