@@ -350,9 +350,9 @@ inline void plan_split(const nrs_ctx* ctx, long tiles, int kb_total, bool limit_
   int s = 1;
   // (More than half a wave of tiles runs unsplit: the second pass over the partial tiles costs more
   // than the idle SMs.)
-  if (2 * tiles <= ctx->sm_count && kb_total >= 16) {
+  if (2 * tiles <= ctx->sm_count && kb_total >= 32) {
     s = (int)(ctx->sm_count / tiles);
-    if (s > kb_total / 8) s = kb_total / 8;
+    if (s > kb_total / 16) s = kb_total / 16;   // a split shorter than 16 K-blocks is all prologue and second pass
   }
   if (limit_chain) {
     const int need = (kb_total * BK + kMaxChainK - 1) / kMaxChainK;
