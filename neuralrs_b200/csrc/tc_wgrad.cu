@@ -203,33 +203,42 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
 __global__ void __launch_bounds__(kReduceThreads)
 tc_wgrad_reduce_kernel(const WgradParams p, int splits, int lanes, float* __restrict__ dw, int accumulate) {
   NRS_PDL_PROLOGUE();
-  __shared__ float lane_sum[kReduceThreads];
-  const int per_block = kReduceThreads / lanes;   // outputs of this block
+  __shared__ float4 lane_sum[kReduceThreads];
+  const int per_block = kReduceThreads / lanes;   // output quads of this block
   const int lane = threadIdx.x / per_block, slot = threadIdx.x - lane * per_block;
   const int taps = p.kh * p.kw;
-  const size_t total = (size_t)p.co * p.ci * taps;
+  const int cq = p.ci / 4;                        // a thread owns four consecutive input channels (ci % 32 == 0)
+  const size_t total = (size_t)p.co * cq * taps;
   const size_t idx = (size_t)blockIdx.x * per_block + slot;
   const bool live = idx < total;
-  // idx enumerates (co, tap, ci) so that reads of the partials are coalesced along ci
-  const int c = (int)(idx % p.ci);
-  const int tap = (int)((idx / p.ci) % taps);
-  const int co = (int)(idx / ((size_t)p.ci * taps));
+  // idx enumerates (co, tap, ci/4) so that reads of the partials are coalesced 128-bit loads along ci
+  const int c = (int)(idx % cq) * 4;
+  const int tap = (int)((idx / cq) % taps);
+  const int co = (int)(idx / ((size_t)cq * taps));
   const int mb = co / 128, row = co - mb * 128;
   const int grp = tap / p.taps_per_group, t = tap - grp * p.taps_per_group;
   const size_t tile = (size_t)128 * p.group_cols;
   const size_t off = (((size_t)mb * p.n_groups + grp) * 128 + row) * p.group_cols + (size_t)t * p.ci + c;
   const size_t split_stride = (size_t)p.m_blocks * p.n_groups * tile;
-  float s = 0.0f;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
   if (live) {
 #pragma unroll 4
-    for (int z = lane; z < splits; z += lanes) s += p.partial[(size_t)z * split_stride + off];
+    for (int z = lane; z < splits; z += lanes) {
+      const float4 v = *reinterpret_cast<const float4*>(p.partial + (size_t)z * split_stride + off);
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
   }
   lane_sum[threadIdx.x] = s;
   __syncthreads();
   if (lane != 0 || !live) return;
-  for (int l = 1; l < lanes; ++l) s += lane_sum[l * per_block + slot];
+  for (int l = 1; l < lanes; ++l) {
+    const float4 v = lane_sum[l * per_block + slot];
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
   float* dst = dw + ((size_t)co * p.ci + c) * taps + tap;
-  *dst = accumulate ? *dst + s : s;
+  const float r[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) dst[(size_t)k * taps] = accumulate ? dst[(size_t)k * taps] + r[k] : r[k];
 }
 
 }  // namespace
@@ -365,7 +374,7 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   if (st != NRS_OK) return st;
   const size_t total = (size_t)co * ci * taps;
   const int lanes = reduce_lanes(splits);
-  NRS_PDL_LAUNCH(tc_wgrad_reduce_kernel, nrs_blocks(total, kReduceThreads / lanes), kReduceThreads, 0, ctx->stream, p, splits, lanes, dw,
+  NRS_PDL_LAUNCH(tc_wgrad_reduce_kernel, nrs_blocks(total / 4, kReduceThreads / lanes), kReduceThreads, 0, ctx->stream, p, splits, lanes, dw,
                  accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;

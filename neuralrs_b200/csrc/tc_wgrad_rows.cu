@@ -286,17 +286,18 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
 __global__ void __launch_bounds__(kReduceThreads)
 tc_wgrad_rows_reduce_kernel(const RowParams p, int splits, int ctas, int lanes, float* __restrict__ dw, int accumulate) {
   NRS_PDL_PROLOGUE();
-  __shared__ float lane_sum[kReduceThreads];
-  const int per_block = kReduceThreads / lanes;   // outputs of this block
+  __shared__ float4 lane_sum[kReduceThreads];
+  const int per_block = kReduceThreads / lanes;   // output quads of this block
   const int lane = threadIdx.x / per_block, slot = threadIdx.x - lane * per_block;
-  const size_t total = (size_t)p.co * 9 * p.ci;
+  const int cq = p.ci / 4;                        // a thread owns four consecutive input channels (ci % 32 == 0)
+  const size_t total = (size_t)p.co * 9 * cq;
   const size_t idx = (size_t)blockIdx.x * per_block + slot;
   const bool live = idx < total;
-  // idx enumerates (co, j, i, ci): consecutive threads read consecutive partial columns
-  const int ci = (int)(idx % p.ci);
-  const int i = (int)((idx / p.ci) % 3);
-  const int j = (int)((idx / ((size_t)p.ci * 3)) % 3);
-  const int co = (int)(idx / ((size_t)p.ci * 9));
+  // idx enumerates (co, j, i, ci/4): consecutive threads read consecutive 128-bit groups of partial columns
+  const int ci = (int)(idx % cq) * 4;
+  const int i = (int)((idx / cq) % 3);
+  const int j = (int)((idx / ((size_t)cq * 3)) % 3);
+  const int co = (int)(idx / ((size_t)cq * 9));
   int mb = co / 128, row = co - mb * 128, jk = j;
   if (p.pack) {   // tap 1 -> kind 0 rows [0,h); tap 0 -> kind 0 rows [h,2h); tap 2 -> kind 1 rows [0,h)
     mb = 0;
@@ -308,17 +309,25 @@ tc_wgrad_rows_reduce_kernel(const RowParams p, int splits, int ctas, int lanes, 
   const size_t cols = (size_t)kTaps * p.chunk;
   const size_t off = ((size_t)cta * 128 + row) * cols + (size_t)i * p.chunk + c;
   const size_t split_stride = (size_t)ctas * 128 * cols;
-  float s = 0.0f;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
   if (live) {
 #pragma unroll 4
-    for (int z = lane; z < splits; z += lanes) s += p.partial[(size_t)z * split_stride + off];
+    for (int z = lane; z < splits; z += lanes) {
+      const float4 v = *reinterpret_cast<const float4*>(p.partial + (size_t)z * split_stride + off);
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
   }
   lane_sum[threadIdx.x] = s;
   __syncthreads();
   if (lane != 0 || !live) return;
-  for (int l = 1; l < lanes; ++l) s += lane_sum[l * per_block + slot];
+  for (int l = 1; l < lanes; ++l) {
+    const float4 v = lane_sum[l * per_block + slot];
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
   float* dst = dw + (((size_t)co * p.ci + ci) * 3 + i) * 3 + j;
-  *dst = accumulate ? *dst + s : s;
+  const float r[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) dst[(size_t)k * 9] = accumulate ? dst[(size_t)k * 9] + r[k] : r[k];
 }
 
 template <int NPLANES, int KS>
@@ -433,7 +442,7 @@ int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float*
   if (st != NRS_OK) return st;
   const size_t total = (size_t)co * ci * 9;
   const int lanes = reduce_lanes(splits);
-  NRS_PDL_LAUNCH(tc_wgrad_rows_reduce_kernel, nrs_blocks(total, kReduceThreads / lanes), kReduceThreads, 0, ctx->stream, p, splits,
+  NRS_PDL_LAUNCH(tc_wgrad_rows_reduce_kernel, nrs_blocks(total / 4, kReduceThreads / lanes), kReduceThreads, 0, ctx->stream, p, splits,
                  ctas, lanes, dw, accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
