@@ -42,7 +42,7 @@ WORKLOADS = {"vgg_cifar": ("VGG_CIFAR", 1024, 3), "small_cnn": ("SMALL_CNN", 64,
              "vgg_cifar_bn": ("VGG_CIFAR_BN", 1024, 7)}
 CPU_SAMPLE_BATCH = {"vgg_cifar": 16, "small_cnn": 64, "wide_mlp": 32, "vgg_cifar_bn": 16}
 MATH = {"3xtf32": 0, "tf32": 1, "fp32": 2}
-PROF_NAMES = ["conv_fwd", "conv_dgrad", "conv_wgrad", "gemm", "adamw"]
+PROF_NAMES = ["conv_fwd", "conv_dgrad", "conv_wgrad", "gemm", "adamw", "batchnorm"]
 
 
 def parse():
@@ -473,6 +473,8 @@ def run_ours(args):
                          "families_ms_per_step": {k: prof[k]["ms"] / bracketed for k in prof},
                          "bracketed_steps": bracketed,
                          "adamw_gbs": (adam["work"] / (adam["ms"] / 1e3) / 1e9) if adam["ms"] > 0 else None,
+                         "batchnorm_gbs": (prof["batchnorm"]["work"] / (prof["batchnorm"]["ms"] / 1e3) / 1e9)
+                         if prof["batchnorm"]["ms"] > 0 else None,
                          "hbm_peak_gbs": peaks["hbm_gbs"]},
         }
         if world == 1 and args.workload == "vgg_cifar":

@@ -89,7 +89,7 @@ int nrs_has_tensor_core_path(void);
  * examples/cifar_cuda.rs:265,284). */
 enum nrs_prof_kind {
   NRS_PROF_CONV_FWD = 0, NRS_PROF_CONV_DGRAD = 1, NRS_PROF_CONV_WGRAD = 2,
-  NRS_PROF_GEMM = 3, NRS_PROF_ADAMW = 4, NRS_PROF_KINDS = 5
+  NRS_PROF_GEMM = 3, NRS_PROF_ADAMW = 4, NRS_PROF_BATCHNORM = 5 /* work = algorithmic bytes */, NRS_PROF_KINDS = 6
 };
 /* Self-test of the time-out path (no reference counterpart).  Every device-side wait of the
  * tensor-core kernels is bounded: on expiry the kernel records a code, and the next nrs_sync /

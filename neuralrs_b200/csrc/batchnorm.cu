@@ -316,6 +316,7 @@ int bn_forward(nrs_ctx* ctx, const char* who, const float* x, const float* gamma
   NRS_REQUIRE_CTX(ctx);
   NRS_REQUIRE(ctx, check_dims(n, c, hw), NRS_ERR_SHAPE, "%s: bad shape [%d,%d,%d]", who, n, c, hw);
   NRS_REQUIRE(ctx, x && gamma && beta && running_mean && running_var && y && istd, NRS_ERR_ARG, "%s: null tensor", who);
+  NrsProfScope prof(ctx, NRS_PROF_BATCHNORM, 12.0 * (double)n * c * hw);   // x in; y, xhat out
   const int splits = training ? plan_splits(ctx, n, c, hw) : 1;
   void* ws = nullptr;
   const int st = nrs_workspace(ctx, ((size_t)splits * c * 2 + c) * sizeof(float), &ws);
@@ -350,6 +351,7 @@ int bn_backward(nrs_ctx* ctx, const char* who, const float* g, const float* xhat
   NRS_REQUIRE(ctx, (dgamma == nullptr) == (dbeta == nullptr), NRS_ERR_ARG, "%s: dgamma and dbeta must be given together", who);
   NRS_REQUIRE(ctx, g && xhat && istd && gamma && (!relu || beta), NRS_ERR_ARG, "%s: null tensor", who);
   if (!dx && !dgamma) return NRS_OK;
+  NrsProfScope prof(ctx, NRS_PROF_BATCHNORM, 12.0 * (double)n * c * hw);   // g, xhat in; dx out
   const bool need_sums = dgamma || training;
   const int splits = need_sums ? plan_splits(ctx, n, c, hw) : 1;
   void* ws = nullptr;
