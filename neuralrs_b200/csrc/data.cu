@@ -8,24 +8,14 @@
 // dy likewise from word 2, with u(w) = (w >> 8) * 2^-24 — the reference's `(random::<f32>() * 9.0) as i32 - 4`
 // for s = 4.  A call consumes n blocks.
 #include "nrs_internal.h"
+#include "philox.cuh"
 
 namespace {
 
 constexpr int kThreads = 256;
 
-__device__ __forceinline__ void philox_round(uint32_t (&ctr)[4], uint32_t k0, uint32_t k1) {
-  const uint64_t p0 = (uint64_t)0xD2511F53u * ctr[0];
-  const uint64_t p1 = (uint64_t)0xCD9E8D57u * ctr[2];
-  const uint32_t n0 = (uint32_t)(p1 >> 32) ^ ctr[1] ^ k0;
-  const uint32_t n1 = (uint32_t)p1;
-  const uint32_t n2 = (uint32_t)(p0 >> 32) ^ ctr[3] ^ k1;
-  const uint32_t n3 = (uint32_t)p0;
-  ctr[0] = n0; ctr[1] = n1; ctr[2] = n2; ctr[3] = n3;
-}
-
 __device__ __forceinline__ int draw_shift(uint32_t word, int max_shift) {
-  const float u = (float)(word >> 8) * (1.0f / 16777216.0f);
-  return (int)(u * (float)(2 * max_shift + 1)) - max_shift;
+  return (int)(nrs_rng::uniform01(word) * (float)(2 * max_shift + 1)) - max_shift;
 }
 
 // One block per (image, channel) plane; the plane's draw is recomputed by every block of the image (ten
@@ -35,15 +25,8 @@ augment_kernel(const float* __restrict__ x, float* __restrict__ y, int c, int h,
                uint64_t seed, uint64_t offset) {
   NRS_PDL_PROLOGUE();
   const int img = blockIdx.x / c;
-  const uint64_t at = offset + (uint64_t)img;
-  uint32_t ctr[4] = {(uint32_t)at, (uint32_t)(at >> 32), 0u, 0u};
-  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
-#pragma unroll
-  for (int r = 0; r < 10; ++r) {
-    philox_round(ctr, k0, k1);
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
-  }
+  uint32_t ctr[4];
+  nrs_rng::block(seed, offset + (uint64_t)img, ctr);
   const bool flip = do_flip && (ctr[0] >> 31);
   const int dx = draw_shift(ctr[1], max_shift), dy = draw_shift(ctr[2], max_shift);
   const float* src = x + (size_t)blockIdx.x * h * w;

@@ -9,33 +9,14 @@
 // 2^-24 in [0,1), mask = u < p ? 0 : 1/(1-p).  The same seed and offset give the same mask on any launch
 // shape; a caller that wants the reference's own masks passes them to nrs_mask_mul instead.
 #include "nrs_internal.h"
+#include "philox.cuh"
 
 namespace {
 
 constexpr int kThreads = 256;
 
-__host__ __device__ __forceinline__ void philox_round(uint32_t (&ctr)[4], uint32_t k0, uint32_t k1) {
-  const uint64_t p0 = (uint64_t)0xD2511F53u * ctr[0];
-  const uint64_t p1 = (uint64_t)0xCD9E8D57u * ctr[2];
-  const uint32_t n0 = (uint32_t)(p1 >> 32) ^ ctr[1] ^ k0;
-  const uint32_t n1 = (uint32_t)p1;
-  const uint32_t n2 = (uint32_t)(p0 >> 32) ^ ctr[3] ^ k1;
-  const uint32_t n3 = (uint32_t)p0;
-  ctr[0] = n0; ctr[1] = n1; ctr[2] = n2; ctr[3] = n3;
-}
-
-__host__ __device__ __forceinline__ void philox4x32_10(uint32_t (&ctr)[4], uint32_t k0, uint32_t k1) {
-#pragma unroll
-  for (int r = 0; r < 10; ++r) {
-    philox_round(ctr, k0, k1);
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
-  }
-}
-
 __device__ __forceinline__ float mask_value(uint32_t word, float p, float scale) {
-  const float u = (float)(word >> 8) * (1.0f / 16777216.0f);
-  return u < p ? 0.0f : scale;
+  return nrs_rng::uniform01(word) < p ? 0.0f : scale;
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -45,9 +26,8 @@ dropout_mask_kernel(float* __restrict__ mask, size_t count, float p, float scale
   const size_t blocks = (count + 3) / 4;
   const bool vec = (reinterpret_cast<uintptr_t>(mask) & 15) == 0;
   for (size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks; b += stride) {
-    const uint64_t at = offset + b;
-    uint32_t ctr[4] = {(uint32_t)at, (uint32_t)(at >> 32), 0u, 0u};
-    philox4x32_10(ctr, (uint32_t)seed, (uint32_t)(seed >> 32));
+    uint32_t ctr[4];
+    nrs_rng::block(seed, offset + b, ctr);
     const float4 v = make_float4(mask_value(ctr[0], p, scale), mask_value(ctr[1], p, scale),
                                  mask_value(ctr[2], p, scale), mask_value(ctr[3], p, scale));
     const size_t i = b * 4;
