@@ -31,29 +31,59 @@ embed_fwd_kernel(const float* __restrict__ w, const int32_t* __restrict__ idx, f
   }
 }
 
-// One block per vocabulary row; thread d owns feature d (strided when dim > blockDim).
-// Token indices are staged through shared memory in chunks.
+// One block per vocabulary row.  The token indices are scanned 256 at a time: every thread tests one
+// token, the matches are compacted IN TOKEN ORDER (warp ballots + a prefix over the warp counts) into a
+// shared list, and then thread d adds the matching gradient rows in that order — the same order of
+// additions as a serial walk over the tokens, so the result is deterministic and independent of the
+// launch shape, at a cost of tokens/256 scan steps per block instead of `tokens` per thread.
 __global__ void __launch_bounds__(256)
 embed_bwd_kernel(const float* __restrict__ g, const int32_t* __restrict__ idx, float* dw, int tokens, int dim,
                  int accumulate) {
   NRS_PDL_PROLOGUE();
-  __shared__ int32_t s_idx[1024];
+  constexpr int kChunk = 1024;             // tokens whose matches are listed before they are summed
+  __shared__ int32_t s_match[kChunk];
+  __shared__ int s_warp[2][8];             // per-warp match counts, double-buffered across scan steps
   const int row = blockIdx.x;
-  for (int d0 = 0; d0 < dim; d0 += blockDim.x) {
-    const int d = d0 + threadIdx.x;
-    float acc = 0.0f;
-    for (int t0 = 0; t0 < tokens; t0 += 1024) {
-      const int nt = min(1024, tokens - t0);
-      __syncthreads();
-      for (int i = threadIdx.x; i < nt; i += blockDim.x) s_idx[i] = idx[t0 + i];
-      __syncthreads();
-      if (d < dim)
-        for (int i = 0; i < nt; ++i)
-          if (s_idx[i] == row) acc += g[(size_t)(t0 + i) * dim + d];
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
+  int step = 0;
+  for (int d0 = 0; d0 < dim; d0 += 4 * 256) {             // four features per thread per pass
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int t0 = 0; t0 < tokens; t0 += kChunk) {
+      const int nt = min(kChunk, tokens - t0);
+      __syncthreads();                                    // the previous chunk's list has been consumed
+      int n_match = 0;                                    // kept by every thread; the same in all of them
+      for (int sub = 0; sub < nt; sub += 256, ++step) {
+        const int t = t0 + sub + threadIdx.x;
+        const bool hit = (sub + (int)threadIdx.x) < nt && idx[t] == row;
+        const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) s_warp[step & 1][wrp] = __popc(ballot);
+        __syncthreads();   // one barrier per step: the next step writes the other buffer, and a warp can only
+                           // reach the step after that once every warp has passed the next barrier
+        int before = n_match, total = 0;
+#pragma unroll
+        for (int w2 = 0; w2 < 8; ++w2) {
+          const int cnt = s_warp[step & 1][w2];
+          if (w2 < wrp) before += cnt;
+          total += cnt;
+        }
+        if (hit) s_match[before + __popc(ballot & ((1u << lane) - 1u))] = t;
+        n_match += total;
+      }
+      __syncthreads();                                    // the list is complete
+      for (int m = 0; m < n_match; ++m) {
+        const float* src = g + (size_t)s_match[m] * dim + d0 + threadIdx.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (d0 + (int)threadIdx.x + k * 256 < dim) acc[k] += src[k * 256];
+      }
     }
-    if (d < dim) {
-      float* dst = dw + (size_t)row * dim + d;
-      *dst = accumulate ? *dst + acc : acc;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int d = d0 + threadIdx.x + k * 256;
+      if (d < dim) {
+        float* dst = dw + (size_t)row * dim + d;
+        *dst = accumulate ? *dst + acc[k] : acc[k];
+      }
     }
   }
 }
