@@ -86,15 +86,12 @@ attn_fwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
   float o[kMaxDh];
 #pragma unroll
   for (int d = 0; d < kMaxDh; ++d) o[d] = 0.0f;
-  float* prow = probs + ((size_t)bh * S + (row_live ? i : 0)) * S;
 #pragma unroll
   for (int jj = 0; jj < 64; ++jj) {
     const int j = j0 + jj;
     const float p = s[jj] * inv;
-    if (row_live && j < S) {
-      prow[j] = p;
-      axpy32(o, p, Vs + j * kLd);
-    }
+    s[jj] = p;
+    if (row_live && j < S) axpy32(o, p, Vs + j * kLd);
   }
 #pragma unroll
   for (int d = 0; d < kMaxDh; ++d) o[d] += __shfl_xor_sync(0xffffffffu, o[d], 1);
@@ -102,6 +99,23 @@ attn_fwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
 #pragma unroll
     for (int d = 0; d < kMaxDh; ++d)
       if ((d >> 4) == half && d < dh) out[base + (size_t)i * D + d] = o[d];   // each thread of the pair writes 16 columns
+  }
+  // The probabilities (saved for the backward pass) leave through shared memory, 32 key columns at a time, so
+  // that a warp writes one 128-byte row segment per store; written from the registers directly, the 32 lanes
+  // of a store would hit 32 different rows.  The K tile is no longer needed and holds the staging rows.
+  float* stage = Ks;
+#pragma unroll
+  for (int chunk = 0; chunk < 4; ++chunk) {
+    __syncthreads();   // the K tile (first round) / the previous chunk has been consumed by every thread
+    if (half == (chunk >> 1) && row_live) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) stage[i * kLd + c] = s[(chunk & 1) * 32 + c];
+    }
+    __syncthreads();
+    for (int e = tid; e < kMaxSeq * 32; e += 256) {
+      const int r = e >> 5, c = e & 31, j = chunk * 32 + c;
+      if (r < S && j < S) probs[((size_t)bh * S + r) * S + j] = stage[r * kLd + c];
+    }
   }
 }
 
