@@ -97,6 +97,10 @@ enum nrs_prof_kind {
  * one-thread kernel that waits `limit_clocks` SM clocks on a barrier nobody completes, so that path
  * can be exercised without a fault or a hang. */
 int nrs_selftest_bounded_wait(nrs_ctx* ctx, int64_t limit_clocks);
+/* Host-only self-test (no reference counterpart, needs no GPU): the library remembers per device
+ * ordinal which kernels already had their dynamic shared-memory limit raised, so that contexts on
+ * several GPUs of one process each get theirs.  Returns 0 when that bookkeeping behaves. */
+int nrs_selftest_smem_attr_bookkeeping(void);
 
 int nrs_profile_enable(nrs_ctx* ctx, int on);
 int nrs_profile_reset(nrs_ctx* ctx);
@@ -288,9 +292,15 @@ int nrs_onehot(nrs_ctx* ctx, const int32_t* labels, float* out, int batch, int c
  * out[t,:] = weight[idx[t],:] for `tokens` int32 device indices, and the
  * scatter-add of the gradient back into dweight[vocab,dim] (+)=.  The backward
  * walks tokens in order per vocabulary row: deterministic, unlike the
- * reference's atomicAdd.  Indices must lie in [0, vocab) (the caller checks, as
- * the reference asserts on the host, embedding.rs:55-57). */
-int nrs_embedding_fwd(nrs_ctx* ctx, const float* weight, const int32_t* idx, float* out, int tokens, int dim);
+ * reference's atomicAdd.  The reference asserts on the host that indices lie in
+ * [0, vocab) (embedding.rs:55-57); these indices live on the device, so the kernel
+ * checks instead: an index outside the range is not dereferenced, its output row
+ * is zeros, and the next nrs_sync / nrs_d2h returns NRS_ERR_ARG. */
+int nrs_embedding_fwd(nrs_ctx* ctx, const float* weight, const int32_t* idx, float* out, int tokens, int dim, int vocab);
+/* The same gather with PositionalEncoding::forward (src/cuda/nn/positional.rs:36-44) folded in:
+ * out[t, :] = weight[idx[t], :] + pos_table[t % seq, :] for tokens laid out [batch, seq]. */
+int nrs_embedding_pos_fwd(nrs_ctx* ctx, const float* weight, const int32_t* idx, const float* pos_table, float* out,
+                          int tokens, int seq, int dim, int vocab);
 int nrs_embedding_bwd(nrs_ctx* ctx, const float* g, const int32_t* idx, float* dweight, int tokens, int dim,
                       int vocab, int accumulate);
 /* Causal mask over [batch, s, s] attention scores.  No reference counterpart (the

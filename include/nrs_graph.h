@@ -36,9 +36,16 @@ int nrs_node_shape(const nrs_node* n, int64_t* shape_out, int capacity);
 int64_t nrs_node_len(const nrs_node* n);
 /* Node.requires_grad — src/autograd/node.rs:33-36,45. */
 int nrs_node_set_requires_grad(nrs_node* n, int flag);
-/* Device pointers of a resident node (NULL when absent). */
+/* Replaces the node's HOST data (what the reference does by assigning `node.borrow_mut().data`);
+ * the next nrs_to_cuda uploads it into the node's existing device buffer. */
+int nrs_node_set_data(nrs_node* n, const float* host_data);
+/* Device pointers of a resident node (NULL when absent).  The library caches re-laid-out copies
+ * of a tensor that a convolution has read (its tensor-core operand planes); a caller that writes
+ * new values through nrs_node_data_ptr must call nrs_node_invalidate afterwards, or use a fresh
+ * node.  nrs_to_cuda invalidates by itself. */
 float* nrs_node_data_ptr(nrs_node* n);
 float* nrs_node_grad_ptr(nrs_node* n);
+int nrs_node_invalidate(nrs_node* n);
 
 /* cuda::runtime — src/cuda/runtime.rs:39-124. */
 int nrs_to_cuda(nrs_node* n);
@@ -157,7 +164,18 @@ enum nrs_layer_kind {
   NRS_LAYER_BATCHNORM = 6, /* a=channels (features after flatten): BatchNorm2d on [C,H,W], BatchNorm on [F];
                               momentum 0.9, eps 1e-5 unless nrs_trainer_set_batchnorm says otherwise */
   NRS_LAYER_DROPOUT = 7,   /* a=drop probability in parts per million (500000 = 0.5) */
-  NRS_LAYER_DROPOUT2D = 8  /* a=as above; whole (sample, channel) planes             */
+  NRS_LAYER_DROPOUT2D = 8, /* a=as above; whole (sample, channel) planes             */
+  /* Token models.  An embedding layer must be the first layer: the model then reads int32 token ids
+   * [batch, seq] (in_shape = {seq}) through the *_tokens entry points, activations are [batch, seq, d],
+   * a linear layer acts on every position, and the loss runs over batch*seq rows. */
+  NRS_LAYER_EMBEDDING = 9, /* a=vocab b=d_model c=max_len: Embedding::forward_batch (src/nn/embedding.rs:60-113)
+                              followed, when c > 0, by PositionalEncoding::new(d_model, max_len).forward
+                              (src/cuda/nn/positional.rs:18-44), both in one gather kernel               */
+  NRS_LAYER_TRANSFORMER_BLOCK = 10, /* a=d_model b=num_heads c=d_ff d=activation (NRS_ACT_RELU as
+                              src/cuda/nn/transformer_block.rs:28-60, or NRS_ACT_GELU) e=flags: bit 0 causal
+                              attention mask, bit 1 forward_no_final_norm.  Adds the block's 12 parameters in
+                              the reference's parameters() order (see nrs_op_transformer_block)             */
+  NRS_LAYER_LAYERNORM = 11 /* a=features; eps 1e-5; adds [gamma, beta]                */
 };
 typedef struct nrs_layer_spec { int kind, a, b, c, d, e; } nrs_layer_spec;
 
@@ -218,7 +236,21 @@ int nrs_trainer_set_augment(nrs_trainer* t, int max_shift, int flip);
 /* Same step on inputs already resident on the device. */
 int nrs_trainer_step_device(nrs_trainer* t, const float* x_dev, const float* target_dev, int batch,
                             float* loss_out);
-/* Loss of the most recent step (waits for it). */
+/* The same entry points for a token model (first layer NRS_LAYER_EMBEDDING): ids is int32
+ * [batch, seq]; labels is int32 [batch*seq], the class of every position (for a language model
+ * the next token), expanded on the device to the one-hot rows cross_entropy takes
+ * (src/cuda/loss/cross_entropy.rs:74-98).  The loss is the mean over batch*seq rows.  An id outside
+ * the vocabulary is not dereferenced; the next call that waits returns NRS_ERR_ARG. */
+int nrs_trainer_forward_backward_tokens(nrs_trainer* t, const int32_t* ids_host, const int32_t* labels_host, int batch,
+                                        float* loss_out);
+int nrs_trainer_step_tokens(nrs_trainer* t, const int32_t* ids_host, const int32_t* labels_host, int batch, float* loss_out);
+int nrs_trainer_stage_next_tokens(nrs_trainer* t, const int32_t* ids_host, const int32_t* labels_host, int batch);
+int nrs_trainer_step_tokens_device(nrs_trainer* t, const int32_t* ids_dev, const int32_t* labels_dev, int batch,
+                                   float* loss_out);
+/* Loss of the most recent step (waits for it).  With data parallelism enabled every loss this
+ * library reports (here and through loss_out) is THIS RANK'S SHARE of the global mean: the sum
+ * over its shard divided by the global batch; the shares of all ranks add up to the loss a single
+ * GPU would report for the whole batch. */
 int nrs_trainer_last_loss(nrs_trainer* t, float* loss_out);
 
 /* Data parallelism (no reference counterpart: the reference is single-GPU).
@@ -227,10 +259,52 @@ int nrs_trainer_last_loss(nrs_trainer* t, float* loss_out);
  * its shard of `global_batch`; the loss/gradient are divided by global_batch so
  * the all-reduced SUM equals the single-GPU full-batch gradient.  Gradients
  * are reduced in flat buckets of about bucket_bytes on a second stream as soon
- * as backward has produced them. */
+ * as backward has produced them, and each bucket's parameters are updated on that
+ * stream right behind its reduce.  Every rank must describe the same model, bucket
+ * size and global batch: nrs_trainer_enable_dp compares a fingerprint of them across
+ * the ranks and fails with NRS_ERR_SHAPE before any gradient is exchanged.
+ * Deadlines: joining the communicator and every host-side wait of a step (a call with
+ * loss_out != NULL, nrs_trainer_last_loss) give up after the time-out (300 s unless
+ * nrs_trainer_set_dp_timeout_ms says otherwise): the communicator is aborted, the
+ * call returns NRS_ERR_TIMEOUT (or NRS_ERR_NCCL for an error NCCL reported), and the
+ * trainer refuses further data-parallel steps. */
 int nrs_dp_unique_id(void* id_out_128_bytes);
 int nrs_trainer_enable_dp(nrs_trainer* t, int rank, int world, const void* unique_id_128_bytes,
                           int global_batch, size_t bucket_bytes);
+int nrs_trainer_set_dp_timeout_ms(nrs_trainer* t, double timeout_ms);
+
+/* The same exchange for a caller's own loop over nodes (examples/cifar_cuda.rs:267-286 run on
+ * several GPUs), without the trainer:
+ *     nrs_dp_create(...);  nrs_bucket_register(dp, params, n, bucket_bytes);      once
+ *     per step: forward, cross-entropy backward, then EITHER
+ *         nrs_backward_graph_dp(logits, dp)       backward_graph that reports each parameter as soon
+ *                                                 as the last node reading it has run, and waits
+ *       OR nrs_dp_begin_step; the caller's own backward calls with nrs_grad_ready(dp, param) after
+ *         each parameter's gradient is complete; nrs_allreduce_wait(dp)
+ *     then the optimizer step (nrs_adamw_step_nodes) on the summed gradients.
+ * nrs_bucket_register moves the parameters into one flat block (as nrs_flatten_params) and plans
+ * buckets from the last parameter to the first.  A bucket is all-reduced (sum) on the group's own
+ * stream once it and every bucket before it are complete, so every rank issues the same sequence
+ * whatever order its gradients arrive in.  nrs_allreduce_wait sends what is left (a parameter that
+ * received no gradient goes out as zeros) and makes the context's stream wait for the exchange; it
+ * does not block the host.  nrs_dp_host_wait blocks the host until the context's stream is idle,
+ * under the group's deadline (see above).  Each rank's cross-entropy must divide by the GLOBAL batch
+ * (nrs_ce_fwd_bwd's divisor) for the summed gradient to be the full-batch one. */
+typedef struct nrs_dp nrs_dp;
+int nrs_dp_create(nrs_ctx* ctx, int rank, int world, const void* unique_id_128_bytes, int global_batch,
+                  double timeout_ms, nrs_dp** out);
+int nrs_dp_free(nrs_dp* dp);
+int nrs_bucket_register(nrs_dp* dp, nrs_node* const* params, int count, size_t bucket_bytes);
+int nrs_dp_bucket_count(const nrs_dp* dp);
+int nrs_dp_begin_step(nrs_dp* dp);
+int nrs_grad_ready(nrs_dp* dp, nrs_node* param);
+int nrs_allreduce_wait(nrs_dp* dp);
+int nrs_backward_graph_dp(nrs_node* root, nrs_dp* dp);
+int nrs_dp_host_wait(nrs_dp* dp);
+int nrs_dp_set_timeout_ms(nrs_dp* dp, double timeout_ms);
+/* Sum of `count` floats at values_dev over all ranks, in place, on the context's stream (the loss
+ * shares, a metric). */
+int nrs_dp_all_reduce_sum(nrs_dp* dp, float* values_dev, size_t count);
 /* Host-only helpers (usable without a GPU): sample range of a rank, and the
  * bucket boundaries (in floats, from the END of the flat gradient, the order
  * backward produces them) for given parameter lengths.  Returns the bucket
@@ -238,6 +312,19 @@ int nrs_trainer_enable_dp(nrs_trainer* t, int rank, int world, const void* uniqu
 int nrs_dp_shard_range(int global_batch, int rank, int world, int* begin_out, int* end_out);
 int nrs_dp_plan_buckets(const int64_t* param_lens, int n_params, size_t bucket_bytes,
                         int64_t* starts_out, int64_t* ends_out, int capacity);
+/* Host-only: the 64-bit fingerprint of what all ranks must agree on (parameter lengths in order,
+ * bucket size, global batch, world size), and the comparison of the ranks' fingerprints
+ * (NRS_ERR_SHAPE naming the first rank that differs from rank 0).  nrs_bucket_register and
+ * nrs_trainer_enable_dp run this check over the communicator; a launcher can run it earlier over
+ * its own channel. */
+uint64_t nrs_dp_fingerprint(const int64_t* param_lens, int n_params, size_t bucket_bytes, int global_batch, int world);
+int nrs_dp_check_fingerprints(const uint64_t* fingerprints, int world);
+/* Host-only: the deadline loop the data-parallel waits run on, over a caller's poll function
+ * (0 = still running, 1 = finished, negative = failed; called at least once, then every
+ * interval_us).  Returns NRS_OK, NRS_ERR_TIMEOUT after timeout_ms, or NRS_ERR_NCCL when poll
+ * reported a failure; waited_ms_out (optional) receives the time spent. */
+typedef int (*nrs_poll_fn)(void* user);
+int nrs_watchdog_wait(nrs_poll_fn poll, void* user, double timeout_ms, double interval_us, double* waited_ms_out);
 
 #ifdef __cplusplus
 }

@@ -35,9 +35,11 @@ class NrsError(RuntimeError):
         self.code = code
 
 
+POLL_FN = C.CFUNCTYPE(C.c_int, C.c_void_p)     # nrs_poll_fn
+
 _C_TYPES = {
-    "int": C.c_int, "float": C.c_float, "size_t": C.c_size_t, "int64_t": C.c_int64, "uint64_t": C.c_uint64,
-    "void": None,
+    "int": C.c_int, "float": C.c_float, "double": C.c_double, "size_t": C.c_size_t, "int64_t": C.c_int64,
+    "uint64_t": C.c_uint64, "nrs_poll_fn": POLL_FN, "void": None,
 }
 
 

@@ -261,11 +261,8 @@ int nrs_attention_bwd(nrs_ctx* ctx, const float* q, const float* k, const float*
               "nrs_attention_bwd: seq %d / d_head %d outside the fused kernel's range (%d / %d)", seq, d_head, kMaxSeq, kMaxDh);
   if (batch == 0) return NRS_OK;
   NRS_REQUIRE(ctx, q && k && v && probs && dout && dq && dk && dv, NRS_ERR_ARG, "nrs_attention_bwd: null tensor");
-  static bool attr_set = false;
-  if (!attr_set) {
-    NRS_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwdSmem));
-    attr_set = true;
-  }
+  static NrsSmemAttr attr;
+  NRS_ENSURE_SMEM(ctx, attr, attn_bwd_kernel, kBwdSmem);
   NRS_PDL_LAUNCH(attn_bwd_kernel, (unsigned)(batch * heads), 256, kBwdSmem, ctx->stream, q, k, v, probs, dout, dq, dk, dv, seq, heads, d_head,
                                                                                1.0f / sqrtf((float)d_head), acc_q, acc_k, acc_v);
   NRS_LAUNCHED(ctx);

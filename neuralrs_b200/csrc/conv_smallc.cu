@@ -247,11 +247,8 @@ int run_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float*
   constexpr int K4 = (CI * KS * KS + 3) / 4 * 4;
   size_t smem = (((size_t)co * K4 + co + 3) / 4 * 4) * sizeof(float);
   if (EMIT) smem += (size_t)8 * 32 * kTileLd * sizeof(float);
-  static size_t attr = 0;
-  if (smem > 48 * 1024 && smem > attr) {
-    NRS_CUDA(ctx, cudaFuncSetAttribute(smallc_fwd_kernel<CI, KS, EMIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = smem;
-  }
+  static NrsSmemAttr attr;
+  NRS_ENSURE_SMEM(ctx, attr, (smallc_fwd_kernel<CI, KS, EMIT>), smem);
   const size_t total = (size_t)n * oh * ow;
   size_t blocks = (total + 255) / 256;
   const size_t cap = (size_t)ctx->sm_count * 8;
@@ -271,11 +268,8 @@ int run_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, i
   if (ns > 8) ns = 8;
   const size_t smem = ((size_t)co + K) * (TP + 1) * sizeof(float);
   if (smem > 200 * 1024) return NRS_ERR_UNSUPPORTED;
-  static size_t attr = 0;
-  if (smem > 48 * 1024 && smem > attr) {
-    NRS_CUDA(ctx, cudaFuncSetAttribute(smallc_wgrad_kernel<CI, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = smem;
-  }
+  static NrsSmemAttr attr;
+  NRS_ENSURE_SMEM(ctx, attr, (smallc_wgrad_kernel<CI, KS>), smem);
   const int plane = oh * ow;
   const int tiles_per_img = (plane + TP - 1) / TP;
   const long total_tiles = (long)tiles_per_img * n;

@@ -76,6 +76,8 @@ int nrs_check_device_error(nrs_ctx* ctx) {
   NRS_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   if (code == 0) return NRS_OK;
   NRS_CUDA(ctx, cudaMemsetAsync(ctx->err_flag, 0, sizeof(int), ctx->stream));
+  if (code == 5)
+    return nrs_fail(ctx, NRS_ERR_ARG, "an embedding lookup met a token index outside the vocabulary; that row was read as zeros");
   static const char* what[] = {"", "TMA producer waiting for a free ring slot", "UMMA issuer waiting for a filled ring slot",
                                "epilogue waiting for the accumulator", "draining outstanding TMA loads"};
   return nrs_fail(ctx, NRS_ERR_TIMEOUT, "a tensor-core kernel gave up a bounded wait (%s); its output is invalid",
@@ -109,6 +111,21 @@ NrsProfScope::~NrsProfScope() {
 }
 
 extern "C" {
+
+int nrs_selftest_smem_attr_bookkeeping(void) {
+  NrsSmemAttr a;
+  int bad = 0;
+  bad += nrs_smem_attr_update(a, 0, 40 * 1024) ? 1 : 0;      // fits the default: never requested
+  bad += nrs_smem_attr_update(a, 0, 100 * 1024) ? 0 : 1;     // first request on device 0
+  bad += nrs_smem_attr_update(a, 0, 100 * 1024) ? 1 : 0;     // already set there
+  bad += nrs_smem_attr_update(a, 0, 90 * 1024) ? 1 : 0;      // smaller than what is set
+  bad += nrs_smem_attr_update(a, 1, 100 * 1024) ? 0 : 1;     // another device starts from nothing
+  bad += nrs_smem_attr_update(a, 0, 200 * 1024) ? 0 : 1;     // growth
+  bad += nrs_smem_attr_update(a, 1, 100 * 1024) ? 1 : 0;
+  bad += nrs_smem_attr_update(a, kNrsMaxDevices, 100 * 1024) ? 0 : 1;   // untracked ordinals always request
+  bad += nrs_smem_attr_update(a, kNrsMaxDevices, 100 * 1024) ? 0 : 1;
+  return bad;
+}
 
 int nrs_profile_enable(nrs_ctx* ctx, int on) {
   NRS_REQUIRE_CTX(ctx);

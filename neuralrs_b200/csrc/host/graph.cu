@@ -57,6 +57,25 @@ FlatStore::~FlatStore() {
   if (grad) nrs_free(ctx, grad);
 }
 
+// Operand planes and patch planes are functions of the tensor's contents: whoever rewrites `data`
+// in place drops them (and the context's hints), so the next convolution stages fresh ones.
+void invalidate_operand_caches(Node* n) {
+  nrs_ctx* ctx = n->ctx;
+  if (!ctx) return;
+  if (n->planes_hi) {
+    ctx->plane_hints.erase(n->data);
+    nrs_free(ctx, n->planes_hi);
+    if (n->planes_lo) nrs_free(ctx, n->planes_lo);
+    n->planes_hi = n->planes_lo = nullptr;
+  }
+  if (n->patches_hi) {
+    ctx->patch_hints.erase(n->data);
+    nrs_free(ctx, n->patches_hi);
+    if (n->patches_lo) nrs_free(ctx, n->patches_lo);
+    n->patches_hi = n->patches_lo = nullptr;
+  }
+}
+
 NodeP node_new(nrs_ctx* ctx, const float* host, const std::vector<size_t>& shape) {
   if (!ctx) fail(NRS_ERR_ARG, "Node::new: null context");
   auto n = std::make_shared<Node>();
@@ -156,6 +175,7 @@ void to_cuda(const NodeP& n) {
   if (!n) fail(NRS_ERR_ARG, "to_cuda: null node");
   if (n->host.size() != n->len()) fail(NRS_ERR_SHAPE, "to_cuda: host data does not match the shape");
   if (!n->data) n->data = dalloc(n->ctx, n->len());
+  invalidate_operand_caches(n.get());   // planes staged from the previous contents are stale
   check(n->ctx, nrs_h2d(n->ctx, n->data, n->host.data(), n->len() * sizeof(float)));
   // The copy is asynchronous and n->host stays alive with the node.
   Node* r = grad_root(n.get());
@@ -508,8 +528,20 @@ static void conv_backward(Node* self, const NodeP& x, const NodeP& w, const Node
       const int cap = (int)(4 * (pixels / 64 + 2));
       ctx->colsum_requests[t.ptr] = NrsColsumRequest{dalloc(ctx, (size_t)cap * ci), cap, 0};
     }
-    check(ctx, nrs_conv2d_bwd(ctx, x->data, w->data, dy, t.ptr, nullptr, nullptr, n, ci, h, wd, co, kh, kw, stride,
-                              pad, t.accumulate));
+    try {
+      check(ctx, nrs_conv2d_bwd(ctx, x->data, w->data, dy, t.ptr, nullptr, nullptr, n, ci, h, wd, co, kh, kw, stride,
+                                pad, t.accumulate));
+    } catch (...) {
+      // the requests are keyed by a pool address that will be handed out again: never leave them behind
+      if (fold) {
+        auto it = ctx->colsum_requests.find(t.ptr);
+        if (it != ctx->colsum_requests.end()) { nrs_free(ctx, it->second.partial); ctx->colsum_requests.erase(it); }
+        ctx->out_extras.erase(t.ptr);
+        if (ghi) nrs_free(ctx, ghi);
+        if (glo) nrs_free(ctx, glo);
+      }
+      throw;
+    }
     if (fold) {
       NrsColsumRequest sums = ctx->colsum_requests[t.ptr];
       ctx->colsum_requests.erase(t.ptr);
@@ -591,8 +623,17 @@ NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, 
     if (ctx->math_mode == NRS_MATH_3XTF32) olo = dalloc(ctx, out->len());
     ctx->out_extras[out->data] = NrsOutExtras{nullptr, ohi, olo};
   }
-  check(ctx, nrs_conv2d_fwd(ctx, x->data, w->data, b->data, out->data, n, ci, h, wd, co, kh, kw, (int)stride,
-                            (int)pad, act));
+  try {
+    check(ctx, nrs_conv2d_fwd(ctx, x->data, w->data, b->data, out->data, n, ci, h, wd, co, kh, kw, (int)stride,
+                              (int)pad, act));
+  } catch (...) {
+    if (ohi) {
+      ctx->out_extras.erase(out->data);
+      nrs_free(ctx, ohi);
+      if (olo) nrs_free(ctx, olo);
+    }
+    throw;
+  }
   if (ohi) {
     if (ctx->out_extras.erase(out->data)) {   // not honoured
       nrs_free(ctx, ohi);
@@ -643,11 +684,19 @@ NodeP conv2d_act(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, 
       // dy feeds both the data and the weight gradient: stage its planes once.
       staged = stage_planes(ctx, dy, self->shape, &dhi, &dlo);
     }
-    conv_backward(self, x, w, b, dy, n, ci, h, wd, co, kh, kw, s, p);
-    if (staged) ctx->plane_hints.erase(dy);
-    if (dhi) nrs_free(ctx, dhi);
-    if (dlo) nrs_free(ctx, dlo);
-    if (masked) nrs_free(ctx, masked);
+    auto cleanup = [&] {
+      if (staged) ctx->plane_hints.erase(dy);
+      if (dhi) nrs_free(ctx, dhi);
+      if (dlo) nrs_free(ctx, dlo);
+      if (masked) nrs_free(ctx, masked);
+    };
+    try {
+      conv_backward(self, x, w, b, dy, n, ci, h, wd, co, kh, kw, s, p);
+    } catch (...) {
+      cleanup();
+      throw;
+    }
+    cleanup();
   };
   return out;
 }
@@ -1093,6 +1142,30 @@ void AdamW::step(const std::vector<NodeP>& params) {
                                  beta1, beta2, epsilon, weight_decay, bc1, bc2, grad_scale));
     }
   }
+  t += 1;
+}
+
+void AdamW::begin_flat_step(const std::vector<NodeP>& params) {
+  for (const auto& p : params) require_gpu(p, "adamw: param");
+  ensure_state(params);
+  auto fs = flat_m_ ? common_flat(params) : nullptr;
+  if (!fs || fs->total != flat_total_) fail(NRS_ERR_ARG, "adamw: a flat step needs parameters that share one flat block");
+  stepping_ = fs;
+}
+
+void AdamW::step_flat_range(size_t begin, size_t end) {
+  if (!stepping_) fail(NRS_ERR_ARG, "adamw: step_flat_range outside begin_flat_step / end_flat_step");
+  if (begin > end || end > flat_total_) fail(NRS_ERR_ARG, "adamw: range outside the flat block");
+  if (begin == end) return;
+  const float bc1 = 1.0f - powi_f32(beta1, (int)t + 1);
+  const float bc2 = 1.0f - powi_f32(beta2, (int)t + 1);
+  check(ctx_, nrs_adamw_step(ctx_, stepping_->data + begin, stepping_->grad + begin, flat_m_ + begin, flat_v_ + begin,
+                             end - begin, lr, beta1, beta2, epsilon, weight_decay, bc1, bc2, grad_scale));
+}
+
+void AdamW::end_flat_step() {
+  if (!stepping_) fail(NRS_ERR_ARG, "adamw: end_flat_step without begin_flat_step");
+  stepping_.reset();
   t += 1;
 }
 

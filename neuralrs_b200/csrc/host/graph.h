@@ -87,6 +87,8 @@ struct FlatStore {
 };
 
 NodeP node_new(nrs_ctx* ctx, const float* host, const std::vector<size_t>& shape);
+// Drops the operand planes cached for a node's data (call after writing `data` in place).
+void invalidate_operand_caches(Node* n);
 
 // Building blocks for operators defined outside graph.cu.
 struct GradSlot {
@@ -170,6 +172,10 @@ struct Embedding {                    // embedding.rs:41-100
   // which the reference has on the CPU only: src/nn/embedding.rs:60-113).
   NodeP forward(const int32_t* indices, size_t count) const;
   NodeP forward_batch(const int32_t* indices, size_t batch, size_t seq) const;
+  // The batched form on token ids already resident on the device (the caller keeps `idx_dev` alive
+  // until the backward pass has run), optionally with PositionalEncoding::forward folded into the
+  // gather (pos_table = PositionalEncoding::table).  Ids are range-checked by the kernel.
+  NodeP forward_resident(const int32_t* idx_dev, size_t batch, size_t seq, const NodeP& pos_table = nullptr) const;
 };
 struct PositionalEncoding {           // positional.rs:18-44; the table is computed once and kept resident
   size_t d_model = 0, max_len = 0;
@@ -190,6 +196,7 @@ struct TransformerBlock {             // transformer_block.rs:28-60: post-LN, Re
   Linear ff1, ff2;
   size_t d_model = 0, d_ff = 0;
   int act = NRS_ACT_RELU;             // NRS_ACT_GELU is an extension for the LM benchmark configuration
+  bool fused_epilogues = false;       // feed-forward bias (+ activation) in the GEMM epilogue instead of separate passes
   NodeP forward(const NodeP& x) const;
   NodeP forward_no_final_norm(const NodeP& x) const;
 };
@@ -209,6 +216,14 @@ struct AdamW {
   AdamW(nrs_ctx* ctx, float lr, float b1, float b2, float eps, float wd);
   ~AdamW();
   void step(const std::vector<NodeP>& params);
+  // The same update in pieces, for parameters that share one FlatStore: begin_flat_step readies the
+  // moments, step_flat_range updates floats [begin, end) of the flat block with the current step's
+  // bias corrections (every float exactly once per step, in any order, on the context's current
+  // stream), end_flat_step advances t.  The data-parallel trainer updates each gradient bucket as
+  // soon as its all-reduce has landed.
+  void begin_flat_step(const std::vector<NodeP>& params);
+  void step_flat_range(size_t begin, size_t end);
+  void end_flat_step();
   // (t, all first moments in parameter order, then all second moments).
   std::vector<std::vector<float>> export_state(size_t* t_out) const;
   void import_state(size_t t, const std::vector<std::vector<float>>& moments);
@@ -221,6 +236,7 @@ struct AdamW {
   float* flat_v_ = nullptr;
   size_t flat_total_ = 0;
   bool owns_each_ = false;
+  std::shared_ptr<FlatStore> stepping_;   // set between begin_flat_step and end_flat_step
   void ensure_state(const std::vector<NodeP>& params);
   void release();
 };

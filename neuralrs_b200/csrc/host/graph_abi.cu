@@ -4,12 +4,10 @@
 #include <cstring>
 
 #include "host/graph.h"
+#include "host/abi_types.h"
 #include "nrs_graph.h"
 #include "nrs_internal.h"
 
-struct nrs_node {
-  nrs::NodeP p;
-};
 struct nrs_adamw {
   nrs_ctx* ctx;
   std::unique_ptr<nrs::cuda::AdamW> opt;
@@ -94,7 +92,27 @@ int nrs_node_set_requires_grad(nrs_node* n, int flag) {
   return NRS_OK;
 }
 
+int nrs_node_set_data(nrs_node* n, const float* host_data) {
+  NODE_OK(n);
+  if (!host_data && n->p->len()) return nrs_fail(ctx_of(n), NRS_ERR_ARG, "nrs_node_set_data: null data");
+  return guarded(ctx_of(n), [&] {
+    // a copy still in flight from an earlier to_cuda reads the old host vector
+    if (n->p->on_gpu()) nrs::cuda::synchronize(n->p->ctx);
+    n->p->host.assign(host_data, host_data + n->p->len());
+  });
+}
+
 float* nrs_node_data_ptr(nrs_node* n) { return n && n->p ? n->p->data : nullptr; }
+
+int nrs_node_invalidate(nrs_node* n) {
+  NODE_OK(n);
+  return guarded(ctx_of(n), [&] {
+    nrs::Node* r = n->p.get();
+    while (r->view_of) r = r->view_of.get();
+    nrs::invalidate_operand_caches(r);
+    if (r != n->p.get()) nrs::invalidate_operand_caches(n->p.get());
+  });
+}
 
 float* nrs_node_grad_ptr(nrs_node* n) {
   if (!n || !n->p) return nullptr;

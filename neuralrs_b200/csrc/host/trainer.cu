@@ -8,14 +8,13 @@
 // ncclAllReduce per bucket, issued on a second stream as soon as backward has
 // produced the bucket, overlapping the rest of backward.
 //
-// NCCL is loaded with dlopen on first use: single-GPU users need no NCCL.
-#include <dlfcn.h>
-
+// The gradient exchange itself lives in dp.cu (DpGroup).
 #include <algorithm>
 #include <cstring>
 #include <unordered_set>
 
 #include "host/graph.h"
+#include "host/dp.h"
 #include "host/checkpoint.h"
 #include "nrs_checkpoint.h"
 #include <map>
@@ -23,75 +22,7 @@
 #include "nrs_graph.h"
 #include "nrs_internal.h"
 
-namespace {
-
 using nrs::NodeP;
-
-// ------------------------------------------------------------------- NCCL
-struct NcclId { char internal[128]; };
-typedef void* ncclComm_p;
-struct NcclApi {
-  void* handle = nullptr;
-  int (*GetUniqueId)(NcclId*) = nullptr;
-  int (*CommInitRank)(ncclComm_p*, int, NcclId, int) = nullptr;
-  int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_p, cudaStream_t) = nullptr;
-  int (*CommDestroy)(ncclComm_p) = nullptr;
-  const char* (*GetErrorString)(int) = nullptr;
-  std::string error;
-};
-constexpr int kNcclFloat32 = 7, kNcclSum = 0;
-
-NcclApi* nccl_api() {
-  static NcclApi api;
-  static bool tried = false;
-  if (tried) return api.handle ? &api : nullptr;
-  tried = true;
-  const char* names[] = {"libnccl.so.2", "libnccl.so"};
-  for (const char* n : names) {
-    api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
-    if (api.handle) break;
-  }
-  if (!api.handle) {
-    api.error = std::string("cannot load libnccl.so.2: ") + (dlerror() ? dlerror() : "unknown");
-    return nullptr;
-  }
-  auto sym = [&](const char* s) { return dlsym(api.handle, s); };
-  api.GetUniqueId = (int (*)(NcclId*))sym("ncclGetUniqueId");
-  api.CommInitRank = (int (*)(ncclComm_p*, int, NcclId, int))sym("ncclCommInitRank");
-  api.AllReduce = (int (*)(const void*, void*, size_t, int, int, ncclComm_p, cudaStream_t))sym("ncclAllReduce");
-  api.CommDestroy = (int (*)(ncclComm_p))sym("ncclCommDestroy");
-  api.GetErrorString = (const char* (*)(int))sym("ncclGetErrorString");
-  if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy || !api.GetErrorString) {
-    api.error = "libnccl.so.2 lacks a required symbol";
-    dlclose(api.handle);
-    api.handle = nullptr;
-    return nullptr;
-  }
-  return &api;
-}
-
-// Buckets over the flat gradient, walking parameters from the LAST to the first
-// (the order backward finishes them); a bucket closes once it holds at least
-// bucket_bytes.  `offsets` are the parameters' (padded) starts, `total` the end.
-struct Bucket { size_t begin, end; int first_param, last_param; };
-std::vector<Bucket> plan_buckets(const std::vector<size_t>& offsets, size_t total, size_t bucket_bytes) {
-  std::vector<Bucket> out;
-  const int n = (int)offsets.size();
-  if (n == 0) return out;
-  const size_t want = std::max<size_t>(1, bucket_bytes / sizeof(float));
-  size_t end = total;
-  int last = n - 1;
-  for (int i = n - 1; i >= 0; --i) {
-    if (end - offsets[i] >= want || i == 0) {
-      out.push_back({offsets[i], end, i, last});
-      end = offsets[i];
-      last = i - 1;
-    }
-  }
-  return out;
-}
-
-}  // namespace
 
 struct nrs_trainer {
   nrs_ctx* ctx = nullptr;
@@ -127,17 +58,18 @@ struct nrs_trainer {
   // On-device augmentation of staged batches (nrs_trainer_set_augment): off when max_shift < 0.
   int aug_shift = -1, aug_flip = 0;
   float* aug_buf = nullptr; size_t aug_cap = 0;
+  // Token models (first layer NRS_LAYER_EMBEDDING): the input is int32 ids [batch, seq] and the loss runs
+  // over batch * seq rows.
+  bool token_input = false;
+  size_t rows_per_sample = 1;
+  NodeP pos_table;                      // sinusoidal table of the embedding layer (no gradient)
+  float* onehot_dev = nullptr; size_t onehot_cap = 0;   // one-hot rows expanded from int32 labels
   // data parallel
   int rank = 0, world = 1, global_batch = 0;
-  ncclComm_p comm = nullptr;
-  cudaStream_t comm_stream = nullptr;
-  cudaEvent_t ready_ev = nullptr, done_ev = nullptr;
-  std::vector<Bucket> buckets;
+  double dp_timeout_ms = 300000.0;      // joining the communicator, and every host wait of a step
+  std::unique_ptr<nrs::DpGroup> dp;
   ~nrs_trainer() {
-    if (comm) { if (NcclApi* a = nccl_api()) a->CommDestroy(comm); }
-    if (comm_stream) cudaStreamDestroy(comm_stream);
-    if (ready_ev) cudaEventDestroy(ready_ev);
-    if (done_ev) cudaEventDestroy(done_ev);
+    dp.reset();
     if (copy_stream) { cudaStreamSynchronize(copy_stream); cudaStreamDestroy(copy_stream); }
     for (Slot& sl : slots) {
       if (sl.filled) cudaEventDestroy(sl.filled);
@@ -150,8 +82,10 @@ struct nrs_trainer {
     opt.reset();
     params.clear();
     buffers.clear();
+    pos_table.reset();
     flat.reset();
     if (ctx) {
+      if (onehot_dev) nrs_free(ctx, onehot_dev);
       if (loss_dev) nrs_free(ctx, loss_dev);
       if (x_dev) nrs_free(ctx, x_dev);
       if (t_dev) nrs_free(ctx, t_dev);
@@ -191,10 +125,43 @@ void validate_and_build_params(nrs_trainer* t) {
         break;
       }
       case NRS_LAYER_LINEAR:
-        if (shp.size() != 1 || (int)shp[0] != l.a || l.b <= 0) fail(NRS_ERR_SHAPE, "trainer: linear layer input size mismatch");
+        // [F] per sample, or [seq, F] per sample of a token model (applied to every position)
+        if ((shp.size() != 1 && shp.size() != 2) || (int)shp.back() != l.a || l.b <= 0)
+          fail(NRS_ERR_SHAPE, "trainer: linear layer input size mismatch");
         t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.a, (size_t)l.b}));
         t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.b}));
-        shp = {(size_t)l.b};
+        shp.back() = (size_t)l.b;
+        break;
+      case NRS_LAYER_EMBEDDING: {
+        if (li != 0) fail(NRS_ERR_ARG, "trainer: an embedding layer must come first (it reads the token ids)");
+        if (shp.size() != 1) fail(NRS_ERR_SHAPE, "trainer: a token model's input shape is {seq}");
+        if (l.a <= 0 || l.b <= 0 || l.c < 0) fail(NRS_ERR_SHAPE, "trainer: bad embedding hyper-parameters");
+        if (l.c > 0 && (size_t)l.c < shp[0]) fail(NRS_ERR_SHAPE, "sequence longer than max_len");
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.a, (size_t)l.b}));
+        if (l.c > 0) t->pos_table = nrs::cuda::PositionalEncoding::make(t->ctx, (size_t)l.b, (size_t)l.c).table;
+        t->token_input = true;
+        t->rows_per_sample = shp[0];
+        shp = {shp[0], (size_t)l.b};
+        break;
+      }
+      case NRS_LAYER_TRANSFORMER_BLOCK: {
+        if (shp.size() != 2 || (int)shp[1] != l.a) fail(NRS_ERR_SHAPE, "trainer: transformer block needs a [seq, d_model] input");
+        if (l.b <= 0 || l.a % l.b != 0 || l.c <= 0) fail(NRS_ERR_SHAPE, "trainer: d_model must be divisible by num_heads");
+        if (l.d != NRS_ACT_RELU && l.d != NRS_ACT_GELU) fail(NRS_ERR_ARG, "trainer: transformer block activation must be ReLU or GELU");
+        const size_t d = (size_t)l.a, ff = (size_t)l.c;
+        // parameters() order of src/nn/transformer_block.rs:58-66
+        for (int k = 0; k < 4; ++k) t->params.push_back(nrs::node_new(t->ctx, nullptr, {d, d}));          // w_q w_k w_v w_o
+        for (int k = 0; k < 4; ++k) t->params.push_back(nrs::node_new(t->ctx, nullptr, {d}));             // norm1/2 gamma, beta
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {d, ff}));
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {ff}));
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {ff, d}));
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {d}));
+        break;
+      }
+      case NRS_LAYER_LAYERNORM:
+        if (shp.empty() || (int)shp.back() != l.a) fail(NRS_ERR_SHAPE, "trainer: layernorm feature count mismatch");
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.a}));
+        t->params.push_back(nrs::node_new(t->ctx, nullptr, {(size_t)l.a}));
         break;
       case NRS_LAYER_RELU:
       case NRS_LAYER_GELU:
@@ -222,7 +189,8 @@ void validate_and_build_params(nrs_trainer* t) {
         fail(NRS_ERR_ARG, "trainer: unknown layer kind");
     }
   }
-  if (shp.size() != 1 || (int)shp[0] != t->classes) fail(NRS_ERR_SHAPE, "trainer: model output does not match `classes`");
+  if (t->token_input ? (shp.size() != 2 || (int)shp[1] != t->classes) : (shp.size() != 1 || (int)shp[0] != t->classes))
+    fail(NRS_ERR_SHAPE, "trainer: model output does not match `classes`");
   if (t->params.empty()) fail(NRS_ERR_ARG, "trainer: model has no parameters");
   for (auto& p : t->params) {
     p->host.assign(p->len(), 0.0f);
@@ -233,7 +201,22 @@ void validate_and_build_params(nrs_trainer* t) {
   t->flat = nrs::cuda::flatten_params(t->params);
 }
 
-NodeP forward(nrs_trainer* t, const NodeP& x) {
+// x@W + b (+ activation) on the last axis of h: [rows, F], or every position of [batch, seq, F].
+NodeP linear_layer(nrs_trainer* t, const NodeP& h, const NodeP& w, const NodeP& b, int act) {
+  const bool tokens = h->shape.size() == 3;
+  NodeP in = tokens ? nrs::cuda::reshape(h, {h->shape[0] * h->shape[1], h->shape[2]}) : h;
+  NodeP out;
+  if (t->fuse) {
+    out = nrs::cuda::linear_act(in, w, b, act);
+  } else {
+    out = nrs::cuda::add(nrs::cuda::matmul(in, w), b);
+    if (act == NRS_ACT_RELU) out = nrs::cuda::relu(out);
+    else if (act == NRS_ACT_GELU) out = nrs::cuda::gelu(out);
+  }
+  return tokens ? nrs::cuda::reshape(out, {h->shape[0], h->shape[1], out->shape[1]}) : out;
+}
+
+NodeP forward(nrs_trainer* t, const NodeP& x, const int32_t* ids_dev, size_t batch) {
   NodeP h = x;
   size_t pi = 0, bi = 0;
   for (size_t li = 0; li < t->layers.size(); ++li) {
@@ -251,15 +234,36 @@ NodeP forward(nrs_trainer* t, const NodeP& x) {
         if (relu_next) ++li;
         break;
       }
-      case NRS_LAYER_LINEAR:
-        if (t->fuse) {
-          const bool gelu_next = li + 1 < t->layers.size() && t->layers[li + 1].kind == NRS_LAYER_GELU;
-          h = nrs::cuda::linear_act(h, t->params[pi], t->params[pi + 1],
-                                    relu_next ? NRS_ACT_RELU : gelu_next ? NRS_ACT_GELU : NRS_ACT_NONE);
-          if (relu_next || gelu_next) ++li;
-        } else {
-          h = nrs::cuda::add(nrs::cuda::matmul(h, t->params[pi]), t->params[pi + 1]);
-        }
+      case NRS_LAYER_LINEAR: {
+        const bool gelu_next = t->fuse && li + 1 < t->layers.size() && t->layers[li + 1].kind == NRS_LAYER_GELU;
+        h = linear_layer(t, h, t->params[pi], t->params[pi + 1], relu_next ? NRS_ACT_RELU : gelu_next ? NRS_ACT_GELU : NRS_ACT_NONE);
+        if (relu_next || gelu_next) ++li;
+        pi += 2;
+        break;
+      }
+      case NRS_LAYER_EMBEDDING: {
+        nrs::cuda::Embedding e;
+        e.weight = t->params[pi];
+        e.vocab_size = (size_t)l.a;
+        e.embedding_dim = (size_t)l.b;
+        h = e.forward_resident(ids_dev, batch, t->in_shape[0], t->pos_table);
+        pi += 1;
+        break;
+      }
+      case NRS_LAYER_TRANSFORMER_BLOCK: {
+        nrs::cuda::TransformerBlock b;
+        const NodeP* p = &t->params[pi];
+        b.mha.w_q = p[0]; b.mha.w_k = p[1]; b.mha.w_v = p[2]; b.mha.w_o = p[3];
+        b.mha.d_model = (size_t)l.a; b.mha.num_heads = (size_t)l.b; b.mha.causal = (l.e & 1) != 0;
+        b.norm1.gamma = p[4]; b.norm1.beta = p[5]; b.norm2.gamma = p[6]; b.norm2.beta = p[7];
+        b.ff1.weights = p[8]; b.ff1.bias = p[9]; b.ff2.weights = p[10]; b.ff2.bias = p[11];
+        b.d_model = (size_t)l.a; b.d_ff = (size_t)l.c; b.act = l.d; b.fused_epilogues = t->fuse;
+        h = (l.e & 2) ? b.forward_no_final_norm(h) : b.forward(h);
+        pi += 12;
+        break;
+      }
+      case NRS_LAYER_LAYERNORM:
+        h = nrs::cuda::layernorm(h, t->params[pi], t->params[pi + 1], 1e-5f);
         pi += 2;
         break;
       case NRS_LAYER_RELU: h = nrs::cuda::relu(h); break;
@@ -285,40 +289,23 @@ NodeP forward(nrs_trainer* t, const NodeP& x) {
   return h;
 }
 
-void topo_order(const NodeP& root, std::vector<NodeP>& topo) {
-  std::unordered_set<const nrs::Node*> seen;
-  struct Frame { NodeP node; size_t next; };
-  std::vector<Frame> stack;
-  seen.insert(root.get());
-  stack.push_back({root, 0});
-  while (!stack.empty()) {
-    Frame& f = stack.back();
-    if (f.next < f.node->parents.size()) {
-      NodeP p = f.node->parents[f.next++];
-      if (seen.insert(p.get()).second) stack.push_back({p, 0});
-    } else {
-      topo.push_back(f.node);
-      stack.pop_back();
-    }
-  }
-}
+// One step's inputs, all on the device: x (float samples) or ids (token models); targets as one-hot rows
+// or as int32 class indices (one per loss row).
+struct StepInput {
+  const float* x = nullptr;
+  const int32_t* ids = nullptr;
+  const float* target = nullptr;
+  const int32_t* labels = nullptr;
+  int batch = 0;
+};
 
-// Enqueue the all-reduce of one bucket on the comm stream, after everything the
-// compute stream has enqueued so far.
-void launch_bucket(nrs_trainer* t, const Bucket& b) {
-  NcclApi* api = nccl_api();
+void run_step(nrs_trainer* t, const StepInput& in, bool optimize) {
   nrs_ctx* ctx = t->ctx;
-  if (cudaEventRecord(t->ready_ev, ctx->stream) != cudaSuccess ||
-      cudaStreamWaitEvent(t->comm_stream, t->ready_ev, 0) != cudaSuccess)
-    fail(NRS_ERR_CUDA, "trainer: event hand-off to the comm stream failed");
-  float* g = t->flat->grad + b.begin;
-  const int rc = api->AllReduce(g, g, b.end - b.begin, kNcclFloat32, kNcclSum, t->comm, t->comm_stream);
-  if (rc != 0) fail(NRS_ERR_NCCL, std::string("ncclAllReduce: ") + api->GetErrorString(rc));
-}
-
-void run_step(nrs_trainer* t, const float* x_dev, const float* t_dev, int batch, bool optimize) {
-  nrs_ctx* ctx = t->ctx;
+  const int batch = in.batch;
   if (batch <= 0) fail(NRS_ERR_SHAPE, "trainer: batch must be positive");
+  if (t->token_input ? !in.ids : !in.x) fail(NRS_ERR_ARG, t->token_input ? "trainer: this model reads token ids" : "trainer: this model reads float samples");
+  const size_t rows = (size_t)batch * t->rows_per_sample;
+  if (rows > 2147483647u) fail(NRS_ERR_UNSUPPORTED, "trainer: more than 2^31-1 loss rows");
   // Input nodes wrap the caller's device buffers (not owned).
   auto wrap = [&](const float* dev, std::vector<size_t> shape) {
     auto n = std::make_shared<nrs::Node>();
@@ -329,48 +316,51 @@ void run_step(nrs_trainer* t, const float* x_dev, const float* t_dev, int batch,
     n->requires_grad = false;  // examples/cifar_cuda.rs:270: skips the first conv's data gradient
     return n;
   };
-  std::vector<size_t> xs{(size_t)batch};
-  xs.insert(xs.end(), t->in_shape.begin(), t->in_shape.end());
-  NodeP x = wrap(x_dev, xs);
-  NodeP target = wrap(t_dev, {(size_t)batch, (size_t)t->classes});
+  const float* target_dev = in.target;
+  if (!target_dev) {
+    if (!in.labels) fail(NRS_ERR_ARG, "trainer: no targets");
+    const size_t floats = rows * (size_t)t->classes;   // class indices -> the one-hot rows cross_entropy takes
+    if (floats > t->onehot_cap) {
+      if (t->onehot_dev) nrs_free(ctx, t->onehot_dev);
+      t->onehot_dev = nullptr;
+      t->onehot_cap = 0;
+      void* p = nullptr;
+      nrs::check(ctx, nrs_alloc(ctx, floats * sizeof(float), 0, &p));
+      t->onehot_dev = (float*)p;
+      t->onehot_cap = floats;
+    }
+    nrs::check(ctx, nrs_onehot(ctx, in.labels, t->onehot_dev, (int)rows, t->classes));
+    target_dev = t->onehot_dev;
+  }
+  NodeP x;
+  if (!t->token_input) {
+    std::vector<size_t> xs{(size_t)batch};
+    xs.insert(xs.end(), t->in_shape.begin(), t->in_shape.end());
+    x = wrap(in.x, xs);
+  }
+  NodeP target = wrap(target_dev, {rows, (size_t)t->classes});
 
   nrs::cuda::zero_grad(t->params);
-  NodeP logits = forward(t, x);
-  const int divisor = t->world > 1 ? t->global_batch : batch;
-  nrs::cuda::cross_entropy_fused(logits, target, t->loss_dev, divisor);
+  NodeP logits = forward(t, x, in.ids, (size_t)batch);
+  if (logits->shape.size() == 3) logits = nrs::cuda::reshape(logits, {rows, (size_t)t->classes});
+  const bool dp = t->dp && t->world > 1 && optimize;
+  const size_t divisor = (t->world > 1 ? (size_t)t->global_batch : (size_t)batch) * t->rows_per_sample;
+  if (divisor > 2147483647u) fail(NRS_ERR_UNSUPPORTED, "trainer: more than 2^31-1 loss rows");
+  nrs::cuda::cross_entropy_fused(logits, target, t->loss_dev, (int)divisor);
 
-  std::vector<NodeP> topo;
-  topo_order(logits, topo);
-  const bool dp = t->world > 1 && optimize;
-  size_t next_bucket = 0;
-  for (auto it = topo.rbegin(); it != topo.rend(); ++it) {
-    if ((*it)->backward_fn) (*it)->backward_fn();
-    if (dp) {
-      // A bucket is ready once every parameter in it has received its gradient
-      // (each parameter has exactly one producer in a sequential model).
-      while (next_bucket < t->buckets.size()) {
-        const Bucket& b = t->buckets[next_bucket];
-        bool ready = true;
-        for (int p = b.first_param; p <= b.last_param; ++p) ready = ready && t->params[p]->grad_valid;
-        if (!ready) break;
-        launch_bucket(t, b);
-        ++next_bucket;
-      }
-    }
-  }
   if (dp) {
-    // Parameters that received no gradient still have to be exchanged as zeros.
-    for (auto& p : t->params)
-      if (!p->grad_valid) {
-        nrs::check(ctx, nrs_memset_zero(ctx, p->grad, p->len() * sizeof(float)));
-        p->grad_valid = true;
-      }
-    for (; next_bucket < t->buckets.size(); ++next_bucket) launch_bucket(t, t->buckets[next_bucket]);
-    if (cudaEventRecord(t->done_ev, t->comm_stream) != cudaSuccess ||
-        cudaStreamWaitEvent(ctx->stream, t->done_ev, 0) != cudaSuccess)
-      fail(NRS_ERR_CUDA, "trainer: event hand-off from the comm stream failed");
+    // Each bucket is all-reduced on the comm stream as soon as backward has produced it, and its
+    // parameters are updated there right behind the reduce (DpGroup::after_bucket), so both overlap
+    // the rest of backward; the compute stream joins at the end.
+    t->opt->begin_flat_step(t->params);
+    t->dp->begin_step();
+    nrs::backward_graph_dp(logits, t->dp.get());
+    t->dp->finish();
+    t->opt->end_flat_step();
+  } else {
+    nrs::backward_graph(logits);
+    if (optimize) t->opt->step(t->params);
   }
-  if (optimize) t->opt->step(t->params);
 }
 
 void stage(nrs_trainer* t, float** buf, size_t* cap, const float* host, size_t floats) {
@@ -405,7 +395,22 @@ void grow_slot_block(float** buf, size_t* cap, size_t floats) {
   *cap = floats;
 }
 
-void stage_next(nrs_trainer* t, const float* x_host, const float* target_host, const int32_t* labels_host, int batch) {
+// Reads the loss of the step just issued.  Under data parallelism the wait runs through the group's
+// deadline loop, so a rank that never arrives surfaces as NRS_ERR_TIMEOUT instead of a hang.
+void read_loss(nrs_trainer* t, float* loss_out) {
+  if (t->dp && t->world > 1) t->dp->host_wait(t->ctx->stream);
+  nrs::check(t->ctx, nrs_d2h(t->ctx, loss_out, t->loss_dev, sizeof(float)));
+}
+
+size_t sample_words(const nrs_trainer* t) {   // 4-byte words per sample: floats, or token ids
+  size_t per = 1;
+  for (size_t d : t->in_shape) per *= d;
+  return per;
+}
+
+// x_host: float samples, or int32 token ids for a token model (same word size).  Exactly one of
+// target_host (one-hot rows) / labels_host (one class index per loss row) is given.
+void stage_next(nrs_trainer* t, const void* x_host, const float* target_host, const int32_t* labels_host, int batch) {
   if (batch <= 0) fail(NRS_ERR_SHAPE, "trainer: batch must be positive");
   nrs_trainer::Slot& sl = t->slots[t->fill_idx];
   if (sl.pending) fail(NRS_ERR_ARG, "trainer: both staging slots hold a batch that no step has consumed yet");
@@ -414,19 +419,17 @@ void stage_next(nrs_trainer* t, const float* x_host, const float* target_host, c
     cuda_ok(cudaEventCreateWithFlags(&sl.filled, cudaEventDisableTiming), "event creation");
     cuda_ok(cudaEventCreateWithFlags(&sl.consumed, cudaEventDisableTiming), "event creation");
   }
-  size_t per = 1;
-  for (size_t d : t->in_shape) per *= d;
+  const size_t per = sample_words(t), rows = (size_t)batch * t->rows_per_sample;
   grow_slot_block(&sl.x, &sl.x_cap, per * batch);
-  grow_slot_block(&sl.t, &sl.t_cap, (size_t)t->classes * batch);
-  if (labels_host) grow_slot_block(&sl.labels, &sl.labels_cap, (size_t)batch);
+  if (labels_host) grow_slot_block(&sl.labels, &sl.labels_cap, rows);
+  else grow_slot_block(&sl.t, &sl.t_cap, (size_t)t->classes * rows);
   // the step that last read this slot must have finished with it
   if (sl.used) cuda_ok(cudaStreamWaitEvent(t->copy_stream, sl.consumed, 0), "wait for the slot's last consumer");
   cuda_ok(cudaMemcpyAsync(sl.x, x_host, per * batch * sizeof(float), cudaMemcpyHostToDevice, t->copy_stream), "input copy");
   if (labels_host) {
-    cuda_ok(cudaMemcpyAsync(sl.labels, labels_host, (size_t)batch * sizeof(int32_t), cudaMemcpyHostToDevice, t->copy_stream),
-            "label copy");
+    cuda_ok(cudaMemcpyAsync(sl.labels, labels_host, rows * sizeof(int32_t), cudaMemcpyHostToDevice, t->copy_stream), "label copy");
   } else {
-    cuda_ok(cudaMemcpyAsync(sl.t, target_host, (size_t)t->classes * batch * sizeof(float), cudaMemcpyHostToDevice, t->copy_stream),
+    cuda_ok(cudaMemcpyAsync(sl.t, target_host, (size_t)t->classes * rows * sizeof(float), cudaMemcpyHostToDevice, t->copy_stream),
             "target copy");
   }
   sl.indexed = labels_host != nullptr;
@@ -436,28 +439,31 @@ void stage_next(nrs_trainer* t, const float* x_host, const float* target_host, c
   t->fill_idx ^= 1;
 }
 
-
 void step_staged(nrs_trainer* t, float* loss_out) {
   nrs_trainer::Slot& sl = t->slots[t->run_idx];
   if (!sl.pending) fail(NRS_ERR_ARG, "trainer: no staged batch (call nrs_trainer_stage_next first)");
   cuda_ok(cudaStreamWaitEvent(t->ctx->stream, sl.filled, 0), "wait for the staged batch");
-  if (sl.indexed)   // class indices -> one-hot rows, on the compute stream
-    nrs::check(t->ctx, nrs_onehot(t->ctx, reinterpret_cast<const int32_t*>(sl.labels), sl.t, sl.batch, t->classes));
-  const float* x_in = sl.x;
-  if (t->aug_shift >= 0 && t->training && t->in_shape.size() == 3) {
-    size_t per = 1;
-    for (size_t d : t->in_shape) per *= d;
-    grow_slot_block(&t->aug_buf, &t->aug_cap, per * sl.batch);
-    nrs::check(t->ctx, nrs_augment_flip_shift(t->ctx, sl.x, t->aug_buf, sl.batch, (int)t->in_shape[0], (int)t->in_shape[1],
-                                              (int)t->in_shape[2], t->aug_shift, t->aug_flip));
-    x_in = t->aug_buf;
+  StepInput in;
+  in.batch = sl.batch;
+  if (sl.indexed) in.labels = reinterpret_cast<const int32_t*>(sl.labels);   // expanded to one-hot rows by the step
+  else in.target = sl.t;
+  if (t->token_input) {
+    in.ids = reinterpret_cast<const int32_t*>(sl.x);
+  } else {
+    in.x = sl.x;
+    if (t->aug_shift >= 0 && t->training && t->in_shape.size() == 3) {
+      grow_slot_block(&t->aug_buf, &t->aug_cap, sample_words(t) * sl.batch);
+      nrs::check(t->ctx, nrs_augment_flip_shift(t->ctx, sl.x, t->aug_buf, sl.batch, (int)t->in_shape[0], (int)t->in_shape[1],
+                                                (int)t->in_shape[2], t->aug_shift, t->aug_flip));
+      in.x = t->aug_buf;
+    }
   }
-  run_step(t, x_in, sl.t, sl.batch, true);
+  run_step(t, in, true);
   cuda_ok(cudaEventRecord(sl.consumed, t->ctx->stream), "event record");
   sl.pending = false;
   sl.used = true;
   t->run_idx ^= 1;
-  if (loss_out) nrs::check(t->ctx, nrs_d2h(t->ctx, loss_out, t->loss_dev, sizeof(float)));
+  if (loss_out) read_loss(t, loss_out);
 }
 
 template <class F>
@@ -472,17 +478,29 @@ int guarded(nrs_ctx* ctx, F&& f) {
   }
 }
 
-int host_step(nrs_trainer* t, const float* x_host, const float* target_host, int batch, float* loss_out, bool optimize) {
+// Synchronous step from host buffers: inputs and targets are copied on the compute stream.
+int host_step(nrs_trainer* t, const void* x_host, const float* target_host, const int32_t* labels_host, int batch,
+              float* loss_out, bool optimize, bool tokens) {
   if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "trainer: null handle");
-  if (!x_host || !target_host) return nrs_fail(t->ctx, NRS_ERR_ARG, "trainer: null input");
+  if (!x_host || (!target_host && !labels_host)) return nrs_fail(t->ctx, NRS_ERR_ARG, "trainer: null input");
   return guarded(t->ctx, [&] {
     if (batch <= 0) fail(NRS_ERR_SHAPE, "trainer: batch must be positive");
-    size_t per = 1;
-    for (size_t d : t->in_shape) per *= d;
-    stage(t, &t->x_dev, &t->x_cap, x_host, per * batch);
-    stage(t, &t->t_dev, &t->t_cap, target_host, (size_t)t->classes * batch);
-    run_step(t, t->x_dev, t->t_dev, batch, optimize);
-    if (loss_out) nrs::check(t->ctx, nrs_d2h(t->ctx, loss_out, t->loss_dev, sizeof(float)));
+    if (tokens != t->token_input)
+      fail(NRS_ERR_ARG, tokens ? "trainer: this model reads float samples, not token ids" : "trainer: this model reads token ids (use the *_tokens entry points)");
+    const size_t rows = (size_t)batch * t->rows_per_sample;
+    stage(t, &t->x_dev, &t->x_cap, (const float*)x_host, sample_words(t) * batch);
+    StepInput in;
+    in.batch = batch;
+    if (tokens) in.ids = reinterpret_cast<const int32_t*>(t->x_dev); else in.x = t->x_dev;
+    if (labels_host) {
+      stage(t, &t->t_dev, &t->t_cap, reinterpret_cast<const float*>(labels_host), rows);
+      in.labels = reinterpret_cast<const int32_t*>(t->t_dev);
+    } else {
+      stage(t, &t->t_dev, &t->t_cap, target_host, (size_t)t->classes * rows);
+      in.target = t->t_dev;
+    }
+    run_step(t, in, optimize);
+    if (loss_out) read_loss(t, loss_out);
   });
 }
 
@@ -682,22 +700,54 @@ int nrs_trainer_get_grad(nrs_trainer* t, int i, float* host_out) {
 }
 
 int nrs_trainer_forward_backward(nrs_trainer* t, const float* x_host, const float* target_host, int batch, float* loss_out) {
-  return host_step(t, x_host, target_host, batch, loss_out, false);
+  return host_step(t, x_host, target_host, nullptr, batch, loss_out, false, false);
 }
 
 int nrs_trainer_step(nrs_trainer* t, const float* x_host, const float* target_host, int batch, float* loss_out) {
-  return host_step(t, x_host, target_host, batch, loss_out, true);
+  return host_step(t, x_host, target_host, nullptr, batch, loss_out, true, false);
+}
+
+int nrs_trainer_forward_backward_tokens(nrs_trainer* t, const int32_t* ids_host, const int32_t* labels_host, int batch,
+                                        float* loss_out) {
+  return host_step(t, ids_host, nullptr, labels_host, batch, loss_out, false, true);
+}
+
+int nrs_trainer_step_tokens(nrs_trainer* t, const int32_t* ids_host, const int32_t* labels_host, int batch, float* loss_out) {
+  return host_step(t, ids_host, nullptr, labels_host, batch, loss_out, true, true);
+}
+
+int nrs_trainer_stage_next_tokens(nrs_trainer* t, const int32_t* ids_host, const int32_t* labels_host, int batch) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_stage_next_tokens: null handle");
+  if (!ids_host || !labels_host) return nrs_fail(t->ctx, NRS_ERR_ARG, "nrs_trainer_stage_next_tokens: null input");
+  NRS_REQUIRE(t->ctx, t->token_input, NRS_ERR_ARG, "nrs_trainer_stage_next_tokens: this model reads float samples");
+  return guarded(t->ctx, [&] { stage_next(t, ids_host, nullptr, labels_host, batch); });
+}
+
+int nrs_trainer_step_tokens_device(nrs_trainer* t, const int32_t* ids_dev, const int32_t* labels_dev, int batch, float* loss_out) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_step_tokens_device: null handle");
+  if (!ids_dev || !labels_dev) return nrs_fail(t->ctx, NRS_ERR_ARG, "nrs_trainer_step_tokens_device: null input");
+  NRS_REQUIRE(t->ctx, t->token_input, NRS_ERR_ARG, "nrs_trainer_step_tokens_device: this model reads float samples");
+  return guarded(t->ctx, [&] {
+    StepInput in;
+    in.ids = ids_dev;
+    in.labels = labels_dev;
+    in.batch = batch;
+    run_step(t, in, true);
+    if (loss_out) read_loss(t, loss_out);
+  });
 }
 
 int nrs_trainer_stage_next(nrs_trainer* t, const float* x_host, const float* target_host, int batch) {
   if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_stage_next: null handle");
   if (!x_host || !target_host) return nrs_fail(t->ctx, NRS_ERR_ARG, "nrs_trainer_stage_next: null input");
+  NRS_REQUIRE(t->ctx, !t->token_input, NRS_ERR_ARG, "nrs_trainer_stage_next: this model reads token ids");
   return guarded(t->ctx, [&] { stage_next(t, x_host, target_host, nullptr, batch); });
 }
 
 int nrs_trainer_stage_next_indexed(nrs_trainer* t, const float* x_host, const int32_t* labels_host, int batch) {
   if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_stage_next_indexed: null handle");
   if (!x_host || !labels_host) return nrs_fail(t->ctx, NRS_ERR_ARG, "nrs_trainer_stage_next_indexed: null input");
+  NRS_REQUIRE(t->ctx, !t->token_input, NRS_ERR_ARG, "nrs_trainer_stage_next_indexed: this model reads token ids");
   return guarded(t->ctx, [&] { stage_next(t, x_host, nullptr, labels_host, batch); });
 }
 
@@ -719,27 +769,21 @@ int nrs_trainer_step_staged(nrs_trainer* t, float* loss_out) {
 int nrs_trainer_step_device(nrs_trainer* t, const float* x_dev, const float* target_dev, int batch, float* loss_out) {
   if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_step_device: null handle");
   if (!x_dev || !target_dev) return nrs_fail(t->ctx, NRS_ERR_ARG, "nrs_trainer_step_device: null input");
+  NRS_REQUIRE(t->ctx, !t->token_input, NRS_ERR_ARG, "nrs_trainer_step_device: this model reads token ids");
   return guarded(t->ctx, [&] {
-    run_step(t, x_dev, target_dev, batch, true);
-    if (loss_out) nrs::check(t->ctx, nrs_d2h(t->ctx, loss_out, t->loss_dev, sizeof(float)));
+    StepInput in;
+    in.x = x_dev;
+    in.target = target_dev;
+    in.batch = batch;
+    run_step(t, in, true);
+    if (loss_out) read_loss(t, loss_out);
   });
 }
 
 int nrs_trainer_last_loss(nrs_trainer* t, float* loss_out) {
   if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_last_loss: null handle");
   NRS_REQUIRE(t->ctx, loss_out != nullptr, NRS_ERR_ARG, "nrs_trainer_last_loss: null output");
-  return nrs_d2h(t->ctx, loss_out, t->loss_dev, sizeof(float));
-}
-
-int nrs_dp_unique_id(void* id_out) {
-  if (!id_out) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_dp_unique_id: null output");
-  NcclApi* api = nccl_api();
-  if (!api) return nrs_fail(nullptr, NRS_ERR_NCCL, "nrs_dp_unique_id: NCCL is not available");
-  NcclId id;
-  const int rc = api->GetUniqueId(&id);
-  if (rc != 0) return nrs_fail(nullptr, NRS_ERR_NCCL, "ncclGetUniqueId: %s", api->GetErrorString(rc));
-  std::memcpy(id_out, &id, sizeof(id));
-  return NRS_OK;
+  return guarded(t->ctx, [&] { read_loss(t, loss_out); });
 }
 
 int nrs_trainer_enable_dp(nrs_trainer* t, int rank, int world, const void* unique_id, int global_batch,
@@ -748,52 +792,28 @@ int nrs_trainer_enable_dp(nrs_trainer* t, int rank, int world, const void* uniqu
   nrs_ctx* ctx = t->ctx;
   NRS_REQUIRE(ctx, world >= 1 && rank >= 0 && rank < world, NRS_ERR_ARG, "nrs_trainer_enable_dp: rank %d / world %d", rank, world);
   NRS_REQUIRE(ctx, global_batch > 0, NRS_ERR_ARG, "nrs_trainer_enable_dp: global batch must be positive");
-  NRS_REQUIRE(ctx, t->comm == nullptr, NRS_ERR_ARG, "nrs_trainer_enable_dp: already enabled");
-  t->rank = rank;
-  t->world = world;
-  t->global_batch = global_batch;
-  if (world == 1) return NRS_OK;
-  NRS_REQUIRE(ctx, unique_id != nullptr, NRS_ERR_ARG, "nrs_trainer_enable_dp: null unique id");
-  NcclApi* api = nccl_api();
-  if (!api) { t->world = 1; return nrs_fail(ctx, NRS_ERR_NCCL, "nrs_trainer_enable_dp: NCCL is not available"); }
-  NcclId id;
-  std::memcpy(&id, unique_id, sizeof(id));
-  const int rc = api->CommInitRank(&t->comm, world, id, rank);
-  if (rc != 0) { t->world = 1; t->comm = nullptr; return nrs_fail(ctx, NRS_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString(rc)); }
-  NRS_CUDA(ctx, cudaStreamCreateWithFlags(&t->comm_stream, cudaStreamNonBlocking));
-  NRS_CUDA(ctx, cudaEventCreateWithFlags(&t->ready_ev, cudaEventDisableTiming));
-  NRS_CUDA(ctx, cudaEventCreateWithFlags(&t->done_ev, cudaEventDisableTiming));
-  t->buckets = plan_buckets(t->flat->offset, t->flat->total, bucket_bytes ? bucket_bytes : ((size_t)32 << 20));
-  return NRS_OK;
-}
-
-int nrs_dp_shard_range(int global_batch, int rank, int world, int* begin_out, int* end_out) {
-  if (world < 1 || rank < 0 || rank >= world || global_batch < 0 || !begin_out || !end_out)
-    return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_dp_shard_range: bad arguments");
-  // Contiguous shards; the first (global_batch % world) ranks take one extra sample.
-  const int base = global_batch / world, extra = global_batch % world;
-  *begin_out = rank * base + std::min(rank, extra);
-  *end_out = *begin_out + base + (rank < extra ? 1 : 0);
-  return NRS_OK;
-}
-
-int nrs_dp_plan_buckets(const int64_t* param_lens, int n_params, size_t bucket_bytes, int64_t* starts_out,
-                        int64_t* ends_out, int capacity) {
-  if (n_params < 0 || (n_params > 0 && !param_lens)) return -1;
-  std::vector<size_t> offsets;
-  size_t total = 0;
-  for (int i = 0; i < n_params; ++i) {
-    if (param_lens[i] < 0) return -1;
-    offsets.push_back(total);
-    total += ((size_t)param_lens[i] + 3) / 4 * 4;
-  }
-  auto b = plan_buckets(offsets, total, bucket_bytes ? bucket_bytes : ((size_t)32 << 20));
-  if (starts_out && ends_out)
-    for (int i = 0; i < (int)b.size() && i < capacity; ++i) {
-      starts_out[i] = (int64_t)b[i].begin;
-      ends_out[i] = (int64_t)b[i].end;
+  NRS_REQUIRE(ctx, !t->dp, NRS_ERR_ARG, "nrs_trainer_enable_dp: already enabled");
+  NRS_REQUIRE(ctx, world == 1 || unique_id != nullptr, NRS_ERR_ARG, "nrs_trainer_enable_dp: null unique id");
+  return guarded(ctx, [&] {
+    std::unique_ptr<nrs::DpGroup> g(new nrs::DpGroup(ctx, rank, world, unique_id, global_batch, t->dp_timeout_ms));
+    if (world > 1) {
+      g->register_params(t->params, bucket_bytes);
+      // each bucket's parameters are updated right behind its all-reduce, on the comm stream
+      g->after_bucket = [t](const nrs::DpBucket& b) { t->opt->step_flat_range(b.begin, b.end); };
     }
-  return (int)b.size();
+    t->dp = std::move(g);
+    t->rank = rank;
+    t->world = world;
+    t->global_batch = global_batch;
+  });
+}
+
+int nrs_trainer_set_dp_timeout_ms(nrs_trainer* t, double timeout_ms) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_set_dp_timeout_ms: null handle");
+  NRS_REQUIRE(t->ctx, timeout_ms > 0, NRS_ERR_ARG, "nrs_trainer_set_dp_timeout_ms: the deadline must be positive");
+  t->dp_timeout_ms = timeout_ms;
+  if (t->dp) t->dp->set_timeout_ms(timeout_ms);
+  return NRS_OK;
 }
 
 }  // extern "C"

@@ -82,30 +82,55 @@ NodeP Linear::forward(const NodeP& x) const { return add(matmul(x, weights), bia
 
 NodeP LayerNorm::forward(const NodeP& x) const { return layernorm(x, gamma, beta, eps); }
 
+// Gather (+ positional table) from indices already on the device; the node does not own `idx_dev`.
+static NodeP embed_resident(const Embedding& e, const int32_t* idx_dev, size_t count, const std::vector<size_t>& out_shape,
+                            const NodeP& pos_table, size_t seq) {
+  nrs_ctx* ctx = e.weight->ctx;
+  const int dim = (int)e.embedding_dim, vocab = (int)e.vocab_size;
+  NodeP out = make_result(ctx, out_shape, {e.weight});
+  check(ctx, nrs_embedding_pos_fwd(ctx, e.weight->data, idx_dev, pos_table ? pos_table->data : nullptr, out->data, (int)count,
+                                   (int)seq, dim, vocab));
+  Node* self = out.get();
+  const NodeP w = e.weight;
+  out->backward_fn = [self, w, idx_dev, count, dim, vocab]() {
+    if (!w->requires_grad) return;
+    const float* g = grad_view(self);
+    GradSlot t = grad_slot(w);
+    check(self->ctx, nrs_embedding_bwd(self->ctx, g, idx_dev, t.ptr, (int)count, dim, vocab, t.accumulate));
+  };
+  return out;
+}
+
 static NodeP embed(const Embedding& e, const int32_t* indices, size_t count, const std::vector<size_t>& out_shape) {
   if (!e.weight || !e.weight->on_gpu()) fail(NRS_ERR_ARG, "cuda embedding: weight not on GPU");
   if (!indices && count) fail(NRS_ERR_ARG, "cuda embedding: null indices");
   for (size_t i = 0; i < count; ++i)
     if (indices[i] < 0 || (size_t)indices[i] >= e.vocab_size) fail(NRS_ERR_ARG, "embedding: token index out of vocab range");
   nrs_ctx* ctx = e.weight->ctx;
-  const int dim = (int)e.embedding_dim;
-  NodeP out = make_result(ctx, out_shape, {e.weight});
   void* idx_dev = nullptr;
   check(ctx, nrs_alloc(ctx, (count ? count : 1) * sizeof(int32_t), 0, &idx_dev));
+  NodeP out;
+  try {
+    check(ctx, nrs_h2d(ctx, idx_dev, indices, count * sizeof(int32_t)));
+    check(ctx, nrs_sync(ctx));  // the caller's index buffer may go away
+    out = embed_resident(e, (const int32_t*)idx_dev, count, out_shape, nullptr, 1);
+  } catch (...) {
+    nrs_free(ctx, idx_dev);
+    throw;
+  }
   out->saved.push_back(idx_dev);
-  check(ctx, nrs_h2d(ctx, idx_dev, indices, count * sizeof(int32_t)));
-  check(ctx, nrs_sync(ctx));  // the caller's index buffer may go away
-  check(ctx, nrs_embedding_fwd(ctx, e.weight->data, (const int32_t*)idx_dev, out->data, (int)count, dim));
-  Node* self = out.get();
-  const NodeP w = e.weight;
-  const int vocab = (int)e.vocab_size;
-  out->backward_fn = [self, w, idx_dev, count, dim, vocab]() {
-    if (!w->requires_grad) return;
-    const float* g = grad_view(self);
-    GradSlot t = grad_slot(w);
-    check(self->ctx, nrs_embedding_bwd(self->ctx, g, (const int32_t*)idx_dev, t.ptr, (int)count, dim, vocab, t.accumulate));
-  };
   return out;
+}
+
+NodeP Embedding::forward_resident(const int32_t* idx_dev, size_t batch, size_t seq, const NodeP& pos_table) const {
+  if (!weight || !weight->on_gpu()) fail(NRS_ERR_ARG, "cuda embedding: weight not on GPU");
+  if (!idx_dev && batch * seq) fail(NRS_ERR_ARG, "cuda embedding: null indices");
+  if (pos_table) {
+    if (!pos_table->on_gpu() || pos_table->shape.size() != 2 || pos_table->shape[1] != embedding_dim)
+      fail(NRS_ERR_SHAPE, "cuda embedding: positional table must be a resident [max_len, dim] tensor");
+    if (seq > pos_table->shape[0]) fail(NRS_ERR_SHAPE, "sequence longer than max_len");
+  }
+  return embed_resident(*this, idx_dev, batch * seq, {batch, seq, embedding_dim}, pos_table, seq);
 }
 
 NodeP Embedding::forward(const int32_t* indices, size_t count) const {
@@ -202,9 +227,16 @@ static NodeP block_body(const TransformerBlock& b, const NodeP& x, bool final_no
   NodeP attn_out = b.mha.forward_batch(x);
   NodeP x1 = b.norm1.forward(add(x, attn_out));
   NodeP flat = reshape(x1, {batch * seq, d});
-  NodeP h = b.ff1.forward(flat);
-  h = b.act == NRS_ACT_GELU ? gelu(h) : relu(h);
-  NodeP ff_out = reshape(b.ff2.forward(h), {batch, seq, d});
+  NodeP h, ff;
+  if (b.fused_epilogues) {
+    h = linear_act(flat, b.ff1.weights, b.ff1.bias, b.act);
+    ff = linear_act(h, b.ff2.weights, b.ff2.bias, NRS_ACT_NONE);
+  } else {
+    h = b.ff1.forward(flat);
+    h = b.act == NRS_ACT_GELU ? gelu(h) : relu(h);
+    ff = b.ff2.forward(h);
+  }
+  NodeP ff_out = reshape(ff, {batch, seq, d});
   NodeP x2 = add(x1, ff_out);
   return final_norm ? b.norm2.forward(x2) : x2;
 }

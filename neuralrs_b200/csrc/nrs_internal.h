@@ -138,6 +138,28 @@ int nrs_check_device_error(nrs_ctx* ctx);
                       cudaGetErrorString(e__));                                          \
   } while (0)
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (kernel, device) pair, and one process may hold
+// contexts on several devices.  Each launcher keeps one NrsSmemAttr per kernel instantiation: the largest
+// value already set on every device ordinal.
+constexpr int kNrsMaxDevices = 64;
+struct NrsSmemAttr {
+  size_t bytes[kNrsMaxDevices] = {};
+};
+// True when `bytes` of dynamic shared memory on `device` still has to be requested (values that fit the
+// 48 KB default never do); records the request.
+inline bool nrs_smem_attr_update(NrsSmemAttr& a, int device, size_t bytes) {
+  if (bytes <= 48 * 1024) return false;
+  if (device < 0 || device >= kNrsMaxDevices) return true;   // not tracked: always set
+  if (bytes <= a.bytes[device]) return false;
+  a.bytes[device] = bytes;
+  return true;
+}
+#define NRS_ENSURE_SMEM(ctx, attr, kernel, bytes)                                                          \
+  do {                                                                                                     \
+    if (nrs_smem_attr_update((attr), (ctx)->device, (size_t)(bytes)))                                      \
+      NRS_CUDA((ctx), cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes))); \
+  } while (0)
+
 // Programmatic dependent launch.  A kernel launched through nrs_pdl_launch may be scheduled while
 // the kernel before it in the stream is still running (as SMs free up in its last wave), so that its
 // launch latency and prologue overlap with that kernel's tail; it must execute NRS_PDL_WAIT() before

@@ -396,11 +396,8 @@ int launch(nrs_ctx* ctx, const CUtensorMap& ta_hi, const CUtensorMap& ta_lo, con
   using L = SmemLayout<BN, NPLANES, emit_bytes<NPLANES, Policy>()>;
   constexpr int kSmem = L::kBytes;
   static_assert(kSmem <= 227 * 1024 && L::kStages >= 2, "shared memory budget");
-  static bool attr_set = false;
-  if (!attr_set) {
-    NRS_CUDA(ctx, cudaFuncSetAttribute(tc_kernel<BN, NPLANES, Policy>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-    attr_set = true;
-  }
+  static NrsSmemAttr attr;
+  NRS_ENSURE_SMEM(ctx, attr, (tc_kernel<BN, NPLANES, Policy>), kSmem);
   const int tiles_n = (n_total + BN - 1) / BN;
   SplitInfo sp{};
   plan_split(ctx, (long)tiles_m * tiles_n * batches, kb_total, NPLANES == 2, &sp.splits, &sp.kb_per_split);

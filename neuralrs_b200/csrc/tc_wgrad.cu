@@ -247,12 +247,8 @@ namespace {
 
 template <int NPLANES, int STAGES>
 int launch_wgrad(nrs_ctx* ctx, const CUtensorMap* maps, const WgradParams& p, int splits, size_t smem_bytes) {
-  static size_t attr_bytes = 0;
-  if (smem_bytes > attr_bytes) {
-    NRS_CUDA(ctx, cudaFuncSetAttribute(tc_wgrad_kernel<NPLANES, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem_bytes));
-    attr_bytes = smem_bytes;
-  }
+  static NrsSmemAttr attr;
+  NRS_ENSURE_SMEM(ctx, attr, (tc_wgrad_kernel<NPLANES, STAGES>), smem_bytes);
   int* err = nullptr;
   const int st = nrs_err_flag(ctx, &err);
   if (st != NRS_OK) return st;

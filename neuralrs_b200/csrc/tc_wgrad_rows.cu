@@ -332,11 +332,8 @@ tc_wgrad_rows_reduce_kernel(const RowParams p, int splits, int ctas, int lanes, 
 
 template <int NPLANES, int KS>
 int launch_rows(nrs_ctx* ctx, const CUtensorMap* maps, const RowParams& p, int ctas, int splits, size_t smem_bytes) {
-  static size_t attr_bytes = 0;
-  if (smem_bytes > attr_bytes) {
-    NRS_CUDA(ctx, cudaFuncSetAttribute(tc_wgrad_rows_kernel<NPLANES, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-    attr_bytes = smem_bytes;
-  }
+  static NrsSmemAttr attr;
+  NRS_ENSURE_SMEM(ctx, attr, (tc_wgrad_rows_kernel<NPLANES, KS>), smem_bytes);
   int* err = nullptr;
   const int st = nrs_err_flag(ctx, &err);
   if (st != NRS_OK) return st;

@@ -10,23 +10,42 @@
 
 namespace {
 
+// out[t, :] = w[idx[t], :] (+ pos[t % seq, :] when a positional table is given).  An index outside
+// [0, vocab) is never dereferenced: its row reads as zeros and the context's error word is set.
+constexpr int kErrBadIndex = 5;
 __global__ void __launch_bounds__(256)
-embed_fwd_kernel(const float* __restrict__ w, const int32_t* __restrict__ idx, float* __restrict__ out, int tokens,
-                 int dim) {
+embed_fwd_kernel(const float* __restrict__ w, const int32_t* __restrict__ idx, const float* __restrict__ pos,
+                 float* __restrict__ out, int tokens, int seq, int dim, int vocab, int* err) {
   NRS_PDL_PROLOGUE();
   const size_t total = (size_t)tokens * dim;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  if ((dim & 3) == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+  const bool vec = (dim & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(pos)) & 15) == 0;
+  if (vec) {
     const int d4 = dim >> 2;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total / 4; i += stride) {
       const size_t t = i / d4;
       const int c = (int)(i - t * d4);
-      reinterpret_cast<float4*>(out)[i] = reinterpret_cast<const float4*>(w + (size_t)idx[t] * dim)[c];
+      const int row = idx[t];
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (row >= 0 && row < vocab) v = reinterpret_cast<const float4*>(w + (size_t)row * dim)[c];
+      else if (c == 0) atomicExch(err, kErrBadIndex);
+      if (pos) {
+        const float4 p = reinterpret_cast<const float4*>(pos + (t % (size_t)seq) * dim)[c];
+        v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+      }
+      reinterpret_cast<float4*>(out)[i] = v;
     }
   } else {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
       const size_t t = i / dim;
-      out[i] = w[(size_t)idx[t] * dim + (i - t * dim)];
+      const int c = (int)(i - t * dim);
+      const int row = idx[t];
+      float v = 0.0f;
+      if (row >= 0 && row < vocab) v = w[(size_t)row * dim + c];
+      else if (c == 0) atomicExch(err, kErrBadIndex);
+      if (pos) v += pos[(t % (size_t)seq) * dim + c];
+      out[i] = v;
     }
   }
 }
@@ -133,14 +152,25 @@ permute_heads_kernel(const float* __restrict__ x, float* y, size_t total, int S,
 
 extern "C" {
 
-int nrs_embedding_fwd(nrs_ctx* ctx, const float* weight, const int32_t* idx, float* out, int tokens, int dim) {
+int nrs_embedding_pos_fwd(nrs_ctx* ctx, const float* weight, const int32_t* idx, const float* pos_table, float* out,
+                          int tokens, int seq, int dim, int vocab) {
   NRS_REQUIRE_CTX(ctx);
-  NRS_REQUIRE(ctx, tokens >= 0 && dim > 0, NRS_ERR_SHAPE, "nrs_embedding_fwd: bad shape [%d,%d]", tokens, dim);
+  NRS_REQUIRE(ctx, tokens >= 0 && dim > 0 && vocab > 0, NRS_ERR_SHAPE, "nrs_embedding_fwd: bad shape [%d,%d], vocabulary %d", tokens,
+              dim, vocab);
+  NRS_REQUIRE(ctx, !pos_table || seq > 0, NRS_ERR_SHAPE, "nrs_embedding_pos_fwd: sequence length must be positive");
   if (tokens == 0) return NRS_OK;
   NRS_REQUIRE(ctx, weight && idx && out, NRS_ERR_ARG, "nrs_embedding_fwd: null tensor");
-  NRS_PDL_LAUNCH(embed_fwd_kernel, grid_for(ctx, (size_t)tokens * dim / 4 + 1), 256, 0, ctx->stream, weight, idx, out, tokens, dim);
+  int* err = nullptr;
+  const int st = nrs_err_flag(ctx, &err);
+  if (st != NRS_OK) return st;
+  NRS_PDL_LAUNCH(embed_fwd_kernel, grid_for(ctx, (size_t)tokens * dim / 4 + 1), 256, 0, ctx->stream, weight, idx, pos_table, out,
+                 tokens, pos_table ? seq : 1, dim, vocab, err);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
+}
+
+int nrs_embedding_fwd(nrs_ctx* ctx, const float* weight, const int32_t* idx, float* out, int tokens, int dim, int vocab) {
+  return nrs_embedding_pos_fwd(ctx, weight, idx, nullptr, out, tokens, 1, dim, vocab);
 }
 
 int nrs_embedding_bwd(nrs_ctx* ctx, const float* g, const int32_t* idx, float* dweight, int tokens, int dim,

@@ -111,6 +111,17 @@ class Node:
     def requires_grad(self, flag: bool):
         check(self.ctx.h, self.ctx._l.nrs_node_set_requires_grad(self.h, int(bool(flag))))
 
+    def set_data(self, data):
+        """New host contents for the node (uploaded by the next runtime.to_cuda)."""
+        arr = _f32(data).reshape(-1)
+        if arr.size != len(self):
+            raise ValueError("data does not match the node's length")
+        check(self.ctx.h, self.ctx._l.nrs_node_set_data(self.h, _ptr(arr)))
+
+    def invalidate(self):
+        """After writing new values through data_ptr(): drops the operand planes cached for the old ones."""
+        check(self.ctx.h, self.ctx._l.nrs_node_invalidate(self.h))
+
     def data_ptr(self) -> int:
         return int(self.ctx._l.nrs_node_data_ptr(self.h) or 0)
 
@@ -450,7 +461,7 @@ class optim:
 
 
 LAYER_KINDS = {"conv": 0, "relu": 1, "maxpool": 2, "flatten": 3, "linear": 4, "gelu": 5, "batchnorm": 6, "dropout": 7,
-               "dropout2d": 8}
+               "dropout2d": 8, "embedding": 9, "transformer_block": 10, "layernorm": 11}
 
 
 class _LayerSpec(C.Structure):
@@ -462,7 +473,9 @@ class Trainer:
 
     `layers` uses the tuples ("conv", c_in, c_out, k, stride, pad), ("relu",), ("gelu",),
     ("maxpool", k, stride), ("flatten",), ("linear", n_in, n_out), ("batchnorm", channels),
-    ("dropout", p), ("dropout2d", p).
+    ("dropout", p), ("dropout2d", p), and for token models ("embedding", vocab, d_model, max_len) as the first
+    layer, ("transformer_block", d_model, heads, d_ff, act, flags), ("layernorm", features); see
+    neuralrs_b200/workloads.py.
     """
 
     def __init__(self, layers, in_shape, classes, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=1e-4,
@@ -593,6 +606,34 @@ class Trainer:
                                                               C.byref(loss) if want_loss else None))
         return float(loss.value) if want_loss else None
 
+    # ---- token models (first layer "embedding"): int32 ids [batch, seq], int32 labels [batch*seq]
+    def _token_call(self, fn, ids, labels, want_loss):
+        ids = np.ascontiguousarray(ids, np.int32)
+        labels = np.ascontiguousarray(labels, np.int32).reshape(-1)
+        assert labels.size == ids.size
+        loss = C.c_float()
+        check(self.ctx.h, fn(self.h, VP(ids.ctypes.data), VP(labels.ctypes.data), int(ids.shape[0]),
+                             C.byref(loss) if want_loss else None))
+        return float(loss.value) if want_loss else None
+
+    def forward_backward_tokens(self, ids, labels, want_loss=True):
+        return self._token_call(self.ctx._l.nrs_trainer_forward_backward_tokens, ids, labels, want_loss)
+
+    def step_tokens(self, ids, labels, want_loss=True):
+        return self._token_call(self.ctx._l.nrs_trainer_step_tokens, ids, labels, want_loss)
+
+    def stage_next_tokens_ptr(self, ids_host_ptr: int, labels_host_ptr: int, batch: int):
+        check(self.ctx.h, self.ctx._l.nrs_trainer_stage_next_tokens(self.h, VP(ids_host_ptr), VP(labels_host_ptr), int(batch)))
+
+    def step_tokens_device(self, ids_dev_ptr: int, labels_dev_ptr: int, batch: int, want_loss=False):
+        loss = C.c_float()
+        check(self.ctx.h, self.ctx._l.nrs_trainer_step_tokens_device(self.h, VP(ids_dev_ptr), VP(labels_dev_ptr), int(batch),
+                                                                     C.byref(loss) if want_loss else None))
+        return float(loss.value) if want_loss else None
+
+    def set_dp_timeout_ms(self, ms: float):
+        check(self.ctx.h, self.ctx._l.nrs_trainer_set_dp_timeout_ms(self.h, C.c_double(ms)))
+
     def last_loss(self) -> float:
         loss = C.c_float()
         check(self.ctx.h, self.ctx._l.nrs_trainer_last_loss(self.h, C.byref(loss)))
@@ -613,6 +654,83 @@ class Trainer:
             self.close()
         except Exception:
             pass
+
+
+class DataParallel:
+    """Operator-level gradient exchange for a loop over nodes (include/nrs_graph.h: nrs_dp_create,
+    nrs_bucket_register, nrs_grad_ready, nrs_allreduce_wait, nrs_backward_graph_dp)."""
+
+    def __init__(self, rank: int, world: int, unique_id: bytes | None, global_batch: int, timeout_ms: float = 0.0,
+                 ctx: Context | None = None):
+        self.ctx = ctx or default_context()
+        buf = C.create_string_buffer(unique_id, 128) if unique_id is not None else None
+        h = VP()
+        check(self.ctx.h, self.ctx._l.nrs_dp_create(self.ctx.h, rank, world, buf, int(global_batch), C.c_double(timeout_ms),
+                                                    C.byref(h)))
+        self.h = h
+
+    def register(self, params, bucket_bytes: int = 0):
+        arr = _handles(params)
+        check(self.ctx.h, self.ctx._l.nrs_bucket_register(self.h, arr, len(params), C.c_size_t(bucket_bytes)))
+
+    @property
+    def bucket_count(self) -> int:
+        return int(self.ctx._l.nrs_dp_bucket_count(self.h))
+
+    def begin_step(self):
+        check(self.ctx.h, self.ctx._l.nrs_dp_begin_step(self.h))
+
+    def grad_ready(self, param: Node):
+        check(self.ctx.h, self.ctx._l.nrs_grad_ready(self.h, param.h))
+
+    def allreduce_wait(self):
+        check(self.ctx.h, self.ctx._l.nrs_allreduce_wait(self.h))
+
+    def backward_graph(self, root: Node):
+        check(self.ctx.h, self.ctx._l.nrs_backward_graph_dp(root.h, self.h))
+
+    def host_wait(self):
+        check(self.ctx.h, self.ctx._l.nrs_dp_host_wait(self.h))
+
+    def set_timeout_ms(self, ms: float):
+        check(self.ctx.h, self.ctx._l.nrs_dp_set_timeout_ms(self.h, C.c_double(ms)))
+
+    def all_reduce_sum(self, dev_ptr: int, count: int):
+        check(self.ctx.h, self.ctx._l.nrs_dp_all_reduce_sum(self.h, VP(dev_ptr), C.c_size_t(count)))
+
+    def close(self):
+        if self.h and self.ctx.h:
+            self.ctx._l.nrs_dp_free(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def dp_fingerprint(param_lens, bucket_bytes: int, global_batch: int, world: int) -> int:
+    arr = (C.c_int64 * len(param_lens))(*[int(v) for v in param_lens])
+    return int(_lib.lib().nrs_dp_fingerprint(arr, len(param_lens), C.c_size_t(bucket_bytes), int(global_batch), int(world)))
+
+
+def dp_check_fingerprints(fingerprints):
+    arr = (C.c_uint64 * len(fingerprints))(*[int(v) for v in fingerprints])
+    st = _lib.lib().nrs_dp_check_fingerprints(arr, len(fingerprints))
+    if st != 0:
+        raise _lib.NrsError(st, (_lib.lib().nrs_last_error(None) or b"").decode())
+
+
+def watchdog_wait(poll, timeout_ms: float, interval_us: float = 200.0) -> float:
+    """Runs the library's deadline loop over a Python poll function (0 running, 1 done, negative failed);
+    returns the milliseconds waited, raises NrsError (NRS_ERR_TIMEOUT / NRS_ERR_NCCL) otherwise."""
+    cb = _lib.POLL_FN(lambda _user: int(poll()))
+    waited = C.c_double()
+    st = _lib.lib().nrs_watchdog_wait(cb, None, C.c_double(timeout_ms), C.c_double(interval_us), C.byref(waited))
+    if st != 0:
+        raise _lib.NrsError(st, (_lib.lib().nrs_last_error(None) or b"").decode())
+    return float(waited.value)
 
 
 def dp_unique_id() -> bytes:

@@ -23,80 +23,9 @@ from __future__ import annotations
 
 import numpy as np
 
-# The benchmark configurations (input shape without batch, layers, classes).
-SMALL_CNN = dict(
-    name="small_cnn", in_shape=(1, 28, 28), classes=10,
-    layers=[("conv", 1, 32, 3, 1, 1), ("relu",), ("maxpool", 2, 2),
-            ("conv", 32, 64, 3, 1, 1), ("relu",), ("maxpool", 2, 2),
-            ("flatten",), ("linear", 3136, 128), ("relu",), ("linear", 128, 10)])
-
-VGG_CIFAR = dict(
-    name="vgg_cifar", in_shape=(3, 32, 32), classes=10,
-    layers=[("conv", 3, 64, 3, 1, 1), ("relu",), ("conv", 64, 64, 3, 1, 1), ("relu",), ("maxpool", 2, 2),
-            ("conv", 64, 128, 3, 1, 1), ("relu",), ("conv", 128, 128, 3, 1, 1), ("relu",), ("maxpool", 2, 2),
-            ("conv", 128, 256, 3, 1, 1), ("relu",), ("conv", 256, 256, 3, 1, 1), ("relu",), ("maxpool", 2, 2),
-            ("flatten",), ("linear", 4096, 512), ("relu",), ("linear", 512, 10)])
-
-# The model of the reference's examples/cifar_cuda.rs:99-136: conv + BatchNorm2d + ReLU units, and a
-# Linear -> BatchNorm -> ReLU -> Dropout(0.5) -> Linear head.
-def _conv_bn(ci, co):
-    return [("conv", ci, co, 3, 1, 1), ("batchnorm", co), ("relu",)]
-
-
-VGG_CIFAR_BN = dict(
-    name="vgg_cifar_bn", in_shape=(3, 32, 32), classes=10,
-    layers=_conv_bn(3, 64) + _conv_bn(64, 64) + [("maxpool", 2, 2)] + _conv_bn(64, 128) + _conv_bn(128, 128)
-    + [("maxpool", 2, 2)] + _conv_bn(128, 256) + _conv_bn(256, 256) + [("maxpool", 2, 2)]
-    + [("flatten",), ("linear", 4096, 512), ("batchnorm", 512), ("relu",), ("dropout", 0.5), ("linear", 512, 10)])
-
-BN_MOMENTUM, BN_EPS = 0.9, 1e-5
-
-WIDE_MLP = dict(
-    name="wide_mlp", in_shape=(4096,), classes=1000,
-    layers=[("linear", 4096, 4096), ("gelu",), ("linear", 4096, 4096), ("gelu",),
-            ("linear", 4096, 4096), ("gelu",), ("linear", 4096, 4096), ("gelu",), ("linear", 4096, 1000)])
-
-ADAMW_HP = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=1e-4)
-
-
-def he_init(layers, seed: int):
-    """N(0, sqrt(2/fan_in)) weights, zero biases; fan_in = c_in*k*k for conv, n_in for Linear
-    (src/init/he.rs:9-21 draws the same distribution from an unseedable RNG)."""
-    rng = np.random.default_rng(seed)
-    params = []
-    for l in layers:
-        if l[0] == "conv":
-            _, ci, co, k, _, _ = l
-            params.append((rng.standard_normal((co, ci, k, k)) * np.sqrt(2.0 / (ci * k * k))).astype(np.float32))
-            params.append(np.zeros(co, np.float32))
-        elif l[0] == "linear":
-            _, n_in, n_out = l
-            params.append((rng.standard_normal((n_in, n_out)) * np.sqrt(2.0 / n_in)).astype(np.float32))
-            params.append(np.zeros(n_out, np.float32))
-        elif l[0] == "batchnorm":   # gamma = 1, beta = 0 (examples/cifar_cuda.rs:42)
-            params.append(np.ones(l[1], np.float32))
-            params.append(np.zeros(l[1], np.float32))
-    return params
-
-
-def bn_buffers(layers):
-    """Running statistics of the batchnorm layers, [mean0, var0, ...], at their initial 0 / 1."""
-    out = []
-    for l in layers:
-        if l[0] == "batchnorm":
-            out += [np.zeros(l[1], np.float32), np.ones(l[1], np.float32)]
-    return out
-
-
-def synthetic_batch(cfg, batch: int, seed: int, uniform01: bool = False):
-    """Synthetic stand-in for the dataset: N(0,1) (or U[0,1)) inputs, uniform labels as one-hot f32."""
-    rng = np.random.default_rng(seed)
-    shape = (batch,) + tuple(cfg["in_shape"])
-    x = rng.random(shape, dtype=np.float32) if uniform01 else rng.standard_normal(shape).astype(np.float32)
-    labels = rng.integers(0, cfg["classes"], batch)
-    t = np.zeros((batch, cfg["classes"]), np.float32)
-    t[np.arange(batch), labels] = 1.0
-    return x, t
+from neuralrs_b200.workloads import (ACT_GELU, ACT_RELU, ADAMW_HP, BN_EPS, BN_MOMENTUM, SMALL_CNN, TRANSFORMER_LM,  # noqa: F401
+                                     VGG_CIFAR, VGG_CIFAR_BN, WIDE_MLP, bn_buffers, he_init, synthetic_batch,
+                                     synthetic_tokens)
 
 
 def forward_backward(o, layers, params, x, target, divisor=None, input_requires_grad=False, buffers=None,
@@ -219,3 +148,52 @@ def train_step(o, layers, params, opt, x, target, buffers=None, rng=None):
     loss, grads, _ = forward_backward(o, layers, params, x, target, buffers=buffers, rng=rng)
     opt.step(params, grads)
     return loss
+
+
+def lm_forward_backward(o, layers, params, ids, labels, divisor=None):
+    """Forward + backward of a token model (first layer "embedding") through the define-by-run CPU graph
+    (oracle/autograd.py), the way the reference composes it: Embedding::forward_batch, PositionalEncoding,
+    TransformerBlock::forward per block, Linear on every position, cross-entropy over batch*seq rows
+    (src/nn/embedding.rs:60-113, positional.rs:36-47, transformer_block.rs:36-55, linear.rs, loss.rs:78-107).
+    labels: int class per position.  Returns (loss, grads in parameter order, logits [batch*seq, classes])."""
+    from oracle.autograd import Graph, Node, backward_graph
+    g = Graph(o)
+    ids = np.asarray(ids, np.int32)
+    batch, seq = ids.shape
+    nodes = [Node(p) for p in params]
+    pi = 0
+    h = None
+    for l in layers:
+        if l[0] == "embedding":
+            h = g.embedding(nodes[pi], ids)
+            pi += 1
+            if l[3] > 0:
+                h = g.positional(h, l[3])
+        elif l[0] == "transformer_block":
+            names = ("w_q", "w_k", "w_v", "w_o", "g1", "b1", "g2", "b2", "ff1_w", "ff1_b", "ff2_w", "ff2_b")
+            p = dict(zip(names, nodes[pi:pi + 12]))
+            pi += 12
+            if l[5] & 2:
+                raise NotImplementedError("forward_no_final_norm")
+            h = g.transformer_block(h, p, l[2], 1e-5, "gelu" if l[4] == ACT_GELU else "relu", causal=bool(l[5] & 1))
+        elif l[0] == "layernorm":
+            h = g.layernorm(h, nodes[pi], nodes[pi + 1], 1e-5)
+            pi += 2
+        elif l[0] == "linear":
+            d = h.shape[-1]
+            flat = g.reshape(h, (batch * seq, d))
+            out = g.add(g.matmul(flat, nodes[pi]), nodes[pi + 1])
+            h = g.reshape(out, (batch, seq, l[2]))
+            pi += 2
+        elif l[0] in ("relu", "gelu"):
+            h = g.relu(h) if l[0] == "relu" else g.gelu(h)
+        else:
+            raise ValueError(l)
+    classes = h.shape[-1]
+    logits = g.reshape(h, (batch * seq, classes))
+    target = np.zeros((batch * seq, classes), np.float32)
+    target[np.arange(batch * seq), np.asarray(labels).ravel()] = 1.0
+    loss = o.ce_fwd(logits.data, target, divisor)
+    logits.grad = o.ce_bwd(logits.data, target, divisor).astype(np.float32)
+    backward_graph(logits)
+    return loss, [n.grad for n in nodes], logits.data

@@ -42,3 +42,9 @@ def test_product_does_not_import_the_oracle():
     for f in pkg.rglob("*"):
         if f.suffix in (".py", ".cu", ".cuh", ".h", ".cpp"):
             assert "oracle" not in f.read_text().lower(), f
+
+
+def test_shared_memory_attribute_bookkeeping_is_per_device(nrs_lib):
+    """A kernel's dynamic shared-memory limit is a per-device setting; the launchers remember it per device
+    ordinal (host-only self-test, no GPU needed)."""
+    assert nrs_lib.nrs_selftest_smem_attr_bookkeeping() == 0

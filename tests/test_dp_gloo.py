@@ -97,3 +97,100 @@ def test_shard_ranges_and_bucket_plan(nrs_lib):
     assert len(many) == len(lens)                                      # every tensor its own bucket
     with pytest.raises(Exception):
         cuda.dp_shard_range(8, 3, 2)
+
+
+# ---------------------------------------------------------------- deadlines and rank agreement
+# Failure handling of the collective path, exercised on the host only: a rank that never joins a
+# collective (gloo ranks on CPU) must surface as NRS_ERR_TIMEOUT through the library's deadline loop,
+# and ranks that disagree about the model must be refused before anything is exchanged.
+
+def test_watchdog_returns_when_the_poll_finishes_and_reports_failures(nrs_lib):
+    from neuralrs_b200 import _lib, cuda
+    calls = {"n": 0}
+
+    def done_on_third():
+        calls["n"] += 1
+        return 1 if calls["n"] >= 3 else 0
+    waited = cuda.watchdog_wait(done_on_third, timeout_ms=2000, interval_us=100)
+    assert calls["n"] == 3 and waited < 1000
+    with pytest.raises(_lib.NrsError) as e:
+        cuda.watchdog_wait(lambda: -1, timeout_ms=2000)
+    assert e.value.code == 5                      # NRS_ERR_NCCL: the polled operation failed
+    with pytest.raises(_lib.NrsError) as e:
+        cuda.watchdog_wait(lambda: 0, timeout_ms=50, interval_us=1000)
+    assert e.value.code == 6                      # NRS_ERR_TIMEOUT
+    polled = {"n": 0}
+
+    def count():
+        polled["n"] += 1
+        return 0
+    with pytest.raises(_lib.NrsError):
+        cuda.watchdog_wait(count, timeout_ms=0)   # a zero deadline still polls once
+    assert polled["n"] == 1
+
+
+def _absent_rank_main(rank, world, port, out_dir):
+    sys.path.insert(0, str(ROOT))
+    import time
+    import torch
+    import torch.distributed as dist
+    from neuralrs_b200 import _lib, cuda
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    flag = Path(out_dir) / "rank0_gave_up"
+    if rank == 0:
+        work = dist.all_reduce(torch.ones(4), async_op=True)      # rank 1 never issues its half
+        t0 = time.time()
+        try:
+            cuda.watchdog_wait(lambda: 1 if work.is_completed() else 0, timeout_ms=400, interval_us=500)
+            outcome = "completed"
+        except _lib.NrsError as e:
+            outcome = f"code{e.code}"
+        (Path(out_dir) / "outcome.txt").write_text(f"{outcome} {time.time() - t0:.3f}")
+        flag.write_text("1")
+    else:
+        t0 = time.time()
+        while not flag.exists() and time.time() - t0 < 30:       # stays alive, never joins the collective
+            time.sleep(0.02)
+    os._exit(0)   # the collective can never complete: leave without tearing the group down
+
+
+def test_rank_that_never_joins_a_collective_times_out(tmp_path, nrs_lib):
+    import torch.multiprocessing as mp
+    mp.spawn(_absent_rank_main, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    outcome, seconds = (tmp_path / "outcome.txt").read_text().split()
+    assert outcome == "code6"                     # NRS_ERR_TIMEOUT from the host watchdog
+    assert 0.35 <= float(seconds) < 5.0
+
+
+def _mismatch_rank_main(rank, world, port, out_dir):
+    sys.path.insert(0, str(ROOT))
+    import torch
+    import torch.distributed as dist
+    from neuralrs_b200 import _lib, cuda
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    lens = [27 * 64, 64, 4096 * 512, 512]
+    results = []
+    for case, mine in enumerate([lens,                                         # all ranks agree
+                                 lens if rank == 0 else lens[:-1] + [513],     # rank 1 has a different layer width
+                                 lens]):
+        gb = 64 if (case < 2 or rank == 0) else 128                            # case 2: ranks disagree on the global batch
+        fp = cuda.dp_fingerprint(mine, 1 << 20, gb, world)
+        t = torch.tensor([fp & 0x7fffffff, fp >> 31 & 0x7fffffff, fp >> 62], dtype=torch.int64)
+        got = [torch.zeros(3, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(got, t)
+        fps = [int(g[0]) | int(g[1]) << 31 | int(g[2]) << 62 for g in got]
+        try:
+            cuda.dp_check_fingerprints(fps)
+            results.append("ok")
+        except _lib.NrsError as e:
+            results.append(f"code{e.code}")
+    (Path(out_dir) / f"result_{rank}.txt").write_text(" ".join(results))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ranks_that_disagree_about_the_model_are_refused_on_the_host(tmp_path, nrs_lib):
+    import torch.multiprocessing as mp
+    mp.spawn(_mismatch_rank_main, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for rank in range(2):
+        assert (tmp_path / f"result_{rank}.txt").read_text() == "ok code2 code2"    # NRS_ERR_SHAPE on every rank

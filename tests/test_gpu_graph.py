@@ -390,3 +390,34 @@ def test_conv_relu_conv_chain_all_modes(gpu_ctx, oracle64, mode, n, h, w, chans)
         assert np.linalg.norm(gpu.read_grad(gx) - g.ravel()) <= tol * np.linalg.norm(g)
     finally:
         gpu_ctx.set_math_mode(0)
+
+
+def test_reuploaded_input_node_restages_its_operand_planes(gpu_ctx, oracle64):
+    # One input node, two uploads: the convolution after the second upload must see the new values
+    # (the tensor-core path caches re-laid-out operand planes per node), forward and weight gradient.
+    rng = np.random.default_rng(77)
+    n, ci, h, w, co = 4, 32, 16, 16, 64
+    wt = (rng.standard_normal((co, ci, 3, 3)) * 0.1).astype(np.float32)
+    b = np.zeros(co, np.float32)
+    gw, gb = on_gpu(wt, list(wt.shape)), on_gpu(b, [co])
+    xs = [rng.standard_normal((n, ci, h, w)).astype(np.float32) for _ in range(3)]
+    seed = rng.standard_normal((n, co, h, w)).astype(np.float32)
+    gx = Node.new(xs[0], list(xs[0].shape))
+    for step, x in enumerate(xs):
+        if step == 2:        # written in place through the device pointer, then declared
+            import ctypes as C
+            from neuralrs_b200 import _lib
+            _lib.check(gpu_ctx.h, _lib.lib().nrs_h2d(gpu_ctx.h, C.c_void_p(gx.data_ptr()), C.c_void_p(x.ctypes.data), x.nbytes))
+            gpu_ctx.sync()
+            gx.invalidate()
+        else:
+            gx.set_data(x)
+            gpu.to_cuda(gx)
+        gpu.zero_grad([gw, gb])
+        out = nn.conv2d(gx, gw, gb, 1, 1)
+        ref = oracle64.conv2d_fwd(x, wt, b, 1, 1)
+        assert np.linalg.norm(gpu.to_host(out) - ref.ravel()) <= 1e-4 * np.linalg.norm(ref), f"forward after upload {step}"
+        gpu.set_grad(out, seed)
+        backward_graph(out)
+        _, dw, _ = oracle64.conv2d_bwd(x, wt, seed, 1, 1)
+        assert np.linalg.norm(gpu.read_grad(gw) - dw.ravel()) <= 1e-4 * np.linalg.norm(dw), f"weight gradient after upload {step}"
