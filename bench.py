@@ -10,15 +10,18 @@ For N > 1 launch under torchrun (one rank per GPU); run without torchrun the
 script re-launches itself through `python -m torch.distributed.run`.
 Rank 0 prints ONE JSON line.
 
-* value        whole-job samples/s with the step's inputs already resident in HBM
-* e2e          the same through the host-buffer entry points (nrs_trainer_stage_next +
+* value        whole-job samples/s with the step's inputs already resident in HBM: the MEDIAN of
+               `windows.n` back-to-back windows of K steps each (min / max beside it)
+* e2e          the same through the host-buffer entry points (nrs_trainer_stage_next[_tokens] +
                nrs_trainer_step_staged): pinned host inputs copied in (the copy of batch i+1
                overlapping step i), loss copied out, every step; `unpipelined_value` is the
-               plain nrs_trainer_step (copy, step, read-back in sequence)
+               plain nrs_trainer_step[_tokens] (copy, step, read-back in sequence)
 * roofline     the dominant contraction family, timed with CUDA events bracketed around
                its launches inside the timed region (nrs_profile_*; every fourth timed step)
 * cpu_baseline the CPU restatement of the reference's training loop (oracle/), timed on
-               this host on a bounded batch
+               this host's cores on a bounded batch; `fast` = the reference's fast forward kernels
+* dp_check     (N > 1) one step on a fixed 64-sample batch before timing: replicas bit-identical,
+               and the relative difference to rank 0 doing the same step alone on the whole batch
 * --impl reference  times that CPU restatement alone (the reference is a Rust crate and
                no Rust toolchain exists in the image, so its own binary cannot be built)
 """
@@ -30,7 +33,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -38,11 +40,13 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 METRIC = "train samples/s (fwd+bwd+AdamW)"
-WORKLOADS = {"vgg_cifar": ("VGG_CIFAR", 1024, 3), "small_cnn": ("SMALL_CNN", 64, 1), "wide_mlp": ("WIDE_MLP", 16384, 5),
-             "vgg_cifar_bn": ("VGG_CIFAR_BN", 1024, 7)}
-CPU_SAMPLE_BATCH = {"vgg_cifar": 16, "small_cnn": 64, "wide_mlp": 32, "vgg_cifar_bn": 16}
+# workload -> (table in neuralrs_b200.workloads, global batch, seed offset, CPU sample batch)
+WORKLOADS = {"vgg_cifar": ("VGG_CIFAR", 1024, 3, 32), "small_cnn": ("SMALL_CNN", 64, 1, 64),
+             "wide_mlp": ("WIDE_MLP", 16384, 5, 64), "vgg_cifar_bn": ("VGG_CIFAR_BN", 1024, 7, 32),
+             "transformer_lm": ("TRANSFORMER_LM", 32, 4, 2)}
 MATH = {"3xtf32": 0, "tf32": 1, "fp32": 2}
 PROF_NAMES = ["conv_fwd", "conv_dgrad", "conv_wgrad", "gemm", "adamw", "batchnorm"]
+N_WINDOWS = 5
 
 
 def parse():
@@ -51,10 +55,11 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="vgg_cifar", choices=list(WORKLOADS) + ["transformer_lm"])
+    ap.add_argument("--workload", default="vgg_cifar", choices=list(WORKLOADS))
     ap.add_argument("--math", default="3xtf32", choices=list(MATH))
     ap.add_argument("--global-batch", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-microbench", action="store_true")
     ap.add_argument("--no-fuse", action="store_true")
     return ap.parse_args()
 
@@ -69,27 +74,28 @@ def measured_peaks():
 
 
 def model_flops_per_sample(layers, in_shape):
-    """Algorithmic FLOP of one forward pass per sample, and of forward+backward (the first
-    layer's data gradient is not computed: its input does not require a gradient)."""
+    """Algorithmic FLOP of one forward pass per sample, and of forward+backward (the first contraction's
+    data gradient is not computed: its input does not require a gradient).  A token model's sample is one
+    sequence; attention scores and mixing are counted in full (the causal half included)."""
     shp = list(in_shape)
-    fwd = 0.0
-    total = 0.0
-    first = True
+    fwd = total = 0.0
+    first, tokens = True, 1
     for l in layers:
+        f = None
         if l[0] == "conv":
             _, ci, co, k, s, p = l
             oh, ow = (shp[1] + 2 * p - k) // s + 1, (shp[2] + 2 * p - k) // s + 1
             f = 2.0 * co * oh * ow * ci * k * k
-            fwd += f
-            total += f * (2 if first else 3)
             shp = [co, oh, ow]
-            first = False
         elif l[0] == "linear":
-            f = 2.0 * l[1] * l[2]
-            fwd += f
-            total += f * (2 if first else 3)
-            shp = [l[2]]
-            first = False
+            f = 2.0 * l[1] * l[2] * tokens
+            shp = shp[:-1] + [l[2]]
+        elif l[0] == "embedding":
+            tokens = shp[0]
+            shp = [shp[0], l[2]]
+        elif l[0] == "transformer_block":
+            d, ff = l[1], l[3]
+            f = tokens * (8.0 * d * d + 4.0 * tokens * d + 4.0 * d * ff)
         elif l[0] == "maxpool":
             shp = [shp[0], (shp[1] - l[1]) // l[2] + 1, (shp[2] - l[1]) // l[2] + 1]
         elif l[0] == "flatten":
@@ -97,6 +103,10 @@ def model_flops_per_sample(layers, in_shape):
             for d in shp:
                 n *= d
             shp = [n]
+        if f is not None:
+            fwd += f
+            total += f * (2 if first else 3)
+            first = False
     return fwd, total
 
 
@@ -154,35 +164,120 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.rows)}
 
 
-def cpu_reference_run(workload: str, steps: int, warmup: int, min_seconds: float = 0.0):
-    """Times the CPU restatement of the reference's training loop on a bounded batch."""
-    from oracle import models
+# ----------------------------------------------------------------------------- CPU baseline (oracle/)
+
+def cpu_reference_run(workload: str, steps: int, warmup: int, min_seconds: float = 0.0, max_seconds: float = 150.0):
+    """Times the CPU restatement of the reference's training loop on a bounded batch, on every host core
+    (the launcher's OMP_NUM_THREADS=1 is overridden: the reference's Rayon pools use all cores)."""
+    from oracle import models, nrs_oracle
     from oracle.nrs_oracle import Oracle
+    cores = nrs_oracle.host_cores()
+    nrs_oracle.set_threads(cores)
     cfg = getattr(models, WORKLOADS[workload][0])
     seed = 1234 + WORKLOADS[workload][2]
-    batch = CPU_SAMPLE_BATCH[workload]
+    batch = WORKLOADS[workload][3]
     o = Oracle("f32")
     params = models.he_init(cfg["layers"], seed)
     hp = models.ADAMW_HP
     opt = models.OracleAdamW(o, hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], hp["wd"])
-    x, t = models.synthetic_batch(cfg, batch, seed + 1, uniform01=(workload == "small_cnn"))
-    extra = dict(buffers=models.bn_buffers(cfg["layers"]), rng={"seed": seed, "offset": 0})
+    if cfg.get("token_model"):
+        ids, labels = models.synthetic_tokens(cfg, batch, seed + 1)
+
+        def step():
+            loss, grads, _ = models.lm_forward_backward(o, cfg["layers"], params, ids, labels)
+            opt.step(params, grads)
+            return loss
+    else:
+        x, t = models.synthetic_batch(cfg, batch, seed + 1, uniform01=(workload == "small_cnn"))
+        extra = dict(buffers=models.bn_buffers(cfg["layers"]), rng={"seed": seed, "offset": 0})
+
+        def step():
+            return models.train_step(o, cfg["layers"], params, opt, x, t, **extra)
+    t_w = time.perf_counter()
+    done_w = 0
     for _ in range(max(0, warmup)):
-        models.train_step(o, cfg["layers"], params, opt, x, t, **extra)
+        step()
+        done_w += 1
+        if time.perf_counter() - t_w > max_seconds / 3:      # bounded: a slow host must not stall the run
+            break
     done = 0
     t0 = time.perf_counter()
     while done < steps or (time.perf_counter() - t0) < min_seconds:
-        models.train_step(o, cfg["layers"], params, opt, x, t, **extra)
+        step()
         done += 1
         if done >= steps and min_seconds <= 0:
             break
-        if time.perf_counter() - t0 > 120:
+        if time.perf_counter() - t0 > max_seconds:
             break
     dt = time.perf_counter() - t0
-    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
-    return dict(value=batch * done / dt, ms_per_step=1e3 * dt / done, steps=done, batch=batch, cores=cores,
-                sample=f"{done} training steps of {cfg['name']} at batch {batch} "
+    return dict(value=batch * done / dt, ms_per_step=1e3 * dt / done, steps=done, warmup=done_w, batch=batch,
+                cores=nrs_oracle.get_threads(),
+                sample=f"{done} training steps of {cfg['name']} at batch {batch} on {cores} host cores "
                        f"(conv/matmul loops OpenMP-parallel as the reference's Rayon loops are)")
+
+
+def cpu_fast_forward(workload: str, seconds: float = 4.0):
+    """Upper bound of the reference's CPU path: the FORWARD pass of the model with the reference's fast kernels
+    restated (conv2d_im2col over matmul_simd, src/ops/im2col.rs:59-98, src/ops/simd.rs:42-77: AVX2 + all cores);
+    the reference has no fast backward kernels, so the naive forward is timed beside it for the ratio."""
+    from oracle import models, nrs_oracle
+    from oracle.nrs_oracle import Oracle
+    cfg = getattr(models, WORKLOADS[workload][0])
+    if cfg.get("token_model") or any(l[0] in ("batchnorm", "dropout", "dropout2d") for l in cfg["layers"]):
+        return None
+    nrs_oracle.set_threads(nrs_oracle.host_cores())
+    o = Oracle("f32")
+    seed = 1234 + WORKLOADS[workload][2]
+    batch = WORKLOADS[workload][3]
+    params = models.he_init(cfg["layers"], seed)
+    x, _ = models.synthetic_batch(cfg, batch, seed + 1, uniform01=(workload == "small_cnn"))
+
+    def forward(fast):
+        a, pi = x, 0
+        for l in cfg["layers"]:
+            if l[0] == "conv":
+                a = (nrs_oracle.conv2d_im2col if fast else o.conv2d_fwd)(a, params[pi], params[pi + 1], l[4], l[5])
+                pi += 2
+            elif l[0] == "linear":
+                a = o.bias_add_fwd(nrs_oracle.matmul_simd(a, params[pi]) if fast else o.matmul_fwd(a, params[pi]), params[pi + 1])
+                pi += 2
+            elif l[0] == "relu":
+                a = o.relu_fwd(a)
+            elif l[0] == "gelu":
+                a = o.gelu_fwd(a)
+            elif l[0] == "maxpool":
+                a, _ = o.maxpool_fwd(a, l[1], l[2])
+            elif l[0] == "flatten":
+                a = a.reshape(a.shape[0], -1)
+        return a
+    out = {}
+    for name, fast in (("fast", True), ("naive", False)):
+        forward(fast)
+        n, t0 = 0, time.perf_counter()
+        while n < 2 or time.perf_counter() - t0 < seconds:
+            forward(fast)
+            n += 1
+        out[name] = batch * n / (time.perf_counter() - t0)
+    return {"fwd_samples_per_s": out["fast"], "naive_fwd_samples_per_s": out["naive"], "batch": batch,
+            "kernels": "conv2d_im2col + matmul_simd (AVX2 FMA, all cores), forward pass only: the reference has no fast "
+                       "backward kernels; activations / pooling from the naive port"}
+
+
+# ----------------------------------------------------------------------------- micro-benchmarks (N = 1)
+
+def _time_calls(ctx, stream, fn, iters):
+    import torch
+    from neuralrs_b200 import _lib
+    for _ in range(3):
+        _lib.check(ctx.h, fn())
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        _lib.check(ctx.h, fn())
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
 
 
 def conv_microbench(ctx, stream, iters=10):
@@ -205,30 +300,21 @@ def conv_microbench(ctx, stream, iters=10):
         "fwd": lambda: l.nrs_conv2d_fwd(ctx.h, P(x), P(wt), P(b), P(y), *dims, 0),
         "dgrad": lambda: l.nrs_conv2d_bwd(ctx.h, P(x), P(wt), P(dy), P(dx), None, None, *dims, 0),
         "wgrad": lambda: l.nrs_conv2d_bwd(ctx.h, P(x), P(wt), P(dy), None, P(dw), None, *dims, 0),
+        "dgrad+wgrad": lambda: l.nrs_conv2d_bwd(ctx.h, P(x), P(wt), P(dy), P(dx), P(dw), None, *dims, 0),
     }
     flop = 2.0 * n * co * h * w * ci * 9
     out = {"shape": "x[256,64,32,32] w[128,64,3,3] s1 p1", "gflop_per_pass": flop / 1e9}
     for name, fn in calls.items():
-        for _ in range(3):
-            _lib.check(ctx.h, fn())
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(iters):
-            _lib.check(ctx.h, fn())
-        e1.record(stream)
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / iters
-        out[name] = {"ms": ms, "tflops": flop / (ms / 1e3) / 1e12}
+        ms = _time_calls(ctx, stream, fn, iters)
+        passes = 2 if "+" in name else 1
+        out[name] = {"ms": ms, "tflops": passes * flop / (ms / 1e3) / 1e12}
     return out
 
 
 def batchnorm_microbench(ctx, stream, hbm_peak_gbs, iters=10):
     """BatchNorm2d (training mode) and Dropout on the conv microbenchmark's activation shape [256,64,32,32]
     through the raw C ABI.  HBM-bound: the algorithmic bytes are one read of every input tensor and one write
-    of every output tensor (forward x -> y, xhat: 3 tensors; backward g, xhat -> dx: 3 tensors; dropout
-    a, mask -> out: 3 tensors); the kernels read their inputs twice (statistics, then the elementwise pass),
-    which the fraction shows."""
+    of every output tensor."""
     import ctypes as C
     import torch
     from neuralrs_b200 import _lib
@@ -254,18 +340,78 @@ def batchnorm_microbench(ctx, stream, hbm_peak_gbs, iters=10):
     }
     out = {"shape": "x[256,64,32,32]", "tensor_mb": tensor_bytes / 1e6, "hbm_peak_gbs": hbm_peak_gbs}
     for name, (tensors, fn) in calls.items():
-        for _ in range(3):
-            _lib.check(ctx.h, fn())
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(iters):
-            _lib.check(ctx.h, fn())
-        e1.record(stream)
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / iters
+        ms = _time_calls(ctx, stream, fn, iters)
         gbs = tensors * tensor_bytes / (ms / 1e3) / 1e9
         out[name] = {"ms": ms, "algorithmic_gbs": gbs, "frac": gbs / hbm_peak_gbs}
+    return out
+
+
+def hbm_microbench(ctx, stream, hbm_peak_gbs, iters=10):
+    """The HBM-bound kernels at bandwidth-bound sizes (every tensor >= 64 MB, well beyond L2 when summed) through the
+    raw C ABI: algorithmic bytes = one read of every input tensor and one write of every output tensor, over the
+    CUDA-event time of `iters` back-to-back calls; frac is against the measured copy bandwidth."""
+    import ctypes as C
+    import torch
+    from neuralrs_b200 import _lib
+    l = _lib.lib()
+    P = lambda t: C.c_void_p(t.data_ptr())
+    F = C.c_float
+    g = torch.Generator(device="cuda").manual_seed(1241)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    out = {"hbm_peak_gbs": hbm_peak_gbs, "iters": iters}
+
+    def entry(name, nbytes, fn, shape):
+        ms = _time_calls(ctx, stream, fn, iters)
+        gbs = nbytes / (ms / 1e3) / 1e9
+        out[name] = {"shape": shape, "ms": ms, "algorithmic_mb": nbytes / 1e6, "algorithmic_gbs": gbs, "frac": gbs / hbm_peak_gbs}
+    # LayerNorm over rows of 256 features (the language model's d_model)
+    rows, f = 65536, 256
+    x, gy = rn(rows, f), rn(rows, f)
+    gamma, beta = torch.rand(f, device="cuda") + 0.5, rn(f)
+    y, xhat, dx = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+    istd, dgm, dbt = torch.empty(rows, device="cuda"), torch.empty(f, device="cuda"), torch.empty(f, device="cuda")
+    tb = x.numel() * 4
+    entry("layernorm_fwd", 3 * tb + rows * 4, lambda: l.nrs_layernorm_fwd(ctx.h, P(x), P(gamma), P(beta), P(y), P(xhat), P(istd), rows, f, F(1e-5)),
+          "x[65536,256] -> y, xhat, istd")
+    entry("layernorm_bwd_dx", 3 * tb + rows * 4, lambda: l.nrs_layernorm_bwd(ctx.h, P(gy), P(xhat), P(istd), P(gamma), P(dx), None, None, rows, f, 0, 0),
+          "g, xhat, istd -> dx [65536,256]")
+    entry("layernorm_bwd_params", 2 * tb, lambda: l.nrs_layernorm_bwd(ctx.h, P(gy), P(xhat), P(istd), P(gamma), None, P(dgm), P(dbt), rows, f, 0, 0),
+          "g, xhat -> dgamma, dbeta [256]")
+    del x, gy, y, xhat, dx
+    # softmax over rows of 128 (the attention score width)
+    rows, wd = 131072, 128
+    x, gy = rn(rows, wd), rn(rows, wd)
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    tb = x.numel() * 4
+    entry("softmax_fwd", 2 * tb, lambda: l.nrs_softmax_fwd(ctx.h, P(x), P(y), rows, wd), "x[131072,128] -> y")
+    entry("softmax_bwd", 3 * tb, lambda: l.nrs_softmax_bwd(ctx.h, P(y), P(gy), P(dx), rows, wd, 0), "y, g -> dx [131072,128]")
+    del x, gy, y, dx
+    # cross-entropy forward + backward over the wide MLP's logits
+    rows, cl = 16384, 1000
+    logits = rn(rows, cl)
+    target = torch.zeros(rows, cl, device="cuda")
+    target[torch.arange(rows, device="cuda"), torch.randint(0, cl, (rows,), device="cuda", generator=g)] = 1.0
+    grad, loss_dev = torch.empty_like(logits), torch.zeros(1, device="cuda")
+    tb = logits.numel() * 4
+    entry("cross_entropy_fwd_bwd", 3 * tb, lambda: l.nrs_ce_fwd_bwd(ctx.h, P(logits), P(target), P(loss_dev), P(grad), rows, cl, rows),
+          "logits, one-hot [16384,1000] -> loss, grad")
+    del logits, target, grad
+    # AdamW over the wide MLP's 71.2 M parameters: 28 B per parameter
+    n = 71222248
+    p, gr, m, v = rn(n), rn(n), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    entry("adamw", 28 * n, lambda: l.nrs_adamw_step(ctx.h, P(p), P(gr), P(m), P(v), C.c_size_t(n), F(1e-3), F(0.9), F(0.999), F(1e-8),
+                                                    F(1e-4), F(0.1), F(0.001), F(1.0)), "71.2 M parameters")
+    del p, gr, m, v
+    # max-pool 2x2 forward / backward on the conv microbenchmark's activation
+    nb, c, h, w = 256, 64, 32, 32
+    x = rn(nb, c, h, w)
+    y = torch.empty(nb, c, h // 2, w // 2, device="cuda")
+    am = torch.empty(nb, c, h // 2, w // 2, device="cuda", dtype=torch.int32)
+    gy, dx = torch.randn_like(y), torch.empty_like(x)
+    entry("maxpool_fwd", x.numel() * 4 + 2 * y.numel() * 4, lambda: l.nrs_maxpool_fwd(ctx.h, P(x), P(y), P(am), nb, c, h, w, 2, 2),
+          "x[256,64,32,32] -> y, argmax")
+    entry("maxpool_bwd", x.numel() * 4 + 2 * y.numel() * 4, lambda: l.nrs_maxpool_bwd(ctx.h, P(gy), P(am), P(dx), nb, c, h, w, 2, 2, 0),
+          "g, argmax -> dx[256,64,32,32]")
     return out
 
 
@@ -289,21 +435,25 @@ def ncu_traffic(workload, math, family, per_gpu_batch):
             "traffic_source": f"ncu --set full capture at per-GPU batch {cap_batch} (profiles/), scaled by the pixel count"}
 
 
+def cpu_baseline_entry(r):
+    return {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     global_batch = args.global_batch or WORKLOADS[args.workload][1]
-    r = cpu_reference_run(args.workload, args.steps, min(args.warmup, 1))
+    r = cpu_reference_run(args.workload, args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "samples/s", "n_gpus": args.gpus,
-        "steps": r["steps"], "warmup": min(args.warmup, 1), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+        "steps": r["steps"], "warmup": r["warmup"], "ms_per_step": r["ms_per_step"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "global_batch": global_batch, "cpu_sample_batch": r["batch"],
-                   "note": "CPU restatement of the reference's own training loop (oracle/); the Rust crate cannot "
-                           "be built here (no cargo/rustc in the image)"},
-        "cpu_baseline": {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "port",
-                         "sample": r["sample"]},
+                   "note": "CPU restatement of the reference's own training loop (oracle/) on every host core; the Rust "
+                           "crate cannot be built here (no cargo/rustc in the image); each step is a bounded sample "
+                           "(cpu_sample_batch samples) of the workload"},
+        "cpu_baseline": cpu_baseline_entry(r),
         "e2e": {"value": r["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -311,12 +461,12 @@ def run_reference(args):
 
 
 def run_ours(args):
+    import ctypes as C
     import numpy as np
     import torch
     import torch.distributed as dist
 
-    from neuralrs_b200 import _lib, cuda
-    from oracle import models   # model tables + synthetic data only; never on the timed path
+    from neuralrs_b200 import _lib, cuda, workloads
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -326,31 +476,83 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    cfg = getattr(models, WORKLOADS[args.workload][0])
+    cfg = getattr(workloads, WORKLOADS[args.workload][0])
+    tokens = bool(cfg.get("token_model"))
     seed = 1234 + WORKLOADS[args.workload][2]
     global_batch = args.global_batch or WORKLOADS[args.workload][1]
     b0, b1 = cuda.dp_shard_range(global_batch, rank, world)
     batch = b1 - b0
+    rows_per_sample = cfg["in_shape"][0] if tokens else 1
 
     ctx = cuda.Context(local_rank)
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     ctx.set_stream(stream.cuda_stream)
     ctx.set_math_mode(MATH[args.math])
-    hp = models.ADAMW_HP
-    tr = cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
-                      hp["wd"], fuse=not args.no_fuse, ctx=ctx)
-    tr.set_params(models.he_init(cfg["layers"], seed))       # identical bytes on every rank
+    hp = workloads.ADAMW_HP
+    l = _lib.lib()
+    init = workloads.he_init(cfg["layers"], seed)       # identical bytes on every rank
+
+    def make_trainer(dp_batch=None):
+        tr = cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
+                          hp["wd"], fuse=not args.no_fuse, ctx=ctx)
+        tr.set_params(init)
+        if world > 1 and dp_batch:
+            box = [cuda.dp_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            tr.enable_dp(rank, world, box[0], dp_batch)
+        return tr
+
+    def make_batch(n, s):
+        """(inputs, targets) as contiguous numpy arrays: float samples + one-hot rows, or token ids + next-token labels."""
+        if tokens:
+            ids, labels = workloads.synthetic_tokens(cfg, n, s)
+            return ids, labels.reshape(n, rows_per_sample)
+        return workloads.synthetic_batch(cfg, n, s, uniform01=(args.workload == "small_cnn"))
+
+    def device_step(tr, x_ptr, t_ptr, n, want_loss=False):
+        return (tr.step_tokens_device if tokens else tr.step_device)(x_ptr, t_ptr, n, want_loss)
+
+    # ---- data-parallel check before timing: one step on a fixed 64-sample batch
+    dp_check = None
     if world > 1:
-        box = [cuda.dp_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
-        tr.enable_dp(rank, world, box[0], global_batch)
+        chk_n = 64
+        cx, ct = make_batch(chk_n, seed + 99)
+        c0, c1 = cuda.dp_shard_range(chk_n, rank, world)
+        tr_dp = make_trainer(chk_n)
+        xs = torch.from_numpy(np.ascontiguousarray(cx[c0:c1])).cuda()
+        ts = torch.from_numpy(np.ascontiguousarray(ct[c0:c1])).cuda()
+        share = device_step(tr_dp, xs.data_ptr(), ts.data_ptr(), c1 - c0, True)
+        flat = np.concatenate([tr_dp.get_param(i) for i in range(tr_dp.n_params)])
+        tr_dp.close()
+        mine = torch.from_numpy(flat).cuda()
+        lo, hi = mine.clone(), mine.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        identical = bool(torch.equal(lo, hi))            # every rank holds the same bits
+        loss_sum = torch.tensor([share], device="cuda", dtype=torch.float64)
+        dist.all_reduce(loss_sum)
+        if rank == 0:
+            tr_one = make_trainer()
+            xf, tf = torch.from_numpy(np.ascontiguousarray(cx)).cuda(), torch.from_numpy(np.ascontiguousarray(ct)).cuda()
+            full_loss = device_step(tr_one, xf.data_ptr(), tf.data_ptr(), chk_n, True)
+            ref = np.concatenate([tr_one.get_param(i) for i in range(tr_one.n_params)])
+            tr_one.close()
+            start = np.concatenate([p.ravel() for p in init])
+            upd, upd_ref = flat.astype(np.float64) - start, ref.astype(np.float64) - start
+            dp_check = {"batch": chk_n, "replicas_bit_identical": identical,
+                        "rel_err_vs_rank0_full_batch_step": float(np.linalg.norm(flat - ref) / np.linalg.norm(ref)),
+                        "rel_err_of_the_update": float(np.linalg.norm(upd - upd_ref) / max(np.linalg.norm(upd_ref), 1e-30)),
+                        "loss_sum_of_shares": float(loss_sum.item()), "loss_rank0_full_batch": full_loss}
+        dist.barrier()
+
+    tr = make_trainer(global_batch)
 
     # Synthetic batches: a few distinct ones, rotated, pinned on the host and resident on the device.
     n_sets = 4
     xs_pin, ts_pin, xs_dev, ts_dev = [], [], [], []
     for i in range(n_sets):
-        x, t = models.synthetic_batch(cfg, global_batch, seed + 10 + i, uniform01=(args.workload == "small_cnn"))
+        x, t = make_batch(global_batch, seed + 10 + i)
         xp = torch.from_numpy(np.ascontiguousarray(x[b0:b1])).pin_memory()
         tp = torch.from_numpy(np.ascontiguousarray(t[b0:b1])).pin_memory()
         xs_pin.append(xp); ts_pin.append(tp)
@@ -379,39 +581,48 @@ def run_ours(args):
             ms = float(tms.item())
         return ms
 
-    dev_step = lambda i: tr.step_device(xs_dev[i % n_sets].data_ptr(), ts_dev[i % n_sets].data_ptr(), batch, False)
-    host_step = lambda i: tr.step_ptr(xs_pin[i % n_sets].data_ptr(), ts_pin[i % n_sets].data_ptr(), batch, True)
+    dev_step = lambda i: device_step(tr, xs_dev[i % n_sets].data_ptr(), ts_dev[i % n_sets].data_ptr(), batch)
+    host_fn = l.nrs_trainer_step_tokens if tokens else l.nrs_trainer_step
+    stage_fn = l.nrs_trainer_stage_next_tokens if tokens else l.nrs_trainer_stage_next
+    loss_box = C.c_float()
+
+    def host_step(i):
+        _lib.check(ctx.h, host_fn(tr.h, C.c_void_p(xs_pin[i % n_sets].data_ptr()), C.c_void_p(ts_pin[i % n_sets].data_ptr()),
+                                  batch, C.byref(loss_box)))
+
+    def stage(j):
+        _lib.check(ctx.h, stage_fn(tr.h, C.c_void_p(xs_pin[j].data_ptr()), C.c_void_p(ts_pin[j].data_ptr()), batch))
 
     def staged_loop(total):
         """End-to-end steps with the input copy double-buffered: batch i+1 is staged (asynchronous copy from
         pinned memory on the copy stream) before step i is issued; every step still reads its loss back."""
         def fn(i):
             if i == 0:
-                tr.stage_next_ptr(xs_pin[0].data_ptr(), ts_pin[0].data_ptr(), batch)
+                stage(0)
             if i + 1 < total:
-                j = (i + 1) % n_sets
-                tr.stage_next_ptr(xs_pin[j].data_ptr(), ts_pin[j].data_ptr(), batch)
+                stage((i + 1) % n_sets)
             tr.step_staged(True)
         return fn
 
     for i in range(max(3, args.warmup)):
         dev_step(i)
-    l = _lib.lib()
     _lib.check(ctx.h, l.nrs_profile_reset(ctx.h))
     # The per-family CUDA-event brackets sit between kernels, where they defeat the chaining of
     # consecutive launches; they are switched on for every fourth timed step only (the first
     # included), and the family figures are scaled to the bracketed steps.
     bracket_every = 4
-    bracketed = len(range(0, args.steps, bracket_every))
+    bracketed = len(range(0, args.steps, bracket_every)) * N_WINDOWS
 
     def dev_step_bracketed(i):
         l.nrs_profile_enable(ctx.h, 1 if i % bracket_every == 0 else 0)
         dev_step(i)
     launches0 = ctx.launch_count()
+    windows = []
     with ClockSampler(local_rank) as clk:
-        ms = timed(dev_step_bracketed, args.steps)
-    launches = ctx.launch_count() - launches0
-    import ctypes as C
+        for _ in range(N_WINDOWS):
+            windows.append(timed(dev_step_bracketed, args.steps))
+    launches = (ctx.launch_count() - launches0) // N_WINDOWS
+    ms = statistics.median(windows)
     prof = {}
     for kind, name in enumerate(PROF_NAMES):
         pms, work, calls = C.c_double(), C.c_double(), C.c_uint64()
@@ -420,6 +631,10 @@ def run_ours(args):
     _lib.check(ctx.h, l.nrs_profile_enable(ctx.h, 0))
     _lib.check(ctx.h, l.nrs_profile_reset(ctx.h))
     loss = tr.last_loss()
+    if world > 1:     # every rank holds its share of the global-mean loss
+        lt = torch.tensor([loss], device="cuda", dtype=torch.float64)
+        dist.all_reduce(lt)
+        loss = float(lt.item())
 
     for i in range(2):
         host_step(i)
@@ -427,27 +642,33 @@ def run_ours(args):
     warm = staged_loop(2)
     for i in range(2):
         warm(i)
-    ms_e2e = timed(staged_loop(args.steps), args.steps)
+    e2e_windows = [timed(staged_loop(args.steps), args.steps) for _ in range(3)]
+    ms_e2e = statistics.median(e2e_windows)
 
     if rank == 0:
         peaks = measured_peaks()
-        value = global_batch * args.steps / (ms / 1e3)
-        e2e_value = global_batch * args.steps / (ms_e2e / 1e3)
+        per_s = lambda w_ms: global_batch * args.steps / (w_ms / 1e3)
         fwd_flop, step_flop = model_flops_per_sample(cfg["layers"], cfg["in_shape"])
-        # dominant contraction family by device time
-        fam = max(("conv_fwd", "conv_dgrad", "conv_wgrad", "gemm"), key=lambda k: prof[k]["ms"])
+        contractions = ("conv_fwd", "conv_dgrad", "conv_wgrad", "gemm")
+        fam = max(contractions, key=lambda k: prof[k]["ms"])      # dominant contraction family by device time
         f = prof[fam]
         achieved = (f["work"] / (f["ms"] / 1e3) / 1e12) if f["ms"] > 0 else 0.0
         tf32_peak = peaks["bf16_sustained"] / 2.0
-        contraction_ms = sum(prof[k]["ms"] for k in ("conv_fwd", "conv_dgrad", "conv_wgrad", "gemm"))
-        contraction_work = sum(prof[k]["work"] for k in ("conv_fwd", "conv_dgrad", "conv_wgrad", "gemm"))
+        umma = C.c_double()
+        _lib.check(ctx.h, l.nrs_measure_tf32_umma_peak(ctx.h, C.byref(umma)))
+        contraction_ms = sum(prof[k]["ms"] for k in contractions)
+        contraction_work = sum(prof[k]["work"] for k in contractions)
         adam = prof["adamw"]
-        x_bytes = sum(int(np.prod((global_batch,) + tuple(cfg["in_shape"]))) * 4 for _ in range(1))
-        t_bytes = global_batch * cfg["classes"] * 4
+        x_bytes = int(np.prod((global_batch,) + tuple(cfg["in_shape"]))) * 4
+        t_bytes = global_batch * rows_per_sample * (4 if tokens else cfg["classes"] * 4)
+        issue = 3.0 if args.math == "3xtf32" else 1.0
         line = {
-            "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
+            "metric": METRIC, "value": per_s(ms), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "windows": {"n": N_WINDOWS, "steps_each": args.steps, "statistic": "median",
+                        "ms_per_step_min": min(windows) / args.steps, "ms_per_step_max": max(windows) / args.steps,
+                        "value_min": per_s(max(windows)), "value_max": per_s(min(windows))},
             "config": {"workload": args.workload, "global_batch": global_batch, "per_gpu_batch": batch,
                        "parallelism": f"dp{world}", "math": args.math, "fused_epilogues": not args.no_fuse,
                        "init": "He N(0,sqrt(2/fan_in)), seed %d" % seed,
@@ -456,18 +677,26 @@ def run_ours(args):
                        "algorithmic_gflop_per_step": step_flop * global_batch / 1e9,
                        "tensor_core_path": bool(l.nrs_has_tensor_core_path())},
             "loss": loss,
-            "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
+            "e2e": {"value": per_s(ms_e2e), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": x_bytes + t_bytes, "d2h_bytes_per_step": 4 * world,
-                    "api": "nrs_trainer_stage_next + nrs_trainer_step_staged: the copy of batch i+1 overlaps step i",
-                    "unpipelined_value": global_batch * args.steps / (ms_e2e_plain / 1e3),
-                    "unpipelined_api": "nrs_trainer_step: copy, step and loss read-back in sequence"},
+                    "windows": {"n": len(e2e_windows), "statistic": "median", "value_min": per_s(max(e2e_windows)),
+                                "value_max": per_s(min(e2e_windows))},
+                    "api": "nrs_trainer_stage_next%s + nrs_trainer_step_staged: the copy of batch i+1 overlaps step i" % ("_tokens" if tokens else ""),
+                    "unpipelined_value": per_s(ms_e2e_plain),
+                    "unpipelined_api": "nrs_trainer_step%s: copy, step and loss read-back in sequence" % ("_tokens" if tokens else "")},
             "gpu_launches": launches * world,
             "clocks": clk.summary(),
             "roofline": {"bound": "tensor", "kernel": fam, "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
                          "frac": achieved / tf32_peak if tf32_peak else None,
                          **ncu_traffic(args.workload, args.math, fam, batch),
                          "peak_source": f"{peaks['source']}: sustained bf16 cuBLAS / 2 (dense TF32 runs at half the bf16 "
-                                        f"rate); 3xTF32 issues 3x the algorithmic FLOP counted in `achieved`",
+                                        f"rate); {args.math} issues {issue:.0f}x the algorithmic FLOP counted in `achieved`",
+                         "issued_tflops": achieved * issue,
+                         "frac_issued_of_peak": achieved * issue / tf32_peak if tf32_peak else None,
+                         "tf32_umma_peak_tflops": umma.value,
+                         "frac_issued_of_umma_peak": achieved * issue / umma.value if umma.value else None,
+                         "tf32_umma_peak_source": "measured in this run: back-to-back tcgen05.mma.kind::tf32 128x256x8 from "
+                                                  "shared memory on every SM (nrs_measure_tf32_umma_peak)",
                          "launch_ms_avg": f["ms"] / f["calls"] if f["calls"] else None, "calls": f["calls"],
                          "all_contractions_tflops": (contraction_work / (contraction_ms / 1e3) / 1e12) if contraction_ms else None,
                          "families_ms_per_step": {k: prof[k]["ms"] / bracketed for k in prof},
@@ -477,103 +706,21 @@ def run_ours(args):
                          if prof["batchnorm"]["ms"] > 0 else None,
                          "hbm_peak_gbs": peaks["hbm_gbs"]},
         }
-        if world == 1 and args.workload == "vgg_cifar":
+        if dp_check:
+            line["dp_check"] = dp_check
+        if world == 1 and args.workload == "vgg_cifar" and not args.no_microbench:
             line["conv_microbench"] = conv_microbench(ctx, stream)
             line["batchnorm_microbench"] = batchnorm_microbench(ctx, stream, peaks["hbm_gbs"])
+            line["hbm_microbench"] = hbm_microbench(ctx, stream, peaks["hbm_gbs"])
         if world == 1 and not args.no_cpu_baseline:
             r = cpu_reference_run(args.workload, 1, 1, min_seconds=10.0)
-            line["cpu_baseline"] = {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "port",
-                                    "sample": r["sample"]}
+            line["cpu_baseline"] = cpu_baseline_entry(r)
+            line["cpu_baseline"]["fast"] = cpu_fast_forward(args.workload)
         print(json.dumps(line), flush=True)
     tr.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-
-
-def run_transformer_lm(args):
-    """The transformer language-model configuration (a parity configuration, not the headline): token embedding + positional
-    encoding + 2 post-LN transformer blocks (GELU feed-forward, causal attention) + vocabulary head +
-    cross-entropy + AdamW at batch 32, sequence 128, vocabulary 1000, d_model 256, 8 heads, d_ff 1024,
-    driven op by op through the node-level C ABI the way the reference's examples drive its API."""
-    import numpy as np
-    import torch
-    from neuralrs_b200 import _lib, cuda
-    from neuralrs_b200.cuda import Node, backward_graph, graph, loss, nn, optim
-    from neuralrs_b200.cuda import runtime as gpu
-    B, S, V, D, H, FF, NB = 32, 128, 1000, 256, 8, 1024, 2
-    ctx = cuda.default_context()
-    ctx.set_math_mode(MATH[args.math])
-    rng = np.random.default_rng(1238)
-
-    def on_gpu(a):
-        n = Node.new(np.ascontiguousarray(a, np.float32), list(np.shape(a)))
-        gpu.to_cuda(n)
-        return n
-    mk = lambda *sh: rng.standard_normal(sh).astype(np.float32) / np.sqrt(sh[0])
-    emb = on_gpu(rng.standard_normal((V, D)).astype(np.float32) * 0.5)
-    blocks = []
-    for _ in range(NB):
-        w = {k: on_gpu(mk(D, D)) for k in ("q", "k", "v", "o")}
-        mha = nn.MultiHeadAttention(w["q"], w["k"], w["v"], w["o"], D, H, True)
-        blocks.append(nn.TransformerBlock(mha, nn.LayerNorm(on_gpu(np.ones(D)), on_gpu(np.zeros(D)), 1e-5),
-                                          nn.LayerNorm(on_gpu(np.ones(D)), on_gpu(np.zeros(D)), 1e-5),
-                                          nn.Linear(on_gpu(mk(D, FF)), on_gpu(np.zeros(FF))),
-                                          nn.Linear(on_gpu(mk(FF, D)), on_gpu(np.zeros(D))), D, FF, _lib.ACT_GELU))
-    head_w, head_b = on_gpu(mk(D, V)), on_gpu(np.zeros(V))
-    params = [emb] + [q for blk in blocks for q in blk.parameters()] + [head_w, head_b]
-    embedding, pe = nn.Embedding(emb, V, D), nn.PositionalEncoding(D, S)
-    opt = optim.AdamW(1e-3, 0.9, 0.999, 1e-8, 1e-4)
-    batches = []
-    for _ in range(4):
-        ids = rng.integers(0, V, (B, S))
-        onehot = np.zeros((B * S, V), np.float32)
-        onehot[np.arange(B * S), np.roll(ids, -1, axis=1).ravel()] = 1
-        batches.append((ids, on_gpu(onehot)))
-
-    def step(i):
-        ids, target = batches[i % len(batches)]
-        gpu.zero_grad(params)
-        h = pe.forward(embedding.forward_batch(ids))
-        for blk in blocks:
-            h = blk.forward(h)
-        logits = graph.add(graph.matmul(graph.reshape(h, [B * S, D]), head_w), head_b)
-        value = loss.cross_entropy(logits, target)     # reads the loss back, as the reference's API does
-        loss.cross_entropy_backward(logits, target)
-        backward_graph(logits)
-        opt.step(params)
-        return value
-
-    l = _lib.lib()
-    for i in range(max(3, args.warmup)):
-        step(i)
-    l.nrs_sync(ctx.h)
-    launches0 = l.nrs_launch_count(ctx.h)
-    clk = ClockSampler(0)
-    with clk:                      # entering and leaving the sampler takes time of its own: keep it outside dt
-        t0 = time.perf_counter()
-        for i in range(args.steps):
-            last = step(i)
-        l.nrs_sync(ctx.h)
-        dt = time.perf_counter() - t0
-    launches = l.nrs_launch_count(ctx.h) - launches0
-    # forward FLOP per token: QKV/O projections 4*2*D*D, scores and mixing 2*2*S*D, feed-forward 2*2*D*FF per block; head 2*D*V
-    fwd = NB * (8.0 * D * D + 4.0 * S * D + 4.0 * D * FF) + 2.0 * D * V
-    line = {"metric": METRIC, "value": B * args.steps / dt, "unit": "samples/s", "n_gpus": 1, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "transformer_lm", "global_batch": B, "seq_len": S, "vocab": V, "d_model": D, "heads": H,
-                       "d_ff": FF, "blocks": NB, "math": args.math, "tokens_per_s": B * S * args.steps / dt,
-                       "algorithmic_gflop_per_step": 3.0 * fwd * B * S / 1e9,
-                       "timing": "host wall clock around K steps with a device sync on both sides: every step is "
-                                 "driven op by op from Python and reads its loss back, so this IS the end-to-end number",
-                       "l2": "4 token batches rotated; the working set of a step (activations of 2 blocks) exceeds no cache "
-                             "claim: this configuration is launch-bound"},
-            "loss": float(last),
-            "e2e": {"value": B * args.steps / dt, "unit": "samples/s", "h2d_bytes_per_step": B * S * 4, "d2h_bytes_per_step": 4},
-            "gpu_launches": int(launches), "clocks": clk.summary(),
-            "roofline": None, "cpu_baseline": None}
-    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -582,13 +729,7 @@ def main():
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 500), __file__] + sys.argv[1:]
         raise SystemExit(subprocess.call(cmd))
-    if args.workload == "transformer_lm":
-        if args.impl == "reference" or args.gpus > 1:
-            print(json.dumps({"impl": args.impl, "unavailable": "transformer_lm is a single-GPU parity configuration; "
-                                                               "the reference arm and N > 1 run the default workload"}))
-            return
-        run_transformer_lm(args)
-    elif args.impl == "reference":
+    if args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -102,6 +102,12 @@ int nrs_selftest_bounded_wait(nrs_ctx* ctx, int64_t limit_clocks);
  * several GPUs of one process each get theirs.  Returns 0 when that bookkeeping behaves. */
 int nrs_selftest_smem_attr_bookkeeping(void);
 
+/* Measures the tensor pipe's dense-TF32 rate on this device (no reference counterpart): every SM
+ * issues tcgen05.mma.kind::tf32 (128 x 256 x 8) back to back on operands resident in shared memory
+ * for a few milliseconds; the result is what the contraction kernels' tensor-core roofline is
+ * quoted against.  Waits for the stream. */
+int nrs_measure_tf32_umma_peak(nrs_ctx* ctx, double* tflops_out);
+
 int nrs_profile_enable(nrs_ctx* ctx, int on);
 int nrs_profile_reset(nrs_ctx* ctx);
 int nrs_profile_get(nrs_ctx* ctx, int kind, double* ms_out, double* work_out, uint64_t* calls_out);

@@ -153,6 +153,73 @@ extern "C" int nrs_selftest_bounded_wait(nrs_ctx* ctx, int64_t limit_clocks) {
   return NRS_OK;
 }
 
+namespace {
+// Back-to-back tcgen05.mma.kind::tf32 (M = 128, N = 256, K = 8) on operands that never leave shared
+// memory: the tensor pipe's own rate, with no TMA traffic and no epilogue.  One issuing thread per CTA,
+// one CTA per SM; every wait is bounded.
+__global__ void __launch_bounds__(128, 1) umma_rate_kernel(int iters, int* __restrict__ err_flag) {
+  extern __shared__ uint8_t umma_rate_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(umma_rate_smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  for (int i = threadIdx.x; i < 48 * 1024 / 4; i += blockDim.x) reinterpret_cast<float*>(smem)[i] = 1.0f;
+  if (threadIdx.x == 0) { tc::mbar_init(&bar, 1); tc::fence_barrier_init(); }
+  if (threadIdx.x < 32) { tc::tmem_alloc(&tmem_slot, 512); tc::tmem_relinquish(); }
+  tc::fence_proxy_async();
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (threadIdx.x == 0) {
+    const uint32_t idesc = tc::make_idesc_tf32(128, 256, false, false);
+    const uint32_t a = tc::smem_u32(smem), b = a + 16384;     // A: 128 rows x 128 B; B: 256 rows x 128 B
+    for (int i = 0; i < iters; ++i) {
+      const uint32_t koff = (uint32_t)(i & 3) * 32u;            // the four K-steps of a 32-element K block
+      tc::umma_tf32(tmem + ((i & 1) ? 256u : 0u), tc::make_smem_desc_sw128(a + koff, 16, 1024),
+                    tc::make_smem_desc_sw128(b + koff, 16, 1024), idesc, 1);
+    }
+    tc::umma_commit(&bar);
+    if (!tc::mbar_wait(&bar, 0)) atomicExch(err_flag, tc::kErrMmaWait);
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x < 32) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem, 512); }
+}
+}  // namespace
+
+extern "C" int nrs_measure_tf32_umma_peak(nrs_ctx* ctx, double* tflops_out) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, tflops_out != nullptr, NRS_ERR_ARG, "nrs_measure_tf32_umma_peak: null output");
+  *tflops_out = 0.0;
+  int* err = nullptr;
+  int st = nrs_err_flag(ctx, &err);
+  if (st != NRS_OK) return st;
+  constexpr int kSmem = 64 * 1024, kIters = 40000;          // ~2.6 ms at 128 clocks per UMMA
+  static NrsSmemAttr attr;
+  NRS_ENSURE_SMEM(ctx, attr, umma_rate_kernel, kSmem);
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  NRS_CUDA(ctx, cudaEventCreate(&e0));
+  NRS_CUDA(ctx, cudaEventCreate(&e1));
+  float best_ms = 0.0f;
+  for (int rep = 0; rep < 4; ++rep) {                        // the first launch warms up
+    cudaEventRecord(e0, ctx->stream);
+    umma_rate_kernel<<<ctx->sm_count, 128, kSmem, ctx->stream>>>(kIters, err);
+    ctx->launches++;
+    cudaEventRecord(e1, ctx->stream);
+    if (cudaEventSynchronize(e1) != cudaSuccess) break;
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (rep > 0 && (best_ms == 0.0f || ms < best_ms)) best_ms = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  NRS_CUDA(ctx, cudaGetLastError());
+  st = nrs_check_device_error(ctx);
+  if (st != NRS_OK) return st;
+  if (best_ms > 0.0f) *tflops_out = 2.0 * 128 * 256 * 8 * (double)kIters * ctx->sm_count / (best_ms * 1e-3) / 1e12;
+  return NRS_OK;
+}
+
 int nrs_tc_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n, int k, const float* a, const float* b,
                 float* c, const float* bias, int act, float beta) {
   if (!tc::tensor_map_encoder()) return NRS_ERR_UNSUPPORTED;

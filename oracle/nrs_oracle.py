@@ -39,6 +39,40 @@ def _load():
     return _lib
 
 
+def host_cores() -> int:
+    return int(_load().nrs_oracle_host_cores())
+
+
+def get_threads() -> int:
+    return int(_load().nrs_oracle_get_threads())
+
+
+def set_threads(n: int) -> None:
+    """Threads of the OpenMP loops (the reference's Rayon pools); overrides OMP_NUM_THREADS."""
+    _load().nrs_oracle_set_threads(int(n))
+
+
+def matmul_simd(a, b):
+    """matmul_simd (src/ops/simd.rs:42-77): the reference's AVX2 + Rayon forward matmul."""
+    a, b = _f(a), _f(b)
+    m, k = a.shape
+    n = b.shape[1]
+    c = np.empty((m, n), np.float32)
+    _load().nrs_oracle_matmul_simd(_p(a), _p(b), _p(c), m, k, n)
+    return c
+
+
+def conv2d_im2col(x, w, b, stride=1, pad=0):
+    """conv2d_im2col (src/ops/im2col.rs:59-98): the reference's im2col + matmul forward convolution."""
+    x, w, b = _f(x), _f(w), _f(b)
+    n, ci, h, wd = x.shape
+    co, _, kh, kw = w.shape
+    oh, ow = (h + 2 * pad - kh) // stride + 1, (wd + 2 * pad - kw) // stride + 1
+    y = np.empty((n, co, oh, ow), np.float32)
+    _load().nrs_oracle_conv2d_im2col(_p(x), _p(w), _p(b), _p(y), n, ci, h, wd, co, kh, kw, stride, pad)
+    return y
+
+
 def _f(a):
     return np.ascontiguousarray(np.asarray(a, dtype=np.float32))
 

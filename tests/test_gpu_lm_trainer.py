@@ -166,7 +166,7 @@ def test_operator_level_buckets_on_one_rank(gpu_ctx, oracle64):
         dp = None
         if use_dp:
             dp = cuda.DataParallel(0, 1, None, 8, ctx=gpu_ctx)
-            dp.register(ps, 64)                       # tiny buckets: one per tensor
+            dp.register(ps, 4)                        # tiny buckets: one per tensor
             assert dp.bucket_count == 5
         gpu.zero_grad(ps)
         h = graph.relu(graph.add(graph.matmul(gx, ps[0]), ps[1]))

@@ -227,3 +227,35 @@ def test_gelu_relu_layernorm_softmax_backward_against_torch(oracle64):
     ys = oracle64.softmax_fwd(x)
     assert np.abs(oracle64.softmax_bwd(ys, g) - xt.grad.numpy()).max() < 1e-6
     assert rel_l2(oracle64.transpose_fwd(x), x.T) == 0
+
+
+def test_fast_cpu_kernels_match_the_naive_ones(oracle32):
+    """The reference's fast forward kernels (matmul_simd, conv2d_im2col), restated for the timed CPU
+    baseline, replaying the reference's own tests of them."""
+    from oracle import nrs_oracle as no
+    # tests/matmul_simd_test.rs:6-29 (tolerance 1e-3)
+    m, k, n = 5, 11, 7
+    a = ((np.arange(m * k) % 9).astype(np.float32) - 4.0) * np.float32(0.3)
+    b = ((np.arange(k * n) % 6).astype(np.float32) - 2.0) * np.float32(0.25)
+    naive = oracle32.matmul_fwd(a.reshape(m, k), b.reshape(k, n))
+    assert np.abs(no.matmul_simd(a.reshape(m, k), b.reshape(k, n)) - naive).max() < 1e-3
+    # tests/im2col_conv_test.rs:10-54 (tolerance 1e-4)
+    nb, ci, co, h, w = 2, 2, 3, 5, 5
+    wt = ((np.arange(co * ci * 9) % 7).astype(np.float32) - 3.0) * np.float32(0.1)
+    bias = np.arange(co, dtype=np.float32) * np.float32(0.5)
+    x = ((np.arange(nb * ci * h * w) % 11).astype(np.float32) - 5.0) * np.float32(0.2)
+    direct = oracle32.conv2d_fwd(x.reshape(nb, ci, h, w), wt.reshape(co, ci, 3, 3), bias, 1, 1)
+    fast = no.conv2d_im2col(x.reshape(nb, ci, h, w), wt.reshape(co, ci, 3, 3), bias, 1, 1)
+    assert fast.shape == direct.shape and np.abs(fast - direct).max() < 1e-4
+    # the known answers of tests/nn_conv_test.rs and nn_conv_padding_test.rs hold for the fast path too
+    y = no.conv2d_im2col(np.arange(1, 10, dtype=np.float32).reshape(1, 1, 3, 3), np.ones((1, 1, 2, 2), np.float32),
+                         np.zeros(1, np.float32), 1, 0)
+    assert y.ravel().tolist() == [12.0, 16.0, 24.0, 28.0]
+    y = no.conv2d_im2col(np.ones((1, 1, 3, 3), np.float32), np.ones((1, 1, 3, 3), np.float32), np.zeros(1, np.float32), 1, 1)
+    assert y.ravel().tolist() == [4, 6, 4, 6, 9, 6, 4, 6, 4]
+    # thread control used by the timed baselines
+    cores = no.host_cores()
+    no.set_threads(1)
+    assert no.get_threads() == 1
+    no.set_threads(cores)
+    assert no.get_threads() == cores
