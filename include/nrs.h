@@ -226,6 +226,15 @@ int nrs_layernorm_fwd(nrs_ctx* ctx, const float* x, const float* gamma, const fl
 int nrs_layernorm_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd,
                       const float* gamma, float* dx, float* dgamma, float* dbeta,
                       int rows, int f, int accumulate_dx, int accumulate_params);
+/* The residual add that precedes a LayerNorm in the transformer block
+ * (add + layernorm, src/cuda/nn/transformer_block.rs:33-34,41-42) folded into the same two
+ * kernels: forward normalises a + b without writing the sum; backward hands the one input
+ * gradient to both addends (da and db, each written or added to; either may be NULL). */
+int nrs_layernorm_residual_fwd(nrs_ctx* ctx, const float* a, const float* b, const float* gamma, const float* beta,
+                               float* y, float* xhat, float* istd, int rows, int f, float eps);
+int nrs_layernorm_residual_bwd(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd, const float* gamma,
+                               float* da, float* db, float* dgamma, float* dbeta, int rows, int f, int accumulate_da,
+                               int accumulate_db, int accumulate_params);
 /* softmax_forward / softmax_backward (src/cuda/graph/softmax.rs:12-35).  The
  * backward takes the forward OUTPUT y: dx (+)= y*(g - sum(y*g)). */
 int nrs_softmax_fwd(nrs_ctx* ctx, const float* x, float* y, int rows, int width);
@@ -349,6 +358,12 @@ int nrs_ce_bwd(nrs_ctx* ctx, const float* logits, const float* target, float* gr
 /* Both in one pass over the logits. */
 int nrs_ce_fwd_bwd(nrs_ctx* ctx, const float* logits, const float* target, float* loss_dev,
                    float* grad, int batch, int classes, int divisor);
+
+/* nrs_ce_fwd_bwd for targets given as one int32 class index per row instead of one-hot rows
+ * (the same values as running it on nrs_onehot's output: an index outside [0, classes) is an
+ * all-zero target row); the dense target tensor is neither built nor read. */
+int nrs_ce_fwd_bwd_indexed(nrs_ctx* ctx, const float* logits, const int32_t* labels, float* loss_dev, float* grad,
+                           int batch, int classes, int divisor);
 
 /* -------------------------------------------------------------- optimizer -- */
 

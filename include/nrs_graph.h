@@ -225,8 +225,8 @@ int nrs_trainer_step(nrs_trainer* t, const float* x_host, const float* target_ho
 int nrs_trainer_stage_next(nrs_trainer* t, const float* x_host, const float* target_host, int batch);
 int nrs_trainer_step_staged(nrs_trainer* t, float* loss_out);
 /* As nrs_trainer_stage_next with int32 class indices instead of one-hot rows
- * (batch * 4 bytes over the bus instead of batch * classes * 4); the step
- * expands them on the device (nrs_onehot). */
+ * (batch * 4 bytes over the bus instead of batch * classes * 4); the loss kernel
+ * reads them directly (nrs_ce_fwd_bwd_indexed). */
 int nrs_trainer_stage_next_indexed(nrs_trainer* t, const float* x_host, const int32_t* labels_host, int batch);
 /* On-device augmentation of staged [C,H,W] batches in training mode
  * (nrs_augment_flip_shift: shift by up to max_shift pixels, horizontal flip when
@@ -238,8 +238,8 @@ int nrs_trainer_step_device(nrs_trainer* t, const float* x_dev, const float* tar
                             float* loss_out);
 /* The same entry points for a token model (first layer NRS_LAYER_EMBEDDING): ids is int32
  * [batch, seq]; labels is int32 [batch*seq], the class of every position (for a language model
- * the next token), expanded on the device to the one-hot rows cross_entropy takes
- * (src/cuda/loss/cross_entropy.rs:74-98).  The loss is the mean over batch*seq rows.  An id outside
+ * the next token): the loss kernel reads the indices directly and gives the values of
+ * cross_entropy on the matching one-hot rows (src/cuda/loss/cross_entropy.rs:74-98).  The loss is the mean over batch*seq rows.  An id outside
  * the vocabulary is not dereferenced; the next call that waits returns NRS_ERR_ARG. */
 int nrs_trainer_forward_backward_tokens(nrs_trainer* t, const int32_t* ids_host, const int32_t* labels_host, int batch,
                                         float* loss_out);

@@ -207,6 +207,7 @@ int nrs_destroy(nrs_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   for (auto& kv : ctx->pool.free_blocks) cudaFree(kv.second);
   for (auto& kv : ctx->pool.live) cudaFree(kv.first);
+  nrs_weight_set_clear(ctx);
   if (ctx->workspace) cudaFree(ctx->workspace);
   for (int i = 0; i < NRS_WS_COUNT; ++i) if (ctx->ws_slot[i]) cudaFree(ctx->ws_slot[i]);
   if (ctx->err_flag) cudaFree(ctx->err_flag);

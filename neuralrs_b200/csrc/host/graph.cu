@@ -778,28 +778,52 @@ NodeP flatten(const NodeP& x) {
   return reshape(x, {x->shape[0], rest});
 }
 
-NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps) {
+// LayerNorm of x (residual == nullptr) or of x + residual with the add folded into the same kernels
+// (the add + layernorm pairs of src/cuda/nn/transformer_block.rs:33-34,41-42).  One backward launch
+// produces the input gradient(s) and, through per-block partial sums, dgamma / dbeta.
+static NodeP layernorm_impl(const NodeP& x, const NodeP& residual, const NodeP& gamma, const NodeP& beta, float eps) {
   require_gpu(x, "cuda layernorm: input");
   require_gpu(gamma, "cuda layernorm: gamma");
   require_gpu(beta, "cuda layernorm: beta");
+  if (residual) require_gpu(residual, "cuda layernorm: residual");
   if (x->shape.empty()) fail(NRS_ERR_SHAPE, "cuda layernorm: scalar input");
+  if (residual && residual->len() != x->len()) fail(NRS_ERR_SHAPE, "cuda layernorm: residual shape differs from the input's");
   nrs_ctx* ctx = x->ctx;
   const int f = (int)x->shape.back();
   if ((int)gamma->len() != f || (int)beta->len() != f) fail(NRS_ERR_SHAPE, "cuda layernorm: gamma/beta length mismatch");
   const int rows = (int)(x->len() / (size_t)f);
-  NodeP out = make_out(ctx, x->shape, {x, gamma, beta});
+  std::vector<NodeP> parents{x, gamma, beta};
+  if (residual) parents.push_back(residual);
+  NodeP out = make_out(ctx, x->shape, parents);
   float* xhat = dalloc(ctx, x->len());
   float* istd = dalloc(ctx, (size_t)rows);
   out->saved.push_back(xhat);
   out->saved.push_back(istd);
-  check(ctx, nrs_layernorm_fwd(ctx, x->data, gamma->data, beta->data, out->data, xhat, istd, rows, f, eps));
+  if (residual)
+    check(ctx, nrs_layernorm_residual_fwd(ctx, x->data, residual->data, gamma->data, beta->data, out->data, xhat, istd, rows, f, eps));
+  else
+    check(ctx, nrs_layernorm_fwd(ctx, x->data, gamma->data, beta->data, out->data, xhat, istd, rows, f, eps));
   Node* self = out.get();
-  out->backward_fn = [self, x, gamma, beta, xhat, istd, rows, f]() {
+  out->backward_fn = [self, x, residual, gamma, beta, xhat, istd, rows, f]() {
     nrs_ctx* ctx = self->ctx;
     const float* g = grad_in(self);
+    float *da = nullptr, *db = nullptr, *dg = nullptr, *dbt = nullptr;
+    int acc_a = 0, acc_b = 0, acc_p = 0;
     if (x->requires_grad) {
       GradTarget t = grad_target(x);
-      check(ctx, nrs_layernorm_bwd(ctx, g, xhat, istd, gamma->data, t.ptr, nullptr, nullptr, rows, f, t.accumulate, 0));
+      da = t.ptr;
+      acc_a = t.accumulate;
+    }
+    if (residual && residual->requires_grad) {
+      if (grad_root(residual.get()) == grad_root(x.get()) && da) {
+        // x + x: the one buffer receives the gradient twice
+        check(ctx, nrs_layernorm_residual_bwd(ctx, g, xhat, istd, gamma->data, da, nullptr, nullptr, nullptr, rows, f, acc_a, 0, 0));
+        acc_a = 1;
+      } else {
+        GradTarget t = grad_target(residual);
+        db = t.ptr;
+        acc_b = t.accumulate;
+      }
     }
     if (gamma->requires_grad || beta->requires_grad) {
       GradTarget tg = grad_target(gamma), tb = grad_target(beta);
@@ -808,10 +832,23 @@ NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps
         if (!tb.accumulate) check(ctx, nrs_memset_zero(ctx, tb.ptr, sizeof(float) * f));
         tg.accumulate = tb.accumulate = 1;
       }
-      check(ctx, nrs_layernorm_bwd(ctx, g, xhat, istd, gamma->data, nullptr, tg.ptr, tb.ptr, rows, f, 0, tg.accumulate));
+      dg = tg.ptr;
+      dbt = tb.ptr;
+      acc_p = tg.accumulate;
     }
+    if (da || db || dg)
+      check(ctx, nrs_layernorm_residual_bwd(ctx, g, xhat, istd, gamma->data, da, db, dg, dbt, rows, f, acc_a, acc_b, acc_p));
   };
   return out;
+}
+
+NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps) {
+  return layernorm_impl(x, nullptr, gamma, beta, eps);
+}
+
+NodeP layernorm_residual(const NodeP& x, const NodeP& residual, const NodeP& gamma, const NodeP& beta, float eps) {
+  if (!residual) fail(NRS_ERR_ARG, "cuda layernorm: null residual");
+  return layernorm_impl(x, residual, gamma, beta, eps);
 }
 
 // batchnorm (src/cuda/nn/batchnorm.rs:110-232) for [batch, features] and batchnorm2d
@@ -1032,6 +1069,17 @@ void cross_entropy_fused(const NodeP& pred, const NodeP& target, float* loss_dev
   Node* r = grad_root(pred.get());
   if (!r->grad) r->grad = dalloc(ctx, r->len());
   check(ctx, nrs_ce_fwd_bwd(ctx, pred->data, target->data, loss_dev, r->grad, batch, classes, divisor));
+  r->grad_valid = true;
+}
+
+void cross_entropy_fused_indexed(const NodeP& pred, const int32_t* labels_dev, float* loss_dev, int divisor) {
+  require_gpu(pred, "cuda ce: logits");
+  if (!labels_dev) fail(NRS_ERR_ARG, "cuda ce: null labels");
+  if (pred->shape.size() != 2) fail(NRS_ERR_SHAPE, "cuda ce: logits must be [rows, classes]");
+  nrs_ctx* ctx = pred->ctx;
+  Node* r = grad_root(pred.get());
+  if (!r->grad) r->grad = dalloc(ctx, r->len());
+  check(ctx, nrs_ce_fwd_bwd_indexed(ctx, pred->data, labels_dev, loss_dev, r->grad, (int)pred->shape[0], (int)pred->shape[1], divisor));
   r->grad_valid = true;
 }
 

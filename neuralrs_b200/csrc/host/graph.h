@@ -129,6 +129,9 @@ NodeP conv2d(const NodeP& x, const NodeP& w, const NodeP& b, size_t stride, size
 NodeP maxpool2d(const NodeP& x, size_t kernel, size_t stride, bool emit_planes = false);   // hint as in conv2d_act
 NodeP flatten(const NodeP& x);
 NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps);
+// layernorm(add(x, residual), ...) as one operator: the sum is never written, and the backward pass
+// hands the input gradient to both addends from one kernel.  Same values as the two-operator form.
+NodeP layernorm_residual(const NodeP& x, const NodeP& residual, const NodeP& gamma, const NodeP& beta, float eps);
 // batchnorm.rs / batchnorm2d.rs: running_mean / running_var are resident nodes updated in place when training
 NodeP batchnorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
                 const NodeP& running_var, float momentum, float eps, bool training);
@@ -207,6 +210,9 @@ void cross_entropy_backward(const NodeP& pred, const NodeP& target);
 // Both at once; the loss stays on the device (read it later with d2h) and the
 // mean is taken over `divisor` rows (the global batch under data parallelism).
 void cross_entropy_fused(const NodeP& pred, const NodeP& target, float* loss_dev, int divisor);
+// The same for targets given as one int32 class index per row (resident on the device): the values
+// of the one-hot form without building or reading the dense target tensor.
+void cross_entropy_fused_indexed(const NodeP& pred, const int32_t* labels_dev, float* loss_dev, int divisor);
 
 // ---- optim (src/cuda/optim/adamw.rs:43-144)
 struct AdamW {

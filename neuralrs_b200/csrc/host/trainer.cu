@@ -63,12 +63,12 @@ struct nrs_trainer {
   bool token_input = false;
   size_t rows_per_sample = 1;
   NodeP pos_table;                      // sinusoidal table of the embedding layer (no gradient)
-  float* onehot_dev = nullptr; size_t onehot_cap = 0;   // one-hot rows expanded from int32 labels
   // data parallel
   int rank = 0, world = 1, global_batch = 0;
   double dp_timeout_ms = 300000.0;      // joining the communicator, and every host wait of a step
   std::unique_ptr<nrs::DpGroup> dp;
   ~nrs_trainer() {
+    if (ctx && ctx->weight_set.owner == this) nrs_weight_set_clear(ctx);
     dp.reset();
     if (copy_stream) { cudaStreamSynchronize(copy_stream); cudaStreamDestroy(copy_stream); }
     for (Slot& sl : slots) {
@@ -85,7 +85,6 @@ struct nrs_trainer {
     pos_table.reset();
     flat.reset();
     if (ctx) {
-      if (onehot_dev) nrs_free(ctx, onehot_dev);
       if (loss_dev) nrs_free(ctx, loss_dev);
       if (x_dev) nrs_free(ctx, x_dev);
       if (t_dev) nrs_free(ctx, t_dev);
@@ -289,6 +288,55 @@ NodeP forward(nrs_trainer* t, const NodeP& x, const int32_t* ids_dev, size_t bat
   return h;
 }
 
+// The model's contraction weights, staged for the tensor-core kernels in one launch per step
+// (weight_set.cu) instead of one small launch per layer and pass.
+void stage_weights(nrs_trainer* t) {
+  nrs_ctx* ctx = t->ctx;
+  NrsWeightSet& ws = ctx->weight_set;
+  if (ws.owner != t || ws.mode != ctx->math_mode) {
+    std::vector<NrsWeightDesc> d;
+    auto linear = [&](const NodeP& w) {   // W[in,out]: transposed for x@W, as stored for dz@W^T
+      const int in = (int)w->shape[0], out = (int)w->shape[1];
+      if (in < 32 || out < 32) return;    // thin products run on the FFMA kernels
+      d.push_back(NrsWeightDesc{w->data, NRS_WF_LINEAR_T, out, in, 0, 0, 0});
+      d.push_back(NrsWeightDesc{w->data, NRS_WF_LINEAR_ROWS, in, out, 0, 0, 0});
+    };
+    size_t pi = 0;
+    bool first_contraction = true;
+    for (const nrs_layer_spec& l : t->layers) {
+      switch (l.kind) {
+        case NRS_LAYER_CONV:
+          if (l.d == 1 && l.a % 32 == 0 && l.b % 32 == 0) {
+            const NodeP& w = t->params[pi];
+            d.push_back(NrsWeightDesc{w->data, NRS_WF_CONV_FWD, 0, 0, l.b, l.a, l.c * l.c});
+            if (!first_contraction) d.push_back(NrsWeightDesc{w->data, NRS_WF_CONV_DGRAD, 0, 0, l.b, l.a, l.c * l.c});
+          }
+          first_contraction = false;
+          pi += 2;
+          break;
+        case NRS_LAYER_LINEAR:
+          linear(t->params[pi]);
+          first_contraction = false;
+          pi += 2;
+          break;
+        case NRS_LAYER_BATCHNORM:
+        case NRS_LAYER_LAYERNORM: pi += 2; break;
+        case NRS_LAYER_EMBEDDING: pi += 1; break;
+        case NRS_LAYER_TRANSFORMER_BLOCK:
+          for (int k : {0, 1, 2, 3, 8, 10}) linear(t->params[pi + k]);
+          first_contraction = false;
+          pi += 12;
+          break;
+        default: break;
+      }
+    }
+    nrs::check(ctx, nrs_weight_set_build(ctx, d.data(), (int)d.size()));
+    ws.owner = t;
+    ws.mode = ctx->math_mode;
+  }
+  nrs::check(ctx, nrs_weight_set_refresh(ctx));
+}
+
 // One step's inputs, all on the device: x (float samples) or ids (token models); targets as one-hot rows
 // or as int32 class indices (one per loss row).
 struct StepInput {
@@ -316,37 +364,25 @@ void run_step(nrs_trainer* t, const StepInput& in, bool optimize) {
     n->requires_grad = false;  // examples/cifar_cuda.rs:270: skips the first conv's data gradient
     return n;
   };
-  const float* target_dev = in.target;
-  if (!target_dev) {
-    if (!in.labels) fail(NRS_ERR_ARG, "trainer: no targets");
-    const size_t floats = rows * (size_t)t->classes;   // class indices -> the one-hot rows cross_entropy takes
-    if (floats > t->onehot_cap) {
-      if (t->onehot_dev) nrs_free(ctx, t->onehot_dev);
-      t->onehot_dev = nullptr;
-      t->onehot_cap = 0;
-      void* p = nullptr;
-      nrs::check(ctx, nrs_alloc(ctx, floats * sizeof(float), 0, &p));
-      t->onehot_dev = (float*)p;
-      t->onehot_cap = floats;
-    }
-    nrs::check(ctx, nrs_onehot(ctx, in.labels, t->onehot_dev, (int)rows, t->classes));
-    target_dev = t->onehot_dev;
-  }
+  if (!in.target && !in.labels) fail(NRS_ERR_ARG, "trainer: no targets");
   NodeP x;
   if (!t->token_input) {
     std::vector<size_t> xs{(size_t)batch};
     xs.insert(xs.end(), t->in_shape.begin(), t->in_shape.end());
     x = wrap(in.x, xs);
   }
-  NodeP target = wrap(target_dev, {rows, (size_t)t->classes});
 
   nrs::cuda::zero_grad(t->params);
+  stage_weights(t);
   NodeP logits = forward(t, x, in.ids, (size_t)batch);
   if (logits->shape.size() == 3) logits = nrs::cuda::reshape(logits, {rows, (size_t)t->classes});
   const bool dp = t->dp && t->world > 1 && optimize;
   const size_t divisor = (t->world > 1 ? (size_t)t->global_batch : (size_t)batch) * t->rows_per_sample;
   if (divisor > 2147483647u) fail(NRS_ERR_UNSUPPORTED, "trainer: more than 2^31-1 loss rows");
-  nrs::cuda::cross_entropy_fused(logits, target, t->loss_dev, (int)divisor);
+  // class indices feed the loss kernel directly: the values of the one-hot rows the reference's
+  // cross_entropy takes (src/cuda/loss/cross_entropy.rs:74-98) without the dense tensor
+  if (in.target) nrs::cuda::cross_entropy_fused(logits, wrap(in.target, {rows, (size_t)t->classes}), t->loss_dev, (int)divisor);
+  else nrs::cuda::cross_entropy_fused_indexed(logits, in.labels, t->loss_dev, (int)divisor);
 
   if (dp) {
     // Each bucket is all-reduced on the comm stream as soon as backward has produced it, and its
@@ -361,6 +397,7 @@ void run_step(nrs_trainer* t, const StepInput& in, bool optimize) {
     nrs::backward_graph(logits);
     if (optimize) t->opt->step(t->params);
   }
+  if (optimize) ctx->weight_set.fresh = false;   // the planes describe the weights before this update
 }
 
 void stage(nrs_trainer* t, float** buf, size_t* cap, const float* host, size_t floats) {

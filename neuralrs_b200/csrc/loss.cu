@@ -21,16 +21,17 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // One warp per row.  row_loss (optional) gets -sum_c t*(x - lse); grad (optional)
-// gets (softmax - t) * inv_div.
+// gets (softmax - t) * inv_div.  Scalar path (any width / alignment).
 __global__ void __launch_bounds__(256)
-ce_rows_kernel(const float* __restrict__ logits, const float* __restrict__ target,
+ce_rows_kernel(const float* __restrict__ logits, const float* __restrict__ target, const int32_t* __restrict__ labels,
                float* __restrict__ row_loss, float* __restrict__ grad, int batch, int classes, float inv_div) {
   NRS_PDL_PROLOGUE();
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   for (int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5); b < batch; b += gridDim.x * warps_per_block) {
     const float* row = logits + (size_t)b * classes;
-    const float* trow = target + (size_t)b * classes;
+    const float* trow = target ? target + (size_t)b * classes : nullptr;
+    const int label = labels ? labels[b] : -1;
     float mx = -INFINITY;
     for (int c = lane; c < classes; c += 32) mx = fmaxf(mx, row[c]);
     mx = warp_max(mx);
@@ -40,9 +41,70 @@ ce_rows_kernel(const float* __restrict__ logits, const float* __restrict__ targe
     const float lse = logf(se) + mx;
     float loss = 0.0f;
     for (int c = lane; c < classes; c += 32) {
-      const float xv = row[c], tv = trow[c];
+      const float xv = row[c], tv = trow ? trow[c] : (c == label ? 1.0f : 0.0f);
       loss += -tv * (xv - lse);
       if (grad) grad[(size_t)b * classes + c] = (expf(xv - mx) / se - tv) * inv_div;
+    }
+    if (row_loss) {
+      loss = warp_sum(loss);
+      if (lane == 0) row_loss[b] = loss;
+    }
+  }
+}
+
+// The same with the row held in registers: logits (and the one-hot row) are read once with 128-bit
+// loads (lane l takes float4s l, l+32, ...: 512 contiguous bytes per load instruction), every
+// exponential is evaluated once, the gradient is written once.  Rows of up to 1024 classes whose
+// width is a multiple of four.  With `labels` (int32 class per row) the dense one-hot tensor is not read.
+template <int VPL>
+__global__ void __launch_bounds__(256)
+ce_rows_vec_kernel(const float* __restrict__ logits, const float* __restrict__ target, const int32_t* __restrict__ labels,
+                   float* __restrict__ row_loss, float* __restrict__ grad, int batch, int classes, float inv_div) {
+  NRS_PDL_PROLOGUE();
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int c4 = classes >> 2;
+  for (int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5); b < batch; b += gridDim.x * warps_per_block) {
+    const size_t base = (size_t)b * classes;
+    float4 x[VPL], e[VPL];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int c = lane + 32 * k;
+      if (c < c4) {
+        x[k] = __ldcs(reinterpret_cast<const float4*>(logits + base) + c);
+        mx = fmaxf(mx, fmaxf(fmaxf(x[k].x, x[k].y), fmaxf(x[k].z, x[k].w)));
+      }
+    }
+    mx = warp_max(mx);
+    float se = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k)
+      if (lane + 32 * k < c4) {
+        e[k] = make_float4(expf(x[k].x - mx), expf(x[k].y - mx), expf(x[k].z - mx), expf(x[k].w - mx));
+        se += (e[k].x + e[k].y) + (e[k].z + e[k].w);
+      }
+    se = warp_sum(se);
+    const float lse = logf(se) + mx;
+    const int label = labels ? labels[b] : -1;
+    float loss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int c = lane + 32 * k;
+      if (c < c4) {
+        float4 t;
+        if (target) {
+          t = __ldcs(reinterpret_cast<const float4*>(target + base) + c);
+        } else {
+          const int d = label - 4 * c;     // position of the label inside this float4, if any
+          t = make_float4(d == 0 ? 1.0f : 0.0f, d == 1 ? 1.0f : 0.0f, d == 2 ? 1.0f : 0.0f, d == 3 ? 1.0f : 0.0f);
+        }
+        loss += (-t.x * (x[k].x - lse) + -t.y * (x[k].y - lse)) + (-t.z * (x[k].z - lse) + -t.w * (x[k].w - lse));
+        if (grad)
+          __stcs(reinterpret_cast<float4*>(grad + base) + c,
+                 make_float4((e[k].x / se - t.x) * inv_div, (e[k].y / se - t.y) * inv_div, (e[k].z / se - t.z) * inv_div,
+                             (e[k].w / se - t.w) * inv_div));
+      }
     }
     if (row_loss) {
       loss = warp_sum(loss);
@@ -68,7 +130,7 @@ ce_mean_kernel(const float* __restrict__ row_loss, float* __restrict__ loss_dev,
   }
 }
 
-int run_ce(nrs_ctx* ctx, const char* who, const float* logits, const float* target, float* loss_dev,
+int run_ce(nrs_ctx* ctx, const char* who, const float* logits, const float* target, const int32_t* labels, float* loss_dev,
            float* row_loss, float* grad, int batch, int classes, int divisor) {
   NRS_REQUIRE(ctx, batch >= 0 && classes > 0, NRS_ERR_SHAPE, "%s: bad shape [%d,%d]", who, batch, classes);
   NRS_REQUIRE(ctx, divisor > 0, NRS_ERR_ARG, "%s: divisor must be positive", who);
@@ -76,7 +138,7 @@ int run_ce(nrs_ctx* ctx, const char* who, const float* logits, const float* targ
     if (loss_dev) NRS_CUDA(ctx, cudaMemsetAsync(loss_dev, 0, sizeof(float), ctx->stream));
     return NRS_OK;
   }
-  NRS_REQUIRE(ctx, logits && target, NRS_ERR_ARG, "%s: null tensor", who);
+  NRS_REQUIRE(ctx, logits && (target || labels), NRS_ERR_ARG, "%s: null tensor", who);
   float* rl = row_loss;
   if (loss_dev && !rl) {
     void* ws = nullptr;
@@ -87,7 +149,17 @@ int run_ce(nrs_ctx* ctx, const char* who, const float* logits, const float* targ
   const float inv_div = 1.0f / (float)divisor;
   int blocks = (batch + 7) / 8;
   if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
-  NRS_PDL_LAUNCH(ce_rows_kernel, blocks, 256, 0, ctx->stream, logits, target, rl, grad, batch, classes, inv_div);
+  const bool vec = classes % 4 == 0 && classes <= 1024 &&
+                   ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(target) | reinterpret_cast<uintptr_t>(grad)) & 15) == 0;
+  if (vec && classes <= 128) {
+    NRS_PDL_LAUNCH(ce_rows_vec_kernel<1>, blocks, 256, 0, ctx->stream, logits, target, labels, rl, grad, batch, classes, inv_div);
+  } else if (vec && classes <= 512) {
+    NRS_PDL_LAUNCH(ce_rows_vec_kernel<4>, blocks, 256, 0, ctx->stream, logits, target, labels, rl, grad, batch, classes, inv_div);
+  } else if (vec) {
+    NRS_PDL_LAUNCH(ce_rows_vec_kernel<8>, blocks, 256, 0, ctx->stream, logits, target, labels, rl, grad, batch, classes, inv_div);
+  } else {
+    NRS_PDL_LAUNCH(ce_rows_kernel, blocks, 256, 0, ctx->stream, logits, target, labels, rl, grad, batch, classes, inv_div);
+  }
   NRS_LAUNCHED(ctx);
   if (loss_dev) {
     NRS_PDL_LAUNCH(ce_mean_kernel, 1, 1024, 0, ctx->stream, rl, loss_dev, batch, inv_div);
@@ -104,21 +176,29 @@ int nrs_ce_fwd(nrs_ctx* ctx, const float* logits, const float* target, float* lo
                int batch, int classes, int divisor) {
   NRS_REQUIRE_CTX(ctx);
   NRS_REQUIRE(ctx, loss_dev || row_loss, NRS_ERR_ARG, "nrs_ce_fwd: no output requested");
-  return run_ce(ctx, "nrs_ce_fwd", logits, target, loss_dev, row_loss, nullptr, batch, classes, divisor);
+  return run_ce(ctx, "nrs_ce_fwd", logits, target, nullptr, loss_dev, row_loss, nullptr, batch, classes, divisor);
 }
 
 int nrs_ce_bwd(nrs_ctx* ctx, const float* logits, const float* target, float* grad, int batch, int classes,
                int divisor) {
   NRS_REQUIRE_CTX(ctx);
   NRS_REQUIRE(ctx, grad || batch == 0, NRS_ERR_ARG, "nrs_ce_bwd: null grad");
-  return run_ce(ctx, "nrs_ce_bwd", logits, target, nullptr, nullptr, grad, batch, classes, divisor);
+  return run_ce(ctx, "nrs_ce_bwd", logits, target, nullptr, nullptr, nullptr, grad, batch, classes, divisor);
 }
 
 int nrs_ce_fwd_bwd(nrs_ctx* ctx, const float* logits, const float* target, float* loss_dev, float* grad,
                    int batch, int classes, int divisor) {
   NRS_REQUIRE_CTX(ctx);
   NRS_REQUIRE(ctx, loss_dev && (grad || batch == 0), NRS_ERR_ARG, "nrs_ce_fwd_bwd: null output");
-  return run_ce(ctx, "nrs_ce_fwd_bwd", logits, target, loss_dev, nullptr, grad, batch, classes, divisor);
+  return run_ce(ctx, "nrs_ce_fwd_bwd", logits, target, nullptr, loss_dev, nullptr, grad, batch, classes, divisor);
+}
+
+int nrs_ce_fwd_bwd_indexed(nrs_ctx* ctx, const float* logits, const int32_t* labels, float* loss_dev, float* grad,
+                           int batch, int classes, int divisor) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, loss_dev && (grad || batch == 0), NRS_ERR_ARG, "nrs_ce_fwd_bwd_indexed: null output");
+  NRS_REQUIRE(ctx, labels || batch == 0, NRS_ERR_ARG, "nrs_ce_fwd_bwd_indexed: null labels");
+  return run_ce(ctx, "nrs_ce_fwd_bwd_indexed", logits, nullptr, labels, loss_dev, nullptr, grad, batch, classes, divisor);
 }
 
 }  // extern "C"

@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <map>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "nrs.h"
@@ -39,6 +40,9 @@ struct NrsPlanes {
   float* hi;
   float* lo;
   int split;
+  // Set for the planes of a 2-D tensor [rows][cols] (cols a multiple of 32) staged for a GEMM; zero for
+  // image planes, whose NHWC order is not the tensor's own row-major order.
+  int rows = 0, cols = 0;
 };
 
 // Extra work a convolution kernel can fold into the epilogue that writes `out` (keyed by the
@@ -58,6 +62,34 @@ struct NrsColsumRequest {
   float* partial;   // [cap_rows][channels]
   int cap_rows;
   int rows;         // out: rows written, 0 = not honoured
+};
+
+// Weight operand planes staged ahead of the contractions by a caller that knows its weights (the
+// trainer): see weight_set.cu.  Forms: convolution forward [co][tap*ci + ci] and data gradient
+// [ci][tap*co + co]; Linear W[in,out] transposed to [out][in] (B operand of x@W) and as stored
+// [in][out] (B operand of dz@W^T), rows padded to a multiple of 32 floats.
+enum NrsWeightForm { NRS_WF_CONV_FWD = 0, NRS_WF_CONV_DGRAD = 1, NRS_WF_LINEAR_T = 2, NRS_WF_LINEAR_ROWS = 3 };
+struct NrsWeightDesc {
+  const float* w;
+  int form;
+  int rows, K;        // linear forms: the DESTINATION's row count and reduction length
+  int co, ci, taps;   // convolution forms
+};
+struct NrsWeightPlanes {
+  float* hi;
+  float* lo;          // null unless 3xTF32
+  int rows, K, co, ci, taps;
+};
+struct NrsWeightSet {
+  void* storage = nullptr;
+  void* jobs_dev = nullptr;
+  int n_jobs = 0;
+  unsigned blocks = 0;
+  bool split = false;
+  bool fresh = false;   // staged since the weights last changed (the owner clears it when it updates them)
+  const void* owner = nullptr;   // whoever built the set (a trainer); a different owner rebuilds it
+  int mode = -1;                 // math mode it was built for
+  std::map<std::pair<const void*, int>, NrsWeightPlanes> planes;
 };
 
 struct nrs_ctx {
@@ -86,6 +118,7 @@ struct nrs_ctx {
   // the host graph makes them once per step for the image layer's forward pass and weight gradient
   // (`split`: bit 0 = residual plane present, bits 8.. = the padding they were made for).
   std::map<const void*, NrsPlanes> patch_hints;
+  NrsWeightSet weight_set;
   // Counter-based generator state of the dropout masks (dropout.cu): seed, and the next unused counter block.
   uint64_t rng_seed = 0, rng_offset = 0;
   // Optional per-family device timing (nrs_profile_*).
@@ -116,6 +149,20 @@ inline const NrsPlanes* nrs_planes_find(nrs_ctx* ctx, const void* src, bool spli
 }
 // Reads and clears the device error word (the stream must be idle); NRS_ERR_TIMEOUT if a kernel gave up a wait.
 int nrs_check_device_error(nrs_ctx* ctx);
+
+// Batched weight staging (weight_set.cu).  build: allocates planes for the described weights in the
+// context's current math mode (nothing in FP32 mode) and replaces any earlier set; refresh: one launch
+// that stages them all from the weights' current values; find: the planes of (w, form) when the set is
+// fresh and was built for the current mode, else null.
+int nrs_weight_set_build(nrs_ctx* ctx, const NrsWeightDesc* descs, int count);
+int nrs_weight_set_refresh(nrs_ctx* ctx);
+void nrs_weight_set_clear(nrs_ctx* ctx);
+inline const NrsWeightPlanes* nrs_weight_planes_find(nrs_ctx* ctx, const void* w, int form) {
+  const NrsWeightSet& ws = ctx->weight_set;
+  if (!ws.fresh || ws.n_jobs == 0 || ws.split != (ctx->math_mode == NRS_MATH_3XTF32) || ctx->math_mode == NRS_MATH_FP32) return nullptr;
+  auto it = ws.planes.find(std::make_pair(w, form));
+  return it == ws.planes.end() ? nullptr : &it->second;
+}
 
 #define NRS_REQUIRE_CTX(ctx) \
   do { if (!(ctx)) return nrs_fail(nullptr, NRS_ERR_ARG, "%s: null context", __func__); } while (0)

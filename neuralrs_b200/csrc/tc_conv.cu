@@ -228,11 +228,17 @@ int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
     st = nrs_tc_stage(ctx, p.act_src, (float*)a_hi, (float*)a_lo, p.a_h * p.a_w, p.a_ch, p.a_ch, p.n_img, img, img, true);
     if (st != NRS_OK) return st;
   }
-  st = nrs_ws_slot(ctx, NRS_WS_B_HI, w_plane * sizeof(float), &w_hi);
-  if (st == NRS_OK && split) st = nrs_ws_slot(ctx, NRS_WS_B_LO, w_plane * sizeof(float), &w_lo);
-  if (st != NRS_OK) return st;
-  st = nrs_tc_stage_conv_weight(ctx, p.w, (float*)w_hi, (float*)w_lo, p.co, p.ci, p.kh, p.kw, p.for_dgrad);
-  if (st != NRS_OK) return st;
+  const NrsWeightPlanes* wp = nrs_weight_planes_find(ctx, p.w, p.for_dgrad ? NRS_WF_CONV_DGRAD : NRS_WF_CONV_FWD);
+  if (wp && wp->co == p.co && wp->ci == p.ci && wp->taps == p.kh * p.kw) {   // staged ahead with the rest of the model's weights
+    w_hi = wp->hi;
+    w_lo = wp->lo;
+  } else {
+    st = nrs_ws_slot(ctx, NRS_WS_B_HI, w_plane * sizeof(float), &w_hi);
+    if (st == NRS_OK && split) st = nrs_ws_slot(ctx, NRS_WS_B_LO, w_plane * sizeof(float), &w_lo);
+    if (st != NRS_OK) return st;
+    st = nrs_tc_stage_conv_weight(ctx, p.w, (float*)w_hi, (float*)w_lo, p.co, p.ci, p.kh, p.kw, p.for_dgrad);
+    if (st != NRS_OK) return st;
+  }
 
   const int bn = p.n_ch_out % 128 == 0 ? 128 : (p.n_ch_out % 64 == 0 ? 64 : 32);
   if (extras != ctx->out_extras.end()) ctx->out_extras.erase(extras);   // honoured from here on

@@ -87,7 +87,26 @@ struct Operand {
 
 // Brings one operand into K-major planes.  stored_kmajor: memory is [rows][K]; else [K][rows].
 int prepare_operand(nrs_ctx* ctx, const float* src, int rows, int K, int batch, bool stored_kmajor, bool split,
-                    int ws_hi, int ws_lo, Operand* out) {
+                    int ws_hi, int ws_lo, Operand* out, bool is_weight) {
+  if (batch == 1) {
+    const int ldk = (K + 31) / 32 * 32;
+    // a weight staged ahead with the rest of the model's (weight_set.cu) ...
+    if (is_weight) {
+      const NrsWeightPlanes* wp = nrs_weight_planes_find(ctx, src, stored_kmajor ? NRS_WF_LINEAR_ROWS : NRS_WF_LINEAR_T);
+      if (wp && wp->rows == rows && wp->K == K) {
+        *out = Operand{wp->hi, wp->lo, ldk, ldk, (size_t)rows * ldk};
+        return NRS_OK;
+      }
+    }
+    // ... or an activation whose [rows][K] planes its producer or an earlier consumer left with the context
+    if (stored_kmajor && K == ldk) {
+      const NrsPlanes* ready = nrs_planes_find(ctx, src, split);
+      if (ready && ready->rows == rows && ready->cols == K) {
+        *out = Operand{ready->hi, ready->lo, ldk, ldk, (size_t)rows * ldk};
+        return NRS_OK;
+      }
+    }
+  }
   const bool direct = !split && stored_kmajor && (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
   if (direct) {
     *out = Operand{src, nullptr, K, K, (size_t)rows * K};
@@ -229,9 +248,9 @@ int nrs_tc_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n,
   // Batched operands read in place need 16-byte aligned batch strides.
   const bool split = ctx->math_mode == NRS_MATH_3XTF32;
   Operand A, B;
-  int st = prepare_operand(ctx, a, m, k, batch, /*stored_kmajor=*/!trans_a, split, NRS_WS_A_HI, NRS_WS_A_LO, &A);
+  int st = prepare_operand(ctx, a, m, k, batch, /*stored_kmajor=*/!trans_a, split, NRS_WS_A_HI, NRS_WS_A_LO, &A, false);
   if (st != NRS_OK) return st;
-  st = prepare_operand(ctx, b, n, k, batch, /*stored_kmajor=*/trans_b != 0, split, NRS_WS_B_HI, NRS_WS_B_LO, &B);
+  st = prepare_operand(ctx, b, n, k, batch, /*stored_kmajor=*/trans_b != 0, split, NRS_WS_B_HI, NRS_WS_B_LO, &B, true);
   if (st != NRS_OK) return st;
   if (batch > 1 && ((A.bstride % 4) || (B.bstride % 4))) return NRS_ERR_UNSUPPORTED;
   GemmPolicy pol{c, bias, act, beta, m, n, (size_t)m * n, false};
