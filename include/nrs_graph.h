@@ -133,6 +133,11 @@ int nrs_cross_entropy_backward(nrs_node* pred, nrs_node* target);
 
 /* autograd::node::backward_graph — src/autograd/node.rs:113-126. */
 int nrs_backward_graph(nrs_node* root);
+/* One node's own backward closure (what backward_graph calls for it, src/autograd/node.rs:121-124):
+ * lets a caller that keeps the reference's graph walk on its side of the boundary (a Rust
+ * `Node` whose backward_fn is this call) drive the same closures in its own topological order.
+ * A node without a closure (a leaf, a reshape) is a no-op. */
+int nrs_node_backward(nrs_node* n);
 
 /* cuda::optim::AdamW — src/cuda/optim/adamw.rs:54-143. */
 int nrs_adamw_new(nrs_ctx* ctx, float lr, float beta1, float beta2, float eps, float weight_decay, nrs_adamw** out);

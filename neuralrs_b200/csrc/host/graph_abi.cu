@@ -150,6 +150,13 @@ int nrs_read_grad(nrs_node* n, float* host_out) {
   });
 }
 
+int nrs_node_backward(nrs_node* n) {
+  NODE_OK(n);
+  return guarded(ctx_of(n), [&] {
+    if (n->p->backward_fn) n->p->backward_fn();
+  });
+}
+
 int nrs_zero_grad(nrs_node* const* params, int count) {
   nrs_ctx* ctx = count > 0 && params && params[0] ? ctx_of(params[0]) : nullptr;
   return guarded(ctx, [&] { nrs::cuda::zero_grad(gather(params, count)); });

@@ -127,3 +127,28 @@ def test_wide_mlp_layer_full_size_properties(gpu_ctx, oracle64):
     first = gw.get().copy()
     call(gpu_ctx, "nrs_gemm", 1, 0, k, n, m, dA, dDY, gw, None, _lib.ACT_NONE, 0.0)
     assert np.array_equal(gw.get(), first)
+
+
+@pytest.mark.parametrize("shape", [(256, 64, 32, 32, 128), (1024, 64, 32, 32, 64)],
+                         ids=["conv_microbench", "vgg_64to64_at_32x32_batch_1024"])
+def test_full_size_weight_gradient_slices_against_the_oracle(gpu_ctx, oracle64, shape):
+    """The weight gradient at the benchmark's own sizes, compared DIRECTLY with the oracle: dW[oc] depends only
+    on dy[:, oc], so the oracle computes a few output channels' slices (under 3 GFLOP) while the device computes
+    the whole tensor — a dropped split, a mis-ordered tap at a row-split boundary or any other error that the
+    scalar identity <w, dW> = <y, dy> cannot see shows up here.  Bias gradient likewise."""
+    n, ci, h, w, co = shape
+    rng = np.random.default_rng(n + co)
+    x = rng.standard_normal((n, ci, h, w), dtype=np.float32)
+    dy = rng.standard_normal((n, co, h, w), dtype=np.float32)
+    wt = np.zeros((co, ci, 3, 3), np.float32)          # not read by the weight gradient
+    dims = (n, ci, h, w, co, 3, 3, 1, 1)
+    gw, gb = Dev(gpu_ctx, shape=wt.shape), Dev(gpu_ctx, shape=(co,))
+    call(gpu_ctx, "nrs_conv2d_bwd", Dev(gpu_ctx, x), Dev(gpu_ctx, wt), Dev(gpu_ctx, dy), None, gw, gb, *dims, 0)
+    got_w, got_b = gw.get(), gb.get()
+    ocs = [0, co // 2 + 1, co - 1]
+    _, ref_w, ref_b = oracle64.conv2d_bwd(x, wt[ocs], np.ascontiguousarray(dy[:, ocs]), 1, 1, need_dx=False)
+    for k, oc in enumerate(ocs):
+        assert rel_l2(got_w[oc], ref_w[k]) <= 1e-4, f"dW[{oc}]"
+        # every tap of every input channel, not only the tensor's norm
+        assert np.abs(got_w[oc] - ref_w[k]).max() <= 1e-4 * np.abs(ref_w[k]).max(), f"dW[{oc}] elementwise"
+    assert rel_l2(got_b[ocs], ref_b) <= 1e-5

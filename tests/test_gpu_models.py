@@ -33,12 +33,13 @@ def run_parity(gpu_ctx, oracle64, cfg, batch, seed, fuse, mode, tol, uniform01=F
         assert abs(loss - loss_ref) <= tol * max(1.0, abs(loss_ref)), (loss, loss_ref)
         errs = [rel_l2(tr.get_grad(i), g) for i, g in enumerate(grads_ref)]
         if mode == _lib.MATH_TF32:
-            # Single-pass TF32 carries ~3e-4 of rounding noise per contraction.  The last
-            # layers stay within 1e-2; the gradient of the FIRST layers of a deep stack is a
-            # heavily cancelling sum over everything behind it and amplifies that noise, so it
-            # is bounded separately (the default 3xTF32 mode holds 1e-4 everywhere).
+            # Single-pass TF32 carries ~3e-4 of rounding noise per pre-activation, which flips ReLU
+            # masks and pooling winners near ties; with the device's own decisions the kernels hold
+            # 1e-2 on EVERY tensor (test_vgg_every_gradient_with_the_device_masks).  Here the oracle
+            # takes its own decisions, so the early layers carry the flipped elements' contribution:
+            # this looser bound is on (kernels + decision flips), labelled as such.
             assert max(errs[-4:]) <= tol, errs
-            assert max(errs) <= 0.15, errs
+            assert max(errs) <= 0.15, errs        # unpinned-mask bound
         else:
             assert max(errs) <= tol, errs
         # full steps: parameters after AdamW follow the oracle's trajectory
@@ -267,3 +268,105 @@ def test_checkpoint_resume_is_exact(gpu_ctx, tmp_path, ext):
             make().load_checkpoint(str(tmp_path / "size.safetensors"), names)
     a.close()
     b.close()
+
+
+@pytest.mark.parametrize("mode,tol", [(_lib.MATH_TF32, 1e-2), (_lib.MATH_3XTF32, 1e-4)], ids=["tf32", "3xtf32"])
+def test_vgg_every_gradient_with_the_device_masks(gpu_ctx, oracle64, mode, tol):
+    """The whole VGG-style model, every parameter gradient held to the mode's bar (1e-2 in the opt-in single-pass TF32
+    mode, 1e-4 in 3xTF32) with the two data-dependent DECISIONS taken out of the comparison: a pre-activation
+    within rounding error of zero can fall on the other side of the ReLU on the device, and two nearly equal
+    values in a pooling window can swap winners; one flipped element moves an early layer's gradient by far more
+    than the tolerance without any kernel being wrong.  The oracle's backward pass therefore uses the ReLU masks
+    and pooling winners the device used (read off its downloaded activations); the values it multiplies are its
+    own f64-accumulated ones.  The fraction of decisions that differ is bounded separately."""
+    from neuralrs_b200.cuda import Node, backward_graph, graph, loss, nn
+    from neuralrs_b200.cuda import runtime as gpu
+    cfg = models.VGG_CIFAR
+    layers = cfg["layers"]
+    batch = 8
+    params = models.he_init(layers, 1237)
+    rng = np.random.default_rng(1238)
+    for i in range(1, len(params), 2):
+        params[i] = (rng.standard_normal(params[i].shape) * 0.05).astype(np.float32)
+    x, t = models.synthetic_batch(cfg, batch, 1239)
+    gpu_ctx.set_math_mode(mode)
+    try:
+        def on_gpu(a):
+            n = Node.new(a, list(a.shape), gpu_ctx)
+            gpu.to_cuda(n)
+            return n
+        gp = [on_gpu(p) for p in params]
+        gx, gt = on_gpu(x), on_gpu(t)
+        gx.requires_grad = False
+        # device forward; keep every layer's output node
+        h, pi, dev_out = gx, 0, []
+        li = 0
+        while li < len(layers):
+            l = layers[li]
+            relu_next = li + 1 < len(layers) and layers[li + 1][0] == "relu"
+            if l[0] == "conv":
+                h = nn.conv2d_act(h, gp[pi], gp[pi + 1], l[4], l[5], 1 if relu_next else 0)
+                pi += 2
+            elif l[0] == "linear":
+                h = nn.linear_act(h, gp[pi], gp[pi + 1], 1 if relu_next else 0)
+                pi += 2
+            elif l[0] == "maxpool":
+                h = nn.maxpool2d(h, l[1], l[2])
+            elif l[0] == "flatten":
+                h = graph.reshape(h, [batch, len(h) // batch])
+            dev_out.append(h)
+            if l[0] in ("conv", "linear") and relu_next:
+                dev_out.append(h)      # the fused ReLU's output is the same node
+                li += 1
+            li += 1
+        g_loss = loss.cross_entropy(h, gt)
+        gpu.zero_grad(gp)
+        loss.cross_entropy_backward(h, gt)
+        backward_graph(h)
+        # oracle forward
+        acts = [x]
+        pi = 0
+        for l in layers:
+            a = acts[-1]
+            if l[0] == "conv":
+                acts.append(oracle64.conv2d_fwd(a, params[pi], params[pi + 1], l[4], l[5])); pi += 2
+            elif l[0] == "linear":
+                acts.append(oracle64.bias_add_fwd(oracle64.matmul_fwd(a, params[pi]), params[pi + 1])); pi += 2
+            elif l[0] == "relu":
+                acts.append(oracle64.relu_fwd(a))
+            elif l[0] == "maxpool":
+                acts.append(oracle64.maxpool_fwd(a, l[1], l[2])[0])
+            elif l[0] == "flatten":
+                acts.append(a.reshape(batch, -1))
+        c_loss = oracle64.ce_fwd(acts[-1], t)
+        assert abs(g_loss - c_loss) <= tol * max(1.0, abs(c_loss))
+        # oracle backward with the device's decisions
+        g = oracle64.ce_bwd(acts[-1], t)
+        grads = [None] * len(params)
+        pi = len(params)
+        flips = []
+        for li in range(len(layers) - 1, -1, -1):
+            l, a_in = layers[li], acts[li]
+            if l[0] == "relu":
+                dev = gpu.to_host(dev_out[li]).reshape(a_in.shape)       # post-ReLU on the device: > 0 where it passed
+                flips.append(np.mean((dev > 0) != (a_in > 0)))
+                g = oracle64.relu_bwd(dev, g)
+            elif l[0] == "maxpool":
+                dev_in = gpu.to_host(dev_out[li - 1]).reshape(a_in.shape)
+                am_dev = oracle64.maxpool_fwd(dev_in, l[1], l[2])[1]
+                flips.append(np.mean(am_dev != oracle64.maxpool_fwd(a_in, l[1], l[2])[1]))
+                g = oracle64.maxpool_bwd(g, am_dev, a_in.shape)
+            elif l[0] == "flatten":
+                g = g.reshape(a_in.shape)
+            elif l[0] == "linear":
+                pi -= 2
+                grads[pi + 1] = oracle64.bias_add_bwd(g)[1]
+                g, grads[pi] = oracle64.matmul_bwd(a_in, params[pi], g)
+            elif l[0] == "conv":
+                pi -= 2
+                g, grads[pi], grads[pi + 1] = oracle64.conv2d_bwd(a_in, params[pi], g, l[4], l[5], need_dx=li > 0)
+        errs = [rel_l2(gpu.read_grad(gp[i]), grads[i]) for i in range(len(params))]
+        assert max(errs) <= tol, errs                                 # EVERY tensor, first layers included
+        assert max(flips) <= (2e-2 if mode == _lib.MATH_TF32 else 1e-3), flips
+    finally:
+        gpu_ctx.set_math_mode(_lib.MATH_3XTF32)
