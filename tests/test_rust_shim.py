@@ -54,7 +54,11 @@ def test_hand_written_modules_call_declared_entry_points_with_the_right_arity():
     for f in sorted((SHIM / "src" / "cuda").glob("*.rs")):
         if f.name == "sys.rs":
             continue
+        types = {"nrs_ctx", "nrs_node", "nrs_adamw", "nrs_trainer", "nrs_dp", "nrs_checkpoint", "nrs_layer_spec", "nrs_named_tensor",
+                 "nrs_poll_fn"}
         for name in re.findall(r"sys::(nrs_\w+)\b", f.read_text()):      # also entry points passed as function pointers
+            if name in types:
+                continue
             assert name in decl, f"{f.name}: {name} is not declared in include/*.h"
             seen.add(name)
         for name, nargs in _calls(f.read_text()):
