@@ -415,6 +415,28 @@ def hbm_microbench(ctx, stream, hbm_peak_gbs, iters=10):
     return out
 
 
+def attention_microbench(ctx, stream, iters=20):
+    """The fused attention core at the language-model configuration's shape (batch 32, sequence 128, 8 heads of 32,
+    causal) through the raw C ABI: forward (scores, softmax, mixing) and backward (five products), tensor cores in
+    the TF32 modes.  Algorithmic FLOP: 4 S^2 d_head per (batch, head) forward, 10 S^2 d_head backward."""
+    import ctypes as C
+    import torch
+    from neuralrs_b200 import _lib
+    l = _lib.lib()
+    B, S, H, dh = 32, 128, 8, 32
+    g = torch.Generator(device="cuda").manual_seed(1242)
+    q, k, v, do = (torch.randn(B, S, H * dh, device="cuda", generator=g) for _ in range(4))
+    out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    probs = torch.empty(B * H, S, S, device="cuda")
+    P = lambda t: C.c_void_p(t.data_ptr())
+    fwd = _time_calls(ctx, stream, lambda: l.nrs_attention_fwd(ctx.h, P(q), P(k), P(v), P(out), P(probs), B, S, H, dh, 1), iters)
+    bwd = _time_calls(ctx, stream, lambda: l.nrs_attention_bwd(ctx.h, P(q), P(k), P(v), P(probs), P(do), P(dq), P(dk), P(dv),
+                                                               B, S, H, dh, 0, 0, 0), iters)
+    flop = 4.0 * S * S * dh * B * H
+    return {"shape": "batch 32, seq 128, 8 heads x 32, causal", "fwd_us": fwd * 1e3, "bwd_us": bwd * 1e3,
+            "fwd_tflops": flop / (fwd / 1e3) / 1e12, "bwd_tflops": 2.5 * flop / (bwd / 1e3) / 1e12}
+
+
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel of a family from
 # the `ncu --set full` captures summarised under profiles/: (bytes, per-GPU batch of the capture,
 # kernel).  Traffic of these kernels is proportional to the pixel count, so it is scaled to the
@@ -708,10 +730,13 @@ def run_ours(args):
         }
         if dp_check:
             line["dp_check"] = dp_check
+        if world == 1 and args.workload == "transformer_lm" and not args.no_microbench:
+            line["attention_microbench"] = attention_microbench(ctx, stream)
         if world == 1 and args.workload == "vgg_cifar" and not args.no_microbench:
             line["conv_microbench"] = conv_microbench(ctx, stream)
             line["batchnorm_microbench"] = batchnorm_microbench(ctx, stream, peaks["hbm_gbs"])
             line["hbm_microbench"] = hbm_microbench(ctx, stream, peaks["hbm_gbs"])
+            line["attention_microbench"] = attention_microbench(ctx, stream)
         if world == 1 and not args.no_cpu_baseline:
             r = cpu_reference_run(args.workload, 1, 1, min_seconds=10.0)
             line["cpu_baseline"] = cpu_baseline_entry(r)

@@ -246,6 +246,10 @@ int nrs_attention_fwd(nrs_ctx* ctx, const float* q, const float* k, const float*
   if (batch == 0) return NRS_OK;
   NRS_REQUIRE(ctx, q && k && v && out && probs, NRS_ERR_ARG, "nrs_attention_fwd: null tensor");
   NRS_REQUIRE(ctx, (long)batch * heads <= 2147483647L, NRS_ERR_UNSUPPORTED, "nrs_attention_fwd: too many (batch, head) pairs");
+  {
+    const int st = nrs_tc_attention_fwd(ctx, q, k, v, out, probs, batch, seq, heads, d_head, causal);   // tensor cores in the TF32 modes
+    if (st != NRS_ERR_UNSUPPORTED) return st;
+  }
   NRS_PDL_LAUNCH(attn_fwd_kernel, (unsigned)(batch * heads), 256, 0, ctx->stream, q, k, v, out, probs, seq, heads, d_head, causal,
                                                                       1.0f / sqrtf((float)d_head));
   NRS_LAUNCHED(ctx);
@@ -261,6 +265,10 @@ int nrs_attention_bwd(nrs_ctx* ctx, const float* q, const float* k, const float*
               "nrs_attention_bwd: seq %d / d_head %d outside the fused kernel's range (%d / %d)", seq, d_head, kMaxSeq, kMaxDh);
   if (batch == 0) return NRS_OK;
   NRS_REQUIRE(ctx, q && k && v && probs && dout && dq && dk && dv, NRS_ERR_ARG, "nrs_attention_bwd: null tensor");
+  {
+    const int st = nrs_tc_attention_bwd(ctx, q, k, v, probs, dout, dq, dk, dv, batch, seq, heads, d_head, acc_q, acc_k, acc_v);
+    if (st != NRS_ERR_UNSUPPORTED) return st;
+  }
   static NrsSmemAttr attr;
   NRS_ENSURE_SMEM(ctx, attr, attn_bwd_kernel, kBwdSmem);
   NRS_PDL_LAUNCH(attn_bwd_kernel, (unsigned)(batch * heads), 256, kBwdSmem, ctx->stream, q, k, v, probs, dout, dq, dk, dv, seq, heads, d_head,

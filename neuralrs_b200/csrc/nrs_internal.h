@@ -260,6 +260,12 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
 // Row-streaming variant for 3x3 / stride 1 / pad 1 (tc_wgrad_rows.cu); tried first.
 int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
                            int kh, int kw, int stride, int pad, int accumulate);
+// Fused attention core on the tensor cores (attention_tc.cu); NRS_ERR_UNSUPPORTED (no error text) outside its range.
+int nrs_tc_attention_fwd(nrs_ctx* ctx, const float* q, const float* k, const float* v, float* out, float* probs, int batch,
+                         int seq, int heads, int d_head, int causal);
+int nrs_tc_attention_bwd(nrs_ctx* ctx, const float* q, const float* k, const float* v, const float* probs, const float* dout,
+                         float* dq, float* dk, float* dv, int batch, int seq, int heads, int d_head, int acc_q, int acc_k,
+                         int acc_v);
 // Patch planes of x[n,ci,h,w] for a 3x3 / pad `pad` image layer (ci = 1 or 3): hi/lo [n*oh*ow][32].
 int nrs_smallc_patch_planes(nrs_ctx* ctx, const float* x, float* hi, float* lo, int n, int ci, int h, int wd, int pad);
 // Direct FFMA kernels for 3x3 stride-1 layers over 1 or 3 input channels (conv_smallc.cu).
