@@ -39,36 +39,51 @@ __device__ __forceinline__ void split4(const float4 v, float4* hi, float4* lo) {
   *lo = make_float4(v.x - hi->x, v.y - hi->y, v.z - hi->z, v.w - hi->w);
 }
 
-// tile[r][0..32) = src[r * ld + (0..dh)) for r < live, zeros elsewhere; hi/lo planes, K-major swizzled.
-__device__ __forceinline__ void stage_rows(uint8_t* hi, uint8_t* lo, const float* __restrict__ src, size_t ld, int live,
-                                           int dh) {
-  for (int idx = threadIdx.x; idx < kS * 8; idx += kThreads) {
-    const int r = idx >> 3, c = idx & 7;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < live && 4 * c < dh) v = *reinterpret_cast<const float4*>(src + (size_t)r * ld + 4 * c);
+// Thread r's row of a [seq][d_head] slice: src[r * ld + (0..32)), zeros beyond d_head and for r >= live.  All
+// eight 128-bit loads are issued before anything waits on them (the CTA has only four warps to hide latency).
+struct RowRegs {
+  float4 c[8];
+};
+__device__ __forceinline__ RowRegs load_row(const float* __restrict__ src, size_t ld, int live, int dh) {
+  RowRegs v;
+  const int r = threadIdx.x;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    v.c[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < live && 4 * c < dh) v.c[c] = *reinterpret_cast<const float4*>(src + (size_t)r * ld + 4 * c);
+  }
+  return v;
+}
+__device__ __forceinline__ void prefetch_row(const float* __restrict__ src, size_t ld, int live) {
+  if ((int)threadIdx.x < live) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + (size_t)threadIdx.x * ld));
+}
+
+// The row as row r of a K-major A / B tile [128][32] (hi/lo planes, 128-byte swizzle).
+__device__ __forceinline__ void store_row_tile(uint8_t* hi, uint8_t* lo, const RowRegs& v) {
+  const int r = threadIdx.x;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
     float4 h, l;
-    split4(v, &h, &l);
+    split4(v.c[c], &h, &l);
     const uint32_t off = sw_off(r, c);
     *reinterpret_cast<float4*>(hi + off) = h;
     *reinterpret_cast<float4*>(lo + off) = l;
   }
 }
 
-// The transpose of the same rows as a B operand [n_rows = d][K = 128 rows of src] in four K blocks of 32:
-// element (d, r) = src[r * ld + d]; rows d >= dh and columns r >= live are zero.
-__device__ __forceinline__ void stage_transposed(uint8_t* hi, uint8_t* lo, const float* __restrict__ src, size_t ld, int live,
-                                                 int dh, int n_rows) {
+// The row as COLUMN r of the transposed operand [n_rows = d][K = 128] in four K blocks of 32: element
+// (d, r) = row[d].  For a fixed d a warp writes 32 consecutive floats of row d: conflict-free.
+__device__ __forceinline__ void store_col_tile(uint8_t* hi, uint8_t* lo, const RowRegs& v, int n_rows) {
+  const int r = threadIdx.x;
   const uint32_t blk_bytes = (uint32_t)n_rows * 128u;
-  for (int idx = threadIdx.x; idx < kS * 8; idx += kThreads) {
-    const int c4 = idx / kS, r = idx - c4 * kS;       // consecutive threads take consecutive source rows: conflict-free stores
-    if (4 * c4 >= n_rows) continue;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < live && 4 * c4 < dh) v = *reinterpret_cast<const float4*>(src + (size_t)r * ld + 4 * c4);
-    const float e[4] = {v.x, v.y, v.z, v.w};
-    const int blk = r >> 5, kk = r & 31;
+  const int blk = r >> 5, kk = r & 31;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    if (4 * c >= n_rows) break;
+    const float e[4] = {v.c[c].x, v.c[c].y, v.c[c].z, v.c[c].w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int d = 4 * c4 + j;
+      const int d = 4 * c + j;
       const float h = tc::tf32_rn(e[j]);
       const uint32_t off = (uint32_t)blk * blk_bytes + sw_off(d, kk >> 2) + (uint32_t)(kk & 3) * 4u;
       *reinterpret_cast<float*>(hi + off) = h;
@@ -179,9 +194,12 @@ attn_fwd_tc_kernel(const float* __restrict__ q, const float* __restrict__ k, con
     tc::tmem_relinquish();
   }
   NRS_PDL_WAIT();
-  stage_rows(q_hi, q_lo, q + base, D, S, dh);
-  stage_rows(k_hi, k_lo, k + base, D, S, dh);
-  stage_transposed(vt_hi, vt_lo, v + base, D, S, dh, n_pv);
+  {
+    const RowRegs rq = load_row(q + base, D, S, dh), rk = load_row(k + base, D, S, dh), rv = load_row(v + base, D, S, dh);
+    store_row_tile(q_hi, q_lo, rq);
+    store_row_tile(k_hi, k_lo, rk);
+    store_col_tile(vt_hi, vt_lo, rv, n_pv);
+  }
   publish_smem();
   const uint32_t tmem = *tmem_slot;
   const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
@@ -307,9 +325,14 @@ attn_bwd_tc_kernel(const float* __restrict__ q, const float* __restrict__ k, con
     tc::tmem_relinquish();
   }
   NRS_PDL_WAIT();
-  stage_rows(x1_hi, x1_lo, dout + base, D, S, dh);
-  stage_rows(x2_hi, x2_lo, v + base, D, S, dh);
-  stage_transposed(x3_hi, x3_lo, dout + base, D, S, dh, n_d);
+  prefetch_row(k + base, D, S);               // read two and three phases from now
+  prefetch_row(q + base, D, S);
+  {
+    const RowRegs rdo = load_row(dout + base, D, S, dh), rv = load_row(v + base, D, S, dh);
+    store_row_tile(x1_hi, x1_lo, rdo);
+    store_row_tile(x2_hi, x2_lo, rv);
+    store_col_tile(x3_hi, x3_lo, rdo, n_d);
+  }
   float p[kS];
   {
     const float* prow = probs + ((size_t)bh * S + tid) * S;
@@ -374,7 +397,7 @@ attn_bwd_tc_kernel(const float* __restrict__ q, const float* __restrict__ k, con
   tc::tc_fence_after_sync();
   if (ok) {
     stage_row_regs(big_hi, big_lo, tid, p);   // dS
-    stage_transposed(x1_hi, x1_lo, k + base, D, S, dh, n_d);   // K^T
+    store_col_tile(x1_hi, x1_lo, load_row(k + base, D, S, dh), n_d);   // K^T
   }
   publish_smem();
   if (tid == 0 && ok) {   // dQ = dS K
@@ -408,7 +431,7 @@ attn_bwd_tc_kernel(const float* __restrict__ q, const float* __restrict__ k, con
   tc::tc_fence_after_sync();
   if (ok) {
     stage_col_regs(big_hi, big_lo, tid, p);   // dS^T
-    stage_transposed(x2_hi, x2_lo, q + base, D, S, dh, n_d);   // Q^T
+    store_col_tile(x2_hi, x2_lo, load_row(q + base, D, S, dh), n_d);   // Q^T
   }
   publish_smem();
   if (tid == 0 && ok) {   // dK = dS^T Q

@@ -163,6 +163,52 @@ static bool stage_planes(nrs_ctx* ctx, const float* src, const std::vector<size_
   return true;
 }
 
+// Row planes of a 2-D tensor [rows][cols] (cols a multiple of 32) for the tensor-core GEMMs: the layout
+// is the tensor's own, so the same planes serve it as the A operand of x@W and, read along the rows, as
+// an operand of the weight gradient x^T dz.  Stages them into fresh pool blocks and registers them with
+// the context under `src`; false (nothing allocated) when a tensor-core GEMM would not read them.
+static bool stage_planes_2d(nrs_ctx* ctx, const float* src, size_t rows, size_t cols, float** hi, float** lo) {
+  *hi = *lo = nullptr;
+  if (ctx->math_mode == NRS_MATH_FP32 || cols % 32 != 0 || rows == 0 || rows > 2147483647u || cols > 2147483647u) return false;
+  if (!tc::tensor_map_encoder() || ctx->plane_hints.count(src)) return false;
+  const bool split = ctx->math_mode == NRS_MATH_3XTF32;
+  *hi = dalloc(ctx, rows * cols);
+  if (split) *lo = dalloc(ctx, rows * cols);
+  check(ctx, nrs_tc_stage(ctx, src, *hi, *lo, (int)rows, (int)cols, (int)cols, 1, 0, 0, false));
+  NrsPlanes pl{*hi, *lo, split ? 1 : 0};
+  pl.rows = (int)rows;
+  pl.cols = (int)cols;
+  ctx->plane_hints[src] = pl;
+  return true;
+}
+
+// Planes of a backward pass's incoming gradient, staged once for the two products that read it
+// (dX = dz W^T and dW = x^T dz) and dropped when the scope ends.
+struct GradPlanes {
+  nrs_ctx* ctx;
+  const float* key = nullptr;
+  float *hi = nullptr, *lo = nullptr;
+  GradPlanes(nrs_ctx* c, const float* dz, size_t rows, size_t cols, bool wanted) : ctx(c) {
+    if (wanted && stage_planes_2d(c, dz, rows, cols, &hi, &lo)) key = dz;
+  }
+  ~GradPlanes() {
+    if (!key) return;
+    ctx->plane_hints.erase(key);
+    nrs_free(ctx, hi);
+    if (lo) nrs_free(ctx, lo);
+  }
+};
+
+// The forward operand's planes live with its node (both products that read x find them there).
+static void cache_planes_2d(const NodeP& x, size_t rows, size_t cols) {
+  if (x->planes_hi) return;
+  float *hi = nullptr, *lo = nullptr;
+  if (stage_planes_2d(x->ctx, x->data, rows, cols, &hi, &lo)) {
+    x->planes_hi = hi;
+    x->planes_lo = lo;
+  }
+}
+
 static bool planes_possible(nrs_ctx* ctx) {
   return ctx->math_mode != NRS_MATH_FP32 && tc::tensor_map_encoder();
 }
@@ -257,11 +303,14 @@ NodeP matmul(const NodeP& a, const NodeP& b) {
   if (b->shape[0] != a->shape[1]) fail(NRS_ERR_SHAPE, "cuda matmul: inner dims mismatch");
   nrs_ctx* ctx = a->ctx;
   NodeP out = make_out(ctx, {(size_t)m, (size_t)n}, {a, b});
+  const bool tensor_cores = nrs_gemm_on_tensor_cores(ctx, m, n, k);
+  if (tensor_cores && b->requires_grad) cache_planes_2d(a, (size_t)m, (size_t)k);   // read again by dB = A^T dC
   check(ctx, nrs_gemm(ctx, 0, 0, m, n, k, a->data, b->data, out->data, nullptr, NRS_ACT_NONE, 0.0f));
   Node* self = out.get();
-  out->backward_fn = [self, a, b, m, k, n]() {
+  out->backward_fn = [self, a, b, m, k, n, tensor_cores]() {
     nrs_ctx* ctx = self->ctx;
     const float* dc = grad_in(self);
+    GradPlanes dc_planes(ctx, dc, (size_t)m, (size_t)n, tensor_cores && a->requires_grad && b->requires_grad);
     if (a->requires_grad) {
       GradTarget t = grad_target(a);  // dA (+)= dC . B^T
       check(ctx, nrs_gemm(ctx, 0, 1, m, k, n, dc, b->data, t.ptr, nullptr, NRS_ACT_NONE, t.accumulate ? 1.0f : 0.0f));
@@ -986,6 +1035,8 @@ NodeP linear_act(const NodeP& x, const NodeP& w, const NodeP& b, int act) {
   nrs_ctx* ctx = x->ctx;
   const int m = (int)x->shape[0], k = (int)x->shape[1], n = (int)w->shape[1];
   NodeP out = make_out(ctx, {(size_t)m, (size_t)n}, {x, w, b});
+  const bool tensor_cores = nrs_gemm_on_tensor_cores(ctx, m, n, k);
+  if (tensor_cores && w->requires_grad) cache_planes_2d(x, (size_t)m, (size_t)k);   // read again by dW = x^T dz
   float* pre = nullptr;  // GELU's derivative needs the pre-activation
   if (act == NRS_ACT_GELU) {
     pre = dalloc(ctx, out->len());
@@ -996,7 +1047,7 @@ NodeP linear_act(const NodeP& x, const NodeP& w, const NodeP& b, int act) {
     check(ctx, nrs_gemm(ctx, 0, 0, m, n, k, x->data, w->data, out->data, b->data, act, 0.0f));
   }
   Node* self = out.get();
-  out->backward_fn = [self, x, w, b, pre, act, m, k, n]() {
+  out->backward_fn = [self, x, w, b, pre, act, m, k, n, tensor_cores]() {
     nrs_ctx* ctx = self->ctx;
     const float* dz = grad_in(self);
     float* tmp = nullptr;
@@ -1006,6 +1057,8 @@ NodeP linear_act(const NodeP& x, const NodeP& w, const NodeP& b, int act) {
       else check(ctx, nrs_gelu_bwd(ctx, pre, dz, tmp, self->len(), 0));
       dz = tmp;
     }
+    // dz feeds both dW = x^T dz and dX = dz W^T: its planes are made once
+    GradPlanes dz_planes(ctx, dz, (size_t)m, (size_t)n, tensor_cores && w->requires_grad && x->requires_grad);
     if (b->requires_grad) {
       GradTarget t = grad_target(b);
       check(ctx, nrs_sum_axis0(ctx, dz, t.ptr, m, n, t.accumulate));

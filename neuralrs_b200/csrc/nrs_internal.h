@@ -257,6 +257,9 @@ int nrs_tc_conv_dgrad(nrs_ctx* ctx, const float* w, const float* dy, float* dx, 
                       int kh, int kw, int stride, int pad, int accumulate);
 int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
                       int kh, int kw, int stride, int pad, int accumulate);
+bool nrs_gemm_on_tensor_cores(const nrs_ctx* ctx, int m, int n, int k);
+// C[m,n] (+)= A^T B, A stored [k][m], B stored [k][n], on the weight-gradient kernel (no transposes).
+int nrs_tc_gemm_tn(nrs_ctx* ctx, int m, int n, int k, const float* a, const float* b, float* c, int accumulate);
 // Row-streaming variant for 3x3 / stride 1 / pad 1 (tc_wgrad_rows.cu); tried first.
 int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
                            int kh, int kw, int stride, int pad, int accumulate);

@@ -16,6 +16,7 @@
 // conv2d im2col/col2out/out2mm/col2im (src/cuda/nn/conv.rs:27-149).
 #include "igemm_problems.cuh"
 #include "nrs_internal.h"
+#include "tc_common.cuh"
 
 namespace {
 
@@ -357,6 +358,12 @@ int check_conv_dims(nrs_ctx* ctx, const char* who, int n, int ci, int h, int wd,
 
 }  // namespace
 
+// True when nrs_gemm would run an [m,k] x [k,n] product (any transposes) on the tensor-core kernels.
+bool nrs_gemm_on_tensor_cores(const nrs_ctx* ctx, int m, int n, int k) {
+  return ctx->math_mode != NRS_MATH_FP32 && k >= 32 && m >= 64 && n >= 32 && !thin_gemm_applies(m, n, k) &&
+         tc::tensor_map_encoder() != nullptr;
+}
+
 extern "C" {
 
 int nrs_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int m, int n, int k, const float* a, const float* b,
@@ -370,6 +377,10 @@ int nrs_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int m, int n, int k, const 
   NrsProfScope prof(ctx, NRS_PROF_GEMM, 2.0 * m * n * k);
   if (k > 0 && thin_gemm_applies(m, n, k)) return thin_gemm(ctx, trans_a, trans_b, m, n, k, a, b, c, bias, act, beta);
   if (ctx->math_mode != NRS_MATH_FP32 && k > 0) {
+    if (trans_a && !trans_b && !bias && act == NRS_ACT_NONE && m >= 64) {   // A^T B: both operands read as stored
+      const int st = nrs_tc_gemm_tn(ctx, m, n, k, a, b, c, beta != 0.0f);
+      if (st != NRS_ERR_UNSUPPORTED) return st;
+    }
     const int st = nrs_tc_gemm(ctx, trans_a, trans_b, 1, m, n, k, a, b, c, bias, act, beta);
     if (st != NRS_ERR_UNSUPPORTED) return st;
   }

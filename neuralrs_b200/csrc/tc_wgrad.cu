@@ -41,8 +41,9 @@ struct WgradParams {
   int cblocks;                    // ci / 32
   int a_box_blocks;               // 32-channel blocks of dy one box brings (min(4, co/32))
   int m_blocks;                   // ceil(co / 128)
-  float* partial;                 // [split][m_block][group][128][group_cols]
-  int group_cols;                 // taps_per_group * ci
+  float* partial;                 // [split][m_block][group][col_block][128][group_cols]
+  int group_cols;                 // taps_per_group * ci (1x1 with more than 256 input channels: 256)
+  int col_blocks;                 // 1x1 only: column blocks of 256 input channels, each its own CTA
 };
 
 template <int NPLANES, int STAGES>
@@ -63,8 +64,12 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   NRS_PDL_TRIGGER();
-  const int mb = blockIdx.x / p.n_groups, grp = blockIdx.x - mb * p.n_groups;
+  const int cbk = blockIdx.x % p.col_blocks;
+  const int mg = blockIdx.x / p.col_blocks;
+  const int mb = mg / p.n_groups, grp = mg - mb * p.n_groups;
   const int split = blockIdx.y;
+  // 32-channel blocks of x this CTA's columns cover (a column block of a wide 1x1 layer may be ragged)
+  const int cblocks = p.col_blocks > 1 ? min(8, p.cblocks - cbk * 8) : p.cblocks;
   const int t_begin = split * p.tiles_per_split;
   const int t_end = min(p.n_tiles, t_begin + p.tiles_per_split);
   const int ntiles = t_end - t_begin;
@@ -95,7 +100,8 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
       // One 5-D box per operand plane brings all 32-channel blocks of a pixel tile at once
       // (the channel-block index is the outermost box dimension), so a tile costs
       // planes x (1 + taps) TMA instructions instead of one per block.
-      const uint32_t tx = NPLANES * (uint32_t)(p.a_box_blocks + ntaps * p.cblocks) * blk_bytes;
+      // (a ragged last column block still receives a full box: TMA zero-fills the blocks beyond the tensor)
+      const uint32_t tx = NPLANES * (uint32_t)(p.a_box_blocks + ntaps * (p.col_blocks > 1 ? 8 : p.cblocks)) * blk_bytes;
       int tap_i[9], tap_j[9];
       for (int t = 0; t < ntaps && t < 9; ++t) { tap_i[t] = (tap0 + t) / p.kw; tap_j[t] = (tap0 + t) - tap_i[t] * p.kw; }
       int issued = 0;
@@ -118,7 +124,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
           tc::tma_load_5d(a_dst, tdy, &full_bar[s], 0, x0, y0, n0, mb * kABlocks);
           for (int t = 0; t < ntaps; ++t)
             tc::tma_load_5d(b_dst + (size_t)t * p.cblocks * blk_bytes, txm, &full_bar[s], 0, x0 + tap_j[t] - p.pad,
-                            y0 + tap_i[t] - p.pad, n0, 0);
+                            y0 + tap_i[t] - p.pad, n0, cbk * 8);
         }
       }
       if (!ok) {
@@ -169,8 +175,9 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
     if (ok) {
       tc::tc_fence_after_sync();
       const int row = q * 32 + lane;
-      const int live_cols = ntaps * p.ci;
-      float* dst = p.partial + ((((size_t)split * p.m_blocks + mb) * p.n_groups + grp) * 128 + row) * p.group_cols;
+      const int live_cols = p.col_blocks > 1 ? cblocks * 32 : ntaps * p.ci;
+      float* dst = p.partial +
+                   (((((size_t)split * p.m_blocks + mb) * p.n_groups + grp) * p.col_blocks + cbk) * 128 + row) * p.group_cols;
       const bool row_live = mb * 128 + row < p.co;
 #pragma unroll 1
       for (int c = 0; c < (live_cols + 31) / 32; ++c) {
@@ -218,8 +225,10 @@ tc_wgrad_reduce_kernel(const WgradParams p, int splits, int lanes, float* __rest
   const int mb = co / 128, row = co - mb * 128;
   const int grp = tap / p.taps_per_group, t = tap - grp * p.taps_per_group;
   const size_t tile = (size_t)128 * p.group_cols;
-  const size_t off = (((size_t)mb * p.n_groups + grp) * 128 + row) * p.group_cols + (size_t)t * p.ci + c;
-  const size_t split_stride = (size_t)p.m_blocks * p.n_groups * tile;
+  const int cbk = p.col_blocks > 1 ? c / 256 : 0;
+  const size_t col = p.col_blocks > 1 ? (size_t)(c - cbk * 256) : (size_t)t * p.ci + c;
+  const size_t off = ((((size_t)mb * p.n_groups + grp) * p.col_blocks + cbk) * 128 + row) * p.group_cols + col;
+  const size_t split_stride = (size_t)p.m_blocks * p.n_groups * p.col_blocks * tile;
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
   if (live) {
 #pragma unroll 4
@@ -252,7 +261,7 @@ int launch_wgrad(nrs_ctx* ctx, const CUtensorMap* maps, const WgradParams& p, in
   int* err = nullptr;
   const int st = nrs_err_flag(ctx, &err);
   if (st != NRS_OK) return st;
-  dim3 grid((unsigned)(p.m_blocks * p.n_groups), (unsigned)splits);
+  dim3 grid((unsigned)(p.m_blocks * p.n_groups * p.col_blocks), (unsigned)splits);
   NRS_PDL_LAUNCH((tc_wgrad_kernel<NPLANES, STAGES>), grid, kWgThreads, smem_bytes, ctx->stream, maps[0], maps[1], maps[2],
                  maps[3], p, p.group_cols, err);
   NRS_LAUNCHED(ctx);
@@ -264,7 +273,8 @@ int launch_wgrad(nrs_ctx* ctx, const CUtensorMap* maps, const WgradParams& p, in
 int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n, int ci, int h, int wd, int co,
                       int kh, int kw, int stride, int pad, int accumulate) {
   if (!tc::tensor_map_encoder()) return NRS_ERR_UNSUPPORTED;
-  if (stride != 1 || ci % 32 != 0 || co % 32 != 0 || ci > kMaxN || n < 1) return NRS_ERR_UNSUPPORTED;
+  if (stride != 1 || ci % 32 != 0 || co % 32 != 0 || n < 1) return NRS_ERR_UNSUPPORTED;
+  if (ci > kMaxN && !(kh == 1 && kw == 1)) return NRS_ERR_UNSUPPORTED;   // wide layers: 1x1 only (column blocks)
   const int oh = h + 2 * pad - kh + 1, ow = wd + 2 * pad - kw + 1;
   if (ow > wd || oh > h || ow < 1 || oh < 1 || ow > 64) return NRS_ERR_UNSUPPORTED;
   const bool split3 = ctx->math_mode == NRS_MATH_3XTF32;
@@ -293,11 +303,18 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   p.cblocks = ci / 32;
   p.m_blocks = (co + 127) / 128;
   const int taps = kh * kw;
-  int tpg = kMaxN / ci;
+  int tpg = ci <= kMaxN ? kMaxN / ci : 1;
   if (tpg > taps) tpg = taps;
   p.n_groups = (taps + tpg - 1) / tpg;
   p.taps_per_group = (taps + p.n_groups - 1) / p.n_groups;
   p.group_cols = p.taps_per_group * ci;
+  p.col_blocks = 1;
+  if (ci > kMaxN) {                 // 1x1: the input channels are cut into column blocks of 256, one CTA each
+    p.col_blocks = (ci + kMaxN - 1) / kMaxN;
+    p.n_groups = 1;
+    p.taps_per_group = 1;
+    p.group_cols = kMaxN;
+  }
 
   // ring depth from the shared-memory budget
   const size_t stage_bytes = (size_t)planes * (kABlocks + p.group_cols / 32) * p.kp * 128;
@@ -307,9 +324,11 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   const size_t smem_bytes = stages * stage_bytes + 1024 + 256;
 
   // pixel split: fill the GPU, and bound the accumulation chain in 3xTF32 mode
-  const int ctas_per_split = p.m_blocks * p.n_groups;
+  const int ctas_per_split = p.m_blocks * p.n_groups * p.col_blocks;
   const int max_tiles = split3 ? tc::kMaxChainK / p.kp : 1 << 30;
   int min_tiles = 512 / p.kp;   // amortise the prologue and the partial-tile store
+  // ... unless that leaves most of the GPU idle (a short reduction with a small output: Linear layers)
+  while (min_tiles > 4 && (long)(p.n_tiles / min_tiles) * ctas_per_split < ctx->sm_count / 2) min_tiles /= 2;
   if (min_tiles > max_tiles) min_tiles = max_tiles;
   const int tps = tc::plan_units_per_cta(ctx->sm_count, ctas_per_split, p.n_tiles, min_tiles, max_tiles, 8);
   p.tiles_per_split = tps;
@@ -318,7 +337,7 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
 
   // workspaces: NHWC planes of dy and x, and the partial tiles
   const size_t dy_plane = (size_t)n * oh * ow * co, x_plane = (size_t)n * h * wd * ci;
-  const size_t partial_floats = (size_t)splits * p.m_blocks * p.n_groups * 128 * p.group_cols;
+  const size_t partial_floats = (size_t)splits * p.m_blocks * p.n_groups * p.col_blocks * 128 * p.group_cols;
   void *dy_hi = nullptr, *dy_lo = nullptr, *x_hi = nullptr, *x_lo = nullptr, *part = nullptr;
   int st = nrs_ws_slot(ctx, NRS_WS_PARTIAL, partial_floats * sizeof(float), &part);
   if (st != NRS_OK) return st;
@@ -330,7 +349,9 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   } else {
     st = nrs_ws_slot(ctx, NRS_WS_A_HI, dy_plane * sizeof(float), &dy_hi);
     if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_A_LO, dy_plane * sizeof(float), &dy_lo);
-    if (st == NRS_OK) st = nrs_tc_stage(ctx, dy, (float*)dy_hi, (float*)dy_lo, oh * ow, co, co, n, dy_img, dy_img, true);
+    if (st == NRS_OK)   // a [n, c, 1, 1] tensor is already pixel-major: split only
+      st = oh * ow == 1 ? nrs_tc_stage(ctx, dy, (float*)dy_hi, (float*)dy_lo, n, co, co, 1, 0, 0, false)
+                        : nrs_tc_stage(ctx, dy, (float*)dy_hi, (float*)dy_lo, oh * ow, co, co, n, dy_img, dy_img, true);
     if (st != NRS_OK) return st;
   }
   if (const NrsPlanes* ready = nrs_planes_find(ctx, x, split3)) {
@@ -339,7 +360,9 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   } else {
     st = nrs_ws_slot(ctx, NRS_WS_B_HI, x_plane * sizeof(float), &x_hi);
     if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_B_LO, x_plane * sizeof(float), &x_lo);
-    if (st == NRS_OK) st = nrs_tc_stage(ctx, x, (float*)x_hi, (float*)x_lo, h * wd, ci, ci, n, x_img, x_img, true);
+    if (st == NRS_OK)
+      st = h * wd == 1 ? nrs_tc_stage(ctx, x, (float*)x_hi, (float*)x_lo, n, ci, ci, 1, 0, 0, false)
+                       : nrs_tc_stage(ctx, x, (float*)x_hi, (float*)x_lo, h * wd, ci, ci, n, x_img, x_img, true);
     if (st != NRS_OK) return st;
   }
 
@@ -351,7 +374,7 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   const uint64_t xdim[5] = {32, (uint64_t)wd, (uint64_t)h, (uint64_t)n, (uint64_t)(ci / 32)};
   const uint64_t xstr[4] = {(uint64_t)ci * 4, (uint64_t)wd * ci * 4, (uint64_t)h * wd * ci * 4, 128};
   const uint32_t dbox[5] = {32, (uint32_t)p.Wt, (uint32_t)p.Ht, (uint32_t)p.Nt, (uint32_t)p.a_box_blocks};
-  const uint32_t xbox[5] = {32, (uint32_t)p.Wt, (uint32_t)p.Ht, (uint32_t)p.Nt, (uint32_t)p.cblocks};
+  const uint32_t xbox[5] = {32, (uint32_t)p.Wt, (uint32_t)p.Ht, (uint32_t)p.Nt, (uint32_t)(p.col_blocks > 1 ? 8 : p.cblocks)};
   bool ok = tc::encode_tmap_f32(&maps[0], dy_hi, 5, ddim, dstr, dbox, true) && tc::encode_tmap_f32(&maps[2], x_hi, 5, xdim, xstr, xbox, true);
   if (split3) ok = ok && tc::encode_tmap_f32(&maps[1], dy_lo, 5, ddim, dstr, dbox, true) && tc::encode_tmap_f32(&maps[3], x_lo, 5, xdim, xstr, xbox, true);
   else { maps[1] = maps[0]; maps[3] = maps[2]; }
@@ -374,4 +397,18 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
                  accumulate);
   NRS_LAUNCHED(ctx);
   return NRS_OK;
+}
+
+// C[m,n] (+)= A^T B for A stored [k][m] and B stored [k][n] (both row-major) without transposing either:
+// the reduction index k is the slow index of both operands, which is what the weight-gradient kernel above
+// consumes (a 1x1 convolution over k "pixels": rows = A's columns, columns = B's columns).  The weight
+// gradient of a Linear layer, dW = x^T dz, is this product on the activations' own row-major planes.
+// NRS_ERR_UNSUPPORTED (no error text) unless m and n are multiples of 32 and k of 8.
+int nrs_tc_gemm_tn(nrs_ctx* ctx, int m, int n, int k, const float* a, const float* b, float* c, int accumulate) {
+  if (m % 32 != 0 || n % 32 != 0 || k < 8 || (k < 32 && k % 8 != 0)) return NRS_ERR_UNSUPPORTED;
+  // Outputs of up to 4 M elements (the Linear layers of the CNN and transformer configurations).  Larger ones
+  // (4096 x 4096 hidden layers) stay on the persistent GEMM kernel: its rastered tiles reuse operands through L2,
+  // and the transposes it needs are small beside such a product.
+  if ((long)m * n > (4L << 20)) return NRS_ERR_UNSUPPORTED;
+  return nrs_tc_conv_wgrad(ctx, /*x=*/b, /*dy=*/a, /*dw=*/c, /*n=*/k, /*ci=*/n, 1, 1, /*co=*/m, 1, 1, 1, 0, accumulate);
 }
