@@ -256,9 +256,19 @@ int nrs_tc_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n,
   GemmPolicy pol{c, bias, act, beta, m, n, (size_t)m * n, false};
   pol.vec_ok = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && (((size_t)m * n) % 4 == 0) &&
                ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
-  const bool narrow = n <= 64;
-  if (split) return narrow ? run<64, 2>(ctx, A, B, batch, m, n, k, pol) : run<128, 2>(ctx, A, B, batch, m, n, k, pol);
-  return narrow ? run<64, 1>(ctx, A, B, batch, m, n, k, pol) : run<128, 1>(ctx, A, B, batch, m, n, k, pol);
+  // Tile width: 128 columns is the efficient shape, but a product with few tiles leaves most SMs idle and
+  // a K-split needs a second pass, so narrower tiles are taken until about two thirds of the SMs have one.
+  const long tiles_m = (m + tc::BM - 1) / tc::BM;
+  auto tiles = [&](int bn) { return tiles_m * ((n + bn - 1) / bn) * batch; };
+  const long want = (long)ctx->sm_count * 2 / 3;
+  int bn = n <= 32 ? 32 : n <= 64 ? 64 : 128;
+  if (bn == 128 && tiles(128) < want) bn = 64;
+  if (bn == 64 && n > 32 && tiles(64) < want) bn = 32;
+#define NRS_RUN_GEMM(BN_) (split ? run<BN_, 2>(ctx, A, B, batch, m, n, k, pol) : run<BN_, 1>(ctx, A, B, batch, m, n, k, pol))
+  if (bn == 128) return NRS_RUN_GEMM(128);
+  if (bn == 64) return NRS_RUN_GEMM(64);
+  return NRS_RUN_GEMM(32);
+#undef NRS_RUN_GEMM
 }
 
 extern "C" int nrs_has_tensor_core_path(void) { return 1; }
