@@ -60,6 +60,9 @@ def parse():
     ap.add_argument("--global-batch", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-microbench", action="store_true")
+    ap.add_argument("--only-microbench", action="store_true",
+                    help="N=1: skip the training loops and print only the micro-benchmarks (the command the ncu captures of "
+                         "the HBM-bound and attention kernels under profiles/ run)")
     ap.add_argument("--no-fuse", action="store_true")
     return ap.parse_args()
 
@@ -375,6 +378,8 @@ def hbm_microbench(ctx, stream, hbm_peak_gbs, iters=10):
           "x[65536,256] -> y, xhat, istd")
     entry("layernorm_bwd_dx", 3 * tb + rows * 4, lambda: l.nrs_layernorm_bwd(ctx.h, P(gy), P(xhat), P(istd), P(gamma), P(dx), None, None, rows, f, 0, 0),
           "g, xhat, istd -> dx [65536,256]")
+    entry("layernorm_bwd", 3 * tb + rows * 4, lambda: l.nrs_layernorm_bwd(ctx.h, P(gy), P(xhat), P(istd), P(gamma), P(dx), P(dgm), P(dbt), rows, f, 0, 0),
+          "g, xhat, istd -> dx, dgamma, dbeta in one launch (+ the partial-sum fold): what the graph operator issues")
     entry("layernorm_bwd_params", 2 * tb, lambda: l.nrs_layernorm_bwd(ctx.h, P(gy), P(xhat), P(istd), P(gamma), None, P(dgm), P(dbt), rows, f, 0, 0),
           "g, xhat -> dgamma, dbeta [256]")
     del x, gy, y, xhat, dx
@@ -748,8 +753,28 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_only_microbench(args):
+    import torch
+    from neuralrs_b200 import cuda
+    torch.cuda.set_device(0)
+    ctx = cuda.Context(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx.set_stream(stream.cuda_stream)
+    ctx.set_math_mode(MATH[args.math])
+    peaks = measured_peaks()
+    line = {"microbench_only": True, "math": args.math,
+            "hbm_microbench": hbm_microbench(ctx, stream, peaks["hbm_gbs"], iters=max(1, min(args.steps, 10))),
+            "batchnorm_microbench": batchnorm_microbench(ctx, stream, peaks["hbm_gbs"], iters=max(1, min(args.steps, 10))),
+            "attention_microbench": attention_microbench(ctx, stream, iters=max(1, min(args.steps, 20))),
+            "conv_microbench": conv_microbench(ctx, stream, iters=max(1, min(args.steps, 10)))}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse()
+    if args.only_microbench:
+        return run_only_microbench(args)
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 500), __file__] + sys.argv[1:]

@@ -179,7 +179,6 @@ attn_fwd_tc_kernel(const float* __restrict__ q, const float* __restrict__ k, con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  NRS_PDL_TRIGGER();
   const int bh = blockIdx.x, b = bh / H, hd = bh - b * H;
   const size_t D = (size_t)H * dh;
   const size_t base = (size_t)b * S * D + (size_t)hd * dh;
@@ -194,6 +193,7 @@ attn_fwd_tc_kernel(const float* __restrict__ q, const float* __restrict__ k, con
     tc::tmem_relinquish();
   }
   NRS_PDL_WAIT();
+  NRS_PDL_TRIGGER();
   {
     const RowRegs rq = load_row(q + base, D, S, dh), rk = load_row(k + base, D, S, dh), rv = load_row(v + base, D, S, dh);
     store_row_tile(q_hi, q_lo, rq);
@@ -310,7 +310,6 @@ attn_bwd_tc_kernel(const float* __restrict__ q, const float* __restrict__ k, con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  NRS_PDL_TRIGGER();
   const int bh = blockIdx.x, b = bh / H, hd = bh - b * H;
   const size_t D = (size_t)H * dh;
   const size_t base = (size_t)b * S * D + (size_t)hd * dh;
@@ -325,6 +324,7 @@ attn_bwd_tc_kernel(const float* __restrict__ q, const float* __restrict__ k, con
     tc::tmem_relinquish();
   }
   NRS_PDL_WAIT();
+  NRS_PDL_TRIGGER();
   prefetch_row(k + base, D, S);               // read two and three phases from now
   prefetch_row(q + base, D, S);
   {

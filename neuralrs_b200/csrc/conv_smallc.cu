@@ -352,6 +352,7 @@ int run_wgrad_tc(nrs_ctx* ctx, const float* x, const float* dy, float* dw, int n
   st = nrs_alloc(ctx, (size_t)co * 32 * sizeof(float), 0, &wide);
   if (st == NRS_OK) {
     ctx->plane_hints[phi] = NrsPlanes{phi, plo, split ? 1 : 0};
+    ctx->independent_next = false;   // phi was written by the kernel just launched
     st = nrs_tc_conv_wgrad(ctx, phi, dy, (float*)wide, n, 32, oh, ow, co, 1, 1, 1, 0, 0);
     ctx->plane_hints.erase(phi);
   }

@@ -316,7 +316,8 @@ NodeP matmul(const NodeP& a, const NodeP& b) {
       check(ctx, nrs_gemm(ctx, 0, 1, m, k, n, dc, b->data, t.ptr, nullptr, NRS_ACT_NONE, t.accumulate ? 1.0f : 0.0f));
     }
     if (b->requires_grad) {
-      GradTarget t = grad_target(b);  // dB (+)= A^T . dC
+      GradTarget t = grad_target(b);  // dB (+)= A^T . dC: reads nothing dA wrote, so it may start under dA's tail
+      NrsIndependentNext overlap(ctx, a->requires_grad);
       check(ctx, nrs_gemm(ctx, 1, 0, k, n, m, a->data, dc, t.ptr, nullptr, NRS_ACT_NONE, t.accumulate ? 1.0f : 0.0f));
     }
   };
@@ -611,8 +612,9 @@ static void conv_backward(Node* self, const NodeP& x, const NodeP& w, const Node
       }
     }
   }
-  if (w->requires_grad) {
+  if (w->requires_grad) {   // reads nothing the data gradient wrote: it may start under that kernel's tail
     GradTarget t = grad_target(w);
+    NrsIndependentNext overlap(ctx, x->requires_grad);
     check(ctx, nrs_conv2d_bwd(ctx, x->data, w->data, dy, nullptr, t.ptr, nullptr, n, ci, h, wd, co, kh, kw, stride,
                               pad, t.accumulate));
   }
@@ -1041,8 +1043,14 @@ NodeP linear_act(const NodeP& x, const NodeP& w, const NodeP& b, int act) {
   if (act == NRS_ACT_GELU) {
     pre = dalloc(ctx, out->len());
     out->saved.push_back(pre);
-    check(ctx, nrs_gemm(ctx, 0, 0, m, n, k, x->data, w->data, pre, b->data, NRS_ACT_NONE, 0.0f));
-    check(ctx, nrs_gelu_fwd(ctx, pre, out->data, out->len()));
+    // one kernel writes the pre-activation (GELU's derivative reads it) and the activation
+    const int st = nrs_linear_act_pre(ctx, m, n, k, x->data, w->data, b->data, NRS_ACT_GELU, out->data, pre);
+    if (st == NRS_ERR_UNSUPPORTED) {
+      check(ctx, nrs_gemm(ctx, 0, 0, m, n, k, x->data, w->data, pre, b->data, NRS_ACT_NONE, 0.0f));
+      check(ctx, nrs_gelu_fwd(ctx, pre, out->data, out->len()));
+    } else {
+      check(ctx, st);
+    }
   } else {
     check(ctx, nrs_gemm(ctx, 0, 0, m, n, k, x->data, w->data, out->data, b->data, act, 0.0f));
   }
@@ -1063,13 +1071,14 @@ NodeP linear_act(const NodeP& x, const NodeP& w, const NodeP& b, int act) {
       GradTarget t = grad_target(b);
       check(ctx, nrs_sum_axis0(ctx, dz, t.ptr, m, n, t.accumulate));
     }
-    if (w->requires_grad) {
-      GradTarget t = grad_target(w);
-      check(ctx, nrs_gemm(ctx, 1, 0, k, n, m, x->data, dz, t.ptr, nullptr, NRS_ACT_NONE, t.accumulate ? 1.0f : 0.0f));
-    }
     if (x->requires_grad) {
       GradTarget t = grad_target(x);
       check(ctx, nrs_gemm(ctx, 0, 1, m, k, n, dz, w->data, t.ptr, nullptr, NRS_ACT_NONE, t.accumulate ? 1.0f : 0.0f));
+    }
+    if (w->requires_grad) {   // after dX: it reads nothing dX wrote, so it may start under dX's tail
+      GradTarget t = grad_target(w);
+      NrsIndependentNext overlap(ctx, x->requires_grad);
+      check(ctx, nrs_gemm(ctx, 1, 0, k, n, m, x->data, dz, t.ptr, nullptr, NRS_ACT_NONE, t.accumulate ? 1.0f : 0.0f));
     }
     if (tmp) nrs_free(ctx, tmp);
   };

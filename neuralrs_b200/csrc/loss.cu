@@ -56,8 +56,10 @@ ce_rows_kernel(const float* __restrict__ logits, const float* __restrict__ targe
 // loads (lane l takes float4s l, l+32, ...: 512 contiguous bytes per load instruction), every
 // exponential is evaluated once, the gradient is written once.  Rows of up to 1024 classes whose
 // width is a multiple of four.  With `labels` (int32 class per row) the dense one-hot tensor is not read.
+// Registers hold the logits row and the target row only (the exponentials are recomputed for the gradient:
+// arithmetic is free here, registers are what bounds the rows in flight per SM); three blocks per SM.
 template <int VPL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 ce_rows_vec_kernel(const float* __restrict__ logits, const float* __restrict__ target, const int32_t* __restrict__ labels,
                    float* __restrict__ row_loss, float* __restrict__ grad, int batch, int classes, float inv_div) {
   NRS_PDL_PROLOGUE();
@@ -66,44 +68,45 @@ ce_rows_vec_kernel(const float* __restrict__ logits, const float* __restrict__ t
   const int c4 = classes >> 2;
   for (int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5); b < batch; b += gridDim.x * warps_per_block) {
     const size_t base = (size_t)b * classes;
-    float4 x[VPL], e[VPL];
+    float4 x[VPL], t[VPL];
     float mx = -INFINITY;
+    const int label = labels ? labels[b] : -1;
+    // every load of the row (logits and one-hot row) is in flight before the first reduction waits
 #pragma unroll
     for (int k = 0; k < VPL; ++k) {
       const int c = lane + 32 * k;
       if (c < c4) {
         x[k] = __ldcs(reinterpret_cast<const float4*>(logits + base) + c);
-        mx = fmaxf(mx, fmaxf(fmaxf(x[k].x, x[k].y), fmaxf(x[k].z, x[k].w)));
+        if (target) {
+          t[k] = __ldcs(reinterpret_cast<const float4*>(target + base) + c);
+        } else {
+          const int d = label - 4 * c;     // position of the label inside this float4, if any
+          t[k] = make_float4(d == 0 ? 1.0f : 0.0f, d == 1 ? 1.0f : 0.0f, d == 2 ? 1.0f : 0.0f, d == 3 ? 1.0f : 0.0f);
+        }
       }
     }
+#pragma unroll
+    for (int k = 0; k < VPL; ++k)
+      if (lane + 32 * k < c4) mx = fmaxf(mx, fmaxf(fmaxf(x[k].x, x[k].y), fmaxf(x[k].z, x[k].w)));
     mx = warp_max(mx);
     float se = 0.0f;
 #pragma unroll
     for (int k = 0; k < VPL; ++k)
-      if (lane + 32 * k < c4) {
-        e[k] = make_float4(expf(x[k].x - mx), expf(x[k].y - mx), expf(x[k].z - mx), expf(x[k].w - mx));
-        se += (e[k].x + e[k].y) + (e[k].z + e[k].w);
-      }
+      if (lane + 32 * k < c4)
+        se += (expf(x[k].x - mx) + expf(x[k].y - mx)) + (expf(x[k].z - mx) + expf(x[k].w - mx));
     se = warp_sum(se);
     const float lse = logf(se) + mx;
-    const int label = labels ? labels[b] : -1;
+    const float inv_se = 1.0f / se;
     float loss = 0.0f;
 #pragma unroll
     for (int k = 0; k < VPL; ++k) {
       const int c = lane + 32 * k;
       if (c < c4) {
-        float4 t;
-        if (target) {
-          t = __ldcs(reinterpret_cast<const float4*>(target + base) + c);
-        } else {
-          const int d = label - 4 * c;     // position of the label inside this float4, if any
-          t = make_float4(d == 0 ? 1.0f : 0.0f, d == 1 ? 1.0f : 0.0f, d == 2 ? 1.0f : 0.0f, d == 3 ? 1.0f : 0.0f);
-        }
-        loss += (-t.x * (x[k].x - lse) + -t.y * (x[k].y - lse)) + (-t.z * (x[k].z - lse) + -t.w * (x[k].w - lse));
+        loss += (-t[k].x * (x[k].x - lse) + -t[k].y * (x[k].y - lse)) + (-t[k].z * (x[k].z - lse) + -t[k].w * (x[k].w - lse));
         if (grad)
           __stcs(reinterpret_cast<float4*>(grad + base) + c,
-                 make_float4((e[k].x / se - t.x) * inv_div, (e[k].y / se - t.y) * inv_div, (e[k].z / se - t.z) * inv_div,
-                             (e[k].w / se - t.w) * inv_div));
+                 make_float4((expf(x[k].x - mx) * inv_se - t[k].x) * inv_div, (expf(x[k].y - mx) * inv_se - t[k].y) * inv_div,
+                             (expf(x[k].z - mx) * inv_se - t[k].z) * inv_div, (expf(x[k].w - mx) * inv_se - t[k].w) * inv_div));
       }
     }
     if (row_loss) {

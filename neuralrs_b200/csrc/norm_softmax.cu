@@ -259,8 +259,17 @@ ln_param_fold_kernel(const float* __restrict__ partial, float* dgamma, float* db
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + lane;          // column of the [2f]-wide partial rows
   float t = 0.0f;
-  if (c < 2 * f)
-    for (int s = wrp; s < parts; s += 8) t += partial[(size_t)s * 2 * f + c];
+  if (c < 2 * f) {
+    // four loads in flight per thread; the additions keep the order s = wrp, wrp + 8, ...
+    const size_t step = (size_t)8 * 2 * f;
+    const float* src = partial + (size_t)wrp * 2 * f + c;
+    int s = wrp;
+    for (; s + 24 < parts; s += 32, src += 4 * step) {
+      const float v0 = src[0], v1 = src[step], v2 = src[2 * step], v3 = src[3 * step];
+      t += v0; t += v1; t += v2; t += v3;
+    }
+    for (; s < parts; s += 8, src += step) t += *src;
+  }
   sm[wrp][lane] = t;
   __syncthreads();
   if (wrp != 0 || c >= 2 * f) return;
@@ -435,7 +444,7 @@ int layernorm_bwd(nrs_ctx* ctx, const char* who, const float* g, const float* xh
     int warps = 8;
     while (dgamma && warps > 1 && (size_t)warps * 2 * f * sizeof(float) > 32 * 1024) warps >>= 1;
     int blocks = row_grid(ctx, rows, warps);
-    if (dgamma && blocks > 2 * ctx->sm_count) blocks = 2 * ctx->sm_count;   // fewer, longer-lived blocks: fewer partial rows to fold
+    if (dgamma && blocks > 4 * ctx->sm_count) blocks = 4 * ctx->sm_count;   // one resident wave of longer-lived blocks: fewer partial rows to fold
     float* partial = nullptr;
     if (dgamma) {
       void* ws = nullptr;

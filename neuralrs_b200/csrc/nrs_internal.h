@@ -119,12 +119,25 @@ struct nrs_ctx {
   // (`split`: bit 0 = residual plane present, bits 8.. = the padding they were made for).
   std::map<const void*, NrsPlanes> patch_hints;
   NrsWeightSet weight_set;
+  // Set by a caller that has just issued a kernel whose output the NEXT tensor-core weight-gradient launch
+  // does not read (see NRS_PDL_PROLOGUE): that launch may overlap it.  Consumed by the launch.
+  bool independent_next = false;
   // Counter-based generator state of the dropout masks (dropout.cu): seed, and the next unused counter block.
   uint64_t rng_seed = 0, rng_offset = 0;
   // Optional per-family device timing (nrs_profile_*).
   bool profiling = false;
   std::vector<NrsProfRecord> prof_records;
   std::vector<cudaEvent_t> prof_free_events;
+};
+
+// Marks, for the duration of a scope, that the kernel launched last wrote nothing the next tensor-core
+// weight-gradient launch reads (nrs_ctx::independent_next).
+struct NrsIndependentNext {
+  nrs_ctx* c;
+  NrsIndependentNext(nrs_ctx* ctx, bool on) : c(ctx) { c->independent_next = on; }
+  ~NrsIndependentNext() { c->independent_next = false; }
+  NrsIndependentNext(const NrsIndependentNext&) = delete;
+  NrsIndependentNext& operator=(const NrsIndependentNext&) = delete;
 };
 
 // Brackets the launches issued during its lifetime with two events when
@@ -139,7 +152,9 @@ struct NrsProfScope {
 
 int nrs_fail(nrs_ctx* ctx, int code, const char* fmt, ...);
 int nrs_workspace(nrs_ctx* ctx, size_t bytes, void** out);
-enum { NRS_WS_A_HI = 0, NRS_WS_A_LO = 1, NRS_WS_B_HI = 2, NRS_WS_B_LO = 3, NRS_WS_PARTIAL = 4, NRS_WS_COUNT = 8 };
+// (the weight-gradient kernels keep their split partials in a slot of their own: they may run while the
+// data gradient's K-split is still being folded out of NRS_WS_PARTIAL)
+enum { NRS_WS_A_HI = 0, NRS_WS_A_LO = 1, NRS_WS_B_HI = 2, NRS_WS_B_LO = 3, NRS_WS_PARTIAL = 4, NRS_WS_WGRAD_PARTIAL = 5, NRS_WS_COUNT = 8 };
 int nrs_ws_slot(nrs_ctx* ctx, int slot, size_t bytes, void** out);
 int nrs_err_flag(nrs_ctx* ctx, int** out);
 inline const NrsPlanes* nrs_planes_find(nrs_ctx* ctx, const void* src, bool split) {
@@ -215,8 +230,15 @@ inline bool nrs_smem_attr_update(NrsSmemAttr& a, int device, size_t bytes) {
 // has to issue it (or exit) before that happens, so only a grid's last wave is ever shared.
 #define NRS_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
 #define NRS_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+// Order: every kernel WAITS first and only then triggers.  That keeps one property a few kernels rely on:
+// when kernel N+1 has been launched, every CTA of kernel N has passed its wait, so kernel N-1 and all
+// before it have completed.  A kernel that does not depend on its immediate predecessor (a weight
+// gradient issued right after the data gradient of the same layer: both read the same inputs) may then
+// skip the wait at its start, begin on the SMs its predecessor's last wave leaves idle, and wait just
+// before it exits instead, so that kernels after it still see everything before them complete.  Such a
+// kernel does not trigger (exiting does).
 #define NRS_PDL_PROLOGUE() \
-  do { NRS_PDL_TRIGGER(); NRS_PDL_WAIT(); } while (0)
+  do { NRS_PDL_WAIT(); NRS_PDL_TRIGGER(); } while (0)
 
 template <class... P, class... A>
 inline cudaError_t nrs_pdl_launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
@@ -249,8 +271,13 @@ static inline unsigned nrs_blocks(size_t work, unsigned per_block) {
 // Tensor-core contraction entry points (tc_gemm.cu / tc_conv.cu).  Each returns
 // NRS_ERR_UNSUPPORTED (without setting an error text) when the shape is outside
 // what the tcgen05 kernels cover, and the caller then runs the FFMA kernels.
+// pre_out (optional, [batch][m][n]): the value before the activation, written by the same epilogue.
 int nrs_tc_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n, int k,
-                const float* a, const float* b, float* c, const float* bias, int act, float beta);
+                const float* a, const float* b, float* c, const float* bias, int act, float beta, float* pre_out = nullptr);
+// c = act(a[m,k] . w[k,n] + bias) and pre = a . w + bias from one tensor-core kernel; NRS_ERR_UNSUPPORTED (no
+// error text) when the product would not run there.
+int nrs_linear_act_pre(nrs_ctx* ctx, int m, int n, int k, const float* a, const float* w, const float* bias, int act, float* c,
+                       float* pre);
 int nrs_tc_conv_fwd(nrs_ctx* ctx, const float* x, const float* w, const float* b, float* y, int n, int ci, int h,
                     int wd, int co, int kh, int kw, int stride, int pad, int act);
 int nrs_tc_conv_dgrad(nrs_ctx* ctx, const float* w, const float* dy, float* dx, int n, int ci, int h, int wd, int co,

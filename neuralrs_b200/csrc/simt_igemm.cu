@@ -364,6 +364,13 @@ bool nrs_gemm_on_tensor_cores(const nrs_ctx* ctx, int m, int n, int k) {
          tc::tensor_map_encoder() != nullptr;
 }
 
+int nrs_linear_act_pre(nrs_ctx* ctx, int m, int n, int k, const float* a, const float* w, const float* bias, int act, float* c,
+                       float* pre) {
+  if (!nrs_gemm_on_tensor_cores(ctx, m, n, k)) return NRS_ERR_UNSUPPORTED;
+  NrsProfScope prof(ctx, NRS_PROF_GEMM, 2.0 * m * n * k);
+  return nrs_tc_gemm(ctx, 0, 0, 1, m, n, k, a, w, c, bias, act, 0.0f, pre);
+}
+
 extern "C" {
 
 int nrs_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int m, int n, int k, const float* a, const float* b,
@@ -432,6 +439,10 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
   int st = check_conv_dims(ctx, "nrs_conv2d_bwd", n, ci, h, wd, co, kh, kw, stride, pad);
   if (st != NRS_OK) return st;
   const NrsConvGeom g(n, ci, h, wd, co, kh, kw, stride, pad);
+  // a caller that issued the data gradient of this layer just before asking for the weight gradient alone
+  // says so through the context; a call that computes both knows it by itself
+  bool wgrad_may_overlap = ctx->independent_next && !dx;
+  ctx->independent_next = false;
   if (n == 0) {  // an empty batch contributes zero gradients
     if (!accumulate) {
       if (dw) NRS_CUDA(ctx, cudaMemsetAsync(dw, 0, sizeof(float) * co * ci * kh * kw, ctx->stream));
@@ -443,12 +454,25 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
   NRS_REQUIRE(ctx, !dx || w, NRS_ERR_ARG, "nrs_conv2d_bwd: dx requested without w");
   NRS_REQUIRE(ctx, !dw || x, NRS_ERR_ARG, "nrs_conv2d_bwd: dw requested without x");
   const double conv_flop = 2.0 * n * co * g.oh * g.ow * ci * kh * kw;
+  // When both gradients are asked for, the data gradient's NHWC planes of dy (staged into the context's
+  // operand scratch) serve the weight gradient too: registered for the rest of this call.
+  const bool split3 = ctx->math_mode == NRS_MATH_3XTF32;
+  const bool dy_had_planes = ctx->math_mode != NRS_MATH_FP32 && nrs_planes_find(ctx, dy, split3) != nullptr;
+  bool dy_planes_lent = false;
+  struct Unlend {
+    nrs_ctx* c; const void* k; bool* on;
+    ~Unlend() { if (*on) c->plane_hints.erase(k); }
+  } unlend{ctx, dy, &dy_planes_lent};
   if (dx) {
     NrsProfScope prof(ctx, NRS_PROF_CONV_DGRAD, conv_flop);
     st = ctx->math_mode != NRS_MATH_FP32
              ? nrs_tc_conv_dgrad(ctx, w, dy, dx, n, ci, h, wd, co, kh, kw, stride, pad, accumulate)
              : NRS_ERR_UNSUPPORTED;
     if (st != NRS_OK && st != NRS_ERR_UNSUPPORTED) return st;
+    if (st == NRS_OK && dw && !dy_had_planes && ctx->ws_slot[NRS_WS_A_HI] && (!split3 || ctx->ws_slot[NRS_WS_A_LO])) {
+      ctx->plane_hints[dy] = NrsPlanes{(float*)ctx->ws_slot[NRS_WS_A_HI], split3 ? (float*)ctx->ws_slot[NRS_WS_A_LO] : nullptr, split3 ? 1 : 0};
+      dy_planes_lent = true;
+    }
     if (st == NRS_ERR_UNSUPPORTED) {
     NrsConvDgradProb p;
     p.g = g; p.M = n * h * wd; p.N = ci; p.K = co * kh * kw; p.batches = 1;
@@ -456,9 +480,11 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
     st = run_igemm(ctx, p, "nrs_conv2d_bwd(dx)");
     if (st != NRS_OK) return st;
     }
+    wgrad_may_overlap = true;   // x and dy (and any planes of them) were complete before the kernel(s) above
   }
   if (dw) {
     NrsProfScope prof(ctx, NRS_PROF_CONV_WGRAD, conv_flop);
+    NrsIndependentNext overlap(ctx, wgrad_may_overlap);
     st = nrs_smallc_conv_wgrad(ctx, x, dy, dw, n, ci, h, wd, co, kh, kw, stride, pad, accumulate);
     if (st == NRS_ERR_UNSUPPORTED && ctx->math_mode != NRS_MATH_FP32)
       st = nrs_tc_conv_wgrad_rows(ctx, x, dy, dw, n, ci, h, wd, co, kh, kw, stride, pad, accumulate);

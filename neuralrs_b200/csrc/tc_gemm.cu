@@ -23,6 +23,7 @@ struct GemmPolicy {
   int M, N;
   size_t batch_stride;
   bool vec_ok;
+  float* pre;   // optional second output: the value before the activation (what GELU's derivative needs)
   static constexpr bool kCanEmit = false;
 
   __device__ __forceinline__ uint32_t a_slice_bytes() const { return tc::BM * tc::BK * 4; }
@@ -34,6 +35,7 @@ struct GemmPolicy {
     if (m >= M || n >= N) return;
     float* dst = C + (size_t)batch * batch_stride + (size_t)m * N + n;
     if (bias) v += bias[n];
+    if (pre) pre[(size_t)batch * batch_stride + (size_t)m * N + n] = v;
     v = nrs_apply_act(v, act);
     if (beta != 0.0f) v += beta * *dst;
     *dst = v;
@@ -52,6 +54,7 @@ struct GemmPolicy {
           const float4 bv = *reinterpret_cast<const float4*>(bias + nb + j);
           v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
         }
+        if (pre) *reinterpret_cast<float4*>(pre + (size_t)batch * batch_stride + (size_t)m * N + nb + j) = v;
         v.x = nrs_apply_act(v.x, act); v.y = nrs_apply_act(v.y, act);
         v.z = nrs_apply_act(v.z, act); v.w = nrs_apply_act(v.w, act);
         float4* dst = reinterpret_cast<float4*>(crow + nb + j);
@@ -68,6 +71,7 @@ struct GemmPolicy {
         if (j < ncols && n < N) {
           float v = __uint_as_float(r[j]);
           if (bias) v += bias[n];
+          if (pre) pre[(size_t)batch * batch_stride + (size_t)m * N + n] = v;
           v = nrs_apply_act(v, act);
           if (beta != 0.0f) v += beta * crow[n];
           crow[n] = v;
@@ -240,7 +244,7 @@ extern "C" int nrs_measure_tf32_umma_peak(nrs_ctx* ctx, double* tflops_out) {
 }
 
 int nrs_tc_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n, int k, const float* a, const float* b,
-                float* c, const float* bias, int act, float beta) {
+                float* c, const float* bias, int act, float beta, float* pre_out) {
   if (!tc::tensor_map_encoder()) return NRS_ERR_UNSUPPORTED;
   // Small or skinny problems stay on the FFMA kernel: a 128-row tile would be mostly padding.
   if (m < 64 || n < 32 || k < 32) return NRS_ERR_UNSUPPORTED;
@@ -253,9 +257,9 @@ int nrs_tc_gemm(nrs_ctx* ctx, int trans_a, int trans_b, int batch, int m, int n,
   st = prepare_operand(ctx, b, n, k, batch, /*stored_kmajor=*/trans_b != 0, split, NRS_WS_B_HI, NRS_WS_B_LO, &B, true);
   if (st != NRS_OK) return st;
   if (batch > 1 && ((A.bstride % 4) || (B.bstride % 4))) return NRS_ERR_UNSUPPORTED;
-  GemmPolicy pol{c, bias, act, beta, m, n, (size_t)m * n, false};
+  GemmPolicy pol{c, bias, act, beta, m, n, (size_t)m * n, false, pre_out};
   pol.vec_ok = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && (((size_t)m * n) % 4 == 0) &&
-               ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
+               ((reinterpret_cast<uintptr_t>(bias) & 15) == 0) && ((reinterpret_cast<uintptr_t>(pre_out) & 15) == 0);
   // Tile width: 128 columns is the efficient shape, but a product with few tiles leaves most SMs idle and
   // a K-split needs a second pass, so narrower tiles are taken until about two thirds of the SMs have one.
   const long tiles_m = (m + tc::BM - 1) / tc::BM;

@@ -113,7 +113,6 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(emit_bar + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  NRS_PDL_TRIGGER();   // the next kernel may be scheduled as this grid's SMs free up
 
   if (warp == 0 && lane == 0) {
     prefetch_tmap(&tm_a_hi);
@@ -136,6 +135,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ C
   // Everything above (barriers, tensor memory, descriptor prefetch) may overlap the tail of the kernel
   // before this one in the stream; from here on its results are needed.
   NRS_PDL_WAIT();
+  NRS_PDL_TRIGGER();   // the next kernel may be scheduled as this grid's SMs free up
 
   if (warp == 0) {
     if (lane == 0) {

@@ -44,6 +44,7 @@ struct WgradParams {
   float* partial;                 // [split][m_block][group][col_block][128][group_cols]
   int group_cols;                 // taps_per_group * ci (1x1 with more than 256 input channels: 256)
   int col_blocks;                 // 1x1 only: column blocks of 256 input channels, each its own CTA
+  int independent;                // reads nothing the kernel launched just before it wrote (NRS_PDL_PROLOGUE)
 };
 
 template <int NPLANES, int STAGES>
@@ -63,7 +64,6 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  NRS_PDL_TRIGGER();
   const int cbk = blockIdx.x % p.col_blocks;
   const int mg = blockIdx.x / p.col_blocks;
   const int mb = mg / p.n_groups, grp = mg - mb * p.n_groups;
@@ -92,7 +92,8 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  NRS_PDL_WAIT();   // set-up above may overlap the previous kernel's tail; its results are needed from here
+  if (!p.independent) NRS_PDL_WAIT();   // set-up above may overlap the previous kernel's tail; its results are needed from here
+  NRS_PDL_TRIGGER();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -195,6 +196,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
     }
   }
 
+  if (p.independent) NRS_PDL_WAIT();   // nothing after this kernel may run ahead of its predecessor
   tc::tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -339,7 +341,8 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   const size_t dy_plane = (size_t)n * oh * ow * co, x_plane = (size_t)n * h * wd * ci;
   const size_t partial_floats = (size_t)splits * p.m_blocks * p.n_groups * p.col_blocks * 128 * p.group_cols;
   void *dy_hi = nullptr, *dy_lo = nullptr, *x_hi = nullptr, *x_lo = nullptr, *part = nullptr;
-  int st = nrs_ws_slot(ctx, NRS_WS_PARTIAL, partial_floats * sizeof(float), &part);
+  bool may_overlap = ctx->independent_next;   // withdrawn below if this call stages an operand itself
+  int st = nrs_ws_slot(ctx, NRS_WS_WGRAD_PARTIAL, partial_floats * sizeof(float), &part);
   if (st != NRS_OK) return st;
   p.partial = (float*)part;
   const size_t dy_img = (size_t)oh * ow * co, x_img = (size_t)h * wd * ci;
@@ -347,6 +350,7 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
     dy_hi = ready->hi;
     dy_lo = ready->lo;
   } else {
+    may_overlap = false;
     st = nrs_ws_slot(ctx, NRS_WS_A_HI, dy_plane * sizeof(float), &dy_hi);
     if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_A_LO, dy_plane * sizeof(float), &dy_lo);
     if (st == NRS_OK)   // a [n, c, 1, 1] tensor is already pixel-major: split only
@@ -358,6 +362,7 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
     x_hi = ready->hi;
     x_lo = ready->lo;
   } else {
+    may_overlap = false;
     st = nrs_ws_slot(ctx, NRS_WS_B_HI, x_plane * sizeof(float), &x_hi);
     if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_B_LO, x_plane * sizeof(float), &x_lo);
     if (st == NRS_OK)
@@ -379,6 +384,7 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   if (split3) ok = ok && tc::encode_tmap_f32(&maps[1], dy_lo, 5, ddim, dstr, dbox, true) && tc::encode_tmap_f32(&maps[3], x_lo, 5, xdim, xstr, xbox, true);
   else { maps[1] = maps[0]; maps[3] = maps[2]; }
   NRS_REQUIRE(ctx, ok, NRS_ERR_CUDA, "tc_wgrad: cuTensorMapEncodeTiled failed");
+  p.independent = may_overlap ? 1 : 0;
 
 #define NRS_WG(PL)                                                                     \
   switch (stages) {                                                                    \

@@ -55,6 +55,7 @@ struct RowParams {
   int SA, SX;                     // ring depths: dy rows, x rows
   int max_run;                    // vertical taps one UMMA may cover (256 / chunk, at most 3)
   float* partial;                 // [split][cta][128][3*chunk]
+  int independent;                // reads nothing the kernel launched just before it wrote (NRS_PDL_PROLOGUE)
 };
 
 // Is vertical tap i (x row = y + i - 1) inside the image for some row of [r0, r1)?
@@ -111,7 +112,6 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  NRS_PDL_TRIGGER();
   // blockIdx.x = (m block, horizontal tap kind, channel chunk).  Unpacked: kind = tap j, x shifted by
   // j - 1.  Packed: kind 0 shifts x by 0 and holds taps j = 1 (plain dy rows) and j = 0 (dy shifted one
   // pixel: sum_p dy[p+1] x[p] = sum_p dy[p] x[p-1]); kind 1 shifts x by +1 and holds j = 2 alone.
@@ -143,7 +143,8 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  NRS_PDL_WAIT();   // set-up above may overlap the previous kernel's tail; its results are needed from here
+  if (!p.independent) NRS_PDL_WAIT();   // set-up above may overlap the previous kernel's tail; its results are needed from here
+  NRS_PDL_TRIGGER();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -271,6 +272,7 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_
     }
   }
 
+  if (p.independent) NRS_PDL_WAIT();   // nothing after this kernel may run ahead of its predecessor
   tc::tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -395,7 +397,8 @@ int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float*
   const size_t dy_plane = (size_t)n * h * wd * co, x_plane = (size_t)n * h * wd * ci;
   const size_t partial_floats = (size_t)splits * ctas * 128 * kTaps * p.chunk;
   void *dy_hi = nullptr, *dy_lo = nullptr, *x_hi = nullptr, *x_lo = nullptr, *part = nullptr;
-  int st = nrs_ws_slot(ctx, NRS_WS_PARTIAL, partial_floats * sizeof(float), &part);
+  bool may_overlap = ctx->independent_next;   // withdrawn below if this call stages an operand itself
+  int st = nrs_ws_slot(ctx, NRS_WS_WGRAD_PARTIAL, partial_floats * sizeof(float), &part);
   if (st != NRS_OK) return st;
   p.partial = (float*)part;
   const size_t dy_img = (size_t)h * wd * co, x_img = (size_t)h * wd * ci;
@@ -403,6 +406,7 @@ int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float*
     dy_hi = ready->hi;
     dy_lo = ready->lo;
   } else {
+    may_overlap = false;
     st = nrs_ws_slot(ctx, NRS_WS_A_HI, dy_plane * sizeof(float), &dy_hi);
     if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_A_LO, dy_plane * sizeof(float), &dy_lo);
     if (st == NRS_OK) st = nrs_tc_stage(ctx, dy, (float*)dy_hi, (float*)dy_lo, h * wd, co, co, n, dy_img, dy_img, true);
@@ -412,6 +416,7 @@ int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float*
     x_hi = ready->hi;
     x_lo = ready->lo;
   } else {
+    may_overlap = false;
     st = nrs_ws_slot(ctx, NRS_WS_B_HI, x_plane * sizeof(float), &x_hi);
     if (st == NRS_OK && split3) st = nrs_ws_slot(ctx, NRS_WS_B_LO, x_plane * sizeof(float), &x_lo);
     if (st == NRS_OK) st = nrs_tc_stage(ctx, x, (float*)x_hi, (float*)x_lo, h * wd, ci, ci, n, x_img, x_img, true);
@@ -430,6 +435,7 @@ int nrs_tc_conv_wgrad_rows(nrs_ctx* ctx, const float* x, const float* dy, float*
   if (split3) ok = ok && tc::encode_tmap_f32(&maps[1], dy_lo, 5, ddim, dstr, dbox, true) && tc::encode_tmap_f32(&maps[3], x_lo, 5, xdim, xstr, xbox, true);
   else { maps[1] = maps[0]; maps[3] = maps[2]; }
   NRS_REQUIRE(ctx, ok, NRS_ERR_CUDA, "tc_wgrad_rows: cuTensorMapEncodeTiled failed");
+  p.independent = may_overlap ? 1 : 0;
 
   switch (wd / 8) {
     case 2: st = split3 ? launch_rows<2, 2>(ctx, maps, p, ctas, splits, smem_bytes) : launch_rows<1, 2>(ctx, maps, p, ctas, splits, smem_bytes); break;
