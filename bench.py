@@ -44,9 +44,20 @@ METRIC = "train samples/s (fwd+bwd+AdamW)"
 WORKLOADS = {"vgg_cifar": ("VGG_CIFAR", 1024, 3, 32), "small_cnn": ("SMALL_CNN", 64, 1, 64),
              "wide_mlp": ("WIDE_MLP", 16384, 5, 64), "vgg_cifar_bn": ("VGG_CIFAR_BN", 1024, 7, 32),
              "transformer_lm": ("TRANSFORMER_LM", 32, 4, 2)}
+# Configurations that state a batch without sharding it ("Batch 32 ... data-parallel at 1/2/4/8 GPUs"): every
+# GPU takes that batch (weak scaling).  The others state a GLOBAL batch "sharded over 1/2/4/8" (strong).
+PER_GPU_BATCH = {"transformer_lm"}
 MATH = {"3xtf32": 0, "tf32": 1, "fp32": 2}
 PROF_NAMES = ["conv_fwd", "conv_dgrad", "conv_wgrad", "gemm", "adamw", "batchnorm"]
 N_WINDOWS = 5
+
+
+def batch_plan(args, world):
+    """(global batch, "weak" | "strong") of this run."""
+    base = args.global_batch or WORKLOADS[args.workload][1]
+    if args.workload in PER_GPU_BATCH and not args.global_batch:
+        return base * world, "weak"
+    return base, "strong"
 
 
 def parse():
@@ -470,12 +481,12 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    global_batch = args.global_batch or WORKLOADS[args.workload][1]
+    global_batch, scaling = batch_plan(args, args.gpus)
     r = cpu_reference_run(args.workload, args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "samples/s", "n_gpus": args.gpus,
         "steps": r["steps"], "warmup": r["warmup"], "ms_per_step": r["ms_per_step"], "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "global_batch": global_batch, "cpu_sample_batch": r["batch"],
                    "note": "CPU restatement of the reference's own training loop (oracle/) on every host core; the Rust "
                            "crate cannot be built here (no cargo/rustc in the image); each step is a bounded sample "
@@ -506,7 +517,7 @@ def run_ours(args):
     cfg = getattr(workloads, WORKLOADS[args.workload][0])
     tokens = bool(cfg.get("token_model"))
     seed = 1234 + WORKLOADS[args.workload][2]
-    global_batch = args.global_batch or WORKLOADS[args.workload][1]
+    global_batch, scaling = batch_plan(args, world)
     b0, b1 = cuda.dp_shard_range(global_batch, rank, world)
     batch = b1 - b0
     rows_per_sample = cfg["in_shape"][0] if tokens else 1
@@ -692,7 +703,7 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": per_s(ms), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "windows": {"n": N_WINDOWS, "steps_each": args.steps, "statistic": "median",
                         "ms_per_step_min": min(windows) / args.steps, "ms_per_step_max": max(windows) / args.steps,
                         "value_min": per_s(max(windows)), "value_max": per_s(min(windows))},

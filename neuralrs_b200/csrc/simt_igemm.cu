@@ -238,12 +238,21 @@ thin_k_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c
 }
 
 // n <= 16, A row-major [m][k]: one warp per output row, lanes stride over k (coalesced reads of
-// the A row), each lane keeps n partial sums, butterfly reduction at the end.
+// the A row), each lane keeps n partial sums, butterfly reduction at the end.  B (k x n, a few KB) is
+// copied to shared memory first when it fits: the n strided reads per k step then cost no L1 round trips.
+constexpr int kThinBFloats = 10240;
 template <bool TB>
 __global__ void __launch_bounds__(256)
-thin_n_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c, const float* __restrict__ bias, int m,
+thin_n_rows_kernel(const float* __restrict__ a, const float* __restrict__ bg, float* c, const float* __restrict__ bias, int m,
                    int n, int k, int act, float beta) {
   NRS_PDL_PROLOGUE();
+  __shared__ float sb[kThinBFloats];
+  const float* b = bg;
+  if (k * n <= kThinBFloats) {
+    for (int i = threadIdx.x; i < k * n; i += blockDim.x) sb[i] = bg[i];
+    __syncthreads();
+    b = sb;
+  }
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= m) return;
@@ -275,21 +284,23 @@ thin_n_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
   }
 }
 
-// n <= 16, A stored [k][m] (a weight gradient X^T . dY): a block owns 32 output rows, lanes are
-// rows (coalesced reads of A[kk][row0..row0+31]), the 8 warps split k and their partial sums are
-// added in warp order through shared memory.
+// n <= 16, A stored [k][m] (a weight gradient X^T . dY): a block owns 8 output rows; a warp is
+// 4 k-groups x 8 rows (32-byte segments of A[kk][row0..row0+7]), so the block's 8 warps split k 32
+// ways, and the 32 partial sums of an output are added in k-group order through shared memory.
+constexpr int kThinColRows = 8, kThinColSplit = 32;
 template <bool TB>
 __global__ void __launch_bounds__(256)
 thin_n_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c, const float* __restrict__ bias, int m,
                    int n, int k, int act, float beta) {
   NRS_PDL_PROLOGUE();
-  __shared__ float part[8][kThinN][33];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int row = blockIdx.x * 32 + lane;
+  __shared__ float part[kThinColSplit][kThinN][kThinColRows + 1];
+  const int lane = threadIdx.x & 31;
+  const int r8 = lane & 7, kg = (threadIdx.x >> 5) * 4 + (lane >> 3);
+  const int row = blockIdx.x * kThinColRows + r8;
   float acc[kThinN];
 #pragma unroll
   for (int j = 0; j < kThinN; ++j) acc[j] = 0.0f;
-  const int per = (k + 7) / 8, k0 = warp * per, k1 = min(k, k0 + per);
+  const int per = (k + kThinColSplit - 1) / kThinColSplit, k0 = kg * per, k1 = min(k, k0 + per);
   if (row < m)
 #pragma unroll 8
     for (int kk = k0; kk < k1; ++kk) {   // unrolled so that several rows of A and B are in flight
@@ -299,18 +310,18 @@ thin_n_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
         if (j < n) acc[j] = fmaf(av, TB ? b[(size_t)j * k + kk] : b[(size_t)kk * n + j], acc[j]);
     }
 #pragma unroll
-  for (int j = 0; j < kThinN; ++j) part[warp][j][lane] = acc[j];
+  for (int j = 0; j < kThinN; ++j) part[kg][j][r8] = acc[j];
   __syncthreads();
-  // thread -> (row r, column j) of the block's 32 x n outputs
-  for (int o = threadIdx.x; o < 32 * n; o += blockDim.x) {
+  // thread -> (row r, column j) of the block's 8 x n outputs
+  for (int o = threadIdx.x; o < kThinColRows * n; o += blockDim.x) {
     const int r = o / n, j = o - r * n;
-    if (blockIdx.x * 32 + r >= m) continue;
+    if (blockIdx.x * kThinColRows + r >= m) continue;
     float v = 0.0f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) v += part[w][j][r];
+    for (int w = 0; w < kThinColSplit; ++w) v += part[w][j][r];
     if (bias) v += bias[j];
     v = nrs_apply_act(v, act);
-    float* dst = c + (size_t)(blockIdx.x * 32 + r) * n + j;
+    float* dst = c + (size_t)(blockIdx.x * kThinColRows + r) * n + j;
     if (beta != 0.0f) v += beta * *dst;
     *dst = v;
   }
@@ -333,7 +344,7 @@ int thin_gemm(nrs_ctx* ctx, int ta, int tb, int m, int n, int k, const float* a,
     if (tb) NRS_PDL_LAUNCH((thin_n_rows_kernel<true>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
     else NRS_PDL_LAUNCH((thin_n_rows_kernel<false>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
   } else {
-    const unsigned blocks = nrs_blocks((size_t)m, 32);
+    const unsigned blocks = nrs_blocks((size_t)m, kThinColRows);
     if (tb) NRS_PDL_LAUNCH((thin_n_cols_kernel<true>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
     else NRS_PDL_LAUNCH((thin_n_cols_kernel<false>), blocks, 256, 0, ctx->stream, a, b, c, bias, m, n, k, act, beta);
   }
