@@ -753,6 +753,7 @@ def run_ours(args):
             line["batchnorm_microbench"] = batchnorm_microbench(ctx, stream, peaks["hbm_gbs"])
             line["hbm_microbench"] = hbm_microbench(ctx, stream, peaks["hbm_gbs"])
             line["attention_microbench"] = attention_microbench(ctx, stream)
+            line["other_configs"] = other_configs(ctx, stream, args.math)
         if world == 1 and not args.no_cpu_baseline:
             r = cpu_reference_run(args.workload, 1, 1, min_seconds=10.0)
             line["cpu_baseline"] = cpu_baseline_entry(r)
@@ -762,6 +763,46 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def other_configs(ctx, stream, math, steps=10):
+    """The other configurations through the same native trainer, resident inputs, one GPU: a short device-timed
+    run each (3 warm-up steps, `steps` timed), so that the default line carries a figure for every configuration."""
+    import numpy as np
+    import torch
+    from neuralrs_b200 import cuda, workloads
+    hp = workloads.ADAMW_HP
+    out = {}
+    for name in ("small_cnn", "transformer_lm", "wide_mlp"):
+        table, batch, seed_off, _ = WORKLOADS[name]
+        cfg = getattr(workloads, table)
+        tokens = bool(cfg.get("token_model"))
+        tr = cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
+                          hp["wd"], fuse=True, ctx=ctx)
+        tr.set_params(workloads.he_init(cfg["layers"], 1234 + seed_off))
+        if tokens:
+            x, t = workloads.synthetic_tokens(cfg, batch, 1234 + seed_off + 10)
+            t = t.reshape(batch, cfg["in_shape"][0])
+        else:
+            x, t = workloads.synthetic_batch(cfg, batch, 1234 + seed_off + 10, uniform01=(name == "small_cnn"))
+        xd, td = torch.from_numpy(np.ascontiguousarray(x)).cuda(), torch.from_numpy(np.ascontiguousarray(t)).cuda()
+        step = tr.step_tokens_device if tokens else tr.step_device
+        for _ in range(3):
+            step(xd.data_ptr(), td.data_ptr(), batch, False)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            step(xd.data_ptr(), td.data_ptr(), batch, False)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        _, step_flop = model_flops_per_sample(cfg["layers"], cfg["in_shape"])
+        out[name] = {"batch": batch, "ms_per_step": ms, "samples_per_s": batch / (ms / 1e3),
+                     "algorithmic_tflops": step_flop * batch / (ms / 1e3) / 1e12, "math": math, "steps": steps}
+        tr.close()
+        del xd, td
+    return out
 
 
 def run_only_microbench(args):

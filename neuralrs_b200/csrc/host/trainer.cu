@@ -334,7 +334,12 @@ void stage_weights(nrs_trainer* t) {
     ws.owner = t;
     ws.mode = ctx->math_mode;
   }
-  nrs::check(ctx, nrs_weight_set_refresh(ctx));
+  if (!ws.fresh) nrs::check(ctx, nrs_weight_set_refresh(ctx));
+}
+
+// Whoever writes a parameter behind the optimizer's back (uploads, checkpoints) calls this.
+void weights_changed(nrs_trainer* t) {
+  if (t->ctx->weight_set.owner == t) t->ctx->weight_set.fresh = false;
 }
 
 // One step's inputs, all on the device: x (float samples) or ids (token models); targets as one-hot rows
@@ -388,16 +393,28 @@ void run_step(nrs_trainer* t, const StepInput& in, bool optimize) {
     // Each bucket is all-reduced on the comm stream as soon as backward has produced it, and its
     // parameters are updated there right behind the reduce (DpGroup::after_bucket), so both overlap
     // the rest of backward; the compute stream joins at the end.
+    // The weight planes of a bucket are restaged there too, behind its update: the next step finds them ready.
     t->opt->begin_flat_step(t->params);
+    ctx->weight_set.refreshed_jobs = 0;
     t->dp->begin_step();
-    nrs::backward_graph_dp(logits, t->dp.get());
-    t->dp->finish();
+    try {
+      nrs::backward_graph_dp(logits, t->dp.get());
+      t->dp->finish();
+    } catch (...) {
+      ctx->weight_set.fresh = false;
+      throw;
+    }
     t->opt->end_flat_step();
+    // every plane was rewritten behind its bucket's update: still fresh; otherwise restage at the next step
+    ctx->weight_set.fresh = ctx->weight_set.n_jobs > 0 && ctx->weight_set.refreshed_jobs == ctx->weight_set.n_jobs;
+    ctx->weight_set.refreshed_jobs = 0;
   } else {
     nrs::backward_graph(logits);
-    if (optimize) t->opt->step(t->params);
+    if (optimize) {
+      t->opt->step(t->params);
+      ctx->weight_set.fresh = false;   // the planes describe the weights before this update
+    }
   }
-  if (optimize) ctx->weight_set.fresh = false;   // the planes describe the weights before this update
 }
 
 void stage(nrs_trainer* t, float** buf, size_t* cap, const float* host, size_t floats) {
@@ -691,6 +708,7 @@ int nrs_trainer_save_checkpoint(nrs_trainer* t, const char* const* names, const 
 
 int nrs_trainer_load_checkpoint(nrs_trainer* t, const char* const* names, const char* path) {
   if (!t || !path) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_load_checkpoint: null handle or path");
+  weights_changed(t);
   return guarded(t->ctx, [&] { load_checkpoint(t, names, path); });
 }
 
@@ -716,6 +734,7 @@ int64_t nrs_trainer_param_len(const nrs_trainer* t, int i) {
 int nrs_trainer_set_param(nrs_trainer* t, int i, const float* host) {
   if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_set_param: null handle");
   NRS_REQUIRE(t->ctx, host && i >= 0 && i < (int)t->params.size(), NRS_ERR_ARG, "nrs_trainer_set_param: bad index or null data");
+  weights_changed(t);
   int st = nrs_h2d(t->ctx, t->params[i]->data, host, t->params[i]->len() * sizeof(float));
   if (st == NRS_OK) st = nrs_sync(t->ctx);
   return st;
@@ -836,8 +855,16 @@ int nrs_trainer_enable_dp(nrs_trainer* t, int rank, int world, const void* uniqu
     if (world > 1) {
       g->register_params(t->params, bucket_bytes);
       // each bucket's parameters are updated right behind its all-reduce, on the comm stream
-      g->after_bucket = [t](const nrs::DpBucket& b) { t->opt->step_flat_range(b.begin, b.end); };
+      g->after_bucket = [t](const nrs::DpBucket& b) {
+        t->opt->step_flat_range(b.begin, b.end);
+        if (t->ctx->weight_set.owner == t && t->ctx->weight_set.fresh) {
+          const nrs::NodeP& last = t->params[b.last_param];
+          nrs::check(t->ctx, nrs_weight_set_refresh_range(t->ctx, t->params[b.first_param]->data, last->data + last->len()));
+        }
+      };
     }
+    // the parameters may have moved into the group's flat block: weight planes are rebuilt at the next step
+    if (ctx->weight_set.owner == t) nrs_weight_set_clear(ctx);
     t->dp = std::move(g);
     t->rank = rank;
     t->world = world;

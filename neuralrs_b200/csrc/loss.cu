@@ -56,8 +56,9 @@ ce_rows_kernel(const float* __restrict__ logits, const float* __restrict__ targe
 // loads (lane l takes float4s l, l+32, ...: 512 contiguous bytes per load instruction), every
 // exponential is evaluated once, the gradient is written once.  Rows of up to 1024 classes whose
 // width is a multiple of four.  With `labels` (int32 class per row) the dense one-hot tensor is not read.
-// Registers hold the logits row and the target row only (the exponentials are recomputed for the gradient:
-// arithmetic is free here, registers are what bounds the rows in flight per SM); three blocks per SM.
+// Registers hold two rows only, which is what bounds the rows in flight per SM (three blocks per SM): the
+// target row, and the logits row that is overwritten by its exponentials once sum(t*x) and sum(t) have been
+// taken (the row loss is lse*sum(t) - sum(t*x)).
 template <int VPL>
 __global__ void __launch_bounds__(256, 3)
 ce_rows_vec_kernel(const float* __restrict__ logits, const float* __restrict__ target, const int32_t* __restrict__ labels,
@@ -85,33 +86,39 @@ ce_rows_vec_kernel(const float* __restrict__ logits, const float* __restrict__ t
         }
       }
     }
+    float stx = 0.0f, st = 0.0f;   // sum(t*x), sum(t) of this lane's elements
 #pragma unroll
     for (int k = 0; k < VPL; ++k)
-      if (lane + 32 * k < c4) mx = fmaxf(mx, fmaxf(fmaxf(x[k].x, x[k].y), fmaxf(x[k].z, x[k].w)));
+      if (lane + 32 * k < c4) {
+        mx = fmaxf(mx, fmaxf(fmaxf(x[k].x, x[k].y), fmaxf(x[k].z, x[k].w)));
+        stx += (t[k].x * x[k].x + t[k].y * x[k].y) + (t[k].z * x[k].z + t[k].w * x[k].w);
+        st += (t[k].x + t[k].y) + (t[k].z + t[k].w);
+      }
     mx = warp_max(mx);
     float se = 0.0f;
 #pragma unroll
     for (int k = 0; k < VPL; ++k)
-      if (lane + 32 * k < c4)
-        se += (expf(x[k].x - mx) + expf(x[k].y - mx)) + (expf(x[k].z - mx) + expf(x[k].w - mx));
+      if (lane + 32 * k < c4) {
+        x[k] = make_float4(expf(x[k].x - mx), expf(x[k].y - mx), expf(x[k].z - mx), expf(x[k].w - mx));
+        se += (x[k].x + x[k].y) + (x[k].z + x[k].w);
+      }
     se = warp_sum(se);
     const float lse = logf(se) + mx;
     const float inv_se = 1.0f / se;
-    float loss = 0.0f;
+    if (grad) {
 #pragma unroll
-    for (int k = 0; k < VPL; ++k) {
-      const int c = lane + 32 * k;
-      if (c < c4) {
-        loss += (-t[k].x * (x[k].x - lse) + -t[k].y * (x[k].y - lse)) + (-t[k].z * (x[k].z - lse) + -t[k].w * (x[k].w - lse));
-        if (grad)
+      for (int k = 0; k < VPL; ++k) {
+        const int c = lane + 32 * k;
+        if (c < c4)
           __stcs(reinterpret_cast<float4*>(grad + base) + c,
-                 make_float4((expf(x[k].x - mx) * inv_se - t[k].x) * inv_div, (expf(x[k].y - mx) * inv_se - t[k].y) * inv_div,
-                             (expf(x[k].z - mx) * inv_se - t[k].z) * inv_div, (expf(x[k].w - mx) * inv_se - t[k].w) * inv_div));
+                 make_float4((x[k].x * inv_se - t[k].x) * inv_div, (x[k].y * inv_se - t[k].y) * inv_div,
+                             (x[k].z * inv_se - t[k].z) * inv_div, (x[k].w * inv_se - t[k].w) * inv_div));
       }
     }
     if (row_loss) {
-      loss = warp_sum(loss);
-      if (lane == 0) row_loss[b] = loss;
+      stx = warp_sum(stx);
+      st = warp_sum(st);
+      if (lane == 0) row_loss[b] = lse * st - stx;
     }
   }
 }

@@ -90,6 +90,10 @@ struct NrsWeightSet {
   const void* owner = nullptr;   // whoever built the set (a trainer); a different owner rebuilds it
   int mode = -1;                 // math mode it was built for
   std::map<std::pair<const void*, int>, NrsWeightPlanes> planes;
+  // per job, in launch order: the weight it reads and its first block (the last entry of job_first is `blocks`)
+  std::vector<const float*> job_src;
+  std::vector<unsigned> job_first;
+  int refreshed_jobs = 0;   // jobs restaged range by range since the last full refresh / reset (refresh_range)
 };
 
 struct nrs_ctx {
@@ -171,6 +175,10 @@ int nrs_check_device_error(nrs_ctx* ctx);
 // fresh and was built for the current mode, else null.
 int nrs_weight_set_build(nrs_ctx* ctx, const NrsWeightDesc* descs, int count);
 int nrs_weight_set_refresh(nrs_ctx* ctx);
+// Restages only the weights stored in [lo, hi) (a bucket of parameters that has just been updated), on the
+// context's current stream; counts the jobs done in refreshed_jobs.  The caller decides when the set as a
+// whole is fresh again.
+int nrs_weight_set_refresh_range(nrs_ctx* ctx, const float* lo, const float* hi);
 void nrs_weight_set_clear(nrs_ctx* ctx);
 inline const NrsWeightPlanes* nrs_weight_planes_find(nrs_ctx* ctx, const void* w, int form) {
   const NrsWeightSet& ws = ctx->weight_set;

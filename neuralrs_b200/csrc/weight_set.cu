@@ -28,17 +28,18 @@ __device__ __forceinline__ void put(float* hi, float* lo, size_t i, float v) {
 }
 
 __global__ void __launch_bounds__(256)
-weight_stage_batch_kernel(const WeightJob* __restrict__ jobs, int n_jobs) {
+weight_stage_batch_kernel(const WeightJob* __restrict__ jobs, int n_jobs, unsigned block_offset) {
   NRS_PDL_PROLOGUE();
   __shared__ float tile[32][33];
-  // the job this block belongs to: the last one whose first_block <= blockIdx.x
+  // the job this block belongs to: the last one whose first_block <= its index in the full launch
+  const unsigned bid = blockIdx.x + block_offset;
   int lo_j = 0, hi_j = n_jobs - 1;
   while (lo_j < hi_j) {
     const int mid = (lo_j + hi_j + 1) >> 1;
-    if (jobs[mid].first_block <= blockIdx.x) lo_j = mid; else hi_j = mid - 1;
+    if (jobs[mid].first_block <= bid) lo_j = mid; else hi_j = mid - 1;
   }
   const WeightJob j = jobs[lo_j];
-  const unsigned blk = blockIdx.x - j.first_block;
+  const unsigned blk = bid - j.first_block;
   if (j.form == NRS_WF_LINEAR_ROWS) {
     // dst[r][k] = src[r*K + k], four consecutive k per thread
     const int q = j.ldk / 4;
@@ -129,6 +130,8 @@ int nrs_weight_set_build(nrs_ctx* ctx, const NrsWeightDesc* descs, int count) {
     else if (d.form == NRS_WF_LINEAR_T) block += (unsigned)(((d.rows + 31) / 32) * (j.ldk / 32));
     else block += (unsigned)(((size_t)d.co * d.ci * d.taps + 255) / 256);
     jobs.push_back(j);
+    ws.job_src.push_back(d.w);
+    ws.job_first.push_back(j.first_block);
     ws.planes[std::make_pair((const void*)d.w, d.form)] = NrsWeightPlanes{j.hi, j.lo, d.rows, d.K, d.co, d.ci, d.taps};
   }
   e = cudaMalloc(&ws.jobs_dev, jobs.size() * sizeof(WeightJob));
@@ -141,6 +144,7 @@ int nrs_weight_set_build(nrs_ctx* ctx, const NrsWeightDesc* descs, int count) {
   }
   ws.n_jobs = (int)jobs.size();
   ws.blocks = block;
+  ws.job_first.push_back(block);
   ws.split = split;
   ws.fresh = false;
   return NRS_OK;
@@ -149,8 +153,29 @@ int nrs_weight_set_build(nrs_ctx* ctx, const NrsWeightDesc* descs, int count) {
 int nrs_weight_set_refresh(nrs_ctx* ctx) {
   NrsWeightSet& ws = ctx->weight_set;
   if (ws.n_jobs == 0) return NRS_OK;
-  NRS_PDL_LAUNCH(weight_stage_batch_kernel, ws.blocks, 256, 0, ctx->stream, (const WeightJob*)ws.jobs_dev, ws.n_jobs);
+  NRS_PDL_LAUNCH(weight_stage_batch_kernel, ws.blocks, 256, 0, ctx->stream, (const WeightJob*)ws.jobs_dev, ws.n_jobs, 0u);
   NRS_LAUNCHED(ctx);
   ws.fresh = true;
+  ws.refreshed_jobs = 0;
+  return NRS_OK;
+}
+
+int nrs_weight_set_refresh_range(nrs_ctx* ctx, const float* lo, const float* hi) {
+  NrsWeightSet& ws = ctx->weight_set;
+  // one launch per run of consecutive jobs whose weight lies in the range (jobs follow the layer order, so
+  // a bucket of adjacent parameters is one run)
+  int j = 0;
+  while (j < ws.n_jobs) {
+    if (ws.job_src[j] < lo || ws.job_src[j] >= hi) { ++j; continue; }
+    int e = j;
+    while (e < ws.n_jobs && ws.job_src[e] >= lo && ws.job_src[e] < hi) ++e;
+    const unsigned first = ws.job_first[j], count = ws.job_first[e] - first;
+    if (count > 0) {
+      NRS_PDL_LAUNCH(weight_stage_batch_kernel, count, 256, 0, ctx->stream, (const WeightJob*)ws.jobs_dev, ws.n_jobs, first);
+      NRS_LAUNCHED(ctx);
+    }
+    ws.refreshed_jobs += e - j;
+    j = e;
+  }
   return NRS_OK;
 }

@@ -65,7 +65,7 @@ def _worker(rank, world, tmp, bucket_bytes, kind):
     tr.enable_dp(rank, world, uid, gb, bucket_bytes)
     b0, b1 = cuda.dp_shard_range(gb, rank, world)
     losses = []
-    for step in range(2):
+    for step in range(3):   # the third step reads weight planes restaged behind the second step's bucket updates
         x, t = _batch(cfg, gb, 50 + step)
         losses.append(_step(tr, cfg, x[b0:b1], t[b0:b1]))
     np.save(Path(tmp) / f"params_{rank}.npy", np.concatenate([tr.get_param(i) for i in range(tr.n_params)]))
@@ -87,7 +87,7 @@ def test_two_gpu_step_matches_single_gpu(tmp_path, gpu_ctx, kind, bucket_bytes):
                       hp["wd"], fuse=True, ctx=gpu_ctx)
     tr.set_params(workloads.he_init(cfg["layers"], 5))
     ref_losses = []
-    for step in range(2):
+    for step in range(3):   # the third step reads weight planes restaged behind the second step's bucket updates
         x, t = _batch(cfg, gb, 50 + step)
         ref_losses.append(_step(tr, cfg, x, t))
     ref = np.concatenate([tr.get_param(i) for i in range(tr.n_params)])
@@ -97,7 +97,7 @@ def test_two_gpu_step_matches_single_gpu(tmp_path, gpu_ctx, kind, bucket_bytes):
     # vs single GPU: summation order only.  (AdamW moves a weight by ~lr whatever the gradient's
     # size, so a near-zero gradient whose sign flips shows up as 2*lr on that one element.)
     assert np.linalg.norm(p0 - ref) <= 1e-4 * np.linalg.norm(ref)
-    assert np.abs(p0 - ref).max() <= 2.5 * hp["lr"] * 2
+    assert np.abs(p0 - ref).max() <= 2.5 * hp["lr"] * 3
     # each rank reports its shard's share of the global-mean loss
     l0, l1 = np.load(tmp_path / "loss_0.npy"), np.load(tmp_path / "loss_1.npy")
     assert np.abs(l0 + l1 - np.array(ref_losses)).max() <= 1e-4
