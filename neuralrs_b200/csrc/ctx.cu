@@ -69,6 +69,15 @@ int nrs_err_flag(nrs_ctx* ctx, int** out) {
   return NRS_OK;
 }
 
+int nrs_fold_ticket(nrs_ctx* ctx, unsigned** out) {
+  if (!ctx->fold_ticket) {
+    NRS_CUDA(ctx, cudaMalloc(&ctx->fold_ticket, sizeof(unsigned)));
+    NRS_CUDA(ctx, cudaMemsetAsync(ctx->fold_ticket, 0, sizeof(unsigned), ctx->stream));
+  }
+  *out = ctx->fold_ticket;
+  return NRS_OK;
+}
+
 int nrs_check_device_error(nrs_ctx* ctx) {
   if (!ctx->err_flag) return NRS_OK;
   int code = 0;
@@ -211,6 +220,7 @@ int nrs_destroy(nrs_ctx* ctx) {
   if (ctx->workspace) cudaFree(ctx->workspace);
   for (int i = 0; i < NRS_WS_COUNT; ++i) if (ctx->ws_slot[i]) cudaFree(ctx->ws_slot[i]);
   if (ctx->err_flag) cudaFree(ctx->err_flag);
+  if (ctx->fold_ticket) cudaFree(ctx->fold_ticket);
   for (auto& r : ctx->prof_records) { cudaEventDestroy(r.start); cudaEventDestroy(r.stop); }
   for (auto& e : ctx->prof_free_events) cudaEventDestroy(e);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);

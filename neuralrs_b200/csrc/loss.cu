@@ -62,16 +62,30 @@ ce_rows_kernel(const float* __restrict__ logits, const float* __restrict__ targe
 template <int VPL>
 __global__ void __launch_bounds__(256, 3)
 ce_rows_vec_kernel(const float* __restrict__ logits, const float* __restrict__ target, const int32_t* __restrict__ labels,
-                   float* __restrict__ row_loss, float* __restrict__ grad, int batch, int classes, float inv_div) {
+                   float* __restrict__ row_loss, float* __restrict__ grad, int batch, int classes, float inv_div,
+                   float* block_partial, unsigned* ticket, float* loss_dev) {
   NRS_PDL_PROLOGUE();
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int c4 = classes >> 2;
+  float warp_loss = 0.0f;   // this warp's rows, in the order it takes them
   for (int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5); b < batch; b += gridDim.x * warps_per_block) {
     const size_t base = (size_t)b * classes;
     float4 x[VPL], t[VPL];
     float mx = -INFINITY;
     const int label = labels ? labels[b] : -1;
+    // the row this warp takes next is pulled into L2 while this one is worked on: a warp is a serial chain
+    // (loads, two reductions, stores), and this takes the DRAM round trip out of the next link
+    {
+      const int nb = b + gridDim.x * warps_per_block;
+      if (nb < batch) {
+        const char* nx = reinterpret_cast<const char*>(logits + (size_t)nb * classes);
+        for (int off = lane * 128; off < classes * 4; off += 32 * 128) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + off));
+          if (target) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(target + (size_t)nb * classes) + off));
+        }
+      }
+    }
     // every load of the row (logits and one-hot row) is in flight before the first reduction waits
 #pragma unroll
     for (int k = 0; k < VPL; ++k) {
@@ -102,7 +116,9 @@ ce_rows_vec_kernel(const float* __restrict__ logits, const float* __restrict__ t
         x[k] = make_float4(expf(x[k].x - mx), expf(x[k].y - mx), expf(x[k].z - mx), expf(x[k].w - mx));
         se += (x[k].x + x[k].y) + (x[k].z + x[k].w);
       }
-    se = warp_sum(se);
+    se = warp_sum(se);          // three independent butterflies: their shuffles interleave
+    stx = warp_sum(stx);
+    st = warp_sum(st);
     const float lse = logf(se) + mx;
     const float inv_se = 1.0f / se;
     if (grad) {
@@ -115,11 +131,34 @@ ce_rows_vec_kernel(const float* __restrict__ logits, const float* __restrict__ t
                              (x[k].z * inv_se - t[k].z) * inv_div, (x[k].w * inv_se - t[k].w) * inv_div));
       }
     }
-    if (row_loss) {
-      stx = warp_sum(stx);
-      st = warp_sum(st);
-      if (lane == 0) row_loss[b] = lse * st - stx;
-    }
+    const float rl = lse * st - stx;
+    if (row_loss && lane == 0) row_loss[b] = rl;
+    warp_loss += rl;
+  }
+  if (!loss_dev) return;
+  // Batch mean without a second launch: warps -> block (warp order) -> block_partial[block]; the block that
+  // arrives last folds the partials in block order (lane l takes l, l+32, ..., then a butterfly), so the order
+  // of the additions is fixed whichever block that is.
+  __shared__ float wsum[32];
+  __shared__ bool last;
+  if (lane == 0) wsum[threadIdx.x >> 5] = warp_loss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.0f;
+    for (int w = 0; w < warps_per_block; ++w) s += wsum[w];
+    block_partial[blockIdx.x] = s;
+    __threadfence();
+    last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!last || threadIdx.x >= 32) return;
+  __threadfence();
+  float s = 0.0f;
+  for (unsigned i = lane; i < gridDim.x; i += 32) s += __ldcg(block_partial + i);
+  s = warp_sum(s);
+  if (lane == 0) {
+    loss_dev[0] = s * inv_div;
+    *ticket = 0;
   }
 }
 
@@ -129,7 +168,16 @@ ce_mean_kernel(const float* __restrict__ row_loss, float* __restrict__ loss_dev,
   NRS_PDL_PROLOGUE();
   __shared__ float sm[32];
   float s = 0.0f;
-  for (int i = threadIdx.x; i < batch; i += blockDim.x) s += row_loss[i];
+  int i = threadIdx.x;
+  const int step = blockDim.x;
+  for (; i + 7 * step < batch; i += 8 * step) {   // eight loads in flight; the additions keep the order of i
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = row_loss[i + u * step];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) s += v[u];
+  }
+  for (; i < batch; i += step) s += row_loss[i];
   s = warp_sum(s);
   if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = s;
   __syncthreads();
@@ -149,29 +197,41 @@ int run_ce(nrs_ctx* ctx, const char* who, const float* logits, const float* targ
     return NRS_OK;
   }
   NRS_REQUIRE(ctx, logits && (target || labels), NRS_ERR_ARG, "%s: null tensor", who);
-  float* rl = row_loss;
-  if (loss_dev && !rl) {
-    void* ws = nullptr;
-    const int st = nrs_workspace(ctx, (size_t)batch * sizeof(float), &ws);
-    if (st != NRS_OK) return st;
-    rl = (float*)ws;
-  }
   const float inv_div = 1.0f / (float)divisor;
   int blocks = (batch + 7) / 8;
   if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+  // wide rows: one resident wave (three blocks of 80 registers per SM) of warps that walk several rows each,
+  // prefetching the next
+  if (classes > 512 && blocks > ctx->sm_count * 3) blocks = ctx->sm_count * 3;
   const bool vec = classes % 4 == 0 && classes <= 1024 &&
                    ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(target) | reinterpret_cast<uintptr_t>(grad)) & 15) == 0;
+  // the vector kernels fold the batch mean themselves (per-block partial sums, last block folds); the scalar
+  // kernel leaves per-row losses to a second launch
+  float* rl = row_loss;
+  float* partial = nullptr;
+  unsigned* ticket = nullptr;
+  if (loss_dev) {
+    void* ws = nullptr;
+    int st = nrs_workspace(ctx, (size_t)(vec ? blocks : (rl ? 0 : batch)) * sizeof(float) + 16, &ws);
+    if (st == NRS_OK && vec) st = nrs_fold_ticket(ctx, &ticket);
+    if (st != NRS_OK) return st;
+    if (vec) partial = (float*)ws;
+    else if (!rl) rl = (float*)ws;
+  }
   if (vec && classes <= 128) {
-    NRS_PDL_LAUNCH(ce_rows_vec_kernel<1>, blocks, 256, 0, ctx->stream, logits, target, labels, rl, grad, batch, classes, inv_div);
+    NRS_PDL_LAUNCH(ce_rows_vec_kernel<1>, blocks, 256, 0, ctx->stream, logits, target, labels, row_loss, grad, batch, classes, inv_div,
+                   partial, ticket, loss_dev);
   } else if (vec && classes <= 512) {
-    NRS_PDL_LAUNCH(ce_rows_vec_kernel<4>, blocks, 256, 0, ctx->stream, logits, target, labels, rl, grad, batch, classes, inv_div);
+    NRS_PDL_LAUNCH(ce_rows_vec_kernel<4>, blocks, 256, 0, ctx->stream, logits, target, labels, row_loss, grad, batch, classes, inv_div,
+                   partial, ticket, loss_dev);
   } else if (vec) {
-    NRS_PDL_LAUNCH(ce_rows_vec_kernel<8>, blocks, 256, 0, ctx->stream, logits, target, labels, rl, grad, batch, classes, inv_div);
+    NRS_PDL_LAUNCH(ce_rows_vec_kernel<8>, blocks, 256, 0, ctx->stream, logits, target, labels, row_loss, grad, batch, classes, inv_div,
+                   partial, ticket, loss_dev);
   } else {
     NRS_PDL_LAUNCH(ce_rows_kernel, blocks, 256, 0, ctx->stream, logits, target, labels, rl, grad, batch, classes, inv_div);
   }
   NRS_LAUNCHED(ctx);
-  if (loss_dev) {
+  if (loss_dev && !vec) {
     NRS_PDL_LAUNCH(ce_mean_kernel, 1, 1024, 0, ctx->stream, rl, loss_dev, batch, inv_div);
     NRS_LAUNCHED(ctx);
   }

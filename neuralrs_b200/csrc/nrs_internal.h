@@ -113,6 +113,7 @@ struct nrs_ctx {
   size_t ws_slot_bytes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   // Device word the tensor-core kernels set when a bounded wait runs out; read at sync points.
   int* err_flag = nullptr;
+  unsigned* fold_ticket = nullptr;   // arrival counter of kernels whose last block folds the blocks' partial sums
   // Planes registered for a source tensor (keyed by its device pointer); the conv kernels
   // use them instead of staging again.  Whoever registers keeps both alive and unregisters.
   std::map<const void*, NrsPlanes> plane_hints;
@@ -161,6 +162,9 @@ int nrs_workspace(nrs_ctx* ctx, size_t bytes, void** out);
 enum { NRS_WS_A_HI = 0, NRS_WS_A_LO = 1, NRS_WS_B_HI = 2, NRS_WS_B_LO = 3, NRS_WS_PARTIAL = 4, NRS_WS_WGRAD_PARTIAL = 5, NRS_WS_COUNT = 8 };
 int nrs_ws_slot(nrs_ctx* ctx, int slot, size_t bytes, void** out);
 int nrs_err_flag(nrs_ctx* ctx, int** out);
+// A zero-initialised device counter for "the last block to arrive folds the partials" reductions; the folding
+// block resets it, so consecutive launches on the context's stream can share it.
+int nrs_fold_ticket(nrs_ctx* ctx, unsigned** out);
 inline const NrsPlanes* nrs_planes_find(nrs_ctx* ctx, const void* src, bool split) {
   auto it = ctx->plane_hints.find(src);
   if (it == ctx->plane_hints.end() || (it->second.split != 0) != split) return nullptr;
