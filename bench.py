@@ -322,6 +322,18 @@ def conv_microbench(ctx, stream, iters=10):
         ms = _time_calls(ctx, stream, fn, iters)
         passes = 2 if "+" in name else 1
         out[name] = {"ms": ms, "tflops": passes * flop / (ms / 1e3) / 1e12}
+    # The same calls with the activations' TF32 planes made once (nrs_planes_cache), which is how a training step
+    # runs them: x is staged once for the forward pass and the weight gradient, dy once for both gradients.
+    _lib.check(ctx.h, l.nrs_planes_cache(ctx.h, P(x), n, ci, h, w))
+    _lib.check(ctx.h, l.nrs_planes_cache(ctx.h, P(dy), n, co, h, w))
+    cached = {}
+    for name, fn in calls.items():
+        ms = _time_calls(ctx, stream, fn, iters)
+        passes = 2 if "+" in name else 1
+        cached[name] = {"ms": ms, "tflops": passes * flop / (ms / 1e3) / 1e12}
+    _lib.check(ctx.h, l.nrs_planes_drop(ctx.h, P(x)))
+    _lib.check(ctx.h, l.nrs_planes_drop(ctx.h, P(dy)))
+    out["operands_cached"] = cached
     return out
 
 

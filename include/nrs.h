@@ -160,6 +160,19 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
                    int n, int ci, int h, int wd, int co, int kh, int kw, int stride, int pad,
                    int accumulate);
 
+/* Operand caching for callers that drive the convolutions operator by operator.  The tensor-core
+ * kernels read an activation as channels-last TF32 planes; nrs_conv2d_fwd / _bwd make them from the
+ * NCHW tensor on every call.  A caller that knows a tensor is read more than once (x by the forward
+ * pass and by the weight gradient; dy by both gradients) has them made once:
+ * nrs_planes_cache(t, [n,c,h,w]) stages the planes of t's CURRENT contents into memory the library
+ * owns and every later convolution call that is given t uses them; nrs_planes_drop(t) forgets them
+ * (required before t's contents change or its memory is freed; dropping an unknown pointer is not an
+ * error).  No-ops (NRS_OK) in FP32 mode and for channel counts the tensor-core path does not take.
+ * The node-level graph and the trainer do this by themselves.  No reference counterpart: its
+ * im2col + GEMM reads f32 tensors directly (src/cuda/nn/conv.rs:244-324). */
+int nrs_planes_cache(nrs_ctx* ctx, const float* t, int n, int c, int h, int w);
+int nrs_planes_drop(nrs_ctx* ctx, const float* t);
+
 /* ------------------------------------------------------------ elementwise -- */
 
 /* out = a + b (src/cuda/graph/add.rs:20-24); out[r,c] = a[r,c] + bias[c]

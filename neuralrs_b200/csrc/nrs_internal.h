@@ -117,6 +117,7 @@ struct nrs_ctx {
   // Planes registered for a source tensor (keyed by its device pointer); the conv kernels
   // use them instead of staging again.  Whoever registers keeps both alive and unregisters.
   std::map<const void*, NrsPlanes> plane_hints;
+  std::map<const void*, NrsPlanes> owned_planes;   // nrs_planes_cache: planes the context itself allocated
   std::map<const void*, NrsOutExtras> out_extras;
   std::map<const void*, NrsColsumRequest> colsum_requests;
   // Patch planes ([pixels][32], see conv_smallc.cu) of an image tensor, keyed by its device pointer:
@@ -165,6 +166,9 @@ int nrs_err_flag(nrs_ctx* ctx, int** out);
 // A zero-initialised device counter for "the last block to arrive folds the partials" reductions; the folding
 // block resets it, so consecutive launches on the context's stream can share it.
 int nrs_fold_ticket(nrs_ctx* ctx, unsigned** out);
+// TF32 planes of a batch of [rows][K] matrices (tc_stage.cu); see tc_mainloop.cuh for the layouts.
+int nrs_tc_stage(nrs_ctx* ctx, const float* src, float* hi, float* lo, int rows, int K, int ldk, int batch,
+                 size_t src_bstride, size_t dst_bstride, bool src_k_by_rows);
 inline const NrsPlanes* nrs_planes_find(nrs_ctx* ctx, const void* src, bool split) {
   auto it = ctx->plane_hints.find(src);
   if (it == ctx->plane_hints.end() || (it->second.split != 0) != split) return nullptr;

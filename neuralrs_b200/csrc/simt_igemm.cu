@@ -517,4 +517,41 @@ int nrs_conv2d_bwd(nrs_ctx* ctx, const float* x, const float* w, const float* dy
   return NRS_OK;
 }
 
+int nrs_planes_drop(nrs_ctx* ctx, const float* t) {
+  NRS_REQUIRE_CTX(ctx);
+  auto it = ctx->owned_planes.find(t);
+  if (it == ctx->owned_planes.end()) return NRS_OK;
+  auto hint = ctx->plane_hints.find(t);
+  if (hint != ctx->plane_hints.end() && hint->second.hi == it->second.hi) ctx->plane_hints.erase(hint);
+  nrs_free(ctx, it->second.hi);
+  if (it->second.lo) nrs_free(ctx, it->second.lo);
+  ctx->owned_planes.erase(it);
+  return NRS_OK;
+}
+
+int nrs_planes_cache(nrs_ctx* ctx, const float* t, int n, int c, int h, int w) {
+  NRS_REQUIRE_CTX(ctx);
+  NRS_REQUIRE(ctx, t != nullptr, NRS_ERR_ARG, "nrs_planes_cache: null tensor");
+  NRS_REQUIRE(ctx, n >= 0 && c > 0 && h > 0 && w > 0, NRS_ERR_SHAPE, "nrs_planes_cache: bad shape [%d,%d,%d,%d]", n, c, h, w);
+  int st = nrs_planes_drop(ctx, t);   // the contents may have changed since an earlier call
+  if (st != NRS_OK) return st;
+  if (ctx->math_mode == NRS_MATH_FP32 || c % 32 != 0 || n == 0 || !tc::tensor_map_encoder()) return NRS_OK;
+  if (ctx->plane_hints.count(t)) return NRS_OK;   // someone else (the node graph) already keeps planes of it
+  const bool split = ctx->math_mode == NRS_MATH_3XTF32;
+  const size_t hw = (size_t)h * w, floats = (size_t)n * c * hw;
+  void *hi = nullptr, *lo = nullptr;
+  st = nrs_alloc(ctx, floats * sizeof(float), 0, &hi);
+  if (st == NRS_OK && split) st = nrs_alloc(ctx, floats * sizeof(float), 0, &lo);
+  if (st == NRS_OK) st = nrs_tc_stage(ctx, t, (float*)hi, (float*)lo, (int)hw, c, c, n, (size_t)c * hw, (size_t)c * hw, true);
+  if (st != NRS_OK) {
+    if (hi) nrs_free(ctx, hi);
+    if (lo) nrs_free(ctx, lo);
+    return st;
+  }
+  const NrsPlanes pl{(float*)hi, (float*)lo, split ? 1 : 0};
+  ctx->owned_planes[t] = pl;
+  ctx->plane_hints[t] = pl;
+  return NRS_OK;
+}
+
 }  // extern "C"

@@ -25,7 +25,8 @@ def math_mode(request, gpu_ctx):
 
 GEMM_SHAPES = [(40, 32, 56), (16, 10, 24), (1, 1, 1), (129, 257, 65), (64, 128, 3136), (256, 512, 1024),
                (300, 1000, 256), (128, 128, 128), (512, 256, 8),
-               (1024, 10, 512), (1024, 512, 10), (512, 10, 1024)]   # classifier head: the thin-product kernel
+               (1024, 10, 512), (1024, 512, 10), (512, 10, 1024),   # classifier head: the thin-product kernels
+               (515, 7, 130), (130, 16, 515), (203, 13, 1027)]      # ... with ragged rows and reduction lengths
 
 
 @pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
@@ -133,6 +134,48 @@ def test_conv2d_fwd_bwd(gpu_ctx, oracle64, math_mode, cfg):
     gw2 = Dev(gpu_ctx, shape=wt.shape)
     call(gpu_ctx, "nrs_conv2d_bwd", dx_, dw_, dyd, None, gw2, None, n, ci, h, w, co, kh, kw, s, p, 0)
     assert np.array_equal(gw2.get(), first)
+
+
+@pytest.mark.parametrize("cfg", [(6, 64, 16, 16, 128, 3, 3, 1, 1), (5, 32, 8, 8, 64, 3, 3, 1, 1), (4, 3, 12, 12, 32, 3, 3, 1, 1)])
+def test_cached_operand_planes_change_nothing(gpu_ctx, math_mode, cfg):
+    """nrs_planes_cache makes a tensor's tensor-core operand once; the convolutions must return the very bits they
+    return when they stage it themselves, stale planes must be droppable, and the calls are no-ops where the
+    tensor-core path does not apply (FP32 mode, 3 channels)."""
+    n, ci, h, w, co, kh, kw, s, p = cfg
+    rng = np.random.default_rng(sum(cfg) + 1)
+    x = rng.normal(size=(n, ci, h, w)).astype(np.float32)
+    wt = (rng.normal(size=(co, ci, kh, kw)) * 0.1).astype(np.float32)
+    dy = rng.normal(size=(n, co, h, w)).astype(np.float32)
+    dx_, dw_, db_, dyd = Dev(gpu_ctx, x), Dev(gpu_ctx, wt), Dev(gpu_ctx, np.zeros(co, np.float32)), Dev(gpu_ctx, dy)
+
+    def run():
+        y, gx, gw = Dev(gpu_ctx, shape=dy.shape), Dev(gpu_ctx, shape=x.shape), Dev(gpu_ctx, shape=wt.shape)
+        call(gpu_ctx, "nrs_conv2d_fwd", dx_, dw_, db_, y, n, ci, h, w, co, kh, kw, s, p, 0)
+        call(gpu_ctx, "nrs_conv2d_bwd", dx_, dw_, dyd, gx, gw, None, n, ci, h, w, co, kh, kw, s, p, 0)
+        return y.get(), gx.get(), gw.get()
+    plain = run()
+    call(gpu_ctx, "nrs_planes_cache", dx_, n, ci, h, w)
+    call(gpu_ctx, "nrs_planes_cache", dyd, n, co, h, w)
+    cached = run()
+    for a, b in zip(plain, cached):
+        assert np.array_equal(a, b)
+    # new contents: drop (or re-cache) first
+    x2 = (x * 0.5 + 1.0).astype(np.float32)
+    call(gpu_ctx, "nrs_planes_drop", dx_)
+    _lib.check(gpu_ctx.h, _lib.lib().nrs_h2d(gpu_ctx.h, dx_.ptr, x2.ctypes.data_as(C.c_void_p), x2.nbytes))
+    gpu_ctx.sync()
+    call(gpu_ctx, "nrs_planes_cache", dx_, n, ci, h, w)
+    again = run()
+    call(gpu_ctx, "nrs_planes_drop", dx_)
+    call(gpu_ctx, "nrs_planes_drop", dyd)
+    call(gpu_ctx, "nrs_planes_drop", dyd)        # dropping twice / an unknown pointer is fine
+    fresh = run()
+    for a, b in zip(again, fresh):
+        assert np.array_equal(a, b)
+    assert not np.array_equal(again[0], plain[0])
+    l = _lib.lib()
+    assert l.nrs_planes_cache(gpu_ctx.h, None, n, ci, h, w) == 1
+    assert l.nrs_planes_cache(gpu_ctx.h, dx_.ptr, n, 0, h, w) == 2
 
 
 def test_conv2d_empty_batch_and_bad_args(gpu_ctx):
