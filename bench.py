@@ -66,7 +66,9 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="vgg_cifar", choices=list(WORKLOADS))
+    ap.add_argument("--workload", default="vgg_cifar", choices=list(WORKLOADS) + ["conv_layer"],
+                    help="a model configuration, or conv_layer: the single-convolution configuration "
+                         "(x[256,64,32,32] -> 128 channels, 3x3) with its batch sharded over the GPUs")
     ap.add_argument("--math", default="3xtf32", choices=list(MATH))
     ap.add_argument("--global-batch", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -817,6 +819,112 @@ def other_configs(ctx, stream, math, steps=10):
     return out
 
 
+def run_conv_layer(args):
+    """The single-convolution configuration at N GPUs: Conv2d x[256,64,32,32] -> 128, 3x3 s1 p1, batch sharded
+    contiguously over the ranks.  Forward and data gradient need no exchange; the weight gradient is summed over
+    the ranks (one 295 KB all-reduce on the library's communicator).  Each pass is timed on its own with CUDA events
+    (max over ranks), activations' operand planes made once as in a training step."""
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    from neuralrs_b200 import _lib, cuda
+    rank, local_rank = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = cuda.Context(local_rank)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx.set_stream(stream.cuda_stream)
+    ctx.set_math_mode(MATH[args.math])
+    l = _lib.lib()
+    global_n, ci, h, w, co = args.global_batch or 256, 64, 32, 32, 128
+    b0, b1 = cuda.dp_shard_range(global_n, rank, world)
+    n = b1 - b0
+    dp = None
+    if world > 1:
+        box = [cuda.dp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        dp = cuda.DataParallel(rank, world, box[0], global_n, timeout_ms=300000.0, ctx=ctx)
+    g = torch.Generator(device="cuda").manual_seed(1236)          # every rank draws the full tensors, keeps its shard
+    x = torch.randn(global_n, ci, h, w, device="cuda", generator=g)[b0:b1].contiguous()
+    wt = torch.randn(co, ci, 3, 3, device="cuda", generator=g) * (2.0 / (ci * 9)) ** 0.5
+    dy = torch.randn(global_n, co, h, w, device="cuda", generator=g)[b0:b1].contiguous()
+    bias = torch.zeros(co, device="cuda")
+    y, dx, dw = torch.empty_like(dy), torch.empty_like(x), torch.empty_like(wt)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    dims = (n, ci, h, w, co, 3, 3, 1, 1)
+
+    def wgrad():
+        st = l.nrs_conv2d_bwd(ctx.h, P(x), P(wt), P(dy), None, P(dw), None, *dims, 0)
+        if st == 0 and dp:
+            dp.all_reduce_sum(dw.data_ptr(), dw.numel())
+        return st
+    calls = {"fwd": lambda: l.nrs_conv2d_fwd(ctx.h, P(x), P(wt), P(bias), P(y), *dims, 0),
+             "dgrad": lambda: l.nrs_conv2d_bwd(ctx.h, P(x), P(wt), P(dy), P(dx), None, None, *dims, 0),
+             "wgrad": wgrad}
+    _lib.check(ctx.h, l.nrs_planes_cache(ctx.h, P(x), n, ci, h, w))
+    _lib.check(ctx.h, l.nrs_planes_cache(ctx.h, P(dy), n, co, h, w))
+    iters, flop = max(args.steps, 1), 2.0 * global_n * co * h * w * ci * 9
+    passes, launches0 = {}, ctx.launch_count()
+    with ClockSampler(local_rank) as clk:
+        for name, fn in calls.items():
+            for _ in range(max(3, args.warmup)):
+                _lib.check(ctx.h, fn())
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(iters):
+                _lib.check(ctx.h, fn())
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            if world > 1:
+                t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            passes[name] = {"ms": ms, "tflops": flop / (ms / 1e3) / 1e12}
+    launches = ctx.launch_count() - launches0
+    # the summed weight gradient is the same on every rank
+    check = None
+    if world > 1:
+        lo, hi = dw.clone(), dw.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        check = {"weight_gradient_identical_on_all_ranks": bool(torch.equal(lo, hi))}
+    if rank == 0:
+        total_ms = sum(p["ms"] for p in passes.values())
+        peaks = measured_peaks()
+        line = {"metric": "conv forward + data gradient + weight gradient, algorithmic TFLOP/s", "value": 3 * flop / (total_ms / 1e3) / 1e12,
+                "unit": "TFLOP/s", "n_gpus": world, "steps": iters, "warmup": max(3, args.warmup), "ms_per_step": total_ms,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "conv_layer", "shape": f"x[{global_n},64,32,32] w[128,64,3,3] s1 p1", "per_gpu_batch": n,
+                           "parallelism": f"dp{world}", "math": args.math,
+                           "operands": "TF32 planes of x and dy made once (nrs_planes_cache), as in a training step",
+                           "l2": "x + dy and their planes are 600 MB per rank at N=1 (75 MB at N=8: below L2 there)"},
+                "passes": passes, "gpu_launches": launches * world, "clocks": clk.summary(),
+                "roofline": {"bound": "tensor", "kernel": "conv (three passes)", "achieved": 3 * flop / (total_ms / 1e3) / 1e12 / world,
+                             "peak": peaks["bf16_sustained"] / 2.0, "unit": "TFLOP/s per GPU",
+                             "frac": 3 * flop / (total_ms / 1e3) / 1e12 / world / (peaks["bf16_sustained"] / 2.0), "traffic": None,
+                             "note": "algorithmic; 3xtf32 issues three times as much"},
+                "e2e": None, "cpu_baseline": None}
+        if check:
+            line["dp_check"] = check
+        print(json.dumps(line), flush=True)
+    _lib.check(ctx.h, l.nrs_planes_drop(ctx.h, P(x)))
+    _lib.check(ctx.h, l.nrs_planes_drop(ctx.h, P(dy)))
+    if dp:
+        dp.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_only_microbench(args):
     import torch
     from neuralrs_b200 import cuda
@@ -843,6 +951,13 @@ def main():
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 500), __file__] + sys.argv[1:]
         raise SystemExit(subprocess.call(cmd))
+    if args.workload == "conv_layer":
+        if args.impl == "reference":
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the reference arm times whole training steps; "
+                                  "run it with a model workload"}), flush=True)
+            return
+        return run_conv_layer(args)
     if args.impl == "reference":
         run_reference(args)
     else:
