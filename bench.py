@@ -77,6 +77,8 @@ def parse():
                     help="N=1: skip the training loops and print only the micro-benchmarks (the command the ncu captures of "
                          "the HBM-bound and attention kernels under profiles/ run)")
     ap.add_argument("--no-fuse", action="store_true")
+    ap.add_argument("--per-rank-batchnorm", action="store_true",
+                    help="at N > 1, normalise with each rank's own shard statistics instead of the global batch's")
     return ap.parse_args()
 
 
@@ -553,6 +555,8 @@ def run_ours(args):
             box = [cuda.dp_unique_id() if rank == 0 else None]
             dist.broadcast_object_list(box, src=0)
             tr.enable_dp(rank, world, box[0], dp_batch)
+            if not args.per_rank_batchnorm:
+                tr.set_sync_batchnorm(True)     # only BatchNorm layers look at it
         return tr
 
     def make_batch(n, s):

@@ -277,6 +277,16 @@ int nrs_dp_unique_id(void* id_out_128_bytes);
 int nrs_trainer_enable_dp(nrs_trainer* t, int rank, int world, const void* unique_id_128_bytes,
                           int global_batch, size_t bucket_bytes);
 int nrs_trainer_set_dp_timeout_ms(nrs_trainer* t, double timeout_ms);
+/* Batch normalisation under data parallelism.  Off (default): every rank normalises with the mean
+ * and variance of its own shard, as the reference would on one GPU with that batch
+ * (src/cuda/nn/batchnorm2d.rs:22-59), so an N-GPU step is NOT the single-GPU full-batch step.
+ * On: the per-channel sums of the forward pass (taken around the running mean, which all ranks share)
+ * and of the backward pass are added up across the ranks together with the element counts (one small
+ * all-reduce per layer and direction, in order on the compute stream), so every rank normalises with
+ * the statistics of the GLOBAL batch, the running statistics stay identical on all ranks, and the
+ * N-GPU step equals the single-GPU step on the full batch up to summation order.  Training mode only;
+ * every rank must set the same value.  No reference counterpart (it is single-GPU). */
+int nrs_trainer_set_sync_batchnorm(nrs_trainer* t, int on);
 
 /* The same exchange for a caller's own loop over nodes (examples/cifar_cuda.rs:267-286 run on
  * several GPUs), without the trainer:

@@ -45,14 +45,15 @@ __device__ __forceinline__ void contribute(float a, float b, float k, float& s, 
 template <bool FWD, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_pair_planes_kernel(const float* __restrict__ a, const float* __restrict__ b, float2* __restrict__ partial, int n,
-                      int c, int hw, int splits, const float* __restrict__ gamma, const float* __restrict__ beta) {
+                      int c, int hw, int splits, const float* __restrict__ gamma, const float* __restrict__ beta,
+                      const float* __restrict__ pivot) {
   NRS_PDL_PROLOGUE();
   __shared__ float2 sm[kThreads / 32];
   const int ch = blockIdx.x, split = blockIdx.y;
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
   const int n_per = (n + splits - 1) / splits;
   const int n0 = split * n_per, n1 = min(n, n0 + n_per);
-  const float k = FWD ? a[(size_t)ch * hw] : 0.0f;
+  const float k = FWD ? (pivot ? pivot[ch] : a[(size_t)ch * hw]) : 0.0f;
   const float ga = RELU ? gamma[ch] : 0.0f, be = RELU ? beta[ch] : 0.0f;
   const bool vec = (hw & 3) == 0 && aligned16(a) && (FWD || aligned16(b));
   // The block's threads walk the split's (image, element) pairs as one flat index, so that planes shorter
@@ -103,7 +104,8 @@ bn_pair_planes_kernel(const float* __restrict__ a, const float* __restrict__ b, 
 template <bool FWD, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_pair_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, float2* __restrict__ partial, int rows,
-                    int cols, int splits, const float* __restrict__ gamma, const float* __restrict__ beta) {
+                    int cols, int splits, const float* __restrict__ gamma, const float* __restrict__ beta,
+                    const float* __restrict__ pivot) {
   NRS_PDL_PROLOGUE();
   __shared__ float2 sm[kThreads / 32][33];
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
@@ -112,7 +114,7 @@ bn_pair_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, fl
   const int r0 = split * rows_per, r1 = min(rows, r0 + rows_per);
   float s = 0.0f, q = 0.0f;
   if (col < cols) {
-    const float k = FWD ? a[col] : 0.0f;
+    const float k = FWD ? (pivot ? pivot[col] : a[col]) : 0.0f;
     const float ga = RELU ? gamma[col] : 0.0f, be = RELU ? beta[col] : 0.0f;
     for (int r = r0 + wrp; r < r1; r += kThreads / 32) {
       const size_t i = (size_t)r * cols + col;
@@ -135,9 +137,12 @@ bn_pair_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, fl
 // One thread per channel folds the splits in order and finishes the statistics: mean, biased variance,
 // running statistics (running = momentum * running + (1 - momentum) * batch value, batchnorm2d.rs:52-53),
 // 1/sqrt(var + eps).  In evaluation mode the running statistics are used as they are (batchnorm2d.rs:57-60).
+// `pivot` / `count_dev` (both or neither): the sums were taken around pivot[ch] (the running mean, read here
+// before it is updated) over *count_dev elements — statistics summed over several processes.
 __global__ void bn_stats_finish_kernel(const float2* __restrict__ partial, const float* __restrict__ x, float* mean,
                                        float* istd, float* running_mean, float* running_var, int c, int hw,
-                                       int splits, float count, float eps, float momentum, int training) {
+                                       int splits, float count, float eps, float momentum, int training,
+                                       const float* __restrict__ pivot, const float* __restrict__ count_dev) {
   NRS_PDL_PROLOGUE();
   const int ch = blockIdx.x * blockDim.x + threadIdx.x;
   if (ch >= c) return;
@@ -152,7 +157,8 @@ __global__ void bn_stats_finish_kernel(const float2* __restrict__ partial, const
     s += t.x;
     q += t.y;
   }
-  const float k = x[(size_t)ch * hw];
+  const float k = pivot ? pivot[ch] : x[(size_t)ch * hw];
+  if (count_dev) count = *count_dev;
   const float d = s / count;
   const float m = k + d;
   const float v = fmaxf(q / count - d * d, 0.0f);
@@ -217,8 +223,9 @@ template <bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_dx_kernel(const float* __restrict__ g, const float* __restrict__ xhat, const float* __restrict__ istd,
              const float* __restrict__ gamma, const float* __restrict__ beta, const float2* __restrict__ sums, float* dx,
-             size_t total, int c, int hw, float count, int training, int accumulate) {
+             size_t total, int c, int hw, float count, int training, int accumulate, const float* __restrict__ count_dev) {
   NRS_PDL_PROLOGUE();
+  if (count_dev) count = *count_dev;   // elements per channel over all processes
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (VEC) {
@@ -269,6 +276,27 @@ bn_dx_kernel(const float* __restrict__ g, const float* __restrict__ xhat, const 
   }
 }
 
+// Statistics shared by several processes: the splits of this process folded in order into out[ch], the
+// element count behind them (one slot), ready for one cross-rank sum of 2c + 1 floats.
+__global__ void bn_fold_for_sync_kernel(const float2* __restrict__ partial, float2* __restrict__ out, float* count_slot,
+                                        int c, int splits, float local_count) {
+  NRS_PDL_PROLOGUE();
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch == 0) *count_slot = local_count;
+  if (ch >= c) return;
+  float s = 0.0f, q = 0.0f;
+  for (int z = 0; z < splits; ++z) {
+    const float2 t = partial[(size_t)z * c + ch];
+    s += t.x;
+    q += t.y;
+  }
+  out[ch] = make_float2(s, q);
+}
+__global__ void bn_set_count_kernel(float* count_slot, float local_count) {
+  NRS_PDL_PROLOGUE();
+  if (blockIdx.x == 0 && threadIdx.x == 0) *count_slot = local_count;
+}
+
 // How many sample splits the per-channel reductions use: enough blocks to fill the device a few times over,
 // no fewer than 8 images (planes) or 64 rows (columns) per block.
 int plan_splits(const nrs_ctx* ctx, int n, int c, int hw) {
@@ -283,13 +311,13 @@ int plan_splits(const nrs_ctx* ctx, int n, int c, int hw) {
 
 template <bool FWD, bool RELU>
 int launch_pair(nrs_ctx* ctx, const float* a, const float* b, float2* partial, int n, int c, int hw, int splits,
-                const float* gamma, const float* beta) {
+                const float* gamma, const float* beta, const float* pivot = nullptr) {
   if (hw == 1) {
     NRS_PDL_LAUNCH((bn_pair_cols_kernel<FWD, RELU>), dim3((c + 31) / 32, splits), kThreads, 0, ctx->stream, a, b, partial, n, c,
-                   splits, gamma, beta);
+                   splits, gamma, beta, pivot);
   } else {
     NRS_PDL_LAUNCH((bn_pair_planes_kernel<FWD, RELU>), dim3(c, splits), kThreads, 0, ctx->stream, a, b, partial, n, c, hw,
-                   splits, gamma, beta);
+                   splits, gamma, beta, pivot);
   }
   NRS_LAUNCHED(ctx);
   return NRS_OK;
@@ -318,17 +346,35 @@ int bn_forward(nrs_ctx* ctx, const char* who, const float* x, const float* gamma
   NRS_REQUIRE(ctx, x && gamma && beta && running_mean && running_var && y && istd, NRS_ERR_ARG, "%s: null tensor", who);
   NrsProfScope prof(ctx, NRS_PROF_BATCHNORM, 12.0 * (double)n * c * hw);   // x in; y, xhat out
   const int splits = training ? plan_splits(ctx, n, c, hw) : 1;
+  // statistics over every process's shard: sums around a pivot all ranks share (the running mean), folded,
+  // summed across ranks together with the element count, then finished as usual
+  const bool shared = training && ctx->stat_sync.all_reduce_sum != nullptr;
   void* ws = nullptr;
-  const int st = nrs_workspace(ctx, ((size_t)splits * c * 2 + c) * sizeof(float), &ws);
+  const int st = nrs_workspace(ctx, ((size_t)splits * c * 2 + c + (size_t)c * 2 + 4) * sizeof(float), &ws);
   if (st != NRS_OK) return st;
   float2* partial = (float2*)ws;
   float* mean = (float*)(partial + (size_t)splits * c);
+  float2* summed = (float2*)(mean + c + (c & 1));   // 8-byte aligned; [c] pairs + the count
+  float* count_slot = (float*)(summed + c);
   if (training) {
-    const int sp = launch_pair<true, false>(ctx, x, nullptr, partial, n, c, hw, splits, nullptr, nullptr);
+    const int sp = launch_pair<true, false>(ctx, x, nullptr, partial, n, c, hw, splits, nullptr, nullptr,
+                                            shared ? running_mean : nullptr);
     if (sp != NRS_OK) return sp;
   }
-  NRS_PDL_LAUNCH(bn_stats_finish_kernel, nrs_blocks(c, 128), 128, 0, ctx->stream, (const float2*)partial, x, mean, istd,
-                 running_mean, running_var, c, hw, splits, (float)((double)n * hw), eps, momentum, training);
+  if (shared) {
+    NRS_PDL_LAUNCH(bn_fold_for_sync_kernel, nrs_blocks(c, 128), 128, 0, ctx->stream, (const float2*)partial, summed, count_slot, c,
+                   splits, (float)((double)n * hw));
+    NRS_LAUNCHED(ctx);
+    const int sr = ctx->stat_sync.all_reduce_sum(ctx->stat_sync.user, (float*)summed, (size_t)c * 2 + 1);
+    if (sr != NRS_OK) return sr;
+    NRS_PDL_LAUNCH(bn_stats_finish_kernel, nrs_blocks(c, 128), 128, 0, ctx->stream, (const float2*)summed, x, mean, istd,
+                   running_mean, running_var, c, hw, 1, 0.0f, eps, momentum, training, (const float*)running_mean,
+                   (const float*)count_slot);
+  } else {
+    NRS_PDL_LAUNCH(bn_stats_finish_kernel, nrs_blocks(c, 128), 128, 0, ctx->stream, (const float2*)partial, x, mean, istd,
+                   running_mean, running_var, c, hw, splits, (float)((double)n * hw), eps, momentum, training,
+                   (const float*)nullptr, (const float*)nullptr);
+  }
   NRS_LAUNCHED(ctx);
   const size_t total = (size_t)n * c * hw;
   const bool vec = (hw & 3) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)xhat & 15) == 0;
@@ -355,10 +401,14 @@ int bn_backward(nrs_ctx* ctx, const char* who, const float* g, const float* xhat
   const bool need_sums = dgamma || training;
   const int splits = need_sums ? plan_splits(ctx, n, c, hw) : 1;
   void* ws = nullptr;
-  const int st = nrs_workspace(ctx, ((size_t)splits * c * 2 + (size_t)c * 2) * sizeof(float), &ws);
+  const int st = nrs_workspace(ctx, ((size_t)splits * c * 2 + (size_t)c * 2 + 4) * sizeof(float), &ws);
   if (st != NRS_OK) return st;
   float2* partial = (float2*)ws;
   float2* sums = partial + (size_t)splits * c;
+  float* count_slot = (float*)(sums + c);
+  // with shared statistics dx needs the sums over every process's shard; the parameter gradients keep this
+  // process's own sums (they are summed across ranks with all other gradients)
+  const bool shared = training && dx && ctx->stat_sync.all_reduce_sum != nullptr;
   if (need_sums) {
     const int sp = relu ? launch_pair<false, true>(ctx, g, xhat, partial, n, c, hw, splits, gamma, beta)
                         : launch_pair<false, false>(ctx, g, xhat, partial, n, c, hw, splits, nullptr, nullptr);
@@ -368,13 +418,19 @@ int bn_backward(nrs_ctx* ctx, const char* who, const float* g, const float* xhat
     NRS_LAUNCHED(ctx);
   }
   if (!dx) return NRS_OK;
+  if (shared) {
+    NRS_PDL_LAUNCH(bn_set_count_kernel, 1, 32, 0, ctx->stream, count_slot, (float)((double)n * hw));
+    NRS_LAUNCHED(ctx);
+    const int sr = ctx->stat_sync.all_reduce_sum(ctx->stat_sync.user, (float*)sums, (size_t)c * 2 + 1);
+    if (sr != NRS_OK) return sr;
+  }
   const size_t total = (size_t)n * c * hw;
   const float count = (float)((double)n * hw);
   const bool vec = (hw & 3) == 0 && ((uintptr_t)g & 15) == 0 && ((uintptr_t)xhat & 15) == 0 && ((uintptr_t)dx & 15) == 0;
   const unsigned blocks = ew_blocks(ctx, vec ? total / 4 : total);
 #define NRS_BN_DX(V, R)                                                                                              \
   NRS_PDL_LAUNCH((bn_dx_kernel<V, R>), blocks, kThreads, 0, ctx->stream, g, xhat, istd, gamma, beta, (const float2*)sums, dx, \
-                 total, c, hw, count, training, accumulate_dx)
+                 total, c, hw, count, training, accumulate_dx, shared ? (const float*)count_slot : (const float*)nullptr)
   if (vec) { if (relu) NRS_BN_DX(true, true); else NRS_BN_DX(true, false); }
   else { if (relu) NRS_BN_DX(false, true); else NRS_BN_DX(false, false); }
 #undef NRS_BN_DX

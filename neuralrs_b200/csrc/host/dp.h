@@ -80,6 +80,7 @@ class DpGroup {
   // All-reduce (sum) of `count` floats at `dev` across the group on the compute stream (small values:
   // the loss share, statistics).
   void all_reduce_sum(float* dev, size_t count);
+  nrs_ctx* context() const { return ctx_; }
 
  private:
   void launch_bucket(size_t index);

@@ -65,6 +65,7 @@ struct nrs_trainer {
   NodeP pos_table;                      // sinusoidal table of the embedding layer (no gradient)
   // data parallel
   int rank = 0, world = 1, global_batch = 0;
+  bool sync_batchnorm = false;          // batch statistics over all ranks' shards (nrs_trainer_set_sync_batchnorm)
   double dp_timeout_ms = 300000.0;      // joining the communicator, and every host wait of a step
   std::unique_ptr<nrs::DpGroup> dp;
   ~nrs_trainer() {
@@ -379,6 +380,26 @@ void run_step(nrs_trainer* t, const StepInput& in, bool optimize) {
 
   nrs::cuda::zero_grad(t->params);
   stage_weights(t);
+  // batch-normalisation statistics over the global batch: the layers find the cross-rank sum in the context
+  // for the duration of this step (forward and backward)
+  struct StatSyncScope {
+    nrs_ctx* c;
+    explicit StatSyncScope(nrs_ctx* ctx, nrs::DpGroup* g) : c(ctx) {
+      if (g) {
+        c->stat_sync.user = g;
+        c->stat_sync.all_reduce_sum = [](void* user, float* dev, size_t count) -> int {
+          nrs::DpGroup* grp = static_cast<nrs::DpGroup*>(user);
+          try {
+            grp->all_reduce_sum(dev, count);
+          } catch (const nrs::Error& e) {
+            return nrs_fail(grp->context(), e.code, "%s", e.what());
+          }
+          return NRS_OK;
+        };
+      }
+    }
+    ~StatSyncScope() { c->stat_sync = NrsStatSync(); }
+  } stat_sync(ctx, t->sync_batchnorm && t->dp && t->world > 1 && t->training ? t->dp.get() : nullptr);
   NodeP logits = forward(t, x, in.ids, (size_t)batch);
   if (logits->shape.size() == 3) logits = nrs::cuda::reshape(logits, {rows, (size_t)t->classes});
   const bool dp = t->dp && t->world > 1 && optimize;
@@ -870,6 +891,12 @@ int nrs_trainer_enable_dp(nrs_trainer* t, int rank, int world, const void* uniqu
     t->world = world;
     t->global_batch = global_batch;
   });
+}
+
+int nrs_trainer_set_sync_batchnorm(nrs_trainer* t, int on) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_set_sync_batchnorm: null handle");
+  t->sync_batchnorm = on != 0;
+  return NRS_OK;
 }
 
 int nrs_trainer_set_dp_timeout_ms(nrs_trainer* t, double timeout_ms) {

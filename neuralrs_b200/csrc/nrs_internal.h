@@ -96,6 +96,14 @@ struct NrsWeightSet {
   int refreshed_jobs = 0;   // jobs restaged range by range since the last full refresh / reset (refresh_range)
 };
 
+// Cross-rank sum of a few per-channel statistics (batch normalisation under data parallelism): set by
+// whoever owns a communicator (the trainer); null = statistics are per process.  Sums `count` floats at
+// `dev` over all ranks in place, in order on the context's stream; every rank must make the same calls.
+struct NrsStatSync {
+  int (*all_reduce_sum)(void* user, float* dev, size_t count) = nullptr;
+  void* user = nullptr;
+};
+
 struct nrs_ctx {
   int device = 0;
   cudaStream_t own_stream = nullptr;
@@ -128,6 +136,7 @@ struct nrs_ctx {
   // Set by a caller that has just issued a kernel whose output the NEXT tensor-core weight-gradient launch
   // does not read (see NRS_PDL_PROLOGUE): that launch may overlap it.  Consumed by the launch.
   bool independent_next = false;
+  NrsStatSync stat_sync;
   // Counter-based generator state of the dropout masks (dropout.cu): seed, and the next unused counter block.
   uint64_t rng_seed = 0, rng_offset = 0;
   // Optional per-family device timing (nrs_profile_*).

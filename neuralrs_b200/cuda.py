@@ -631,6 +631,9 @@ class Trainer:
                                                                      C.byref(loss) if want_loss else None))
         return float(loss.value) if want_loss else None
 
+    def set_sync_batchnorm(self, on: bool = True):
+        check(self.ctx.h, self.ctx._l.nrs_trainer_set_sync_batchnorm(self.h, int(bool(on))))
+
     def set_dp_timeout_ms(self, ms: float):
         check(self.ctx.h, self.ctx._l.nrs_trainer_set_dp_timeout_ms(self.h, C.c_double(ms)))
 

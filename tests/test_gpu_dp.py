@@ -19,9 +19,16 @@ SMALL_LM = dict(name="small_lm", in_shape=(16,), classes=50, vocab=50, token_mod
                         ("linear", 32, 50)])
 
 
+# conv + BatchNorm2d + ReLU, Linear + BatchNorm + ReLU: batch statistics couple the samples of a batch
+SMALL_BN = dict(name="small_bn", in_shape=(3, 8, 8), classes=10,
+                layers=[("conv", 3, 32, 3, 1, 1), ("batchnorm", 32), ("relu",), ("conv", 32, 32, 3, 1, 1), ("batchnorm", 32),
+                        ("relu",), ("maxpool", 2, 2), ("flatten",), ("linear", 512, 64), ("batchnorm", 64), ("relu",),
+                        ("linear", 64, 10)])
+
+
 def _config(kind):
     from neuralrs_b200 import workloads
-    return SMALL_LM if kind == "lm" else workloads.SMALL_CNN
+    return {"lm": SMALL_LM, "bn": SMALL_BN, "bn_local": SMALL_BN}.get(kind, workloads.SMALL_CNN)
 
 
 def _batch(cfg, gb, seed):
@@ -55,7 +62,7 @@ def _worker(rank, world, tmp, bucket_bytes, kind):
     sys.path.insert(0, str(ROOT))
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     from neuralrs_b200 import cuda, workloads
-    cfg, hp, gb = _config(kind), workloads.ADAMW_HP, 64 if kind == "cnn" else 8
+    cfg, hp, gb = _config(kind), workloads.ADAMW_HP, 8 if kind == "lm" else 64
     ctx = cuda.Context(rank)
     uid = _rendezvous(rank, tmp)
     tr = cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
@@ -63,6 +70,8 @@ def _worker(rank, world, tmp, bucket_bytes, kind):
     tr.set_params(workloads.he_init(cfg["layers"], 5))
     tr.set_dp_timeout_ms(120000)
     tr.enable_dp(rank, world, uid, gb, bucket_bytes)
+    if kind == "bn":
+        tr.set_sync_batchnorm(True)
     b0, b1 = cuda.dp_shard_range(gb, rank, world)
     losses = []
     for step in range(3):   # the third step reads weight planes restaged behind the second step's bucket updates
@@ -70,6 +79,8 @@ def _worker(rank, world, tmp, bucket_bytes, kind):
         losses.append(_step(tr, cfg, x[b0:b1], t[b0:b1]))
     np.save(Path(tmp) / f"params_{rank}.npy", np.concatenate([tr.get_param(i) for i in range(tr.n_params)]))
     np.save(Path(tmp) / f"loss_{rank}.npy", np.array(losses))
+    if tr.n_buffers:
+        np.save(Path(tmp) / f"buffers_{rank}.npy", np.concatenate([tr.get_buffer(i) for i in range(tr.n_buffers)]))
     tr.close()
     ctx.close()
 
@@ -101,6 +112,63 @@ def test_two_gpu_step_matches_single_gpu(tmp_path, gpu_ctx, kind, bucket_bytes):
     # each rank reports its shard's share of the global-mean loss
     l0, l1 = np.load(tmp_path / "loss_0.npy"), np.load(tmp_path / "loss_1.npy")
     assert np.abs(l0 + l1 - np.array(ref_losses)).max() <= 1e-4
+
+
+def _bn_run(tmp_path, gpu_ctx, kind):
+    import torch.multiprocessing as mp
+    from neuralrs_b200 import cuda, workloads
+    mp.spawn(_worker, args=(2, str(tmp_path), 4096, kind), nprocs=2, join=True)
+    cfg, hp, gb = SMALL_BN, workloads.ADAMW_HP, 64
+    tr = cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
+                      hp["wd"], fuse=True, ctx=gpu_ctx)
+    tr.set_params(workloads.he_init(cfg["layers"], 5))
+    ref_losses = []
+    for step in range(3):
+        x, t = _batch(cfg, gb, 50 + step)
+        ref_losses.append(_step(tr, cfg, x, t))
+    parts = [tr.get_param(i) for i in range(tr.n_params)]
+    ref = np.concatenate(parts)
+    ref_buf = np.concatenate([tr.get_buffer(i) for i in range(tr.n_buffers)])
+    tr.close()
+    # A bias in front of a BatchNorm layer has a gradient of exactly zero in real arithmetic (the layer removes
+    # the mean); what is computed is rounding noise of either sign, which AdamW's normalisation turns into steps
+    # of a fraction of lr.  Those three vectors are compared with that bound only.
+    keep = np.concatenate([np.full(p.size, i not in (1, 5, 9)) for i, p in enumerate(parts)])
+    p0, p1 = np.load(tmp_path / "params_0.npy"), np.load(tmp_path / "params_1.npy")
+    b0, b1 = np.load(tmp_path / "buffers_0.npy"), np.load(tmp_path / "buffers_1.npy")
+    l0, l1 = np.load(tmp_path / "loss_0.npy"), np.load(tmp_path / "loss_1.npy")
+    return dict(p0=p0, p1=p1, b0=b0, b1=b1, loss=l0 + l1, ref=ref, ref_buf=ref_buf, ref_losses=np.array(ref_losses), lr=hp["lr"],
+                keep=keep)
+
+
+def test_shared_batchnorm_statistics_make_two_gpus_equal_one(tmp_path, gpu_ctx):
+    """With nrs_trainer_set_sync_batchnorm the per-channel sums of both passes are added up across the ranks, so a
+    model with BatchNorm layers trains on two GPUs exactly as on one with the full batch (up to summation order),
+    running statistics included."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _bn_run(tmp_path, gpu_ctx, "bn")
+    assert np.array_equal(r["p0"], r["p1"]) and np.array_equal(r["b0"], r["b1"])
+    k = r["keep"]
+    assert np.linalg.norm((r["p0"] - r["ref"])[k]) <= 1e-4 * np.linalg.norm(r["ref"][k])
+    assert np.abs(r["p0"] - r["ref"]).max() <= 2.5 * r["lr"] * 3
+    # running means carry those biases (a few 1e-5 absolute after three steps); per-rank statistics differ by percents
+    assert np.linalg.norm(r["b0"] - r["ref_buf"]) <= 1e-3 * np.linalg.norm(r["ref_buf"])
+    assert np.abs(r["loss"] - r["ref_losses"]).max() <= 1e-4
+
+
+def test_per_rank_batchnorm_statistics_differ_from_one_gpu(tmp_path, gpu_ctx):
+    """The default (every rank normalises with its own shard's statistics, as the single-GPU reference would with
+    that batch) is a different computation from the full-batch one: the running statistics differ between the
+    ranks and the loss differs from the single-GPU run.  This is what the shared statistics remove."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _bn_run(tmp_path, gpu_ctx, "bn_local")
+    assert np.array_equal(r["p0"], r["p1"])                 # parameters still move together (summed gradients)
+    assert not np.array_equal(r["b0"], r["b1"])             # running statistics are per rank
+    assert np.abs(r["loss"] - r["ref_losses"]).max() > 1e-4
 
 
 def _mlp(seed):
