@@ -575,6 +575,7 @@ def run_ours(args):
         chk_n = 64
         cx, ct = make_batch(chk_n, seed + 99)
         c0, c1 = cuda.dp_shard_range(chk_n, rank, world)
+        _lib.check(ctx.h, l.nrs_rng_seed(ctx.h, C.c_uint64(seed)))     # both runs draw from the start of the same stream
         tr_dp = make_trainer(chk_n)
         xs = torch.from_numpy(np.ascontiguousarray(cx[c0:c1])).cuda()
         ts = torch.from_numpy(np.ascontiguousarray(ct[c0:c1])).cuda()
@@ -589,6 +590,7 @@ def run_ours(args):
         loss_sum = torch.tensor([share], device="cuda", dtype=torch.float64)
         dist.all_reduce(loss_sum)
         if rank == 0:
+            _lib.check(ctx.h, l.nrs_rng_seed(ctx.h, C.c_uint64(seed)))
             tr_one = make_trainer()
             xf, tf = torch.from_numpy(np.ascontiguousarray(cx)).cuda(), torch.from_numpy(np.ascontiguousarray(ct)).cuda()
             full_loss = device_step(tr_one, xf.data_ptr(), tf.data_ptr(), chk_n, True)

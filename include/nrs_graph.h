@@ -287,6 +287,9 @@ int nrs_trainer_set_dp_timeout_ms(nrs_trainer* t, double timeout_ms);
  * N-GPU step equals the single-GPU step on the full batch up to summation order.  Training mode only;
  * every rank must set the same value.  No reference counterpart (it is single-GPU). */
 int nrs_trainer_set_sync_batchnorm(nrs_trainer* t, int on);
+/* Random draws under data parallelism need no call: when a rank's batch is its contiguous share of the
+ * global batch (nrs_dp_shard_range), its dropout masks and augmentation draws are the ones its samples
+ * have in the global batch's counter stream, so N ranks reproduce a single process's draws. */
 
 /* The same exchange for a caller's own loop over nodes (examples/cifar_cuda.rs:267-286 run on
  * several GPUs), without the trainer:

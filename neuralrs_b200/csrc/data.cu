@@ -59,10 +59,16 @@ int nrs_augment_flip_shift(nrs_ctx* ctx, const float* x, float* y, int n, int c,
   NRS_REQUIRE(ctx, max_shift >= 0 && max_shift < 4096, NRS_ERR_ARG, "nrs_augment_flip_shift: bad shift range %d", max_shift);
   if (n == 0) return NRS_OK;
   NRS_REQUIRE(ctx, x && y && x != y, NRS_ERR_ARG, "nrs_augment_flip_shift: null tensor, or input and output are the same");
+  // one block of the stream per image; a data-parallel shard takes the blocks its images have in the global batch
+  uint64_t first = ctx->rng_offset, advance = (uint64_t)n;
+  if (ctx->shard_global > 0 && n == ctx->shard_local) {
+    first += (uint64_t)ctx->shard_begin;
+    advance = (uint64_t)ctx->shard_global;
+  }
   NRS_PDL_LAUNCH(augment_kernel, (unsigned)(n * c), kThreads, 0, ctx->stream, x, y, c, h, w, max_shift, flip, ctx->rng_seed,
-                 ctx->rng_offset);
+                 first);
   NRS_LAUNCHED(ctx);
-  ctx->rng_offset += (uint64_t)n;
+  ctx->rng_offset += advance;
   return NRS_OK;
 }
 

@@ -110,10 +110,12 @@ int nrs_dropout_mask(nrs_ctx* ctx, float* mask, size_t count, float p) {
   // p == 1 drops everything (u < 1 always holds), so the infinite scale is never used: the reference's
   // 1/(1-p) is kept as it is (dropout.rs:38).
   const float scale = 1.0f / (1.0f - p);
+  uint64_t first = 0, advance = 0;
+  nrs_rng_window(ctx, count, &first, &advance);   // a data-parallel shard draws its samples' part of the global mask
   NRS_PDL_LAUNCH(dropout_mask_kernel, ew_blocks(ctx, blocks), kThreads, 0, ctx->stream, mask, count, p, scale, ctx->rng_seed,
-                 ctx->rng_offset);
+                 first);
   NRS_LAUNCHED(ctx);
-  ctx->rng_offset += blocks;
+  ctx->rng_offset += advance;
   return NRS_OK;
 }
 

@@ -338,6 +338,22 @@ void stage_weights(nrs_trainer* t) {
   if (!ws.fresh) nrs::check(ctx, nrs_weight_set_refresh(ctx));
 }
 
+// For the duration of a scope, tells the context which samples of the global batch this rank holds, so that
+// per-sample random draws (dropout masks, augmentation) are the ones a single process would make for them.
+// Applies when the batch is this rank's contiguous share of the global batch (nrs_dp_shard_range).
+struct ShardScope {
+  nrs_ctx* c;
+  ShardScope(nrs_trainer* t, int batch) : c(t->ctx) {
+    if (!t->dp || t->world <= 1) return;
+    int b0 = 0, b1 = 0;
+    if (nrs_dp_shard_range(t->global_batch, t->rank, t->world, &b0, &b1) != NRS_OK || b1 - b0 != batch) return;
+    c->shard_begin = b0;
+    c->shard_local = batch;
+    c->shard_global = t->global_batch;
+  }
+  ~ShardScope() { c->shard_begin = c->shard_local = c->shard_global = 0; }
+};
+
 // Whoever writes a parameter behind the optimizer's back (uploads, checkpoints) calls this.
 void weights_changed(nrs_trainer* t) {
   if (t->ctx->weight_set.owner == t) t->ctx->weight_set.fresh = false;
@@ -400,6 +416,7 @@ void run_step(nrs_trainer* t, const StepInput& in, bool optimize) {
     }
     ~StatSyncScope() { c->stat_sync = NrsStatSync(); }
   } stat_sync(ctx, t->sync_batchnorm && t->dp && t->world > 1 && t->training ? t->dp.get() : nullptr);
+  ShardScope shard(t, batch);
   NodeP logits = forward(t, x, in.ids, (size_t)batch);
   if (logits->shape.size() == 3) logits = nrs::cuda::reshape(logits, {rows, (size_t)t->classes});
   const bool dp = t->dp && t->world > 1 && optimize;
@@ -528,6 +545,7 @@ void step_staged(nrs_trainer* t, float* loss_out) {
     in.x = sl.x;
     if (t->aug_shift >= 0 && t->training && t->in_shape.size() == 3) {
       grow_slot_block(&t->aug_buf, &t->aug_cap, sample_words(t) * sl.batch);
+      ShardScope shard(t, sl.batch);
       nrs::check(t->ctx, nrs_augment_flip_shift(t->ctx, sl.x, t->aug_buf, sl.batch, (int)t->in_shape[0], (int)t->in_shape[1],
                                                 (int)t->in_shape[2], t->aug_shift, t->aug_flip));
       in.x = t->aug_buf;

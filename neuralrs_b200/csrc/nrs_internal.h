@@ -139,6 +139,11 @@ struct nrs_ctx {
   NrsStatSync stat_sync;
   // Counter-based generator state of the dropout masks (dropout.cu): seed, and the next unused counter block.
   uint64_t rng_seed = 0, rng_offset = 0;
+  // A process that works on samples [shard_begin, shard_begin + shard_local) of a batch of shard_global
+  // (data parallelism; set by the trainer for the duration of a step, 0 = off): per-sample random draws
+  // (dropout masks, augmentation) then take the counters those samples have in the GLOBAL batch's stream
+  // and the stream advances by the global batch's amount, so N processes draw what one process would.
+  int shard_begin = 0, shard_local = 0, shard_global = 0;
   // Optional per-family device timing (nrs_profile_*).
   bool profiling = false;
   std::vector<NrsProfRecord> prof_records;
@@ -178,6 +183,20 @@ int nrs_fold_ticket(nrs_ctx* ctx, unsigned** out);
 // TF32 planes of a batch of [rows][K] matrices (tc_stage.cu); see tc_mainloop.cuh for the layouts.
 int nrs_tc_stage(nrs_ctx* ctx, const float* src, float* hi, float* lo, int rows, int K, int ldk, int batch,
                  size_t src_bstride, size_t dst_bstride, bool src_k_by_rows);
+// Counter window of a per-sample draw of `count` elements (count = samples * per-sample) in blocks of four:
+// first block to use and by how many blocks the stream advances.  Falls back to the plain stream (this
+// process's own draws) when no shard is set, the call is not per-sample, or the shard does not start on a
+// block boundary.
+inline void nrs_rng_window(const nrs_ctx* ctx, size_t count, uint64_t* first_block, uint64_t* advance) {
+  *first_block = ctx->rng_offset;
+  *advance = (count + 3) / 4;
+  if (ctx->shard_global <= 0 || ctx->shard_local <= 0 || count % (size_t)ctx->shard_local != 0) return;
+  const size_t per = count / (size_t)ctx->shard_local, before = (size_t)ctx->shard_begin * per;
+  if (before % 4 != 0) return;
+  *first_block = ctx->rng_offset + before / 4;
+  *advance = ((size_t)ctx->shard_global * per + 3) / 4;
+}
+
 inline const NrsPlanes* nrs_planes_find(nrs_ctx* ctx, const void* src, bool split) {
   auto it = ctx->plane_hints.find(src);
   if (it == ctx->plane_hints.end() || (it->second.split != 0) != split) return nullptr;

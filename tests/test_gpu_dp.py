@@ -19,11 +19,12 @@ SMALL_LM = dict(name="small_lm", in_shape=(16,), classes=50, vocab=50, token_mod
                         ("linear", 32, 50)])
 
 
-# conv + BatchNorm2d + ReLU, Linear + BatchNorm + ReLU: batch statistics couple the samples of a batch
+# conv + BatchNorm2d + ReLU, Linear + BatchNorm + ReLU + Dropout: batch statistics couple the samples of a batch,
+# and the dropout mask of a rank's samples must be the one they have in the full batch
 SMALL_BN = dict(name="small_bn", in_shape=(3, 8, 8), classes=10,
                 layers=[("conv", 3, 32, 3, 1, 1), ("batchnorm", 32), ("relu",), ("conv", 32, 32, 3, 1, 1), ("batchnorm", 32),
                         ("relu",), ("maxpool", 2, 2), ("flatten",), ("linear", 512, 64), ("batchnorm", 64), ("relu",),
-                        ("linear", 64, 10)])
+                        ("dropout", 0.25), ("linear", 64, 10)])
 
 
 def _config(kind):
