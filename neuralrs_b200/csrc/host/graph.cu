@@ -832,7 +832,11 @@ NodeP flatten(const NodeP& x) {
 // LayerNorm of x (residual == nullptr) or of x + residual with the add folded into the same kernels
 // (the add + layernorm pairs of src/cuda/nn/transformer_block.rs:33-34,41-42).  One backward launch
 // produces the input gradient(s) and, through per-block partial sums, dgamma / dbeta.
-static NodeP layernorm_impl(const NodeP& x, const NodeP& residual, const NodeP& gamma, const NodeP& beta, float eps) {
+// emit_planes: the caller knows that the result feeds tensor-core GEMMs and that the residual addend's only
+// reader is this node (the transformer block): the forward kernel then writes the result's TF32 planes itself,
+// and the backward kernel those of the addend's gradient, instead of a staging pass per tensor.
+static NodeP layernorm_impl(const NodeP& x, const NodeP& residual, const NodeP& gamma, const NodeP& beta, float eps,
+                            bool emit_planes = false) {
   require_gpu(x, "cuda layernorm: input");
   require_gpu(gamma, "cuda layernorm: gamma");
   require_gpu(beta, "cuda layernorm: beta");
@@ -850,12 +854,33 @@ static NodeP layernorm_impl(const NodeP& x, const NodeP& residual, const NodeP& 
   float* istd = dalloc(ctx, (size_t)rows);
   out->saved.push_back(xhat);
   out->saved.push_back(istd);
-  if (residual)
+  const bool planes = emit_planes && planes_possible(ctx) && f % 32 == 0 && rows > 0;
+  const bool split = ctx->math_mode == NRS_MATH_3XTF32;
+  if (planes && !ctx->plane_hints.count(out->data)) {
+    float* hi = dalloc(ctx, x->len());
+    float* lo = split ? dalloc(ctx, x->len()) : nullptr;
+    int emitted = 0;
+    const int st = nrs_layernorm_fwd_planes(ctx, x->data, residual ? residual->data : nullptr, gamma->data, beta->data, out->data,
+                                            xhat, istd, rows, f, eps, hi, lo, &emitted);
+    if (st == NRS_OK && emitted) {
+      out->planes_hi = hi;
+      out->planes_lo = lo;
+      NrsPlanes pl{hi, lo, split ? 1 : 0};
+      pl.rows = rows;
+      pl.cols = f;
+      ctx->plane_hints[out->data] = pl;
+    } else {
+      nrs_free(ctx, hi);
+      if (lo) nrs_free(ctx, lo);
+    }
+    check(ctx, st);
+  } else if (residual) {
     check(ctx, nrs_layernorm_residual_fwd(ctx, x->data, residual->data, gamma->data, beta->data, out->data, xhat, istd, rows, f, eps));
-  else
+  } else {
     check(ctx, nrs_layernorm_fwd(ctx, x->data, gamma->data, beta->data, out->data, xhat, istd, rows, f, eps));
+  }
   Node* self = out.get();
-  out->backward_fn = [self, x, residual, gamma, beta, xhat, istd, rows, f]() {
+  out->backward_fn = [self, x, residual, gamma, beta, xhat, istd, rows, f, planes, split]() {
     nrs_ctx* ctx = self->ctx;
     const float* g = grad_in(self);
     float *da = nullptr, *db = nullptr, *dg = nullptr, *dbt = nullptr;
@@ -887,8 +912,47 @@ static NodeP layernorm_impl(const NodeP& x, const NodeP& residual, const NodeP& 
       dbt = tb.ptr;
       acc_p = tg.accumulate;
     }
-    if (da || db || dg)
-      check(ctx, nrs_layernorm_residual_bwd(ctx, g, xhat, istd, gamma->data, da, db, dg, dbt, rows, f, acc_a, acc_b, acc_p));
+    if (!(da || db || dg)) return;
+    Node* rb = db ? grad_root(residual.get()) : nullptr;
+    // planes an earlier backward pass over this graph left with the addend describe its old gradient
+    auto hint = db ? ctx->plane_hints.find(db) : ctx->plane_hints.end();
+    const bool mine = rb && rb->gplanes_hi && hint != ctx->plane_hints.end() && hint->second.hi == rb->gplanes_hi &&
+                      (hint->second.split != 0) == split;
+    const bool fresh_slot = rb && !rb->gplanes_hi && hint == ctx->plane_hints.end();
+    if (planes && da && db && acc_b == 0 && (mine || fresh_slot)) {
+      // the addend's gradient is exactly this kernel's result: its planes come out of the same pass
+      float* hi = mine ? rb->gplanes_hi : dalloc(ctx, self->len());
+      float* lo = mine ? rb->gplanes_lo : (split ? dalloc(ctx, self->len()) : nullptr);
+      int emitted = 0;
+      const int st = nrs_layernorm_bwd_planes(ctx, g, xhat, istd, gamma->data, da, db, dg, dbt, rows, f, acc_a, acc_b, acc_p, hi, lo,
+                                              &emitted);
+      if (st == NRS_OK && emitted) {
+        if (!mine) {
+          rb->gplanes_hi = hi;
+          rb->gplanes_lo = lo;
+          NrsPlanes pl{hi, lo, split ? 1 : 0};
+          pl.rows = rows;
+          pl.cols = f;
+          ctx->plane_hints[db] = pl;   // dropped with the node (keyed by its gradient buffer)
+        }
+      } else {
+        if (mine) {
+          ctx->plane_hints.erase(db);
+          rb->gplanes_hi = rb->gplanes_lo = nullptr;
+        }
+        nrs_free(ctx, hi);
+        if (lo) nrs_free(ctx, lo);
+      }
+      check(ctx, st);
+      return;
+    }
+    if (mine) {   // this pass adds to the gradient (or stages nothing): the old planes must go
+      ctx->plane_hints.erase(db);
+      nrs_free(ctx, rb->gplanes_hi);
+      if (rb->gplanes_lo) nrs_free(ctx, rb->gplanes_lo);
+      rb->gplanes_hi = rb->gplanes_lo = nullptr;
+    }
+    check(ctx, nrs_layernorm_residual_bwd(ctx, g, xhat, istd, gamma->data, da, db, dg, dbt, rows, f, acc_a, acc_b, acc_p));
   };
   return out;
 }
@@ -897,9 +961,10 @@ NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps
   return layernorm_impl(x, nullptr, gamma, beta, eps);
 }
 
-NodeP layernorm_residual(const NodeP& x, const NodeP& residual, const NodeP& gamma, const NodeP& beta, float eps) {
+NodeP layernorm_residual(const NodeP& x, const NodeP& residual, const NodeP& gamma, const NodeP& beta, float eps,
+                         bool emit_planes) {
   if (!residual) fail(NRS_ERR_ARG, "cuda layernorm: null residual");
-  return layernorm_impl(x, residual, gamma, beta, eps);
+  return layernorm_impl(x, residual, gamma, beta, eps, emit_planes);
 }
 
 // batchnorm (src/cuda/nn/batchnorm.rs:110-232) for [batch, features] and batchnorm2d

@@ -131,7 +131,10 @@ NodeP flatten(const NodeP& x);
 NodeP layernorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, float eps);
 // layernorm(add(x, residual), ...) as one operator: the sum is never written, and the backward pass
 // hands the input gradient to both addends from one kernel.  Same values as the two-operator form.
-NodeP layernorm_residual(const NodeP& x, const NodeP& residual, const NodeP& gamma, const NodeP& beta, float eps);
+// emit_planes: see layernorm_impl (graph.cu): only for callers that know the result's readers are tensor-core
+// GEMMs and that `residual` has no other reader.
+NodeP layernorm_residual(const NodeP& x, const NodeP& residual, const NodeP& gamma, const NodeP& beta, float eps,
+                         bool emit_planes = false);
 // batchnorm.rs / batchnorm2d.rs: running_mean / running_var are resident nodes updated in place when training
 NodeP batchnorm(const NodeP& x, const NodeP& gamma, const NodeP& beta, const NodeP& running_mean,
                 const NodeP& running_var, float momentum, float eps, bool training);

@@ -225,7 +225,7 @@ static NodeP block_body(const TransformerBlock& b, const NodeP& x, bool final_no
   if (!x || x->shape.size() != 3) fail(NRS_ERR_SHAPE, "cuda transformer block: input must be [batch, seq, d_model]");
   const size_t batch = x->shape[0], seq = x->shape[1], d = x->shape[2];
   NodeP attn_out = b.mha.forward_batch(x);
-  NodeP x1 = b.fused_epilogues ? layernorm_residual(x, attn_out, b.norm1.gamma, b.norm1.beta, b.norm1.eps)
+  NodeP x1 = b.fused_epilogues ? layernorm_residual(x, attn_out, b.norm1.gamma, b.norm1.beta, b.norm1.eps, true)
                                : b.norm1.forward(add(x, attn_out));
   NodeP flat = reshape(x1, {batch * seq, d});
   NodeP h, ff;
@@ -238,7 +238,7 @@ static NodeP block_body(const TransformerBlock& b, const NodeP& x, bool final_no
     ff = b.ff2.forward(h);
   }
   NodeP ff_out = reshape(ff, {batch, seq, d});
-  if (final_norm && b.fused_epilogues) return layernorm_residual(x1, ff_out, b.norm2.gamma, b.norm2.beta, b.norm2.eps);
+  if (final_norm && b.fused_epilogues) return layernorm_residual(x1, ff_out, b.norm2.gamma, b.norm2.beta, b.norm2.eps, true);
   NodeP x2 = add(x1, ff_out);
   return final_norm ? b.norm2.forward(x2) : x2;
 }

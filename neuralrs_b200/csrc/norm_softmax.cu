@@ -13,8 +13,17 @@
 // softmax_forward / softmax_backward (src/cuda/graph/softmax.rs:12-35); CPU
 // semantics src/nn/normalization.rs:38-103, src/autograd/graph/softmax.rs:23-60.
 #include "nrs_internal.h"
+#include "tc_common.cuh"
 
 namespace {
+
+// The TF32 operand planes of a value that the next tensor-core GEMM will read (rows x f, the tensor's own
+// layout): written by the producing kernel so that no separate staging pass reads the tensor again.
+__device__ __forceinline__ void put_planes(float* hi, float* lo, size_t at, float4 v) {
+  const float4 h = make_float4(tc::tf32_rn(v.x), tc::tf32_rn(v.y), tc::tf32_rn(v.z), tc::tf32_rn(v.w));
+  *reinterpret_cast<float4*>(hi + at) = h;
+  if (lo) *reinterpret_cast<float4*>(lo + at) = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+}
 
 __device__ __forceinline__ float wsum(float v) {
 #pragma unroll
@@ -42,7 +51,8 @@ template <int VPL>
 __global__ void __launch_bounds__(kRowThreads)
 ln_fwd_vec_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ gamma,
                   const float* __restrict__ beta, float* __restrict__ y, float* __restrict__ xhat,
-                  float* __restrict__ istd_out, int rows, int f, float eps) {
+                  float* __restrict__ istd_out, int rows, int f, float eps, float* __restrict__ y_hi,
+                  float* __restrict__ y_lo) {
   NRS_PDL_PROLOGUE();
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   const int f4 = f >> 2;
@@ -83,7 +93,9 @@ ln_fwd_vec_kernel(const float* __restrict__ a, const float* __restrict__ b, cons
         xn.x = (v[k].x - mean) * istd; xn.y = (v[k].y - mean) * istd;
         xn.z = (v[k].z - mean) * istd; xn.w = (v[k].w - mean) * istd;
         if (xhat) st4_stream(xhat + base + 4 * c, xn);
-        st4_stream(y + base + 4 * c, make_float4(gm.x * xn.x + bt.x, gm.y * xn.y + bt.y, gm.z * xn.z + bt.z, gm.w * xn.w + bt.w));
+        const float4 out = make_float4(gm.x * xn.x + bt.x, gm.y * xn.y + bt.y, gm.z * xn.z + bt.z, gm.w * xn.w + bt.w);
+        st4_stream(y + base + 4 * c, out);
+        if (y_hi) put_planes(y_hi, y_lo, base + 4 * c, out);
       }
     }
   }
@@ -122,7 +134,7 @@ template <int VPL>
 __global__ void __launch_bounds__(kRowThreads)
 ln_bwd_vec_kernel(const float* __restrict__ g, const float* __restrict__ xhat, const float* __restrict__ istd,
                   const float* __restrict__ gamma, float* dx, float* dx2, float* __restrict__ partial, int rows, int f,
-                  int acc1, int acc2) {
+                  int acc1, int acc2, float* __restrict__ d_hi, float* __restrict__ d_lo) {
   NRS_PDL_PROLOGUE();
   extern __shared__ float ln_smem[];          // [warps][2][f] when partial != nullptr
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
@@ -166,6 +178,7 @@ ln_bwd_vec_kernel(const float* __restrict__ g, const float* __restrict__ xhat, c
           float4 o;
           o.x = is * (gv[k].x - s1 - xh[k].x * s2); o.y = is * (gv[k].y - s1 - xh[k].y * s2);
           o.z = is * (gv[k].z - s1 - xh[k].z * s2); o.w = is * (gv[k].w - s1 - xh[k].w * s2);
+          if (d_hi) put_planes(d_hi, d_lo, base + 4 * c, o);   // planes of the gradient itself (before any accumulation)
           float4 w = o;
           if (acc1) { const float4 old = ld4(dx + base + 4 * c); w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w; }
           st4(dx + base + 4 * c, w);
@@ -409,14 +422,17 @@ int vec_vpl(int width, std::initializer_list<const void*> ptrs) {
   } while (0)
 
 int layernorm_fwd(nrs_ctx* ctx, const char* who, const float* a, const float* b, const float* gamma, const float* beta,
-                  float* y, float* xhat, float* istd, int rows, int f, float eps) {
+                  float* y, float* xhat, float* istd, int rows, int f, float eps, float* y_hi = nullptr, float* y_lo = nullptr,
+                  int* emitted = nullptr) {
+  if (emitted) *emitted = 0;
   NRS_REQUIRE(ctx, rows >= 0 && f > 0, NRS_ERR_SHAPE, "%s: bad shape [%d,%d]", who, rows, f);
   if (rows == 0) return NRS_OK;
   NRS_REQUIRE(ctx, a && gamma && beta && y, NRS_ERR_ARG, "%s: null tensor", who);
-  const int vpl = vec_vpl(f, {a, b, gamma, beta, y, xhat});
+  const int vpl = vec_vpl(f, {a, b, gamma, beta, y, xhat, y_hi, y_lo});
   if (vpl) {
     NRS_DISPATCH_VPL(vpl, NRS_PDL_LAUNCH(ln_fwd_vec_kernel<V>, row_grid(ctx, rows), kRowThreads, 0, ctx->stream, a, b, gamma, beta, y,
-                                         xhat, istd, rows, f, eps));
+                                         xhat, istd, rows, f, eps, y_hi, y_lo));
+    if (emitted && y_hi) *emitted = 1;
   } else {
     NRS_PDL_LAUNCH(ln_fwd_kernel, row_grid(ctx, rows), kRowThreads, 0, ctx->stream, a, b, gamma, beta, y, xhat, istd, rows, f, eps);
   }
@@ -425,7 +441,9 @@ int layernorm_fwd(nrs_ctx* ctx, const char* who, const float* a, const float* b,
 }
 
 int layernorm_bwd(nrs_ctx* ctx, const char* who, const float* g, const float* xhat, const float* istd, const float* gamma,
-                  float* dx, float* dx2, float* dgamma, float* dbeta, int rows, int f, int acc1, int acc2, int accumulate_params) {
+                  float* dx, float* dx2, float* dgamma, float* dbeta, int rows, int f, int acc1, int acc2, int accumulate_params,
+                  float* d_hi = nullptr, float* d_lo = nullptr, int* emitted = nullptr) {
+  if (emitted) *emitted = 0;
   NRS_REQUIRE(ctx, rows >= 0 && f > 0, NRS_ERR_SHAPE, "%s: bad shape [%d,%d]", who, rows, f);
   NRS_REQUIRE(ctx, (dgamma == nullptr) == (dbeta == nullptr), NRS_ERR_ARG, "%s: dgamma and dbeta must be given together", who);
   NRS_REQUIRE(ctx, dx || !dx2, NRS_ERR_ARG, "%s: a second input gradient without the first", who);
@@ -438,7 +456,7 @@ int layernorm_bwd(nrs_ctx* ctx, const char* who, const float* g, const float* xh
   }
   NRS_REQUIRE(ctx, g && xhat && istd && gamma, NRS_ERR_ARG, "%s: null tensor", who);
   if (!dx && !dgamma) return NRS_OK;
-  const int vpl = vec_vpl(f, {g, xhat, gamma, dx, dx2});
+  const int vpl = vec_vpl(f, {g, xhat, gamma, dx, dx2, d_hi, d_lo});
   if (vpl) {
     // one pass over g and xhat for everything; the block size keeps the per-warp column partials within 32 KB
     int warps = 8;
@@ -454,7 +472,8 @@ int layernorm_bwd(nrs_ctx* ctx, const char* who, const float* g, const float* xh
     }
     const size_t smem = dgamma ? (size_t)warps * 2 * f * sizeof(float) : 0;
     NRS_DISPATCH_VPL(vpl, NRS_PDL_LAUNCH(ln_bwd_vec_kernel<V>, blocks, warps * 32, smem, ctx->stream, g, xhat, istd, gamma, dx, dx2,
-                                         partial, rows, f, acc1, acc2));
+                                         partial, rows, f, acc1, acc2, dx ? d_hi : nullptr, dx ? d_lo : nullptr));
+    if (emitted && dx && d_hi) *emitted = 1;
     NRS_LAUNCHED(ctx);
     if (dgamma) {
       NRS_PDL_LAUNCH(ln_param_fold_kernel, nrs_blocks(2 * (size_t)f, 32), 256, 0, ctx->stream, (const float*)partial, dgamma, dbeta, f,
@@ -520,6 +539,26 @@ int nrs_layernorm_residual_bwd(nrs_ctx* ctx, const float* g, const float* xhat, 
   const int acc_first = da ? accumulate_da : accumulate_db;
   return layernorm_bwd(ctx, "nrs_layernorm_residual_bwd", g, xhat, istd, gamma, first, second, dgamma, dbeta, rows, f, acc_first,
                        accumulate_db, accumulate_params);
+}
+
+// The same two operators with the TF32 planes of their result written by the kernel itself (y forward; the
+// input gradient backward): *emitted = 1 when the planes were written (vector path), 0 when the caller has
+// to stage them itself.  Internal: the graph's fused transformer block calls them.
+int nrs_layernorm_fwd_planes(nrs_ctx* ctx, const float* a, const float* b, const float* gamma, const float* beta, float* y,
+                             float* xhat, float* istd, int rows, int f, float eps, float* y_hi, float* y_lo, int* emitted) {
+  NRS_REQUIRE_CTX(ctx);
+  return layernorm_fwd(ctx, "nrs_layernorm_fwd_planes", a, b, gamma, beta, y, xhat, istd, rows, f, eps, y_hi, y_lo, emitted);
+}
+
+int nrs_layernorm_bwd_planes(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd, const float* gamma, float* da,
+                             float* db, float* dgamma, float* dbeta, int rows, int f, int accumulate_da, int accumulate_db,
+                             int accumulate_params, float* d_hi, float* d_lo, int* emitted) {
+  NRS_REQUIRE_CTX(ctx);
+  float* first = da ? da : db;
+  float* second = da ? db : nullptr;
+  const int acc_first = da ? accumulate_da : accumulate_db;
+  return layernorm_bwd(ctx, "nrs_layernorm_bwd_planes", g, xhat, istd, gamma, first, second, dgamma, dbeta, rows, f, acc_first,
+                       accumulate_db, accumulate_params, d_hi, d_lo, emitted);
 }
 
 int nrs_softmax_fwd(nrs_ctx* ctx, const float* x, float* y, int rows, int width) {

@@ -180,6 +180,13 @@ int nrs_err_flag(nrs_ctx* ctx, int** out);
 // A zero-initialised device counter for "the last block to arrive folds the partials" reductions; the folding
 // block resets it, so consecutive launches on the context's stream can share it.
 int nrs_fold_ticket(nrs_ctx* ctx, unsigned** out);
+// LayerNorm with the TF32 planes of its result written by the kernel (norm_softmax.cu).
+extern "C" int nrs_layernorm_fwd_planes(nrs_ctx* ctx, const float* a, const float* b, const float* gamma, const float* beta,
+                                        float* y, float* xhat, float* istd, int rows, int f, float eps, float* y_hi, float* y_lo,
+                                        int* emitted);
+extern "C" int nrs_layernorm_bwd_planes(nrs_ctx* ctx, const float* g, const float* xhat, const float* istd, const float* gamma,
+                                        float* da, float* db, float* dgamma, float* dbeta, int rows, int f, int accumulate_da,
+                                        int accumulate_db, int accumulate_params, float* d_hi, float* d_lo, int* emitted);
 // TF32 planes of a batch of [rows][K] matrices (tc_stage.cu); see tc_mainloop.cuh for the layouts.
 int nrs_tc_stage(nrs_ctx* ctx, const float* src, float* hi, float* lo, int rows, int K, int ldk, int batch,
                  size_t src_bstride, size_t dst_bstride, bool src_k_by_rows);
