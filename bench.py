@@ -694,13 +694,32 @@ def run_ours(args):
         dist.all_reduce(lt)
         loss = float(lt.item())
 
+    def lagged_loop(total):
+        """The same with every step's loss read one step behind (nrs_trainer_step_staged_lagged): step i is issued,
+        then the host waits for the loss of step i-1 only; the last step's loss is read (synchronously) inside the
+        timed region too, so K steps read K losses."""
+        def fn(i):
+            if i == 0:
+                stage(0)
+            if i + 1 < total:
+                stage((i + 1) % n_sets)
+            tr.step_staged_lagged()
+            if i + 1 == total:
+                tr.last_loss()
+        return fn
+
     for i in range(2):
         host_step(i)
     ms_e2e_plain = timed(host_step, args.steps)
     warm = staged_loop(2)
     for i in range(2):
         warm(i)
-    e2e_windows = [timed(staged_loop(args.steps), args.steps) for _ in range(3)]
+    sync_windows = [timed(staged_loop(args.steps), args.steps) for _ in range(3)]
+    ms_e2e_sync = statistics.median(sync_windows)
+    warm = lagged_loop(2)
+    for i in range(2):
+        warm(i)
+    e2e_windows = [timed(lagged_loop(args.steps), args.steps) for _ in range(3)]
     ms_e2e = statistics.median(e2e_windows)
 
     if rank == 0:
@@ -726,6 +745,7 @@ def run_ours(args):
             "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "windows": {"n": N_WINDOWS, "steps_each": args.steps, "statistic": "median",
                         "ms_per_step_min": min(windows) / args.steps, "ms_per_step_max": max(windows) / args.steps,
+                        "ms_per_step_in_order": [w / args.steps for w in windows],
                         "value_min": per_s(max(windows)), "value_max": per_s(min(windows))},
             "config": {"workload": args.workload, "global_batch": global_batch, "per_gpu_batch": batch,
                        "parallelism": f"dp{world}", "math": args.math, "fused_epilogues": not args.no_fuse,
@@ -738,8 +758,13 @@ def run_ours(args):
             "e2e": {"value": per_s(ms_e2e), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": x_bytes + t_bytes, "d2h_bytes_per_step": 4 * world,
                     "windows": {"n": len(e2e_windows), "statistic": "median", "value_min": per_s(max(e2e_windows)),
-                                "value_max": per_s(min(e2e_windows))},
-                    "api": "nrs_trainer_stage_next%s + nrs_trainer_step_staged: the copy of batch i+1 overlaps step i" % ("_tokens" if tokens else ""),
+                                "value_max": per_s(min(e2e_windows)),
+                                "ms_per_step_in_order": [w / args.steps for w in e2e_windows]},
+                    "api": "nrs_trainer_stage_next%s + nrs_trainer_step_staged_lagged: the copy of batch i+1 overlaps step i and "
+                           "the loss of step i is read after step i+1 has been issued (every step's loss is read inside the "
+                           "timed region, the last one synchronously)" % ("_tokens" if tokens else ""),
+                    "synchronous_loss_value": per_s(ms_e2e_sync),
+                    "synchronous_loss_api": "nrs_trainer_step_staged: the loss of step i is read before step i+1 is issued",
                     "unpipelined_value": per_s(ms_e2e_plain),
                     "unpipelined_api": "nrs_trainer_step%s: copy, step and loss read-back in sequence" % ("_tokens" if tokens else "")},
             "gpu_launches": launches * world,

@@ -229,6 +229,16 @@ int nrs_trainer_step(nrs_trainer* t, const float* x_host, const float* target_ho
  * them has been issued and the stream synchronised (loss_out != NULL does that). */
 int nrs_trainer_stage_next(nrs_trainer* t, const float* x_host, const float* target_host, int batch);
 int nrs_trainer_step_staged(nrs_trainer* t, float* loss_out);
+/* The same step with the loss read one step behind: the step is issued, an asynchronous copy of ITS loss
+ * into a pinned slot is queued behind it, and the call returns the loss of the PREVIOUS lagged step
+ * (*have_prev = 0 on the first call, when there is none) after waiting for that earlier copy only.  The
+ * host thus stays one step ahead of the device, which never idles while the next step is being enqueued
+ * (a read-back of the step just issued drains the stream first: a fifth of the step at small batches).
+ * Every step's loss is still read, in order; nrs_trainer_last_loss returns the newest one (and is where
+ * a device-side error of a lagged step is reported).  Under data parallelism the wait runs through the
+ * group's deadline.  The reference reads its loss synchronously every step
+ * (src/cuda/loss/cross_entropy.rs:96-97). */
+int nrs_trainer_step_staged_lagged(nrs_trainer* t, float* prev_loss_out, int* have_prev);
 /* As nrs_trainer_stage_next with int32 class indices instead of one-hot rows
  * (batch * 4 bytes over the bus instead of batch * classes * 4); the loss kernel
  * reads them directly (nrs_ce_fwd_bwd_indexed). */

@@ -353,7 +353,16 @@ void DpGroup::host_wait(cudaStream_t stream) {
     return;
   }
   if (cudaEventRecord(wait_ev_, stream) != cudaSuccess) fail(NRS_ERR_CUDA, "data parallel: event record failed");
-  WaitState w{wait_ev_, require_nccl(), comm_, {}};
+  host_wait_event(wait_ev_);
+}
+
+void DpGroup::host_wait_event(cudaEvent_t ev) {
+  require_alive("data-parallel wait");
+  if (world_ == 1) {
+    if (cudaEventSynchronize(ev) != cudaSuccess) fail(NRS_ERR_CUDA, "data parallel: event synchronisation failed");
+    return;
+  }
+  WaitState w{ev, require_nccl(), comm_, {}};
   double waited = 0.0;
   const int st = dp_watchdog_wait(poll_event_and_comm, &w, timeout_ms_, 20.0, &waited);
   if (st == NRS_OK) return;

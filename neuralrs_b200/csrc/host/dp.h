@@ -77,6 +77,7 @@ class DpGroup {
   // communicator for asynchronous errors; on an error or after the deadline the communicator is
   // aborted and every later call fails (NRS_ERR_NCCL / NRS_ERR_TIMEOUT).
   void host_wait(cudaStream_t stream);
+  void host_wait_event(cudaEvent_t ev);   // the same for an event the caller recorded earlier
   // All-reduce (sum) of `count` floats at `dev` across the group on the compute stream (small values:
   // the loss share, statistics).
   void all_reduce_sum(float* dev, size_t count);

@@ -37,6 +37,12 @@ struct nrs_trainer {
   std::shared_ptr<nrs::FlatStore> flat;
   std::unique_ptr<nrs::cuda::AdamW> opt;
   float* loss_dev = nullptr;
+  // Loss read-back one step behind (nrs_trainer_step_staged_lagged): pinned slots the stream copies each
+  // step's loss into, and the events that say a slot is filled.
+  float* loss_ring = nullptr;
+  cudaEvent_t loss_ready[2] = {nullptr, nullptr};
+  bool loss_pending[2] = {false, false};
+  int loss_slot = 0;
   // staging for host inputs (grow-only device buffers)
   float* x_dev = nullptr; size_t x_cap = 0;
   float* t_dev = nullptr; size_t t_cap = 0;
@@ -80,6 +86,11 @@ struct nrs_trainer {
       if (sl.labels) cudaFree(sl.labels);
     }
     if (aug_buf) cudaFree(aug_buf);
+    if (loss_ring) {
+      if (ctx) cudaStreamSynchronize(ctx->stream);   // a queued loss copy may still target the pinned slots
+      cudaFreeHost(loss_ring);
+      for (cudaEvent_t e : loss_ready) if (e) cudaEventDestroy(e);
+    }
     opt.reset();
     params.clear();
     buffers.clear();
@@ -559,6 +570,30 @@ void step_staged(nrs_trainer* t, float* loss_out) {
   if (loss_out) read_loss(t, loss_out);
 }
 
+// Issues the staged step, queues an asynchronous copy of its loss into a pinned slot, and hands back the loss of
+// the step BEFORE it (which has finished, or nearly): the host is never more than one step behind the device
+// and the device never waits for the host to enqueue.
+void step_staged_lagged(nrs_trainer* t, float* prev_loss_out, int* have_prev) {
+  if (!t->loss_ring) {
+    cuda_ok(cudaMallocHost((void**)&t->loss_ring, 2 * sizeof(float)), "pinned loss slots");
+    for (int i = 0; i < 2; ++i) cuda_ok(cudaEventCreateWithFlags(&t->loss_ready[i], cudaEventDisableTiming), "event creation");
+  }
+  step_staged(t, nullptr);
+  const int cur = t->loss_slot, prev = cur ^ 1;
+  cuda_ok(cudaMemcpyAsync(t->loss_ring + cur, t->loss_dev, sizeof(float), cudaMemcpyDeviceToHost, t->ctx->stream), "loss copy");
+  cuda_ok(cudaEventRecord(t->loss_ready[cur], t->ctx->stream), "event record");
+  t->loss_pending[cur] = true;
+  t->loss_slot = prev;
+  if (have_prev) *have_prev = 0;
+  if (t->loss_pending[prev]) {
+    if (t->dp && t->world > 1) t->dp->host_wait_event(t->loss_ready[prev]);
+    else cuda_ok(cudaEventSynchronize(t->loss_ready[prev]), "waiting for the previous step's loss");
+    t->loss_pending[prev] = false;
+    if (prev_loss_out) *prev_loss_out = t->loss_ring[prev];
+    if (have_prev) *have_prev = 1;
+  }
+}
+
 template <class F>
 int guarded(nrs_ctx* ctx, F&& f) {
   try {
@@ -859,6 +894,11 @@ int nrs_trainer_set_augment(nrs_trainer* t, int max_shift, int flip) {
 int nrs_trainer_step_staged(nrs_trainer* t, float* loss_out) {
   if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_step_staged: null handle");
   return guarded(t->ctx, [&] { step_staged(t, loss_out); });
+}
+
+int nrs_trainer_step_staged_lagged(nrs_trainer* t, float* prev_loss_out, int* have_prev) {
+  if (!t) return nrs_fail(nullptr, NRS_ERR_ARG, "nrs_trainer_step_staged_lagged: null handle");
+  return guarded(t->ctx, [&] { step_staged_lagged(t, prev_loss_out, have_prev); });
 }
 
 int nrs_trainer_step_device(nrs_trainer* t, const float* x_dev, const float* target_dev, int batch, float* loss_out) {

@@ -600,6 +600,15 @@ class Trainer:
             self._staged.pop(0)   # the step has run to completion: its host arrays may go
         return float(loss.value) if want_loss else None
 
+    def step_staged_lagged(self):
+        """A full training step on the oldest staged batch; returns the loss of the PREVIOUS lagged step (None on
+        the first call).  last_loss() gives the newest one."""
+        loss, have = C.c_float(), C.c_int()
+        check(self.ctx.h, self.ctx._l.nrs_trainer_step_staged_lagged(self.h, C.byref(loss), C.byref(have)))
+        if have.value and len(getattr(self, "_staged", None) or []) > 1:
+            self._staged.pop(0)   # the step before this one has run to completion: its host arrays may go
+        return float(loss.value) if have.value else None
+
     def step_device(self, x_dev_ptr: int, target_dev_ptr: int, batch: int, want_loss=False):
         loss = C.c_float()
         check(self.ctx.h, self.ctx._l.nrs_trainer_step_device(self.h, VP(x_dev_ptr), VP(target_dev_ptr), int(batch),

@@ -88,3 +88,50 @@ def test_trainer_indexed_labels_and_augmentation(gpu_ctx, oracle32):
     assert staged.step_staged() == plain.step(batches[0][0], batches[0][2])
     plain.close()
     staged.close()
+
+
+def test_lagged_loss_readback_returns_every_loss_one_step_late(gpu_ctx):
+    """nrs_trainer_step_staged_lagged issues step i and returns the loss of step i-1: the sequence of losses and the
+    final parameters are those of synchronous staged steps, bit for bit."""
+    cfg = dict(in_shape=(3, 16, 16), classes=10,
+               layers=[("conv", 3, 32, 3, 1, 1), ("relu",), ("maxpool", 2, 2), ("flatten",), ("linear", 2048, 10)])
+    hp = models.ADAMW_HP
+    params = models.he_init(cfg["layers"], 610)
+    rng = np.random.default_rng(611)
+    batches = []
+    for i in range(5):
+        x = rng.random((16,) + cfg["in_shape"], dtype=np.float32)
+        onehot = np.eye(10, dtype=np.float32)[rng.integers(0, 10, 16)]
+        batches.append((x, onehot))
+
+    def make():
+        tr = cuda.Trainer(cfg["layers"], cfg["in_shape"], cfg["classes"], hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
+                          hp["wd"], fuse=True, ctx=gpu_ctx)
+        tr.set_params(params)
+        return tr
+
+    sync, lag = make(), make()
+    want = []
+    sync.stage_next(*batches[0])
+    for i in range(5):
+        if i + 1 < 5:
+            sync.stage_next(*batches[i + 1])
+        want.append(sync.step_staged())
+    got = []
+    lag.stage_next(*batches[0])
+    for i in range(5):
+        if i + 1 < 5:
+            lag.stage_next(*batches[i + 1])
+        prev = lag.step_staged_lagged()
+        assert (prev is None) == (i == 0)
+        if prev is not None:
+            got.append(prev)
+    got.append(lag.last_loss())
+    assert got == want
+    for i in range(sync.n_params):
+        assert np.array_equal(lag.get_param(i), sync.get_param(i))
+    # a lagged step with nothing staged is refused like a synchronous one
+    with pytest.raises(Exception):
+        lag.step_staged_lagged()
+    sync.close()
+    lag.close()
