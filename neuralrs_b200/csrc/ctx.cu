@@ -71,8 +71,8 @@ int nrs_err_flag(nrs_ctx* ctx, int** out) {
 
 int nrs_fold_ticket(nrs_ctx* ctx, unsigned** out) {
   if (!ctx->fold_ticket) {
-    NRS_CUDA(ctx, cudaMalloc(&ctx->fold_ticket, sizeof(unsigned)));
-    NRS_CUDA(ctx, cudaMemsetAsync(ctx->fold_ticket, 0, sizeof(unsigned), ctx->stream));
+    NRS_CUDA(ctx, cudaMalloc(&ctx->fold_ticket, kNrsFoldTickets * sizeof(unsigned)));
+    NRS_CUDA(ctx, cudaMemsetAsync(ctx->fold_ticket, 0, kNrsFoldTickets * sizeof(unsigned), ctx->stream));
   }
   *out = ctx->fold_ticket;
   return NRS_OK;

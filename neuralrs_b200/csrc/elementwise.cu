@@ -104,7 +104,7 @@ bias_add_kernel(const float* __restrict__ a, const float* __restrict__ bias, flo
 // partial sums that a second pass folds in a fixed order (no atomics).
 __global__ void __launch_bounds__(256)
 colsum_kernel(const float* __restrict__ g, float* __restrict__ out, int rows, int cols, int row_splits,
-              int accumulate, float* __restrict__ partial) {
+              int accumulate, float* partial, unsigned* tickets) {
   NRS_PDL_PROLOGUE();
   __shared__ float sm[8][33];
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
@@ -124,6 +124,23 @@ colsum_kernel(const float* __restrict__ g, float* __restrict__ out, int rows, in
     if (row_splits > 1) partial[(size_t)split * cols + c] = t;
     else out[c] = accumulate ? out[c] + t : t;
   }
+  if (row_splits == 1 || !tickets) return;
+  // With a ticket per column block the second pass is folded in: the block of a column group that finishes
+  // last adds the group's partial rows in split order (a fixed order whichever block that is).
+  __shared__ bool last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(&tickets[blockIdx.x], 1u) == gridDim.y - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  if (wrp == 0 && c < cols) {
+    float t = 0.0f;
+#pragma unroll 4
+    for (int s = 0; s < row_splits; ++s) t += __ldcg(partial + (size_t)s * cols + c);
+    out[c] = accumulate ? out[c] + t : t;
+  }
+  if (threadIdx.x == 0) tickets[blockIdx.x] = 0;
 }
 __global__ void colsum_fold_kernel(const float* __restrict__ partial, float* __restrict__ out, int cols,
                                    int row_splits, int accumulate) {
@@ -285,9 +302,16 @@ int nrs_sum_axis0(nrs_ctx* ctx, const float* g, float* out, int rows, int cols, 
     if (st != NRS_OK) return st;
     partial = (float*)ws;
   }
-  NRS_PDL_LAUNCH(colsum_kernel, dim3(col_blocks, splits), 256, 0, ctx->stream, g, out, rows, cols, splits, accumulate, partial);
+  unsigned* tickets = nullptr;
+  if (splits > 1 && col_blocks + 1 <= kNrsFoldTickets) {
+    const int st = nrs_fold_ticket(ctx, &tickets);
+    if (st != NRS_OK) return st;
+    tickets += 1;   // slot 0 belongs to the single-counter users
+  }
+  NRS_PDL_LAUNCH(colsum_kernel, dim3(col_blocks, splits), 256, 0, ctx->stream, g, out, rows, cols, splits, accumulate, partial,
+                 tickets);
   NRS_LAUNCHED(ctx);
-  if (splits > 1) {
+  if (splits > 1 && !tickets) {
     NRS_PDL_LAUNCH(colsum_fold_kernel, nrs_blocks(cols, 256), 256, 0, ctx->stream, partial, out, cols, splits, accumulate);
     NRS_LAUNCHED(ctx);
   }
@@ -457,7 +481,8 @@ extern "C" int nrs_sum_axis0_static(nrs_ctx* ctx, const float* g, float* out, in
   }
   // Every partial the fold reads is written by the first kernel, so stale contents of the
   // shared scratch never need clearing.
-  NRS_PDL_LAUNCH(colsum_kernel, dim3(col_blocks, splits), 256, 0, ctx->stream, g, out, rows, cols, splits, accumulate, scratch);
+  NRS_PDL_LAUNCH(colsum_kernel, dim3(col_blocks, splits), 256, 0, ctx->stream, g, out, rows, cols, splits, accumulate, scratch,
+                 (unsigned*)nullptr);
   NRS_LAUNCHED(ctx);
   if (splits > 1) {
     NRS_PDL_LAUNCH(colsum_fold_kernel, nrs_blocks(cols, 256), 256, 0, ctx->stream, scratch, out, cols, splits, accumulate);

@@ -177,8 +177,10 @@ int nrs_workspace(nrs_ctx* ctx, size_t bytes, void** out);
 enum { NRS_WS_A_HI = 0, NRS_WS_A_LO = 1, NRS_WS_B_HI = 2, NRS_WS_B_LO = 3, NRS_WS_PARTIAL = 4, NRS_WS_WGRAD_PARTIAL = 5, NRS_WS_COUNT = 8 };
 int nrs_ws_slot(nrs_ctx* ctx, int slot, size_t bytes, void** out);
 int nrs_err_flag(nrs_ctx* ctx, int** out);
-// A zero-initialised device counter for "the last block to arrive folds the partials" reductions; the folding
-// block resets it, so consecutive launches on the context's stream can share it.
+// Zero-initialised device counters (kNrsFoldTickets of them) for "the last block to arrive folds the partials"
+// reductions; the folding block resets its counter, so consecutive launches on the context's stream can share
+// them.  Slot 0 serves kernels with one counter, slots 1.. kernels with a counter per column block.
+constexpr int kNrsFoldTickets = 4096;
 int nrs_fold_ticket(nrs_ctx* ctx, unsigned** out);
 // LayerNorm with the TF32 planes of its result written by the kernel (norm_softmax.cu).
 extern "C" int nrs_layernorm_fwd_planes(nrs_ctx* ctx, const float* a, const float* b, const float* gamma, const float* beta,
