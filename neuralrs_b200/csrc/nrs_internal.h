@@ -289,7 +289,9 @@ inline bool nrs_smem_attr_update(NrsSmemAttr& a, int device, size_t bytes) {
 // gradient issued right after the data gradient of the same layer: both read the same inputs) may then
 // skip the wait at its start, begin on the SMs its predecessor's last wave leaves idle, and wait just
 // before it exits instead, so that kernels after it still see everything before them complete.  Such a
-// kernel does not trigger (exiting does).
+// kernel triggers at once: its successor's own wait returns only when this kernel has completed, late wait
+// included, so the successor still sees everything before it.  Two such kernels are never adjacent: the
+// callers mark a launch independent only right after issuing the data gradient it may overlap.
 #define NRS_PDL_PROLOGUE() \
   do { NRS_PDL_WAIT(); NRS_PDL_TRIGGER(); } while (0)
 
