@@ -83,6 +83,92 @@ def test_sharded_gradients_sum_to_full_batch(world, tmp_path, nrs_lib):
         assert e1 == s0 and s0 < e0
 
 
+def _bn_rank(rank, world, port, out_dir):
+    """Batch normalisation with statistics shared across ranks, as the device library does it: per-channel sums
+    around a pivot every rank has (the running mean), summed across ranks together with the element count;
+    backward sums of g and g*xhat likewise before dx, the parameter gradients summed like any other gradient."""
+    sys.path.insert(0, str(ROOT))
+    import torch
+    import torch.distributed as dist
+    from neuralrs_b200 import cuda
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    rng = np.random.default_rng(7)                          # identical data on every rank; each keeps its shard
+    n, c, h, w = 11, 6, 5, 4
+    x = (rng.normal(size=(n, c, h, w)) * 2 + np.arange(c)[None, :, None, None]).astype(np.float32)
+    g = rng.normal(size=(n, c, h, w)).astype(np.float32)
+    gamma, beta = rng.normal(size=c).astype(np.float32), rng.normal(size=c).astype(np.float32)
+    running_mean = rng.normal(size=c).astype(np.float32)
+    b0, b1 = cuda.dp_shard_range(n, rank, world)
+    xs, gs = x[b0:b1].astype(np.float64), g[b0:b1].astype(np.float64)
+    k = running_mean.astype(np.float64)[None, :, None, None]
+    fwd = np.concatenate([(xs - k).sum(axis=(0, 2, 3)), ((xs - k) ** 2).sum(axis=(0, 2, 3)), [xs.size / c]])
+    ft = torch.from_numpy(fwd)
+    dist.all_reduce(ft)
+    s, q, count = fwd[:c], fwd[c:2 * c], fwd[2 * c]
+    mean = running_mean + s / count
+    var = np.maximum(q / count - (s / count) ** 2, 0.0)
+    istd = 1.0 / np.sqrt(var + 1e-5)
+    xhat = (xs - mean[None, :, None, None]) * istd[None, :, None, None]
+    local = np.concatenate([gs.sum(axis=(0, 2, 3)), (gs * xhat).sum(axis=(0, 2, 3))])   # dbeta, dgamma of this shard
+    shared = torch.from_numpy(local.copy())
+    dist.all_reduce(shared)
+    sg, sgx = shared.numpy()[:c], shared.numpy()[c:]
+    ga = gamma.astype(np.float64)[None, :, None, None]
+    dx = istd[None, :, None, None] * (gs * ga - ga * sg[None, :, None, None] / count -
+                                      xhat * ga * sgx[None, :, None, None] / count)
+    # dbeta / dgamma stay this shard's own sums: they are summed across ranks with every other parameter gradient
+    # (here: by the test, over the ranks' files)
+    np.save(os.path.join(out_dir, f"bn_{rank}.npy"), np.concatenate([mean, var, dx.ravel(), local]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_shared_batchnorm_statistics_equal_the_full_batch(world, tmp_path, nrs_lib):
+    import torch.multiprocessing as mp
+    from neuralrs_b200 import cuda
+    from oracle.nrs_oracle import Oracle
+    mp.spawn(_bn_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    o = Oracle("f64")
+    rng = np.random.default_rng(7)
+    n, c, h, w = 11, 6, 5, 4
+    x = (rng.normal(size=(n, c, h, w)) * 2 + np.arange(c)[None, :, None, None]).astype(np.float32)
+    g = rng.normal(size=(n, c, h, w)).astype(np.float32)
+    gamma, beta = rng.normal(size=c).astype(np.float32), rng.normal(size=c).astype(np.float32)
+    running_mean = rng.normal(size=c).astype(np.float32)
+    y, xhat, istd, rm, rv = o.batchnorm_fwd(x, gamma, beta, running_mean, np.ones(c, np.float32), 1e-5, 0.0, True)
+    dx, dgamma, dbeta = o.batchnorm_bwd(g, xhat, istd, gamma, True)
+    # momentum 0: the oracle's running statistics after the call ARE the batch statistics
+    dx_parts, dgamma_sum, dbeta_sum = [], np.zeros(c), np.zeros(c)
+    for r in range(world):
+        got = np.load(tmp_path / f"bn_{r}.npy")
+        b0, b1 = cuda.dp_shard_range(n, r, world)
+        m = (b1 - b0) * c * h * w
+        assert np.allclose(got[:c], rm, rtol=1e-5, atol=1e-6) and np.allclose(got[c:2 * c], rv, rtol=1e-4, atol=1e-6)
+        dx_parts.append(got[2 * c:2 * c + m].reshape(b1 - b0, c, h, w))
+        dbeta_sum += got[2 * c + m:2 * c + m + c]
+        dgamma_sum += got[2 * c + m + c:]
+    assert np.linalg.norm(np.concatenate(dx_parts) - dx) <= 1e-5 * np.linalg.norm(dx)
+    assert np.allclose(dgamma_sum, dgamma, rtol=1e-4, atol=1e-5) and np.allclose(dbeta_sum, dbeta, rtol=1e-4, atol=1e-5)
+
+
+def test_a_shard_draws_its_samples_part_of_the_global_mask(nrs_lib):
+    """Element i of a mask of `count` elements is word i%4 of counter block offset + i/4: a rank holding samples
+    [b0, b1) of the global batch that starts its draw at block offset + b0*per/4 reproduces its rows of the mask a
+    single process draws for the whole batch (what nrs_rng_window arranges on the device)."""
+    from neuralrs_b200 import cuda
+    from oracle.nrs_oracle import Oracle
+    o = Oracle("f32")
+    per, gb, seed, offset = 12, 10, 99, 5
+    full = o.dropout_mask(gb * per, 0.3, seed, offset).reshape(gb, per)
+    for world in (2, 3, 5):
+        for r in range(world):
+            b0, b1 = cuda.dp_shard_range(gb, r, world)
+            assert (b0 * per) % 4 == 0
+            part = o.dropout_mask((b1 - b0) * per, 0.3, seed, offset + b0 * per // 4).reshape(b1 - b0, per)
+            assert np.array_equal(part, full[b0:b1])
+
+
 def test_shard_ranges_and_bucket_plan(nrs_lib):
     from neuralrs_b200 import cuda
     for gb, world in [(1024, 8), (10, 4), (7, 8), (0, 2), (1, 1)]:
