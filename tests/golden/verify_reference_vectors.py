@@ -6,7 +6,7 @@ import re
 import sys
 from pathlib import Path
 
-EXPECT_KEYS = ("y", "gx", "gw", "running_mean", "first_row")
+EXPECT_KEYS = ("y", "gx", "gw", "gb", "right", "running_mean", "first_row")
 
 
 def literals(text):

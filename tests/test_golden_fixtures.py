@@ -60,6 +60,21 @@ def test_oracle_reproduces_the_reference_vectors(case, oracle32, oracle64):
             pe = o.positional_table(case["rows"], case["d_model"])
             assert np.abs(pe[0] - np.asarray(case["first_row"])).max() < 1e-5
             assert abs(pe[1, 0] - np.sin(case["row1_dim0_is_sin_of"])) < case["tolerance"]
+        elif op == "matmul":
+            assert o.matmul_fwd(_arr(case, "a"), _arr(case, "b")).ravel().tolist() == [float(v) for v in case["y"]]
+        elif op == "linear":
+            x = _arr(case, "x")
+            y = o.bias_add_fwd(o.matmul_fwd(x, _arr(case, "w")), np.asarray(case["b"], np.float32))
+            assert y.ravel().tolist() == [float(v) for v in case["y"]]
+            _, gb = o.bias_add_bwd(np.asarray(case["gy"], np.float32).reshape(y.shape))
+            assert gb.ravel().tolist() == [float(v) for v in case["gb"]]
+        elif op == "slice_cols":
+            x = _arr(case, "x")
+            assert o.slice_cols_fwd(x, case["c0"], case["c1"]).ravel().tolist() == [float(v) for v in case["y"]]
+            assert o.slice_cols_fwd(x, case["c1"], case["c2"]).ravel().tolist() == [float(v) for v in case["right"]]
+        elif op == "relu_bwd":
+            gx = o.relu_bwd(np.asarray(case["x"], np.float32), np.asarray(case["gy"], np.float32))
+            assert gx.ravel().tolist() == [float(v) for v in case["gx"]]
         else:
             raise AssertionError(f"unknown op {op}")
 
@@ -93,12 +108,34 @@ def test_oracle_still_reproduces_the_seeded_fixtures(oracle64):
 
 # ---------------------------------------------------------------------------------------------- GPU: the device
 
+_DEVICE_OPS = ("conv2d_fwd", "maxpool", "matmul", "linear", "relu_bwd")
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("case", [c for c in CASES if c["op"] in ("conv2d_fwd", "maxpool")],
-                         ids=[c["source"] for c in CASES if c["op"] in ("conv2d_fwd", "maxpool")])
+@pytest.mark.parametrize("case", [c for c in CASES if c["op"] in _DEVICE_OPS],
+                         ids=[c["source"] for c in CASES if c["op"] in _DEVICE_OPS])
 def test_device_reproduces_the_reference_vectors(case, gpu_ctx):
     from .gpu_util import Dev, call
-    if case["op"] == "conv2d_fwd":
+    if case["op"] == "matmul":
+        a, b = _arr(case, "a"), _arr(case, "b")
+        c = Dev(gpu_ctx, shape=(a.shape[0], b.shape[1]))
+        call(gpu_ctx, "nrs_gemm", 0, 0, a.shape[0], b.shape[1], a.shape[1], Dev(gpu_ctx, a), Dev(gpu_ctx, b), c, None, 0, F(0))
+        assert c.get().ravel().tolist() == [float(v) for v in case["y"]]
+    elif case["op"] == "linear":
+        x, w = _arr(case, "x"), _arr(case, "w")
+        y = Dev(gpu_ctx, shape=(x.shape[0], w.shape[1]))
+        call(gpu_ctx, "nrs_gemm", 0, 0, x.shape[0], w.shape[1], x.shape[1], Dev(gpu_ctx, x), Dev(gpu_ctx, w), y,
+             Dev(gpu_ctx, np.asarray(case["b"], np.float32)), 0, F(0))
+        assert y.get().ravel().tolist() == [float(v) for v in case["y"]]
+        gb = Dev(gpu_ctx, shape=(w.shape[1],))
+        call(gpu_ctx, "nrs_sum_axis0", Dev(gpu_ctx, np.asarray(case["gy"], np.float32)), gb, x.shape[0], w.shape[1], 0)
+        assert gb.get().ravel().tolist() == [float(v) for v in case["gb"]]
+    elif case["op"] == "relu_bwd":
+        gx = Dev(gpu_ctx, shape=(len(case["x"]),))
+        call(gpu_ctx, "nrs_relu_bwd", Dev(gpu_ctx, np.asarray(case["x"], np.float32)), Dev(gpu_ctx, np.asarray(case["gy"], np.float32)),
+             gx, C.c_size_t(len(case["x"])), 0)
+        assert gx.get().ravel().tolist() == [float(v) for v in case["gx"]]
+    elif case["op"] == "conv2d_fwd":
         x, w = _arr(case, "x"), _arr(case, "w")
         n, ci, h, wd = x.shape
         co, _, kh, kw = w.shape
