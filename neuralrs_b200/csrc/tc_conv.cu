@@ -240,7 +240,11 @@ int conv_common(nrs_ctx* ctx, const ConvPlan& p) {
     if (st != NRS_OK) return st;
   }
 
-  const int bn = p.n_ch_out % 128 == 0 ? 128 : (p.n_ch_out % 64 == 0 ? 64 : 32);
+  int bn = p.n_ch_out % 128 == 0 ? 128 : (p.n_ch_out % 64 == 0 ? 64 : 32);
+  // Few tiles (small batches): 64-column tiles before a K-split, whose second pass costs more than the narrower
+  // tile loses and cannot produce the per-tile channel sums — taken while 128-wide tiles would leave more than a
+  // third of the SMs without one.
+  if (bn == 128 && (long)tiles_m * (p.n_ch_out / 128) * 3 < 2L * ctx->sm_count) bn = 64;
   if (extras != ctx->out_extras.end()) ctx->out_extras.erase(extras);   // honoured from here on
   int splits = 0;
 #define NRS_RUN(BN_)                                                                                                     \
