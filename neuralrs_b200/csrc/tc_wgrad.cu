@@ -45,6 +45,7 @@ struct WgradParams {
   int group_cols;                 // taps_per_group * ci (1x1 with more than 256 input channels: 256)
   int col_blocks;                 // 1x1 only: column blocks of 256 input channels, each its own CTA
   int independent;                // reads nothing the kernel launched just before it wrote (NRS_PDL_PROLOGUE)
+  float* direct;                  // 1x1, one split, no accumulation: the tile is the result; written straight to dw[co][ci]
 };
 
 template <int NPLANES, int STAGES>
@@ -177,8 +178,9 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy_hi, const __grid_const
       tc::tc_fence_after_sync();
       const int row = q * 32 + lane;
       const int live_cols = p.col_blocks > 1 ? cblocks * 32 : ntaps * p.ci;
-      float* dst = p.partial +
-                   (((((size_t)split * p.m_blocks + mb) * p.n_groups + grp) * p.col_blocks + cbk) * 128 + row) * p.group_cols;
+      float* dst = p.direct ? p.direct + (size_t)(mb * 128 + row) * p.ci + (size_t)cbk * 256
+                            : p.partial + (((((size_t)split * p.m_blocks + mb) * p.n_groups + grp) * p.col_blocks + cbk) * 128 + row) *
+                                              p.group_cols;
       const bool row_live = mb * 128 + row < p.co;
 #pragma unroll 1
       for (int c = 0; c < (live_cols + 31) / 32; ++c) {
@@ -385,6 +387,8 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   else { maps[1] = maps[0]; maps[3] = maps[2]; }
   NRS_REQUIRE(ctx, ok, NRS_ERR_CUDA, "tc_wgrad: cuTensorMapEncodeTiled failed");
   p.independent = may_overlap ? 1 : 0;
+  // a single split of a 1x1 "convolution" (A^T B) that overwrites its output needs no second pass
+  p.direct = (splits == 1 && taps == 1 && !accumulate && (reinterpret_cast<uintptr_t>(dw) & 15) == 0) ? dw : nullptr;
 
 #define NRS_WG(PL)                                                                     \
   switch (stages) {                                                                    \
@@ -397,6 +401,7 @@ int nrs_tc_conv_wgrad(nrs_ctx* ctx, const float* x, const float* dy, float* dw, 
   if (split3) { NRS_WG(2) } else { NRS_WG(1) }
 #undef NRS_WG
   if (st != NRS_OK) return st;
+  if (p.direct) return NRS_OK;
   const size_t total = (size_t)co * ci * taps;
   const int lanes = reduce_lanes(splits);
   NRS_PDL_LAUNCH(tc_wgrad_reduce_kernel, nrs_blocks(total / 4, kReduceThreads / lanes), kReduceThreads, 0, ctx->stream, p, splits, lanes, dw,
