@@ -47,7 +47,8 @@ __device__ __forceinline__ void st4_stream(float* p, float4 v) { __stcs(reinterp
 
 // ------------------------------------------------------------------ LayerNorm forward
 // x = a (+ b when given: the residual add folded in); y = gamma * xhat + beta.
-template <int VPL>
+// EMIT: also write the TF32 planes of y (a separate instantiation, so that the plain kernel keeps its registers).
+template <int VPL, bool EMIT>
 __global__ void __launch_bounds__(kRowThreads)
 ln_fwd_vec_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ gamma,
                   const float* __restrict__ beta, float* __restrict__ y, float* __restrict__ xhat,
@@ -95,7 +96,7 @@ ln_fwd_vec_kernel(const float* __restrict__ a, const float* __restrict__ b, cons
         if (xhat) st4_stream(xhat + base + 4 * c, xn);
         const float4 out = make_float4(gm.x * xn.x + bt.x, gm.y * xn.y + bt.y, gm.z * xn.z + bt.z, gm.w * xn.w + bt.w);
         st4_stream(y + base + 4 * c, out);
-        if (y_hi) put_planes(y_hi, y_lo, base + 4 * c, out);
+        if (EMIT) put_planes(y_hi, y_lo, base + 4 * c, out);
       }
     }
   }
@@ -130,7 +131,7 @@ ln_fwd_kernel(const float* __restrict__ a, const float* __restrict__ b, const fl
 // dx (+)= istd * (g*gamma - mean(g*gamma) - xhat * mean(g*gamma*xhat)), optionally also into dx2 (the
 // second addend of a fused residual add receives the same gradient); per-block column partials of
 // dgamma = sum_r g*xhat and dbeta = sum_r g into partial[block][2][f] when `partial` is given.
-template <int VPL>
+template <int VPL, bool EMIT>
 __global__ void __launch_bounds__(kRowThreads)
 ln_bwd_vec_kernel(const float* __restrict__ g, const float* __restrict__ xhat, const float* __restrict__ istd,
                   const float* __restrict__ gamma, float* dx, float* dx2, float* __restrict__ partial, int rows, int f,
@@ -178,7 +179,7 @@ ln_bwd_vec_kernel(const float* __restrict__ g, const float* __restrict__ xhat, c
           float4 o;
           o.x = is * (gv[k].x - s1 - xh[k].x * s2); o.y = is * (gv[k].y - s1 - xh[k].y * s2);
           o.z = is * (gv[k].z - s1 - xh[k].z * s2); o.w = is * (gv[k].w - s1 - xh[k].w * s2);
-          if (d_hi) put_planes(d_hi, d_lo, base + 4 * c, o);   // planes of the gradient itself (before any accumulation)
+          if (EMIT) put_planes(d_hi, d_lo, base + 4 * c, o);   // planes of the gradient itself (before any accumulation)
           float4 w = o;
           if (acc1) { const float4 old = ld4(dx + base + 4 * c); w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w; }
           st4(dx + base + 4 * c, w);
@@ -430,8 +431,12 @@ int layernorm_fwd(nrs_ctx* ctx, const char* who, const float* a, const float* b,
   NRS_REQUIRE(ctx, a && gamma && beta && y, NRS_ERR_ARG, "%s: null tensor", who);
   const int vpl = vec_vpl(f, {a, b, gamma, beta, y, xhat, y_hi, y_lo});
   if (vpl) {
-    NRS_DISPATCH_VPL(vpl, NRS_PDL_LAUNCH(ln_fwd_vec_kernel<V>, row_grid(ctx, rows), kRowThreads, 0, ctx->stream, a, b, gamma, beta, y,
-                                         xhat, istd, rows, f, eps, y_hi, y_lo));
+    if (y_hi)
+      NRS_DISPATCH_VPL(vpl, NRS_PDL_LAUNCH((ln_fwd_vec_kernel<V, true>), row_grid(ctx, rows), kRowThreads, 0, ctx->stream, a, b, gamma,
+                                           beta, y, xhat, istd, rows, f, eps, y_hi, y_lo));
+    else
+      NRS_DISPATCH_VPL(vpl, NRS_PDL_LAUNCH((ln_fwd_vec_kernel<V, false>), row_grid(ctx, rows), kRowThreads, 0, ctx->stream, a, b, gamma,
+                                           beta, y, xhat, istd, rows, f, eps, y_hi, y_lo));
     if (emitted && y_hi) *emitted = 1;
   } else {
     NRS_PDL_LAUNCH(ln_fwd_kernel, row_grid(ctx, rows), kRowThreads, 0, ctx->stream, a, b, gamma, beta, y, xhat, istd, rows, f, eps);
@@ -471,8 +476,12 @@ int layernorm_bwd(nrs_ctx* ctx, const char* who, const float* g, const float* xh
       partial = (float*)ws;
     }
     const size_t smem = dgamma ? (size_t)warps * 2 * f * sizeof(float) : 0;
-    NRS_DISPATCH_VPL(vpl, NRS_PDL_LAUNCH(ln_bwd_vec_kernel<V>, blocks, warps * 32, smem, ctx->stream, g, xhat, istd, gamma, dx, dx2,
-                                         partial, rows, f, acc1, acc2, dx ? d_hi : nullptr, dx ? d_lo : nullptr));
+    if (dx && d_hi)
+      NRS_DISPATCH_VPL(vpl, NRS_PDL_LAUNCH((ln_bwd_vec_kernel<V, true>), blocks, warps * 32, smem, ctx->stream, g, xhat, istd, gamma, dx,
+                                           dx2, partial, rows, f, acc1, acc2, d_hi, d_lo));
+    else
+      NRS_DISPATCH_VPL(vpl, NRS_PDL_LAUNCH((ln_bwd_vec_kernel<V, false>), blocks, warps * 32, smem, ctx->stream, g, xhat, istd, gamma, dx,
+                                           dx2, partial, rows, f, acc1, acc2, (float*)nullptr, (float*)nullptr));
     if (emitted && dx && d_hi) *emitted = 1;
     NRS_LAUNCHED(ctx);
     if (dgamma) {
